@@ -1,0 +1,193 @@
+// CUDA-core skinny GEMM ("GEMV") family: y[n, N] = x[n, K] * W[N, K]^T for a handful of rows.
+//
+// This is the exact arm of every projection: fp32 accumulation in a fixed order that does not
+// depend on how many rows share the launch (row i's bits are the same for n = 1 and n = 64), which
+// is the batch-invariance the rows step relies on.  The tensor-core arm (k_umma_*.cu) covers the
+// same shapes with tcgen05; this file is also the fallback for shapes it does not take.
+//
+// Weight formats: MXFP8 (E4M3, one UE8M0 scale per row per 32 K) and MXFP4 (packed E2M1, same
+// scales), both with scales in the prepared 128x4-atom order (codecs.h sf_offset); plain bf16.
+// Activations: per-32 FP8 (codes + row-major scales) or bf16.
+//
+// Reference behaviour: kernels/opt_gemv_sm121.cu:418-435,732-740 (decode MXFP8 GEMV, rows variants),
+// kernels/b12x_bf16a_mxfp8w_dense_sm121.cu (bf16 activations on FP8 weights), kernels/q4e_gemv_sm121.cuh.
+#include "k_common.cuh"
+
+namespace sfb {
+
+constexpr int GV_THREADS = 256;
+constexpr int GV_WARPS = 8;
+constexpr int GV_RPW = 2;                    // output rows per warp, loaded together
+constexpr int GV_ROWS = GV_WARPS * GV_RPW;   // output rows per block
+
+struct GemvArgs {
+  const uint8_t* w;        // payload, row-major [groups*N, row_bytes]
+  const uint8_t* sf;       // prepared scales for the whole [groups*N, K] matrix (null for bf16 weights)
+  int64_t row_bytes;
+  int N;                   // output rows per group
+  int K;                   // reduction length per group
+  int KB;                  // K/32
+  int groups;              // blockIdx.y; group g reads activation columns [g*K, (g+1)*K)
+  int n;                   // activation rows
+  // activations
+  const uint8_t* xq;       // fp8 codes [n, x_stride] or null
+  const uint8_t* xs;       // scales [n, x_stride/32]
+  const __nv_bfloat16* xb; // bf16 [n, x_stride] or null
+  const float* xf;         // fp32 [n, x_stride] or null
+  int64_t x_stride;        // elements per activation row
+  int x_quant;             // quantise bf16/fp32 activations per 32 to FP8 while loading (W8A8 semantics)
+  // outputs [n, out_stride], column = group*N + row
+  __nv_bfloat16* out_b;
+  float* out_f;
+  int64_t out_stride;
+};
+
+template <int R>
+__device__ __forceinline__ void load_x(const GemvArgs& a, int r0, int kcol0, float* xs_sm) {
+  // xs_sm[r][k] for r < R, k < K (zero rows past n)
+  for (int idx = threadIdx.x; idx < R * a.K; idx += GV_THREADS) {
+    const int r = idx / a.K, k = idx - r * a.K;
+    const int row = r0 + r;
+    float v = 0.f;
+    if (row < a.n) {
+      const int64_t off = (int64_t)row * a.x_stride + kcol0 + k;
+      if (a.xq) {
+        v = e4m3_to_f32(a.xq[off]) * ue8m0_to_f32(a.xs[(int64_t)row * (a.x_stride / 32) + (kcol0 + k) / 32]);
+      } else if (a.xb) {
+        v = bf16_to_f(a.xb[off]);
+      } else {
+        v = a.xf[off];
+      }
+    }
+    if (a.x_quant) {  // per-32 FP8 round trip on the fly (K % 32 == 0, so a warp holds one aligned group)
+      float amax = warp_max(fabsf(v));
+      const uint8_t sc = act_scale_code_fp8(amax);
+      const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+      v = e4m3_to_f32(enc_e4m3(v * inv)) * ue8m0_to_f32(sc);
+    }
+    xs_sm[r * sm_pad(a.K) + sm_pad(k)] = v;
+  }
+}
+
+// WF: 0 = fp8 weights, 1 = fp4 weights, 2 = bf16 weights
+template <int WF, int R>
+__global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
+  extern __shared__ float xs_sm[];
+  const int g = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * GV_ROWS + warp * GV_RPW;
+  constexpr int EPC = WF == 0 ? 16 : (WF == 1 ? 32 : 8);  // elements per 16-byte chunk
+  const int chunks = a.K / EPC;
+
+  for (int r0 = 0; r0 < a.n; r0 += R) {
+    __syncthreads();
+    load_x<R>(a, r0, g * a.K, xs_sm);
+    __syncthreads();
+    float acc[GV_RPW][R];
+#pragma unroll
+    for (int i = 0; i < GV_RPW; ++i)
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[i][r] = 0.f;
+
+    if (row0 < a.N) {
+      const int64_t grow0 = (int64_t)g * a.N + row0;
+      for (int c = lane; c < chunks; c += 32) {
+        uint4 wv[GV_RPW];
+        float sc[GV_RPW];
+#pragma unroll
+        for (int i = 0; i < GV_RPW; ++i) {
+          const bool ok = row0 + i < a.N;
+          const int64_t gr = ok ? grow0 + i : grow0;
+          wv[i] = ldg_nc(a.w + gr * a.row_bytes + (int64_t)c * 16);
+          if (WF == 2) sc[i] = ok ? 1.f : 0.f;
+          else {
+            const int kb = (c * EPC) >> 5;
+            sc[i] = ok ? ue8m0_to_f32(__ldg(a.sf + sf_offset(gr, kb, a.KB))) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < GV_RPW; ++i) {
+          float f[EPC];
+          if (WF == 0) decode16_e4m3(wv[i], f);
+          else if (WF == 1) decode32_e2m1(wv[i], f);
+          else {
+            const uint32_t* p = reinterpret_cast<const uint32_t*>(&wv[i]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { f[2 * j] = __uint_as_float(p[j] << 16); f[2 * j + 1] = __uint_as_float(p[j] & 0xffff0000u); }
+          }
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const float4* xp = reinterpret_cast<const float4*>(xs_sm + r * sm_pad(a.K) + sm_pad(c * EPC));
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < EPC / 4; ++j) {
+              float4 xv = xp[j];
+              s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
+              s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+            }
+            acc[i][r] = fmaf(s, sc[i], acc[i][r]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < GV_RPW; ++i)
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float v = warp_sum(acc[i][r]);
+        const int orow = row0 + i, arow = r0 + r;
+        if (lane == 0 && orow < a.N && arow < a.n) {
+          const int64_t o = (int64_t)arow * a.out_stride + (int64_t)g * a.N + orow;
+          if (a.out_b) a.out_b[o] = __float2bfloat16_rn(v);
+          if (a.out_f) a.out_f[o] = v;
+        }
+      }
+  }
+}
+
+template <int WF>
+static int launch_gemv(const GemvArgs& a, cudaStream_t stream) {
+  const int64_t smem1 = (int64_t)sm_pad(a.K) * 4;
+  int R = 1;
+  if (a.n >= 4 && smem1 * 4 <= 96 * 1024) R = 4;
+  else if (a.n >= 2 && smem1 * 2 <= 96 * 1024) R = 2;
+  if (smem1 > 96 * 1024) return (int)cudaErrorInvalidValue;
+  dim3 grid((a.N + GV_ROWS - 1) / GV_ROWS, a.groups);
+  const size_t smem = (size_t)smem1 * R;
+#define SFB_GV(RR)                                                                                   \
+  {                                                                                                  \
+    static bool attr_done = false;                                                                   \
+    if (!attr_done) {                                                                                \
+      cudaFuncSetAttribute(gemv_kernel<WF, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
+      attr_done = true;                                                                              \
+    }                                                                                                \
+    gemv_kernel<WF, RR><<<grid, GV_THREADS, smem, stream>>>(a);                                       \
+  }
+  if (R == 4) SFB_GV(4) else if (R == 2) SFB_GV(2) else SFB_GV(1)
+#undef SFB_GV
+  return SFB_CHECK_LAUNCH();
+}
+
+}  // namespace sfb
+
+using namespace sfb;
+
+extern "C" {
+
+// wfmt: 0 fp8, 1 fp4, 2 bf16.  Exactly one of xq / xb / xf is non-null; one or both outputs.
+int sfb_gemv(int wfmt, const void* w, const void* sf, int64_t row_bytes, int N, int K, int groups, int n,
+             const void* xq, const void* xs, const void* xb, const void* xf, int64_t x_stride, int x_quant,
+             void* out_b, void* out_f, int64_t out_stride, cudaStream_t stream) {
+  const int epc = wfmt == 0 ? 16 : (wfmt == 1 ? 32 : 8);
+  if (K % 32 || K % epc || n <= 0 || (wfmt != 2 && sf == nullptr)) return (int)cudaErrorInvalidValue;
+  GemvArgs a{};
+  a.w = (const uint8_t*)w; a.sf = (const uint8_t*)sf; a.row_bytes = row_bytes; a.N = N; a.K = K;
+  a.KB = K / 32; a.groups = groups; a.n = n; a.xq = (const uint8_t*)xq; a.xs = (const uint8_t*)xs;
+  a.xb = (const __nv_bfloat16*)xb; a.xf = (const float*)xf; a.x_stride = x_stride; a.x_quant = x_quant;
+  a.out_b = (__nv_bfloat16*)out_b; a.out_f = (float*)out_f; a.out_stride = out_stride;
+  if (wfmt == 0) return launch_gemv<0>(a, stream);
+  if (wfmt == 1) return launch_gemv<1>(a, stream);
+  return launch_gemv<2>(a, stream);
+}
+
+}  // extern "C"

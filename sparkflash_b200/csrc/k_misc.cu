@@ -1,0 +1,214 @@
+// Embedding gather, stateless Gumbel-max sampling, taps for the drafter and synthetic weight fill.
+//
+// Reference behaviour: kernels/opt_rows_sm121.cu embed_own:2564 / argmax_fold:1810 / argmax_pick:1834,
+// kernels/opt_sample_sm121.cuh (noise keyed on seed, position, token id),
+// crates/sparkflash-model-deepseek-v41/src/synthetic.rs (weights from a hash of name and seed).
+#include "k_common.cuh"
+
+namespace sfb {
+
+// h[row, c, :] = embed[token[row], :] for every hc copy
+__global__ void embed_kernel(const __nv_bfloat16* embed, const int* tokens, __nv_bfloat16* h, int n, int hc,
+                             int d, int vocab, Status* st) {
+  const int row = blockIdx.y;
+  int tok = tokens[row];
+  if (tok < 0 || tok >= vocab) { if (threadIdx.x == 0 && blockIdx.x == 0) status_set(st, ST_BOUNDS, 3, tok, vocab); tok = 0; }
+  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (col >= d) return;
+  const uint4 v = *reinterpret_cast<const uint4*>(embed + (size_t)tok * d + col);
+  for (int c = 0; c < hc; ++c) *reinterpret_cast<uint4*>(h + ((size_t)row * hc + c) * d + col) = v;
+}
+
+// tap[row, :] = bf16(mean over copies of h[row, c, :])
+__global__ void tap_mean_kernel(const __nv_bfloat16* h, __nv_bfloat16* tap, int64_t tap_stride, int hc, int d) {
+  const int row = blockIdx.y;
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= d) return;
+  float s = 0.f;
+  for (int c = 0; c < hc; ++c) s += bf16_to_f(h[((size_t)row * hc + c) * d + col]);
+  tap[(size_t)row * tap_stride + col] = __float2bfloat16_rn(s / (float)hc);
+}
+
+__device__ __forceinline__ float gumbel(uint64_t base, int id) {
+  const uint64_t h = splitmix64(base ^ ((uint64_t)id * 0x9E3779B97F4A7C15ull));
+  const double u = ((double)(h >> 40) + 0.5) * (1.0 / 16777216.0);
+  return (float)(-log(-log(u)));
+}
+
+struct SampleArgs {
+  const float* logits;    // [n, V] this rank's vocabulary slice
+  int64_t stride;
+  const int* row_pos;     // sampling position = row_pos + 1 (the position the new token will occupy)
+  const float* temperature;  // [n]
+  const uint64_t* seed;      // [n]
+  const uint8_t* mask;    // optional [n, mask_stride] allowed-token bytes (constrained decoding), 0 = banned
+  int64_t mask_stride;
+  float* best_val;        // [n]
+  int* best_id;           // [n] global token id
+  int V, vocab_offset;
+};
+
+__global__ void __launch_bounds__(1024) sample_kernel(SampleArgs a) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int row = blockIdx.x;
+  const float T = a.temperature[row];
+  const bool greedy = T < 1e-5f;
+  const uint64_t base = splitmix64(a.seed[row] ^ splitmix64((uint64_t)(a.row_pos[row] + 1)));
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < a.V; i += 1024) {
+    const int id = a.vocab_offset + i;
+    if (a.mask && a.mask[(size_t)row * a.mask_stride + id] == 0) continue;
+    float v = a.logits[(size_t)row * a.stride + i];
+    if (!greedy) v = v / T + gumbel(base, id);
+    if (v > bv || (v == bv && id < bi)) { bv = v; bi = id; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 32; ++w)
+      if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    a.best_val[row] = bv;
+    a.best_id[row] = bi;
+  }
+}
+
+// Fold W ranks' (value, id) winners: larger value wins, ties to the lower id.
+__global__ void sample_fold_kernel(const float* vals, const int* ids, int W, int n, int* out_tokens) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n) return;
+  float bv = vals[row];
+  int bi = ids[row];
+  for (int r = 1; r < W; ++r) {
+    float v = vals[(size_t)r * n + row];
+    int id = ids[(size_t)r * n + row];
+    if (v > bv || (v == bv && id < bi)) { bv = v; bi = id; }
+  }
+  out_tokens[row] = bi;
+}
+
+// ---- synthetic weights: bytes from a hash of (tensor seed, element index) ----------------------------------
+// fp8: E4M3 codes of ~N(0, sigma) values pre-divided by the block scale 2^(scale_code-127).
+__global__ void synth_fp8_kernel(uint8_t* q, int64_t count, uint64_t seed, float sigma_over_scale) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i * 4 >= count) return;
+  uint64_t h = splitmix64(seed ^ (uint64_t)i);
+  // four values per hash: each from the sum of four 4-bit uniforms (approximately normal)
+  uint32_t packed = 0;
+  for (int j = 0; j < 4; ++j) {
+    uint32_t bits = (uint32_t)(h >> (16 * j)) & 0xffffu;
+    float s = (float)((bits & 15) + ((bits >> 4) & 15) + ((bits >> 8) & 15) + ((bits >> 12) & 15)) - 30.f;
+    float v = s * (1.f / 9.2195f) * sigma_over_scale;  // var of the sum = 4 * (255/12) = 85 -> std 9.2195
+    packed |= (uint32_t)enc_e4m3(v) << (8 * j);
+  }
+  if (i * 4 + 3 < count) *reinterpret_cast<uint32_t*>(q + i * 4) = packed;
+  else for (int j = 0; i * 4 + j < count; ++j) q[i * 4 + j] = (uint8_t)(packed >> (8 * j));
+}
+
+// fp4: packed E2M1 codes of ~N(0, sigma)/scale values, 8 per 32-bit word
+__global__ void synth_fp4_kernel(uint32_t* q, int64_t words, uint64_t seed, float sigma_over_scale) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= words) return;
+  uint64_t h0 = splitmix64(seed ^ (uint64_t)(2 * i)), h1 = splitmix64(seed ^ (uint64_t)(2 * i + 1));
+  uint32_t packed = 0;
+  for (int j = 0; j < 8; ++j) {
+    uint32_t bits = (uint32_t)((j < 4 ? h0 : h1) >> (16 * (j & 3))) & 0xffffu;
+    float s = (float)((bits & 15) + ((bits >> 4) & 15) + ((bits >> 8) & 15) + ((bits >> 12) & 15)) - 30.f;
+    float v = s * (1.f / 9.2195f) * sigma_over_scale;
+    packed |= (uint32_t)f32_to_e2m1(v) << (4 * j);
+  }
+  q[i] = packed;
+}
+
+__global__ void synth_bf16_kernel(__nv_bfloat16* w, int64_t count, uint64_t seed, float sigma, float mean) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  uint64_t h = splitmix64(seed ^ (uint64_t)i);
+  uint32_t bits = (uint32_t)h;
+  float s = 0.f;
+  for (int j = 0; j < 8; ++j) s += (float)((bits >> (4 * j)) & 15);
+  w[i] = __float2bfloat16_rn(mean + (s - 60.f) * (1.f / 13.038f) * sigma);  // std of sum of 8 = 13.038
+}
+
+__global__ void synth_f32_kernel(float* w, int64_t count, uint64_t seed, float sigma, float mean) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  uint64_t h = splitmix64(seed ^ (uint64_t)i);
+  uint32_t bits = (uint32_t)h;
+  float s = 0.f;
+  for (int j = 0; j < 8; ++j) s += (float)((bits >> (4 * j)) & 15);
+  w[i] = mean + (s - 60.f) * (1.f / 13.038f) * sigma;
+}
+
+}  // namespace sfb
+
+using namespace sfb;
+
+extern "C" {
+
+int sfb_embed(const void* embed, const int* tokens, void* h, int n, int hc, int d, int vocab, void* status,
+              cudaStream_t stream) {
+  if (d % 8) return (int)cudaErrorInvalidValue;
+  embed_kernel<<<dim3((d / 8 + 127) / 128, n), 128, 0, stream>>>((const __nv_bfloat16*)embed, tokens,
+                                                               (__nv_bfloat16*)h, n, hc, d, vocab, (Status*)status);
+  return SFB_CHECK_LAUNCH();
+}
+
+int sfb_tap_mean(const void* h, void* tap, int64_t tap_stride, int n, int hc, int d, cudaStream_t stream) {
+  tap_mean_kernel<<<dim3((d + 255) / 256, n), 256, 0, stream>>>((const __nv_bfloat16*)h, (__nv_bfloat16*)tap,
+                                                               tap_stride, hc, d);
+  return SFB_CHECK_LAUNCH();
+}
+
+int sfb_sample(const float* logits, int64_t stride, const int* row_pos, const float* temperature,
+               const void* seed, const void* mask, int64_t mask_stride, float* best_val, int* best_id, int n,
+               int V, int vocab_offset, cudaStream_t stream) {
+  SampleArgs a{logits, stride, row_pos, temperature, (const uint64_t*)seed, (const uint8_t*)mask, mask_stride,
+               best_val, best_id, V, vocab_offset};
+  sample_kernel<<<n, 1024, 0, stream>>>(a);
+  return SFB_CHECK_LAUNCH();
+}
+
+int sfb_sample_fold(const float* vals, const int* ids, int W, int n, int* out_tokens, cudaStream_t stream) {
+  sample_fold_kernel<<<(n + 63) / 64, 64, 0, stream>>>(vals, ids, W, n, out_tokens);
+  return SFB_CHECK_LAUNCH();
+}
+
+// kind: 0 fp8 bytes, 1 fp4 bytes (count = bytes), 2 bf16 elements, 3 f32 elements
+int sfb_synth_fill(int kind, void* dst, int64_t count, uint64_t seed, float sigma, float mean,
+                   cudaStream_t stream) {
+  const int T = 256;
+  if (kind == 0) {
+    int64_t thr = (count + 3) / 4;
+    synth_fp8_kernel<<<(unsigned)((thr + T - 1) / T), T, 0, stream>>>((uint8_t*)dst, count, seed, sigma);
+  } else if (kind == 1) {
+    if (count % 4) return (int)cudaErrorInvalidValue;
+    int64_t words = count / 4;
+    synth_fp4_kernel<<<(unsigned)((words + T - 1) / T), T, 0, stream>>>((uint32_t*)dst, words, seed, sigma);
+  } else if (kind == 2) {
+    synth_bf16_kernel<<<(unsigned)((count + T - 1) / T), T, 0, stream>>>((__nv_bfloat16*)dst, count, seed, sigma, mean);
+  } else if (kind == 3) {
+    synth_f32_kernel<<<(unsigned)((count + T - 1) / T), T, 0, stream>>>((float*)dst, count, seed, sigma, mean);
+  } else return (int)cudaErrorInvalidValue;
+  return SFB_CHECK_LAUNCH();
+}
+
+int sfb_device_info(int* sm_count, int* cc_major, int* cc_minor, int64_t* total_mem) {
+  cudaDeviceProp p;
+  int dev = 0;
+  int e = (int)cudaGetDevice(&dev);
+  if (e) return e;
+  e = (int)cudaGetDeviceProperties(&p, dev);
+  if (e) return e;
+  *sm_count = p.multiProcessorCount; *cc_major = p.major; *cc_minor = p.minor; *total_mem = (int64_t)p.totalGlobalMem;
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,276 @@
+// MoE for the rows step (exact CUDA-core arm): router, gate/up with clamp-SwiGLU + FP8 re-quant,
+// and down projection with the top-k + shared-expert sum.  Routed experts are W4A8 (MXFP4 weights,
+// per-32 FP8 activations); the shared expert is W8A8 and rides along as slot `top_k`.
+//
+// Each rank holds an intermediate-width slice of every expert (tensor-parallel experts) or whole
+// experts (expert-parallel); the kernels only see `inter` = the local width and per-expert base
+// pointers.
+//
+// Reference behaviour: kernels/opt_router_sm121.cu:219-221, kernels/opt_moe_sm121.cu:225-227 (gate/up),
+// :348-349 (down + combine), kernels/swiglu_quant_sm121.cuh; docs/architecture/03-moe.md:25-163.
+#include "k_common.cuh"
+
+namespace sfb {
+
+// ---- router ----------------------------------------------------------------------------------------------
+struct RouterArgs {
+  const float* dots;      // [n, E] raw gate logits (fp32)
+  const float* bias;      // [E]
+  const float* bias_vl;   // [E] (image rows) or null
+  const uint8_t* is_image;  // [n] or null
+  int* ids;               // [n, k] ascending expert ids
+  float* wts;             // [n, k]
+  int n, E, k;
+  float route_scale;
+};
+
+__global__ void __launch_bounds__(128) router_topk_kernel(RouterArgs a) {
+  extern __shared__ float sm[];
+  float* s = sm;            // [E] scores
+  float* key = sm + a.E;    // [E] selection keys
+  __shared__ float rv[4];
+  __shared__ int ri[4];
+  __shared__ int pick[16];
+  const int row = blockIdx.x;
+  const float* bias = (a.is_image && a.bias_vl && a.is_image[row]) ? a.bias_vl : a.bias;
+  for (int e = threadIdx.x; e < a.E; e += 128) {
+    float x = a.dots[(size_t)row * a.E + e];
+    float sp = x > 20.f ? x : log1pf(expf(x));
+    float v = sqrtf(sp);
+    s[e] = v;
+    key[e] = v + bias[e];
+  }
+  __syncthreads();
+  for (int t = 0; t < a.k; ++t) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = threadIdx.x; e < a.E; e += 128) {
+      float v = key[e];
+      if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { rv[threadIdx.x >> 5] = bv; ri[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < 4; ++w)
+        if (rv[w] > bv || (rv[w] == bv && ri[w] < bi)) { bv = rv[w]; bi = ri[w]; }
+      pick[t] = bi;
+      key[bi] = -INFINITY;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < a.k; ++i) {  // ascending ids
+      int v = pick[i], j = i - 1;
+      while (j >= 0 && pick[j] > v) { pick[j + 1] = pick[j]; --j; }
+      pick[j + 1] = v;
+    }
+    float sum = 0.f;
+    for (int i = 0; i < a.k; ++i) sum += s[pick[i]];
+    for (int i = 0; i < a.k; ++i) {
+      a.ids[(size_t)row * a.k + i] = pick[i];
+      a.wts[(size_t)row * a.k + i] = s[pick[i]] / (sum + 1e-20f) * a.route_scale;
+    }
+  }
+}
+
+// ---- gate / up ---------------------------------------------------------------------------------------------
+struct GateUpArgs {
+  const uint8_t* xq;      // [n, d] e4m3
+  const uint8_t* xs;      // [n, d/32]
+  const int* ids;         // [n, k]
+  const float* wts;       // [n, k]
+  const uint8_t* w13;     // routed: [E, 2, inter, d/2] packed e2m1
+  const uint8_t* w13_sf;  // routed: [E, 2, sf_bytes(inter, d/32)]
+  const uint8_t* s13;     // shared: [2, inter, d] e4m3 (null when there is no shared expert)
+  const uint8_t* s13_sf;  // shared: [2, sf_bytes(inter, d/32)]
+  uint8_t* act_q;         // [n, k+1, inter] e4m3
+  uint8_t* act_s;         // [n, k+1, inter/32]
+  int n, k, d, inter;
+  float limit;
+};
+
+template <int FP4>
+__device__ __forceinline__ float dot_row(const uint8_t* wrow, const uint8_t* sf, int64_t sf_row, int KB,
+                                         const float* x, int K, int lane) {
+  constexpr int EPC = FP4 ? 32 : 16;
+  float acc = 0.f;
+  for (int c = lane; c < K / EPC; c += 32) {
+    uint4 wv = ldg_nc(wrow + (size_t)c * 16);
+    const float sc = ue8m0_to_f32(__ldg(sf + sf_offset(sf_row, (c * EPC) >> 5, KB)));
+    float f[EPC];
+    if (FP4) decode32_e2m1(wv, f); else decode16_e4m3(wv, f);
+    const float4* xp = reinterpret_cast<const float4*>(x + sm_pad(c * EPC));
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPC / 4; ++j) {
+      float4 xv = xp[j];
+      s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
+      s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+    }
+    acc = fmaf(s, sc, acc);
+  }
+  return warp_sum(acc);
+}
+
+// grid (inter/32, k+1, n), block 256; dynamic smem d floats
+__global__ void __launch_bounds__(256) moe_gate_up_kernel(GateUpArgs a) {
+  extern __shared__ float xsm[];
+  __shared__ float gu[2][32];
+  const int row = blockIdx.z, slot = blockIdx.y, ob = blockIdx.x * 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int d = a.d, KB = d / 32;
+  for (int i = threadIdx.x; i < d; i += 256)
+    xsm[sm_pad(i)] = e4m3_to_f32(a.xq[(size_t)row * d + i]) * ue8m0_to_f32(a.xs[(size_t)row * KB + i / 32]);
+  __syncthreads();
+  const bool shared_slot = slot == a.k;
+  float weight = 1.f;
+  const uint8_t *w1, *w3, *sf1, *sf3;
+  const int64_t sfb = sf_bytes(a.inter, KB);
+  if (shared_slot) {
+    w1 = a.s13; w3 = a.s13 + (size_t)a.inter * d;
+    sf1 = a.s13_sf; sf3 = a.s13_sf + sfb;
+  } else {
+    const int e = a.ids[(size_t)row * a.k + slot];
+    weight = a.wts[(size_t)row * a.k + slot];
+    const size_t per = (size_t)a.inter * (d / 2);
+    w1 = a.w13 + (size_t)e * 2 * per; w3 = w1 + per;
+    sf1 = a.w13_sf + (size_t)e * 2 * sfb; sf3 = sf1 + sfb;
+  }
+  // 64 dot products (32 gate + 32 up), 8 per warp
+  for (int t = warp; t < 64; t += 8) {
+    const int which = t >> 5, o = ob + (t & 31);
+    float v;
+    if (shared_slot)
+      v = dot_row<0>((which ? w3 : w1) + (size_t)o * d, which ? sf3 : sf1, o, KB, xsm, d, lane);
+    else
+      v = dot_row<1>((which ? w3 : w1) + (size_t)o * (d / 2), which ? sf3 : sf1, o, KB, xsm, d, lane);
+    if (lane == 0) gu[which][t & 31] = bfr(v);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float g = fminf(gu[0][lane], a.limit);
+    float u = fminf(fmaxf(gu[1][lane], -a.limit), a.limit);
+    float v = bfr(g / (1.f + expf(-g)) * u * weight);
+    uint8_t sc;
+    uint8_t q = warp_quant_fp8(v, &sc);
+    const size_t base = ((size_t)row * (a.k + 1) + slot) * a.inter;
+    a.act_q[base + ob + lane] = q;
+    if (lane == 0) a.act_s[base / 32 + ob / 32] = sc;
+  }
+}
+
+// ---- down + combine -------------------------------------------------------------------------------------------
+struct DownArgs {
+  const uint8_t* act_q;   // [n, k+1, inter]
+  const uint8_t* act_s;   // [n, k+1, inter/32]
+  const int* ids;         // [n, k]
+  const uint8_t* w2;      // routed: [E, d, inter/2]
+  const uint8_t* w2_sf;   // routed: [E, sf_bytes(d, inter/32)]
+  const uint8_t* s2;      // shared: [d, inter] e4m3
+  const uint8_t* s2_sf;   // shared: sf_bytes(d, inter/32)
+  __nv_bfloat16* out;     // [n, d] this rank's partial
+  int n, k, d, inter, has_shared;
+};
+
+constexpr int DN_COLS = 16;  // output columns per block (2 per warp)
+
+// grid (d/16, n), block 256; dynamic smem (k+1)*inter floats
+__global__ void __launch_bounds__(256) moe_down_kernel(DownArgs a) {
+  extern __shared__ float asm_[];
+  const int row = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int inter = a.inter, KB = inter / 32, slots = a.k + a.has_shared;
+  for (int i = threadIdx.x; i < slots * inter; i += 256) {
+    const size_t o = (size_t)row * (a.k + 1) * inter + i;
+    asm_[sm_pad(i)] = e4m3_to_f32(a.act_q[o]) * ue8m0_to_f32(a.act_s[o / 32]);
+  }
+  __syncthreads();
+  const int64_t sfb = sf_bytes(a.d, KB);
+  const int c4 = inter / 32, c8 = inter / 16;      // chunks per routed / shared slot
+  const int items = a.k * c4 + (a.has_shared ? c8 : 0);
+  for (int cc = 0; cc < 2; ++cc) {
+    const int col = blockIdx.x * DN_COLS + warp * 2 + cc;
+    if (col >= a.d) break;
+    float acc = 0.f;
+    for (int it = lane; it < items; it += 32) {
+      float s = 0.f, sc;
+      if (it < a.k * c4) {
+        const int slot = it / c4, c = it - slot * c4;
+        const int e = a.ids[(size_t)row * a.k + slot];
+        uint4 wv = ldg_nc(a.w2 + ((size_t)e * a.d + col) * (inter / 2) + (size_t)c * 16);
+        sc = ue8m0_to_f32(__ldg(a.w2_sf + (size_t)e * sfb + sf_offset(col, c, KB)));
+        float f[32];
+        decode32_e2m1(wv, f);
+        const float4* x = reinterpret_cast<const float4*>(asm_ + sm_pad(slot * inter + c * 32));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 xv = x[j];
+          s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
+          s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+        }
+      } else {
+        const int c = it - a.k * c4;
+        uint4 wv = ldg_nc(a.s2 + (size_t)col * inter + (size_t)c * 16);
+        sc = ue8m0_to_f32(__ldg(a.s2_sf + sf_offset(col, c >> 1, KB)));
+        float f[16];
+        decode16_e4m3(wv, f);
+        const float4* x = reinterpret_cast<const float4*>(asm_ + sm_pad(a.k * inter + c * 16));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float4 xv = x[j];
+          s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
+          s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+        }
+      }
+      acc = fmaf(s, sc, acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) a.out[(size_t)row * a.d + col] = __float2bfloat16_rn(acc);
+  }
+}
+
+}  // namespace sfb
+
+using namespace sfb;
+
+extern "C" {
+
+int sfb_router_topk(const float* dots, const float* bias, const float* bias_vl, const void* is_image, int* ids,
+                    float* wts, int n, int E, int k, float route_scale, cudaStream_t stream) {
+  if (k > 16) return (int)cudaErrorInvalidValue;
+  RouterArgs a{dots, bias, bias_vl, (const uint8_t*)is_image, ids, wts, n, E, k, route_scale};
+  router_topk_kernel<<<n, 128, sizeof(float) * 2 * E, stream>>>(a);
+  return SFB_CHECK_LAUNCH();
+}
+
+int sfb_moe_gate_up(const void* xq, const void* xs, const int* ids, const float* wts, const void* w13,
+                    const void* w13_sf, const void* s13, const void* s13_sf, void* act_q, void* act_s, int n,
+                    int k, int d, int inter, float limit, cudaStream_t stream) {
+  if (inter % 32 || d % 32) return (int)cudaErrorInvalidValue;
+  GateUpArgs a{(const uint8_t*)xq, (const uint8_t*)xs, ids, wts, (const uint8_t*)w13, (const uint8_t*)w13_sf,
+               (const uint8_t*)s13, (const uint8_t*)s13_sf, (uint8_t*)act_q, (uint8_t*)act_s, n, k, d, inter, limit};
+  const int slots = k + (s13 ? 1 : 0);
+  moe_gate_up_kernel<<<dim3(inter / 32, slots, n), 256, sizeof(float) * sm_pad(d), stream>>>(a);
+  return SFB_CHECK_LAUNCH();
+}
+
+int sfb_moe_down(const void* act_q, const void* act_s, const int* ids, const void* w2, const void* w2_sf,
+                 const void* s2, const void* s2_sf, void* out, int n, int k, int d, int inter,
+                 cudaStream_t stream) {
+  DownArgs a{(const uint8_t*)act_q, (const uint8_t*)act_s, ids, (const uint8_t*)w2, (const uint8_t*)w2_sf,
+             (const uint8_t*)s2, (const uint8_t*)s2_sf, (__nv_bfloat16*)out, n, k, d, inter, s2 ? 1 : 0};
+  const size_t smem = sizeof(float) * (size_t)sm_pad((k + 1) * inter);
+  static bool done = false;
+  if (!done) { cudaFuncSetAttribute(moe_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); done = true; }
+  if (smem > 160 * 1024) return (int)cudaErrorInvalidValue;
+  moe_down_kernel<<<dim3((d + DN_COLS - 1) / DN_COLS, n), 256, smem, stream>>>(a);
+  return SFB_CHECK_LAUNCH();
+}
+
+}  // extern "C"

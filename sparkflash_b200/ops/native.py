@@ -1,0 +1,214 @@
+"""Python faces of the CUDA launchers in ``csrc/k_*.cu`` (C ABI, called through ctypes).
+
+Every wrapper takes torch tensors that already live on the current CUDA device, validates shapes
+and dtypes, and launches on the current torch stream, so the calls can be captured into a CUDA
+graph.  There is no eager fallback: a missing library or a launch error raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_uint32, c_uint64, c_void_p
+
+import torch
+
+from .. import _lib
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def _p(t: torch.Tensor | None):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise NativeError(f"{what}: CUDA error {code}")
+
+
+_declared = False
+
+
+def lib():
+    global _declared
+    L = _lib.cuda()
+    if not _declared:
+        for name in dir(L):
+            pass
+        _declared = True
+    return L
+
+
+def _ptr_array(tensors) -> ctypes.Array:
+    arr = (c_void_p * 8)()
+    for i, t in enumerate(tensors):
+        arr[i] = t if isinstance(t, int) else t.data_ptr()
+    return arr
+
+
+# ---- seam -----------------------------------------------------------------------------------------------
+def seam_nblk(d: int) -> int:
+    return int(lib().sfb_seam_nblk(c_int(d)))
+
+
+def coef_stride(hc: int) -> int:
+    return 2 * hc + hc * hc
+
+
+def seam(h, y_parts, coef_prev, a_pre, a_stride, fn, xhat, partials, norm_w, hc_scale, hc_base, coef_out,
+         xn, xq, xs, n, hc, d, iters, norm_eps, hc_eps, ysum=None, flags=None, epoch=0, status=None):
+    """One mHC seam (see csrc/k_seam.cu).  ``y_parts``: list of W partial outputs (tensors or raw device
+    addresses) or None for the first seam of a forward."""
+    has_post = y_parts is not None
+    W = len(y_parts) if has_post else 1
+    yp = _ptr_array(y_parts) if has_post else None
+    fp = _ptr_array(flags) if flags is not None else None
+    code = lib().sfb_seam(_p(h), yp, fp, c_uint32(epoch), c_int(W), c_int(1 if has_post else 0),
+                          _p(coef_prev), _p(a_pre), c_int(a_stride), _p(fn), _p(xhat), _p(partials), _p(ysum),
+                          _p(norm_w), _p(hc_scale), _p(hc_base), _p(coef_out), _p(xn), _p(xq), _p(xs),
+                          _p(status), c_int(n), c_int(hc), c_int(d), c_int(iters), c_float(norm_eps),
+                          c_float(hc_eps), _stream())
+    _check(code, "seam")
+
+
+# ---- gemv -----------------------------------------------------------------------------------------------
+WF_FP8, WF_FP4, WF_BF16 = 0, 1, 2
+
+
+def gemv(wfmt, w, sf, row_bytes, N, K, n, *, groups=1, xq=None, xs=None, xb=None, xf=None, x_stride=None,
+         x_quant=False, out_b=None, out_f=None, out_stride=None):
+    if x_stride is None:
+        x_stride = K * groups
+    if out_stride is None:
+        out_stride = N * groups
+    code = lib().sfb_gemv(c_int(wfmt), _p(w), _p(sf), c_int64(row_bytes), c_int(N), c_int(K), c_int(groups),
+                          c_int(n), _p(xq), _p(xs), _p(xb), _p(xf), c_int64(x_stride), c_int(1 if x_quant else 0),
+                          _p(out_b), _p(out_f), c_int64(out_stride), _stream())
+    _check(code, "gemv")
+
+
+# ---- kv -------------------------------------------------------------------------------------------------
+def qkv_post(raw, q_norm_w, kv_norm_w, inv_freq, row_lane, row_pos, qr_q, qr_s, win_q, win_s, n, q, hd, rd,
+             ring, eps, qr_b=None):
+    code = lib().sfb_qkv_post(_p(raw), _p(q_norm_w), _p(kv_norm_w), _p(inv_freq), _p(row_lane), _p(row_pos),
+                              _p(qr_q), _p(qr_s), _p(qr_b), _p(win_q), _p(win_s), c_int64(win_q.stride(0)),
+                              c_int64(win_s.stride(0)), c_int(n), c_int(q), c_int(hd), c_int(rd), c_int(ring),
+                              c_float(eps), _stream())
+    _check(code, "qkv_post")
+
+
+def compress_append(raw, raw_stride, norm_w, wk, k_norm_w, inv_freq, row_lane, row_pos, cin, cring, ckv_q,
+                    ckv_s, ik_q, ik_s, max_entries, n, hd, idh, rd, ratio, eps, status=None):
+    code = lib().sfb_compress_append(
+        _p(raw), c_int64(raw_stride), _p(norm_w), _p(wk), _p(k_norm_w), _p(inv_freq), _p(row_lane), _p(row_pos),
+        _p(cin), c_int64(cin.stride(0) if cin is not None else 0), c_int(cring), _p(ckv_q), _p(ckv_s), _p(ik_q),
+        _p(ik_s), c_int64(ckv_q.stride(0)), c_int64(ckv_s.stride(0)), c_int64(ik_q.stride(0)),
+        c_int64(ik_s.stride(0)), c_int(max_entries), c_int(n), c_int(hd), c_int(idh), c_int(rd), c_int(ratio),
+        c_float(eps), _p(status), _stream())
+    _check(code, "compress_append")
+
+
+# ---- indexer ---------------------------------------------------------------------------------------------
+def index_q(qraw, q_stride, q_off, wraw, w_stride, w_off, inv_freq, row_pos, qi, wt, n, inh, idh, rd, wscale):
+    code = lib().sfb_index_q(_p(qraw), c_int64(q_stride), c_int64(q_off), _p(wraw), c_int64(w_stride),
+                             c_int64(w_off), _p(inv_freq), _p(row_pos), _p(qi), _p(wt), c_int(n), c_int(inh),
+                             c_int(idh), c_int(rd), c_float(wscale), _stream())
+    _check(code, "index_q")
+
+
+def index_scores(qi, wt, ik_q, ik_s, row_lane, row_pos, cand, cand_block, scores, n, inh, idh, ratio, max_len):
+    code = lib().sfb_index_scores(_p(qi), _p(wt), _p(ik_q), _p(ik_s), c_int64(ik_q.stride(0)),
+                                  c_int64(ik_s.stride(0)), _p(row_lane), _p(row_pos), _p(cand),
+                                  c_int64(cand.stride(0) if cand is not None else 0), c_int(cand_block),
+                                  _p(scores), c_int64(scores.stride(0)), c_int(n), c_int(inh), c_int(idh),
+                                  c_int(ratio), c_int(max_len), _stream())
+    _check(code, "index_scores")
+
+
+def hsi_blockmax(scores, row_pos, ratio, bs, bscore, max_blocks, n):
+    code = lib().sfb_hsi_blockmax(_p(scores), c_int64(scores.stride(0)), _p(row_pos), c_int(ratio), c_int(bs),
+                                  _p(bscore), c_int64(bscore.stride(0)), c_int(max_blocks), c_int(n), _stream())
+    _check(code, "hsi_blockmax")
+
+
+def hsi_mark(ids, K, flags, max_blocks, n):
+    code = lib().sfb_hsi_mark(_p(ids), c_int(K), _p(flags), c_int64(flags.stride(0)), c_int(max_blocks), c_int(n),
+                              _stream())
+    _check(code, "hsi_mark")
+
+
+def select_topk(scores, row_pos, ratio, len_div, max_len, K, ids, count, n):
+    code = lib().sfb_select_topk(_p(scores), c_int64(scores.stride(0)), _p(row_pos), c_int(ratio), c_int(len_div),
+                                 c_int(max_len), c_int(K), _p(ids), _p(count), c_int(n), _stream())
+    _check(code, "select_topk")
+
+
+# ---- attention ---------------------------------------------------------------------------------------------
+def attn_rows(q, q_stride, inv_freq, row_lane, row_pos, win_q, win_s, ckv_q, ckv_s, sel, sel_count, K, sink,
+              out, n, heads, hd, rd, window, ring, scale):
+    code = lib().sfb_attn_rows(
+        _p(q), c_int64(q_stride), _p(inv_freq), _p(row_lane), _p(row_pos), _p(win_q), _p(win_s),
+        c_int64(win_q.stride(0)), c_int64(win_s.stride(0)), _p(ckv_q), _p(ckv_s),
+        c_int64(ckv_q.stride(0) if ckv_q is not None else 0), c_int64(ckv_s.stride(0) if ckv_s is not None else 0),
+        _p(sel), _p(sel_count), c_int(K), _p(sink), _p(out), c_int(n), c_int(heads), c_int(hd), c_int(rd),
+        c_int(window), c_int(ring), c_float(scale), _stream())
+    _check(code, "attn_rows")
+
+
+# ---- moe ---------------------------------------------------------------------------------------------------
+def router_topk(dots, bias, bias_vl, is_image, ids, wts, n, E, k, route_scale):
+    code = lib().sfb_router_topk(_p(dots), _p(bias), _p(bias_vl), _p(is_image), _p(ids), _p(wts), c_int(n),
+                                 c_int(E), c_int(k), c_float(route_scale), _stream())
+    _check(code, "router_topk")
+
+
+def moe_gate_up(xq, xs, ids, wts, w13, w13_sf, s13, s13_sf, act_q, act_s, n, k, d, inter, limit):
+    code = lib().sfb_moe_gate_up(_p(xq), _p(xs), _p(ids), _p(wts), _p(w13), _p(w13_sf), _p(s13), _p(s13_sf),
+                                 _p(act_q), _p(act_s), c_int(n), c_int(k), c_int(d), c_int(inter), c_float(limit),
+                                 _stream())
+    _check(code, "moe_gate_up")
+
+
+def moe_down(act_q, act_s, ids, w2, w2_sf, s2, s2_sf, out, n, k, d, inter):
+    code = lib().sfb_moe_down(_p(act_q), _p(act_s), _p(ids), _p(w2), _p(w2_sf), _p(s2), _p(s2_sf), _p(out),
+                              c_int(n), c_int(k), c_int(d), c_int(inter), _stream())
+    _check(code, "moe_down")
+
+
+# ---- misc --------------------------------------------------------------------------------------------------
+def embed(table, tokens, h, n, hc, d, vocab, status=None):
+    _check(lib().sfb_embed(_p(table), _p(tokens), _p(h), c_int(n), c_int(hc), c_int(d), c_int(vocab), _p(status),
+                           _stream()), "embed")
+
+
+def tap_mean(h, tap, tap_stride, n, hc, d):
+    _check(lib().sfb_tap_mean(_p(h), _p(tap), c_int64(tap_stride), c_int(n), c_int(hc), c_int(d), _stream()),
+           "tap_mean")
+
+
+def sample(logits, row_pos, temperature, seed, mask, best_val, best_id, n, V, vocab_offset):
+    code = lib().sfb_sample(_p(logits), c_int64(logits.stride(0)), _p(row_pos), _p(temperature), _p(seed),
+                            _p(mask), c_int64(mask.stride(0) if mask is not None else 0), _p(best_val),
+                            _p(best_id), c_int(n), c_int(V), c_int(vocab_offset), _stream())
+    _check(code, "sample")
+
+
+def sample_fold(vals, ids, W, n, out_tokens):
+    _check(lib().sfb_sample_fold(_p(vals), _p(ids), c_int(W), c_int(n), _p(out_tokens), _stream()), "sample_fold")
+
+
+def synth_fill(kind: int, dst: torch.Tensor, count: int, seed: int, sigma: float, mean: float = 0.0):
+    _check(lib().sfb_synth_fill(c_int(kind), _p(dst), c_int64(count), c_uint64(seed & 0xFFFFFFFFFFFFFFFF),
+                                c_float(sigma), c_float(mean), _stream()), "synth_fill")
+
+
+def device_info() -> dict:
+    sm, ma, mi, mem = c_int(), c_int(), c_int(), c_int64()
+    _check(lib().sfb_device_info(ctypes.byref(sm), ctypes.byref(ma), ctypes.byref(mi), ctypes.byref(mem)),
+           "device_info")
+    return {"sm_count": sm.value, "cc": (ma.value, mi.value), "total_mem": mem.value}
