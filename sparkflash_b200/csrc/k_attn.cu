@@ -70,10 +70,13 @@ __global__ void __launch_bounds__(256) attn_rows_kernel(AttnArgs a) {
     if (e < n_win) {
       const int slot = (w_first + e) % a.ring;
       const uint8_t* kq = a.win_q + (size_t)L * a.win_lane_q + (size_t)slot * HD + lane * EPL;
-      const float sc = ue8m0_to_f32(a.win_s[(size_t)L * a.win_lane_s + (size_t)slot * (HD / 32) + (lane * EPL) / 32]);
+      float sc = ue8m0_to_f32(a.win_s[(size_t)L * a.win_lane_s + (size_t)slot * (HD / 32) + (lane * EPL) / 32]);
       if (EPL == 16) {
         uint4 v = *reinterpret_cast<const uint4*>(kq);
-        decode16_e4m3(v, kv);
+        decode16_e4m3_raw(v, kv);  // values carry a fixed 2^-120; undo it in two exact steps
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) kv[j] *= 1.152921504606847e18f;  // 2^60
+        sc *= 1.152921504606847e18f;
       } else {
 #pragma unroll
         for (int j = 0; j < EPL; j += 2) {
@@ -86,12 +89,13 @@ __global__ void __launch_bounds__(256) attn_rows_kernel(AttnArgs a) {
     } else {
       const int id = a.sel[(size_t)row * a.K + (e - n_win)];
       const uint8_t* kq = a.ckv_q + (size_t)L * a.ckv_lane_q + (size_t)id * (HD / 2) + lane * (EPL / 2);
-      const float sc = e4m3_to_f32(a.ckv_s[(size_t)L * a.ckv_lane_s + (size_t)id * (HD / 16) + (lane * EPL) / 16]);
+      float sc = e4m3_to_f32(a.ckv_s[(size_t)L * a.ckv_lane_s + (size_t)id * (HD / 16) + (lane * EPL) / 16]);
       if (EPL == 16) {
         uint2 v = *reinterpret_cast<const uint2*>(kq);
-        const uint8_t* b = reinterpret_cast<const uint8_t*>(&v);
+        decode8_e2m1_raw(v.x, kv); decode8_e2m1_raw(v.y, kv + 8);  // fixed 2^-126
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { float2 t = cvt_e2m1x2(b[j]); kv[2 * j] = t.x; kv[2 * j + 1] = t.y; }
+        for (int j = 0; j < EPL; ++j) kv[j] *= 9.223372036854776e18f;  // 2^63
+        sc *= 9.223372036854776e18f;
       } else {
 #pragma unroll
         for (int j = 0; j < EPL / 2; ++j) { float2 t = cvt_e2m1x2(kq[j]); kv[2 * j] = t.x; kv[2 * j + 1] = t.y; }

@@ -51,6 +51,41 @@ __device__ __forceinline__ void decode32_e2m1(const uint4& v, float* f) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) { float2 t = cvt_e2m1x2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
 }
+// ---- integer-pipe decodes ------------------------------------------------------------------------------------
+// Format converts run on a narrow pipe; hot loops instead build fp32 bit patterns with shifts and
+// masks.  The result is the true value times a fixed power of two (2^-120 for E4M3, 2^-126 for
+// E2M1; subnormal codes land on fp32 subnormals, which FMA handles exactly), and the caller folds
+// the inverse power into the block scale it multiplies by anyway.
+#define SFB_E4M3_RAW_EXP 120
+#define SFB_E2M1_RAW_EXP 126
+__device__ __forceinline__ void decode4_e4m3_raw(uint32_t w, float* f) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t t = w << (24 - 8 * j);  // byte j in the top byte
+    f[j] = __uint_as_float((t & 0x80000000u) | ((t & 0x7f000000u) >> 4));
+  }
+}
+__device__ __forceinline__ void decode16_e4m3_raw(const uint4& v, float* f) {
+  decode4_e4m3_raw(v.x, f); decode4_e4m3_raw(v.y, f + 4); decode4_e4m3_raw(v.z, f + 8); decode4_e4m3_raw(v.w, f + 12);
+}
+__device__ __forceinline__ void decode8_e2m1_raw(uint32_t w, float* f) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t t = w << (28 - 4 * j);  // nibble j in the top nibble
+    f[j] = __uint_as_float((t & 0x80000000u) | ((t & 0x70000000u) >> 6));
+  }
+}
+__device__ __forceinline__ void decode32_e2m1_raw(const uint4& v, float* f) {
+  decode8_e2m1_raw(v.x, f); decode8_e2m1_raw(v.y, f + 8); decode8_e2m1_raw(v.z, f + 16); decode8_e2m1_raw(v.w, f + 24);
+}
+// block scale 2^(code-127) times 2^extra, as one float (code + extra stays below 255 for any
+// weight or cache scale the model produces; saturates otherwise)
+__device__ __forceinline__ float ue8m0_shifted(uint8_t code, int extra) {
+  int e = (int)code + extra;
+  e = e > 254 ? 254 : (e < 1 ? 1 : e);
+  return __uint_as_float((uint32_t)e << 23);
+}
+
 __device__ __forceinline__ float bf16_to_f(__nv_bfloat16 b) { return __bfloat162float(b); }
 __device__ __forceinline__ float bfr(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
 __device__ __forceinline__ uint8_t enc_e4m3(float f) {
@@ -143,6 +178,21 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want
 // Shared-memory activation rows are padded by 4 floats per 32 so that lanes reading consecutive
 // 16-byte-chunk-aligned slices with 128-bit loads do not collide on banks.
 __host__ __device__ __forceinline__ int sm_pad(int k) { return k + ((k >> 5) << 2); }
+
+// Dequantise `count16` chunks of 16 FP8 codes (+ one UE8M0 scale per 32) into padded shared memory.
+// src codes are 16-byte aligned; dst index space is sm_pad().
+__device__ __forceinline__ void stage_fp8_to_smem(const uint8_t* q, const uint8_t* sc, int count16,
+                                                  float* dst, int nthreads) {
+  for (int i = threadIdx.x; i < count16; i += nthreads) {
+    const uint4 v = *reinterpret_cast<const uint4*>(q + (size_t)i * 16);
+    const float s = ue8m0_to_f32(sc[i >> 1]);
+    float f[16];
+    decode16_e4m3(v, f);
+    float4* o = reinterpret_cast<float4*>(dst + sm_pad(i * 16));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = make_float4(f[4 * j] * s, f[4 * j + 1] * s, f[4 * j + 2] * s, f[4 * j + 3] * s);
+  }
+}
 
 // splitmix64: the sampler's stateless noise and the synthetic-weight generator
 __host__ __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {

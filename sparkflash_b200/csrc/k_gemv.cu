@@ -44,28 +44,67 @@ struct GemvArgs {
 
 template <int R>
 __device__ __forceinline__ void load_x(const GemvArgs& a, int r0, int kcol0, float* xs_sm) {
-  // xs_sm[r][k] for r < R, k < K (zero rows past n)
-  for (int idx = threadIdx.x; idx < R * a.K; idx += GV_THREADS) {
-    const int r = idx / a.K, k = idx - r * a.K;
-    const int row = r0 + r;
-    float v = 0.f;
-    if (row < a.n) {
-      const int64_t off = (int64_t)row * a.x_stride + kcol0 + k;
-      if (a.xq) {
-        v = e4m3_to_f32(a.xq[off]) * ue8m0_to_f32(a.xs[(int64_t)row * (a.x_stride / 32) + (kcol0 + k) / 32]);
-      } else if (a.xb) {
-        v = bf16_to_f(a.xb[off]);
+  // xs_sm[r][sm_pad(k)] for r < R, k < K (zero rows past n)
+  const int KP = sm_pad(a.K);
+  if (a.xq) {
+    const int c16 = a.K / 16;
+    for (int i = threadIdx.x; i < R * c16; i += GV_THREADS) {
+      const int r = i / c16, c = i - r * c16, row = r0 + r;
+      float f[16];
+      float s = 0.f;
+      if (row < a.n) {
+        const uint4 v = *reinterpret_cast<const uint4*>(a.xq + (int64_t)row * a.x_stride + kcol0 + c * 16);
+        s = ue8m0_to_f32(a.xs[(int64_t)row * (a.x_stride / 32) + (kcol0 + c * 16) / 32]);
+        decode16_e4m3(v, f);
       } else {
-        v = a.xf[off];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) f[j] = 0.f;
+      }
+      float4* o = reinterpret_cast<float4*>(xs_sm + r * KP + sm_pad(c * 16));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = make_float4(f[4 * j] * s, f[4 * j + 1] * s, f[4 * j + 2] * s, f[4 * j + 3] * s);
+    }
+  } else if (a.xb) {
+    const int c8 = a.K / 8, total = R * c8;
+    for (int base = 0; base < total; base += GV_THREADS) {  // uniform trip count: shuffles below
+      const int i = base + threadIdx.x;
+      const bool on = i < total;
+      const int r = on ? i / c8 : 0, c = on ? i - r * c8 : 0, row = r0 + r;
+      float f[8];
+      if (on && row < a.n) {
+        const uint4 v = *reinterpret_cast<const uint4*>(a.xb + (int64_t)row * a.x_stride + kcol0 + c * 8);
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { f[2 * j] = __uint_as_float(p[j] << 16); f[2 * j + 1] = __uint_as_float(p[j] & 0xffff0000u); }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = 0.f;
+      }
+      if (a.x_quant) {  // per-32 FP8 round trip: 4 neighbouring lanes hold one aligned group
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const uint8_t sc = act_scale_code_fp8(amax);
+        const float inv = bits_f32(((uint32_t)(254 - sc)) << 23), s = ue8m0_to_f32(sc);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 t = cvt_e4m3x2(enc_e4m3x2(f[2 * j] * inv, f[2 * j + 1] * inv));
+          f[2 * j] = t.x * s; f[2 * j + 1] = t.y * s;
+        }
+      }
+      if (on) {
+        float4* o = reinterpret_cast<float4*>(xs_sm + r * KP + sm_pad(c * 8));
+        o[0] = make_float4(f[0], f[1], f[2], f[3]);
+        o[1] = make_float4(f[4], f[5], f[6], f[7]);
       }
     }
-    if (a.x_quant) {  // per-32 FP8 round trip on the fly (K % 32 == 0, so a warp holds one aligned group)
-      float amax = warp_max(fabsf(v));
-      const uint8_t sc = act_scale_code_fp8(amax);
-      const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
-      v = e4m3_to_f32(enc_e4m3(v * inv)) * ue8m0_to_f32(sc);
+  } else {
+    for (int idx = threadIdx.x; idx < R * a.K; idx += GV_THREADS) {
+      const int r = idx / a.K, k = idx - r * a.K, row = r0 + r;
+      xs_sm[r * KP + sm_pad(k)] = row < a.n ? a.xf[(int64_t)row * a.x_stride + kcol0 + k] : 0.f;
     }
-    xs_sm[r * sm_pad(a.K) + sm_pad(k)] = v;
   }
 }
 
@@ -75,7 +114,6 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
   extern __shared__ float xs_sm[];
   const int g = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * GV_ROWS + warp * GV_RPW;
   constexpr int EPC = WF == 0 ? 16 : (WF == 1 ? 32 : 8);  // elements per 16-byte chunk
   const int chunks = a.K / EPC;
 
@@ -83,6 +121,8 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
     __syncthreads();
     load_x<R>(a, r0, g * a.K, xs_sm);
     __syncthreads();
+   for (int tile = blockIdx.x; tile * GV_ROWS < a.N; tile += gridDim.x) {
+    const int row0 = tile * GV_ROWS + warp * GV_RPW;
     float acc[GV_RPW][R];
 #pragma unroll
     for (int i = 0; i < GV_RPW; ++i)
@@ -91,41 +131,54 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
 
     if (row0 < a.N) {
       const int64_t grow0 = (int64_t)g * a.N + row0;
-      for (int c = lane; c < chunks; c += 32) {
-        uint4 wv[GV_RPW];
-        float sc[GV_RPW];
+      constexpr int U = 4;  // chunks in flight per row per lane
+      for (int cb = lane; cb < chunks; cb += 32 * U) {
+        uint4 wv[U][GV_RPW];
+        float sc[U][GV_RPW];
 #pragma unroll
-        for (int i = 0; i < GV_RPW; ++i) {
-          const bool ok = row0 + i < a.N;
-          const int64_t gr = ok ? grow0 + i : grow0;
-          wv[i] = ldg_nc(a.w + gr * a.row_bytes + (int64_t)c * 16);
-          if (WF == 2) sc[i] = ok ? 1.f : 0.f;
-          else {
-            const int kb = (c * EPC) >> 5;
-            sc[i] = ok ? ue8m0_to_f32(__ldg(a.sf + sf_offset(gr, kb, a.KB))) : 0.f;
+        for (int u = 0; u < U; ++u) {
+          const int c = cb + 32 * u;
+#pragma unroll
+          for (int i = 0; i < GV_RPW; ++i) {
+            const bool ok = row0 + i < a.N && c < chunks;
+            const int64_t gr = row0 + i < a.N ? grow0 + i : grow0;
+            if (ok) {
+              wv[u][i] = ldg_nc(a.w + gr * a.row_bytes + (int64_t)c * 16);
+              sc[u][i] = WF == 2 ? 1.f
+                                 : ue8m0_shifted(__ldg(a.sf + sf_offset(gr, (c * EPC) >> 5, a.KB)),
+                                                 WF == 0 ? SFB_E4M3_RAW_EXP : SFB_E2M1_RAW_EXP);
+            } else {
+              wv[u][i] = make_uint4(0, 0, 0, 0);
+              sc[u][i] = 0.f;
+            }
           }
         }
 #pragma unroll
-        for (int i = 0; i < GV_RPW; ++i) {
-          float f[EPC];
-          if (WF == 0) decode16_e4m3(wv[i], f);
-          else if (WF == 1) decode32_e2m1(wv[i], f);
-          else {
-            const uint32_t* p = reinterpret_cast<const uint32_t*>(&wv[i]);
+        for (int u = 0; u < U; ++u) {
+          const int c = cb + 32 * u;
+          if (c >= chunks) break;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { f[2 * j] = __uint_as_float(p[j] << 16); f[2 * j + 1] = __uint_as_float(p[j] & 0xffff0000u); }
-          }
+          for (int i = 0; i < GV_RPW; ++i) {
+            float f[EPC];
+            if (WF == 0) decode16_e4m3_raw(wv[u][i], f);
+            else if (WF == 1) decode32_e2m1_raw(wv[u][i], f);
+            else {
+              const uint32_t* p = reinterpret_cast<const uint32_t*>(&wv[u][i]);
 #pragma unroll
-          for (int r = 0; r < R; ++r) {
-            const float4* xp = reinterpret_cast<const float4*>(xs_sm + r * sm_pad(a.K) + sm_pad(c * EPC));
-            float s = 0.f;
-#pragma unroll
-            for (int j = 0; j < EPC / 4; ++j) {
-              float4 xv = xp[j];
-              s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
-              s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+              for (int j = 0; j < 4; ++j) { f[2 * j] = __uint_as_float(p[j] << 16); f[2 * j + 1] = __uint_as_float(p[j] & 0xffff0000u); }
             }
-            acc[i][r] = fmaf(s, sc[i], acc[i][r]);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              const float4* xp = reinterpret_cast<const float4*>(xs_sm + r * sm_pad(a.K) + sm_pad(c * EPC));
+              float s = 0.f;
+#pragma unroll
+              for (int j = 0; j < EPC / 4; ++j) {
+                float4 xv = xp[j];
+                s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
+                s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+              }
+              acc[i][r] = fmaf(s, sc[u][i], acc[i][r]);
+            }
           }
         }
       }
@@ -142,6 +195,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
           if (a.out_f) a.out_f[o] = v;
         }
       }
+   }
   }
 }
 
@@ -152,7 +206,9 @@ static int launch_gemv(const GemvArgs& a, cudaStream_t stream) {
   if (a.n >= 4 && smem1 * 4 <= 96 * 1024) R = 4;
   else if (a.n >= 2 && smem1 * 2 <= 96 * 1024) R = 2;
   if (smem1 > 96 * 1024) return (int)cudaErrorInvalidValue;
-  dim3 grid((a.N + GV_ROWS - 1) / GV_ROWS, a.groups);
+  int tiles = (a.N + GV_ROWS - 1) / GV_ROWS;
+  const int cap = (148 * 4 + a.groups - 1) / a.groups;  // a few resident blocks per SM; each loops over row tiles
+  dim3 grid(tiles < cap ? tiles : cap, a.groups);
   const size_t smem = (size_t)smem1 * R;
 #define SFB_GV(RR)                                                                                   \
   {                                                                                                  \

@@ -95,38 +95,63 @@ struct GateUpArgs {
   float limit;
 };
 
-template <int FP4>
-__device__ __forceinline__ float dot_row(const uint8_t* wrow, const uint8_t* sf, int64_t sf_row, int KB,
-                                         const float* x, int K, int lane) {
+// NR weight rows against one activation row; all NR loads of a chunk step are issued before use.
+template <int FP4, int NR>
+__device__ __forceinline__ void dot_rows(const uint8_t* const* wrow, const uint8_t* const* sf, const int64_t* sf_row,
+                                         int KB, const float* x, int K, int lane, float* out) {
   constexpr int EPC = FP4 ? 32 : 16;
-  float acc = 0.f;
-  for (int c = lane; c < K / EPC; c += 32) {
-    uint4 wv = ldg_nc(wrow + (size_t)c * 16);
-    const float sc = ue8m0_to_f32(__ldg(sf + sf_offset(sf_row, (c * EPC) >> 5, KB)));
-    float f[EPC];
-    if (FP4) decode32_e2m1(wv, f); else decode16_e4m3(wv, f);
-    const float4* xp = reinterpret_cast<const float4*>(x + sm_pad(c * EPC));
-    float s = 0.f;
+  constexpr int U = 2;
+  float acc[NR];
 #pragma unroll
-    for (int j = 0; j < EPC / 4; ++j) {
-      float4 xv = xp[j];
-      s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
-      s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+  for (int i = 0; i < NR; ++i) acc[i] = 0.f;
+  const int chunks = K / EPC;
+  for (int cb = lane; cb < chunks; cb += 32 * U) {
+    uint4 wv[U][NR];
+    float sc[U][NR];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int c = cb + 32 * u;
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        if (c < chunks) {
+          wv[u][i] = ldg_nc(wrow[i] + (size_t)c * 16);
+          sc[u][i] = ue8m0_shifted(__ldg(sf[i] + sf_offset(sf_row[i], (c * EPC) >> 5, KB)),
+                                   FP4 ? SFB_E2M1_RAW_EXP : SFB_E4M3_RAW_EXP);
+        } else { wv[u][i] = make_uint4(0, 0, 0, 0); sc[u][i] = 0.f; }
+      }
     }
-    acc = fmaf(s, sc, acc);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int c = cb + 32 * u;
+      if (c >= chunks) break;
+      const float4* xp = reinterpret_cast<const float4*>(x + sm_pad(c * EPC));
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        float f[EPC];
+        if (FP4) decode32_e2m1_raw(wv[u][i], f); else decode16_e4m3_raw(wv[u][i], f);
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPC / 4; ++j) {
+          float4 xv = xp[j];
+          s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
+          s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+        }
+        acc[i] = fmaf(s, sc[u][i], acc[i]);
+      }
+    }
   }
-  return warp_sum(acc);
+#pragma unroll
+  for (int i = 0; i < NR; ++i) out[i] = warp_sum(acc[i]);
 }
 
 // grid (inter/32, k+1, n), block 256; dynamic smem d floats
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(GateUpArgs a) {
   extern __shared__ float xsm[];
   __shared__ float gu[2][32];
-  const int row = blockIdx.z, slot = blockIdx.y, ob = blockIdx.x * 32;
+  const int row = blockIdx.z, slot = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int d = a.d, KB = d / 32;
-  for (int i = threadIdx.x; i < d; i += 256)
-    xsm[sm_pad(i)] = e4m3_to_f32(a.xq[(size_t)row * d + i]) * ue8m0_to_f32(a.xs[(size_t)row * KB + i / 32]);
+  stage_fp8_to_smem(a.xq + (size_t)row * d, a.xs + (size_t)row * KB, d / 16, xsm, 256);
   __syncthreads();
   const bool shared_slot = slot == a.k;
   float weight = 1.f;
@@ -142,16 +167,28 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(GateUpArgs a) {
     w1 = a.w13 + (size_t)e * 2 * per; w3 = w1 + per;
     sf1 = a.w13_sf + (size_t)e * 2 * sfb; sf3 = sf1 + sfb;
   }
-  // 64 dot products (32 gate + 32 up), 8 per warp
-  for (int t = warp; t < 64; t += 8) {
-    const int which = t >> 5, o = ob + (t & 31);
-    float v;
-    if (shared_slot)
-      v = dot_row<0>((which ? w3 : w1) + (size_t)o * d, which ? sf3 : sf1, o, KB, xsm, d, lane);
-    else
-      v = dot_row<1>((which ? w3 : w1) + (size_t)o * (d / 2), which ? sf3 : sf1, o, KB, xsm, d, lane);
-    if (lane == 0) gu[which][t & 31] = bfr(v);
-  }
+  // 64 dot products (32 gate + 32 up) per column tile: each warp takes 4 output columns, gate and up
+  // rows together
+  for (int ob = blockIdx.x * 32; ob < a.inter; ob += gridDim.x * 32) {
+    const int oc = warp * 4;  // columns oc..oc+3 of this block's 32
+    const uint8_t* wr[8];
+    const uint8_t* sfp[8];
+    int64_t sfr[8];
+    const size_t rb = shared_slot ? (size_t)d : (size_t)(d / 2);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int which = i >> 2, o = ob + oc + (i & 3);
+      wr[i] = (which ? w3 : w1) + (size_t)o * rb;
+      sfp[i] = which ? sf3 : sf1;
+      sfr[i] = o;
+    }
+    float v[8];
+    if (shared_slot) dot_rows<0, 8>(wr, sfp, sfr, KB, xsm, d, lane, v);
+    else dot_rows<1, 8>(wr, sfp, sfr, KB, xsm, d, lane, v);
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) gu[i >> 2][oc + (i & 3)] = bfr(v[i]);
+    }
   __syncthreads();
   if (warp == 0) {
     float g = fminf(gu[0][lane], a.limit);
@@ -162,6 +199,8 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(GateUpArgs a) {
     const size_t base = ((size_t)row * (a.k + 1) + slot) * a.inter;
     a.act_q[base + ob + lane] = q;
     if (lane == 0) a.act_s[base / 32 + ob / 32] = sc;
+  }
+  __syncthreads();
   }
 }
 
@@ -186,52 +225,85 @@ __global__ void __launch_bounds__(256) moe_down_kernel(DownArgs a) {
   const int row = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int inter = a.inter, KB = inter / 32, slots = a.k + a.has_shared;
-  for (int i = threadIdx.x; i < slots * inter; i += 256) {
-    const size_t o = (size_t)row * (a.k + 1) * inter + i;
-    asm_[sm_pad(i)] = e4m3_to_f32(a.act_q[o]) * ue8m0_to_f32(a.act_s[o / 32]);
+  {
+    const size_t o = (size_t)row * (a.k + 1) * inter;
+    stage_fp8_to_smem(a.act_q + o, a.act_s + o / 32, slots * inter / 16, asm_, 256);
   }
   __syncthreads();
   const int64_t sfb = sf_bytes(a.d, KB);
   const int c4 = inter / 32, c8 = inter / 16;      // chunks per routed / shared slot
   const int items = a.k * c4 + (a.has_shared ? c8 : 0);
-  for (int cc = 0; cc < 2; ++cc) {
-    const int col = blockIdx.x * DN_COLS + warp * 2 + cc;
-    if (col >= a.d) break;
-    float acc = 0.f;
-    for (int it = lane; it < items; it += 32) {
-      float s = 0.f, sc;
-      if (it < a.k * c4) {
-        const int slot = it / c4, c = it - slot * c4;
-        const int e = a.ids[(size_t)row * a.k + slot];
-        uint4 wv = ldg_nc(a.w2 + ((size_t)e * a.d + col) * (inter / 2) + (size_t)c * 16);
-        sc = ue8m0_to_f32(__ldg(a.w2_sf + (size_t)e * sfb + sf_offset(col, c, KB)));
-        float f[32];
-        decode32_e2m1(wv, f);
-        const float4* x = reinterpret_cast<const float4*>(asm_ + sm_pad(slot * inter + c * 32));
+  for (int cb = blockIdx.x * DN_COLS; cb < a.d; cb += gridDim.x * DN_COLS) {
+    const int col0 = cb + warp * 2;
+    constexpr int U = 2;
+    float acc[2] = {0.f, 0.f};
+    for (int ib = lane; ib < items; ib += 32 * U) {
+      uint4 wv[U][2];
+      float sc[U][2];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float4 xv = x[j];
-          s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
-          s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
-        }
-      } else {
-        const int c = it - a.k * c4;
-        uint4 wv = ldg_nc(a.s2 + (size_t)col * inter + (size_t)c * 16);
-        sc = ue8m0_to_f32(__ldg(a.s2_sf + sf_offset(col, c >> 1, KB)));
-        float f[16];
-        decode16_e4m3(wv, f);
-        const float4* x = reinterpret_cast<const float4*>(asm_ + sm_pad(a.k * inter + c * 16));
+      for (int u = 0; u < U; ++u) {
+        const int it = ib + 32 * u;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float4 xv = x[j];
-          s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
-          s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+        for (int cc = 0; cc < 2; ++cc) {
+          const int col = col0 + cc;
+          if (it < items && col < a.d) {
+            if (it < a.k * c4) {
+              const int slot = it / c4, c = it - slot * c4;
+              const int e = a.ids[(size_t)row * a.k + slot];
+              wv[u][cc] = ldg_nc(a.w2 + ((size_t)e * a.d + col) * (inter / 2) + (size_t)c * 16);
+              sc[u][cc] = ue8m0_shifted(__ldg(a.w2_sf + (size_t)e * sfb + sf_offset(col, c, KB)), SFB_E2M1_RAW_EXP);
+            } else {
+              const int c = it - a.k * c4;
+              wv[u][cc] = ldg_nc(a.s2 + (size_t)col * inter + (size_t)c * 16);
+              sc[u][cc] = ue8m0_shifted(__ldg(a.s2_sf + sf_offset(col, c >> 1, KB)), SFB_E4M3_RAW_EXP);
+            }
+          } else { wv[u][cc] = make_uint4(0, 0, 0, 0); sc[u][cc] = 0.f; }
         }
       }
-      acc = fmaf(s, sc, acc);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int it = ib + 32 * u;
+        if (it >= items) break;
+        if (it < a.k * c4) {
+          const int slot = it / c4, c = it - slot * c4;
+          const float4* x = reinterpret_cast<const float4*>(asm_ + sm_pad(slot * inter + c * 32));
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            float f[32];
+            decode32_e2m1_raw(wv[u][cc], f);
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 xv = x[j];
+              s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
+              s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+            }
+            acc[cc] = fmaf(s, sc[u][cc], acc[cc]);
+          }
+        } else {
+          const int c = it - a.k * c4;
+          const float4* x = reinterpret_cast<const float4*>(asm_ + sm_pad(a.k * inter + c * 16));
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            float f[16];
+            decode16_e4m3_raw(wv[u][cc], f);
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float4 xv = x[j];
+              s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
+              s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+            }
+            acc[cc] = fmaf(s, sc[u][cc], acc[cc]);
+          }
+        }
+      }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) a.out[(size_t)row * a.d + col] = __float2bfloat16_rn(acc);
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      const float v = warp_sum(acc[cc]);
+      if (lane == 0 && col0 + cc < a.d) a.out[(size_t)row * a.d + col0 + cc] = __float2bfloat16_rn(v);
+    }
   }
 }
 
@@ -256,7 +328,10 @@ int sfb_moe_gate_up(const void* xq, const void* xs, const int* ids, const float*
   GateUpArgs a{(const uint8_t*)xq, (const uint8_t*)xs, ids, wts, (const uint8_t*)w13, (const uint8_t*)w13_sf,
                (const uint8_t*)s13, (const uint8_t*)s13_sf, (uint8_t*)act_q, (uint8_t*)act_s, n, k, d, inter, limit};
   const int slots = k + (s13 ? 1 : 0);
-  moe_gate_up_kernel<<<dim3(inter / 32, slots, n), 256, sizeof(float) * sm_pad(d), stream>>>(a);
+  int gx = inter / 32;
+  const int cap = (148 * 3 + slots * n - 1) / (slots * n);  // ~3 resident blocks per SM in total
+  if (gx > cap) gx = cap > 0 ? cap : 1;
+  moe_gate_up_kernel<<<dim3(gx, slots, n), 256, sizeof(float) * sm_pad(d), stream>>>(a);
   return SFB_CHECK_LAUNCH();
 }
 
@@ -269,7 +344,10 @@ int sfb_moe_down(const void* act_q, const void* act_s, const int* ids, const voi
   static bool done = false;
   if (!done) { cudaFuncSetAttribute(moe_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); done = true; }
   if (smem > 160 * 1024) return (int)cudaErrorInvalidValue;
-  moe_down_kernel<<<dim3((d + DN_COLS - 1) / DN_COLS, n), 256, smem, stream>>>(a);
+  int gx = (d + DN_COLS - 1) / DN_COLS;
+  const int cap = (148 * 2 + n - 1) / n;
+  if (gx > cap) gx = cap > 0 ? cap : 1;
+  moe_down_kernel<<<dim3(gx, n), 256, smem, stream>>>(a);
   return SFB_CHECK_LAUNCH();
 }
 

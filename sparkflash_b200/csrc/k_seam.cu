@@ -151,11 +151,17 @@ __global__ void __launch_bounds__(256) seam_b_kernel(SeamBArgs a) {
   const int row = blockIdx.y;
   __shared__ float tot[2 + MAX_MIX];
   const int nv = 2 + a.mix;
-  if (threadIdx.x < nv) {
-    const float* p = a.partials + (size_t)row * a.nblk * nv + threadIdx.x;
-    float s = 0.f;
-    for (int b = 0; b < a.nblk; ++b) s += p[(size_t)b * nv];
-    tot[threadIdx.x] = s;
+  {
+    // 8 warps x 32 lanes: warp w sums values v = w, w+8, .. ; lanes stride the blocks, then a fixed
+    // shuffle tree - the order depends only on nblk, never on the row count.
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int v = w; v < nv; v += 8) {
+      const float* p = a.partials + (size_t)row * a.nblk * nv + v;
+      float s = 0.f;
+      for (int b = lane; b < a.nblk; b += 32) s += p[(size_t)b * nv];
+      s = warp_sum(s);
+      if (lane == 0) tot[v] = s;
+    }
   }
   __syncthreads();
   const int hc = a.hc, d = a.d;

@@ -134,11 +134,17 @@ class Engine:
         self.graphs: dict[tuple[int, int], torch.cuda.CUDAGraph] = {}
         self.launches_per_step = 0
         self._counting = False
+        self.min_bucket = 1024
+        self.debug: dict[str, torch.Tensor] | None = None  # set to {} (graphs off) to keep intermediates
 
     # ---- bookkeeping -----------------------------------------------------------------------------------
     def _k(self):
         if self._counting:
             self.launches_per_step += 1
+
+    def _dbg(self, key: str, t: torch.Tensor, n: int) -> None:
+        if self.debug is not None:
+            self.debug[key] = t[:n].detach().clone()
 
     def check_status(self) -> None:
         st = self.status.tolist()
@@ -197,6 +203,7 @@ class Engine:
                 N.hsi_mark(self.cand_ids, cfg.candidate_topk_blocks, self.cand, mb, n)
                 self.launches_per_step += 2 if self._counting else 0
             N.select_topk(self.scores, self.row_pos, ratio, 1, max_len, cfg.index_topk, self.sel, self.sel_cnt, n); self._k()
+            self._dbg(f"L{l}.iscore", self.scores, n)
         has_c = ratio > 0
         N.attn_rows(self.qfull, self.qfull.stride(0), invf, self.row_lane, self.row_pos, kv.win_q[l], kv.win_s[l],
                     kv.ckv_q[owner] if has_c else None, kv.ckv_s[owner] if has_c else None,
@@ -239,12 +246,20 @@ class Engine:
                 N.tap_mean(self.h, self.taps[:, tap_i * cfg.hidden_size:], self.taps.stride(0), n, cfg.hc_mult,
                            cfg.hidden_size); self._k()
                 tap_i += 1
+            self._dbg(f"L{l}.attn_in", self.xn, n)
             self._attention(n, l, L, len_bucket)
+            self._dbg(f"L{l}.q", self.qfull, n); self._dbg(f"L{l}.o", self.attn_out, n)
+            self._dbg(f"L{l}.oa", self.oa, n); self._dbg(f"L{l}.attn_out", self.y_attn, n)
+            self._dbg(f"L{l}.sel", self.sel, n); self._dbg(f"L{l}.sel_cnt", self.sel_cnt, n)
             self._seam(n, k, self._reduce_parts(self.y_attn, n), L.hc_ffn_fn, L.hc_ffn_base, L.hc_ffn_scale,
                        L.ffn_norm); k += 1
+            self._dbg(f"L{l}.ffn_in", self.xn, n)
             self._ffn(n, L)
+            self._dbg(f"L{l}.ffn_out", self.y_ffn, n)
+            self._dbg(f"L{l}.route_ids", self.ids, n); self._dbg(f"L{l}.route_w", self.wts, n)
             y_prev = self._reduce_parts(self.y_ffn, n)
         self._seam(n, k, y_prev, None, None, None, w.norm, quant=False)
+        self._dbg("final_x", self.xn, n); self._dbg("final_h", self.h, n)
         N.gemv(N.WF_BF16, w.head, None, 2 * cfg.hidden_size, self.vl, cfg.hidden_size, n, xb=self.xn,
                out_f=self.logits); self._k()
         N.sample(self.logits, self.row_pos, self.temp, self.seed, None, self.best_val[self.rank], self.best_id[self.rank],
@@ -254,9 +269,10 @@ class Engine:
         N.sample_fold(self.best_val, self.best_id, self.world if self.comm is not None else 1, n, self.tokens_out); self._k()
 
     # ---- public step -------------------------------------------------------------------------------------
-    @staticmethod
-    def _bucket(max_pos: int) -> int:
-        b = 1024
+    def _bucket(self, max_pos: int) -> int:
+        """Context-length bucket a captured graph is valid for (grids of the indexer kernels are sized
+        by it); ``min_bucket`` pins one bucket for a whole run."""
+        b = self.min_bucket
         while b < max_pos + 1:
             b *= 2
         return b

@@ -1,0 +1,299 @@
+"""GPU tests: every rows-step kernel against a plain PyTorch fp32 reference of the same op, and the
+whole tiny model against the CPU oracle (reference test strategy: CPU twins vs device kernels,
+batch_exactness.rs / verify_rows.rs style invariance checks)."""
+import pytest
+import torch
+
+from sparkflash_b200 import codecs as C
+from sparkflash_b200.config import tiny_config
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    from sparkflash_b200.models.deepseek_v41 import oracle as O, prepare as P, weights as W
+    cfg = tiny_config()
+    ck = W.synthetic_checkpoint(cfg, 0)
+    w = W.dequantize_checkpoint(ck, cfg)
+    return cfg, ck, w, O.Oracle(cfg, w), P.prepare_from_checkpoint(ck, cfg)
+
+
+def _prompt(cfg, n, seed=1):
+    return torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+# ---- kernels -----------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("wfmt,N_,K,n", [(0, 96, 256, 1), (0, 40, 128, 5), (1, 64, 256, 3), (1, 130, 512, 9),
+                                         (2, 48, 256, 2), (2, 1000, 64, 7)])
+def test_gemv_matches_fp32_reference(wfmt, N_, K, n):
+    from sparkflash_b200.ops import native as N
+    g = torch.Generator().manual_seed(wfmt * 100 + N_)
+    w = torch.randn(N_, K, generator=g) * 0.05
+    x = torch.randn(n, K, generator=g)
+    dev = "cuda"
+    out = torch.zeros(n, N_, dtype=torch.float32, device=dev)
+    if wfmt == 0:
+        q, s = C.weight_quant_fp8_block32(w)
+        wd = C.weight_dequant_fp8_block32(q, s)
+        sf = C.scales_to_prepared(s, N_, 32)
+        xq, xs = C.act_quant_fp8(x)
+        ref = C.act_dequant_fp8(xq, xs) @ wd.t()
+        N.gemv(0, q.to(dev), sf.to(dev), K, N_, K, n, xq=xq.to(dev), xs=xs.to(dev), out_f=out)
+    elif wfmt == 1:
+        q, s = C.weight_quant_fp4_row32(w)
+        wd = C.weight_dequant_fp4_row32(q, s)
+        sf = C.scales_to_prepared(s, N_, 1)
+        xb = x.to(torch.bfloat16)
+        ref = C.act_roundtrip_fp8(xb.float()) @ wd.t()
+        N.gemv(1, q.to(dev), sf.to(dev), K // 2, N_, K, n, xb=xb.to(dev), x_quant=True, out_f=out)
+    else:
+        wb = w.to(torch.bfloat16)
+        xb = x.to(torch.bfloat16)
+        ref = xb.float() @ wb.float().t()
+        N.gemv(2, wb.to(dev), None, 2 * K, N_, K, n, xb=xb.to(dev), out_f=out)
+    torch.cuda.synchronize()
+    err = (out.cpu() - ref).abs().max().item()
+    assert err <= 2e-4 * ref.abs().max().item() + 1e-6, err
+
+
+def test_gemv_grouped_and_batch_invariant():
+    from sparkflash_b200.ops import native as N
+    g = torch.Generator().manual_seed(5)
+    groups, N_, K, n = 2, 64, 128, 6
+    w = torch.randn(groups * N_, K, generator=g) * 0.05
+    q, s = C.weight_quant_fp8_block32(w)
+    wd = C.weight_dequant_fp8_block32(q, s)
+    sf = C.scales_to_prepared(s, groups * N_, 32).cuda()
+    xb = torch.randn(n, groups * K, generator=g).to(torch.bfloat16)
+    out = torch.zeros(n, groups * N_, dtype=torch.float32, device="cuda")
+    N.gemv(0, q.cuda(), sf, K, N_, K, n, groups=groups, xb=xb.cuda(), out_f=out)
+    ref = torch.cat([xb.float()[:, gi * K:(gi + 1) * K] @ wd[gi * N_:(gi + 1) * N_].t() for gi in range(groups)], 1)
+    assert (out.cpu() - ref).abs().max() <= 2e-4 * ref.abs().max()
+    one = torch.zeros(1, groups * N_, dtype=torch.float32, device="cuda")
+    for r in range(n):
+        N.gemv(0, q.cuda(), sf, K, N_, K, 1, groups=groups, xb=xb[r:r + 1].cuda(), out_f=one)
+        assert torch.equal(one[0], out[r]), "row bits depend on the batch"
+
+
+def test_select_topk_rules():
+    from sparkflash_b200.ops import native as N
+    n, L, K = 5, 300, 16
+    g = torch.Generator().manual_seed(3)
+    sc = torch.randn(n, 512, generator=g)
+    sc[1, :L] = 1.0                      # all ties: lowest indices win
+    sc[2, 10:290] = float("-inf")        # fewer finite entries than K
+    sc[3, 5] = sc[3, 200] = sc[3, 100] = 9.0
+    pos = torch.full((n,), L - 1, dtype=torch.int32)
+    pos[4] = 7                            # short row
+    ids = torch.zeros(n, K, dtype=torch.int32, device="cuda")
+    cnt = torch.zeros(n, dtype=torch.int32, device="cuda")
+    N.select_topk(sc.cuda(), pos.cuda(), 1, 1, 512, K, ids, cnt, n)
+    torch.cuda.synchronize()
+    for r in range(n):
+        ln = int(pos[r]) + 1
+        vals = sc[r, :ln].tolist()
+        order = sorted(range(ln), key=lambda i: (-vals[i], i))
+        want = sorted(i for i in order[:K] if vals[i] > float("-inf"))
+        got = ids[r, :int(cnt[r])].tolist()
+        assert got == want, (r, got, want)
+        assert all(v == -1 for v in ids[r, int(cnt[r]):].tolist())
+
+
+def test_router_matches_oracle(tiny):
+    from sparkflash_b200.ops import native as N
+    cfg, ck, w, orc, dw = tiny
+    g = torch.Generator().manual_seed(7)
+    n, E, k = 6, 24, 4
+    dots = torch.randn(n, E, generator=g) * 2
+    bias = torch.randn(E, generator=g) * 0.1
+    ids = torch.zeros(n, k, dtype=torch.int32, device="cuda")
+    wts = torch.zeros(n, k, dtype=torch.float32, device="cuda")
+    N.router_topk(dots.cuda(), bias.cuda(), None, None, ids, wts, n, E, k, 1.5)
+    s = torch.sqrt(torch.nn.functional.softplus(dots))
+    for r in range(n):
+        pick = sorted(torch.topk(s[r] + bias, k).indices.tolist())
+        assert ids[r].tolist() == pick
+        ww = s[r][pick]
+        ww = ww / (ww.sum() + 1e-20) * 1.5
+        assert torch.allclose(wts[r].cpu(), ww, rtol=1e-5, atol=1e-6)
+
+
+def test_sampler_matches_oracle():
+    from sparkflash_b200.models.deepseek_v41 import oracle as O
+    from sparkflash_b200.ops import native as N
+    g = torch.Generator().manual_seed(9)
+    n, V = 3, 500
+    logits = torch.randn(n, V, generator=g)
+    pos = torch.tensor([4, 17, 900], dtype=torch.int32)
+    temp = torch.tensor([0.0, 1.0, 0.7], dtype=torch.float32)
+    seed = torch.tensor([1, 2, 3], dtype=torch.int64)
+    bv = torch.zeros(n, device="cuda"); bi = torch.zeros(n, dtype=torch.int32, device="cuda")
+    N.sample(logits.cuda(), pos.cuda(), temp.cuda(), seed.cuda(), None, bv, bi, n, V, 0)
+    for r in range(n):
+        assert int(bi[r]) == O.sample_token(logits[r], float(temp[r]), int(seed[r]), int(pos[r]) + 1)
+
+
+# ---- whole model ---------------------------------------------------------------------------------------------
+def test_engine_matches_oracle_token_by_token(tiny):
+    """Positions whose whole history stays within one warp's accumulation order are bit-close; later
+    ones differ by reassociation plus bf16 re-rounding of the residual stream, so the bar is the kind
+    the reference uses for its served gate (mean error, top-1 agreement), not equality."""
+    from sparkflash_b200.models.deepseek_v41 import engine as E
+    cfg, ck, w, orc, dw = tiny
+    eng = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, use_graphs=False)
+    prompt = _prompt(cfg, 40)
+    st = orc.new_state()
+    agree, mean_err, worst = 0, [], 0.0
+    for pos, tok in enumerate(prompt):
+        ol = orc.step(st, tok)
+        eng.step([tok], [0], [pos])
+        el = eng.logits[0].cpu()
+        scale = ol.abs().max().item()
+        err = (el - ol).abs()
+        if pos < 4:
+            assert err.max().item() < 1e-3 * scale, (pos, err.max().item())
+        mean_err.append(err.mean().item() / scale)
+        worst = max(worst, err.max().item() / scale)
+        agree += int(el.argmax()) == int(ol.argmax())
+    eng.check_status()
+    assert sum(mean_err) / len(mean_err) < 0.03, sum(mean_err) / len(mean_err)
+    assert worst < 0.6, worst
+    assert agree >= 0.7 * len(prompt), agree
+
+
+def test_seam_matches_oracle_math():
+    from sparkflash_b200.config import ModelConfig
+    from sparkflash_b200.models.deepseek_v41 import oracle as O
+    from sparkflash_b200.ops import native as N
+    for d, n, W in ((256, 3, 1), (5120, 2, 2)):
+        cfg = ModelConfig(hidden_size=d)
+        hc, mix = 4, 24
+        g = torch.Generator().manual_seed(d)
+        h = (torch.randn(n, hc, d, generator=g) * 0.5).to(torch.bfloat16)
+        ys = [(torch.randn(n, d, generator=g) * 0.3).to(torch.bfloat16) for _ in range(W)]
+        fn = torch.randn(mix, hc * d, generator=g) * 0.05
+        base = torch.randn(mix, generator=g) * 0.1
+        scale = torch.tensor([1.0, 0.9, 1.1])
+        norm_w = 1 + 0.05 * torch.randn(d, generator=g)
+        prev = torch.zeros(n, N.coef_stride(hc))
+        ref_h, ref_xn, ref_coef = [], [], []
+        for r in range(n):
+            pre, post, comb = O.hc_coeffs(h[r].float() * 0.7, fn, scale, base, cfg)  # any valid coefficients
+            prev[r] = torch.cat([pre, post, comb.flatten()])
+            y = O.bf(sum(y_[r].float() for y_ in ys))
+            hn = O.hc_post(y, h[r].float(), post, comb)
+            p2, q2, c2 = O.hc_coeffs(hn, fn, scale, base, cfg)
+            ref_h.append(hn); ref_coef.append(torch.cat([p2, q2, c2.flatten()]))
+            ref_xn.append(O.rmsnorm(O.hc_pre(hn, pre), norm_w, cfg.norm_eps))
+        dev = "cuda"
+        hd_ = h.clone().to(dev)
+        nblk = N.seam_nblk(d)
+        xhat = torch.zeros(n, d, dtype=torch.bfloat16, device=dev)
+        partials = torch.zeros(n, nblk, 2 + mix, device=dev)
+        coef = torch.zeros(n, N.coef_stride(hc), device=dev)
+        xn = torch.zeros(n, d, dtype=torch.bfloat16, device=dev)
+        xq = torch.zeros(n, d, dtype=torch.uint8, device=dev)
+        xs = torch.zeros(n, d // 32, dtype=torch.uint8, device=dev)
+        prev_d = prev.to(dev)
+        N.seam(hd_, [y_.to(dev) for y_ in ys], prev_d, prev_d, prev_d.stride(0), fn.to(dev), xhat, partials,
+               norm_w.to(dev), scale.to(dev), base.to(dev), coef, xn, xq, xs, n, hc, d, cfg.hc_sinkhorn_iters,
+               cfg.norm_eps, cfg.hc_eps)
+        torch.cuda.synchronize()
+        rh = torch.stack(ref_h)
+        assert (hd_.cpu().float() - rh).abs().max() <= 2 ** -7 * rh.abs().max(), "residual copies"
+        assert torch.allclose(coef.cpu(), torch.stack(ref_coef), rtol=2e-4, atol=2e-5)
+        ref = torch.stack(ref_xn)
+        got = xn.cpu().float()
+        assert (got - ref).abs().max() <= 2 ** -7 * ref.abs().max()  # one bf16 ulp at most
+        rq, rs = C.act_quant_fp8(got)
+        assert torch.equal(xq.cpu(), rq) and torch.equal(xs.cpu(), rs)
+
+
+def test_attention_rows_matches_fp32_reference():
+    from sparkflash_b200.models.deepseek_v41 import oracle as O
+    from sparkflash_b200.config import full_config
+    from sparkflash_b200.ops import native as N
+    cfg = full_config()
+    hd, rd, heads, window, ring, K = 512, 64, 4, 128, 256, 512
+    g = torch.Generator().manual_seed(11)
+    lanes, n = 2, 3
+    pos = torch.tensor([700, 5, 131], dtype=torch.int32)
+    lane = torch.tensor([0, 1, 1], dtype=torch.int32)
+    invf = O.rope_inv_freq(cfg, True)
+    win = torch.randn(lanes, ring, hd, generator=g) * 0.7
+    wq, ws = C.act_quant_fp8(win)
+    entries = 400
+    ckv = torch.randn(lanes, entries, hd, generator=g) * 0.7
+    cq, cs = C.kv_quant_fp4(ckv)
+    sel = torch.full((n, K), -1, dtype=torch.int32)
+    cnt = torch.zeros(n, dtype=torch.int32)
+    for r in range(n):
+        clen = min(entries, int(pos[r]) + 1)
+        k = min(K, clen, 300)
+        ids = torch.randperm(clen, generator=g)[:k].sort().values
+        sel[r, :k] = ids.int(); cnt[r] = k
+    q = (torch.randn(n, heads * hd, generator=g) * 0.5).to(torch.bfloat16)
+    sink = torch.randn(heads, generator=g)
+    out = torch.zeros(n, heads * hd, dtype=torch.bfloat16, device="cuda")
+    dev = "cuda"
+    N.attn_rows(q.to(dev), heads * hd, invf.to(dev), lane.to(dev), pos.to(dev), wq.to(dev), ws.to(dev),
+                C.pack_nibbles(cq).to(dev), cs.to(dev), sel.to(dev), cnt.to(dev), K, sink.to(dev), out, n, heads,
+                hd, rd, window, ring, hd ** -0.5)
+    torch.cuda.synchronize()
+    wd = C.act_dequant_fp8(wq, ws)
+    cd = C.kv_dequant_fp4(cq, cs)
+    for r in range(n):
+        p, L = int(pos[r]), int(lane[r])
+        keys = [wd[L, t % ring] for t in range(max(0, p - window + 1), p + 1)]
+        keys += [cd[L, j] for j in sel[r, :int(cnt[r])].tolist()]
+        Kmat = torch.stack(keys)
+        qq = O.apply_rope(q[r].float().view(heads, hd), p, invf)
+        s = (qq @ Kmat.t()) * hd ** -0.5
+        m = s.max(-1, keepdim=True).values
+        e = torch.exp(s - m)
+        o = O.bf((e @ Kmat) / (e.sum(-1, keepdim=True) + torch.exp(sink.view(heads, 1) - m)))
+        o = O.apply_rope(o, p, invf, inverse=True)
+        got = out[r].cpu().float().view(heads, hd)
+        assert (got - o).abs().max() <= 0.02 * o.abs().max() + 1e-4, (r, (got - o).abs().max(), o.abs().max())
+
+
+def test_rows_step_is_batch_invariant_and_graph_replay_is_exact(tiny):
+    from sparkflash_b200.models.deepseek_v41 import engine as E
+    cfg, ck, w, orc, dw = tiny
+    prompt = _prompt(cfg, 37, seed=4)
+    a = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, use_graphs=False)
+    b = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, use_graphs=True)
+    single = []
+    for pos, tok in enumerate(prompt):
+        a.step([tok], [0], [pos])
+        single.append(a.logits[0].clone())
+    pos = 0
+    chunked = []
+    for c in (16, 5, 16):
+        b.step(prompt[pos:pos + c], [1] * c, list(range(pos, pos + c)))
+        chunked += [b.logits[i].clone() for i in range(c)]
+        pos += c
+    for i, (x, y) in enumerate(zip(single, chunked)):
+        assert torch.equal(x, y), f"row {i} differs between 1-row steps and chunked rows steps"
+    a.check_status(); b.check_status()
+
+
+def test_generate_greedy_matches_oracle_prefix(tiny):
+    from sparkflash_b200.models.deepseek_v41 import engine as E
+    cfg, ck, w, orc, dw = tiny
+    eng = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16)
+    prompt = _prompt(cfg, 32)
+    toks, logits = eng.generate(prompt, 16, collect_logits=True)
+    ref, ref_logits = orc.generate(prompt, 16)
+    # free-running generations stay comparable only while the tokens agree
+    same = 0
+    for a, b in zip(toks, ref):
+        if a != b:
+            break
+        same += 1
+    assert same >= 1
+    for i in range(same):
+        scale = ref_logits[i].abs().max().item()
+        err = (logits[i].cpu() - ref_logits[i]).abs()
+        assert err.mean().item() < 0.03 * scale and err.max().item() < 0.5 * scale
