@@ -6,7 +6,7 @@
 // same shapes with tcgen05; this file is also the fallback for shapes it does not take.
 //
 // Weight formats: MXFP8 (E4M3, one UE8M0 scale per row per 32 K) and MXFP4 (packed E2M1, same
-// scales), both with scales in the prepared 128x4-atom order (codecs.h sf_offset); plain bf16.
+// scales), here with the scales row-major [rows, K/32]; plain bf16.
 // Activations: per-32 FP8 (codes + row-major scales) or bf16.
 //
 // Reference behaviour: kernels/opt_gemv_sm121.cu:418-435,732-740 (decode MXFP8 GEMV, rows variants),
@@ -22,7 +22,8 @@ constexpr int GV_ROWS = GV_WARPS * GV_RPW;   // output rows per block
 
 struct GemvArgs {
   const uint8_t* w;        // payload, row-major [groups*N, row_bytes]
-  const uint8_t* sf;       // prepared scales for the whole [groups*N, K] matrix (null for bf16 weights)
+  const uint8_t* sf;       // row-major scales [groups*N, K/32] (null for bf16 weights); consecutive lanes read
+                           // consecutive bytes, unlike the 128x4-atom order the tensor-core arm consumes
   int64_t row_bytes;
   int N;                   // output rows per group
   int K;                   // reduction length per group
@@ -145,7 +146,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
             if (ok) {
               wv[u][i] = ldg_nc(a.w + gr * a.row_bytes + (int64_t)c * 16);
               sc[u][i] = WF == 2 ? 1.f
-                                 : ue8m0_shifted(__ldg(a.sf + sf_offset(gr, (c * EPC) >> 5, a.KB)),
+                                 : ue8m0_shifted(__ldg(a.sf + gr * a.KB + ((c * EPC) >> 5)),
                                                  WF == 0 ? SFB_E4M3_RAW_EXP : SFB_E2M1_RAW_EXP);
             } else {
               wv[u][i] = make_uint4(0, 0, 0, 0);

@@ -86,9 +86,9 @@ struct GateUpArgs {
   const int* ids;         // [n, k]
   const float* wts;       // [n, k]
   const uint8_t* w13;     // routed: [E, 2, inter, d/2] packed e2m1
-  const uint8_t* w13_sf;  // routed: [E, 2, sf_bytes(inter, d/32)]
+  const uint8_t* w13_sf;  // routed: [E, 2, inter, d/32] row-major scales
   const uint8_t* s13;     // shared: [2, inter, d] e4m3 (null when there is no shared expert)
-  const uint8_t* s13_sf;  // shared: [2, sf_bytes(inter, d/32)]
+  const uint8_t* s13_sf;  // shared: [2, inter, d/32]
   uint8_t* act_q;         // [n, k+1, inter] e4m3
   uint8_t* act_s;         // [n, k+1, inter/32]
   int n, k, d, inter;
@@ -115,7 +115,7 @@ __device__ __forceinline__ void dot_rows(const uint8_t* const* wrow, const uint8
       for (int i = 0; i < NR; ++i) {
         if (c < chunks) {
           wv[u][i] = ldg_nc(wrow[i] + (size_t)c * 16);
-          sc[u][i] = ue8m0_shifted(__ldg(sf[i] + sf_offset(sf_row[i], (c * EPC) >> 5, KB)),
+          sc[u][i] = ue8m0_shifted(__ldg(sf[i] + sf_row[i] * KB + ((c * EPC) >> 5)),
                                    FP4 ? SFB_E2M1_RAW_EXP : SFB_E4M3_RAW_EXP);
         } else { wv[u][i] = make_uint4(0, 0, 0, 0); sc[u][i] = 0.f; }
       }
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(GateUpArgs a) {
   const bool shared_slot = slot == a.k;
   float weight = 1.f;
   const uint8_t *w1, *w3, *sf1, *sf3;
-  const int64_t sfb = sf_bytes(a.inter, KB);
+  const int64_t sfb = (int64_t)a.inter * KB;  // row-major scales per matrix
   if (shared_slot) {
     w1 = a.s13; w3 = a.s13 + (size_t)a.inter * d;
     sf1 = a.s13_sf; sf3 = a.s13_sf + sfb;
@@ -210,9 +210,9 @@ struct DownArgs {
   const uint8_t* act_s;   // [n, k+1, inter/32]
   const int* ids;         // [n, k]
   const uint8_t* w2;      // routed: [E, d, inter/2]
-  const uint8_t* w2_sf;   // routed: [E, sf_bytes(d, inter/32)]
+  const uint8_t* w2_sf;   // routed: [E, d, inter/32]
   const uint8_t* s2;      // shared: [d, inter] e4m3
-  const uint8_t* s2_sf;   // shared: sf_bytes(d, inter/32)
+  const uint8_t* s2_sf;   // shared: [d, inter/32]
   __nv_bfloat16* out;     // [n, d] this rank's partial
   int n, k, d, inter, has_shared;
 };
@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(256) moe_down_kernel(DownArgs a) {
     stage_fp8_to_smem(a.act_q + o, a.act_s + o / 32, slots * inter / 16, asm_, 256);
   }
   __syncthreads();
-  const int64_t sfb = sf_bytes(a.d, KB);
+  const int64_t sfb = (int64_t)a.d * KB;  // row-major scales per expert
   const int c4 = inter / 32, c8 = inter / 16;      // chunks per routed / shared slot
   const int items = a.k * c4 + (a.has_shared ? c8 : 0);
   for (int cb = blockIdx.x * DN_COLS; cb < a.d; cb += gridDim.x * DN_COLS) {
@@ -251,11 +251,11 @@ __global__ void __launch_bounds__(256) moe_down_kernel(DownArgs a) {
               const int slot = it / c4, c = it - slot * c4;
               const int e = a.ids[(size_t)row * a.k + slot];
               wv[u][cc] = ldg_nc(a.w2 + ((size_t)e * a.d + col) * (inter / 2) + (size_t)c * 16);
-              sc[u][cc] = ue8m0_shifted(__ldg(a.w2_sf + (size_t)e * sfb + sf_offset(col, c, KB)), SFB_E2M1_RAW_EXP);
+              sc[u][cc] = ue8m0_shifted(__ldg(a.w2_sf + (size_t)e * sfb + (size_t)col * KB + c), SFB_E2M1_RAW_EXP);
             } else {
               const int c = it - a.k * c4;
               wv[u][cc] = ldg_nc(a.s2 + (size_t)col * inter + (size_t)c * 16);
-              sc[u][cc] = ue8m0_shifted(__ldg(a.s2_sf + sf_offset(col, c >> 1, KB)), SFB_E4M3_RAW_EXP);
+              sc[u][cc] = ue8m0_shifted(__ldg(a.s2_sf + (size_t)col * KB + (c >> 1)), SFB_E4M3_RAW_EXP);
             }
           } else { wv[u][cc] = make_uint4(0, 0, 0, 0); sc[u][cc] = 0.f; }
         }

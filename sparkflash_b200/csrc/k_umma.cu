@@ -1,0 +1,386 @@
+// Tensor-core arm: block-scaled MXFP8 / MXFP4 (W4A8) skinny GEMM on tcgen05 with TMEM accumulators.
+//
+//   out[token, col] = sum_k  W[col, k] * X[token, k]        W: E4M3 or E2M1 + UE8M0/32,  X: E4M3 + UE8M0/32
+//
+// "Swap-AB": the weight rows are the M = 128 operand of `tcgen05.mma.kind::mxf8f6f4.block_scale`
+// and the (few) token rows are N = 16..128, so one CTA streams a 128-row weight tile through the
+// whole reduction at full TMA rate no matter how few tokens there are, and every token is an
+// independent accumulator column (row i's result does not depend on which other tokens share the
+// launch).  FP4 weights stay packed in HBM; TMA unpacks them into 8-bit containers on the way into
+// shared memory (16U4_ALIGN16B), and the tensor core widens them - the model's W4A8 arithmetic.
+//
+// Roles inside a CTA of 192 threads: warp 0 = TMA producer (one elected lane), warp 1 = TMEM
+// allocator + MMA issuer (one elected lane), warps 2..5 = epilogue (each owns the 32 TMEM lanes
+// its warp id selects).  Stages are handed over with mbarriers; every wait is bounded and reports
+// through the status word instead of spinning forever.  No cluster launch, no multicast.
+//
+// Split-K (for shapes with few weight tiles) writes fp32 partials to a scratch buffer; the CTA
+// that arrives last at the tile's ticket adds the splits in index order, so the result does not
+// depend on arrival order.
+//
+// Reference behaviour replaced: kernels/opt_gemv_sm121.cu:967-969 (decode GEMV on warp-level
+// block-scaled MMA), kernels/opt_mma_sm121.cu (128x128 bulk GEMMs), kernels/opt_moe_sm121.cu.
+#include <cuda.h>
+
+#include "k_common.cuh"
+
+namespace sfb {
+
+constexpr int UM_THREADS = 192;
+constexpr int UM_BK = 128;        // K elements (= bytes in shared memory) per stage
+constexpr int UM_STAGES = 4;
+constexpr int UM_A_BYTES = 128 * UM_BK;  // 16 KiB
+constexpr uint32_t UM_SPIN_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false after UM_SPIN_LIMIT polls (several hundred milliseconds).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < UM_SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bs(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                          uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major shared-memory matrix descriptor. SWIZZLE_128B: rows of 128 bytes, 8-row groups 1024 bytes
+// apart (SBO); no swizzle (scale-factor atoms): 8 rows x 16 bytes per core matrix, 128 bytes apart.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t sbo_bytes, uint32_t lbo_bytes, uint32_t layout) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fff);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;              // descriptor version for sm_100
+  d |= (uint64_t)(layout & 7) << 61;   // 2 = SWIZZLE_128B, 0 = none
+  return d;
+}
+
+// instruction descriptor for kind::mxf8f6f4.block_scale (see the bit layout in the file header of
+// the CUTLASS sm100 descriptor definitions): formats E4M3 = 0, E2M1 = 5; UE8M0 scales.
+__host__ __device__ inline uint32_t make_idesc(int a_fmt, int b_fmt, int M, int N) {
+  uint32_t d = 0;
+  d |= (uint32_t)(a_fmt & 7) << 7;
+  d |= (uint32_t)(b_fmt & 7) << 10;
+  d |= (uint32_t)((N >> 3) & 63) << 17;
+  d |= 1u << 23;                       // scale format UE8M0
+  d |= (uint32_t)((M >> 4) & 31) << 24;
+  return d;
+}
+
+enum UmmaMode : int { UM_DENSE = 0, UM_GATE_UP = 1, UM_DOWN = 2 };
+
+struct UmmaArgs {
+  // A (weights): rows x K through tmapA; scale atoms (128 rows x 4 k-blocks, 512 bytes each)
+  const uint8_t* sfa;         // atom (ra, ka) at ((ra * katoms_a) + ka) * 512
+  int katoms_a;               // atoms along K of the A matrix
+  // B (activations): token rows x K_total through tmapB; scale atoms likewise
+  const uint8_t* sfb;
+  int katoms_b;
+  int n;                      // valid token rows
+  int K;                      // reduction length per item (multiple of 128)
+  int a_fp4;
+  int mode;
+  // dense / grouped
+  int N;                      // output columns per group (multiple of 128)
+  int groups;                 // group g: A rows g*N.., B k-offset g*K, out column g*N..
+  // split-K
+  int splits;
+  float* scratch;             // [splits, tiles_total, 128, NP] fp32
+  unsigned int* tickets;      // [tiles_total], zero before the launch; reset by the last CTA
+  // outputs [n, out_stride]
+  __nv_bfloat16* out_b;
+  float* out_f;
+  int64_t out_stride;
+  // MoE (gate_up / down): slot table
+  const int* ids;             // [n_tok, k] expert ids
+  const float* wts;           // [n_tok, k]
+  int top_k, slots;           // slots = top_k + shared
+  int inter;                  // local intermediate width
+  int rows_per_expert;        // rows of one expert's block in tmapA
+  int shared_row0;            // first row of the shared expert's block in tmapA2 (second map)
+  uint8_t* act_q;             // gate_up out: [n_tok, slots, inter]
+  uint8_t* act_s;             //              [n_tok, slots, inter/32] row-major
+  uint8_t* act_sf;            //              atoms: rows = n_tok*slots, kb = inter/32
+  float limit;
+  Status* status;
+};
+
+template <int NP>  // token columns per accumulator (16, 32, 64, 128)
+struct UmmaSmem {
+  alignas(1024) uint8_t a[UM_STAGES][UM_A_BYTES];
+  alignas(1024) uint8_t b[UM_STAGES][NP * UM_BK];
+  alignas(128) uint8_t sfa[UM_STAGES][512];
+  alignas(128) uint8_t sfb[UM_STAGES][512];
+  alignas(8) uint64_t full[UM_STAGES];
+  alignas(8) uint64_t empty[UM_STAGES];
+  alignas(8) uint64_t acc_full;
+  uint32_t tmem_base;
+  int last_flag;
+  int fail;
+};
+
+template <int NP>
+__global__ void __launch_bounds__(UM_THREADS, 1)
+umma_dense_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  UmmaSmem<NP>& S = *reinterpret_cast<UmmaSmem<NP>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x;           // 128-row tile inside the group
+  const int split = blockIdx.y;
+  const int g = blockIdx.z;
+  const int ksteps_total = a.K / UM_BK;
+  const int ks0 = (int)((int64_t)ksteps_total * split / a.splits);
+  const int ks1 = (int)((int64_t)ksteps_total * (split + 1) / a.splits);
+  const int nks = ks1 - ks0;
+  const int a_row0 = g * a.N + tile * 128;
+  constexpr uint32_t TMEM_COLS = NP + 16 <= 32 ? 32 : (NP + 16 <= 64 ? 64 : (NP + 16 <= 128 ? 128 : 256));
+  // bytes TMA reports per stage: packed FP4 counts 4 bits per element although it lands in 8-bit containers
+  const uint32_t STAGE_TX = (a.a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 1024;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
+    mbar_init(&S.acc_full, 1);
+    S.fail = 0;
+    S.last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = S.tmem_base;
+  const uint32_t t_acc = tmem;               // NP fp32 columns
+  const uint32_t t_sfa = tmem + NP;          // 2 x 4 columns
+  const uint32_t t_sfb = tmem + NP + 8;      // 2 x 4 columns
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < nks; ++i) {
+        const int s = i % UM_STAGES;
+        if (i >= UM_STAGES && !mbar_wait(&S.empty[s], ((i / UM_STAGES) - 1) & 1)) { S.fail = 1; break; }
+        const int ks = ks0 + i;
+        mbar_expect_tx(&S.full[s], STAGE_TX);
+        tma_load_2d(S.a[s], &tmapA, ks * UM_BK, a_row0, &S.full[s]);
+        tma_load_2d(S.b[s], &tmapB, g * a.K + ks * UM_BK, 0, &S.full[s]);
+        bulk_load(S.sfa[s], a.sfa + ((size_t)(a_row0 >> 7) * a.katoms_a + ks) * 512, 512, &S.full[s]);
+        bulk_load(S.sfb[s], a.sfb + ((size_t)(g * (a.K / UM_BK) + ks)) * 512, 512, &S.full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(a.a_fp4 ? 5 : 0, 0, 128, NP);
+      bool ok = true;
+      for (int i = 0; i < nks && ok; ++i) {
+        const int s = i % UM_STAGES;
+        if (!mbar_wait(&S.full[s], (i / UM_STAGES) & 1)) { S.fail = 2; ok = false; break; }
+        tc_fence_after();
+        const uint32_t sf_slot = (uint32_t)(i & 1) * 4;
+        tc_cp_sf(t_sfa + sf_slot, make_desc(smem_u32(S.sfa[s]), 128, 0, 0));
+        tc_cp_sf(t_sfb + sf_slot, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
+        const uint32_t a_addr = smem_u32(S.a[s]), b_addr = smem_u32(S.b[s]);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t ad = make_desc(a_addr + kk * 32, 1024, 16, 2);
+          const uint64_t bd = make_desc(b_addr + kk * 32, 1024, 16, 2);
+          const uint32_t id = idesc | ((uint32_t)kk << 29) | ((uint32_t)kk << 4);  // scale-factor byte ids
+          tc_mma_bs(t_acc, ad, bd, id, t_sfa + sf_slot, t_sfb + sf_slot, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&S.empty[s]);   // frees this stage's shared memory once the MMAs have read it
+      }
+      tc_commit(&S.acc_full);     // arrives even after a failed wait so the epilogue never hangs
+    }
+  } else {
+    // ---- epilogue: warp w owns TMEM lanes 32*(w%4) .. +31 = weight rows of the tile ----
+    const int q = warp & 3;
+    const bool got = mbar_wait(&S.acc_full, 0);
+    tc_fence_after();
+    const int col = a_row0 + q * 32 + lane;     // output column (row of A)
+    const bool single = a.splits == 1;
+    const int tile_id = g * gridDim.x + tile;
+    float* part = a.scratch ? a.scratch + (((size_t)split * gridDim.x * gridDim.z + tile_id) * 128 + q * 32 + lane) * NP : nullptr;
+#pragma unroll
+    for (int c0 = 0; c0 < NP; c0 += 16) {
+      uint32_t v[16];
+      tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0, v);
+      tc_wait_ld();
+      if (!got || S.fail) continue;
+      if (single) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int tok = c0 + j;
+          if (tok < a.n) {
+            const float f = __uint_as_float(v[j]);
+            const int64_t o = (int64_t)tok * a.out_stride + col;
+            if (a.out_b) a.out_b[o] = __float2bfloat16_rn(f);
+            if (a.out_f) a.out_f[o] = f;
+          }
+        }
+      } else {
+        float4* p4 = reinterpret_cast<float4*>(part + c0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          p4[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                              __uint_as_float(v[4 * j + 3]));
+      }
+    }
+    if (!single) {
+      // last-arriving split of this tile reduces all splits in index order
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        const unsigned int prev = atomicAdd(&a.tickets[tile_id], 1u);
+        S.last_flag = (prev == (unsigned int)a.splits - 1) ? 1 : 0;
+        if (S.last_flag) a.tickets[tile_id] = 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (S.last_flag) {
+        __threadfence();
+        for (int tok = 0; tok < a.n; ++tok) {
+          float s = 0.f;
+          for (int sp = 0; sp < a.splits; ++sp)
+            s += a.scratch[(((size_t)sp * gridDim.x * gridDim.z + tile_id) * 128 + q * 32 + lane) * NP + tok];
+          const int64_t o = (int64_t)tok * a.out_stride + col;
+          if (a.out_b) a.out_b[o] = __float2bfloat16_rn(s);
+          if (a.out_f) a.out_f[o] = s;
+        }
+      }
+    }
+    if ((!got || S.fail) && lane == 0 && q == 0) status_set(a.status, ST_TIMEOUT, 10 + S.fail, blockIdx.x, blockIdx.y);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+}  // namespace sfb
+
+using namespace sfb;
+
+extern "C" {
+
+// Encode a 2-D K-major tensor map with a 128-byte swizzled box of `box_rows` rows x 128 K elements.
+// fp4 != 0: packed E2M1 in memory (row_bytes = K/2), unpacked to 8-bit containers by TMA.
+// Returns 0 on success, a CUresult otherwise (or -1 when the driver entry point is unavailable).
+int sfb_tmap_encode(void* out_map /*128 bytes, 64-aligned*/, const void* base, int64_t rows, int64_t K,
+                    int64_t row_bytes, int box_rows, int fp4) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  return (int)enc((CUtensorMap*)out_map, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                  2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
+int sfb_umma_scratch_floats(int tiles_total, int splits, int NP) { return tiles_total * splits * 128 * NP; }
+
+// Dense / grouped block-scaled GEMM. NP = token columns (16/32/64/128) >= n.
+int sfb_umma_dense(const void* tmapA, const void* tmapB, const void* sfa, int katoms_a, const void* sfb, int katoms_b,
+                   int n, int NP, int N, int K, int groups, int a_fp4, int splits, float* scratch,
+                   unsigned int* tickets, void* out_b, float* out_f, int64_t out_stride, void* status,
+                   cudaStream_t stream) {
+  if (N % 128 || K % UM_BK || n > NP || splits < 1 || splits > K / UM_BK) return (int)cudaErrorInvalidValue;
+  if (splits > 1 && (!scratch || !tickets)) return (int)cudaErrorInvalidValue;
+  UmmaArgs a{};
+  a.sfa = (const uint8_t*)sfa; a.katoms_a = katoms_a; a.sfb = (const uint8_t*)sfb; a.katoms_b = katoms_b;
+  a.n = n; a.K = K; a.a_fp4 = a_fp4; a.mode = UM_DENSE; a.N = N; a.groups = groups; a.splits = splits;
+  a.scratch = scratch; a.tickets = tickets; a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f;
+  a.out_stride = out_stride; a.status = (Status*)status;
+  dim3 grid(N / 128, splits, groups);
+  const CUtensorMap* mA = (const CUtensorMap*)tmapA;
+  const CUtensorMap* mB = (const CUtensorMap*)tmapB;
+#define SFB_UM(NPV)                                                                                          \
+  {                                                                                                          \
+    const size_t smem = sizeof(UmmaSmem<NPV>) + 1024;                                                        \
+    static bool done = false;                                                                                \
+    if (!done) {                                                                                             \
+      cudaFuncSetAttribute(umma_dense_kernel<NPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+      done = true;                                                                                           \
+    }                                                                                                        \
+    umma_dense_kernel<NPV><<<grid, UM_THREADS, smem, stream>>>(*mA, *mB, a);                                 \
+  }
+  if (NP == 16) SFB_UM(16) else if (NP == 32) SFB_UM(32) else if (NP == 64) SFB_UM(64) else if (NP == 128) SFB_UM(128)
+  else return (int)cudaErrorInvalidValue;
+#undef SFB_UM
+  return SFB_CHECK_LAUNCH();
+}
+
+}  // extern "C"

@@ -10,8 +10,9 @@ classes; crates/sparkflash-cli/src/convert.rs:15-76 for the offline conversion):
     compressor and indexer weights, embedding;
   * column split: wq_b (heads), wo_a (groups), attn_sink, expert and shared w1/w3 (intermediate
     width), head (vocabulary);   row split: wo_b, expert and shared w2;
-  * every quantised matrix carries per-row, per-32-K UE8M0 scales in 128x4 atoms (csrc/codecs.h) -
-    the order tcgen05 block-scaled MMA consumes - so 32x32 checkpoint blocks are expanded here.
+  * every quantised matrix carries per-row, per-32-K UE8M0 scales (32x32 checkpoint blocks are expanded
+    here), row-major for the CUDA-core arm; ``codecs.scales_to_prepared`` re-orders them into the
+    128x4 atoms tcgen05 block-scaled MMA consumes.
 """
 from __future__ import annotations
 
@@ -98,7 +99,9 @@ class DeviceWeights:
 
 
 def _prep_sf_block32(sc: torch.Tensor, rows: int) -> torch.Tensor:
-    return C.scales_to_prepared(sc, rows, 32)
+    """32x32-block checkpoint scales -> one scale per row per 32 K, row-major [rows, K/32] (what the
+    CUDA-core arm reads; the tensor-core arm re-orders these into 128x4 atoms, codecs.scales_to_prepared)."""
+    return sc.repeat_interleave(32, 0)[:rows].contiguous()
 
 
 def _layer_from_ckpt(ck: dict, cfg: ModelConfig, p: str, l: int, n_exp: int, rank: int, world: int, dev) -> LayerW:
@@ -174,10 +177,10 @@ def _layer_from_ckpt(ck: dict, cfg: ModelConfig, p: str, l: int, n_exp: int, ran
         ws, ss = [], []
         for nm in ("w1", "w3"):
             ws.append(ck[f"{p}.ffn.experts.{e}.{nm}.weight"][i0:i1])
-            ss.append(C.scales_to_prepared(ck[f"{p}.ffn.experts.{e}.{nm}.scale"][i0:i1].contiguous(), il, 1))
+            ss.append(ck[f"{p}.ffn.experts.{e}.{nm}.scale"][i0:i1].contiguous())
         w13.append(torch.stack(ws)); w13sf.append(torch.stack(ss))
         w2.append(ck[f"{p}.ffn.experts.{e}.w2.weight"][:, i0 // 2:i1 // 2])
-        w2sf.append(C.scales_to_prepared(ck[f"{p}.ffn.experts.{e}.w2.scale"][:, i0 // 32:i1 // 32].contiguous(), d, 1))
+        w2sf.append(ck[f"{p}.ffn.experts.{e}.w2.scale"][:, i0 // 32:i1 // 32].contiguous())
     L.w13 = torch.stack(w13).contiguous().to(dev)
     L.w13_sf = torch.stack(w13sf).contiguous().to(dev)
     L.w2 = torch.stack(w2).contiguous().to(dev)
@@ -227,7 +230,7 @@ def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="c
     def fp8(name, rows, cols, shard=False):
         t = torch.empty((rows, cols), dtype=torch.uint8, device=dev)
         N.synth_fill(0, t, t.numel(), sd(name, shard), sig8)
-        sf = torch.full((C.sf_bytes(rows, cols // 32),), FP8_CODE, dtype=torch.uint8, device=dev)
+        sf = torch.full((rows, cols // 32), FP8_CODE, dtype=torch.uint8, device=dev)
         return t, sf
 
     def bf16(name, shape, sigma=0.02, mean=0.0, shard=False):
@@ -281,7 +284,7 @@ def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="c
             setattr(L, f"hc_{k}_scale", f32(f"{p}.hc_{k}_scale", (3,), 0.05, 1.0))
         L.gate_w = bf16(f"{p}.gate", (E, d))
         L.gate_bias, L.gate_bias_vl = f32(f"{p}.gate_bias", (E,), 0.1), f32(f"{p}.gate_bias_vl", (E,), 0.1)
-        sfb13, sfb2 = C.sf_bytes(il, d // 32), C.sf_bytes(d, il // 32)
+        sfb13, sfb2 = il * (d // 32), d * (il // 32)
         L.s13 = torch.empty((2, il, d), dtype=torch.uint8, device=dev)
         N.synth_fill(0, L.s13, L.s13.numel(), sd(f"{p}.s13", True), sig8)
         L.s13_sf = torch.full((2, sfb13), FP8_CODE, dtype=torch.uint8, device=dev)

@@ -212,3 +212,39 @@ def device_info() -> dict:
     _check(lib().sfb_device_info(ctypes.byref(sm), ctypes.byref(ma), ctypes.byref(mi), ctypes.byref(mem)),
            "device_info")
     return {"sm_count": sm.value, "cc": (ma.value, mi.value), "total_mem": mem.value}
+
+
+# ---- tensor-core arm (csrc/k_umma.cu) ----------------------------------------------------------------------
+class TensorMap:
+    """A TMA descriptor (128 bytes, 64-byte aligned, host memory) for a K-major 2-D operand: rows x K
+    elements with a 128-element swizzled box.  Keeps the described tensor alive."""
+
+    def __init__(self, t: torch.Tensor, rows: int, K: int, row_bytes: int, box_rows: int, fp4: bool = False):
+        self._raw = ctypes.create_string_buffer(128 + 64)
+        addr = ctypes.addressof(self._raw)
+        self.ptr = (addr + 63) & ~63
+        self.tensor = t
+        code = lib().sfb_tmap_encode(c_void_p(self.ptr), _p(t), c_int64(rows), c_int64(K), c_int64(row_bytes),
+                                     c_int(box_rows), c_int(1 if fp4 else 0))
+        if code != 0:
+            raise NativeError(f"cuTensorMapEncodeTiled failed with {code} (rows={rows}, K={K}, row_bytes={row_bytes}, "
+                              f"box_rows={box_rows}, fp4={fp4})")
+
+
+def umma_np(n: int) -> int:
+    for v in (16, 32, 64, 128):
+        if n <= v:
+            return v
+    raise ValueError("more than 128 token rows per launch")
+
+
+def umma_dense(tmap_a: TensorMap, tmap_b: TensorMap, sfa, sfb, n, N, K, *, groups=1, a_fp4=False, splits=1,
+               scratch=None, tickets=None, out_b=None, out_f=None, out_stride=None, status=None, NP=None):
+    NP = NP or umma_np(n)
+    if out_stride is None:
+        out_stride = N * groups
+    code = lib().sfb_umma_dense(c_void_p(tmap_a.ptr), c_void_p(tmap_b.ptr), _p(sfa), c_int(K // 128), _p(sfb),
+                                c_int(K * groups // 128), c_int(n), c_int(NP), c_int(N), c_int(K), c_int(groups),
+                                c_int(1 if a_fp4 else 0), c_int(splits), _p(scratch), _p(tickets), _p(out_b),
+                                _p(out_f), c_int64(out_stride), _p(status), _stream())
+    _check(code, "umma_dense")

@@ -36,14 +36,14 @@ def test_gemv_matches_fp32_reference(wfmt, N_, K, n):
     if wfmt == 0:
         q, s = C.weight_quant_fp8_block32(w)
         wd = C.weight_dequant_fp8_block32(q, s)
-        sf = C.scales_to_prepared(s, N_, 32)
+        sf = s.repeat_interleave(32, 0)[:N_].contiguous()
         xq, xs = C.act_quant_fp8(x)
         ref = C.act_dequant_fp8(xq, xs) @ wd.t()
         N.gemv(0, q.to(dev), sf.to(dev), K, N_, K, n, xq=xq.to(dev), xs=xs.to(dev), out_f=out)
     elif wfmt == 1:
         q, s = C.weight_quant_fp4_row32(w)
         wd = C.weight_dequant_fp4_row32(q, s)
-        sf = C.scales_to_prepared(s, N_, 1)
+        sf = s.contiguous()
         xb = x.to(torch.bfloat16)
         ref = C.act_roundtrip_fp8(xb.float()) @ wd.t()
         N.gemv(1, q.to(dev), sf.to(dev), K // 2, N_, K, n, xb=xb.to(dev), x_quant=True, out_f=out)
@@ -64,7 +64,7 @@ def test_gemv_grouped_and_batch_invariant():
     w = torch.randn(groups * N_, K, generator=g) * 0.05
     q, s = C.weight_quant_fp8_block32(w)
     wd = C.weight_dequant_fp8_block32(q, s)
-    sf = C.scales_to_prepared(s, groups * N_, 32).cuda()
+    sf = s.repeat_interleave(32, 0)[:groups * N_].contiguous().cuda()
     xb = torch.randn(n, groups * K, generator=g).to(torch.bfloat16)
     out = torch.zeros(n, groups * N_, dtype=torch.float32, device="cuda")
     N.gemv(0, q.cuda(), sf, K, N_, K, n, groups=groups, xb=xb.cuda(), out_f=out)
