@@ -21,8 +21,10 @@
 // Reference behaviour replaced: kernels/opt_gemv_sm121.cu:967-969 (decode GEMV on warp-level
 // block-scaled MMA), kernels/opt_mma_sm121.cu (128x128 bulk GEMMs), kernels/opt_moe_sm121.cu.
 #include <cuda.h>
+#include <stdio.h>
 
 #include "k_common.cuh"
+#include "sfb_noalloc.h"
 
 namespace sfb {
 
@@ -381,6 +383,73 @@ int sfb_umma_dense(const void* tmapA, const void* tmapB, const void* sfa, int ka
   else return (int)cudaErrorInvalidValue;
 #undef SFB_UM
   return SFB_CHECK_LAUNCH();
+}
+
+}  // extern "C"
+
+// ---- allocation-free entry point (declared and documented in sfb_noalloc.h) ---------------------------------
+// The arrays below are device memory that belongs to the library image.  In host code their names
+// are only handles for the runtime's symbol lookup - not device addresses - so the launcher asks
+// cudaGetSymbolAddress once per device and hands the kernel the pointer it gets back.
+static __device__ __align__(256) float g_noalloc_partials[SFB_NOALLOC_MAX_FLOATS];
+static __device__ __align__(256) unsigned int g_noalloc_tickets[SFB_NOALLOC_MAX_TILES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_partials_ptr[kMaxDevices] = {};
+unsigned int* g_tickets_ptr[kMaxDevices] = {};
+thread_local char g_noalloc_err[256] = "";
+}  // namespace
+
+extern "C" {
+
+const char* sfb_noalloc_last_error(void) { return g_noalloc_err; }
+
+int sfb_umma_dense_noalloc(const void* tmapA, const void* tmapB, const void* sfa, int katoms_a, const void* sfb,
+                           int katoms_b, int n, int NP, int N, int K, int groups, int a_fp4, int splits,
+                           void* out_b, float* out_f, int64_t out_stride, void* status, cudaStream_t stream) {
+  g_noalloc_err[0] = 0;
+  if (N <= 0 || N % 128 || groups <= 0 || splits < 1 || NP <= 0) {
+    snprintf(g_noalloc_err, sizeof g_noalloc_err, "bad shape: N=%d groups=%d splits=%d NP=%d", N, groups, splits, NP);
+    return (int)cudaErrorInvalidValue;
+  }
+  const long long tiles = (long long)groups * (N / 128);
+  const long long floats = tiles * splits * 128 * NP;
+  if (tiles > SFB_NOALLOC_MAX_TILES || floats > SFB_NOALLOC_MAX_FLOATS) {
+    snprintf(g_noalloc_err, sizeof g_noalloc_err,
+             "problem needs %lld partial-sum floats and %lld tile counters; the built-in scratch holds %d and %d",
+             floats, tiles, SFB_NOALLOC_MAX_FLOATS, SFB_NOALLOC_MAX_TILES);
+    return SFB_NOALLOC_TOO_LARGE;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    snprintf(g_noalloc_err, sizeof g_noalloc_err, "cudaGetDevice failed (%d) or device index %d unsupported", (int)e, dev);
+    return SFB_NOALLOC_SETUP_FAILED;
+  }
+  if (g_partials_ptr[dev] == nullptr || g_tickets_ptr[dev] == nullptr) {
+    // first call on this device: resolve the arrays' device addresses (device `dev` is current)
+    float* p = nullptr;
+    unsigned int* t = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_partials);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress((void**)&t, g_noalloc_tickets);
+    if (e != cudaSuccess || p == nullptr || t == nullptr) {
+      snprintf(g_noalloc_err, sizeof g_noalloc_err, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return SFB_NOALLOC_SETUP_FAILED;
+    }
+    g_partials_ptr[dev] = p;
+    g_tickets_ptr[dev] = t;
+  }
+  // the counters must start at zero whatever an earlier (possibly failed) call left behind
+  e = cudaMemsetAsync(g_tickets_ptr[dev], 0, (size_t)tiles * sizeof(unsigned int), stream);
+  if (e != cudaSuccess) {
+    snprintf(g_noalloc_err, sizeof g_noalloc_err, "clearing the tile counters failed: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  const int rc = sfb_umma_dense(tmapA, tmapB, sfa, katoms_a, sfb, katoms_b, n, NP, N, K, groups, a_fp4, splits,
+                                g_partials_ptr[dev], g_tickets_ptr[dev], out_b, out_f, out_stride, status, stream);
+  if (rc != 0) snprintf(g_noalloc_err, sizeof g_noalloc_err, "launch failed with CUDA error %d", rc);
+  return rc;
 }
 
 }  // extern "C"
