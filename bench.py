@@ -108,6 +108,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--collective", default=os.environ.get("SFB_COLLECTIVE", "fused"))
     ap.add_argument("--skip-extras", action="store_true")
+    ap.add_argument("--arm", default=os.environ.get("SFB_ARM", "tc"), choices=["tc", "cuda"])
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -140,7 +141,8 @@ def main() -> None:
     t_init = time.time() - t0
     S = args.streams
     max_ctx = args.prompt + args.steps * 2 + args.warmup * 2 + 1024
-    eng = E.Engine(weights, max_lanes=max(S, 1), max_context=max_ctx, max_rows=64, comm=comm)
+    eng = E.Engine(weights, max_lanes=max(S, 1), max_context=max_ctx, max_rows=64, comm=comm, arm=args.arm,
+                   synthetic_scales=True)
     if comm is not None:
         comm.attach(eng)
     b = 1024
@@ -260,6 +262,7 @@ def main() -> None:
                        "reduced_expert_pool": reduced, "global_batch": 1, "seq_len": args.prompt,
                        "parallelism": f"tp{world}", "collective": args.collective if world > 1 else "none",
                        "speculation": "off (one token per step)", "sampling": "greedy",
+                       "arm": "tcgen05 block-scaled MMA for projections and experts" if args.arm == "tc" else "CUDA-core",
                        "l2": "inputs larger than L2 (every step streams the step's weights, >1 GB per GPU, from HBM)",
                        "weights_gb_per_gpu": weights.nbytes() / 1e9, "kv_gb_per_gpu": eng.kv.nbytes() / 1e9,
                        "init_s": t_init},

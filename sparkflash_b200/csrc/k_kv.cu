@@ -28,6 +28,7 @@ struct QkvPostArgs {
   const int* row_pos;         // [n]
   uint8_t* qr_q;              // [n, q] e4m3
   uint8_t* qr_s;              // [n, q/32]
+  uint8_t* qr_atom;           // optional scale atoms (rows = tokens) for the tensor-core arm
   __nv_bfloat16* qr_b;        // optional [n, q] bf16 (tests)
   uint8_t* win_q;             // [lanes, ring, hd] e4m3
   uint8_t* win_s;             // [lanes, ring, hd/32]
@@ -54,7 +55,10 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
     uint8_t sc;
     uint8_t qv = warp_quant_fp8(v, &sc);
     a.qr_q[(size_t)row * a.q + i] = qv;
-    if ((threadIdx.x & 31) == 0) a.qr_s[(size_t)row * (a.q / 32) + i / 32] = sc;
+    if ((threadIdx.x & 31) == 0) {
+      a.qr_s[(size_t)row * (a.q / 32) + i / 32] = sc;
+      if (a.qr_atom) a.qr_atom[sf_offset(row, i / 32, a.q / 32)] = sc;
+    }
   }
   __syncthreads();
   // ---- kv_norm + rope + fp8 + window append ----
@@ -226,12 +230,12 @@ using namespace sfb;
 extern "C" {
 
 int sfb_qkv_post(const void* raw, const float* q_norm_w, const float* kv_norm_w, const double* inv_freq,
-                 const int* row_lane, const int* row_pos, void* qr_q, void* qr_s, void* qr_b, void* win_q,
+                 const int* row_lane, const int* row_pos, void* qr_q, void* qr_s, void* qr_atom, void* qr_b, void* win_q,
                  void* win_s, int64_t win_lane_stride_q, int64_t win_lane_stride_s, int n, int q, int hd,
                  int rd, int ring, float eps, cudaStream_t stream) {
   if (q % 32 || hd % 32 || rd % 2) return (int)cudaErrorInvalidValue;
   QkvPostArgs a{(const __nv_bfloat16*)raw, q_norm_w, kv_norm_w, inv_freq, row_lane, row_pos,
-                (uint8_t*)qr_q, (uint8_t*)qr_s, (__nv_bfloat16*)qr_b, (uint8_t*)win_q, (uint8_t*)win_s,
+                (uint8_t*)qr_q, (uint8_t*)qr_s, (uint8_t*)qr_atom, (__nv_bfloat16*)qr_b, (uint8_t*)win_q, (uint8_t*)win_s,
                 win_lane_stride_q, win_lane_stride_s, n, q, hd, rd, ring, eps};
   const size_t smem = sizeof(float) * (size_t)(q > hd ? q : hd);
   qkv_post_kernel<<<n, 256, smem, stream>>>(a);

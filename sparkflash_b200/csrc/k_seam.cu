@@ -143,6 +143,8 @@ struct SeamBArgs {
   __nv_bfloat16* xn;          // [n, d] normalised bf16 (may be null)
   uint8_t* xq;                // [n, d] e4m3 (may be null)
   uint8_t* xs;                // [n, d/32] ue8m0, row-major
+  uint8_t* xs_atom;           // optional scale atoms for the tensor-core arm (see atom_mode)
+  int atom_mode;              // 0: rows of one atom set = tokens; 1: one atom set per token, token at row 0
   int n, hc, d, mix, iters;
   float norm_eps, hc_eps;
 };
@@ -213,7 +215,14 @@ __global__ void __launch_bounds__(256) seam_b_kernel(SeamBArgs a) {
     uint8_t q = warp_quant_fp8(v, &sc);
     if (col < d) {
       a.xq[(size_t)row * d + col] = q;
-      if ((threadIdx.x & 31) == 0) a.xs[(size_t)row * (d / 32) + col / 32] = sc;
+      if ((threadIdx.x & 31) == 0) {
+        a.xs[(size_t)row * (d / 32) + col / 32] = sc;
+        if (a.xs_atom) {
+          const int kb = col / 32, KB = d / 32;
+          if (a.atom_mode == 0) a.xs_atom[sf_offset(row, kb, KB)] = sc;
+          else a.xs_atom[(size_t)row * sf_bytes(1, KB) + sf_offset(0, kb, KB)] = sc;
+        }
+      }
     }
   }
 }
@@ -231,8 +240,8 @@ int sfb_coef_stride(int hc) { return coef_stride(hc); }
 int sfb_seam(void* h, const void* const* y_ptrs, const void* const* flag_ptrs, uint32_t epoch, int W,
              int has_post, const float* coef_prev, const float* a_pre, int a_stride, const float* fn,
              void* xhat, float* partials, void* ysum, const float* norm_w, const float* hc_scale,
-             const float* hc_base, float* coef_out, void* xn, void* xq, void* xs, void* status, int n,
-             int hc, int d, int iters, float norm_eps, float hc_eps, cudaStream_t stream) {
+             const float* hc_base, float* coef_out, void* xn, void* xq, void* xs, void* xs_atom, int atom_mode,
+             void* status, int n, int hc, int d, int iters, float norm_eps, float hc_eps, cudaStream_t stream) {
   if (hc > MAX_HC || W > 8 || (hc & (hc - 1))) return (int)cudaErrorInvalidValue;
   SeamArgs a{};
   a.h = (__nv_bfloat16*)h;
@@ -249,7 +258,8 @@ int sfb_seam(void* h, const void* const* y_ptrs, const void* const* flag_ptrs, u
   SeamBArgs b{};
   b.partials = partials; b.nblk = nblk; b.xhat = (const __nv_bfloat16*)xhat; b.norm_w = norm_w;
   b.hc_scale = hc_scale; b.hc_base = hc_base; b.coef = fn ? coef_out : nullptr;
-  b.xn = (__nv_bfloat16*)xn; b.xq = (uint8_t*)xq; b.xs = (uint8_t*)xs; b.n = n; b.hc = hc; b.d = d;
+  b.xn = (__nv_bfloat16*)xn; b.xq = (uint8_t*)xq; b.xs = (uint8_t*)xs; b.xs_atom = (uint8_t*)xs_atom;
+  b.atom_mode = atom_mode; b.n = n; b.hc = hc; b.d = d;
   b.mix = a.mix; b.iters = iters; b.norm_eps = norm_eps; b.hc_eps = hc_eps;
   seam_b_kernel<<<dim3((d + 255) / 256, n), 256, 0, stream>>>(b);
   return SFB_CHECK_LAUNCH();

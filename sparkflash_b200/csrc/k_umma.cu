@@ -126,49 +126,51 @@ __host__ __device__ inline uint32_t make_idesc(int a_fmt, int b_fmt, int M, int 
   return d;
 }
 
-enum UmmaMode : int { UM_DENSE = 0, UM_GATE_UP = 1, UM_DOWN = 2 };
+enum UmmaMode : int { UM_DENSE = 0, UM_DOWN = 2 };
 
 struct UmmaArgs {
-  // A (weights): rows x K through tmapA; scale atoms (128 rows x 4 k-blocks, 512 bytes each)
-  const uint8_t* sfa;         // atom (ra, ka) at ((ra * katoms_a) + ka) * 512
-  int katoms_a;               // atoms along K of the A matrix
+  // A (weights): rows x K through tmapA (tmapA2 = the shared expert in MoE modes); scale atoms
+  // (128 rows x 4 k-blocks, 512 bytes each), atom (ra, ka) at ((ra * katoms_a) + ka) * 512
+  const uint8_t* sfa;
+  const uint8_t* sfa2;
+  int katoms_a;
   // B (activations): token rows x K_total through tmapB; scale atoms likewise
   const uint8_t* sfb;
   int katoms_b;
-  int n;                      // valid token rows
-  int K;                      // reduction length per item (multiple of 128)
-  int a_fp4;
+  int n;                      // valid token rows (dense); number of tokens = gridDim.z (MoE)
+  int K;                      // reduction length per item
+  int a_fp4;                  // format of tmapA (tmapA2 is always FP8)
   int mode;
   // dense / grouped
-  int N;                      // output columns per group (multiple of 128)
+  int N;                      // output columns per group
   int groups;                 // group g: A rows g*N.., B k-offset g*K, out column g*N..
-  // split-K
+  int pair;                   // > 0: out[t] = acc[t] + acc[t + pair] (two-term activations)
+  // split-K (dense) or slot accumulation (down)
   int splits;
   float* scratch;             // [splits, tiles_total, 128, NP] fp32
   unsigned int* tickets;      // [tiles_total], zero before the launch; reset by the last CTA
-  // outputs [n, out_stride]
+  // outputs [rows, out_stride]
   __nv_bfloat16* out_b;
   float* out_f;
   int64_t out_stride;
-  // MoE (gate_up / down): slot table
-  const int* ids;             // [n_tok, k] expert ids
-  const float* wts;           // [n_tok, k]
-  int top_k, slots;           // slots = top_k + shared
-  int inter;                  // local intermediate width
-  int rows_per_expert;        // rows of one expert's block in tmapA
-  int shared_row0;            // first row of the shared expert's block in tmapA2 (second map)
+  // MoE
+  const int* ids;             // [n_tok, top_k] expert ids
+  const float* wts;           // [n_tok, top_k]
+  int top_k, slots;           // slots = top_k + (shared ? 1 : 0)
+  int inter;                  // stored local intermediate width (multiple of 128)
+  int d;                      // model width
   uint8_t* act_q;             // gate_up out: [n_tok, slots, inter]
   uint8_t* act_s;             //              [n_tok, slots, inter/32] row-major
-  uint8_t* act_sf;            //              atoms: rows = n_tok*slots, kb = inter/32
+  uint8_t* act_sf;            //              one atom set per (token, slot), the row at atom row 0
   float limit;
   Status* status;
 };
 
-template <int NP>  // token columns per accumulator (16, 32, 64, 128)
+template <int NP, int NA>  // token columns per accumulator; NA weight tiles per stage (2 for gate|up)
 struct UmmaSmem {
-  alignas(1024) uint8_t a[UM_STAGES][UM_A_BYTES];
+  alignas(1024) uint8_t a[UM_STAGES][NA][UM_A_BYTES];
   alignas(1024) uint8_t b[UM_STAGES][NP * UM_BK];
-  alignas(128) uint8_t sfa[UM_STAGES][512];
+  alignas(128) uint8_t sfa[UM_STAGES][NA][512];
   alignas(128) uint8_t sfb[UM_STAGES][512];
   alignas(8) uint64_t full[UM_STAGES];
   alignas(8) uint64_t empty[UM_STAGES];
@@ -178,23 +180,64 @@ struct UmmaSmem {
   int fail;
 };
 
+// what one CTA multiplies
+struct UmmaWork {
+  const CUtensorMap* ma;
+  int a_fp4;
+  int a_row0;                 // first weight row of the tile in `ma`
+  const uint8_t* sfa;         // atom of k-step 0 for this tile (512 bytes per k-step)
+  int b_x0, b_row0;           // B coordinates of k-step 0
+  const uint8_t* sfb;         // atom of k-step 0
+  int ks0, nks;
+  int split, splits, tile_id, tiles_total;
+  int out_row0, n_valid, col0, col_limit;
+};
+
 template <int NP>
 __global__ void __launch_bounds__(UM_THREADS, 1)
-umma_dense_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
+                 const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
   extern __shared__ uint8_t smem_raw[];
-  UmmaSmem<NP>& S = *reinterpret_cast<UmmaSmem<NP>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  using Smem = UmmaSmem<NP, 1>;
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x;           // 128-row tile inside the group
-  const int split = blockIdx.y;
-  const int g = blockIdx.z;
-  const int ksteps_total = a.K / UM_BK;
-  const int ks0 = (int)((int64_t)ksteps_total * split / a.splits);
-  const int ks1 = (int)((int64_t)ksteps_total * (split + 1) / a.splits);
-  const int nks = ks1 - ks0;
-  const int a_row0 = g * a.N + tile * 128;
+  UmmaWork w;
+  if (a.mode == UM_DENSE) {
+    const int tile = blockIdx.x, g = blockIdx.z;
+    const int ksteps = (a.K + UM_BK - 1) / UM_BK;
+    w.ma = &tmapA; w.a_fp4 = a.a_fp4;
+    w.a_row0 = g * a.N + tile * 128;
+    w.ks0 = (int)((int64_t)ksteps * blockIdx.y / a.splits);
+    w.nks = (int)((int64_t)ksteps * (blockIdx.y + 1) / a.splits) - w.ks0;
+    w.sfa = a.sfa + ((size_t)(w.a_row0 >> 7) * a.katoms_a + w.ks0) * 512;
+    w.b_x0 = g * a.K + w.ks0 * UM_BK; w.b_row0 = 0;
+    w.sfb = a.sfb + ((size_t)(g * ksteps + w.ks0)) * 512;
+    w.split = blockIdx.y; w.splits = a.splits;
+    w.tile_id = g * gridDim.x + tile; w.tiles_total = gridDim.x * gridDim.z;
+    w.out_row0 = 0; w.n_valid = a.n; w.col0 = w.a_row0; w.col_limit = (g + 1) * a.N;
+  } else {  // UM_DOWN: x = column tile of d, y = slot, z = token
+    const int tile = blockIdx.x, slot = blockIdx.y, tok = blockIdx.z;
+    const int ksteps = (a.inter + UM_BK - 1) / UM_BK;
+    if (slot < a.top_k) {
+      const int e = a.ids[(size_t)tok * a.top_k + slot];
+      w.ma = &tmapA; w.a_fp4 = a.a_fp4;
+      w.a_row0 = e * a.d + tile * 128;
+      w.sfa = a.sfa + ((size_t)(w.a_row0 >> 7) * a.katoms_a) * 512;
+    } else {
+      w.ma = &tmapA2; w.a_fp4 = 0;
+      w.a_row0 = tile * 128;
+      w.sfa = a.sfa2 + ((size_t)tile * a.katoms_a) * 512;
+    }
+    w.ks0 = 0; w.nks = ksteps;
+    w.b_x0 = 0; w.b_row0 = tok * a.slots + slot;
+    w.sfb = a.sfb + (size_t)w.b_row0 * a.katoms_b * 512;
+    w.split = slot; w.splits = a.slots;
+    w.tile_id = tok * gridDim.x + tile; w.tiles_total = gridDim.x * gridDim.z;
+    w.out_row0 = tok; w.n_valid = 1; w.col0 = tile * 128; w.col_limit = a.d;
+  }
   constexpr uint32_t TMEM_COLS = NP + 16 <= 32 ? 32 : (NP + 16 <= 64 ? 64 : (NP + 16 <= 128 ? 128 : 256));
   // bytes TMA reports per stage: packed FP4 counts 4 bits per element although it lands in 8-bit containers
-  const uint32_t STAGE_TX = (a.a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 1024;
+  const uint32_t STAGE_TX = (w.a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 1024;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
@@ -217,29 +260,27 @@ umma_dense_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < nks; ++i) {
+      for (int i = 0; i < w.nks; ++i) {
         const int s = i % UM_STAGES;
         if (i >= UM_STAGES && !mbar_wait(&S.empty[s], ((i / UM_STAGES) - 1) & 1)) { S.fail = 1; break; }
-        const int ks = ks0 + i;
         mbar_expect_tx(&S.full[s], STAGE_TX);
-        tma_load_2d(S.a[s], &tmapA, ks * UM_BK, a_row0, &S.full[s]);
-        tma_load_2d(S.b[s], &tmapB, g * a.K + ks * UM_BK, 0, &S.full[s]);
-        bulk_load(S.sfa[s], a.sfa + ((size_t)(a_row0 >> 7) * a.katoms_a + ks) * 512, 512, &S.full[s]);
-        bulk_load(S.sfb[s], a.sfb + ((size_t)(g * (a.K / UM_BK) + ks)) * 512, 512, &S.full[s]);
+        tma_load_2d(S.a[s][0], w.ma, (w.ks0 + i) * UM_BK, w.a_row0, &S.full[s]);
+        tma_load_2d(S.b[s], &tmapB, w.b_x0 + i * UM_BK, w.b_row0, &S.full[s]);
+        bulk_load(S.sfa[s][0], w.sfa + (size_t)i * 512, 512, &S.full[s]);
+        bulk_load(S.sfb[s], w.sfb + (size_t)i * 512, 512, &S.full[s]);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(a.a_fp4 ? 5 : 0, 0, 128, NP);
-      bool ok = true;
-      for (int i = 0; i < nks && ok; ++i) {
+      const uint32_t idesc = make_idesc(w.a_fp4 ? 5 : 0, 0, 128, NP);
+      for (int i = 0; i < w.nks; ++i) {
         const int s = i % UM_STAGES;
-        if (!mbar_wait(&S.full[s], (i / UM_STAGES) & 1)) { S.fail = 2; ok = false; break; }
+        if (!mbar_wait(&S.full[s], (i / UM_STAGES) & 1)) { S.fail = 2; break; }
         tc_fence_after();
         const uint32_t sf_slot = (uint32_t)(i & 1) * 4;
-        tc_cp_sf(t_sfa + sf_slot, make_desc(smem_u32(S.sfa[s]), 128, 0, 0));
+        tc_cp_sf(t_sfa + sf_slot, make_desc(smem_u32(S.sfa[s][0]), 128, 0, 0));
         tc_cp_sf(t_sfb + sf_slot, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
-        const uint32_t a_addr = smem_u32(S.a[s]), b_addr = smem_u32(S.b[s]);
+        const uint32_t a_addr = smem_u32(S.a[s][0]), b_addr = smem_u32(S.b[s]);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const uint64_t ad = make_desc(a_addr + kk * 32, 1024, 16, 2);
@@ -256,23 +297,26 @@ umma_dense_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
     const int q = warp & 3;
     const bool got = mbar_wait(&S.acc_full, 0);
     tc_fence_after();
-    const int col = a_row0 + q * 32 + lane;     // output column (row of A)
-    const bool single = a.splits == 1;
-    const int tile_id = g * gridDim.x + tile;
-    float* part = a.scratch ? a.scratch + (((size_t)split * gridDim.x * gridDim.z + tile_id) * 128 + q * 32 + lane) * NP : nullptr;
+    const int col = w.col0 + q * 32 + lane;     // output column (row of A)
+    const bool col_ok = col < w.col_limit;
+    const bool single = w.splits == 1;
+    const size_t lane_off = ((size_t)w.tile_id * 128 + q * 32 + lane) * NP;
+    const size_t split_stride = (size_t)w.tiles_total * 128 * NP;
+    float* part = a.scratch ? a.scratch + (size_t)w.split * split_stride + lane_off : nullptr;
+    const int nv = a.pair > 0 ? a.pair : w.n_valid;
 #pragma unroll
     for (int c0 = 0; c0 < NP; c0 += 16) {
       uint32_t v[16];
       tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0, v);
       tc_wait_ld();
       if (!got || S.fail) continue;
-      if (single) {
+      if (single && a.pair == 0) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int tok = c0 + j;
-          if (tok < a.n) {
+          if (tok < nv && col_ok) {
             const float f = __uint_as_float(v[j]);
-            const int64_t o = (int64_t)tok * a.out_stride + col;
+            const int64_t o = (int64_t)(w.out_row0 + tok) * a.out_stride + col;
             if (a.out_b) a.out_b[o] = __float2bfloat16_rn(f);
             if (a.out_f) a.out_f[o] = f;
           }
@@ -285,29 +329,154 @@ umma_dense_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
                               __uint_as_float(v[4 * j + 3]));
       }
     }
-    if (!single) {
+    if (!(single && a.pair == 0)) {
       // last-arriving split of this tile reduces all splits in index order
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (warp == 2 && lane == 0) {
-        const unsigned int prev = atomicAdd(&a.tickets[tile_id], 1u);
-        S.last_flag = (prev == (unsigned int)a.splits - 1) ? 1 : 0;
-        if (S.last_flag) a.tickets[tile_id] = 0;
+        const unsigned int prev = atomicAdd(&a.tickets[w.tile_id], 1u);
+        S.last_flag = (prev == (unsigned int)w.splits - 1) ? 1 : 0;
+        if (S.last_flag) a.tickets[w.tile_id] = 0;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (S.last_flag) {
+      if (S.last_flag && col_ok) {
         __threadfence();
-        for (int tok = 0; tok < a.n; ++tok) {
+        for (int tok = 0; tok < nv; ++tok) {
           float s = 0.f;
-          for (int sp = 0; sp < a.splits; ++sp)
-            s += a.scratch[(((size_t)sp * gridDim.x * gridDim.z + tile_id) * 128 + q * 32 + lane) * NP + tok];
-          const int64_t o = (int64_t)tok * a.out_stride + col;
+          for (int sp = 0; sp < w.splits; ++sp) {
+            const float* pp = a.scratch + (size_t)sp * split_stride + lane_off;
+            s += pp[tok];
+            if (a.pair > 0) s += pp[tok + a.pair];
+          }
+          const int64_t o = (int64_t)(w.out_row0 + tok) * a.out_stride + col;
           if (a.out_b) a.out_b[o] = __float2bfloat16_rn(s);
           if (a.out_f) a.out_f[o] = s;
         }
       }
     }
     if ((!got || S.fail) && lane == 0 && q == 0) status_set(a.status, ST_TIMEOUT, 10 + S.fail, blockIdx.x, blockIdx.y);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// ---- MoE gate/up: two weight tiles (w1, w3) against one token, clamp-SwiGLU x route weight, FP8 re-quant ------
+// grid: x = 128-column tile of the intermediate width, y = slot (top_k routed + shared), z = token
+__global__ void __launch_bounds__(UM_THREADS, 1)
+umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
+                   const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
+  constexpr int NP = 16;
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = UmmaSmem<NP, 2>;
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, slot = blockIdx.y, tok = blockIdx.z;
+  const int il = a.inter;
+  const int nks = (a.d + UM_BK - 1) / UM_BK;
+  const CUtensorMap* ma;
+  int a_fp4, row_g, row_u;
+  const uint8_t *sf_g, *sf_u;
+  float weight = 1.f;
+  if (slot < a.top_k) {
+    const int e = a.ids[(size_t)tok * a.top_k + slot];
+    weight = a.wts[(size_t)tok * a.top_k + slot];
+    ma = &tmapA; a_fp4 = a.a_fp4;
+    row_g = (e * 2) * il + tile * 128; row_u = row_g + il;
+    sf_g = a.sfa + ((size_t)(row_g >> 7) * a.katoms_a) * 512;
+    sf_u = a.sfa + ((size_t)(row_u >> 7) * a.katoms_a) * 512;
+  } else {
+    ma = &tmapA2; a_fp4 = 0;
+    row_g = tile * 128; row_u = row_g + il;
+    sf_g = a.sfa2 + ((size_t)(row_g >> 7) * a.katoms_a) * 512;
+    sf_u = a.sfa2 + ((size_t)(row_u >> 7) * a.katoms_a) * 512;
+  }
+  const uint8_t* sfb = a.sfb + (size_t)tok * a.katoms_b * 512;
+  constexpr uint32_t TMEM_COLS = 64;
+  const uint32_t STAGE_TX = 2 * (a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 3 * 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
+    mbar_init(&S.acc_full, 1);
+    S.fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = S.tmem_base;
+  const uint32_t t_g = tmem, t_u = tmem + NP;
+  const uint32_t t_sfg = tmem + 2 * NP, t_sfu = tmem + 2 * NP + 8, t_sfb = tmem + 2 * NP + 16;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < nks; ++i) {
+        const int s = i % UM_STAGES;
+        if (i >= UM_STAGES && !mbar_wait(&S.empty[s], ((i / UM_STAGES) - 1) & 1)) { S.fail = 1; break; }
+        mbar_expect_tx(&S.full[s], STAGE_TX);
+        tma_load_2d(S.a[s][0], ma, i * UM_BK, row_g, &S.full[s]);
+        tma_load_2d(S.a[s][1], ma, i * UM_BK, row_u, &S.full[s]);
+        tma_load_2d(S.b[s], &tmapB, i * UM_BK, tok, &S.full[s]);
+        bulk_load(S.sfa[s][0], sf_g + (size_t)i * 512, 512, &S.full[s]);
+        bulk_load(S.sfa[s][1], sf_u + (size_t)i * 512, 512, &S.full[s]);
+        bulk_load(S.sfb[s], sfb + (size_t)i * 512, 512, &S.full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(a_fp4 ? 5 : 0, 0, 128, NP);
+      for (int i = 0; i < nks; ++i) {
+        const int s = i % UM_STAGES;
+        if (!mbar_wait(&S.full[s], (i / UM_STAGES) & 1)) { S.fail = 2; break; }
+        tc_fence_after();
+        const uint32_t sl = (uint32_t)(i & 1) * 4;
+        tc_cp_sf(t_sfg + sl, make_desc(smem_u32(S.sfa[s][0]), 128, 0, 0));
+        tc_cp_sf(t_sfu + sl, make_desc(smem_u32(S.sfa[s][1]), 128, 0, 0));
+        tc_cp_sf(t_sfb + sl, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
+        const uint32_t g_addr = smem_u32(S.a[s][0]), u_addr = smem_u32(S.a[s][1]), b_addr = smem_u32(S.b[s]);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t bd = make_desc(b_addr + kk * 32, 1024, 16, 2);
+          const uint32_t id = idesc | ((uint32_t)kk << 29) | ((uint32_t)kk << 4);
+          const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+          tc_mma_bs(t_g, make_desc(g_addr + kk * 32, 1024, 16, 2), bd, id, t_sfg + sl, t_sfb + sl, acc);
+          tc_mma_bs(t_u, make_desc(u_addr + kk * 32, 1024, 16, 2), bd, id, t_sfu + sl, t_sfb + sl, acc);
+        }
+        tc_commit(&S.empty[s]);
+      }
+      tc_commit(&S.acc_full);
+    }
+  } else {
+    const int q = warp & 3;
+    const bool got = mbar_wait(&S.acc_full, 0);
+    tc_fence_after();
+    uint32_t vg[16], vu[16];
+    tc_ld16(t_g + ((uint32_t)(q * 32) << 16), vg);
+    tc_ld16(t_u + ((uint32_t)(q * 32) << 16), vu);
+    tc_wait_ld();
+    const int col = tile * 128 + q * 32 + lane;   // column of the intermediate activation
+    float act = 0.f;
+    if (got && !S.fail && col < il) {
+      const float g = fminf(bfr(__uint_as_float(vg[0])), a.limit);
+      const float u = fminf(fmaxf(bfr(__uint_as_float(vu[0])), -a.limit), a.limit);
+      act = bfr(g / (1.f + expf(-g)) * u * weight);
+    }
+    uint8_t sc;
+    const uint8_t code = warp_quant_fp8(act, &sc);
+    if (got && !S.fail && col < il) {
+      const size_t row = (size_t)tok * a.slots + slot;
+      a.act_q[row * il + col] = code;
+      if (lane == 0) {
+        const int KBi = il / 32;
+        if (a.act_s) a.act_s[row * KBi + col / 32] = sc;
+        if (a.act_sf) a.act_sf[row * sf_bytes(1, KBi) + sf_offset(0, col / 32, KBi)] = sc;
+      }
+    }
+    if ((!got || S.fail) && lane == 0 && q == 0) status_set(a.status, ST_TIMEOUT, 20 + S.fail, blockIdx.x, blockIdx.y);
   }
   tc_fence_before();
   __syncthreads();
@@ -354,35 +523,97 @@ int sfb_tmap_encode(void* out_map /*128 bytes, 64-aligned*/, const void* base, i
 
 int sfb_umma_scratch_floats(int tiles_total, int splits, int NP) { return tiles_total * splits * 128 * NP; }
 
-// Dense / grouped block-scaled GEMM. NP = token columns (16/32/64/128) >= n.
+static int launch_umma(const void* tmapA, const void* tmapA2, const void* tmapB, const UmmaArgs& a, dim3 grid, int NP,
+                       cudaStream_t stream) {
+  const CUtensorMap* mA = (const CUtensorMap*)tmapA;
+  const CUtensorMap* mA2 = (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA);
+  const CUtensorMap* mB = (const CUtensorMap*)tmapB;
+#define SFB_UM(NPV)                                                                                           \
+  {                                                                                                           \
+    const size_t smem = sizeof(UmmaSmem<NPV, 1>) + 1024;                                                      \
+    static bool done = false;                                                                                 \
+    if (!done) {                                                                                              \
+      cudaFuncSetAttribute(umma_gemm_kernel<NPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+      done = true;                                                                                            \
+    }                                                                                                         \
+    umma_gemm_kernel<NPV><<<grid, UM_THREADS, smem, stream>>>(*mA, *mA2, *mB, a);                             \
+  }
+  if (NP == 16) SFB_UM(16) else if (NP == 32) SFB_UM(32) else if (NP == 64) SFB_UM(64) else if (NP == 128) SFB_UM(128)
+  else return (int)cudaErrorInvalidValue;
+#undef SFB_UM
+  return SFB_CHECK_LAUNCH();
+}
+
+// Dense / grouped block-scaled GEMM. NP = token columns (16/32/64/128) >= n (>= 2*pair when pair > 0).
+// pair > 0: activations are two-term (hi rows 0..pair-1, lo rows pair..2*pair-1); out[t] = acc[t] + acc[t+pair].
 int sfb_umma_dense(const void* tmapA, const void* tmapB, const void* sfa, int katoms_a, const void* sfb, int katoms_b,
                    int n, int NP, int N, int K, int groups, int a_fp4, int splits, float* scratch,
                    unsigned int* tickets, void* out_b, float* out_f, int64_t out_stride, void* status,
                    cudaStream_t stream) {
-  if (N % 128 || K % UM_BK || n > NP || splits < 1 || splits > K / UM_BK) return (int)cudaErrorInvalidValue;
+  if ((N % 128 && groups > 1) || K % UM_BK || n > NP || splits < 1 || splits > K / UM_BK)
+    return (int)cudaErrorInvalidValue;
   if (splits > 1 && (!scratch || !tickets)) return (int)cudaErrorInvalidValue;
   UmmaArgs a{};
   a.sfa = (const uint8_t*)sfa; a.katoms_a = katoms_a; a.sfb = (const uint8_t*)sfb; a.katoms_b = katoms_b;
   a.n = n; a.K = K; a.a_fp4 = a_fp4; a.mode = UM_DENSE; a.N = N; a.groups = groups; a.splits = splits;
   a.scratch = scratch; a.tickets = tickets; a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f;
   a.out_stride = out_stride; a.status = (Status*)status;
-  dim3 grid(N / 128, splits, groups);
-  const CUtensorMap* mA = (const CUtensorMap*)tmapA;
-  const CUtensorMap* mB = (const CUtensorMap*)tmapB;
-#define SFB_UM(NPV)                                                                                          \
-  {                                                                                                          \
-    const size_t smem = sizeof(UmmaSmem<NPV>) + 1024;                                                        \
-    static bool done = false;                                                                                \
-    if (!done) {                                                                                             \
-      cudaFuncSetAttribute(umma_dense_kernel<NPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-      done = true;                                                                                           \
-    }                                                                                                        \
-    umma_dense_kernel<NPV><<<grid, UM_THREADS, smem, stream>>>(*mA, *mB, a);                                 \
+  return launch_umma(tmapA, nullptr, tmapB, a, dim3((N + 127) / 128, splits, groups), NP, stream);
+}
+
+// Same with two-term activations (see k_quant.cu): rows [0, pair) are the hi terms, [pair, 2*pair) the lo terms.
+int sfb_umma_dense_pair(const void* tmapA, const void* tmapB, const void* sfa, int katoms_a, const void* sfb,
+                        int katoms_b, int pair, int NP, int N, int K, int groups, int a_fp4, int splits,
+                        float* scratch, unsigned int* tickets, void* out_b, float* out_f, int64_t out_stride,
+                        void* status, cudaStream_t stream) {
+  if (N % 128 || K % UM_BK || 2 * pair > NP || pair < 1 || splits < 1 || splits > K / UM_BK || !scratch || !tickets)
+    return (int)cudaErrorInvalidValue;
+  UmmaArgs a{};
+  a.sfa = (const uint8_t*)sfa; a.katoms_a = katoms_a; a.sfb = (const uint8_t*)sfb; a.katoms_b = katoms_b;
+  a.n = 2 * pair; a.pair = pair; a.K = K; a.a_fp4 = a_fp4; a.mode = UM_DENSE; a.N = N; a.groups = groups;
+  a.splits = splits; a.scratch = scratch; a.tickets = tickets; a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f;
+  a.out_stride = out_stride; a.status = (Status*)status;
+  return launch_umma(tmapA, nullptr, tmapB, a, dim3(N / 128, splits, groups), NP, stream);
+}
+
+// MoE gate/up for n_tok tokens: tmapA = routed w13 [E*2*inter, d] (FP4), tmapA2 = shared [2*inter, d] (FP8, may be
+// null when slots == top_k), tmapB = activations [rows, d] with a 16-row box; sfb = one atom set per token.
+int sfb_umma_gate_up(const void* tmapA, const void* tmapA2, const void* tmapB, const void* sfa, const void* sfa2,
+                     const void* sfb, const int* ids, const float* wts, void* act_q, void* act_s, void* act_sf,
+                     int n_tok, int top_k, int slots, int d, int inter, float limit, void* status,
+                     cudaStream_t stream) {
+  if (inter % 128 || d % 32 || slots < top_k || slots > top_k + 1) return (int)cudaErrorInvalidValue;
+  UmmaArgs a{};
+  a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (d / 32 + 3) / 4;
+  a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a; a.a_fp4 = 1; a.ids = ids; a.wts = wts; a.top_k = top_k;
+  a.slots = slots; a.inter = inter; a.d = d; a.act_q = (uint8_t*)act_q; a.act_s = (uint8_t*)act_s;
+  a.act_sf = (uint8_t*)act_sf; a.limit = limit; a.status = (Status*)status;
+  const size_t smem = sizeof(UmmaSmem<16, 2>) + 1024;
+  static bool done = false;
+  if (!done) {
+    cudaFuncSetAttribute(umma_gateup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    done = true;
   }
-  if (NP == 16) SFB_UM(16) else if (NP == 32) SFB_UM(32) else if (NP == 64) SFB_UM(64) else if (NP == 128) SFB_UM(128)
-  else return (int)cudaErrorInvalidValue;
-#undef SFB_UM
+  const CUtensorMap* mA = (const CUtensorMap*)tmapA;
+  const CUtensorMap* mA2 = (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA);
+  umma_gateup_kernel<<<dim3(inter / 128, slots, n_tok), UM_THREADS, smem, stream>>>(*mA, *mA2, *(const CUtensorMap*)tmapB, a);
   return SFB_CHECK_LAUNCH();
+}
+
+// MoE down + combine: out[tok, :] = sum over slots of W2_slot . act[tok, slot, :] (fp32 partial per slot, added in
+// slot order by the last CTA of each column tile).  tmapA = routed w2 [E*d, inter] (FP4), tmapA2 = shared [d, inter]
+// (FP8), tmapB = activations [n_tok*slots, inter] with a 16-row box; sfb = one atom set per (token, slot).
+int sfb_umma_down(const void* tmapA, const void* tmapA2, const void* tmapB, const void* sfa, const void* sfa2,
+                  const void* sfb, const int* ids, void* out_b, float* out_f, int64_t out_stride, float* scratch,
+                  unsigned int* tickets, int n_tok, int top_k, int slots, int d, int inter, void* status,
+                  cudaStream_t stream) {
+  if (d % 128 || inter % 128 || !scratch || !tickets) return (int)cudaErrorInvalidValue;
+  UmmaArgs a{};
+  a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (inter / 32 + 3) / 4;
+  a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a; a.a_fp4 = 1; a.mode = UM_DOWN; a.ids = ids; a.top_k = top_k;
+  a.slots = slots; a.inter = inter; a.d = d; a.scratch = scratch; a.tickets = tickets;
+  a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f; a.out_stride = out_stride; a.status = (Status*)status;
+  return launch_umma(tmapA, tmapA2, tmapB, a, dim3(d / 128, slots, n_tok), 16, stream);
 }
 
 }  // extern "C"

@@ -70,7 +70,10 @@ class StepIO:
 
 class Engine:
     def __init__(self, weights: DeviceWeights, max_lanes: int = 4, max_context: int = 4096, max_rows: int = 64,
-                 comm=None, use_graphs: bool = True, keep_logits: bool = False):
+                 comm=None, use_graphs: bool = True, keep_logits: bool = False, arm: str = "cuda",
+                 synthetic_scales: bool = False):
+        """``arm``: "cuda" = CUDA-core exact arm for every projection; "tc" = tcgen05 tensor-core arm for
+        every shape it takes (the rest falls back to the CUDA-core kernels)."""
         self.w, self.cfg = weights, weights.cfg
         cfg = self.cfg
         self.rank, self.world = weights.rank, weights.world
@@ -131,6 +134,15 @@ class Engine:
         self.seed = torch.zeros((R,), dtype=torch.int64, device=dev)
         pin = lambda dt: torch.zeros((R,), dtype=dt).pin_memory()
         self.io = StepIO(pin(i32), pin(i32), pin(i32), pin(f32), pin(torch.int64), pin(i32))
+        self.arm = arm
+        self.tcl = None
+        if arm == "tc":
+            from . import tc as TC
+            self.tcl = TC.attach(weights, synthetic=synthetic_scales)
+            self.tcb = TC.TcBuffers(self)
+            self._splits = TC.pick_splits
+        elif arm != "cuda":
+            raise ValueError(f"unknown arm {arm!r}")
         self.graphs: dict[tuple[int, int], torch.cuda.CUDAGraph] = {}
         self.launches_per_step = 0
         self._counting = False
@@ -152,7 +164,7 @@ class Engine:
             raise RuntimeError(f"device status code={st[0]} where={st[1]} detail=({st[2]}, {st[3]})")
 
     # ---- sublayers -------------------------------------------------------------------------------------
-    def _seam(self, n: int, k: int, y_parts, fn, base, scale, norm_w, quant: bool = True):
+    def _seam(self, n: int, k: int, y_parts, fn, base, scale, norm_w, quant: bool = True, atoms: int = 0):
         """Seam number k (0-based over the whole forward): finishes the previous sublayer with
         coef[(k-1)%2] and writes this seam's coefficients to coef[k%2]."""
         cfg = self.cfg
@@ -162,27 +174,55 @@ class Engine:
                0 if first else prev.stride(0), fn, self.xhat, self.partials, norm_w, scale, base,
                self.coef[k % 2] if fn is not None else None, self.xn, self.xq if quant else None,
                self.xs if quant else None, n, cfg.hc_mult, cfg.hidden_size, cfg.hc_sinkhorn_iters, cfg.norm_eps,
-               cfg.hc_eps, status=self.status)
+               cfg.hc_eps, status=self.status,
+               xs_atom=None if (self.tcl is None or not quant) else (self.tcb.xs_atom if atoms == 0 else self.tcb.xs_atom_tok),
+               atom_mode=atoms)
         self.launches_per_step += 2 if self._counting else 0
+
+    def _tc_dense(self, M, xq_buf, x_rows, atoms, n, N_, K, out_b, out_stride=None, groups=1, pair=0):
+        """One projection on the tensor-core arm: M = TcMatrix, xq_buf = FP8 activation codes [x_rows, K*groups]."""
+        tcb = self.tcb
+        NP = N.umma_np(2 * pair if pair else n)
+        tb = tcb.bmap(xq_buf, x_rows, K * groups, NP)
+        tiles = groups * ((N_ + 127) // 128)
+        splits = self._splits(tiles, K // 128)
+        if pair:
+            N.umma_dense_pair(M.tmap, tb, M.atoms, atoms, pair, N_, K, groups=groups, a_fp4=M.fp4, splits=splits,
+                              scratch=tcb.scratch, tickets=tcb.tickets, out_b=out_b, out_stride=out_stride,
+                              status=self.status, NP=NP)
+        else:
+            N.umma_dense(M.tmap, tb, M.atoms, atoms, n, N_, K, groups=groups, a_fp4=M.fp4, splits=splits,
+                         scratch=tcb.scratch, tickets=tcb.tickets, out_b=out_b, out_stride=out_stride,
+                         status=self.status, NP=NP)
+        self._k()
 
     def _attention(self, n: int, l: int, L: LayerW, len_bucket: int):
         cfg, kv = self.cfg, self.kv
         d, hd, q, rd = cfg.hidden_size, cfg.head_dim, cfg.q_lora_rank, cfg.rope_dim
         ratio = cfg.ratio(l)
         invf = self.w.inv_freq[ratio > 0]
-        N.gemv(N.WF_FP8, L.wqkv_a, L.wqkv_a_sf, d, q + hd, d, n, xq=self.xq, xs=self.xs, out_b=self.qkv_raw); self._k()
+        T = self.tcl[l] if self.tcl is not None else None
+        if T is not None and T.wqkv_a is not None:
+            self._tc_dense(T.wqkv_a, self.xq, self.max_rows, self.tcb.xs_atom, n, q + hd, d, self.qkv_raw)
+        else:
+            N.gemv(N.WF_FP8, L.wqkv_a, L.wqkv_a_sf, d, q + hd, d, n, xq=self.xq, xs=self.xs, out_b=self.qkv_raw); self._k()
         if L.aux_w is not None:
             N.gemv(N.WF_BF16, L.aux_w, None, 2 * d, L.aux_rows, d, n, xb=self.xn, out_f=self.aux_raw,
                    out_stride=self.aux_raw.stride(0)); self._k()
         N.qkv_post(self.qkv_raw, L.q_norm, L.kv_norm, invf, self.row_lane, self.row_pos, self.qr_q, self.qr_s,
-                   kv.win_q[l], kv.win_s[l], n, q, hd, rd, kv.ring, cfg.norm_eps); self._k()
+                   kv.win_q[l], kv.win_s[l], n, q, hd, rd, kv.ring, cfg.norm_eps,
+                   qr_atom=self.tcb.qr_atom if T is not None else None); self._k()
         if cfg.is_kv_source(l):
             N.compress_append(self.aux_raw, self.aux_raw.stride(0), L.comp_norm, L.idx_wk, L.idx_knorm, invf,
                               self.row_lane, self.row_pos, kv.cin.get(l), kv.ring, kv.ckv_q[l], kv.ckv_s[l],
                               kv.ik_q[l], kv.ik_s[l], kv.max_entries[l], n, hd, cfg.index_head_dim, rd, ratio,
                               cfg.norm_eps, status=self.status); self._k()
-        N.gemv(N.WF_FP8, L.wq_b, L.wq_b_sf, q, L.wq_b_rows, q, n, xq=self.qr_q, xs=self.qr_s, out_b=self.qfull,
-               out_stride=self.qfull.stride(0)); self._k()
+        if T is not None and T.wq_b is not None:
+            self._tc_dense(T.wq_b, self.qr_q, self.max_rows, self.tcb.qr_atom, n, L.wq_b_rows, q, self.qfull,
+                           out_stride=self.qfull.stride(0))
+        else:
+            N.gemv(N.WF_FP8, L.wq_b, L.wq_b_sf, q, L.wq_b_rows, q, n, xq=self.qr_q, xs=self.qr_s, out_b=self.qfull,
+                   out_stride=self.qfull.stride(0)); self._k()
         owner = cfg.kv_owner(l)
         if ratio > 0 and cfg.is_index_source(l):
             inh, idh = cfg.index_n_heads, cfg.index_head_dim
@@ -210,15 +250,37 @@ class Engine:
                     self.sel if has_c else None, self.sel_cnt if has_c else None, cfg.index_topk, L.sink,
                     self.attn_out, n, self.hl, hd, rd, cfg.window, kv.ring, hd ** -0.5); self._k()
         ol, gin = cfg.o_lora_rank, cfg.group_in
-        N.gemv(N.WF_FP8, L.wo_a, L.wo_a_sf, gin, ol, gin, n, groups=self.gl, xb=self.attn_out, out_b=self.oa); self._k()
-        N.gemv(N.WF_FP8, L.wo_b, L.wo_b_sf, self.gl * ol, d, self.gl * ol, n, xb=self.oa, x_quant=True,
-               out_b=self.y_attn); self._k()
+        if T is not None and T.wo_a is not None and 2 * n <= 128:
+            # bf16 activations through the FP8 tensor path as a two-term split (hi + lo)
+            tcb = self.tcb
+            N.quant_rows(self.attn_out, tcb.ao_q, None, tcb.ao_atom, n, self.hl * hd, split=True, split_off=n); self._k()
+            self._tc_dense(T.wo_a, tcb.ao_q, 2 * self.max_rows, tcb.ao_atom, n, ol, gin, self.oa, groups=self.gl, pair=n)
+        else:
+            N.gemv(N.WF_FP8, L.wo_a, L.wo_a_sf, gin, ol, gin, n, groups=self.gl, xb=self.attn_out, out_b=self.oa); self._k()
+        if T is not None and T.wo_b is not None:
+            tcb = self.tcb
+            N.quant_rows(self.oa, tcb.oa_q, None, tcb.oa_atom, n, self.gl * ol); self._k()
+            self._tc_dense(T.wo_b, tcb.oa_q, self.max_rows, tcb.oa_atom, n, d, self.gl * ol, self.y_attn)
+        else:
+            N.gemv(N.WF_FP8, L.wo_b, L.wo_b_sf, self.gl * ol, d, self.gl * ol, n, xb=self.oa, x_quant=True,
+                   out_b=self.y_attn); self._k()
 
-    def _ffn(self, n: int, L: LayerW):
+    def _ffn(self, n: int, L: LayerW, l: int = 0):
         cfg = self.cfg
         d, E, k = cfg.hidden_size, cfg.n_routed_experts, cfg.top_k
         N.gemv(N.WF_BF16, L.gate_w, None, 2 * d, E, d, n, xb=self.xn, out_f=self.dots); self._k()
         N.router_topk(self.dots, L.gate_bias, L.gate_bias_vl, None, self.ids, self.wts, n, E, k, cfg.route_scale); self._k()
+        T = self.tcl[l] if self.tcl is not None else None
+        if T is not None and T.w13 is not None:
+            tcb = self.tcb
+            tbx = tcb.bmap(self.xq, self.max_rows, d, 16)
+            N.umma_gate_up(T.w13.tmap, T.s13.tmap, tbx, T.w13.atoms, T.s13.atoms, tcb.xs_atom_tok, self.ids, self.wts,
+                           self.act_q, self.act_s, tcb.act_sf, n, k, k + 1, d, self.il, cfg.swiglu_limit,
+                           status=self.status); self._k()
+            tba = tcb.bmap(self.act_q, self.max_rows * (k + 1), self.il, 16)
+            N.umma_down(T.w2.tmap, T.s2.tmap, tba, T.w2.atoms, T.s2.atoms, tcb.act_sf, self.ids, self.y_ffn, None, d,
+                        tcb.scratch, tcb.tickets, n, k, k + 1, d, self.il, status=self.status); self._k()
+            return
         N.moe_gate_up(self.xq, self.xs, self.ids, self.wts, L.w13, L.w13_sf, L.s13, L.s13_sf, self.act_q, self.act_s,
                       n, k, d, self.il, cfg.swiglu_limit); self._k()
         N.moe_down(self.act_q, self.act_s, self.ids, L.w2, L.w2_sf, L.s2, L.s2_sf, self.y_ffn, n, k, d, self.il); self._k()
@@ -252,9 +314,9 @@ class Engine:
             self._dbg(f"L{l}.oa", self.oa, n); self._dbg(f"L{l}.attn_out", self.y_attn, n)
             self._dbg(f"L{l}.sel", self.sel, n); self._dbg(f"L{l}.sel_cnt", self.sel_cnt, n)
             self._seam(n, k, self._reduce_parts(self.y_attn, n), L.hc_ffn_fn, L.hc_ffn_base, L.hc_ffn_scale,
-                       L.ffn_norm); k += 1
+                       L.ffn_norm, atoms=1); k += 1
             self._dbg(f"L{l}.ffn_in", self.xn, n)
-            self._ffn(n, L)
+            self._ffn(n, L, l)
             self._dbg(f"L{l}.ffn_out", self.y_ffn, n)
             self._dbg(f"L{l}.route_ids", self.ids, n); self._dbg(f"L{l}.route_w", self.wts, n)
             y_prev = self._reduce_parts(self.y_ffn, n)

@@ -61,7 +61,8 @@ def coef_stride(hc: int) -> int:
 
 
 def seam(h, y_parts, coef_prev, a_pre, a_stride, fn, xhat, partials, norm_w, hc_scale, hc_base, coef_out,
-         xn, xq, xs, n, hc, d, iters, norm_eps, hc_eps, ysum=None, flags=None, epoch=0, status=None):
+         xn, xq, xs, n, hc, d, iters, norm_eps, hc_eps, ysum=None, flags=None, epoch=0, status=None,
+         xs_atom=None, atom_mode=0):
     """One mHC seam (see csrc/k_seam.cu).  ``y_parts``: list of W partial outputs (tensors or raw device
     addresses) or None for the first seam of a forward."""
     has_post = y_parts is not None
@@ -71,7 +72,7 @@ def seam(h, y_parts, coef_prev, a_pre, a_stride, fn, xhat, partials, norm_w, hc_
     code = lib().sfb_seam(_p(h), yp, fp, c_uint32(epoch), c_int(W), c_int(1 if has_post else 0),
                           _p(coef_prev), _p(a_pre), c_int(a_stride), _p(fn), _p(xhat), _p(partials), _p(ysum),
                           _p(norm_w), _p(hc_scale), _p(hc_base), _p(coef_out), _p(xn), _p(xq), _p(xs),
-                          _p(status), c_int(n), c_int(hc), c_int(d), c_int(iters), c_float(norm_eps),
+                          _p(xs_atom), c_int(atom_mode), _p(status), c_int(n), c_int(hc), c_int(d), c_int(iters), c_float(norm_eps),
                           c_float(hc_eps), _stream())
     _check(code, "seam")
 
@@ -94,9 +95,9 @@ def gemv(wfmt, w, sf, row_bytes, N, K, n, *, groups=1, xq=None, xs=None, xb=None
 
 # ---- kv -------------------------------------------------------------------------------------------------
 def qkv_post(raw, q_norm_w, kv_norm_w, inv_freq, row_lane, row_pos, qr_q, qr_s, win_q, win_s, n, q, hd, rd,
-             ring, eps, qr_b=None):
+             ring, eps, qr_b=None, qr_atom=None):
     code = lib().sfb_qkv_post(_p(raw), _p(q_norm_w), _p(kv_norm_w), _p(inv_freq), _p(row_lane), _p(row_pos),
-                              _p(qr_q), _p(qr_s), _p(qr_b), _p(win_q), _p(win_s), c_int64(win_q.stride(0)),
+                              _p(qr_q), _p(qr_s), _p(qr_atom), _p(qr_b), _p(win_q), _p(win_s), c_int64(win_q.stride(0)),
                               c_int64(win_s.stride(0)), c_int(n), c_int(q), c_int(hd), c_int(rd), c_int(ring),
                               c_float(eps), _stream())
     _check(code, "qkv_post")
@@ -248,3 +249,39 @@ def umma_dense(tmap_a: TensorMap, tmap_b: TensorMap, sfa, sfb, n, N, K, *, group
                                 c_int(1 if a_fp4 else 0), c_int(splits), _p(scratch), _p(tickets), _p(out_b),
                                 _p(out_f), c_int64(out_stride), _p(status), _stream())
     _check(code, "umma_dense")
+
+
+def quant_rows(x, q, s, atom, n, K, split=False, split_off=0):
+    _check(lib().sfb_quant_rows(_p(x), _p(q), _p(s), _p(atom), c_int(n), c_int(K), c_int(1 if split else 0),
+                                c_int(split_off), _stream()), "quant_rows")
+
+
+def umma_dense_pair(tmap_a, tmap_b, sfa, sfb, pair, N, K, *, groups=1, a_fp4=False, splits=1, scratch=None,
+                    tickets=None, out_b=None, out_f=None, out_stride=None, status=None, NP=None):
+    """Two-term activations (rows [0, pair) hi, [pair, 2*pair) lo, see csrc/k_quant.cu): out = A.hi + A.lo."""
+    NP = NP or umma_np(2 * pair)
+    if out_stride is None:
+        out_stride = N * groups
+    code = lib().sfb_umma_dense_pair(c_void_p(tmap_a.ptr), c_void_p(tmap_b.ptr), _p(sfa), c_int(K // 128), _p(sfb),
+                                     c_int(K * groups // 128), c_int(pair), c_int(NP), c_int(N), c_int(K),
+                                     c_int(groups), c_int(1 if a_fp4 else 0), c_int(splits), _p(scratch), _p(tickets),
+                                     _p(out_b), _p(out_f), c_int64(out_stride), _p(status), _stream())
+    _check(code, "umma_dense_pair")
+
+
+def umma_gate_up(tmap_a, tmap_a2, tmap_b, sfa, sfa2, sfb, ids, wts, act_q, act_s, act_sf, n_tok, top_k, slots, d,
+                 inter, limit, status=None):
+    code = lib().sfb_umma_gate_up(c_void_p(tmap_a.ptr), c_void_p(tmap_a2.ptr) if tmap_a2 else None,
+                                  c_void_p(tmap_b.ptr), _p(sfa), _p(sfa2), _p(sfb), _p(ids), _p(wts), _p(act_q),
+                                  _p(act_s), _p(act_sf), c_int(n_tok), c_int(top_k), c_int(slots), c_int(d),
+                                  c_int(inter), c_float(limit), _p(status), _stream())
+    _check(code, "umma_gate_up")
+
+
+def umma_down(tmap_a, tmap_a2, tmap_b, sfa, sfa2, sfb, ids, out_b, out_f, out_stride, scratch, tickets, n_tok, top_k,
+              slots, d, inter, status=None):
+    code = lib().sfb_umma_down(c_void_p(tmap_a.ptr), c_void_p(tmap_a2.ptr) if tmap_a2 else None, c_void_p(tmap_b.ptr),
+                               _p(sfa), _p(sfa2), _p(sfb), _p(ids), _p(out_b), _p(out_f), c_int64(out_stride),
+                               _p(scratch), _p(tickets), c_int(n_tok), c_int(top_k), c_int(slots), c_int(d),
+                               c_int(inter), _p(status), _stream())
+    _check(code, "umma_down")

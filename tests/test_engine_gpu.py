@@ -297,3 +297,41 @@ def test_generate_greedy_matches_oracle_prefix(tiny):
         scale = ref_logits[i].abs().max().item()
         err = (logits[i].cpu() - ref_logits[i]).abs()
         assert err.mean().item() < 0.03 * scale and err.max().item() < 0.5 * scale
+
+
+def test_tensor_core_arm_matches_cuda_core_arm_and_oracle(tiny):
+    """Same model through the tcgen05 arm: per-position logits stay within the reassociation tolerance
+    of the CUDA-core arm, and the first positions (no reduction-order freedom yet) agree closely with
+    the oracle."""
+    from sparkflash_b200.models.deepseek_v41 import engine as E
+    cfg, ck, w, orc, dw = tiny
+    a = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, use_graphs=False, arm="cuda")
+    b = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, use_graphs=False, arm="tc")
+    assert b.tcl[0].wqkv_a is not None and b.tcl[0].w13 is not None
+    prompt = _prompt(cfg, 24, seed=8)
+    st = orc.new_state()
+    errs, agree = [], 0
+    for pos, tok in enumerate(prompt):
+        ol = orc.step(st, tok)
+        a.step([tok], [0], [pos]); b.step([tok], [0], [pos])
+        la, lb = a.logits[0].cpu(), b.logits[0].cpu()
+        scale = ol.abs().max().item()
+        if pos < 3:
+            assert (lb - ol).abs().max().item() < 0.02 * scale, (pos, (lb - ol).abs().max().item())
+        errs.append((la - lb).abs().mean().item() / scale)
+        agree += int(la.argmax()) == int(lb.argmax())
+    a.check_status(); b.check_status()
+    assert sum(errs) / len(errs) < 0.03 and agree >= 0.7 * len(prompt), (sum(errs) / len(errs), agree)
+    # rows step on the tensor-core arm: chunked rows reproduce the single-row logits bit for bit
+    c = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, use_graphs=True, arm="tc")
+    single = []
+    d_ = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, use_graphs=False, arm="tc")
+    for pos, tok in enumerate(prompt[:20]):
+        d_.step([tok], [0], [pos]); single.append(d_.logits[0].clone())
+    pos = 0
+    for n_ in (7, 13):
+        c.step(prompt[pos:pos + n_], [1] * n_, list(range(pos, pos + n_)))
+        for i in range(n_):
+            assert torch.equal(c.logits[i], single[pos + i]), f"row {pos + i} depends on the batch (tc arm)"
+        pos += n_
+    c.check_status()
