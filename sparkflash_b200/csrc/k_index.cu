@@ -11,10 +11,8 @@
 
 namespace sfb {
 
-__device__ __forceinline__ void rope_pair_f(float& a, float& b, int pos, double inv_freq) {
-  double s, c;
-  sincos((double)pos * inv_freq, &s, &c);
-  float cf = (float)c, sf = (float)s;
+__device__ __forceinline__ void rope_pair_f(float& a, float& b, float2 cs) {
+  float cf = cs.x, sf = cs.y;
   float na = a * cf - b * sf, nb = a * sf + b * cf;
   a = na; b = nb;
 }
@@ -25,7 +23,8 @@ struct IndexQArgs {
   int64_t q_stride, q_off;
   const float* wraw;          // [n, w_stride] weights_proj output (fp32) at w_off: [inh]
   int64_t w_stride, w_off;
-  const double* inv_freq;
+  const float2* rope;         // [n, rope_stride]
+  int rope_stride;
   const int* row_pos;
   float* qi;                  // [n, idh, inh]  (transposed: element-major, head-minor)
   float* wt;                  // [n, inh]
@@ -35,7 +34,7 @@ struct IndexQArgs {
 
 // grid n, block 256; one warp per (head, 32-group)
 __global__ void __launch_bounds__(256) index_q_kernel(IndexQArgs a) {
-  const int row = blockIdx.x, pos = a.row_pos[row];
+  const int row = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gph = a.idh / 32;
   for (int item = warp; item < a.inh * gph; item += 8) {
@@ -47,7 +46,7 @@ __global__ void __launch_bounds__(256) index_q_kernel(IndexQArgs a) {
       const int p = (e - r0) >> 1;
       float other = __shfl_xor_sync(0xffffffffu, v, 1);
       float x = (e & 1) ? other : v, y = (e & 1) ? v : other;
-      rope_pair_f(x, y, pos, a.inv_freq[p]);
+      rope_pair_f(x, y, a.rope[(size_t)row * a.rope_stride + p]);
       v = (e & 1) ? y : x;
     } else {
       (void)__shfl_xor_sync(0xffffffffu, v, 1);
@@ -276,10 +275,11 @@ using namespace sfb;
 extern "C" {
 
 int sfb_index_q(const void* qraw, int64_t q_stride, int64_t q_off, const float* wraw, int64_t w_stride,
-                int64_t w_off, const double* inv_freq, const int* row_pos, float* qi, float* wt, int n,
+                int64_t w_off, const void* rope, int rope_stride, const int* row_pos, float* qi, float* wt, int n,
                 int inh, int idh, int rd, float wscale, cudaStream_t stream) {
   if (idh % 32) return (int)cudaErrorInvalidValue;
-  IndexQArgs a{(const __nv_bfloat16*)qraw, q_stride, q_off, wraw, w_stride, w_off, inv_freq, row_pos, qi, wt,
+  IndexQArgs a{(const __nv_bfloat16*)qraw, q_stride, q_off, wraw, w_stride, w_off, (const float2*)rope, rope_stride,
+               row_pos, qi, wt,
                n, inh, idh, rd, wscale};
   index_q_kernel<<<n, 256, 0, stream>>>(a);
   return SFB_CHECK_LAUNCH();

@@ -10,10 +10,8 @@
 
 namespace sfb {
 
-__device__ __forceinline__ void rope_pair(float& a, float& b, int pos, double inv_freq, bool inverse) {
-  double s, c;
-  sincos((double)pos * inv_freq, &s, &c);
-  float cf = (float)c, sf = (float)s;
+__device__ __forceinline__ void rope_pair(float& a, float& b, float2 cs, bool inverse) {
+  float cf = cs.x, sf = cs.y;
   if (inverse) sf = -sf;
   float na = a * cf - b * sf, nb = a * sf + b * cf;
   a = na; b = nb;
@@ -23,7 +21,8 @@ struct QkvPostArgs {
   const __nv_bfloat16* raw;   // [n, q + hd]: wq_a output then wkv output
   const float* q_norm_w;      // [q]
   const float* kv_norm_w;     // [hd]
-  const double* inv_freq;     // [rd/2]
+  const float2* rope;         // [n, rope_stride]: (cos, sin) of the row's position, this layer's variant
+  int rope_stride;
   const int* row_lane;        // [n]
   const int* row_pos;         // [n]
   uint8_t* qr_q;              // [n, q] e4m3
@@ -43,11 +42,12 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
   extern __shared__ float buf[];  // max(q, hd) floats
   const int row = blockIdx.x;
   const __nv_bfloat16* raw = a.raw + (size_t)row * (a.q + a.hd);
+  float ss = 0.f, rs;
+  if (blockIdx.y == 0) {
   // ---- q_norm + quant ----
-  float ss = 0.f;
   for (int i = threadIdx.x; i < a.q; i += 256) { float v = bf16_to_f(raw[i]); buf[i] = v; ss += v * v; }
   ss = block_sum(ss, sh);
-  float rs = rsqrtf(ss / (float)a.q + a.eps);
+  rs = rsqrtf(ss / (float)a.q + a.eps);
   for (int i0 = (threadIdx.x >> 5) * 32; i0 < a.q; i0 += 256) {
     const int i = i0 + (threadIdx.x & 31);
     float v = bfr(buf[i] * rs * a.q_norm_w[i]);
@@ -60,7 +60,8 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
       if (a.qr_atom) a.qr_atom[sf_offset(row, i / 32, a.q / 32)] = sc;
     }
   }
-  __syncthreads();
+  return;
+  }
   // ---- kv_norm + rope + fp8 + window append ----
   const int pos = a.row_pos[row], lane_id = a.row_lane[row];
   ss = 0.f;
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
   const int r0 = a.hd - a.rd;
   for (int p = threadIdx.x; p < a.rd / 2; p += 256) {
     float x = buf[r0 + 2 * p], y = buf[r0 + 2 * p + 1];
-    rope_pair(x, y, pos, a.inv_freq[p], false);
+    rope_pair(x, y, a.rope[(size_t)row * a.rope_stride + p], false);
     buf[r0 + 2 * p] = bfr(x); buf[r0 + 2 * p + 1] = bfr(y);
   }
   __syncthreads();
@@ -94,7 +95,8 @@ struct CompressArgs {
   const float* norm_w;       // [hd]
   const __nv_bfloat16* wk;   // [idh, hd] indexer key projection
   const float* k_norm_w;     // [idh]
-  const double* inv_freq;    // [rd/2]
+  const float2* rope;        // [n, rope_stride]: (cos, sin) at the compressed position of the row
+  int rope_stride;
   const int* row_lane;
   const int* row_pos;
   float* cin;                // [lanes, cring, 2*hd] pending (kv, score) per position (ratio > 1)
@@ -159,7 +161,7 @@ __global__ void __launch_bounds__(256) compress_append_kernel(CompressArgs a) {
   float rs = rsqrtf(ss / (float)hd + a.eps);
   for (int i = threadIdx.x; i < hd; i += 256) lat[i] = bfr(lat[i] * rs * a.norm_w[i]);
   __syncthreads();
-  const int j = pos / ratio, cpos = j * ratio;
+  const int j = pos / ratio;
   if (j >= a.max_entries) { status_set(a.status, ST_BOUNDS, 2, j, a.max_entries); return; }
   // ---- index key: k_norm(wk . latent), rope, MXFP4 ----
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -182,13 +184,13 @@ __global__ void __launch_bounds__(256) compress_append_kernel(CompressArgs a) {
     {
       const int r0 = a.idh - a.rd;
       float x = key[r0 + 2 * p], y = key[r0 + 2 * p + 1];
-      rope_pair(x, y, cpos, a.inv_freq[p], false);
+      rope_pair(x, y, a.rope[(size_t)row * a.rope_stride + p], false);
       key[r0 + 2 * p] = bfr(x); key[r0 + 2 * p + 1] = bfr(y);
     }
     {
       const int r0 = hd - a.rd;
       float x = rot[r0 + 2 * p], y = rot[r0 + 2 * p + 1];
-      rope_pair(x, y, cpos, a.inv_freq[p], false);
+      rope_pair(x, y, a.rope[(size_t)row * a.rope_stride + p], false);
       rot[r0 + 2 * p] = bfr(x); rot[r0 + 2 * p + 1] = bfr(y);
     }
   }
@@ -229,27 +231,28 @@ using namespace sfb;
 
 extern "C" {
 
-int sfb_qkv_post(const void* raw, const float* q_norm_w, const float* kv_norm_w, const double* inv_freq,
+int sfb_qkv_post(const void* raw, const float* q_norm_w, const float* kv_norm_w, const void* rope, int rope_stride,
                  const int* row_lane, const int* row_pos, void* qr_q, void* qr_s, void* qr_atom, void* qr_b, void* win_q,
                  void* win_s, int64_t win_lane_stride_q, int64_t win_lane_stride_s, int n, int q, int hd,
                  int rd, int ring, float eps, cudaStream_t stream) {
   if (q % 32 || hd % 32 || rd % 2) return (int)cudaErrorInvalidValue;
-  QkvPostArgs a{(const __nv_bfloat16*)raw, q_norm_w, kv_norm_w, inv_freq, row_lane, row_pos,
+  QkvPostArgs a{(const __nv_bfloat16*)raw, q_norm_w, kv_norm_w, (const float2*)rope, rope_stride, row_lane, row_pos,
                 (uint8_t*)qr_q, (uint8_t*)qr_s, (uint8_t*)qr_atom, (__nv_bfloat16*)qr_b, (uint8_t*)win_q, (uint8_t*)win_s,
                 win_lane_stride_q, win_lane_stride_s, n, q, hd, rd, ring, eps};
   const size_t smem = sizeof(float) * (size_t)(q > hd ? q : hd);
-  qkv_post_kernel<<<n, 256, smem, stream>>>(a);
+  qkv_post_kernel<<<dim3(n, 2), 256, smem, stream>>>(a);
   return SFB_CHECK_LAUNCH();
 }
 
 int sfb_compress_append(const float* raw, int64_t raw_stride, const float* norm_w, const void* wk,
-                        const float* k_norm_w, const double* inv_freq, const int* row_lane,
+                        const float* k_norm_w, const void* rope, int rope_stride, const int* row_lane,
                         const int* row_pos, float* cin, int64_t cin_lane_stride, int cring, void* ckv_q,
                         void* ckv_s, void* ik_q, void* ik_s, int64_t ckv_lane_q, int64_t ckv_lane_s,
                         int64_t ik_lane_q, int64_t ik_lane_s, int max_entries, int n, int hd, int idh,
                         int rd, int ratio, float eps, void* status, cudaStream_t stream) {
   if (hd % 32 || idh % 32) return (int)cudaErrorInvalidValue;
-  CompressArgs a{raw, raw_stride, norm_w, (const __nv_bfloat16*)wk, k_norm_w, inv_freq, row_lane, row_pos,
+  CompressArgs a{raw, raw_stride, norm_w, (const __nv_bfloat16*)wk, k_norm_w, (const float2*)rope, rope_stride,
+                 row_lane, row_pos,
                  cin, cin_lane_stride, cring, (uint8_t*)ckv_q, (uint8_t*)ckv_s, (uint8_t*)ik_q,
                  (uint8_t*)ik_s, ckv_lane_q, ckv_lane_s, ik_lane_q, ik_lane_s, max_entries, n, hd, idh, rd,
                  ratio, eps, (Status*)status};

@@ -29,6 +29,27 @@ __global__ void tap_mean_kernel(const __nv_bfloat16* h, __nv_bfloat16* tap, int6
   tap[(size_t)row * tap_stride + col] = __float2bfloat16_rn(s / (float)hc);
 }
 
+// rope[row, v, p] = (cos, sin)(angle) with angle = ((pos / ratio_v) * ratio_v) * inv_freq_v[p], evaluated in
+// double once per step; every layer's kernels read this table instead of calling sincos themselves.
+struct RopeTableArgs {
+  const double* inv_freq[4];
+  int ratio[4];
+  int V, half;
+  const int* row_pos;
+  float2* out;  // [n, V, half]
+};
+__global__ void rope_table_kernel(RopeTableArgs a) {
+  const int row = blockIdx.x;
+  const int pos = a.row_pos[row];
+  for (int i = threadIdx.x; i < a.V * a.half; i += blockDim.x) {
+    const int v = i / a.half, p = i - v * a.half;
+    const int pp = (pos / a.ratio[v]) * a.ratio[v];
+    double s, c;
+    sincos((double)pp * a.inv_freq[v][p], &s, &c);
+    a.out[((size_t)row * a.V + v) * a.half + p] = make_float2((float)c, (float)s);
+  }
+}
+
 __device__ __forceinline__ float gumbel(uint64_t base, int id) {
   const uint64_t h = splitmix64(base ^ ((uint64_t)id * 0x9E3779B97F4A7C15ull));
   const double u = ((double)(h >> 40) + 0.5) * (1.0 / 16777216.0);
@@ -158,6 +179,17 @@ int sfb_embed(const void* embed, const int* tokens, void* h, int n, int hc, int 
   if (d % 8) return (int)cudaErrorInvalidValue;
   embed_kernel<<<dim3((d / 8 + 127) / 128, n), 128, 0, stream>>>((const __nv_bfloat16*)embed, tokens,
                                                                (__nv_bfloat16*)h, n, hc, d, vocab, (Status*)status);
+  return SFB_CHECK_LAUNCH();
+}
+
+// variants: V <= 4 (inv_freq device pointer, ratio) pairs
+int sfb_rope_table(const double* const* inv_freq, const int* ratio, int V, int half, const int* row_pos, void* out,
+                   int n, cudaStream_t stream) {
+  if (V < 1 || V > 4) return (int)cudaErrorInvalidValue;
+  RopeTableArgs a{};
+  for (int v = 0; v < V; ++v) { a.inv_freq[v] = inv_freq[v]; a.ratio[v] = ratio[v] > 0 ? ratio[v] : 1; }
+  a.V = V; a.half = half; a.row_pos = row_pos; a.out = (float2*)out;
+  rope_table_kernel<<<n, 128, 0, stream>>>(a);
   return SFB_CHECK_LAUNCH();
 }
 

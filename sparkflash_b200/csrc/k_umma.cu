@@ -153,6 +153,8 @@ struct UmmaArgs {
   __nv_bfloat16* out_b;
   float* out_f;
   int64_t out_stride;
+  uint8_t* out_q;             // optional: the bf16-rounded output re-quantised per 32 columns (E4M3)
+  uint8_t* out_q_atom;        //           and its scale atoms (rows = tokens, kb = out_stride/32)
   // MoE
   const int* ids;             // [n_tok, top_k] expert ids
   const float* wts;           // [n_tok, top_k]
@@ -314,11 +316,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int tok = c0 + j;
-          if (tok < nv && col_ok) {
-            const float f = __uint_as_float(v[j]);
+          if (tok < nv) {   // warp-uniform
+            const float f = col_ok ? __uint_as_float(v[j]) : 0.f;
             const int64_t o = (int64_t)(w.out_row0 + tok) * a.out_stride + col;
-            if (a.out_b) a.out_b[o] = __float2bfloat16_rn(f);
-            if (a.out_f) a.out_f[o] = f;
+            if (col_ok) {
+              if (a.out_b) a.out_b[o] = __float2bfloat16_rn(f);
+              if (a.out_f) a.out_f[o] = f;
+            }
+            if (a.out_q) {
+              uint8_t sc;
+              const uint8_t code = warp_quant_fp8(bfr(f), &sc);
+              if (col_ok) {
+                a.out_q[o] = code;
+                if (lane == 0) a.out_q_atom[sf_offset(w.out_row0 + tok, col >> 5, (int)(a.out_stride >> 5))] = sc;
+              }
+            }
           }
         }
       } else {
@@ -339,18 +351,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         if (S.last_flag) a.tickets[w.tile_id] = 0;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (S.last_flag && col_ok) {
+      if (S.last_flag) {
         __threadfence();
         for (int tok = 0; tok < nv; ++tok) {
           float s = 0.f;
           for (int sp = 0; sp < w.splits; ++sp) {
             const float* pp = a.scratch + (size_t)sp * split_stride + lane_off;
-            s += pp[tok];
-            if (a.pair > 0) s += pp[tok + a.pair];
+            s += __ldcg(pp + tok);
+            if (a.pair > 0) s += __ldcg(pp + tok + a.pair);
           }
+          if (!col_ok) s = 0.f;
           const int64_t o = (int64_t)(w.out_row0 + tok) * a.out_stride + col;
-          if (a.out_b) a.out_b[o] = __float2bfloat16_rn(s);
-          if (a.out_f) a.out_f[o] = s;
+          if (col_ok) {
+            if (a.out_b) a.out_b[o] = __float2bfloat16_rn(s);
+            if (a.out_f) a.out_f[o] = s;
+          }
+          if (a.out_q) {
+            uint8_t sc;
+            const uint8_t code = warp_quant_fp8(bfr(s), &sc);
+            if (col_ok) {
+              a.out_q[o] = code;
+              if (lane == 0) a.out_q_atom[sf_offset(w.out_row0 + tok, col >> 5, (int)(a.out_stride >> 5))] = sc;
+            }
+          }
         }
       }
     }
@@ -565,14 +588,14 @@ int sfb_umma_dense(const void* tmapA, const void* tmapB, const void* sfa, int ka
 int sfb_umma_dense_pair(const void* tmapA, const void* tmapB, const void* sfa, int katoms_a, const void* sfb,
                         int katoms_b, int pair, int NP, int N, int K, int groups, int a_fp4, int splits,
                         float* scratch, unsigned int* tickets, void* out_b, float* out_f, int64_t out_stride,
-                        void* status, cudaStream_t stream) {
+                        void* out_q, void* out_q_atom, void* status, cudaStream_t stream) {
   if (N % 128 || K % UM_BK || 2 * pair > NP || pair < 1 || splits < 1 || splits > K / UM_BK || !scratch || !tickets)
     return (int)cudaErrorInvalidValue;
   UmmaArgs a{};
   a.sfa = (const uint8_t*)sfa; a.katoms_a = katoms_a; a.sfb = (const uint8_t*)sfb; a.katoms_b = katoms_b;
   a.n = 2 * pair; a.pair = pair; a.K = K; a.a_fp4 = a_fp4; a.mode = UM_DENSE; a.N = N; a.groups = groups;
   a.splits = splits; a.scratch = scratch; a.tickets = tickets; a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f;
-  a.out_stride = out_stride; a.status = (Status*)status;
+  a.out_stride = out_stride; a.out_q = (uint8_t*)out_q; a.out_q_atom = (uint8_t*)out_q_atom; a.status = (Status*)status;
   return launch_umma(tmapA, nullptr, tmapB, a, dim3(N / 128, splits, groups), NP, stream);
 }
 

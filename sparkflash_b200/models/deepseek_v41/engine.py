@@ -94,7 +94,10 @@ class Engine:
         self.xq, self.xs = e((R, d), u8), e((R, d // 32), u8)
         self.nblk = N.seam_nblk(d)
         self.mix = (2 + hc) * hc
-        self.partials = e((R, self.nblk, 2 + self.mix), f32)
+        self.partials = e((R, self.nblk, 1 + self.mix), f32)
+        self._side_stream = torch.cuda.Stream(device=dev)
+        self._coef_event = None
+        self.seam_tickets = e((R,), i32)
         cs = N.coef_stride(hc)
         self.coef = [e((R, cs), f32), e((R, cs), f32)]
         self.qkv_raw = e((R, q + hd), bf)
@@ -114,7 +117,13 @@ class Engine:
         self.cand_cnt = e((R,), i32)
         self.sel = e((R, cfg.index_topk), i32)
         self.sel_cnt = e((R,), i32)
+        # rotary table of the step: variants (plain theta, ratio 1), (compressed theta, ratio r) for each r used
+        ratios = sorted({cfg.ratio(l) for l in range(cfg.n_layers) if cfg.ratio(l) > 0} | {1})
+        self.rope_variants = [(False, 1)] + [(True, r) for r in ratios]
+        self.rope = e((R, len(self.rope_variants), cfg.rope_dim // 2, 2), f32)
         self.attn_out = e((R, self.hl * hd), bf)
+        self.attn_scratch = e((N.attn_scratch_floats(R, self.hl, hd, 16),), f32)
+        self.attn_tickets = e((R * ((self.hl + 7) // 8),), i32)
         self.oa = e((R, self.gl * cfg.o_lora_rank), bf)
         # sublayer outputs: one bf16 partial per rank, folded by the next seam
         self.y_attn = e((R, d), bf)
@@ -165,21 +174,37 @@ class Engine:
 
     # ---- sublayers -------------------------------------------------------------------------------------
     def _seam(self, n: int, k: int, y_parts, fn, base, scale, norm_w, quant: bool = True, atoms: int = 0):
-        """Seam number k (0-based over the whole forward): finishes the previous sublayer with
-        coef[(k-1)%2] and writes this seam's coefficients to coef[k%2]."""
+        """Seam number k (0-based over the whole forward).  The fold half (critical path) finishes the previous
+        sublayer with coef[(k-1)%2]; the coefficient half runs on the side stream beside the sublayer's GEMMs
+        and writes coef[k%2] for the next seam."""
         cfg = self.cfg
         first = k == 0
         prev = self.coef[(k - 1) % 2]
-        N.seam(self.h, y_parts, None if first else prev, self.w.onehot if first else prev,
-               0 if first else prev.stride(0), fn, self.xhat, self.partials, norm_w, scale, base,
-               self.coef[k % 2] if fn is not None else None, self.xn, self.xq if quant else None,
-               self.xs if quant else None, n, cfg.hc_mult, cfg.hidden_size, cfg.hc_sinkhorn_iters, cfg.norm_eps,
-               cfg.hc_eps, status=self.status,
-               xs_atom=None if (self.tcl is None or not quant) else (self.tcb.xs_atom if atoms == 0 else self.tcb.xs_atom_tok),
-               atom_mode=atoms)
-        self.launches_per_step += 2 if self._counting else 0
+        main = torch.cuda.current_stream()
+        if self._coef_event is not None:
+            main.wait_event(self._coef_event)   # coefficients of seam k-1 are ready
+            self._coef_event = None
+        N.seam_fold(self.h, y_parts, None if first else prev, self.w.onehot if first else prev,
+                    0 if first else prev.stride(0), norm_w, self.xn, self.xq if quant else None,
+                    self.xs if quant else None, n, cfg.hc_mult, cfg.hidden_size, cfg.norm_eps, status=self.status,
+                    xs_atom=None if (self.tcl is None or not quant) else (self.tcb.xs_atom if atoms == 0 else self.tcb.xs_atom_tok),
+                    atom_mode=atoms)
+        self._k()
+        if fn is not None:
+            ev = torch.cuda.Event()
+            ev.record(main)
+            side = self._side_stream
+            side.wait_event(ev)
+            with torch.cuda.stream(side):
+                N.seam_coef(self.h, fn, scale, base, self.partials, self.seam_tickets, self.coef[k % 2], n, cfg.hc_mult,
+                            cfg.hidden_size, cfg.hc_sinkhorn_iters, cfg.norm_eps, cfg.hc_eps)
+                done = torch.cuda.Event()
+                done.record(side)
+            self._coef_event = done
+            self._k()
 
-    def _tc_dense(self, M, xq_buf, x_rows, atoms, n, N_, K, out_b, out_stride=None, groups=1, pair=0):
+    def _tc_dense(self, M, xq_buf, x_rows, atoms, n, N_, K, out_b, out_stride=None, groups=1, pair=0, out_q=None,
+                  out_q_atom=None):
         """One projection on the tensor-core arm: M = TcMatrix, xq_buf = FP8 activation codes [x_rows, K*groups]."""
         tcb = self.tcb
         NP = N.umma_np(2 * pair if pair else n)
@@ -189,18 +214,24 @@ class Engine:
         if pair:
             N.umma_dense_pair(M.tmap, tb, M.atoms, atoms, pair, N_, K, groups=groups, a_fp4=M.fp4, splits=splits,
                               scratch=tcb.scratch, tickets=tcb.tickets, out_b=out_b, out_stride=out_stride,
-                              status=self.status, NP=NP)
+                              status=self.status, NP=NP, out_q=out_q, out_q_atom=out_q_atom)
         else:
             N.umma_dense(M.tmap, tb, M.atoms, atoms, n, N_, K, groups=groups, a_fp4=M.fp4, splits=splits,
                          scratch=tcb.scratch, tickets=tcb.tickets, out_b=out_b, out_stride=out_stride,
                          status=self.status, NP=NP)
         self._k()
 
+    def _rope_view(self, compressed: bool, ratio: int) -> torch.Tensor:
+        """[R, stride] view of the step's rotary table for one variant (row stride = all variants)."""
+        v = self.rope_variants.index((compressed, ratio))
+        return self.rope[:, v]
+
     def _attention(self, n: int, l: int, L: LayerW, len_bucket: int):
         cfg, kv = self.cfg, self.kv
         d, hd, q, rd = cfg.hidden_size, cfg.head_dim, cfg.q_lora_rank, cfg.rope_dim
         ratio = cfg.ratio(l)
-        invf = self.w.inv_freq[ratio > 0]
+        invf = self._rope_view(ratio > 0, 1)                     # at the row's own position
+        invf_c = self._rope_view(True, ratio) if ratio > 0 else None   # at the compressed position
         T = self.tcl[l] if self.tcl is not None else None
         if T is not None and T.wqkv_a is not None:
             self._tc_dense(T.wqkv_a, self.xq, self.max_rows, self.tcb.xs_atom, n, q + hd, d, self.qkv_raw)
@@ -213,7 +244,7 @@ class Engine:
                    kv.win_q[l], kv.win_s[l], n, q, hd, rd, kv.ring, cfg.norm_eps,
                    qr_atom=self.tcb.qr_atom if T is not None else None); self._k()
         if cfg.is_kv_source(l):
-            N.compress_append(self.aux_raw, self.aux_raw.stride(0), L.comp_norm, L.idx_wk, L.idx_knorm, invf,
+            N.compress_append(self.aux_raw, self.aux_raw.stride(0), L.comp_norm, L.idx_wk, L.idx_knorm, invf_c,
                               self.row_lane, self.row_pos, kv.cin.get(l), kv.ring, kv.ckv_q[l], kv.ckv_s[l],
                               kv.ik_q[l], kv.ik_s[l], kv.max_entries[l], n, hd, cfg.index_head_dim, rd, ratio,
                               cfg.norm_eps, status=self.status); self._k()
@@ -245,21 +276,29 @@ class Engine:
             N.select_topk(self.scores, self.row_pos, ratio, 1, max_len, cfg.index_topk, self.sel, self.sel_cnt, n); self._k()
             self._dbg(f"L{l}.iscore", self.scores, n)
         has_c = ratio > 0
+        tc_wo_a = T is not None and T.wo_a is not None and 2 * n <= 128
         N.attn_rows(self.qfull, self.qfull.stride(0), invf, self.row_lane, self.row_pos, kv.win_q[l], kv.win_s[l],
                     kv.ckv_q[owner] if has_c else None, kv.ckv_s[owner] if has_c else None,
                     self.sel if has_c else None, self.sel_cnt if has_c else None, cfg.index_topk, L.sink,
-                    self.attn_out, n, self.hl, hd, rd, cfg.window, kv.ring, hd ** -0.5); self._k()
+                    self.attn_out, n, self.hl, hd, rd, cfg.window, kv.ring, hd ** -0.5, self.attn_scratch,
+                    self.attn_tickets, N.attn_pick_splits(self.hl),
+                    out_q=self.tcb.ao_q if tc_wo_a else None, out_atom=self.tcb.ao_atom if tc_wo_a else None); self._k()
         ol, gin = cfg.o_lora_rank, cfg.group_in
-        if T is not None and T.wo_a is not None and 2 * n <= 128:
-            # bf16 activations through the FP8 tensor path as a two-term split (hi + lo)
+        tc_wo_b = T is not None and T.wo_b is not None
+        fused_oa_q = False
+        if tc_wo_a:
+            # bf16 activations through the FP8 tensor path as a two-term split (hi + lo, written by the
+            # attention kernel); the epilogue re-quantises its output for wo_b
             tcb = self.tcb
-            N.quant_rows(self.attn_out, tcb.ao_q, None, tcb.ao_atom, n, self.hl * hd, split=True, split_off=n); self._k()
-            self._tc_dense(T.wo_a, tcb.ao_q, 2 * self.max_rows, tcb.ao_atom, n, ol, gin, self.oa, groups=self.gl, pair=n)
+            fused_oa_q = tc_wo_b
+            self._tc_dense(T.wo_a, tcb.ao_q, 2 * self.max_rows, tcb.ao_atom, n, ol, gin, self.oa, groups=self.gl, pair=n,
+                           out_q=tcb.oa_q if fused_oa_q else None, out_q_atom=tcb.oa_atom if fused_oa_q else None)
         else:
             N.gemv(N.WF_FP8, L.wo_a, L.wo_a_sf, gin, ol, gin, n, groups=self.gl, xb=self.attn_out, out_b=self.oa); self._k()
-        if T is not None and T.wo_b is not None:
+        if tc_wo_b:
             tcb = self.tcb
-            N.quant_rows(self.oa, tcb.oa_q, None, tcb.oa_atom, n, self.gl * ol); self._k()
+            if not fused_oa_q:
+                N.quant_rows(self.oa, tcb.oa_q, None, tcb.oa_atom, n, self.gl * ol); self._k()
             self._tc_dense(T.wo_b, tcb.oa_q, self.max_rows, tcb.oa_atom, n, d, self.gl * ol, self.y_attn)
         else:
             N.gemv(N.WF_FP8, L.wo_b, L.wo_b_sf, self.gl * ol, d, self.gl * ol, n, xb=self.oa, x_quant=True,
@@ -295,6 +334,8 @@ class Engine:
     def _forward(self, n: int, len_bucket: int):
         cfg, w = self.cfg, self.w
         N.embed(w.embed, self.tokens, self.h, n, cfg.hc_mult, cfg.hidden_size, cfg.vocab_size, self.status); self._k()
+        N.rope_table([w.inv_freq[c] for c, _ in self.rope_variants], [r for _, r in self.rope_variants], self.row_pos,
+                     self.rope, n); self._k()
         k = 0
         y_prev = None
         tap_i = 0

@@ -60,21 +60,26 @@ def coef_stride(hc: int) -> int:
     return 2 * hc + hc * hc
 
 
-def seam(h, y_parts, coef_prev, a_pre, a_stride, fn, xhat, partials, norm_w, hc_scale, hc_base, coef_out,
-         xn, xq, xs, n, hc, d, iters, norm_eps, hc_eps, ysum=None, flags=None, epoch=0, status=None,
-         xs_atom=None, atom_mode=0):
-    """One mHC seam (see csrc/k_seam.cu).  ``y_parts``: list of W partial outputs (tensors or raw device
-    addresses) or None for the first seam of a forward."""
+def seam_fold(h, y_parts, coef_prev, a_pre, a_stride, norm_w, xn, xq, xs, n, hc, d, norm_eps, ysum=None,
+              flags=None, epoch=0, status=None, xs_atom=None, atom_mode=0):
+    """Critical-path half of an mHC seam (see csrc/k_seam.cu).  ``y_parts``: list of W partial outputs
+    (tensors or raw device addresses) or None for the first seam of a forward."""
     has_post = y_parts is not None
     W = len(y_parts) if has_post else 1
     yp = _ptr_array(y_parts) if has_post else None
     fp = _ptr_array(flags) if flags is not None else None
-    code = lib().sfb_seam(_p(h), yp, fp, c_uint32(epoch), c_int(W), c_int(1 if has_post else 0),
-                          _p(coef_prev), _p(a_pre), c_int(a_stride), _p(fn), _p(xhat), _p(partials), _p(ysum),
-                          _p(norm_w), _p(hc_scale), _p(hc_base), _p(coef_out), _p(xn), _p(xq), _p(xs),
-                          _p(xs_atom), c_int(atom_mode), _p(status), c_int(n), c_int(hc), c_int(d), c_int(iters), c_float(norm_eps),
-                          c_float(hc_eps), _stream())
-    _check(code, "seam")
+    code = lib().sfb_seam_fold(_p(h), yp, fp, c_uint32(epoch), c_int(W), c_int(1 if has_post else 0), _p(coef_prev),
+                               _p(a_pre), c_int(a_stride), _p(ysum), _p(norm_w), _p(xn), _p(xq), _p(xs), _p(xs_atom),
+                               c_int(atom_mode), _p(status), c_int(n), c_int(hc), c_int(d), c_float(norm_eps),
+                               _stream())
+    _check(code, "seam_fold")
+
+
+def seam_coef(h, fn, hc_scale, hc_base, partials, tickets, coef_out, n, hc, d, iters, norm_eps, hc_eps):
+    code = lib().sfb_seam_coef(_p(h), _p(fn), _p(hc_scale), _p(hc_base), _p(partials), _p(tickets), _p(coef_out),
+                               c_int(n), c_int(hc), c_int(d), c_int(iters), c_float(norm_eps), c_float(hc_eps),
+                               _stream())
+    _check(code, "seam_coef")
 
 
 # ---- gemv -----------------------------------------------------------------------------------------------
@@ -94,19 +99,21 @@ def gemv(wfmt, w, sf, row_bytes, N, K, n, *, groups=1, xq=None, xs=None, xb=None
 
 
 # ---- kv -------------------------------------------------------------------------------------------------
-def qkv_post(raw, q_norm_w, kv_norm_w, inv_freq, row_lane, row_pos, qr_q, qr_s, win_q, win_s, n, q, hd, rd,
+def qkv_post(raw, q_norm_w, kv_norm_w, rope, row_lane, row_pos, qr_q, qr_s, win_q, win_s, n, q, hd, rd,
              ring, eps, qr_b=None, qr_atom=None):
-    code = lib().sfb_qkv_post(_p(raw), _p(q_norm_w), _p(kv_norm_w), _p(inv_freq), _p(row_lane), _p(row_pos),
+    code = lib().sfb_qkv_post(_p(raw), _p(q_norm_w), _p(kv_norm_w), _p(rope), c_int(rope.stride(0) // 2), _p(row_lane),
+                              _p(row_pos),
                               _p(qr_q), _p(qr_s), _p(qr_atom), _p(qr_b), _p(win_q), _p(win_s), c_int64(win_q.stride(0)),
                               c_int64(win_s.stride(0)), c_int(n), c_int(q), c_int(hd), c_int(rd), c_int(ring),
                               c_float(eps), _stream())
     _check(code, "qkv_post")
 
 
-def compress_append(raw, raw_stride, norm_w, wk, k_norm_w, inv_freq, row_lane, row_pos, cin, cring, ckv_q,
+def compress_append(raw, raw_stride, norm_w, wk, k_norm_w, rope, row_lane, row_pos, cin, cring, ckv_q,
                     ckv_s, ik_q, ik_s, max_entries, n, hd, idh, rd, ratio, eps, status=None):
     code = lib().sfb_compress_append(
-        _p(raw), c_int64(raw_stride), _p(norm_w), _p(wk), _p(k_norm_w), _p(inv_freq), _p(row_lane), _p(row_pos),
+        _p(raw), c_int64(raw_stride), _p(norm_w), _p(wk), _p(k_norm_w), _p(rope), c_int(rope.stride(0) // 2), _p(row_lane),
+        _p(row_pos),
         _p(cin), c_int64(cin.stride(0) if cin is not None else 0), c_int(cring), _p(ckv_q), _p(ckv_s), _p(ik_q),
         _p(ik_s), c_int64(ckv_q.stride(0)), c_int64(ckv_s.stride(0)), c_int64(ik_q.stride(0)),
         c_int64(ik_s.stride(0)), c_int(max_entries), c_int(n), c_int(hd), c_int(idh), c_int(rd), c_int(ratio),
@@ -115,9 +122,9 @@ def compress_append(raw, raw_stride, norm_w, wk, k_norm_w, inv_freq, row_lane, r
 
 
 # ---- indexer ---------------------------------------------------------------------------------------------
-def index_q(qraw, q_stride, q_off, wraw, w_stride, w_off, inv_freq, row_pos, qi, wt, n, inh, idh, rd, wscale):
+def index_q(qraw, q_stride, q_off, wraw, w_stride, w_off, rope, row_pos, qi, wt, n, inh, idh, rd, wscale):
     code = lib().sfb_index_q(_p(qraw), c_int64(q_stride), c_int64(q_off), _p(wraw), c_int64(w_stride),
-                             c_int64(w_off), _p(inv_freq), _p(row_pos), _p(qi), _p(wt), c_int(n), c_int(inh),
+                             c_int64(w_off), _p(rope), c_int(rope.stride(0) // 2), _p(row_pos), _p(qi), _p(wt), c_int(n), c_int(inh),
                              c_int(idh), c_int(rd), c_float(wscale), _stream())
     _check(code, "index_q")
 
@@ -150,15 +157,28 @@ def select_topk(scores, row_pos, ratio, len_div, max_len, K, ids, count, n):
 
 
 # ---- attention ---------------------------------------------------------------------------------------------
-def attn_rows(q, q_stride, inv_freq, row_lane, row_pos, win_q, win_s, ckv_q, ckv_s, sel, sel_count, K, sink,
-              out, n, heads, hd, rd, window, ring, scale):
+def attn_rows(q, q_stride, rope, row_lane, row_pos, win_q, win_s, ckv_q, ckv_s, sel, sel_count, K, sink,
+              out, n, heads, hd, rd, window, ring, scale, scratch, tickets, splits, out_q=None, out_atom=None):
     code = lib().sfb_attn_rows(
-        _p(q), c_int64(q_stride), _p(inv_freq), _p(row_lane), _p(row_pos), _p(win_q), _p(win_s),
+        _p(q), c_int64(q_stride), _p(rope), c_int(rope.stride(0) // 2), _p(row_lane), _p(row_pos), _p(win_q), _p(win_s),
         c_int64(win_q.stride(0)), c_int64(win_s.stride(0)), _p(ckv_q), _p(ckv_s),
         c_int64(ckv_q.stride(0) if ckv_q is not None else 0), c_int64(ckv_s.stride(0) if ckv_s is not None else 0),
-        _p(sel), _p(sel_count), c_int(K), _p(sink), _p(out), c_int(n), c_int(heads), c_int(hd), c_int(rd),
+        _p(sel), _p(sel_count), c_int(K), _p(sink), _p(out), _p(out_q), _p(out_atom), _p(scratch), _p(tickets), c_int(splits),
+        c_int(n), c_int(heads),
+        c_int(hd), c_int(rd),
         c_int(window), c_int(ring), c_float(scale), _stream())
     _check(code, "attn_rows")
+
+
+def attn_scratch_floats(n, heads, hd, splits):
+    return int(lib().sfb_attn_scratch_floats(c_int(n), c_int(heads), c_int(hd), c_int(splits)))
+
+
+def attn_pick_splits(heads, target_blocks=148):
+    """Entry splits per (row, head group).  Depends on the head count only - never on the number of rows -
+    so that a row's partition and merge order (hence its bits) are the same in every batch."""
+    groups = (heads + 7) // 8
+    return max(1, min(16, -(-target_blocks // groups)))
 
 
 # ---- moe ---------------------------------------------------------------------------------------------------
@@ -185,6 +205,15 @@ def moe_down(act_q, act_s, ids, w2, w2_sf, s2, s2_sf, out, n, k, d, inter):
 def embed(table, tokens, h, n, hc, d, vocab, status=None):
     _check(lib().sfb_embed(_p(table), _p(tokens), _p(h), c_int(n), c_int(hc), c_int(d), c_int(vocab), _p(status),
                            _stream()), "embed")
+
+
+def rope_table(inv_freqs, ratios, row_pos, out, n):
+    """out: float32 [n, V, rd/2, 2] - (cos, sin) per row, variant and rotary pair (csrc/k_misc.cu)."""
+    V = len(inv_freqs)
+    ptrs = (c_void_p * 4)(*[t.data_ptr() for t in inv_freqs])
+    rat = (c_int * 4)(*ratios)
+    _check(lib().sfb_rope_table(ptrs, rat, c_int(V), c_int(out.shape[2]), _p(row_pos), _p(out), c_int(n), _stream()),
+           "rope_table")
 
 
 def tap_mean(h, tap, tap_stride, n, hc, d):
@@ -257,7 +286,8 @@ def quant_rows(x, q, s, atom, n, K, split=False, split_off=0):
 
 
 def umma_dense_pair(tmap_a, tmap_b, sfa, sfb, pair, N, K, *, groups=1, a_fp4=False, splits=1, scratch=None,
-                    tickets=None, out_b=None, out_f=None, out_stride=None, status=None, NP=None):
+                    tickets=None, out_b=None, out_f=None, out_stride=None, status=None, NP=None, out_q=None,
+                    out_q_atom=None):
     """Two-term activations (rows [0, pair) hi, [pair, 2*pair) lo, see csrc/k_quant.cu): out = A.hi + A.lo."""
     NP = NP or umma_np(2 * pair)
     if out_stride is None:
@@ -265,7 +295,8 @@ def umma_dense_pair(tmap_a, tmap_b, sfa, sfb, pair, N, K, *, groups=1, a_fp4=Fal
     code = lib().sfb_umma_dense_pair(c_void_p(tmap_a.ptr), c_void_p(tmap_b.ptr), _p(sfa), c_int(K // 128), _p(sfb),
                                      c_int(K * groups // 128), c_int(pair), c_int(NP), c_int(N), c_int(K),
                                      c_int(groups), c_int(1 if a_fp4 else 0), c_int(splits), _p(scratch), _p(tickets),
-                                     _p(out_b), _p(out_f), c_int64(out_stride), _p(status), _stream())
+                                     _p(out_b), _p(out_f), c_int64(out_stride), _p(out_q), _p(out_q_atom), _p(status),
+                                     _stream())
     _check(code, "umma_dense_pair")
 
 

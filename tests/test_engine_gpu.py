@@ -189,16 +189,17 @@ def test_seam_matches_oracle_math():
         dev = "cuda"
         hd_ = h.clone().to(dev)
         nblk = N.seam_nblk(d)
-        xhat = torch.zeros(n, d, dtype=torch.bfloat16, device=dev)
-        partials = torch.zeros(n, nblk, 2 + mix, device=dev)
+        partials = torch.zeros(n, nblk, 1 + mix, device=dev)
         coef = torch.zeros(n, N.coef_stride(hc), device=dev)
         xn = torch.zeros(n, d, dtype=torch.bfloat16, device=dev)
         xq = torch.zeros(n, d, dtype=torch.uint8, device=dev)
         xs = torch.zeros(n, d // 32, dtype=torch.uint8, device=dev)
         prev_d = prev.to(dev)
-        N.seam(hd_, [y_.to(dev) for y_ in ys], prev_d, prev_d, prev_d.stride(0), fn.to(dev), xhat, partials,
-               norm_w.to(dev), scale.to(dev), base.to(dev), coef, xn, xq, xs, n, hc, d, cfg.hc_sinkhorn_iters,
-               cfg.norm_eps, cfg.hc_eps)
+        tickets = torch.zeros(n, dtype=torch.int32, device=dev)
+        N.seam_fold(hd_, [y_.to(dev) for y_ in ys], prev_d, prev_d, prev_d.stride(0), norm_w.to(dev), xn, xq, xs, n,
+                    hc, d, cfg.norm_eps)
+        N.seam_coef(hd_, fn.to(dev), scale.to(dev), base.to(dev), partials, tickets, coef, n, hc, d,
+                    cfg.hc_sinkhorn_iters, cfg.norm_eps, cfg.hc_eps)
         torch.cuda.synchronize()
         rh = torch.stack(ref_h)
         assert (hd_.cpu().float() - rh).abs().max() <= 2 ** -7 * rh.abs().max(), "residual copies"
@@ -235,11 +236,15 @@ def test_attention_rows_matches_fp32_reference():
         sel[r, :k] = ids.int(); cnt[r] = k
     q = (torch.randn(n, heads * hd, generator=g) * 0.5).to(torch.bfloat16)
     sink = torch.randn(heads, generator=g)
-    out = torch.zeros(n, heads * hd, dtype=torch.bfloat16, device="cuda")
     dev = "cuda"
-    N.attn_rows(q.to(dev), heads * hd, invf.to(dev), lane.to(dev), pos.to(dev), wq.to(dev), ws.to(dev),
+    out = torch.zeros(n, heads * hd, dtype=torch.bfloat16, device=dev)
+    rope = torch.zeros(n, 1, rd // 2, 2, dtype=torch.float32, device=dev)
+    N.rope_table([invf.to(dev)], [1], pos.to(dev), rope, n)
+    N.attn_rows(q.to(dev), heads * hd, rope[:, 0], lane.to(dev), pos.to(dev), wq.to(dev), ws.to(dev),
                 C.pack_nibbles(cq).to(dev), cs.to(dev), sel.to(dev), cnt.to(dev), K, sink.to(dev), out, n, heads,
-                hd, rd, window, ring, hd ** -0.5)
+                hd, rd, window, ring, hd ** -0.5,
+                torch.zeros(N.attn_scratch_floats(n, heads, hd, 5), device=dev),
+                torch.zeros(n, dtype=torch.int32, device=dev), 5)
     torch.cuda.synchronize()
     wd = C.act_dequant_fp8(wq, ws)
     cd = C.kv_dequant_fp4(cq, cs)
