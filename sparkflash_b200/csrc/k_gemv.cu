@@ -41,6 +41,10 @@ struct GemvArgs {
   __nv_bfloat16* out_b;
   float* out_f;
   int64_t out_stride;
+  // split-K (blockIdx.z): slice z covers chunks [z*chunks/ksplit, (z+1)*chunks/ksplit) and writes its fp32
+  // partial to out_f + z*split_stride; the consumer adds the slices in index order
+  int ksplit;
+  int64_t split_stride;
 };
 
 template <int R>
@@ -117,6 +121,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int EPC = WF == 0 ? 16 : (WF == 1 ? 32 : 8);  // elements per 16-byte chunk
   const int chunks = a.K / EPC;
+  const int c_lo = (int)((int64_t)chunks * blockIdx.z / a.ksplit), c_hi = (int)((int64_t)chunks * (blockIdx.z + 1) / a.ksplit);
 
   for (int r0 = 0; r0 < a.n; r0 += R) {
     __syncthreads();
@@ -133,7 +138,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
     if (row0 < a.N) {
       const int64_t grow0 = (int64_t)g * a.N + row0;
       constexpr int U = 4;  // chunks in flight per row per lane
-      for (int cb = lane; cb < chunks; cb += 32 * U) {
+      for (int cb = c_lo + lane; cb < c_hi; cb += 32 * U) {
         uint4 wv[U][GV_RPW];
         float sc[U][GV_RPW];
 #pragma unroll
@@ -141,7 +146,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
           const int c = cb + 32 * u;
 #pragma unroll
           for (int i = 0; i < GV_RPW; ++i) {
-            const bool ok = row0 + i < a.N && c < chunks;
+            const bool ok = row0 + i < a.N && c < c_hi;
             const int64_t gr = row0 + i < a.N ? grow0 + i : grow0;
             if (ok) {
               wv[u][i] = ldg_nc(a.w + gr * a.row_bytes + (int64_t)c * 16);
@@ -157,7 +162,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const int c = cb + 32 * u;
-          if (c >= chunks) break;
+          if (c >= c_hi) break;
 #pragma unroll
           for (int i = 0; i < GV_RPW; ++i) {
             float f[EPC];
@@ -193,7 +198,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
         if (lane == 0 && orow < a.N && arow < a.n) {
           const int64_t o = (int64_t)arow * a.out_stride + (int64_t)g * a.N + orow;
           if (a.out_b) a.out_b[o] = __float2bfloat16_rn(v);
-          if (a.out_f) a.out_f[o] = v;
+          if (a.out_f) a.out_f[o + (int64_t)blockIdx.z * a.split_stride] = v;
         }
       }
    }
@@ -209,7 +214,7 @@ static int launch_gemv(const GemvArgs& a, cudaStream_t stream) {
   if (smem1 > 96 * 1024) return (int)cudaErrorInvalidValue;
   int tiles = (a.N + GV_ROWS - 1) / GV_ROWS;
   const int cap = (148 * 4 + a.groups - 1) / a.groups;  // a few resident blocks per SM; each loops over row tiles
-  dim3 grid(tiles < cap ? tiles : cap, a.groups);
+  dim3 grid(tiles < cap ? tiles : cap, a.groups, a.ksplit);
   const size_t smem = (size_t)smem1 * R;
 #define SFB_GV(RR)                                                                                   \
   {                                                                                                  \
@@ -234,7 +239,7 @@ extern "C" {
 // wfmt: 0 fp8, 1 fp4, 2 bf16.  Exactly one of xq / xb / xf is non-null; one or both outputs.
 int sfb_gemv(int wfmt, const void* w, const void* sf, int64_t row_bytes, int N, int K, int groups, int n,
              const void* xq, const void* xs, const void* xb, const void* xf, int64_t x_stride, int x_quant,
-             void* out_b, void* out_f, int64_t out_stride, cudaStream_t stream) {
+             void* out_b, void* out_f, int64_t out_stride, int ksplit, int64_t split_stride, cudaStream_t stream) {
   const int epc = wfmt == 0 ? 16 : (wfmt == 1 ? 32 : 8);
   if (K % 32 || K % epc || n <= 0 || (wfmt != 2 && sf == nullptr)) return (int)cudaErrorInvalidValue;
   GemvArgs a{};
@@ -242,6 +247,8 @@ int sfb_gemv(int wfmt, const void* w, const void* sf, int64_t row_bytes, int N, 
   a.KB = K / 32; a.groups = groups; a.n = n; a.xq = (const uint8_t*)xq; a.xs = (const uint8_t*)xs;
   a.xb = (const __nv_bfloat16*)xb; a.xf = (const float*)xf; a.x_stride = x_stride; a.x_quant = x_quant;
   a.out_b = (__nv_bfloat16*)out_b; a.out_f = (float*)out_f; a.out_stride = out_stride;
+  a.ksplit = ksplit < 1 ? 1 : ksplit; a.split_stride = split_stride;
+  if (a.ksplit > 1 && (out_b || !out_f)) return (int)cudaErrorInvalidValue;
   if (wfmt == 0) return launch_gemv<0>(a, stream);
   if (wfmt == 1) return launch_gemv<1>(a, stream);
   return launch_gemv<2>(a, stream);

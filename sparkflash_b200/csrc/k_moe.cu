@@ -14,7 +14,9 @@ namespace sfb {
 
 // ---- router ----------------------------------------------------------------------------------------------
 struct RouterArgs {
-  const float* dots;      // [n, E] raw gate logits (fp32)
+  const float* dots;      // [nsplit, n, E] raw gate logits (fp32), split-K slices added in index order
+  int nsplit;
+  int64_t split_stride;
   const float* bias;      // [E]
   const float* bias_vl;   // [E] (image rows) or null
   const uint8_t* is_image;  // [n] or null
@@ -34,7 +36,8 @@ __global__ void __launch_bounds__(128) router_topk_kernel(RouterArgs a) {
   const int row = blockIdx.x;
   const float* bias = (a.is_image && a.bias_vl && a.is_image[row]) ? a.bias_vl : a.bias;
   for (int e = threadIdx.x; e < a.E; e += 128) {
-    float x = a.dots[(size_t)row * a.E + e];
+    float x = 0.f;
+    for (int z = 0; z < a.nsplit; ++z) x += a.dots[(size_t)z * a.split_stride + (size_t)row * a.E + e];
     float sp = x > 20.f ? x : log1pf(expf(x));
     float v = sqrtf(sp);
     s[e] = v;
@@ -313,10 +316,10 @@ using namespace sfb;
 
 extern "C" {
 
-int sfb_router_topk(const float* dots, const float* bias, const float* bias_vl, const void* is_image, int* ids,
+int sfb_router_topk(const float* dots, int nsplit, int64_t split_stride, const float* bias, const float* bias_vl, const void* is_image, int* ids,
                     float* wts, int n, int E, int k, float route_scale, cudaStream_t stream) {
   if (k > 16) return (int)cudaErrorInvalidValue;
-  RouterArgs a{dots, bias, bias_vl, (const uint8_t*)is_image, ids, wts, n, E, k, route_scale};
+  RouterArgs a{dots, nsplit < 1 ? 1 : nsplit, split_stride, bias, bias_vl, (const uint8_t*)is_image, ids, wts, n, E, k, route_scale};
   router_topk_kernel<<<n, 128, sizeof(float) * 2 * E, stream>>>(a);
   return SFB_CHECK_LAUNCH();
 }

@@ -30,7 +30,10 @@ namespace sfb {
 
 constexpr int UM_THREADS = 192;
 constexpr int UM_BK = 128;        // K elements (= bytes in shared memory) per stage
-constexpr int UM_STAGES = 4;
+// pipeline depth per kernel flavour: as many bytes in flight per SM as shared memory allows
+constexpr int UM_STAGES_DENSE = 4;    // 16 KiB weights + <= 2 KiB tokens + 1 KiB scales per stage (NP <= 32)
+constexpr int UM_STAGES_WIDE = 4;     // NP = 64 / 128
+constexpr int UM_STAGES_GATEUP = 6;   // two weight tiles per stage
 constexpr int UM_A_BYTES = 128 * UM_BK;  // 16 KiB
 constexpr uint32_t UM_SPIN_LIMIT = 1u << 22;
 
@@ -168,14 +171,14 @@ struct UmmaArgs {
   Status* status;
 };
 
-template <int NP, int NA>  // token columns per accumulator; NA weight tiles per stage (2 for gate|up)
+template <int NP, int NA, int ST>  // token columns; weight tiles per stage (2 for gate|up); stages
 struct UmmaSmem {
-  alignas(1024) uint8_t a[UM_STAGES][NA][UM_A_BYTES];
-  alignas(1024) uint8_t b[UM_STAGES][NP * UM_BK];
-  alignas(128) uint8_t sfa[UM_STAGES][NA][512];
-  alignas(128) uint8_t sfb[UM_STAGES][512];
-  alignas(8) uint64_t full[UM_STAGES];
-  alignas(8) uint64_t empty[UM_STAGES];
+  alignas(1024) uint8_t a[ST][NA][UM_A_BYTES];
+  alignas(1024) uint8_t b[ST][NP * UM_BK];
+  alignas(128) uint8_t sfa[ST][NA][512];
+  alignas(128) uint8_t sfb[ST][512];
+  alignas(8) uint64_t full[ST];
+  alignas(8) uint64_t empty[ST];
   alignas(8) uint64_t acc_full;
   uint32_t tmem_base;
   int last_flag;
@@ -200,7 +203,8 @@ __global__ void __launch_bounds__(UM_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
                  const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
   extern __shared__ uint8_t smem_raw[];
-  using Smem = UmmaSmem<NP, 1>;
+  constexpr int UM_STAGES = NP <= 32 ? UM_STAGES_DENSE : UM_STAGES_WIDE;
+  using Smem = UmmaSmem<NP, 1, UM_STAGES>;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   UmmaWork w;
@@ -390,8 +394,9 @@ __global__ void __launch_bounds__(UM_THREADS, 1)
 umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
                    const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
   constexpr int NP = 16;
+  constexpr int UM_STAGES = UM_STAGES_GATEUP;
   extern __shared__ uint8_t smem_raw[];
-  using Smem = UmmaSmem<NP, 2>;
+  using Smem = UmmaSmem<NP, 2, UM_STAGES>;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, slot = blockIdx.y, tok = blockIdx.z;
@@ -553,7 +558,7 @@ static int launch_umma(const void* tmapA, const void* tmapA2, const void* tmapB,
   const CUtensorMap* mB = (const CUtensorMap*)tmapB;
 #define SFB_UM(NPV)                                                                                           \
   {                                                                                                           \
-    const size_t smem = sizeof(UmmaSmem<NPV, 1>) + 1024;                                                      \
+    const size_t smem = sizeof(UmmaSmem<NPV, 1, (NPV <= 32 ? UM_STAGES_DENSE : UM_STAGES_WIDE)>) + 1024;                                                      \
     static bool done = false;                                                                                 \
     if (!done) {                                                                                              \
       cudaFuncSetAttribute(umma_gemm_kernel<NPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
@@ -611,7 +616,7 @@ int sfb_umma_gate_up(const void* tmapA, const void* tmapA2, const void* tmapB, c
   a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a; a.a_fp4 = 1; a.ids = ids; a.wts = wts; a.top_k = top_k;
   a.slots = slots; a.inter = inter; a.d = d; a.act_q = (uint8_t*)act_q; a.act_s = (uint8_t*)act_s;
   a.act_sf = (uint8_t*)act_sf; a.limit = limit; a.status = (Status*)status;
-  const size_t smem = sizeof(UmmaSmem<16, 2>) + 1024;
+  const size_t smem = sizeof(UmmaSmem<16, 2, UM_STAGES_GATEUP>) + 1024;
   static bool done = false;
   if (!done) {
     cudaFuncSetAttribute(umma_gateup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

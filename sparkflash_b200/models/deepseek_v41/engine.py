@@ -122,13 +122,12 @@ class Engine:
         self.rope_variants = [(False, 1)] + [(True, r) for r in ratios]
         self.rope = e((R, len(self.rope_variants), cfg.rope_dim // 2, 2), f32)
         self.attn_out = e((R, self.hl * hd), bf)
-        self.attn_scratch = e((N.attn_scratch_floats(R, self.hl, hd, 16),), f32)
-        self.attn_tickets = e((R * ((self.hl + 7) // 8),), i32)
         self.oa = e((R, self.gl * cfg.o_lora_rank), bf)
         # sublayer outputs: one bf16 partial per rank, folded by the next seam
         self.y_attn = e((R, d), bf)
         self.y_ffn = e((R, d), bf)
-        self.dots = e((R, cfg.n_routed_experts), f32)
+        self.gate_ksplit = 8 if cfg.hidden_size >= 2048 else 1
+        self.dots = e((self.gate_ksplit, R, cfg.n_routed_experts), f32)
         self.ids, self.wts = e((R, cfg.top_k), i32), e((R, cfg.top_k), f32)
         self.act_q = e((R, cfg.top_k + 1, self.il), u8)
         self.act_s = e((R, cfg.top_k + 1, self.il // 32), u8)
@@ -280,8 +279,7 @@ class Engine:
         N.attn_rows(self.qfull, self.qfull.stride(0), invf, self.row_lane, self.row_pos, kv.win_q[l], kv.win_s[l],
                     kv.ckv_q[owner] if has_c else None, kv.ckv_s[owner] if has_c else None,
                     self.sel if has_c else None, self.sel_cnt if has_c else None, cfg.index_topk, L.sink,
-                    self.attn_out, n, self.hl, hd, rd, cfg.window, kv.ring, hd ** -0.5, self.attn_scratch,
-                    self.attn_tickets, N.attn_pick_splits(self.hl),
+                    self.attn_out, n, self.hl, hd, rd, cfg.window, kv.ring, hd ** -0.5,
                     out_q=self.tcb.ao_q if tc_wo_a else None, out_atom=self.tcb.ao_atom if tc_wo_a else None); self._k()
         ol, gin = cfg.o_lora_rank, cfg.group_in
         tc_wo_b = T is not None and T.wo_b is not None
@@ -307,8 +305,11 @@ class Engine:
     def _ffn(self, n: int, L: LayerW, l: int = 0):
         cfg = self.cfg
         d, E, k = cfg.hidden_size, cfg.n_routed_experts, cfg.top_k
-        N.gemv(N.WF_BF16, L.gate_w, None, 2 * d, E, d, n, xb=self.xn, out_f=self.dots); self._k()
-        N.router_topk(self.dots, L.gate_bias, L.gate_bias_vl, None, self.ids, self.wts, n, E, k, cfg.route_scale); self._k()
+        ks = self.gate_ksplit
+        N.gemv(N.WF_BF16, L.gate_w, None, 2 * d, E, d, n, xb=self.xn, out_f=self.dots, out_stride=E, ksplit=ks,
+               split_stride=self.dots.stride(0)); self._k()
+        N.router_topk(self.dots, L.gate_bias, L.gate_bias_vl, None, self.ids, self.wts, n, E, k, cfg.route_scale,
+                      nsplit=ks, split_stride=self.dots.stride(0)); self._k()
         T = self.tcl[l] if self.tcl is not None else None
         if T is not None and T.w13 is not None:
             tcb = self.tcb

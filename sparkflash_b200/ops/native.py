@@ -87,14 +87,14 @@ WF_FP8, WF_FP4, WF_BF16 = 0, 1, 2
 
 
 def gemv(wfmt, w, sf, row_bytes, N, K, n, *, groups=1, xq=None, xs=None, xb=None, xf=None, x_stride=None,
-         x_quant=False, out_b=None, out_f=None, out_stride=None):
+         x_quant=False, out_b=None, out_f=None, out_stride=None, ksplit=1, split_stride=0):
     if x_stride is None:
         x_stride = K * groups
     if out_stride is None:
         out_stride = N * groups
     code = lib().sfb_gemv(c_int(wfmt), _p(w), _p(sf), c_int64(row_bytes), c_int(N), c_int(K), c_int(groups),
                           c_int(n), _p(xq), _p(xs), _p(xb), _p(xf), c_int64(x_stride), c_int(1 if x_quant else 0),
-                          _p(out_b), _p(out_f), c_int64(out_stride), _stream())
+                          _p(out_b), _p(out_f), c_int64(out_stride), c_int(ksplit), c_int64(split_stride), _stream())
     _check(code, "gemv")
 
 
@@ -158,32 +158,20 @@ def select_topk(scores, row_pos, ratio, len_div, max_len, K, ids, count, n):
 
 # ---- attention ---------------------------------------------------------------------------------------------
 def attn_rows(q, q_stride, rope, row_lane, row_pos, win_q, win_s, ckv_q, ckv_s, sel, sel_count, K, sink,
-              out, n, heads, hd, rd, window, ring, scale, scratch, tickets, splits, out_q=None, out_atom=None):
+              out, n, heads, hd, rd, window, ring, scale, out_q=None, out_atom=None):
     code = lib().sfb_attn_rows(
         _p(q), c_int64(q_stride), _p(rope), c_int(rope.stride(0) // 2), _p(row_lane), _p(row_pos), _p(win_q), _p(win_s),
         c_int64(win_q.stride(0)), c_int64(win_s.stride(0)), _p(ckv_q), _p(ckv_s),
         c_int64(ckv_q.stride(0) if ckv_q is not None else 0), c_int64(ckv_s.stride(0) if ckv_s is not None else 0),
-        _p(sel), _p(sel_count), c_int(K), _p(sink), _p(out), _p(out_q), _p(out_atom), _p(scratch), _p(tickets), c_int(splits),
-        c_int(n), c_int(heads),
+        _p(sel), _p(sel_count), c_int(K), _p(sink), _p(out), _p(out_q), _p(out_atom), c_int(n), c_int(heads),
         c_int(hd), c_int(rd),
         c_int(window), c_int(ring), c_float(scale), _stream())
     _check(code, "attn_rows")
 
 
-def attn_scratch_floats(n, heads, hd, splits):
-    return int(lib().sfb_attn_scratch_floats(c_int(n), c_int(heads), c_int(hd), c_int(splits)))
-
-
-def attn_pick_splits(heads, target_blocks=148):
-    """Entry splits per (row, head group).  Depends on the head count only - never on the number of rows -
-    so that a row's partition and merge order (hence its bits) are the same in every batch."""
-    groups = (heads + 7) // 8
-    return max(1, min(16, -(-target_blocks // groups)))
-
-
 # ---- moe ---------------------------------------------------------------------------------------------------
-def router_topk(dots, bias, bias_vl, is_image, ids, wts, n, E, k, route_scale):
-    code = lib().sfb_router_topk(_p(dots), _p(bias), _p(bias_vl), _p(is_image), _p(ids), _p(wts), c_int(n),
+def router_topk(dots, bias, bias_vl, is_image, ids, wts, n, E, k, route_scale, nsplit=1, split_stride=0):
+    code = lib().sfb_router_topk(_p(dots), c_int(nsplit), c_int64(split_stride), _p(bias), _p(bias_vl), _p(is_image), _p(ids), _p(wts), c_int(n),
                                  c_int(E), c_int(k), c_float(route_scale), _stream())
     _check(code, "router_topk")
 

@@ -242,9 +242,7 @@ def test_attention_rows_matches_fp32_reference():
     N.rope_table([invf.to(dev)], [1], pos.to(dev), rope, n)
     N.attn_rows(q.to(dev), heads * hd, rope[:, 0], lane.to(dev), pos.to(dev), wq.to(dev), ws.to(dev),
                 C.pack_nibbles(cq).to(dev), cs.to(dev), sel.to(dev), cnt.to(dev), K, sink.to(dev), out, n, heads,
-                hd, rd, window, ring, hd ** -0.5,
-                torch.zeros(N.attn_scratch_floats(n, heads, hd, 5), device=dev),
-                torch.zeros(n, dtype=torch.int32, device=dev), 5)
+                hd, rd, window, ring, hd ** -0.5)
     torch.cuda.synchronize()
     wd = C.act_dequant_fp8(wq, ws)
     cd = C.kv_dequant_fp4(cq, cs)
