@@ -58,6 +58,8 @@ __global__ void __cluster_dims__(AT_SPLITS, 1, 1) __launch_bounds__(AT_THREADS) 
   float* kvs = smem + AT_HPB * HD;         // [SUB][HD]
   float* part = kvs + SUB * HD;            // [HPB][HD + 2]: acc | m | l
   const int sp = blockIdx.x, hg = blockIdx.y, row = blockIdx.z;
+  pdl_launch_dependents();
+  pdl_wait();
   const int pos = a.row_pos[row], L = a.row_lane[row];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = hg * AT_HPB + warp;
@@ -271,6 +273,7 @@ int sfb_attn_rows(const void* q, int64_t q_stride, const void* rope, int rope_st
              n, heads, rd, window, ring, scale};
   dim3 grid(AT_SPLITS, (heads + AT_HPB - 1) / AT_HPB, n);
   const size_t smem = sizeof(float) * (size_t)(AT_HPB * hd + AT_THREADS * 32 + AT_HPB * (hd + 2));
+  cudaError_t launch_rc = cudaSuccess;
 #define SFB_AT(HDV)                                                                                         \
   {                                                                                                         \
     static bool done = false;                                                                               \
@@ -278,12 +281,12 @@ int sfb_attn_rows(const void* q, int64_t q_stride, const void* rope, int rope_st
       cudaFuncSetAttribute(attn_rows_kernel<HDV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
       done = true;                                                                                          \
     }                                                                                                       \
-    attn_rows_kernel<HDV><<<grid, AT_THREADS, smem, stream>>>(a);                                           \
+    launch_rc = sfb_launch(attn_rows_kernel<HDV>, grid, dim3(AT_THREADS), smem, stream, a);                \
   }
   if (hd == 512) SFB_AT(512) else if (hd == 64) SFB_AT(64) else if (hd == 128) SFB_AT(128)
   else return (int)cudaErrorInvalidValue;
 #undef SFB_AT
-  return SFB_CHECK_LAUNCH();
+  return (int)launch_rc;
 }
 
 }  // extern "C"

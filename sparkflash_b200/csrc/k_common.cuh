@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include "codecs.h"
+#include "launch.cuh"
 
 #define SFB_CHECK_LAUNCH() (int)cudaGetLastError()
 

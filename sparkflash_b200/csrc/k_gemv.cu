@@ -117,6 +117,8 @@ __device__ __forceinline__ void load_x(const GemvArgs& a, int r0, int kcol0, flo
 template <int WF, int R>
 __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
   extern __shared__ float xs_sm[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int g = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int EPC = WF == 0 ? 16 : (WF == 1 ? 32 : 8);  // elements per 16-byte chunk
@@ -216,6 +218,7 @@ static int launch_gemv(const GemvArgs& a, cudaStream_t stream) {
   const int cap = (148 * 4 + a.groups - 1) / a.groups;  // a few resident blocks per SM; each loops over row tiles
   dim3 grid(tiles < cap ? tiles : cap, a.groups, a.ksplit);
   const size_t smem = (size_t)smem1 * R;
+  cudaError_t launch_rc = cudaSuccess;
 #define SFB_GV(RR)                                                                                   \
   {                                                                                                  \
     static bool attr_done = false;                                                                   \
@@ -223,11 +226,11 @@ static int launch_gemv(const GemvArgs& a, cudaStream_t stream) {
       cudaFuncSetAttribute(gemv_kernel<WF, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
       attr_done = true;                                                                              \
     }                                                                                                \
-    gemv_kernel<WF, RR><<<grid, GV_THREADS, smem, stream>>>(a);                                       \
+    launch_rc = sfb_launch(gemv_kernel<WF, RR>, grid, dim3(GV_THREADS), smem, stream, a);             \
   }
   if (R == 4) SFB_GV(4) else if (R == 2) SFB_GV(2) else SFB_GV(1)
 #undef SFB_GV
-  return SFB_CHECK_LAUNCH();
+  return (int)launch_rc;
 }
 
 }  // namespace sfb

@@ -43,6 +43,8 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
   const int row = blockIdx.x;
   const __nv_bfloat16* raw = a.raw + (size_t)row * (a.q + a.hd);
   float ss = 0.f, rs;
+  pdl_launch_dependents();
+  pdl_wait();
   if (blockIdx.y == 0) {
   // ---- q_norm + quant ----
   for (int i = threadIdx.x; i < a.q; i += 256) { float v = bf16_to_f(raw[i]); buf[i] = v; ss += v * v; }
@@ -240,8 +242,7 @@ int sfb_qkv_post(const void* raw, const float* q_norm_w, const float* kv_norm_w,
                 (uint8_t*)qr_q, (uint8_t*)qr_s, (uint8_t*)qr_atom, (__nv_bfloat16*)qr_b, (uint8_t*)win_q, (uint8_t*)win_s,
                 win_lane_stride_q, win_lane_stride_s, n, q, hd, rd, ring, eps};
   const size_t smem = sizeof(float) * (size_t)(q > hd ? q : hd);
-  qkv_post_kernel<<<dim3(n, 2), 256, smem, stream>>>(a);
-  return SFB_CHECK_LAUNCH();
+  return (int)sfb_launch(qkv_post_kernel, dim3(n, 2), dim3(256), smem, stream, a);
 }
 
 int sfb_compress_append(const float* raw, int64_t raw_stride, const float* norm_w, const void* wk,

@@ -50,6 +50,26 @@ __global__ void rope_table_kernel(RopeTableArgs a) {
   }
 }
 
+// L2 prefetch of a weight range: decode kernels are short and latency-bound, so the next kernel's weights are
+// pulled into L2 on a side stream while the current one runs (reference: kernels/prefetch_sm121.cuh:44,
+// opt_rows prefetch_l2:2508 - the same instruction, there issued under the all-reduce).
+__global__ void prefetch_l2_kernel(const uint8_t* p, size_t bytes) {
+  const size_t off = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2048;
+  if (off >= bytes) return;
+  size_t sz = bytes - off < 2048 ? bytes - off : 2048;
+  sz &= ~(size_t)15;
+  if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + off), "r"((uint32_t)sz) : "memory");
+}
+// the same for the experts a row selected: expert e occupies [base + e*stride, +bytes)
+__global__ void prefetch_experts_kernel(const uint8_t* base, size_t stride, size_t bytes, const int* ids, int k) {
+  const int e = ids[blockIdx.y];  // blockIdx.y indexes (row, slot) pairs: ids is [rows*k] flattened
+  const size_t off = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2048;
+  if (off >= bytes) return;
+  size_t sz = bytes - off < 2048 ? bytes - off : 2048;
+  sz &= ~(size_t)15;
+  if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + (size_t)e * stride + off), "r"((uint32_t)sz) : "memory");
+}
+
 __device__ __forceinline__ float gumbel(uint64_t base, int id) {
   const uint64_t h = splitmix64(base ^ ((uint64_t)id * 0x9E3779B97F4A7C15ull));
   const double u = ((double)(h >> 40) + 0.5) * (1.0 / 16777216.0);
@@ -190,6 +210,21 @@ int sfb_rope_table(const double* const* inv_freq, const int* ratio, int V, int h
   for (int v = 0; v < V; ++v) { a.inv_freq[v] = inv_freq[v]; a.ratio[v] = ratio[v] > 0 ? ratio[v] : 1; }
   a.V = V; a.half = half; a.row_pos = row_pos; a.out = (float2*)out;
   rope_table_kernel<<<n, 128, 0, stream>>>(a);
+  return SFB_CHECK_LAUNCH();
+}
+
+int sfb_prefetch_l2(const void* p, int64_t bytes, cudaStream_t stream) {
+  if (bytes <= 0) return 0;
+  const int64_t threads = (bytes + 2047) / 2048;
+  prefetch_l2_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, stream>>>((const uint8_t*)p, (size_t)bytes);
+  return SFB_CHECK_LAUNCH();
+}
+
+int sfb_prefetch_experts(const void* base, int64_t stride, int64_t bytes, const int* ids, int n_ids, cudaStream_t stream) {
+  if (bytes <= 0 || n_ids <= 0) return 0;
+  const int64_t threads = (bytes + 2047) / 2048;
+  prefetch_experts_kernel<<<dim3((unsigned)((threads + 127) / 128), n_ids), 128, 0, stream>>>(
+      (const uint8_t*)base, (size_t)stride, (size_t)bytes, ids, 0);
   return SFB_CHECK_LAUNCH();
 }
 

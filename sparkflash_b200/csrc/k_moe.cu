@@ -34,6 +34,8 @@ __global__ void __launch_bounds__(128) router_topk_kernel(RouterArgs a) {
   __shared__ int ri[4];
   __shared__ int pick[16];
   const int row = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const float* bias = (a.is_image && a.bias_vl && a.is_image[row]) ? a.bias_vl : a.bias;
   for (int e = threadIdx.x; e < a.E; e += 128) {
     float x = 0.f;
@@ -320,8 +322,7 @@ int sfb_router_topk(const float* dots, int nsplit, int64_t split_stride, const f
                     float* wts, int n, int E, int k, float route_scale, cudaStream_t stream) {
   if (k > 16) return (int)cudaErrorInvalidValue;
   RouterArgs a{dots, nsplit < 1 ? 1 : nsplit, split_stride, bias, bias_vl, (const uint8_t*)is_image, ids, wts, n, E, k, route_scale};
-  router_topk_kernel<<<n, 128, sizeof(float) * 2 * E, stream>>>(a);
-  return SFB_CHECK_LAUNCH();
+  return (int)sfb_launch(router_topk_kernel, dim3(n), dim3(128), sizeof(float) * 2 * E, stream, a);
 }
 
 int sfb_moe_gate_up(const void* xq, const void* xs, const int* ids, const float* wts, const void* w13,

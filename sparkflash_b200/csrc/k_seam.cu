@@ -67,6 +67,8 @@ __global__ void __cluster_dims__(FOLD_CLUSTER, 1, 1) __launch_bounds__(FOLD_THRE
   const int c_lo = rank * cpc;
   __shared__ float part_ss;
   __shared__ float sh[32];
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (a.has_post && a.flags[0] != nullptr) {
     if (threadIdx.x < a.W && !wait_flag_ge(a.flags[threadIdx.x], a.epoch, 2000000000ull))
@@ -296,8 +298,7 @@ int sfb_seam_fold(void* h, const void* const* y_ptrs, const void* const* flag_pt
   a.ysum = (__nv_bfloat16*)ysum; a.norm_w = norm_w; a.xn = (__nv_bfloat16*)xn; a.xq = (uint8_t*)xq;
   a.xs = (uint8_t*)xs; a.xs_atom = (uint8_t*)xs_atom; a.atom_mode = atom_mode; a.status = (Status*)status;
   a.n = n; a.hc = hc; a.d = d; a.norm_eps = norm_eps;
-  seam_fold_kernel<<<dim3(FOLD_CLUSTER, n), FOLD_THREADS, 0, stream>>>(a);
-  return SFB_CHECK_LAUNCH();
+  return (int)sfb_launch(seam_fold_kernel, dim3(FOLD_CLUSTER, n), dim3(FOLD_THREADS), 0, stream, a);
 }
 
 // Coefficient half: reads the folded residual, writes (pre, post, comb) for the next seam.

@@ -207,6 +207,24 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   using Smem = UmmaSmem<NP, 1, UM_STAGES>;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = NP + 16 <= 32 ? 32 : (NP + 16 <= 64 ? 64 : (NP + 16 <= 128 ? 128 : 256));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
+    mbar_init(&S.acc_full, 1);
+    S.fail = 0;
+    S.last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_wait();   // everything above is set-up; operands written by the previous kernel are read below
   UmmaWork w;
   if (a.mode == UM_DENSE) {
     const int tile = blockIdx.x, g = blockIdx.z;
@@ -241,24 +259,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     w.tile_id = tok * gridDim.x + tile; w.tiles_total = gridDim.x * gridDim.z;
     w.out_row0 = tok; w.n_valid = 1; w.col0 = tile * 128; w.col_limit = a.d;
   }
-  constexpr uint32_t TMEM_COLS = NP + 16 <= 32 ? 32 : (NP + 16 <= 64 ? 64 : (NP + 16 <= 128 ? 128 : 256));
   // bytes TMA reports per stage: packed FP4 counts 4 bits per element although it lands in 8-bit containers
   const uint32_t STAGE_TX = (w.a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 1024;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
-    mbar_init(&S.acc_full, 1);
-    S.fail = 0;
-    S.last_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    tmem_alloc(&S.tmem_base, TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
   const uint32_t tmem = S.tmem_base;
   const uint32_t t_acc = tmem;               // NP fp32 columns
   const uint32_t t_sfa = tmem + NP;          // 2 x 4 columns
@@ -402,6 +404,23 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   const int tile = blockIdx.x, slot = blockIdx.y, tok = blockIdx.z;
   const int il = a.inter;
   const int nks = (a.d + UM_BK - 1) / UM_BK;
+  constexpr uint32_t TMEM_COLS = 64;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
+    mbar_init(&S.acc_full, 1);
+    S.fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_wait();
   const CUtensorMap* ma;
   int a_fp4, row_g, row_u;
   const uint8_t *sf_g, *sf_u;
@@ -420,22 +439,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
     sf_u = a.sfa2 + ((size_t)(row_u >> 7) * a.katoms_a) * 512;
   }
   const uint8_t* sfb = a.sfb + (size_t)tok * a.katoms_b * 512;
-  constexpr uint32_t TMEM_COLS = 64;
   const uint32_t STAGE_TX = 2 * (a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 3 * 512;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
-    mbar_init(&S.acc_full, 1);
-    S.fail = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    tmem_alloc(&S.tmem_base, TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
   const uint32_t tmem = S.tmem_base;
   const uint32_t t_g = tmem, t_u = tmem + NP;
   const uint32_t t_sfg = tmem + 2 * NP, t_sfu = tmem + 2 * NP + 8, t_sfb = tmem + 2 * NP + 16;
@@ -556,6 +560,7 @@ static int launch_umma(const void* tmapA, const void* tmapA2, const void* tmapB,
   const CUtensorMap* mA = (const CUtensorMap*)tmapA;
   const CUtensorMap* mA2 = (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA);
   const CUtensorMap* mB = (const CUtensorMap*)tmapB;
+  cudaError_t launch_rc = cudaSuccess;
 #define SFB_UM(NPV)                                                                                           \
   {                                                                                                           \
     const size_t smem = sizeof(UmmaSmem<NPV, 1, (NPV <= 32 ? UM_STAGES_DENSE : UM_STAGES_WIDE)>) + 1024;                                                      \
@@ -564,12 +569,12 @@ static int launch_umma(const void* tmapA, const void* tmapA2, const void* tmapB,
       cudaFuncSetAttribute(umma_gemm_kernel<NPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
       done = true;                                                                                            \
     }                                                                                                         \
-    umma_gemm_kernel<NPV><<<grid, UM_THREADS, smem, stream>>>(*mA, *mA2, *mB, a);                             \
+    launch_rc = sfb_launch(umma_gemm_kernel<NPV>, grid, dim3(UM_THREADS), smem, stream, *mA, *mA2, *mB, a);   \
   }
   if (NP == 16) SFB_UM(16) else if (NP == 32) SFB_UM(32) else if (NP == 64) SFB_UM(64) else if (NP == 128) SFB_UM(128)
   else return (int)cudaErrorInvalidValue;
 #undef SFB_UM
-  return SFB_CHECK_LAUNCH();
+  return (int)launch_rc;
 }
 
 // Dense / grouped block-scaled GEMM. NP = token columns (16/32/64/128) >= n (>= 2*pair when pair > 0).
@@ -624,8 +629,8 @@ int sfb_umma_gate_up(const void* tmapA, const void* tmapA2, const void* tmapB, c
   }
   const CUtensorMap* mA = (const CUtensorMap*)tmapA;
   const CUtensorMap* mA2 = (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA);
-  umma_gateup_kernel<<<dim3(inter / 128, slots, n_tok), UM_THREADS, smem, stream>>>(*mA, *mA2, *(const CUtensorMap*)tmapB, a);
-  return SFB_CHECK_LAUNCH();
+  return (int)sfb_launch(umma_gateup_kernel, dim3(inter / 128, slots, n_tok), dim3(UM_THREADS), smem, stream, *mA, *mA2,
+                         *(const CUtensorMap*)tmapB, a);
 }
 
 // MoE down + combine: out[tok, :] = sum over slots of W2_slot . act[tok, slot, :] (fp32 partial per slot, added in

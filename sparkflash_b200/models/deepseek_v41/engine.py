@@ -97,6 +97,9 @@ class Engine:
         self.partials = e((R, self.nblk, 1 + self.mix), f32)
         self._side_stream = torch.cuda.Stream(device=dev)
         self._coef_event = None
+        self._pf_stream = torch.cuda.Stream(device=dev)
+        self._pf_event = None
+        self.prefetch = False  # pull the next kernels' weights into L2 on a side stream (decode steps only)
         self.seam_tickets = e((R,), i32)
         cs = N.coef_stride(hc)
         self.coef = [e((R, cs), f32), e((R, cs), f32)]
@@ -220,6 +223,31 @@ class Engine:
                          status=self.status, NP=NP)
         self._k()
 
+    def _prefetch(self, n: int, tensors=(), experts=None):
+        """Issue L2 prefetches on the prefetch stream, ordered after everything already queued on the main stream.
+        ``experts`` = (per-expert weight tensor, number of (row, slot) ids to read from self.ids)."""
+        if not self.prefetch or n > 4:
+            return
+        main = torch.cuda.current_stream()
+        ev = torch.cuda.Event()
+        ev.record(main)
+        pf = self._pf_stream
+        pf.wait_event(ev)
+        with torch.cuda.stream(pf):
+            for t in tensors:
+                if t is not None:
+                    N.prefetch_l2(t)
+            if experts is not None:
+                N.prefetch_experts(experts[0], self.ids, experts[1])
+            done = torch.cuda.Event()
+            done.record(pf)
+        self._pf_event = done
+
+    def _join_prefetch(self):
+        if self._pf_event is not None:
+            torch.cuda.current_stream().wait_event(self._pf_event)
+            self._pf_event = None
+
     def _rope_view(self, compressed: bool, ratio: int) -> torch.Tensor:
         """[R, stride] view of the step's rotary table for one variant (row stride = all variants)."""
         v = self.rope_variants.index((compressed, ratio))
@@ -253,6 +281,7 @@ class Engine:
         else:
             N.gemv(N.WF_FP8, L.wq_b, L.wq_b_sf, q, L.wq_b_rows, q, n, xq=self.qr_q, xs=self.qr_s, out_b=self.qfull,
                    out_stride=self.qfull.stride(0)); self._k()
+        self._prefetch(n, (L.wo_a, L.wo_b))
         owner = cfg.kv_owner(l)
         if ratio > 0 and cfg.is_index_source(l):
             inh, idh = cfg.index_n_heads, cfg.index_head_dim
@@ -310,6 +339,7 @@ class Engine:
                split_stride=self.dots.stride(0)); self._k()
         N.router_topk(self.dots, L.gate_bias, L.gate_bias_vl, None, self.ids, self.wts, n, E, k, cfg.route_scale,
                       nsplit=ks, split_stride=self.dots.stride(0)); self._k()
+        self._prefetch(n, (), experts=(L.w2, n * k))
         T = self.tcl[l] if self.tcl is not None else None
         if T is not None and T.w13 is not None:
             tcb = self.tcb
@@ -317,6 +347,7 @@ class Engine:
             N.umma_gate_up(T.w13.tmap, T.s13.tmap, tbx, T.w13.atoms, T.s13.atoms, tcb.xs_atom_tok, self.ids, self.wts,
                            self.act_q, self.act_s, tcb.act_sf, n, k, k + 1, d, self.il, cfg.swiglu_limit,
                            status=self.status); self._k()
+            self._prefetch(n, (self._next_wqkv,) if self._next_wqkv is not self.w.head else ())
             tba = tcb.bmap(self.act_q, self.max_rows * (k + 1), self.il, 16)
             N.umma_down(T.w2.tmap, T.s2.tmap, tba, T.w2.atoms, T.s2.atoms, tcb.act_sf, self.ids, self.y_ffn, None, d,
                         tcb.scratch, tcb.tickets, n, k, k + 1, d, self.il, status=self.status); self._k()
@@ -351,6 +382,7 @@ class Engine:
                            cfg.hidden_size); self._k()
                 tap_i += 1
             self._dbg(f"L{l}.attn_in", self.xn, n)
+            self._prefetch(n, (L.wq_b,))
             self._attention(n, l, L, len_bucket)
             self._dbg(f"L{l}.q", self.qfull, n); self._dbg(f"L{l}.o", self.attn_out, n)
             self._dbg(f"L{l}.oa", self.oa, n); self._dbg(f"L{l}.attn_out", self.y_attn, n)
@@ -358,6 +390,8 @@ class Engine:
             self._seam(n, k, self._reduce_parts(self.y_attn, n), L.hc_ffn_fn, L.hc_ffn_base, L.hc_ffn_scale,
                        L.ffn_norm, atoms=1); k += 1
             self._dbg(f"L{l}.ffn_in", self.xn, n)
+            self._prefetch(n, (L.s13, L.s2))
+            self._next_wqkv = w.layers[l + 1].wqkv_a if l + 1 < len(w.layers) else w.head
             self._ffn(n, L, l)
             self._dbg(f"L{l}.ffn_out", self.y_ffn, n)
             self._dbg(f"L{l}.route_ids", self.ids, n); self._dbg(f"L{l}.route_w", self.wts, n)
@@ -371,6 +405,7 @@ class Engine:
         if self.world > 1 and self.comm is not None:
             self.comm.gather_best(self.best_val, self.best_id, n)
         N.sample_fold(self.best_val, self.best_id, self.world if self.comm is not None else 1, n, self.tokens_out); self._k()
+        self._join_prefetch()
 
     # ---- public step -------------------------------------------------------------------------------------
     def _bucket(self, max_pos: int) -> int:

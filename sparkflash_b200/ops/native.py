@@ -204,6 +204,17 @@ def rope_table(inv_freqs, ratios, row_pos, out, n):
            "rope_table")
 
 
+def prefetch_l2(t: torch.Tensor):
+    _check(lib().sfb_prefetch_l2(_p(t), c_int64(t.numel() * t.element_size()), _stream()), "prefetch_l2")
+
+
+def prefetch_experts(t: torch.Tensor, ids: torch.Tensor, n_ids: int):
+    """t: [E, ...] per-expert weights; ids: int32 expert ids (first n_ids entries are read on the device)."""
+    per = t[0].numel() * t.element_size()
+    _check(lib().sfb_prefetch_experts(_p(t), c_int64(per), c_int64(per), _p(ids), c_int(n_ids), _stream()),
+           "prefetch_experts")
+
+
 def tap_mean(h, tap, tap_stride, n, hc, d):
     _check(lib().sfb_tap_mean(_p(h), _p(tap), c_int64(tap_stride), c_int(n), c_int(hc), c_int(d), _stream()),
            "tap_mean")
