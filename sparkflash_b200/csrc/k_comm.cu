@@ -1,0 +1,107 @@
+// Symmetric memory and the push half of the fused collectives.
+//
+// Every rank owns one symmetric allocation; all ranks map all allocations (CUDA IPC inside one box, the
+// traffic goes over NVLink through NVSwitch).  A producer stores its partial result into "its" slot of
+// every rank's buffer with plain peer stores and then raises an arrival flag on every rank; a consumer
+// only ever reads its own memory and waits - with a time limit - on its own flags.  The reduction itself
+// (rank-order fold in fp32) lives in the consumer, csrc/k_seam.cu.  No TMA, no multicast loads.
+//
+// Reference behaviour replaced: crates/sparkflash-comm/src/rdma/write_exchange.rs (one write per peer +
+// arrival flag, doorbell deadline, abort word), kernels/opt_exchange_sm121.cuh (opt_exchange_stage_bf16:68),
+// kernels/opt_misc_sm121.cu:399 (opt_sum_ranks_bf16, the canonical rank-order fold).
+#include "k_common.cuh"
+
+namespace sfb {
+
+struct PushArgs {
+  const uint4* src;        // n16 x 16 bytes
+  uint4* dst[8];           // the same slot on every rank (including this one)
+  uint32_t* flag[8];       // this rank's flag word on every rank
+  int W;
+  int64_t n16;
+  const uint32_t* epoch_ptr;
+  uint32_t epoch_add;
+  unsigned int* done;      // zero between launches
+};
+
+__global__ void __launch_bounds__(256) push_rows_kernel(PushArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int is_last;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n16; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 v = a.src[i];
+    for (int r = 0; r < a.W; ++r) a.dst[r][i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(a.done, 1u);
+    is_last = prev == gridDim.x - 1;
+    if (is_last) *a.done = 0;
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x < a.W) {
+    __threadfence_system();
+    st_release_sys(a.flag[threadIdx.x], *a.epoch_ptr + a.epoch_add);
+  }
+}
+
+__global__ void epoch_bump_kernel(uint32_t* epoch, uint32_t add) { *epoch += add; }
+
+// Test / emulation helper: wait (bounded) until every flag reaches the epoch; records a timeout in status.
+__global__ void wait_flags_kernel(const uint32_t* const* flags, int W, const uint32_t* epoch_ptr, uint32_t epoch_add,
+                                  uint64_t budget_ns, Status* st) {
+  if (threadIdx.x < W && !wait_flag_ge(flags[threadIdx.x], *epoch_ptr + epoch_add, budget_ns))
+    status_set(st, ST_TIMEOUT, 30, threadIdx.x, (int)(*epoch_ptr + epoch_add));
+}
+
+}  // namespace sfb
+
+using namespace sfb;
+
+extern "C" {
+
+int sfb_symm_alloc(void** out, int64_t bytes) {
+  cudaError_t e = cudaMalloc(out, (size_t)bytes);
+  if (e == cudaSuccess) e = cudaMemset(*out, 0, (size_t)bytes);
+  return (int)e;
+}
+int sfb_symm_free(void* p) { return (int)cudaFree(p); }
+int sfb_ipc_get_handle(void* p, void* handle64) { return (int)cudaIpcGetMemHandle((cudaIpcMemHandle_t*)handle64, p); }
+int sfb_ipc_open_handle(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof h);
+  return (int)cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+}
+int sfb_ipc_close_handle(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+int sfb_memcpy_d2h(void* dst, const void* src, int64_t bytes) { return (int)cudaMemcpy(dst, src, (size_t)bytes, cudaMemcpyDeviceToHost); }
+int sfb_memset_async(void* p, int v, int64_t bytes, cudaStream_t s) { return (int)cudaMemsetAsync(p, v, (size_t)bytes, s); }
+
+// dst_ptrs / flag_ptrs: host arrays of W device addresses
+int sfb_push_rows(const void* src, const void* const* dst_ptrs, const void* const* flag_ptrs, int W, int64_t bytes,
+                  const void* epoch_ptr, uint32_t epoch_add, void* done, cudaStream_t stream) {
+  if (bytes % 16 || W < 1 || W > 8) return (int)cudaErrorInvalidValue;
+  PushArgs a{};
+  a.src = (const uint4*)src;
+  for (int r = 0; r < W; ++r) { a.dst[r] = (uint4*)dst_ptrs[r]; a.flag[r] = (uint32_t*)flag_ptrs[r]; }
+  a.W = W; a.n16 = bytes / 16; a.epoch_ptr = (const uint32_t*)epoch_ptr; a.epoch_add = epoch_add;
+  a.done = (unsigned int*)done;
+  int64_t blocks = (a.n16 + 255) / 256;
+  if (blocks > 64) blocks = 64;
+  if (blocks < 1) blocks = 1;
+  return (int)sfb_launch(push_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, a);
+}
+
+int sfb_epoch_bump(void* epoch, uint32_t add, cudaStream_t stream) {
+  epoch_bump_kernel<<<1, 1, 0, stream>>>((uint32_t*)epoch, add);
+  return SFB_CHECK_LAUNCH();
+}
+
+int sfb_wait_flags(const void* const* flags_dev_array, int W, const void* epoch_ptr, uint32_t epoch_add,
+                   uint64_t budget_ns, void* status, cudaStream_t stream) {
+  wait_flags_kernel<<<1, 32, 0, stream>>>((const uint32_t* const*)flags_dev_array, W, (const uint32_t*)epoch_ptr,
+                                          epoch_add, budget_ns, (Status*)status);
+  return SFB_CHECK_LAUNCH();
+}
+
+}  // extern "C"

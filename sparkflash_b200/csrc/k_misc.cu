@@ -121,18 +121,38 @@ __global__ void __launch_bounds__(1024) sample_kernel(SampleArgs a) {
   }
 }
 
-// Fold W ranks' (value, id) winners: larger value wins, ties to the lower id.
-__global__ void sample_fold_kernel(const float* vals, const int* ids, int W, int n, int* out_tokens) {
-  const int row = blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= n) return;
-  float bv = vals[row];
-  int bi = ids[row];
-  for (int r = 1; r < W; ++r) {
-    float v = vals[(size_t)r * n + row];
-    int id = ids[(size_t)r * n + row];
-    if (v > bv || (v == bv && id < bi)) { bv = v; bi = id; }
+// Fold W ranks' (value, id) winners: larger value wins, ties to the lower id.  vals / ids are [W, stride].
+// With flags the kernel first waits (bounded) until every rank's winners have arrived.
+struct FoldBestArgs {
+  const float* vals;
+  const int* ids;
+  int W, n, stride;
+  int* out_tokens;
+  const uint32_t* flags[8];
+  const uint32_t* epoch_ptr;
+  uint32_t epoch_add;
+  uint64_t wait_ns;
+  Status* status;
+};
+__global__ void sample_fold_kernel(FoldBestArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (a.flags[0] != nullptr) {
+    const uint32_t want = *a.epoch_ptr + a.epoch_add;
+    if (threadIdx.x < a.W && !wait_flag_ge(a.flags[threadIdx.x], want, a.wait_ns))
+      status_set(a.status, ST_TIMEOUT, 4, threadIdx.x, (int)want);
+    __syncthreads();
   }
-  out_tokens[row] = bi;
+  for (int row = threadIdx.x; row < a.n; row += blockDim.x) {
+    float bv = a.vals[row];
+    int bi = a.ids[row];
+    for (int r = 1; r < a.W; ++r) {
+      const float v = a.vals[(size_t)r * a.stride + row];
+      const int id = a.ids[(size_t)r * a.stride + row];
+      if (v > bv || (v == bv && id < bi)) { bv = v; bi = id; }
+    }
+    a.out_tokens[row] = bi;
+  }
 }
 
 // ---- synthetic weights: bytes from a hash of (tensor seed, element index) ----------------------------------
@@ -243,9 +263,16 @@ int sfb_sample(const float* logits, int64_t stride, const int* row_pos, const fl
   return SFB_CHECK_LAUNCH();
 }
 
-int sfb_sample_fold(const float* vals, const int* ids, int W, int n, int* out_tokens, cudaStream_t stream) {
-  sample_fold_kernel<<<(n + 63) / 64, 64, 0, stream>>>(vals, ids, W, n, out_tokens);
-  return SFB_CHECK_LAUNCH();
+int sfb_sample_fold(const void* vals, const void* ids, int W, int n, int stride, int* out_tokens,
+                    const void* const* flag_ptrs, const void* epoch_ptr, uint32_t epoch_add, uint64_t wait_ns,
+                    void* status, cudaStream_t stream) {
+  if (W < 1 || W > 8) return (int)cudaErrorInvalidValue;
+  FoldBestArgs a{};
+  a.vals = (const float*)vals; a.ids = (const int*)ids; a.W = W; a.n = n; a.stride = stride; a.out_tokens = out_tokens;
+  for (int r = 0; r < 8; ++r) a.flags[r] = (flag_ptrs && r < W) ? (const uint32_t*)flag_ptrs[r] : nullptr;
+  a.epoch_ptr = (const uint32_t*)epoch_ptr; a.epoch_add = epoch_add; a.wait_ns = wait_ns ? wait_ns : 2000000000ull;
+  a.status = (Status*)status;
+  return (int)sfb_launch(sample_fold_kernel, dim3(1), dim3(64), 0, stream, a);
 }
 
 // kind: 0 fp8 bytes, 1 fp4 bytes (count = bytes), 2 bf16 elements, 3 f32 elements

@@ -40,7 +40,8 @@ struct FoldArgs {
   __nv_bfloat16* h;              // [n, hc, d] residual copies, updated in place
   const __nv_bfloat16* y[8];     // W partial sublayer outputs [n, d] (unused when !has_post)
   const uint32_t* flags[8];      // optional arrival flags (one per producer rank), may be null
-  uint32_t epoch;                // value the flags must reach
+  const uint32_t* epoch_ptr;     // device step counter (may be null: epoch_add alone)
+  uint32_t epoch_add;            // flags must reach *epoch_ptr + epoch_add
   int W;
   int has_post;
   const float* coef_prev;        // [n, COEF] coefficients of the finished sublayer (post, comb)
@@ -54,6 +55,7 @@ struct FoldArgs {
   uint8_t* xs_atom;              // optional scale atoms for the tensor-core arm (see atom_mode)
   int atom_mode;                 // 0: rows of one atom set = tokens; 1: one atom set per token, token at row 0
   Status* status;
+  uint64_t wait_ns;              // time limit of the flag wait
   int n, hc, d;
   float norm_eps;
 };
@@ -71,8 +73,9 @@ __global__ void __cluster_dims__(FOLD_CLUSTER, 1, 1) __launch_bounds__(FOLD_THRE
   pdl_wait();
 
   if (a.has_post && a.flags[0] != nullptr) {
-    if (threadIdx.x < a.W && !wait_flag_ge(a.flags[threadIdx.x], a.epoch, 2000000000ull))
-      status_set(a.status, ST_TIMEOUT, 1, threadIdx.x, (int)a.epoch);
+    const uint32_t want = (a.epoch_ptr ? *a.epoch_ptr : 0u) + a.epoch_add;
+    if (threadIdx.x < a.W && !wait_flag_ge(a.flags[threadIdx.x], want, a.wait_ns))
+      status_set(a.status, ST_TIMEOUT, 1, threadIdx.x, (int)want);
     __syncthreads();
   }
   float post[MAX_HC], comb[MAX_HC * MAX_HC], ap[MAX_HC];
@@ -282,7 +285,8 @@ int sfb_seam_nblk(int d) { return (d + COEF_COLS - 1) / COEF_COLS; }
 int sfb_coef_stride(int hc) { return coef_stride(hc); }
 
 // Critical-path half of a seam. y_ptrs / flag_ptrs: host arrays of W device pointers (flag_ptrs may be null).
-int sfb_seam_fold(void* h, const void* const* y_ptrs, const void* const* flag_ptrs, uint32_t epoch, int W,
+int sfb_seam_fold(void* h, const void* const* y_ptrs, const void* const* flag_ptrs, const void* epoch_ptr,
+                  uint32_t epoch_add, uint64_t wait_ns, int W,
                   int has_post, const float* coef_prev, const float* a_pre, int a_stride, void* ysum,
                   const float* norm_w, void* xn, void* xq, void* xs, void* xs_atom, int atom_mode, void* status,
                   int n, int hc, int d, float norm_eps, cudaStream_t stream) {
@@ -294,7 +298,7 @@ int sfb_seam_fold(void* h, const void* const* y_ptrs, const void* const* flag_pt
     a.y[r] = (has_post && r < W) ? (const __nv_bfloat16*)y_ptrs[r] : nullptr;
     a.flags[r] = (has_post && flag_ptrs && r < W) ? (const uint32_t*)flag_ptrs[r] : nullptr;
   }
-  a.epoch = epoch; a.W = W; a.has_post = has_post; a.coef_prev = coef_prev; a.a_pre = a_pre; a.a_stride = a_stride;
+  a.epoch_ptr = (const uint32_t*)epoch_ptr; a.epoch_add = epoch_add; a.wait_ns = wait_ns ? wait_ns : 2000000000ull; a.W = W; a.has_post = has_post; a.coef_prev = coef_prev; a.a_pre = a_pre; a.a_stride = a_stride;
   a.ysum = (__nv_bfloat16*)ysum; a.norm_w = norm_w; a.xn = (__nv_bfloat16*)xn; a.xq = (uint8_t*)xq;
   a.xs = (uint8_t*)xs; a.xs_atom = (uint8_t*)xs_atom; a.atom_mode = atom_mode; a.status = (Status*)status;
   a.n = n; a.hc = hc; a.d = d; a.norm_eps = norm_eps;

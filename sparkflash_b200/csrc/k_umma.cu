@@ -156,6 +156,14 @@ struct UmmaArgs {
   __nv_bfloat16* out_b;
   float* out_f;
   int64_t out_stride;
+  // fused collective (producer half): the bf16 output also goes to the same offset of every rank's slot buffer
+  // with plain peer stores, and when the last tile of the kernel is done an arrival flag is raised on every rank
+  __nv_bfloat16* peer_out[8];
+  uint32_t* peer_flag[8];
+  int n_peers;                // 0 = off
+  const uint32_t* epoch_ptr;  // flag value = *epoch_ptr + epoch_add
+  uint32_t epoch_add;
+  unsigned int* done_counter; // zero between launches
   uint8_t* out_q;             // optional: the bf16-rounded output re-quantised per 32 columns (E4M3)
   uint8_t* out_q_atom;        //           and its scale atoms (rows = tokens, kb = out_stride/32)
   // MoE
@@ -326,8 +334,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             const float f = col_ok ? __uint_as_float(v[j]) : 0.f;
             const int64_t o = (int64_t)(w.out_row0 + tok) * a.out_stride + col;
             if (col_ok) {
-              if (a.out_b) a.out_b[o] = __float2bfloat16_rn(f);
+              const __nv_bfloat16 fb = __float2bfloat16_rn(f);
+              if (a.out_b) a.out_b[o] = fb;
               if (a.out_f) a.out_f[o] = f;
+              for (int pr = 0; pr < a.n_peers; ++pr) a.peer_out[pr][o] = fb;
             }
             if (a.out_q) {
               uint8_t sc;
@@ -369,8 +379,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           if (!col_ok) s = 0.f;
           const int64_t o = (int64_t)(w.out_row0 + tok) * a.out_stride + col;
           if (col_ok) {
-            if (a.out_b) a.out_b[o] = __float2bfloat16_rn(s);
+            const __nv_bfloat16 sb = __float2bfloat16_rn(s);
+            if (a.out_b) a.out_b[o] = sb;
             if (a.out_f) a.out_f[o] = s;
+            for (int pr = 0; pr < a.n_peers; ++pr) a.peer_out[pr][o] = sb;
           }
           if (a.out_q) {
             uint8_t sc;
@@ -379,6 +391,24 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
               a.out_q[o] = code;
               if (lane == 0) a.out_q_atom[sf_offset(w.out_row0 + tok, col >> 5, (int)(a.out_stride >> 5))] = sc;
             }
+          }
+        }
+      }
+    }
+    if (a.n_peers > 0) {
+      // this CTA finalised its tile (directly, or as the last split): count it; the CTA that completes the
+      // kernel's last tile raises this rank's arrival flag on every rank
+      const bool finalised = (single && a.pair == 0) || S.last_flag;
+      if (finalised) {
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const unsigned int prev = atomicAdd(a.done_counter, 1u);
+          if (prev == (unsigned int)w.tiles_total - 1) {
+            *a.done_counter = 0;
+            __threadfence_system();
+            const uint32_t ep = *a.epoch_ptr + a.epoch_add;
+            for (int pr = 0; pr < a.n_peers; ++pr) st_release_sys(a.peer_flag[pr], ep);
           }
         }
       }
@@ -555,12 +585,32 @@ int sfb_tmap_encode(void* out_map /*128 bytes, 64-aligned*/, const void* base, i
 
 int sfb_umma_scratch_floats(int tiles_total, int splits, int NP) { return tiles_total * splits * 128 * NP; }
 
-static int launch_umma(const void* tmapA, const void* tmapA2, const void* tmapB, const UmmaArgs& a, dim3 grid, int NP,
+// Peer table of the next launch (set by sfb_umma_set_push, consumed and cleared by the launch).
+struct PushSpec {
+  void* out[8];
+  void* flag[8];
+  int n = 0;
+  const void* epoch_ptr = nullptr;
+  uint32_t epoch_add = 0;
+  void* done = nullptr;
+};
+static thread_local PushSpec g_push;
+
+static void apply_push(UmmaArgs& a) {
+  a.n_peers = g_push.n;
+  for (int i = 0; i < g_push.n; ++i) { a.peer_out[i] = (__nv_bfloat16*)g_push.out[i]; a.peer_flag[i] = (uint32_t*)g_push.flag[i]; }
+  a.epoch_ptr = (const uint32_t*)g_push.epoch_ptr; a.epoch_add = g_push.epoch_add; a.done_counter = (unsigned int*)g_push.done;
+  g_push.n = 0;
+}
+
+static int launch_umma(const void* tmapA, const void* tmapA2, const void* tmapB, const UmmaArgs& a_in, dim3 grid, int NP,
                        cudaStream_t stream) {
   const CUtensorMap* mA = (const CUtensorMap*)tmapA;
   const CUtensorMap* mA2 = (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA);
   const CUtensorMap* mB = (const CUtensorMap*)tmapB;
   cudaError_t launch_rc = cudaSuccess;
+  UmmaArgs a = a_in;
+  apply_push(a);
 #define SFB_UM(NPV)                                                                                           \
   {                                                                                                           \
     const size_t smem = sizeof(UmmaSmem<NPV, 1, (NPV <= 32 ? UM_STAGES_DENSE : UM_STAGES_WIDE)>) + 1024;                                                      \
@@ -575,6 +625,16 @@ static int launch_umma(const void* tmapA, const void* tmapA2, const void* tmapB,
   else return (int)cudaErrorInvalidValue;
 #undef SFB_UM
   return (int)launch_rc;
+}
+
+// Arm the fused-collective epilogue for the next sfb_umma_dense / sfb_umma_down call of this thread: the bf16 output
+// is also stored to out_ptrs[0..W) (this rank's slot on every rank) and flag_ptrs[0..W) are raised at the end.
+int sfb_umma_set_push(const void* const* out_ptrs, const void* const* flag_ptrs, int W, const void* epoch_ptr,
+                      uint32_t epoch_add, void* done_counter) {
+  if (W < 0 || W > 8) return (int)cudaErrorInvalidValue;
+  for (int i = 0; i < W; ++i) { g_push.out[i] = (void*)out_ptrs[i]; g_push.flag[i] = (void*)flag_ptrs[i]; }
+  g_push.n = W; g_push.epoch_ptr = epoch_ptr; g_push.epoch_add = epoch_add; g_push.done = done_counter;
+  return 0;
 }
 
 // Dense / grouped block-scaled GEMM. NP = token columns (16/32/64/128) >= n (>= 2*pair when pair > 0).

@@ -85,7 +85,8 @@ class Engine:
         self.kv = KVCache(cfg, max_lanes, max_context, max_rows, self.dev)
         R, d, hc, hd, q = max_rows, cfg.hidden_size, cfg.hc_mult, cfg.head_dim, cfg.q_lora_rank
         W = self.world
-        self.hl, self.gl, self.il, self.vl = cfg.n_heads // W, cfg.o_groups // W, cfg.moe_inter // W, cfg.vocab_size // W
+        self.hl, self.gl, self.vl = cfg.n_heads // W, cfg.o_groups // W, cfg.vocab_size // W
+        self.il = weights.il or cfg.moe_inter // W
         dev = self.dev
         e = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
         bf, f32, u8, i32 = torch.bfloat16, torch.float32, torch.uint8, torch.int32
@@ -186,9 +187,15 @@ class Engine:
         if self._coef_event is not None:
             main.wait_event(self._coef_event)   # coefficients of seam k-1 are ready
             self._coef_event = None
+        flags, epoch_ptr, epoch_add = None, None, 0
+        if isinstance(y_parts, tuple):      # fused collective: (slots, flags, epoch_add)
+            y_parts, flags, epoch_add = y_parts
+            epoch_ptr = self.comm.epoch_ptr
         N.seam_fold(self.h, y_parts, None if first else prev, self.w.onehot if first else prev,
                     0 if first else prev.stride(0), norm_w, self.xn, self.xq if quant else None,
                     self.xs if quant else None, n, cfg.hc_mult, cfg.hidden_size, cfg.norm_eps, status=self.status,
+                    flags=flags, epoch_ptr=epoch_ptr, epoch_add=epoch_add,
+                    wait_ns=self.comm.wait_ns if flags is not None else 0,
                     xs_atom=None if (self.tcl is None or not quant) else (self.tcb.xs_atom if atoms == 0 else self.tcb.xs_atom_tok),
                     atom_mode=atoms)
         self._k()
@@ -322,10 +329,12 @@ class Engine:
                            out_q=tcb.oa_q if fused_oa_q else None, out_q_atom=tcb.oa_atom if fused_oa_q else None)
         else:
             N.gemv(N.WF_FP8, L.wo_a, L.wo_a_sf, gin, ol, gin, n, groups=self.gl, xb=self.attn_out, out_b=self.oa); self._k()
+        self._pushed = False
         if tc_wo_b:
             tcb = self.tcb
             if not fused_oa_q:
                 N.quant_rows(self.oa, tcb.oa_q, None, tcb.oa_atom, n, self.gl * ol); self._k()
+            self._pushed = self._arm_push(0, 2 * l)
             self._tc_dense(T.wo_b, tcb.oa_q, self.max_rows, tcb.oa_atom, n, d, self.gl * ol, self.y_attn)
         else:
             N.gemv(N.WF_FP8, L.wo_b, L.wo_b_sf, self.gl * ol, d, self.gl * ol, n, xb=self.oa, x_quant=True,
@@ -333,6 +342,7 @@ class Engine:
 
     def _ffn(self, n: int, L: LayerW, l: int = 0):
         cfg = self.cfg
+        self._pushed = False
         d, E, k = cfg.hidden_size, cfg.n_routed_experts, cfg.top_k
         ks = self.gate_ksplit
         N.gemv(N.WF_BF16, L.gate_w, None, 2 * d, E, d, n, xb=self.xn, out_f=self.dots, out_stride=E, ksplit=ks,
@@ -349,6 +359,7 @@ class Engine:
                            status=self.status); self._k()
             self._prefetch(n, (self._next_wqkv,) if self._next_wqkv is not self.w.head else ())
             tba = tcb.bmap(self.act_q, self.max_rows * (k + 1), self.il, 16)
+            self._pushed = self._arm_push(1, 2 * l + 1)
             N.umma_down(T.w2.tmap, T.s2.tmap, tba, T.w2.atoms, T.s2.atoms, tcb.act_sf, self.ids, self.y_ffn, None, d,
                         tcb.scratch, tcb.tickets, n, k, k + 1, d, self.il, status=self.status); self._k()
             return
@@ -356,15 +367,40 @@ class Engine:
                       n, k, d, self.il, cfg.swiglu_limit); self._k()
         N.moe_down(self.act_q, self.act_s, self.ids, L.w2, L.w2_sf, L.s2, L.s2_sf, self.y_ffn, n, k, d, self.il); self._k()
 
-    def _reduce_parts(self, y: torch.Tensor, n: int):
-        """Partials every rank's next seam will fold.  One rank: the local buffer.  NCCL arm: an
-        all-reduce in place (then a single part)."""
+    def _fused(self) -> bool:
+        return self.world > 1 and self.comm is not None and getattr(self.comm, "name", "") == "fused"
+
+    def _arm_push(self, kind: int, sub: int) -> bool:
+        """Fused arm: make the next tcgen05 GEMM launch push its output to every rank (sublayer index ``sub``)."""
+        if not self._fused():
+            return False
+        self.comm.arm_umma_push(kind, sub + 1)
+        return True
+
+    def _reduce_parts(self, y: torch.Tensor, n: int, kind: int, sub: int, pushed: bool):
+        """What the next seam folds.  One rank: the local buffer.  NCCL arm: all-reduce in place, then one part.
+        Fused arm: the W slots of this rank's symmetric buffer plus the arrival flags (the producer kernel
+        pushed already when ``pushed``; otherwise the generic push kernel does)."""
         if self.world == 1 or self.comm is None:
             return [y]
-        return self.comm.parts(y, n)
+        if not self._fused():
+            return self.comm.parts(y, n)
+        if not pushed:
+            self.comm.push(y, n, kind, sub + 1); self._k()
+        slots, flags = self.comm.slots(kind)
+        return (slots, flags, sub + 1)
 
     def _forward(self, n: int, len_bucket: int):
+        for _ in self._forward_gen(n, len_bucket):
+            pass
+
+    def _forward_gen(self, n: int, len_bucket: int):
+        """The rows-step forward.  Yields after every point where this rank has published a partial result, so
+        that a lockstep driver can interleave several ranks living in one process; a normal run just exhausts it."""
         cfg, w = self.cfg, self.w
+        fused = self._fused()
+        if fused:
+            self.comm.begin_step(); self._k()
         N.embed(w.embed, self.tokens, self.h, n, cfg.hc_mult, cfg.hidden_size, cfg.vocab_size, self.status); self._k()
         N.rope_table([w.inv_freq[c] for c, _ in self.rope_variants], [r for _, r in self.rope_variants], self.row_pos,
                      self.rope, n); self._k()
@@ -372,10 +408,6 @@ class Engine:
         y_prev = None
         tap_i = 0
         for l, L in enumerate(w.layers):
-            if l in cfg.dspark_taps and cfg.n_mtp_stages:
-                # taps read the block input, which only exists after the previous FFN has been folded:
-                # they are taken inside the attention seam below (ysum path), see _tap
-                pass
             self._seam(n, k, y_prev, L.hc_attn_fn, L.hc_attn_base, L.hc_attn_scale, L.attn_norm); k += 1
             if l in cfg.dspark_taps and cfg.n_mtp_stages:
                 N.tap_mean(self.h, self.taps[:, tap_i * cfg.hidden_size:], self.taps.stride(0), n, cfg.hc_mult,
@@ -387,24 +419,36 @@ class Engine:
             self._dbg(f"L{l}.q", self.qfull, n); self._dbg(f"L{l}.o", self.attn_out, n)
             self._dbg(f"L{l}.oa", self.oa, n); self._dbg(f"L{l}.attn_out", self.y_attn, n)
             self._dbg(f"L{l}.sel", self.sel, n); self._dbg(f"L{l}.sel_cnt", self.sel_cnt, n)
-            self._seam(n, k, self._reduce_parts(self.y_attn, n), L.hc_ffn_fn, L.hc_ffn_base, L.hc_ffn_scale,
-                       L.ffn_norm, atoms=1); k += 1
+            parts = self._reduce_parts(self.y_attn, n, 0, 2 * l, self._pushed)
+            yield ("attn", l)
+            self._seam(n, k, parts, L.hc_ffn_fn, L.hc_ffn_base, L.hc_ffn_scale, L.ffn_norm, atoms=1); k += 1
             self._dbg(f"L{l}.ffn_in", self.xn, n)
             self._prefetch(n, (L.s13, L.s2))
             self._next_wqkv = w.layers[l + 1].wqkv_a if l + 1 < len(w.layers) else w.head
             self._ffn(n, L, l)
             self._dbg(f"L{l}.ffn_out", self.y_ffn, n)
             self._dbg(f"L{l}.route_ids", self.ids, n); self._dbg(f"L{l}.route_w", self.wts, n)
-            y_prev = self._reduce_parts(self.y_ffn, n)
+            y_prev = self._reduce_parts(self.y_ffn, n, 1, 2 * l + 1, self._pushed)
+            yield ("ffn", l)
         self._seam(n, k, y_prev, None, None, None, w.norm, quant=False)
         self._dbg("final_x", self.xn, n); self._dbg("final_h", self.h, n)
         N.gemv(N.WF_BF16, w.head, None, 2 * cfg.hidden_size, self.vl, cfg.hidden_size, n, xb=self.xn,
                out_f=self.logits); self._k()
         N.sample(self.logits, self.row_pos, self.temp, self.seed, None, self.best_val[self.rank], self.best_id[self.rank],
                  n, self.vl, self.rank * self.vl); self._k()
-        if self.world > 1 and self.comm is not None:
-            self.comm.gather_best(self.best_val, self.best_id, n)
-        N.sample_fold(self.best_val, self.best_id, self.world if self.comm is not None else 1, n, self.tokens_out); self._k()
+        R = self.max_rows
+        if fused:
+            sub = 2 * len(w.layers)
+            self.comm.push_best(self.best_val, self.best_id, n, sub + 1); self._k(); self._k()
+            yield ("best",)
+            vals, ids, flags = self.comm.best_views()
+            N.sample_fold(vals, ids, self.world, n, R, self.tokens_out, flags=flags, epoch_ptr=self.comm.epoch_ptr,
+                          epoch_add=sub + 1, wait_ns=self.comm.wait_ns, status=self.status); self._k()
+        else:
+            if self.world > 1 and self.comm is not None:
+                self.comm.gather_best(self.best_val, self.best_id, n)
+            N.sample_fold(self.best_val, self.best_id, self.world if self.comm is not None else 1, n, R,
+                          self.tokens_out); self._k()
         self._join_prefetch()
 
     # ---- public step -------------------------------------------------------------------------------------

@@ -80,6 +80,7 @@ class DeviceWeights:
     inv_freq: dict = field(default_factory=dict)   # bool(compressed layer) -> f64 [rd/2]
     layers: list[LayerW] = field(default_factory=list)
     onehot: torch.Tensor = None      # f32 [hc] = (1, 0, 0, ..)
+    il: int = 0                      # stored local intermediate width (moe_inter / world, padded to 128)
 
     def nbytes(self) -> int:
         n = 0
@@ -96,6 +97,28 @@ class DeviceWeights:
             for v in vars(L).values():
                 add(v)
         return n
+
+
+def stored_inter(cfg: ModelConfig, world: int) -> int:
+    """Local expert width as stored: the 1/world slice padded with zero rows / zero K to a multiple of 128
+    (tensor-core tiles and the packed-FP4 TMA box want it; reference: the 576 -> 640 padded MoE layout,
+    crates/sparkflash-deepseek-forward/src/tp4_operands.rs)."""
+    il = cfg.moe_inter // world
+    return (il + 127) // 128 * 128
+
+
+def _pad_rows(t: torch.Tensor, rows: int, fill: int = 0) -> torch.Tensor:
+    if t.shape[0] == rows:
+        return t
+    pad = torch.full((rows - t.shape[0],) + tuple(t.shape[1:]), fill, dtype=t.dtype)
+    return torch.cat([t, pad], 0)
+
+
+def _pad_cols(t: torch.Tensor, cols: int, fill: int = 0) -> torch.Tensor:
+    if t.shape[1] == cols:
+        return t
+    pad = torch.full((t.shape[0], cols - t.shape[1]), fill, dtype=t.dtype)
+    return torch.cat([t, pad], 1)
 
 
 def _prep_sf_block32(sc: torch.Tensor, rows: int) -> torch.Tensor:
@@ -160,27 +183,30 @@ def _layer_from_ckpt(ck: dict, cfg: ModelConfig, p: str, l: int, n_exp: int, ran
     i0, i1 = rank * il, (rank + 1) * il
     kb_d, kb_i = d // 32, il // 32
 
+    ils = stored_inter(cfg, world)
+
     def slice13(name):
         w = ck[f"{name}.weight"][i0:i1]
         s = ck[f"{name}.scale"][i0 // 32:i1 // 32]
-        return w, _prep_sf_block32(s, il)
+        return _pad_rows(w, ils), _pad_rows(_prep_sf_block32(s, il), ils, 127)
 
     w1, s1 = slice13(f"{p}.ffn.shared_experts.w1")
     w3, s3 = slice13(f"{p}.ffn.shared_experts.w3")
     L.s13 = torch.stack([w1, w3]).contiguous().to(dev)
     L.s13_sf = torch.stack([s1, s3]).contiguous().to(dev)
-    L.s2 = ck[f"{p}.ffn.shared_experts.w2.weight"][:, i0:i1].contiguous().to(dev)
-    L.s2_sf = _prep_sf_block32(ck[f"{p}.ffn.shared_experts.w2.scale"][:, i0 // 32:i1 // 32].contiguous(), d).to(dev)
+    L.s2 = _pad_cols(ck[f"{p}.ffn.shared_experts.w2.weight"][:, i0:i1], ils).contiguous().to(dev)
+    L.s2_sf = _pad_cols(_prep_sf_block32(ck[f"{p}.ffn.shared_experts.w2.scale"][:, i0 // 32:i1 // 32].contiguous(), d),
+                        ils // 32, 127).contiguous().to(dev)
     # routed experts (fp4, per-row scales)
     w13, w13sf, w2, w2sf = [], [], [], []
     for e in range(n_exp):
         ws, ss = [], []
         for nm in ("w1", "w3"):
-            ws.append(ck[f"{p}.ffn.experts.{e}.{nm}.weight"][i0:i1])
-            ss.append(ck[f"{p}.ffn.experts.{e}.{nm}.scale"][i0:i1].contiguous())
+            ws.append(_pad_rows(ck[f"{p}.ffn.experts.{e}.{nm}.weight"][i0:i1], ils))
+            ss.append(_pad_rows(ck[f"{p}.ffn.experts.{e}.{nm}.scale"][i0:i1].contiguous(), ils, 127))
         w13.append(torch.stack(ws)); w13sf.append(torch.stack(ss))
-        w2.append(ck[f"{p}.ffn.experts.{e}.w2.weight"][:, i0 // 2:i1 // 2])
-        w2sf.append(ck[f"{p}.ffn.experts.{e}.w2.scale"][:, i0 // 32:i1 // 32].contiguous())
+        w2.append(_pad_cols(ck[f"{p}.ffn.experts.{e}.w2.weight"][:, i0 // 2:i1 // 2], ils // 2))
+        w2sf.append(_pad_cols(ck[f"{p}.ffn.experts.{e}.w2.scale"][:, i0 // 32:i1 // 32].contiguous(), ils // 32, 127))
     L.w13 = torch.stack(w13).contiguous().to(dev)
     L.w13_sf = torch.stack(w13sf).contiguous().to(dev)
     L.w2 = torch.stack(w2).contiguous().to(dev)
@@ -200,6 +226,7 @@ def prepare_from_checkpoint(ck: dict, cfg: ModelConfig, rank: int = 0, world: in
     oh = torch.zeros(cfg.hc_mult, dtype=torch.float32)
     oh[0] = 1.0
     W.onehot = oh.to(dev)
+    W.il = stored_inter(cfg, world)
     for l in range(cfg.n_layers):
         W.layers.append(_layer_from_ckpt(ck, cfg, f"layers.{l}", l, cfg.n_routed_experts, rank, world, dev))
     return W
@@ -217,7 +244,8 @@ def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="c
     dev = torch.device(device)
     d, h, hd, q = cfg.hidden_size, cfg.n_heads, cfg.head_dim, cfg.q_lora_rank
     og, ol, mi, hc = cfg.o_groups, cfg.o_lora_rank, cfg.moe_inter, cfg.hc_mult
-    hl, gl, il = h // world, og // world, mi // world
+    hl, gl = h // world, og // world
+    il = stored_inter(cfg, world)   # padding rows / K of a synthetic expert are ordinary random values
     E, V = cfg.n_routed_experts, cfg.vocab_size
     mix = (2 + hc) * hc
     FP8_CODE, FP4_CODE = 115, 120
@@ -251,6 +279,7 @@ def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="c
     oh = torch.zeros(hc, dtype=torch.float32)
     oh[0] = 1.0
     W.onehot = oh.to(dev)
+    W.il = il
     for l in range(cfg.n_layers):
         p = f"layers.{l}"
         L = LayerW()

@@ -57,7 +57,7 @@ def attach(weights: DeviceWeights, synthetic: bool = False) -> list[TcLayer]:
     cfg = weights.cfg
     W = weights.world
     d, q, hd = cfg.hidden_size, cfg.q_lora_rank, cfg.head_dim
-    gl, il = cfg.o_groups // W, cfg.moe_inter // W
+    gl, il = cfg.o_groups // W, weights.il or cfg.moe_inter // W
     ol, gin = cfg.o_lora_rank, cfg.group_in
     E = cfg.n_routed_experts
     c8 = 115 if synthetic else None

@@ -61,14 +61,15 @@ def coef_stride(hc: int) -> int:
 
 
 def seam_fold(h, y_parts, coef_prev, a_pre, a_stride, norm_w, xn, xq, xs, n, hc, d, norm_eps, ysum=None,
-              flags=None, epoch=0, status=None, xs_atom=None, atom_mode=0):
+              flags=None, epoch_ptr=None, epoch_add=0, wait_ns=0, status=None, xs_atom=None, atom_mode=0):
     """Critical-path half of an mHC seam (see csrc/k_seam.cu).  ``y_parts``: list of W partial outputs
     (tensors or raw device addresses) or None for the first seam of a forward."""
     has_post = y_parts is not None
     W = len(y_parts) if has_post else 1
     yp = _ptr_array(y_parts) if has_post else None
     fp = _ptr_array(flags) if flags is not None else None
-    code = lib().sfb_seam_fold(_p(h), yp, fp, c_uint32(epoch), c_int(W), c_int(1 if has_post else 0), _p(coef_prev),
+    ep = c_void_p(epoch_ptr) if isinstance(epoch_ptr, int) else _p(epoch_ptr)
+    code = lib().sfb_seam_fold(_p(h), yp, fp, ep, c_uint32(epoch_add), c_uint64(wait_ns), c_int(W), c_int(1 if has_post else 0), _p(coef_prev),
                                _p(a_pre), c_int(a_stride), _p(ysum), _p(norm_w), _p(xn), _p(xq), _p(xs), _p(xs_atom),
                                c_int(atom_mode), _p(status), c_int(n), c_int(hc), c_int(d), c_float(norm_eps),
                                _stream())
@@ -227,8 +228,14 @@ def sample(logits, row_pos, temperature, seed, mask, best_val, best_id, n, V, vo
     _check(code, "sample")
 
 
-def sample_fold(vals, ids, W, n, out_tokens):
-    _check(lib().sfb_sample_fold(_p(vals), _p(ids), c_int(W), c_int(n), _p(out_tokens), _stream()), "sample_fold")
+def sample_fold(vals, ids, W, n, stride, out_tokens, flags=None, epoch_ptr=None, epoch_add=0, wait_ns=0, status=None):
+    """vals / ids: tensors or raw device addresses of [W, stride] winners."""
+    pv = c_void_p(vals) if isinstance(vals, int) else _p(vals)
+    pi = c_void_p(ids) if isinstance(ids, int) else _p(ids)
+    fp = _ptr_array(flags) if flags is not None else None
+    ep = c_void_p(epoch_ptr) if isinstance(epoch_ptr, int) else _p(epoch_ptr)
+    _check(lib().sfb_sample_fold(pv, pi, c_int(W), c_int(n), c_int(stride), _p(out_tokens), fp, ep, c_uint32(epoch_add),
+                                 c_uint64(wait_ns), _p(status), _stream()), "sample_fold")
 
 
 def synth_fill(kind: int, dst: torch.Tensor, count: int, seed: int, sigma: float, mean: float = 0.0):

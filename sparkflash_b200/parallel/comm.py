@@ -18,6 +18,7 @@ import torch.distributed as dist
 
 class NcclComm:
     name = "nccl"
+    wait_ns = 0
 
     def __init__(self, rank: int, world: int):
         self.rank, self.world = rank, world

@@ -1,0 +1,56 @@
+"""Multi-GPU tests: real ranks (one process per GPU, torch.distributed over NCCL) running the fused
+push / flag / fold collectives and the NCCL arm; both must sample the same tokens as each other."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+WORKER = r'''
+import json, os, sys, torch
+import torch.distributed as dist
+sys.path.insert(0, os.environ["SFB_REPO"])
+from sparkflash_b200.config import tiny_config
+from sparkflash_b200.models.deepseek_v41 import engine as E, prepare as P, weights as W
+from sparkflash_b200.parallel import comm as PC
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+cfg = tiny_config()
+ck = W.synthetic_checkpoint(cfg, 0)
+out = {}
+for arm in ("fused", "nccl"):
+    comm = PC.make_comm(arm, rank, world)
+    eng = E.Engine(P.prepare_from_checkpoint(ck, cfg, rank, world), max_lanes=2, max_context=256, max_rows=16,
+                   comm=comm, arm=os.environ.get("SFB_TEST_ARM", "tc"))
+    comm.attach(eng)
+    prompt = torch.randint(0, cfg.vocab_size, (20,), generator=torch.Generator().manual_seed(3)).tolist()
+    toks = eng.generate(prompt, 12)
+    eng.check_status()
+    out[arm] = toks
+    dist.barrier()
+if rank == 0:
+    print("RESULT " + json.dumps(out))
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.parametrize("arm", ["tc", "cuda"])
+def test_two_ranks_fused_and_nccl_agree(tmp_path, arm):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, SFB_REPO=repo, NCCL_NVLS_ENABLE="0", SFB_TEST_ARM=arm)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29533", str(script)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    res = json.loads(line[7:])
+    # the fused arm folds in rank order in fp32, NCCL reduces in bf16: the first tokens agree, later ones may drift
+    assert res["fused"][:2] == res["nccl"][:2], res
+    assert len(res["fused"]) == 12
