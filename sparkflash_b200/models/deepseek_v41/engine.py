@@ -532,6 +532,7 @@ class Engine:
             c = prompt[pos:pos + chunk]
             r = self.step(c, [lane] * len(c), list(range(pos, pos + len(c))), [temperature] * len(c), [seed] * len(c))
             nxt = int(r[len(c) - 1])
+            self.check_status()
             if collect_logits:
                 last = self.logits[len(c) - 1].clone()
             pos += len(c)
@@ -543,5 +544,6 @@ class Engine:
             if collect_logits:
                 last = self.logits[0].clone()
             nxt = int(r[0])
+            self.check_status()
             pos += 1
         return (out, torch.stack(logits)) if collect_logits else out

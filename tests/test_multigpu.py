@@ -2,6 +2,7 @@
 push / flag / fold collectives and the NCCL arm; both must sample the same tokens as each other."""
 import json
 import os
+import signal
 import subprocess
 import sys
 
@@ -30,6 +31,7 @@ for arm in os.environ["SFB_TEST_COLLECTIVES"].split(","):
     eng = E.Engine(P.prepare_from_checkpoint(ck, cfg, rank, world), max_lanes=2, max_context=256, max_rows=16,
                    comm=comm, arm=os.environ.get("SFB_TEST_ARM", "tc"))
     comm.attach(eng)
+    comm.wait_ns = 200_000_000      # a protocol error shows as a status word within a step, not as a long stall
     print("attached", arm, file=log, flush=True)
     prompt = torch.randint(0, cfg.vocab_size, (20,), generator=torch.Generator().manual_seed(3)).tolist()
     toks = eng.generate(prompt, 12)
@@ -56,9 +58,15 @@ def test_two_ranks_fused_and_nccl_agree(tmp_path, arm, collectives):
                SFB_WORKER_LOG=os.path.join(logdir, f"mgpu_worker_{arm}.log"))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", "29533", str(script)]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=150)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, start_new_session=True)
+    try:
+        stdout, stderr = proc.communicate(timeout=150)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)      # the launcher and both workers: exactly the group started here
+        stdout, stderr = proc.communicate()
+        pytest.fail("2-rank worker timed out\n" + stdout[-2000:] + stderr[-2000:])
+    assert proc.returncode == 0, stdout[-3000:] + stderr[-3000:]
+    line = [l for l in stdout.splitlines() if l.startswith("RESULT ")][-1]
     res = json.loads(line[7:])
     # the fused arm folds in rank order in fp32, NCCL reduces in bf16: the first tokens agree, later ones may drift
     if "nccl" in res:
