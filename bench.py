@@ -277,6 +277,7 @@ def main() -> None:
         print(json.dumps(out))
     if world > 1:
         dist.barrier()
+        eng.close()      # captured graphs reference the communicator: drop them before it is destroyed
         dist.destroy_process_group()
 
 

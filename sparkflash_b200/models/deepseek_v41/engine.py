@@ -170,6 +170,15 @@ class Engine:
         if self.debug is not None:
             self.debug[key] = t[:n].detach().clone()
 
+    def close(self) -> None:
+        """Drop the captured graphs (and with them any collective work they hold).  A communicator cannot
+        be destroyed while a live CUDA graph still references it, so call this before tearing the process
+        group down."""
+        torch.cuda.synchronize()
+        self.graphs.clear()
+        if self.comm is not None and hasattr(self.comm, "close"):
+            self.comm.close()
+
     def check_status(self) -> None:
         st = self.status.tolist()
         if st[0] != 0:

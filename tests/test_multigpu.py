@@ -41,9 +41,13 @@ for arm in os.environ["SFB_TEST_COLLECTIVES"].split(","):
     torch.cuda.synchronize()
     dist.barrier()
     print("barrier", arm, file=log, flush=True)
+    eng.close()          # graphs that captured collectives must go before the communicator does
+    del eng, comm
+    print("closed", arm, file=log, flush=True)
 if rank == 0:
     print("RESULT " + json.dumps(out))
 dist.destroy_process_group()
+print('destroyed', file=log, flush=True)
 '''
 
 
