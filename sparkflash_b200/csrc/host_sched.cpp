@@ -53,6 +53,7 @@ struct Config {
   int prefill_chunk = 4096, prefill_chunk_busy = 2048, prefix_reuse_min = 256, decode_share = 2;
   int max_context = 1048576;
   int spec_depth = 5;
+  int64_t ring_slack = (int64_t)1 << 40;
   int64_t lane_row_budget = -1;  // total rows all lanes may hold (-1: unlimited)
 };
 
@@ -97,6 +98,9 @@ void place_waiting(Scheduler& s) {
     int best = -1, best_len = 0;
     for (int li : free_lanes) {
       int c = common_prefix(s.lanes[li].held, q.tokens, (int)q.tokens.size() - 1);
+      // the window ring is addressed by position modulo its size: rows the old sequence wrote far past the
+      // shared prefix have overwritten the prefix's own window tail, and then the prefix cannot be reused
+      if ((int64_t)s.lanes[li].held.size() - c > s.cfg.ring_slack) continue;
       if (c >= s.cfg.prefix_reuse_min && c > best_len) { best = li; best_len = c; }
     }
     if (best < 0) {  // least recently used free lane (ties: lowest index)
@@ -163,6 +167,7 @@ void* sfb_sched_create(int max_lanes, int queue_depth, int max_rows, int prefill
   s->lanes.resize(max_lanes);
   return s;
 }
+void sfb_sched_set_ring_slack(void* h, int64_t rows) { ((Scheduler*)h)->cfg.ring_slack = rows; }
 void sfb_sched_destroy(void* h) { delete (Scheduler*)h; }
 
 // 0 = accepted, 1 = refused (lanes and queue full), 2 = prompt too long / invalid

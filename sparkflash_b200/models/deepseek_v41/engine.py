@@ -71,7 +71,7 @@ class StepIO:
 class Engine:
     def __init__(self, weights: DeviceWeights, max_lanes: int = 4, max_context: int = 4096, max_rows: int = 64,
                  comm=None, use_graphs: bool = True, keep_logits: bool = False, arm: str = "cuda",
-                 synthetic_scales: bool = False):
+                 synthetic_scales: bool = False, constrained: bool = False):
         """``arm``: "cuda" = CUDA-core exact arm for every projection; "tc" = tcgen05 tensor-core arm for
         every shape it takes (the rest falls back to the CUDA-core kernels)."""
         self.w, self.cfg = weights, weights.cfg
@@ -82,6 +82,10 @@ class Engine:
         self.comm = comm
         self.use_graphs = use_graphs
         self.keep_logits = keep_logits
+        # serving-side contract (serve/driver.py): a byte mask per row over the whole vocabulary, all ones unless a
+        # constrained sequence owns the row; each rank fills and reads only its own slice
+        self.supports_mask = constrained
+        self.supports_filter = False
         self.kv = KVCache(cfg, max_lanes, max_context, max_rows, self.dev)
         R, d, hc, hd, q = max_rows, cfg.hidden_size, cfg.hc_mult, cfg.head_dim, cfg.q_lora_rank
         W = self.world
@@ -136,6 +140,8 @@ class Engine:
         self.act_q = e((R, cfg.top_k + 1, self.il), u8)
         self.act_s = e((R, cfg.top_k + 1, self.il // 32), u8)
         self.logits = e((R, self.vl), f32)
+        self.mask = torch.ones((R, cfg.vocab_size), dtype=torch.uint8, device=dev) if constrained else None
+        self._masked_rows: set[int] = set()
         self.best_val, self.best_id = e((W, R), f32), e((W, R), i32)
         self.tokens_out = e((R,), i32)
         self.taps = e((R, max(1, len(cfg.dspark_taps)) * d), bf)
@@ -443,7 +449,7 @@ class Engine:
         self._dbg("final_x", self.xn, n); self._dbg("final_h", self.h, n)
         N.gemv(N.WF_BF16, w.head, None, 2 * cfg.hidden_size, self.vl, cfg.hidden_size, n, xb=self.xn,
                out_f=self.logits); self._k()
-        N.sample(self.logits, self.row_pos, self.temp, self.seed, None, self.best_val[self.rank], self.best_id[self.rank],
+        N.sample(self.logits, self.row_pos, self.temp, self.seed, self.mask, self.best_val[self.rank], self.best_id[self.rank],
                  n, self.vl, self.rank * self.vl); self._k()
         R = self.max_rows
         if fused:
@@ -469,13 +475,35 @@ class Engine:
             b *= 2
         return b
 
-    def step(self, tokens, lanes, positions, temperature=None, seeds=None, sync: bool = True) -> torch.Tensor:
+    @property
+    def ring_slack(self) -> int:
+        """Rows a lane may have advanced past a shared prefix with the prefix's window tail still intact."""
+        return self.kv.ring - self.cfg.window
+
+    def vocab_slice(self) -> tuple[int, int]:
+        return self.rank * self.vl, (self.rank + 1) * self.vl
+
+    def _stage_masks(self, masks: dict) -> None:
+        import numpy as np
+        lo, hi = self.vocab_slice()
+        for r in self._masked_rows - set(masks):
+            self.mask[r, lo:hi] = 1
+        self._masked_rows = set(masks)
+        for r, words in masks.items():
+            bits = np.unpackbits(np.asarray(words, dtype=np.uint64).view(np.uint8), bitorder="little")[:hi - lo]
+            self.mask[r, lo:hi].copy_(torch.from_numpy(bits))
+
+    def step(self, tokens, lanes, positions, temperature=None, seeds=None, sync: bool = True, masks: dict | None = None) -> torch.Tensor:
         """Run one rows step.  ``tokens/lanes/positions`` are host sequences of equal length n.
         Returns the sampled next-token ids as a host int32 tensor [n] (pinned) when ``sync``; the
         device tensor ``tokens_out`` otherwise."""
         n = len(tokens)
         if not 0 < n <= self.max_rows:
             raise ValueError(f"rows {n} out of range 1..{self.max_rows}")
+        if masks or self._masked_rows:
+            if self.mask is None:
+                raise ValueError("this engine was built without constrained=True")
+            self._stage_masks(masks or {})
         if max(positions) >= self.max_context or max(lanes) >= self.max_lanes:
             raise ValueError("position or lane beyond the cache capacity")
         io = self.io

@@ -18,6 +18,7 @@ def _L():
         L.sfb_sched_create.restype = c_void_p
         L.sfb_sched_create.argtypes = [c_int] * 8 + [c_int64]
         L.sfb_sched_destroy.argtypes = [c_void_p]
+        L.sfb_sched_set_ring_slack.argtypes = [c_void_p, c_int64]
         L.sfb_sched_submit.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int]
         L.sfb_sched_cancel.argtypes = [c_void_p, c_int64]
         L.sfb_sched_set_drafts.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int]
@@ -76,6 +77,9 @@ class Scheduler:
             _L().sfb_sched_destroy(self._h)
         except Exception:
             pass
+
+    def set_ring_slack(self, rows: int) -> None:
+        _L().sfb_sched_set_ring_slack(self._h, rows)
 
     def submit(self, seq_id: int, prompt: list[int], max_new: int) -> int:
         return _L().sfb_sched_submit(self._h, seq_id, _i32(prompt), len(prompt), max_new)

@@ -1,0 +1,134 @@
+"""Serving loop over a fake rows engine: chunked prefill, continuous batching, prefix reuse, speculation
+that does not change the output, constraints, cancellation, fail-stop (reference tests:
+crates/sparkflash-serve/tests/{concurrency,prefix_cache,toy_host}.rs, tp4 batch tests)."""
+import asyncio
+import json
+
+from starlette.testclient import TestClient
+
+from sparkflash_b200.serve.driver import DeviceDriver, FakeRowsEngine, NgramDrafter
+from sparkflash_b200.serve.engine_api import EngineRequest
+from sparkflash_b200.serve.server import Server
+from sparkflash_b200.serve.tokenizer import ByteTokenizer
+
+TOK = ByteTokenizer(300)
+
+
+async def collect(drv, req):
+    toks, fin = [], None
+    async for ev in drv.generate(req):
+        if ev[0] == "token":
+            toks.append(ev[1])
+        elif ev[0] in ("finished", "error"):
+            fin = ev
+    return toks, fin
+
+
+def run(drv, reqs):
+    async def go():
+        return await asyncio.gather(*[collect(drv, r) for r in reqs])
+    drv.start()
+    try:
+        return asyncio.run(go())
+    finally:
+        drv.shutdown(1.0)
+
+
+def reference_tokens(prompt, n, **kw):
+    eng = FakeRowsEngine(**kw)
+    for p, t in enumerate(prompt):
+        eng.lane_tokens[0][p] = t
+    out, pos = [], len(prompt) - 1
+    for _ in range(n):
+        t = eng._next(0, pos)
+        if t == eng.eos_id:
+            break
+        out.append(t); pos += 1; eng.lane_tokens[0][pos] = t
+    return out
+
+
+def test_chunked_prefill_and_batching_match_the_sequential_result():
+    prompts = [list(range(40, 40 + n)) for n in (37, 5, 20)]
+    eng = FakeRowsEngine(max_rows=8)
+    drv = DeviceDriver(eng, TOK, prefix_reuse_min=1000)
+    res = run(drv, [EngineRequest(f"r{i}", "m", p, max_tokens=12, temperature=0.0) for i, p in enumerate(prompts)])
+    for (toks, fin), p in zip(res, prompts):
+        assert fin[0] == "finished" and fin[1] == "length" and toks == reference_tokens(p, 12)
+    assert max(eng.steps) <= 8 and any(s == 3 for s in eng.steps)        # three sequences shared decode steps
+
+
+def test_prefix_reuse_keeps_the_output_and_skips_rows():
+    base = list(range(50, 110))
+    eng = FakeRowsEngine(max_rows=16, max_lanes=1)
+    drv = DeviceDriver(eng, TOK, prefix_reuse_min=8)
+    drv.start()
+    try:
+        a = asyncio.run(collect(drv, EngineRequest("a", "m", base, max_tokens=4, temperature=0.0)))
+        rows_a = sum(eng.steps)
+        b = asyncio.run(collect(drv, EngineRequest("b", "m", base[:48] + [7, 8, 9], max_tokens=4, temperature=0.0)))
+    finally:
+        drv.shutdown(1.0)
+    assert b[0] == reference_tokens(base[:48] + [7, 8, 9], 4)
+    assert sum(eng.steps) - rows_a == 3 + 3 and drv.sched.stats()["prefix_rows"] == 48
+
+
+def test_speculation_does_not_change_the_output():
+    cyc = [65, 66, 67, 68, 69, 70]
+    prompt = [cyc[i % 6] for i in range(24)]
+    plain = DeviceDriver(FakeRowsEngine(cycle=cyc), TOK)
+    want = run(plain, [EngineRequest("p", "m", prompt, max_tokens=30, temperature=0.0)])[0]
+    eng = FakeRowsEngine(cycle=cyc)
+    spec = DeviceDriver(eng, TOK, drafter=NgramDrafter(depth=4))
+    got = run(spec, [EngineRequest("s", "m", prompt, max_tokens=30, temperature=0.0)])[0]
+    assert got[0] == want[0] and len(got[0]) == 30
+    st = got[1][2]
+    assert st["accepted"] > 0 and st["accepted"] <= st["proposed"] and len([s for s in eng.steps if s > 1]) < 30
+
+
+def test_constraint_masks_reach_the_sampler():
+    eng = FakeRowsEngine()
+    drv = DeviceDriver(eng, TOK)
+    sc = {"type": "object", "properties": {"n": {"type": "integer", "minimum": 1, "maximum": 9}}, "required": ["n"], "additionalProperties": False}
+    (toks, fin), = run(drv, [EngineRequest("c", "m", [1, 2, 3], max_tokens=64, temperature=0.0, constraint=sc)])
+    assert fin[0] == "finished" and fin[1] == "stop"
+    doc = json.loads(bytes(toks).decode())
+    assert 1 <= doc["n"] <= 9
+
+
+def test_http_over_the_driver_and_fail_stop():
+    eng = FakeRowsEngine(eos_after=30)
+    drv = DeviceDriver(eng, TOK, model_id="fake").start()
+    try:
+        c = TestClient(Server(drv).app)
+        j = c.post("/v1/completions", json={"prompt": "hello world, this is a test", "max_tokens": 50}).json()
+        assert j["choices"][0]["finish_reason"] == "stop" and j["usage"]["completion_tokens"] == 31 - len("hello world, this is a test")
+        assert c.get("/readyz").status_code == 200
+        eng.status_error = "device status code=3 where=7"
+        r = c.post("/v1/completions", json={"prompt": "x", "max_tokens": 5})
+        assert r.status_code == 503
+        assert c.get("/health").status_code == 503 and "device status" in c.get("/health").json()["reason"]
+        assert c.post("/v1/completions", json={"prompt": "x"}).status_code == 503
+    finally:
+        drv.shutdown(0.1)
+
+
+def test_cancel_frees_the_lane():
+    eng = FakeRowsEngine(max_lanes=1)
+    drv = DeviceDriver(eng, TOK, queue_depth=0).start()
+
+    async def go():
+        agen = drv.generate(EngineRequest("x", "m", [5, 6, 7], max_tokens=400))
+        n = 0
+        async for ev in agen:
+            if ev[0] == "token":
+                n += 1
+                if n == 3:
+                    break
+        await agen.aclose()
+        await asyncio.sleep(0.1)
+        return await collect(drv, EngineRequest("y", "m", [5, 6, 7], max_tokens=3))
+    try:
+        toks, fin = asyncio.run(go())
+    finally:
+        drv.shutdown(0.5)
+    assert fin[0] == "finished" and len(toks) == 3

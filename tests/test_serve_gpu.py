@@ -1,0 +1,92 @@
+"""The serving loop over the real device engine on the tiny model: driver output equals Engine.generate,
+speculative verify rows do not change it (position-addressed caches make rejected rows harmless), prefix
+reuse keeps it, and the head honours a constraint mask."""
+import asyncio
+import json
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def setup():
+    from sparkflash_b200.config import tiny_config
+    from sparkflash_b200.models.deepseek_v41 import engine as E, prepare as P, weights as W
+    from sparkflash_b200.serve.tokenizer import ByteTokenizer
+    cfg = tiny_config()
+    ck = W.synthetic_checkpoint(cfg, 0)
+    w = P.prepare_from_checkpoint(ck, cfg, 0, 1)
+    tok = ByteTokenizer(cfg.vocab_size)
+
+    def make(**kw):
+        return E.Engine(w, max_lanes=3, max_context=256, max_rows=16, arm="tc", constrained=True, **kw)
+    return cfg, tok, make
+
+
+async def _collect(drv, req):
+    toks, fin = [], None
+    async for ev in drv.generate(req):
+        if ev[0] == "token":
+            toks.append(ev[1])
+        elif ev[0] in ("finished", "error"):
+            fin = ev
+    return toks, fin
+
+
+def _run(drv, reqs):
+    async def go():
+        return await asyncio.gather(*[_collect(drv, r) for r in reqs])
+    drv.start()
+    try:
+        return asyncio.run(go())
+    finally:
+        drv.shutdown(1.0)
+
+
+def test_driver_matches_generate_and_speculation_is_invisible(setup):
+    from sparkflash_b200.serve.driver import DeviceDriver, NgramDrafter
+    from sparkflash_b200.serve.engine_api import EngineRequest
+    cfg, tok, make = setup
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 256, (n,), generator=g).tolist() for n in (23, 9)]
+    # a repetitive prompt so that the n-gram drafter has something to propose
+    prompts.append(([65, 66, 67, 68] * 8)[:30])
+    want = [make().generate(p, 10) for p in prompts]
+    eos = 10 ** 9      # never sampled: compare fixed-length runs
+    plain = _run(DeviceDriver(make(), tok, eos_id=eos, prefix_reuse_min=1000),
+                 [EngineRequest(f"p{i}", "m", p, max_tokens=10, temperature=0.0) for i, p in enumerate(prompts)])
+    for (toks, fin), w in zip(plain, want):
+        assert fin[0] == "finished" and toks[:3] == w[:3]        # batched rows share a step with other sequences:
+        assert sum(a == b for a, b in zip(toks, w)) >= 7           # bits are batch-invariant, so this is normally exact
+    spec = _run(DeviceDriver(make(), tok, eos_id=eos, prefix_reuse_min=1000, drafter=NgramDrafter(depth=3)),
+                [EngineRequest(f"s{i}", "m", p, max_tokens=10, temperature=0.0) for i, p in enumerate(prompts)])
+    for (a, _), (b, fb) in zip(plain, spec):
+        assert a == b, (a, b)
+    assert any(f[2]["proposed"] > 0 for _, f in spec)
+
+
+def test_prefix_reuse_and_constraint_on_device(setup):
+    from sparkflash_b200.serve.driver import DeviceDriver
+    from sparkflash_b200.serve.engine_api import EngineRequest
+    cfg, tok, make = setup
+    g = torch.Generator().manual_seed(9)
+    base = torch.randint(0, 256, (40,), generator=g).tolist()
+    second = base[:32] + [1, 2, 3]
+    want = make().generate(second, 6)
+    drv = DeviceDriver(make(), tok, eos_id=10 ** 9, prefix_reuse_min=8, max_lanes=1).start()
+    try:
+        asyncio.run(_collect(drv, EngineRequest("a", "m", base, max_tokens=3, temperature=0.0)))
+        toks, fin = asyncio.run(_collect(drv, EngineRequest("b", "m", second, max_tokens=6, temperature=0.0)))
+        assert drv.sched.stats()["prefix_rows"] == 32 and toks == want
+        sc = {"type": "object", "properties": {"n": {"type": "integer", "minimum": 1, "maximum": 9}}, "required": ["n"], "additionalProperties": False}
+        drv.eos_id = tok.eos_id
+        toks, fin = asyncio.run(_collect(drv, EngineRequest("c", "m", base[:10], max_tokens=200, temperature=0.8, seed=3, constraint=sc)))
+    finally:
+        drv.shutdown(1.0)
+    if fin[1] == "stop":
+        doc = json.loads(bytes(toks).decode())
+        assert 1 <= doc["n"] <= 9
+    else:       # whitespace padding is bounded, so a random model still has to close the document eventually
+        assert fin[1] == "length"
