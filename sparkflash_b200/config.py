@@ -294,3 +294,57 @@ def load_toml(path: str) -> dict[str, Any]:
     import tomllib
     with open(path, "rb") as f:
         return tomllib.load(f)
+
+
+# released checkpoint's config.json key -> ModelConfig field (reference: crates/sparkflash-model-deepseek-v41/
+# src/config.rs:64-207; keys this engine has no use for are listed so that a NEW unknown key is refused)
+_HF_KEYS = {
+    "vocab_size": "vocab_size", "dim": "hidden_size", "n_layers": "n_layers", "n_heads": "n_heads", "head_dim": "head_dim",
+    "rope_head_dim": "rope_dim", "q_lora_rank": "q_lora_rank", "o_groups": "o_groups", "o_lora_rank": "o_lora_rank",
+    "moe_inter_dim": "moe_inter", "n_routed_experts": "n_routed_experts", "n_shared_experts": "n_shared_experts",
+    "n_activated_experts": "top_k", "route_scale": "route_scale", "swiglu_limit": "swiglu_limit", "norm_eps": "norm_eps",
+    "window_size": "window", "rope_theta": "rope_theta", "compress_rope_theta": "compress_rope_theta", "rope_factor": "yarn_factor",
+    "original_seq_len": "yarn_orig_max_pos", "beta_fast": "yarn_beta_fast", "beta_slow": "yarn_beta_slow",
+    "compress_ratios": "compress_ratios", "kv_source_layers": "kv_source_layers", "index_source_layers": "index_source_layers",
+    "candidate_source_layer": "candidate_source_layer", "candidate_topk_blocks": "candidate_topk_blocks",
+    "candidate_block_size": "candidate_block_size", "index_n_heads": "index_n_heads", "index_head_dim": "index_head_dim",
+    "index_topk": "index_topk", "hc_mult": "hc_mult", "hc_sinkhorn_iters": "hc_sinkhorn_iters", "hc_eps": "hc_eps",
+    "engram_layer_ids": "engram_layers", "engram_num_embeddings": "engram_rows", "engram_max_ngram_size": "engram_max_ngram",
+    "engram_n_heads": "engram_n_heads", "engram_head_dim": "engram_head_dim", "engram_compressed_vocab_size": "engram_compressed_vocab",
+    "n_mtp_layers": "n_mtp_stages", "dspark_block_size": "dspark_block", "dspark_noise_token_id": "dspark_noise_token",
+    "dspark_target_layer_ids": "dspark_taps", "dspark_markov_rank": "dspark_markov_rank", "dspark_n_routed_experts": "dspark_n_experts",
+    "dspark_n_activated_experts": "dspark_top_k", "image_token_id": "image_token_id",
+}
+_HF_IGNORED = {"score_func", "dtype", "expert_dtype", "gate_temp", "norm_topk_prob", "engram_vocab_size", "engram_pad_id",
+               "model_type", "architectures", "torch_dtype", "transformers_version", "max_position_embeddings", "bos_token_id",
+               "eos_token_id", "pad_token_id", "tie_word_embeddings", "quantization_config", "auto_map"}
+
+
+def config_from_hf(d: dict[str, Any]) -> ModelConfig:
+    """ModelConfig from a checkpoint's ``config.json``.  Unknown keys are refused (a typo or a new
+    architecture knob must not be silently dropped); ``vision_*`` keys belong to the vision tower's own config."""
+    kw: dict[str, Any] = {}
+    for k, v in d.items():
+        if k in _HF_KEYS:
+            kw[_HF_KEYS[k]] = v
+        elif k in _HF_IGNORED or k.startswith("vision_"):
+            continue
+        else:
+            raise ValueError(f"config.json: unknown key {k!r}")
+    if d.get("score_func", "sqrtsoftplus") != "sqrtsoftplus":
+        raise ValueError(f"score_func {d['score_func']!r} is not implemented (sqrtsoftplus only)")
+    if "eos_token_id" in d:
+        kw["eos_id"] = d["eos_token_id"]
+    if "bos_token_id" in d:
+        kw["bos_id"] = d["bos_token_id"]
+    if "max_position_embeddings" in d:
+        kw["max_positions"] = d["max_position_embeddings"]
+    return dataclasses.replace(ModelConfig(), **kw)
+
+
+def config_to_hf(c: ModelConfig) -> dict[str, Any]:
+    inv = {v: k for k, v in _HF_KEYS.items()}
+    out = {inv[f.name]: getattr(c, f.name) for f in dataclasses.fields(c) if f.name in inv}
+    out.update(score_func="sqrtsoftplus", eos_token_id=c.eos_id, bos_token_id=c.bos_id, max_position_embeddings=c.max_positions,
+               model_type="deepseek_v41")
+    return out
