@@ -25,8 +25,16 @@ class KVCache:
     """Position-addressed caches for ``lanes`` sequences (fixed-capacity arm; the lazily backed arm
     lives in kv/lanes.py).  Window ring slots = position % ring; compressed entry = position // ratio."""
 
-    def __init__(self, cfg: ModelConfig, lanes: int, max_context: int, max_rows: int, device):
+    def __init__(self, cfg: ModelConfig, lanes: int, max_context: int, max_rows: int, device, lane_budget_bytes: int | None = None):
+        """``lane_budget_bytes``: back the per-position regions (compressed KV, index keys) lazily from a chunk
+        pool of this size instead of allocating ``lanes * max_context`` up front (kv/lanes.py)."""
         self.cfg, self.lanes, self.max_context = cfg, lanes, max_context
+        self.pool = None
+        self._regions: dict[int, list] = {}
+        self._backed: dict[int, list[int]] = {}
+        if lane_budget_bytes is not None:
+            from ...kv.lanes import LanePool
+            self.pool = LanePool(lane_budget_bytes)
         hd, idh = cfg.head_dim, cfg.index_head_dim
         ring = 1
         while ring < cfg.window + max_rows:
@@ -44,12 +52,45 @@ class KVCache:
                 self.max_entries[l] = me
                 if r > 1:
                     self.cin[l] = torch.zeros((lanes, ring, 2 * hd), dtype=torch.float32, device=device)
+                if self.pool is not None:
+                    from ...kv.lanes import LaneRegion
+                    regs = [LaneRegion(self.pool, lanes, me, w) for w in (hd // 2, hd // 16, idh // 2, idh // 32)]
+                    self.ckv_q[l], self.ckv_s[l], self.ik_q[l], self.ik_s[l] = (r.tensor for r in regs)
+                    self._regions[l], self._backed[l] = regs, [0] * lanes
+                    continue
                 self.ckv_q[l] = torch.zeros((lanes, me, hd // 2), **u8)
                 self.ckv_s[l] = torch.zeros((lanes, me, hd // 16), **u8)
                 self.ik_q[l] = torch.zeros((lanes, me, idh // 2), **u8)
                 self.ik_s[l] = torch.zeros((lanes, me, idh // 32), **u8)
 
+    def ensure(self, lanes, positions) -> None:
+        """Back every lazily mapped region far enough for the rows of this step (a no-op for dense caches)."""
+        if self.pool is None:
+            return
+        top: dict[int, int] = {}
+        for ln, p in zip(lanes, positions):
+            top[ln] = max(top.get(ln, 0), p)
+        for l, regs in self._regions.items():
+            r = self.cfg.ratio(l)
+            for ln, p in top.items():
+                need = p // r + 2
+                if need > self._backed[l][ln]:
+                    need = min(regs[0].rows, (need + 4095) // 4096 * 4096)
+                    for reg in regs:
+                        reg.ensure_rows(ln, need)
+                    self._backed[l][ln] = need
+
+    def release_lane(self, lane: int) -> None:
+        """Give a finished sequence's chunks back to the pool (its kernels must have completed)."""
+        for l, regs in self._regions.items():
+            for reg in regs:
+                reg.release(lane)
+            self._backed[l][lane] = 0
+
     def nbytes(self) -> int:
+        if self.pool is not None:
+            return sum(t.numel() * t.element_size() for dct in (self.win_q, self.win_s, self.cin) for t in dct.values()) + \
+                sum(reg.mapped_bytes for regs in self._regions.values() for reg in regs)
         n = 0
         for dct in (self.win_q, self.win_s, self.cin, self.ckv_q, self.ckv_s, self.ik_q, self.ik_s):
             for t in dct.values():
@@ -71,7 +112,7 @@ class StepIO:
 class Engine:
     def __init__(self, weights: DeviceWeights, max_lanes: int = 4, max_context: int = 4096, max_rows: int = 64,
                  comm=None, use_graphs: bool = True, keep_logits: bool = False, arm: str = "cuda",
-                 synthetic_scales: bool = False, constrained: bool = False):
+                 synthetic_scales: bool = False, constrained: bool = False, lane_budget_bytes: int | None = None):
         """``arm``: "cuda" = CUDA-core exact arm for every projection; "tc" = tcgen05 tensor-core arm for
         every shape it takes (the rest falls back to the CUDA-core kernels)."""
         self.w, self.cfg = weights, weights.cfg
@@ -86,7 +127,7 @@ class Engine:
         # constrained sequence owns the row; each rank fills and reads only its own slice
         self.supports_mask = constrained
         self.supports_filter = False
-        self.kv = KVCache(cfg, max_lanes, max_context, max_rows, self.dev)
+        self.kv = KVCache(cfg, max_lanes, max_context, max_rows, self.dev, lane_budget_bytes)
         R, d, hc, hd, q = max_rows, cfg.hidden_size, cfg.hc_mult, cfg.head_dim, cfg.q_lora_rank
         W = self.world
         self.hl, self.gl, self.vl = cfg.n_heads // W, cfg.o_groups // W, cfg.vocab_size // W
@@ -500,6 +541,7 @@ class Engine:
         n = len(tokens)
         if not 0 < n <= self.max_rows:
             raise ValueError(f"rows {n} out of range 1..{self.max_rows}")
+        self.kv.ensure(lanes, positions)
         if masks or self._masked_rows:
             if self.mask is None:
                 raise ValueError("this engine was built without constrained=True")
