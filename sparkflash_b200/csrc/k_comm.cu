@@ -55,6 +55,70 @@ __global__ void wait_flags_kernel(const uint32_t* const* flags, int W, const uin
     status_set(st, ST_TIMEOUT, 30, threadIdx.x, (int)(*epoch_ptr + epoch_add));
 }
 
+
+// ---- consumer half of GEMM -> all-reduce / reduce-scatter: fold the W arrival slots, add the residual, RMSNorm ----
+struct FoldArgs {
+  const __nv_bfloat16* slot[8];   // rank r's partial for this rank's rows, [n, stride]
+  const uint32_t* flag[8];        // arrival flags (null = do not wait)
+  int W, n, d;
+  int64_t stride;
+  const uint32_t* epoch_ptr;
+  uint32_t epoch_add;
+  uint64_t wait_ns;
+  const __nv_bfloat16* residual;  // optional [n, d]
+  const float* norm_w;            // optional [d]: out = rmsnorm(sum + residual) * w
+  float eps;
+  __nv_bfloat16* out_sum;         // optional: sum + residual (the new residual stream)
+  __nv_bfloat16* out;             // normalised (or plain sum when norm_w is null)
+  uint8_t* out_q;                 // optional FP8 re-quantisation of `out` for the next GEMM, [n, d]
+  uint8_t* out_atom;              //   its scale atoms (rows = tokens, d / 32 k-blocks)
+  Status* status;
+};
+
+// one block per token row, 256 threads; thread t owns columns t, t + 256, ... so a warp covers 32 consecutive columns
+__global__ void __launch_bounds__(256) fold_slots_kernel(FoldArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  __shared__ int ok;
+  const int row = blockIdx.x;
+  if (threadIdx.x == 0) {
+    ok = 1;
+    if (a.flag[0]) {
+      const uint32_t want = *a.epoch_ptr + a.epoch_add;
+      for (int r = 0; r < a.W; ++r)
+        if (!wait_flag_ge(a.flag[r], want, a.wait_ns)) { ok = 0; status_set(a.status, ST_TIMEOUT, 40, r, row); break; }
+    }
+  }
+  __syncthreads();
+  if (!ok) return;
+  float vals[24];                 // d <= 6144
+  float ss = 0.f;
+  int cnt = 0;
+  for (int c = threadIdx.x; c < a.d; c += 256, ++cnt) {
+    float s = 0.f;
+    for (int r = 0; r < a.W; ++r) s += __bfloat162float(a.slot[r][(int64_t)row * a.stride + c]);   // rank order
+    if (a.residual) s += __bfloat162float(a.residual[(int64_t)row * a.d + c]);
+    if (a.out_sum) a.out_sum[(int64_t)row * a.d + c] = __float2bfloat16_rn(s);
+    vals[cnt] = s;
+    ss += s * s;
+  }
+  float scale = 1.f;
+  if (a.norm_w) scale = rsqrtf(block_sum(ss, red) / (float)a.d + a.eps);
+  cnt = 0;
+  for (int c = threadIdx.x; c < a.d; c += 256, ++cnt) {
+    const float y = a.norm_w ? vals[cnt] * scale * a.norm_w[c] : vals[cnt];
+    const __nv_bfloat16 yb = __float2bfloat16_rn(y);
+    a.out[(int64_t)row * a.d + c] = yb;
+    if (a.out_q) {
+      uint8_t sc;
+      const uint8_t code = warp_quant_fp8(__bfloat162float(yb), &sc);
+      a.out_q[(int64_t)row * a.d + c] = code;
+      if ((threadIdx.x & 31) == 0) a.out_atom[sf_offset(row, c >> 5, a.d >> 5)] = sc;
+    }
+  }
+}
+
 }  // namespace sfb
 
 using namespace sfb;
@@ -90,6 +154,19 @@ int sfb_push_rows(const void* src, const void* const* dst_ptrs, const void* cons
   if (blocks > 64) blocks = 64;
   if (blocks < 1) blocks = 1;
   return (int)sfb_launch(push_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, a);
+}
+
+// slots / flags: host arrays of W device addresses (flags may be null: no waiting)
+int sfb_fold_slots(const void* const* slots, const void* const* flags, int W, int n, int d, int64_t stride, const void* epoch_ptr,
+                   uint32_t epoch_add, uint64_t wait_ns, const void* residual, const void* norm_w, float eps, void* out_sum,
+                   void* out, void* out_q, void* out_atom, void* status, cudaStream_t stream) {
+  if (W < 1 || W > 8 || d > 24 * 256 || d % 32 || n < 1) return (int)cudaErrorInvalidValue;
+  FoldArgs a{};
+  for (int r = 0; r < W; ++r) { a.slot[r] = (const __nv_bfloat16*)slots[r]; a.flag[r] = flags ? (const uint32_t*)flags[r] : nullptr; }
+  a.W = W; a.n = n; a.d = d; a.stride = stride; a.epoch_ptr = (const uint32_t*)epoch_ptr; a.epoch_add = epoch_add; a.wait_ns = wait_ns;
+  a.residual = (const __nv_bfloat16*)residual; a.norm_w = (const float*)norm_w; a.eps = eps; a.out_sum = (__nv_bfloat16*)out_sum;
+  a.out = (__nv_bfloat16*)out; a.out_q = (uint8_t*)out_q; a.out_atom = (uint8_t*)out_atom; a.status = (Status*)status;
+  return (int)sfb_launch(fold_slots_kernel, dim3(n), dim3(256), 0, stream, a);
 }
 
 int sfb_epoch_bump(void* epoch, uint32_t add, cudaStream_t stream) {

@@ -164,6 +164,12 @@ struct UmmaArgs {
   const uint32_t* epoch_ptr;  // flag value = *epoch_ptr + epoch_add
   uint32_t epoch_add;
   unsigned int* done_counter; // zero between launches
+  // bulk shapes and the other fused collectives (dense mode, template flag BULK)
+  int tok_tiles;              // > 1: blockIdx.z = group * tok_tiles + token tile (NP must be 128)
+  const CUtensorMap* b_maps;  // all-gather -> GEMM: activations sharded along K over the ranks; map r covers k in
+  int b_k_per_map;            //   [r * b_k_per_map, (r+1) * b_k_per_map) and may point into rank r's memory
+  const uint8_t* sfb_maps[8]; //   scale atoms of each shard (katoms = b_k_per_map / 128 per row block)
+  int rs_rows;                // GEMM -> reduce-scatter: token row t goes only to rank t / rs_rows, at row t % rs_rows
   uint8_t* out_q;             // optional: the bf16-rounded output re-quantised per 32 columns (E4M3)
   uint8_t* out_q_atom;        //           and its scale atoms (rows = tokens, kb = out_stride/32)
   // MoE
@@ -206,7 +212,7 @@ struct UmmaWork {
   int out_row0, n_valid, col0, col_limit;
 };
 
-template <int NP>
+template <int NP, bool BULK>
 __global__ void __launch_bounds__(UM_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
                  const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
@@ -234,8 +240,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   tc_fence_after();
   pdl_wait();   // everything above is set-up; operands written by the previous kernel are read below
   UmmaWork w;
+  int tok_tile = 0;
   if (a.mode == UM_DENSE) {
-    const int tile = blockIdx.x, g = blockIdx.z;
+    const int tile = blockIdx.x;
+    int g = blockIdx.z;
+    if (BULK) { tok_tile = blockIdx.z % a.tok_tiles; g = blockIdx.z / a.tok_tiles; }
     const int ksteps = (a.K + UM_BK - 1) / UM_BK;
     w.ma = &tmapA; w.a_fp4 = a.a_fp4;
     w.a_row0 = g * a.N + tile * 128;
@@ -247,6 +256,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     w.split = blockIdx.y; w.splits = a.splits;
     w.tile_id = g * gridDim.x + tile; w.tiles_total = gridDim.x * gridDim.z;
     w.out_row0 = 0; w.n_valid = a.n; w.col0 = w.a_row0; w.col_limit = (g + 1) * a.N;
+    if (BULK) {
+      w.b_row0 = tok_tile * NP; w.out_row0 = tok_tile * NP;
+      w.n_valid = min(NP, a.n - tok_tile * NP);
+      w.sfb = a.sfb + ((size_t)((tok_tile * NP) >> 7) * a.katoms_b + g * ksteps + w.ks0) * 512;
+    }
   } else {  // UM_DOWN: x = column tile of d, y = slot, z = token
     const int tile = blockIdx.x, slot = blockIdx.y, tok = blockIdx.z;
     const int ksteps = (a.inter + UM_BK - 1) / UM_BK;
@@ -281,9 +295,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         if (i >= UM_STAGES && !mbar_wait(&S.empty[s], ((i / UM_STAGES) - 1) & 1)) { S.fail = 1; break; }
         mbar_expect_tx(&S.full[s], STAGE_TX);
         tma_load_2d(S.a[s][0], w.ma, (w.ks0 + i) * UM_BK, w.a_row0, &S.full[s]);
-        tma_load_2d(S.b[s], &tmapB, w.b_x0 + i * UM_BK, w.b_row0, &S.full[s]);
+        if (BULK && a.b_maps) {
+          // the k-slab lives on the rank that owns this range of the hidden dimension: a plain (non-multicast)
+          // TMA load from that rank's memory, and its scale atoms with a bulk copy
+          const int k = (w.ks0 + i) * UM_BK, owner = k / a.b_k_per_map, kl = k - owner * a.b_k_per_map;
+          tma_load_2d(S.b[s], &a.b_maps[owner], kl, w.b_row0, &S.full[s]);
+          bulk_load(S.sfb[s], a.sfb_maps[owner] + ((size_t)(w.b_row0 >> 7) * (a.b_k_per_map / UM_BK) + kl / UM_BK) * 512, 512, &S.full[s]);
+        } else {
+          tma_load_2d(S.b[s], &tmapB, w.b_x0 + i * UM_BK, w.b_row0, &S.full[s]);
+          bulk_load(S.sfb[s], w.sfb + (size_t)i * 512, 512, &S.full[s]);
+        }
         bulk_load(S.sfa[s][0], w.sfa + (size_t)i * 512, 512, &S.full[s]);
-        bulk_load(S.sfb[s], w.sfb + (size_t)i * 512, 512, &S.full[s]);
       }
     }
   } else if (warp == 1) {
@@ -337,7 +359,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
               const __nv_bfloat16 fb = __float2bfloat16_rn(f);
               if (a.out_b) a.out_b[o] = fb;
               if (a.out_f) a.out_f[o] = f;
-              for (int pr = 0; pr < a.n_peers; ++pr) a.peer_out[pr][o] = fb;
+              if (BULK && a.rs_rows > 0) {
+                const int row = w.out_row0 + tok, pr = row / a.rs_rows;
+                a.peer_out[pr][(int64_t)(row - pr * a.rs_rows) * a.out_stride + col] = fb;
+              } else {
+                for (int pr = 0; pr < a.n_peers; ++pr) a.peer_out[pr][o] = fb;
+              }
             }
             if (a.out_q) {
               uint8_t sc;
@@ -382,7 +409,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             const __nv_bfloat16 sb = __float2bfloat16_rn(s);
             if (a.out_b) a.out_b[o] = sb;
             if (a.out_f) a.out_f[o] = s;
-            for (int pr = 0; pr < a.n_peers; ++pr) a.peer_out[pr][o] = sb;
+            if (BULK && a.rs_rows > 0) {
+              const int row = w.out_row0 + tok, pr = row / a.rs_rows;
+              a.peer_out[pr][(int64_t)(row - pr * a.rs_rows) * a.out_stride + col] = sb;
+            } else {
+              for (int pr = 0; pr < a.n_peers; ++pr) a.peer_out[pr][o] = sb;
+            }
           }
           if (a.out_q) {
             uint8_t sc;
@@ -565,6 +597,18 @@ static EncodeTiledFn get_encode() {
 
 using namespace sfb;
 
+template <int NPV, bool BULK>
+static cudaError_t launch_umma_t(const CUtensorMap* mA, const CUtensorMap* mA2, const CUtensorMap* mB, const UmmaArgs& a, dim3 grid,
+                                 cudaStream_t stream) {
+  const size_t smem = sizeof(UmmaSmem<NPV, 1, (NPV <= 32 ? UM_STAGES_DENSE : UM_STAGES_WIDE)>) + 1024;
+  static bool done = false;
+  if (!done) {
+    cudaFuncSetAttribute(umma_gemm_kernel<NPV, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    done = true;
+  }
+  return sfb_launch(umma_gemm_kernel<NPV, BULK>, grid, dim3(UM_THREADS), smem, stream, *mA, *mA2, *mB, a);
+}
+
 extern "C" {
 
 // Encode a 2-D K-major tensor map with a 128-byte swizzled box of `box_rows` rows x 128 K elements.
@@ -611,16 +655,9 @@ static int launch_umma(const void* tmapA, const void* tmapA2, const void* tmapB,
   cudaError_t launch_rc = cudaSuccess;
   UmmaArgs a = a_in;
   apply_push(a);
-#define SFB_UM(NPV)                                                                                           \
-  {                                                                                                           \
-    const size_t smem = sizeof(UmmaSmem<NPV, 1, (NPV <= 32 ? UM_STAGES_DENSE : UM_STAGES_WIDE)>) + 1024;                                                      \
-    static bool done = false;                                                                                 \
-    if (!done) {                                                                                              \
-      cudaFuncSetAttribute(umma_gemm_kernel<NPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-      done = true;                                                                                            \
-    }                                                                                                         \
-    launch_rc = sfb_launch(umma_gemm_kernel<NPV>, grid, dim3(UM_THREADS), smem, stream, *mA, *mA2, *mB, a);   \
-  }
+const bool bulk = a.tok_tiles > 1 || a.b_maps != nullptr || a.rs_rows > 0;
+  if (a.tok_tiles < 1) a.tok_tiles = 1;
+#define SFB_UM(NPV) { launch_rc = bulk ? launch_umma_t<NPV, true>(mA, mA2, mB, a, grid, stream) : launch_umma_t<NPV, false>(mA, mA2, mB, a, grid, stream); }
   if (NP == 16) SFB_UM(16) else if (NP == 32) SFB_UM(32) else if (NP == 64) SFB_UM(64) else if (NP == 128) SFB_UM(128)
   else return (int)cudaErrorInvalidValue;
 #undef SFB_UM
@@ -652,6 +689,29 @@ int sfb_umma_dense(const void* tmapA, const void* tmapB, const void* sfa, int ka
   a.scratch = scratch; a.tickets = tickets; a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f;
   a.out_stride = out_stride; a.status = (Status*)status;
   return launch_umma(tmapA, nullptr, tmapB, a, dim3((N + 127) / 128, splits, groups), NP, stream);
+}
+
+// Bulk GEMM with the fused-collective options: any number of token rows (tiles of NP = 128 when n > 128),
+//   b_maps != null : all-gather -> GEMM.  Activations are sharded along K; device array of n_maps tensor maps, map r
+//                    = rank r's [rows, b_k_per_map] shard (peer memory is read with plain TMA loads), sfb_maps[r] its atoms
+//   rs_rows > 0    : GEMM -> reduce-scatter.  With sfb_umma_set_push armed, token row t is stored only to rank t / rs_rows
+//   (push armed, rs_rows == 0: GEMM -> all-reduce, every rank receives the whole partial)
+int sfb_umma_bulk(const void* tmapA, const void* tmapB, const void* sfa, int katoms_a, const void* sfb, int katoms_b, int n,
+                  int NP, int N, int K, int splits, float* scratch, unsigned int* tickets, void* out_b, float* out_f,
+                  int64_t out_stride, const void* b_maps, int b_k_per_map, const void* const* sfb_maps, int n_maps,
+                  int rs_rows, void* status, cudaStream_t stream) {
+  const int tok_tiles = (n + NP - 1) / NP;
+  if (K % UM_BK || splits < 1 || splits > K / UM_BK || n < 1 || (tok_tiles > 1 && NP != 128)) return (int)cudaErrorInvalidValue;
+  if (splits > 1 && (!scratch || !tickets)) return (int)cudaErrorInvalidValue;
+  if (b_maps && (n_maps < 1 || n_maps > 8 || b_k_per_map % UM_BK || b_k_per_map * n_maps != K)) return (int)cudaErrorInvalidValue;
+  UmmaArgs a{};
+  a.sfa = (const uint8_t*)sfa; a.katoms_a = katoms_a; a.sfb = (const uint8_t*)sfb; a.katoms_b = katoms_b;
+  a.n = n; a.K = K; a.mode = UM_DENSE; a.N = N; a.groups = 1; a.splits = splits; a.scratch = scratch; a.tickets = tickets;
+  a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f; a.out_stride = out_stride; a.status = (Status*)status;
+  a.tok_tiles = tok_tiles; a.b_maps = (const CUtensorMap*)b_maps; a.b_k_per_map = b_k_per_map; a.rs_rows = rs_rows;
+  for (int i = 0; i < n_maps && b_maps; ++i) a.sfb_maps[i] = (const uint8_t*)sfb_maps[i];
+  const int rc = launch_umma(tmapA, nullptr, tmapB ? tmapB : tmapA, a, dim3((N + 127) / 128, splits, tok_tiles), NP, stream);
+  return rc;
 }
 
 // Same with two-term activations (see k_quant.cu): rows [0, pair) are the hi terms, [pair, 2*pair) the lo terms.

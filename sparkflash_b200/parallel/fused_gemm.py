@@ -1,0 +1,223 @@
+"""Fused GEMM + collective operators on the tcgen05 block-scaled GEMM (csrc/k_umma.cu) and the symmetric heap.
+
+* ``RowParallelLinear`` (GEMM -> all-reduce or reduce-scatter): every rank multiplies its K-shard; the GEMM
+  epilogue stores the bf16 partial tile by tile straight into the consumer's slot over NVLink (all ranks for
+  all-reduce, only the owner of the token row for reduce-scatter) and raises an arrival flag when its last tile is
+  out; the consumer kernel waits on its own flags with a time limit and folds the slots in rank order in fp32,
+  adds the residual, applies RMSNorm and re-quantises for the next GEMM.
+* ``ColumnParallelLinear`` (all-gather -> GEMM): activations are sharded along the hidden dimension (the output
+  layout of the reduce-scatter above, transposed roles); the GEMM's TMA producer reads each K-slab directly from
+  the rank that owns it (plain loads from peer memory, no multicast), so the gather overlaps the MMAs slab by
+  slab and no gathered copy is ever materialised.
+
+Waits are bounded; buffers are double-buffered by step parity, which orders re-use without extra handshakes:
+a rank that passed step i's wait knows every peer finished step i-1.
+Reference behaviour replaced: crates/sparkflash-comm/src/device_reduce.rs:693-1082 (RunReduce all-reduce /
+reduce-scatter / all-gather around cuBLAS-free GEMMs), tp4_forward.rs reduce_rows:13112, SP prefill seams.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_uint32, c_uint64, c_void_p
+
+import torch
+
+from .. import _lib, codecs as C
+from ..ops import native as N
+from .symm import SymmHeap
+
+
+def _L():
+    return _lib.cuda()
+
+
+def _maps_device(maps: list[N.TensorMap]) -> torch.Tensor:
+    """W tensor maps copied into one 64-byte aligned device buffer."""
+    raw = bytearray()
+    for m in maps:
+        raw += ctypes.string_at(m.ptr, 128)
+    buf = torch.empty((len(raw) + 64,), dtype=torch.uint8, device="cuda")
+    off = (-buf.data_ptr()) % 64
+    view = buf[off:off + len(raw)]
+    view.copy_(torch.frombuffer(raw, dtype=torch.uint8))
+    view._keep = buf
+    return view
+
+
+def tensor_map_at(addr: int, rows: int, K: int, box_rows: int) -> N.TensorMap:
+    class _Addr:
+        def __init__(self, a): self._a = a
+        def data_ptr(self): return self._a
+    return N.TensorMap(_Addr(addr), rows, K, K, box_rows)
+
+
+class _Base:
+    def __init__(self, heap: SymmHeap, M: int, wait_ns: int = 1_000_000_000):
+        self.heap, self.rank, self.world, self.M = heap, heap.rank, heap.world, M
+        self.wait_ns = wait_ns
+        self.step = 0
+        self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        self.epoch = torch.zeros(1, dtype=torch.int32, device="cuda")     # incremented on the device every step
+
+    def _bump(self):
+        N._check(_L().sfb_epoch_bump(N._p(self.epoch), c_uint32(1), N._stream()), "epoch_bump")
+
+    def check(self):
+        st = self.status.tolist()
+        if st[0]:
+            raise RuntimeError(f"fused collective: device status code={st[0]} where={st[1]} detail=({st[2]}, {st[3]})")
+
+
+class RowParallelLinear(_Base):
+    """y = sum_r x_r @ W_r^T over ranks; ``mode`` "ar" (every rank gets all M rows) or "rs" (rank r gets rows
+    [r*M/W, (r+1)*M/W)).  Weight shard: FP8 codes [N, K/W] with UE8M0 scales per 32x32 block [N/32, K/W/32] (the checkpoint's form)."""
+
+    def __init__(self, heap: SymmHeap, w_q: torch.Tensor, w_sf: torch.Tensor, M: int, mode: str = "ar", heap_offset: int = 0,
+                 norm_w: torch.Tensor | None = None, eps: float = 1e-6, **kw):
+        super().__init__(heap, M, **kw)
+        self.N, self.Kl = w_q.shape
+        self.mode = mode
+        W = self.world
+        if mode == "rs" and M % W:
+            raise ValueError("reduce-scatter needs M divisible by the world size")
+        self.rows_out = M // W if mode == "rs" else M
+        self.w_q = w_q
+        self.w_atoms = C.scales_to_prepared(w_sf, self.N, 32).cuda()
+        self.tmap_a = N.TensorMap(w_q, self.N, self.Kl, self.Kl, 128)
+        self.NP = N.umma_np(min(M, 128))
+        Mp = max(self.NP, (M + 127) // 128 * 128)
+        self.x_q = torch.zeros((Mp, self.Kl), dtype=torch.uint8, device="cuda")
+        self.x_atom = torch.full((C.sf_bytes(Mp, self.Kl // 32),), 127, dtype=torch.uint8, device="cuda")
+        self.tmap_b = N.TensorMap(self.x_q, Mp, self.Kl, self.Kl, self.NP)
+        # symmetric layout: [2 parities][W slots][rows_out, N] bf16 | flags [2][W] u32 | done u32
+        self.slot_bytes = self.rows_out * self.N * 2
+        self.off_slots = heap_offset
+        self.off_flags = heap_offset + 2 * W * self.slot_bytes
+        self.off_done = self.off_flags + 2 * 256
+        self.bytes = self.off_done + 256 - heap_offset
+        tiles = ((self.N + 127) // 128) * ((M + self.NP - 1) // self.NP)
+        ksteps = self.Kl // 128
+        self.splits = max(1, min(ksteps, 296 // max(1, tiles))) if M <= 128 else 1
+        self.scratch = torch.zeros((tiles * self.splits * 128 * self.NP,), dtype=torch.float32, device="cuda") if self.splits > 1 else None
+        self.tickets = torch.zeros((max(tiles, 1),), dtype=torch.int32, device="cuda")
+        self.norm_w, self.eps = norm_w, eps
+        self.out = torch.empty((self.rows_out, self.N), dtype=torch.bfloat16, device="cuda")
+        self.out_sum = torch.empty_like(self.out)
+
+    @staticmethod
+    def heap_bytes(M: int, Nn: int, W: int, mode: str) -> int:
+        rows = M // W if mode == "rs" else M
+        return 2 * W * rows * Nn * 2 + 2 * 256 + 256
+
+    def _slot(self, base: int, parity: int, r: int) -> int:
+        return base + self.off_slots + (parity * self.world + r) * self.slot_bytes
+
+    def _flag(self, base: int, parity: int, r: int) -> int:
+        return base + self.off_flags + parity * 256 + r * 4
+
+    def produce(self, x: torch.Tensor) -> None:
+        """x bf16 [M, K/W]: quantise, multiply, push the partial to the consumers, raise the flags."""
+        self.step += 1
+        par = self.step & 1
+        self._bump()
+        N.quant_rows(x, self.x_q, None, self.x_atom, self.M, self.Kl)
+        h = self.heap
+        outs = [self._slot(b, par, self.rank) for b in h.bases]
+        flags = [self._flag(b, par, self.rank) for b in h.bases]
+        N._check(_L().sfb_umma_set_push(N._ptr_array(outs), N._ptr_array(flags), c_int(self.world), N._p(self.epoch), c_uint32(0),
+                                        c_void_p(h.base + self.off_done)), "umma_set_push")
+        N._check(_L().sfb_umma_bulk(c_void_p(self.tmap_a.ptr), c_void_p(self.tmap_b.ptr), N._p(self.w_atoms), c_int(self.Kl // 128),
+                                    N._p(self.x_atom), c_int(self.Kl // 128), c_int(self.M), c_int(self.NP), c_int(self.N), c_int(self.Kl),
+                                    c_int(self.splits), N._p(self.scratch), N._p(self.tickets), None, None, c_int64(self.N), None, c_int(0),
+                                    None, c_int(0), c_int(self.rows_out if self.mode == "rs" else 0), N._p(self.status), N._stream()), "umma_bulk")
+
+    def consume(self, residual: torch.Tensor | None = None, out_q: torch.Tensor | None = None, out_atom: torch.Tensor | None = None) -> torch.Tensor:
+        par = self.step & 1
+        b = self.heap.base
+        slots = [self._slot(b, par, r) for r in range(self.world)]
+        flags = [self._flag(b, par, r) for r in range(self.world)]
+        N._check(_L().sfb_fold_slots(N._ptr_array(slots), N._ptr_array(flags), c_int(self.world), c_int(self.rows_out), c_int(self.N),
+                                     c_int64(self.N), N._p(self.epoch), c_uint32(0), c_uint64(self.wait_ns), N._p(residual), N._p(self.norm_w),
+                                     c_float(self.eps), N._p(self.out_sum), N._p(self.out), N._p(out_q), N._p(out_atom), N._p(self.status),
+                                     N._stream()), "fold_slots")
+        return self.out
+
+    def forward(self, x, residual=None):
+        self.produce(x)
+        return self.consume(residual)
+
+
+class ColumnParallelLinear(_Base):
+    """y_r = x @ W_r^T with x [M, K] held as W shards along K, one per rank, in symmetric memory (FP8 + atoms).
+    Weight shard: FP8 codes [N/W, K] with UE8M0 scales per 32x32 block."""
+
+    def __init__(self, heap: SymmHeap, w_q: torch.Tensor, w_sf: torch.Tensor, M: int, heap_offset: int = 0, **kw):
+        super().__init__(heap, M, **kw)
+        self.Nl, self.K = w_q.shape
+        W = self.world
+        self.Kl = self.K // W
+        if self.Kl % 128:
+            raise ValueError("K / world must be a multiple of 128")
+        self.w_q = w_q
+        self.w_atoms = C.scales_to_prepared(w_sf, self.Nl, 32).cuda()
+        self.tmap_a = N.TensorMap(w_q, self.Nl, self.K, self.K, 128)
+        self.NP = N.umma_np(min(M, 128))
+        self.Mp = max(self.NP, (M + 127) // 128 * 128)
+        self.xq_bytes = self.Mp * self.Kl
+        self.atom_bytes = (C.sf_bytes(self.Mp, self.Kl // 32) + 255) // 256 * 256
+        # symmetric layout: [2 parities] (x_q shard | atoms) | flags [2][W] | dummy 16 B | done
+        self.off_x = heap_offset
+        self.off_flags = heap_offset + 2 * (self.xq_bytes + self.atom_bytes)
+        self.off_dummy = self.off_flags + 2 * 256
+        self.off_done = self.off_dummy + 256
+        self.bytes = self.off_done + 256 - heap_offset
+        h = heap
+        self.maps, self.sfb_ptrs, self.local_q, self.local_atom = [], [], [], []
+        for par in range(2):
+            ms = [tensor_map_at(b + self.off_x + par * (self.xq_bytes + self.atom_bytes), self.Mp, self.Kl, self.NP) for b in h.bases]
+            self._keep_maps = getattr(self, "_keep_maps", []) + ms
+            self.maps.append(_maps_device(ms))
+            self.sfb_ptrs.append([b + self.off_x + par * (self.xq_bytes + self.atom_bytes) + self.xq_bytes for b in h.bases])
+            self.local_q.append(h.view(self.off_x + par * (self.xq_bytes + self.atom_bytes), (self.Mp, self.Kl), torch.uint8))
+            self.local_atom.append(h.view(self.off_x + par * (self.xq_bytes + self.atom_bytes) + self.xq_bytes, (self.atom_bytes,), torch.uint8))
+            self.local_atom[-1].fill_(127)
+        tiles = ((self.Nl + 127) // 128) * ((M + self.NP - 1) // self.NP)
+        ksteps = self.K // 128
+        self.splits = max(1, min(ksteps, 296 // max(1, tiles))) if M <= 128 else 1
+        self.scratch = torch.zeros((tiles * self.splits * 128 * self.NP,), dtype=torch.float32, device="cuda") if self.splits > 1 else None
+        self.tickets = torch.zeros((max(tiles, 1),), dtype=torch.int32, device="cuda")
+        self.out = torch.empty((M, self.Nl), dtype=torch.bfloat16, device="cuda")
+        self.flag_ptrs = [torch.tensor([b_ + self.off_flags + par * 256 + r * 4 for r in range(W)], dtype=torch.int64, device="cuda")
+                          for par in range(2) for b_ in [h.base]]
+        self._dummy = torch.zeros(16, dtype=torch.uint8, device="cuda")
+
+    @staticmethod
+    def heap_bytes(M: int, K: int, W: int) -> int:
+        Mp = max(16, (M + 127) // 128 * 128)
+        return 2 * (Mp * (K // W) + (C.sf_bytes(Mp, K // W // 32) + 255) // 256 * 256) + 2 * 256 + 512
+
+    def publish(self, x_shard: torch.Tensor) -> None:
+        """x_shard bf16 [M, K/W]: quantise into this rank's symmetric shard and tell every rank it is there."""
+        self.step += 1
+        par = self.step & 1
+        self._bump()
+        N.quant_rows(x_shard, self.local_q[par], None, self.local_atom[par], self.M, self.Kl)
+        h = self.heap
+        dst = [b + self.off_dummy for b in h.bases]
+        flags = [b + self.off_flags + par * 256 + self.rank * 4 for b in h.bases]
+        N._check(_L().sfb_push_rows(N._p(self._dummy), N._ptr_array(dst), N._ptr_array(flags), c_int(self.world), c_int64(16), N._p(self.epoch),
+                                    c_uint32(0), c_void_p(h.base + self.off_done), N._stream()), "push_rows")
+
+    def gemm(self) -> torch.Tensor:
+        par = self.step & 1
+        N._check(_L().sfb_wait_flags(N._p(self.flag_ptrs[par]), c_int(self.world), N._p(self.epoch), c_uint32(0), c_uint64(self.wait_ns),
+                                     N._p(self.status), N._stream()), "wait_flags")
+        N._check(_L().sfb_umma_bulk(c_void_p(self.tmap_a.ptr), None, N._p(self.w_atoms), c_int(self.K // 128), None, c_int(self.Kl // 128),
+                                    c_int(self.M), c_int(self.NP), c_int(self.Nl), c_int(self.K), c_int(self.splits), N._p(self.scratch),
+                                    N._p(self.tickets), N._p(self.out), None, c_int64(self.Nl), N._p(self.maps[par]), c_int(self.Kl),
+                                    N._ptr_array(self.sfb_ptrs[par]), c_int(self.world), c_int(0), N._p(self.status), N._stream()), "umma_bulk")
+        return self.out
+
+    def forward(self, x_shard):
+        self.publish(x_shard)
+        return self.gemm()
