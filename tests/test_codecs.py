@@ -118,3 +118,9 @@ def test_weight_quant_and_prepared_scales():
 def test_sf_atom_layout_is_a_bijection():
     off = C.sf_offsets(256, 8).flatten()
     assert off.unique().numel() == off.numel() and int(off.max()) < C.sf_bytes(256, 8)
+
+
+def test_mla_v3_cached_engine_matches_the_fp32_oracle():
+    from sparkflash_b200.models import mla_v3
+    r = mla_v3.run(n_new=6, prompt_len=12)
+    assert r["max_abs_logit_err_vs_fp32_oracle"] < 1e-4 and r["argmax_agree"] == "6/6"
