@@ -75,8 +75,9 @@ struct FoldArgs {
   Status* status;
 };
 
-// one block per token row, 256 threads; thread t owns columns t, t + 256, ... so a warp covers 32 consecutive columns
-__global__ void __launch_bounds__(256) fold_slots_kernel(FoldArgs a) {
+// one block per token row, 128 threads; a thread owns 8 consecutive columns per pass (16-byte loads), so four lanes
+// hold one 32-column scale group
+__global__ void __launch_bounds__(128) fold_slots_kernel(FoldArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[32];
@@ -92,29 +93,64 @@ __global__ void __launch_bounds__(256) fold_slots_kernel(FoldArgs a) {
   }
   __syncthreads();
   if (!ok) return;
-  float vals[24];                 // d <= 6144
+  constexpr int PASS = 6;          // d <= 6 * 1024
+  float vals[PASS][8];
   float ss = 0.f;
-  int cnt = 0;
-  for (int c = threadIdx.x; c < a.d; c += 256, ++cnt) {
-    float s = 0.f;
-    for (int r = 0; r < a.W; ++r) s += __bfloat162float(a.slot[r][(int64_t)row * a.stride + c]);   // rank order
-    if (a.residual) s += __bfloat162float(a.residual[(int64_t)row * a.d + c]);
-    if (a.out_sum) a.out_sum[(int64_t)row * a.d + c] = __float2bfloat16_rn(s);
-    vals[cnt] = s;
-    ss += s * s;
+#pragma unroll
+  for (int p = 0; p < PASS; ++p) {
+    const int c = (p * 128 + threadIdx.x) * 8;
+    if (c >= a.d) break;
+    float s8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < a.W; ++r) {      // rank order
+      const uint4 u = *reinterpret_cast<const uint4*>(a.slot[r] + (int64_t)row * a.stride + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); s8[2 * j] += f.x; s8[2 * j + 1] += f.y; }
+    }
+    if (a.residual) {
+      const uint4 u = *reinterpret_cast<const uint4*>(a.residual + (int64_t)row * a.d + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); s8[2 * j] += f.x; s8[2 * j + 1] += f.y; }
+    }
+    if (a.out_sum) {
+      uint4 o;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(s8[2 * j], s8[2 * j + 1]);
+      *reinterpret_cast<uint4*>(a.out_sum + (int64_t)row * a.d + c) = o;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { vals[p][j] = s8[j]; ss += s8[j] * s8[j]; }
   }
   float scale = 1.f;
   if (a.norm_w) scale = rsqrtf(block_sum(ss, red) / (float)a.d + a.eps);
-  cnt = 0;
-  for (int c = threadIdx.x; c < a.d; c += 256, ++cnt) {
-    const float y = a.norm_w ? vals[cnt] * scale * a.norm_w[c] : vals[cnt];
-    const __nv_bfloat16 yb = __float2bfloat16_rn(y);
-    a.out[(int64_t)row * a.d + c] = yb;
+#pragma unroll
+  for (int p = 0; p < PASS; ++p) {
+    const int c = (p * 128 + threadIdx.x) * 8;
+    if (c >= a.d) break;
+    float y[8];
+    uint4 o;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = a.norm_w ? vals[p][j] * scale * a.norm_w[c + j] : vals[p][j];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+    *reinterpret_cast<uint4*>(a.out + (int64_t)row * a.d + c) = o;
     if (a.out_q) {
-      uint8_t sc;
-      const uint8_t code = warp_quant_fp8(__bfloat162float(yb), &sc);
-      a.out_q[(int64_t)row * a.d + c] = code;
-      if ((threadIdx.x & 31) == 0) a.out_atom[sf_offset(row, c >> 5, a.d >> 5)] = sc;
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { y[j] = bfr(y[j]); amax = fmaxf(amax, fabsf(y[j])); }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const uint8_t sc = act_scale_code_fp8(amax);
+      const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+      uint2 qv;
+      uint8_t* qb = reinterpret_cast<uint8_t*>(&qv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qb[j] = enc_e4m3(y[j] * inv);
+      *reinterpret_cast<uint2*>(a.out_q + (int64_t)row * a.d + c) = qv;
+      if ((threadIdx.x & 3) == 0) a.out_atom[sf_offset(row, c >> 5, a.d >> 5)] = sc;
     }
   }
 }
@@ -160,13 +196,13 @@ int sfb_push_rows(const void* src, const void* const* dst_ptrs, const void* cons
 int sfb_fold_slots(const void* const* slots, const void* const* flags, int W, int n, int d, int64_t stride, const void* epoch_ptr,
                    uint32_t epoch_add, uint64_t wait_ns, const void* residual, const void* norm_w, float eps, void* out_sum,
                    void* out, void* out_q, void* out_atom, void* status, cudaStream_t stream) {
-  if (W < 1 || W > 8 || d > 24 * 256 || d % 32 || n < 1) return (int)cudaErrorInvalidValue;
+  if (W < 1 || W > 8 || d > 6 * 1024 || d % 32 || n < 1 || (stride & 7)) return (int)cudaErrorInvalidValue;
   FoldArgs a{};
   for (int r = 0; r < W; ++r) { a.slot[r] = (const __nv_bfloat16*)slots[r]; a.flag[r] = flags ? (const uint32_t*)flags[r] : nullptr; }
   a.W = W; a.n = n; a.d = d; a.stride = stride; a.epoch_ptr = (const uint32_t*)epoch_ptr; a.epoch_add = epoch_add; a.wait_ns = wait_ns;
   a.residual = (const __nv_bfloat16*)residual; a.norm_w = (const float*)norm_w; a.eps = eps; a.out_sum = (__nv_bfloat16*)out_sum;
   a.out = (__nv_bfloat16*)out; a.out_q = (uint8_t*)out_q; a.out_atom = (uint8_t*)out_atom; a.status = (Status*)status;
-  return (int)sfb_launch(fold_slots_kernel, dim3(n), dim3(256), 0, stream, a);
+  return (int)sfb_launch(fold_slots_kernel, dim3(n), dim3(128), 0, stream, a);
 }
 
 int sfb_epoch_bump(void* epoch, uint32_t add, cudaStream_t stream) {

@@ -72,6 +72,14 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+// shared -> global bulk copy (works for peer memory too); completion is tracked by the thread's bulk group
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_store_commit_wait() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
 }
@@ -169,6 +177,7 @@ struct UmmaArgs {
   const CUtensorMap* b_maps;  // all-gather -> GEMM: activations sharded along K over the ranks; map r covers k in
   int b_k_per_map;            //   [r * b_k_per_map, (r+1) * b_k_per_map) and may point into rank r's memory
   const uint8_t* sfb_maps[8]; //   scale atoms of each shard (katoms = b_k_per_map / 128 per row block)
+  int force_bulk;             // entry point for bulk shapes: always the staged-epilogue instantiation
   int rs_rows;                // GEMM -> reduce-scatter: token row t goes only to rank t / rs_rows, at row t % rs_rows
   uint8_t* out_q;             // optional: the bf16-rounded output re-quantised per 32 columns (E4M3)
   uint8_t* out_q_atom;        //           and its scale atoms (rows = tokens, kb = out_stride/32)
@@ -217,7 +226,8 @@ __global__ void __launch_bounds__(UM_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
                  const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
   extern __shared__ uint8_t smem_raw[];
-  constexpr int UM_STAGES = NP <= 32 ? UM_STAGES_DENSE : UM_STAGES_WIDE;
+  // bulk tiles of 128 tokens run two CTAs per SM (3 stages = 99 KiB each): one CTA's epilogue hides behind the other's mainloop
+  constexpr int UM_STAGES = NP <= 32 ? UM_STAGES_DENSE : ((BULK && NP == 128) ? 3 : UM_STAGES_WIDE);
   using Smem = UmmaSmem<NP, 1, UM_STAGES>;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -241,6 +251,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   pdl_wait();   // everything above is set-up; operands written by the previous kernel are read below
   UmmaWork w;
   int tok_tile = 0;
+  bool skip = false;
   if (a.mode == UM_DENSE) {
     const int tile = blockIdx.x;
     int g = blockIdx.z;
@@ -265,7 +276,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     const int tile = blockIdx.x, slot = blockIdx.y, tok = blockIdx.z;
     const int ksteps = (a.inter + UM_BK - 1) / UM_BK;
     if (slot < a.top_k) {
-      const int e = a.ids[(size_t)tok * a.top_k + slot];
+      int e = a.ids[(size_t)tok * a.top_k + slot];
+      if (e < 0) { skip = true; e = 0; }       // an expert this rank does not hold: the slot contributes zeros
       w.ma = &tmapA; w.a_fp4 = a.a_fp4;
       w.a_row0 = e * a.d + tile * 128;
       w.sfa = a.sfa + ((size_t)(w.a_row0 >> 7) * a.katoms_a) * 512;
@@ -274,7 +286,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       w.a_row0 = tile * 128;
       w.sfa = a.sfa2 + ((size_t)tile * a.katoms_a) * 512;
     }
-    w.ks0 = 0; w.nks = ksteps;
+    w.ks0 = 0; w.nks = skip ? 0 : ksteps;
     w.b_x0 = 0; w.b_row0 = tok * a.slots + slot;
     w.sfb = a.sfb + (size_t)w.b_row0 * a.katoms_b * 512;
     w.split = slot; w.splits = a.slots;
@@ -342,13 +354,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     const size_t split_stride = (size_t)w.tiles_total * 128 * NP;
     float* part = a.scratch ? a.scratch + (size_t)w.split * split_stride + lane_off : nullptr;
     const int nv = a.pair > 0 ? a.pair : w.n_valid;
+    // bulk shapes: the bf16 tile is staged token-major in the (now idle) operand stages and leaves the SM as
+    // 256-byte bulk copies, one per token row and destination - element stores to a peer serialise on NVLink
+    const bool staged = BULK && a.pair == 0 && !a.out_f && !a.out_q && (a.out_b || a.n_peers > 0) &&
+                        w.col0 + 128 <= w.col_limit && (a.out_stride & 7) == 0;
+    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(&S.a[0][0][0]);
 #pragma unroll
     for (int c0 = 0; c0 < NP; c0 += 16) {
       uint32_t v[16];
       tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0, v);
       tc_wait_ld();
       if (!got || S.fail) continue;
-      if (single && a.pair == 0) {
+      if (skip) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0u;
+      }
+      if (single && staged) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (c0 + j < nv) stage[(c0 + j) * 128 + q * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[j]));
+      } else if (single && a.pair == 0) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int tok = c0 + j;
@@ -394,7 +419,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         if (S.last_flag) a.tickets[w.tile_id] = 0;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (S.last_flag) {
+      if (S.last_flag && staged) {
+        __threadfence();
+        for (int tok0 = 0; tok0 < nv; tok0 += 4) {
+          float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int sp = 0; sp < w.splits; ++sp) {      // split order: the sum does not depend on arrival order
+            const float4 t = __ldcg(reinterpret_cast<const float4*>(a.scratch + (size_t)sp * split_stride + lane_off + tok0));
+            acc4.x += t.x; acc4.y += t.y; acc4.z += t.z; acc4.w += t.w;
+          }
+          const float r4[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (tok0 + j < nv) stage[(tok0 + j) * 128 + q * 32 + lane] = __float2bfloat16_rn(r4[j]);
+        }
+      } else if (S.last_flag) {
         __threadfence();
         for (int tok = 0; tok < nv; ++tok) {
           float s = 0.f;
@@ -425,6 +463,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             }
           }
         }
+      }
+    }
+    if (staged && got && !S.fail && (single || S.last_flag)) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int tok = q * 32 + lane;
+      if (tok < nv) {
+        const int row = w.out_row0 + tok;
+        const uint32_t src = smem_u32(stage + tok * 128);
+        if (a.out_b) bulk_store(a.out_b + (int64_t)row * a.out_stride + w.col0, src, 256);
+        if (a.rs_rows > 0) {
+          const int pr = row / a.rs_rows;
+          bulk_store(a.peer_out[pr] + (int64_t)(row - pr * a.rs_rows) * a.out_stride + w.col0, src, 256);
+        } else {
+          for (int pr = 0; pr < a.n_peers; ++pr) bulk_store(a.peer_out[pr] + (int64_t)row * a.out_stride + w.col0, src, 256);
+        }
+        bulk_store_commit_wait();
       }
     }
     if (a.n_peers > 0) {
@@ -487,8 +542,10 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   int a_fp4, row_g, row_u;
   const uint8_t *sf_g, *sf_u;
   float weight = 1.f;
+  bool skip = false;
   if (slot < a.top_k) {
-    const int e = a.ids[(size_t)tok * a.top_k + slot];
+    int e = a.ids[(size_t)tok * a.top_k + slot];
+    if (e < 0) { skip = true; e = 0; }         // not this rank's expert: nothing is loaded, multiplied or written
     weight = a.wts[(size_t)tok * a.top_k + slot];
     ma = &tmapA; a_fp4 = a.a_fp4;
     row_g = (e * 2) * il + tile * 128; row_u = row_g + il;
@@ -505,10 +562,11 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   const uint32_t tmem = S.tmem_base;
   const uint32_t t_g = tmem, t_u = tmem + NP;
   const uint32_t t_sfg = tmem + 2 * NP, t_sfu = tmem + 2 * NP + 8, t_sfb = tmem + 2 * NP + 16;
+  const int nks_run = skip ? 0 : nks;
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < nks; ++i) {
+      for (int i = 0; i < nks_run; ++i) {
         const int s = i % UM_STAGES;
         if (i >= UM_STAGES && !mbar_wait(&S.empty[s], ((i / UM_STAGES) - 1) & 1)) { S.fail = 1; break; }
         mbar_expect_tx(&S.full[s], STAGE_TX);
@@ -523,7 +581,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(a_fp4 ? 5 : 0, 0, 128, NP);
-      for (int i = 0; i < nks; ++i) {
+      for (int i = 0; i < nks_run; ++i) {
         const int s = i % UM_STAGES;
         if (!mbar_wait(&S.full[s], (i / UM_STAGES) & 1)) { S.fail = 2; break; }
         tc_fence_after();
@@ -561,7 +619,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
     }
     uint8_t sc;
     const uint8_t code = warp_quant_fp8(act, &sc);
-    if (got && !S.fail && col < il) {
+    if (got && !S.fail && col < il && !skip) {
       const size_t row = (size_t)tok * a.slots + slot;
       a.act_q[row * il + col] = code;
       if (lane == 0) {
@@ -600,7 +658,7 @@ using namespace sfb;
 template <int NPV, bool BULK>
 static cudaError_t launch_umma_t(const CUtensorMap* mA, const CUtensorMap* mA2, const CUtensorMap* mB, const UmmaArgs& a, dim3 grid,
                                  cudaStream_t stream) {
-  const size_t smem = sizeof(UmmaSmem<NPV, 1, (NPV <= 32 ? UM_STAGES_DENSE : UM_STAGES_WIDE)>) + 1024;
+  const size_t smem = sizeof(UmmaSmem<NPV, 1, (NPV <= 32 ? UM_STAGES_DENSE : ((BULK && NPV == 128) ? 3 : UM_STAGES_WIDE))>) + 1024;
   static bool done = false;
   if (!done) {
     cudaFuncSetAttribute(umma_gemm_kernel<NPV, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -655,7 +713,7 @@ static int launch_umma(const void* tmapA, const void* tmapA2, const void* tmapB,
   cudaError_t launch_rc = cudaSuccess;
   UmmaArgs a = a_in;
   apply_push(a);
-const bool bulk = a.tok_tiles > 1 || a.b_maps != nullptr || a.rs_rows > 0;
+const bool bulk = a.force_bulk || a.tok_tiles > 1 || a.b_maps != nullptr || a.rs_rows > 0;
   if (a.tok_tiles < 1) a.tok_tiles = 1;
 #define SFB_UM(NPV) { launch_rc = bulk ? launch_umma_t<NPV, true>(mA, mA2, mB, a, grid, stream) : launch_umma_t<NPV, false>(mA, mA2, mB, a, grid, stream); }
   if (NP == 16) SFB_UM(16) else if (NP == 32) SFB_UM(32) else if (NP == 64) SFB_UM(64) else if (NP == 128) SFB_UM(128)
@@ -708,6 +766,7 @@ int sfb_umma_bulk(const void* tmapA, const void* tmapB, const void* sfa, int kat
   a.sfa = (const uint8_t*)sfa; a.katoms_a = katoms_a; a.sfb = (const uint8_t*)sfb; a.katoms_b = katoms_b;
   a.n = n; a.K = K; a.mode = UM_DENSE; a.N = N; a.groups = 1; a.splits = splits; a.scratch = scratch; a.tickets = tickets;
   a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f; a.out_stride = out_stride; a.status = (Status*)status;
+  a.force_bulk = 1;
   a.tok_tiles = tok_tiles; a.b_maps = (const CUtensorMap*)b_maps; a.b_k_per_map = b_k_per_map; a.rs_rows = rs_rows;
   for (int i = 0; i < n_maps && b_maps; ++i) a.sfb_maps[i] = (const uint8_t*)sfb_maps[i];
   const int rc = launch_umma(tmapA, nullptr, tmapB ? tmapB : tmapA, a, dim3((N + 127) / 128, splits, tok_tiles), NP, stream);

@@ -221,3 +221,47 @@ class ColumnParallelLinear(_Base):
     def forward(self, x_shard):
         self.publish(x_shard)
         return self.gemm()
+
+
+def _demo(argv=None) -> None:
+    """Lockstep demonstration on one GPU (W virtual ranks): ``python -m sparkflash_b200.parallel.fused_gemm --m 8192``.
+    Runs a few GEMM -> reduce steps and one all-gather -> GEMM step; a small fixed workload for profilers."""
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=512)
+    ap.add_argument("--hidden", type=int, default=5120)
+    ap.add_argument("--world", type=int, default=2)
+    ap.add_argument("--mode", default="rs", choices=["ar", "rs"])
+    ap.add_argument("--steps", type=int, default=3)
+    a = ap.parse_args(argv)
+    W, H, M = a.world, a.hidden, a.m
+    g = torch.Generator().manual_seed(0)
+    qr, sr = C.weight_quant_fp8_block32(torch.randn(H, H // W, generator=g) * 0.02)
+    qc, sc = C.weight_quant_fp8_block32(torch.randn(H // W, H, generator=g) * 0.02)
+    mode = a.mode if M % W == 0 else "ar"
+    heaps = SymmHeap.local_group(W, RowParallelLinear.heap_bytes(M, H, W, mode))
+    rows = [RowParallelLinear(heaps[r], qr.cuda(), sr, M, mode, norm_w=torch.ones(H, device="cuda")) for r in range(W)]
+    heaps2 = SymmHeap.local_group(W, ColumnParallelLinear.heap_bytes(M, H, W))
+    cols = [ColumnParallelLinear(heaps2[r], qc.cuda(), sc, M) for r in range(W)]
+    x = torch.randn(M, H // W, generator=g).to(torch.bfloat16).cuda()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    for s in range(a.steps):
+        if s == a.steps - 1:
+            ev[0].record()
+        for o in rows:
+            o.produce(x)
+        for o in rows:
+            o.consume()
+        for o in cols:
+            o.publish(x)
+        for o in cols:
+            o.gemm()
+    ev[1].record()
+    torch.cuda.synchronize()
+    for o in rows + cols:
+        o.check()
+    print(f"fused_gemm demo: M={M} hidden={H} W={W} mode={mode}: last step {ev[0].elapsed_time(ev[1]) * 1e3:.0f} us for {W} virtual ranks (eager launches)")
+
+
+if __name__ == "__main__":
+    _demo()

@@ -5,8 +5,8 @@ NVLink roofline.  One process per GPU:
     python -m torch.distributed.run --nnodes=1 --nproc-per-node W --master-addr 127.0.0.1 --master-port 29511 \
         -m sparkflash_b200.parallel.microbench [--hidden 5120] [--m 1,8,64,512,8192] [--iters 30]
 
-Timing: CUDA events on the launching stream around ``iters`` back-to-back operations after warm-up, max over
-ranks.  Weights of every M are distinct buffers and larger than nothing but L2 is not flushed between
+Timing: CUDA events on the launching stream around replays of a CUDA graph holding two operations (both arms), after
+warm-up, max over ranks.  Weights of every M are distinct buffers and larger than nothing but L2 is not flushed between
 iterations: the activations change every iteration, the weights (13-26 MB per rank) stay L2-resident exactly as
 they do inside a decode step.  Roofline: the slower of FLOPs / measured GEMM peak and bytes over NVLink / 770 GB/s.
 """
@@ -20,19 +20,30 @@ import torch
 import torch.distributed as dist
 
 
-def timed(fn, iters, warm=5):
+def timed(fn, iters, warm=4):
+    """Microseconds per call, max over ranks.  Two calls (both buffer parities) are captured into one CUDA graph and
+    the graph is replayed, so that launch overhead of the Python layer is outside the measurement for both arms."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
     dist.barrier()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn(); fn()
+    for _ in range(2):
+        g.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(1, iters // 2)
     a.record()
-    for _ in range(iters):
-        fn()
+    for _ in range(reps):
+        g.replay()
     b.record()
     torch.cuda.synchronize()
-    t = torch.tensor([a.elapsed_time(b) * 1e3 / iters], dtype=torch.float64, device="cuda")
+    t = torch.tensor([a.elapsed_time(b) * 1e3 / (2 * reps)], dtype=torch.float64, device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    del g
     return float(t)
 
 
