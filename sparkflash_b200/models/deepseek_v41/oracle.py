@@ -362,7 +362,86 @@ class Oracle:
         st.pos = pos + 1
         st.tokens.append(token)
         self.last_taps = torch.cat(taps) if taps else None
+        if cfg.n_mtp_stages and len(taps) == len(cfg.dspark_taps) and "mtp.0.main_proj" in w:
+            self._dspark_seed(st, pos)
         return logits
+
+    # ---- DSpark draft stages (docs/architecture/05-dspark.md of the reference) ---------------------------------
+    def _dspark_seed(self, st: SeqState, pos: int) -> None:
+        """Every backbone position leaves one un-rotated window key per draft stage: kv_norm(wkv(main_x)), FP8."""
+        cfg, w = self.cfg, self.w
+        main_x = rmsnorm(bf(fp8_linear(self.last_taps, w["mtp.0.main_proj"])), w["mtp.0.main_norm.weight"], cfg.norm_eps)
+        self.last_main_x = main_x
+        for s in range(cfg.n_mtp_stages):
+            p = f"mtp.{s}"
+            ls = st.layers[cfg.n_layers + s]
+            kv = rmsnorm(bf(fp8_linear(main_x, w[f"{p}.attn.wkv"])), w[f"{p}.attn.kv_norm.weight"], cfg.norm_eps)
+            ls.window[pos] = C.act_roundtrip_fp8(kv)
+            for old in [k for k in ls.window if k <= pos - cfg.window]:
+                del ls.window[old]
+
+    def _dspark_attention(self, s: int, xs: list[torch.Tensor], st: SeqState, P: int) -> list[torch.Tensor]:
+        """Window attention over [history of main keys ; the block's own keys]; no causal mask inside the block."""
+        cfg, w = self.cfg, self.w
+        p = f"mtp.{s}"
+        h, hd = cfg.n_heads, cfg.head_dim
+        invf = self.inv_freq[False]
+        ls = st.layers[cfg.n_layers + s]
+        hist = [ls.window[t] for t in range(max(0, P - cfg.window + 1), P + 1)]
+        qs, own = [], []
+        for i, x in enumerate(xs):
+            pos = P + 1 + i
+            qr = rmsnorm(bf(fp8_linear(x, w[f"{p}.attn.wq_a"])), w[f"{p}.attn.q_norm.weight"], cfg.norm_eps)
+            qs.append(apply_rope(bf(fp8_linear(qr, w[f"{p}.attn.wq_b"])).view(h, hd), pos, invf))
+            kv = rmsnorm(bf(fp8_linear(x, w[f"{p}.attn.wkv"])), w[f"{p}.attn.kv_norm.weight"], cfg.norm_eps)
+            own.append(C.act_roundtrip_fp8(apply_rope(kv, pos, invf)))
+        K = torch.stack(hist + own)
+        outs = []
+        for i, q in enumerate(qs):
+            sc = (q @ K.t()) * (hd ** -0.5)
+            m = sc.max(-1, keepdim=True).values.clamp_min(-1e30)
+            e = torch.exp(sc - m)
+            den = e.sum(-1, keepdim=True) + torch.exp(w[f"{p}.attn.attn_sink"].view(h, 1) - m)
+            o = apply_rope(bf((e @ K) / den), P + 1 + i, invf, inverse=True)
+            wo_a = w[f"{p}.attn.wo_a"].view(cfg.o_groups, cfg.o_lora_rank, -1)
+            oa = bf(torch.einsum("gd,grd->gr", o.reshape(cfg.o_groups, -1), wo_a)).flatten()
+            outs.append(self._row_parallel([oa], [w[f"{p}.attn.wo_b"]]))
+        return outs
+
+    def draft(self, st: SeqState, anchor: int, temperature: float = 0.0, seed: int = 0):
+        """One DSpark block after ``step`` handled position P = st.pos - 1 and ``anchor`` was sampled for P + 1.
+        Returns (tokens [block] proposed for positions P+2 .., confidence logits [block], logits [block, vocab])."""
+        cfg, w = self.cfg, self.w
+        P, B, hc = st.pos - 1, cfg.dspark_block, cfg.hc_mult
+        ids = [anchor] + [cfg.dspark_noise_token % cfg.vocab_size] * (B - 1)
+        H = [w["embed.weight"][t].unsqueeze(0).repeat(hc, 1) for t in ids]
+        onehot = torch.zeros(hc); onehot[0] = 1.0
+        pre = [onehot.clone() for _ in range(B)]
+        for s in range(cfg.n_mtp_stages):
+            p = f"mtp.{s}"
+            co = [hc_coeffs(H[i], w[f"{p}.hc_attn_fn"], w[f"{p}.hc_attn_scale"], w[f"{p}.hc_attn_base"], cfg) for i in range(B)]
+            xs = [rmsnorm(hc_pre(H[i], pre[i]), w[f"{p}.attn_norm.weight"], cfg.norm_eps) for i in range(B)]
+            ys = self._dspark_attention(s, xs, st, P)
+            for i in range(B):
+                a_pre, a_post, a_comb = co[i]
+                h1 = hc_post(bf(ys[i]), H[i], a_post, a_comb)
+                f_pre, f_post, f_comb = hc_coeffs(h1, w[f"{p}.hc_ffn_fn"], w[f"{p}.hc_ffn_scale"], w[f"{p}.hc_ffn_base"], cfg)
+                x = rmsnorm(hc_pre(h1, a_pre), w[f"{p}.ffn_norm.weight"], cfg.norm_eps)
+                y = bf(self._moe(p, x, cfg.dspark_n_experts, cfg.dspark_top_k))
+                H[i], pre[i] = hc_post(y, h1, f_post, f_comb), f_pre
+        last = f"mtp.{cfg.n_mtp_stages - 1}"
+        xs = [hc_pre(H[i], pre[i]) for i in range(B)]
+        logits = torch.stack([rmsnorm(x, w[f"{last}.norm.weight"], cfg.norm_eps) @ w["head.weight"].t() for x in xs])
+        me, mh = w[f"{last}.markov_head.embed.weight"], w[f"{last}.markov_head.head.weight"]
+        cw = w[f"{last}.confidence_head.proj.weight"].to(torch.float32).flatten()
+        out, conf, prev = [], [], anchor
+        for i in range(B):
+            emb = me[prev].to(torch.float32)
+            logits[i] = logits[i] + mh.to(torch.float32) @ emb          # previous-token dependent bias, then sample
+            conf.append(float(torch.cat([xs[i].to(torch.float32), emb]) @ cw))
+            prev = sample_token(logits[i], temperature, seed, P + 2 + i)
+            out.append(prev)
+        return out, conf, logits
 
     def prefill(self, st: SeqState, tokens: list[int]) -> torch.Tensor:
         logits = None
