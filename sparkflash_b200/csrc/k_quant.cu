@@ -50,6 +50,39 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(QuantArgs a) {
   }
 }
 
+
+// Bulk variant (many rows): a thread owns 8 consecutive columns (one 16-byte load, one 8-byte store), four lanes
+// share a 32-column scale group.  grid (ceil(K / 1024), n), block 128.
+__global__ void __launch_bounds__(128) quant_rows_vec_kernel(QuantArgs a) {
+  const int row = blockIdx.y;
+  const int col = (blockIdx.x * 128 + threadIdx.x) * 8;
+  const int KB = a.K / 32;
+  float v[8];
+  float amax = 0.f;
+  if (col < a.K) {
+    const uint4 u = *reinterpret_cast<const uint4*>(a.x + (size_t)row * a.K + col);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  if (col >= a.K) return;
+  const uint8_t sc = act_scale_code_fp8(amax);
+  const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+  uint2 q;
+  uint8_t* qb = reinterpret_cast<uint8_t*>(&q);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) qb[j] = enc_e4m3(v[j] * inv);
+  *reinterpret_cast<uint2*>(a.q + (size_t)row * a.K + col) = q;
+  if ((threadIdx.x & 3) == 0) {
+    if (a.s) a.s[(size_t)row * KB + col / 32] = sc;
+    if (a.atom) a.atom[sf_offset(row, col / 32, KB)] = sc;
+  }
+}
+
 }  // namespace sfb
 
 using namespace sfb;
@@ -58,6 +91,10 @@ extern "C" int sfb_quant_rows(const void* x, void* q, void* s, void* atom, int n
                               cudaStream_t stream) {
   if (K % 32) return (int)cudaErrorInvalidValue;
   QuantArgs a{(const __nv_bfloat16*)x, (uint8_t*)q, (uint8_t*)s, (uint8_t*)atom, n, K, split, split_off};
+  if (!split && n >= 32) {      // same arithmetic, wider accesses
+    quant_rows_vec_kernel<<<dim3((K + 1023) / 1024, n), 128, 0, stream>>>(a);
+    return SFB_CHECK_LAUNCH();
+  }
   quant_rows_kernel<<<dim3((K + 255) / 256, n), 256, 0, stream>>>(a);
   return SFB_CHECK_LAUNCH();
 }

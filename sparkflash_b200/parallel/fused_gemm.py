@@ -97,7 +97,7 @@ class RowParallelLinear(_Base):
         self.bytes = self.off_done + 256 - heap_offset
         tiles = ((self.N + 127) // 128) * ((M + self.NP - 1) // self.NP)
         ksteps = self.Kl // 128
-        self.splits = max(1, min(ksteps, 296 // max(1, tiles))) if M <= 128 else 1
+        self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles))) if M <= 128 else 1
         self.scratch = torch.zeros((tiles * self.splits * 128 * self.NP,), dtype=torch.float32, device="cuda") if self.splits > 1 else None
         self.tickets = torch.zeros((max(tiles, 1),), dtype=torch.int32, device="cuda")
         self.norm_w, self.eps = norm_w, eps
@@ -183,7 +183,7 @@ class ColumnParallelLinear(_Base):
             self.local_atom[-1].fill_(127)
         tiles = ((self.Nl + 127) // 128) * ((M + self.NP - 1) // self.NP)
         ksteps = self.K // 128
-        self.splits = max(1, min(ksteps, 296 // max(1, tiles))) if M <= 128 else 1
+        self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles))) if M <= 128 else 1
         self.scratch = torch.zeros((tiles * self.splits * 128 * self.NP,), dtype=torch.float32, device="cuda") if self.splits > 1 else None
         self.tickets = torch.zeros((max(tiles, 1),), dtype=torch.int32, device="cuda")
         self.out = torch.empty((M, self.Nl), dtype=torch.bfloat16, device="cuda")

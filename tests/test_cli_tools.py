@@ -88,3 +88,29 @@ def test_served_benchmark_client_over_mock():
     srv = Server(MockEngine(tok, lambda p: tok.encode("x" * 40), lanes=4, queue=8, delay=0.001))
     out = asyncio.run(run_async("http://t", 4, 8, 64, 32, transport=httpx.ASGITransport(app=srv.app)))
     assert out["ok"] == 8 and out["aggregate_tok_s"] > 0 and out["ttft_p50_s"] <= out["ttft_p99_s"]
+
+
+def test_fit_estimator_and_control_panel(tmp_path):
+    import time as _t
+    from starlette.testclient import TestClient
+    from sparkflash_b200.web import app as WA, fit
+    full = CF.full_config()
+    one = fit.estimate(full, 1, 131072, 32)
+    eight = fit.estimate(full, 8, 1048576, 32)
+    assert not one.fits and one.weights_gb > 180            # the whole model does not fit one GPU
+    assert eight.fits and eight.weights_gb < 60 and eight.max_lanes_that_fit >= 32
+    assert fit.estimate(CF.reduced_config(128, 40), 1, 65536, 16).fits
+    assert fit.kv_bytes_per_lane(full, 1 << 20) > 20 * fit.kv_bytes_per_lane(full, 1 << 14) / 2
+    c = TestClient(WA.create_app(nvml=FakeNvml(2)))
+    assert len(c.get("/api/nodes").json()["nodes"][0]["gpus"]) == 2
+    r = c.get("/api/fit?world=8&context=1048576&lanes=32").json()
+    assert r["fits"] and r["world"] == 8
+    assert c.get("/api/stats").status_code == 502            # nothing is serving
+    jid = c.post("/api/jobs", json={"kind": "convert", "synthetic": "tiny", "checkpoint": str(tmp_path / "ck"), "output_dir": str(tmp_path / "o"), "world": 1}).json()["id"]
+    for _ in range(200):
+        j = [x for x in c.get("/api/jobs").json()["jobs"] if x["id"] == jid][0]
+        if j["state"] != "running":
+            break
+        _t.sleep(0.1)
+    assert j["state"] == "done" and j["progress"]["done"] == 1
+    assert c.post("/api/jobs", json={"kind": "rm -rf"}).status_code == 400
