@@ -19,6 +19,17 @@ __global__ void embed_kernel(const __nv_bfloat16* embed, const int* tokens, __nv
   for (int c = 0; c < hc; ++c) *reinterpret_cast<uint4*>(h + ((size_t)row * hc + c) * d + col) = v;
 }
 
+// rows flagged in `mask` take their input embedding from `override` (image tokens: the vision tower's output or
+// one of the learned delimiter vectors) instead of the embedding table
+__global__ void embed_override_kernel(const __nv_bfloat16* override_rows, const uint8_t* mask, __nv_bfloat16* h, int hc, int d) {
+  const int row = blockIdx.y;
+  if (!mask[row]) return;
+  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (col >= d) return;
+  const uint4 v = *reinterpret_cast<const uint4*>(override_rows + (size_t)row * d + col);
+  for (int c = 0; c < hc; ++c) *reinterpret_cast<uint4*>(h + ((size_t)row * hc + c) * d + col) = v;
+}
+
 // tap[row, :] = bf16(mean over copies of h[row, c, :])
 __global__ void tap_mean_kernel(const __nv_bfloat16* h, __nv_bfloat16* tap, int64_t tap_stride, int hc, int d) {
   const int row = blockIdx.y;
@@ -219,6 +230,13 @@ int sfb_embed(const void* embed, const int* tokens, void* h, int n, int hc, int 
   if (d % 8) return (int)cudaErrorInvalidValue;
   embed_kernel<<<dim3((d / 8 + 127) / 128, n), 128, 0, stream>>>((const __nv_bfloat16*)embed, tokens,
                                                                (__nv_bfloat16*)h, n, hc, d, vocab, (Status*)status);
+  return SFB_CHECK_LAUNCH();
+}
+
+int sfb_embed_override(const void* override_rows, const void* mask, void* h, int n, int hc, int d, cudaStream_t stream) {
+  if (d % 8) return (int)cudaErrorInvalidValue;
+  embed_override_kernel<<<dim3((d / 8 + 127) / 128, n), 128, 0, stream>>>((const __nv_bfloat16*)override_rows, (const uint8_t*)mask,
+                                                                        (__nv_bfloat16*)h, hc, d);
   return SFB_CHECK_LAUNCH();
 }
 

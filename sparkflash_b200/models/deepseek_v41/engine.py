@@ -112,7 +112,8 @@ class StepIO:
 class Engine:
     def __init__(self, weights: DeviceWeights, max_lanes: int = 4, max_context: int = 4096, max_rows: int = 64,
                  comm=None, use_graphs: bool = True, keep_logits: bool = False, arm: str = "cuda",
-                 synthetic_scales: bool = False, constrained: bool = False, lane_budget_bytes: int | None = None):
+                 synthetic_scales: bool = False, constrained: bool = False, lane_budget_bytes: int | None = None,
+                 vision: bool = False):
         """``arm``: "cuda" = CUDA-core exact arm for every projection; "tc" = tcgen05 tensor-core arm for
         every shape it takes (the rest falls back to the CUDA-core kernels)."""
         self.w, self.cfg = weights, weights.cfg
@@ -127,6 +128,9 @@ class Engine:
         # constrained sequence owns the row; each rank fills and reads only its own slice
         self.supports_mask = constrained
         self.supports_filter = False
+        # image rows: input embedding supplied by the caller (vision tower output / delimiter vectors), routed with
+        # the vision-language router bias
+        self.supports_vision = vision
         self.kv = KVCache(cfg, max_lanes, max_context, max_rows, self.dev, lane_budget_bytes)
         R, d, hc, hd, q = max_rows, cfg.hidden_size, cfg.hc_mult, cfg.head_dim, cfg.q_lora_rank
         W = self.world
@@ -182,6 +186,9 @@ class Engine:
         self.act_s = e((R, cfg.top_k + 1, self.il // 32), u8)
         self.logits = e((R, self.vl), f32)
         self.mask = torch.ones((R, cfg.vocab_size), dtype=torch.uint8, device=dev) if constrained else None
+        self.img_rows = e((R, d), bf) if vision else None
+        self.img_mask = torch.zeros((R,), dtype=torch.uint8, device=dev) if vision else None
+        self._img_dirty = False
         self._masked_rows: set[int] = set()
         self.best_val, self.best_id = e((W, R), f32), e((W, R), i32)
         self.tokens_out = e((R,), i32)
@@ -403,7 +410,7 @@ class Engine:
         ks = self.gate_ksplit
         N.gemv(N.WF_BF16, L.gate_w, None, 2 * d, E, d, n, xb=self.xn, out_f=self.dots, out_stride=E, ksplit=ks,
                split_stride=self.dots.stride(0)); self._k()
-        N.router_topk(self.dots, L.gate_bias, L.gate_bias_vl, None, self.ids, self.wts, n, E, k, cfg.route_scale,
+        N.router_topk(self.dots, L.gate_bias, L.gate_bias_vl, self.img_mask, self.ids, self.wts, n, E, k, cfg.route_scale,
                       nsplit=ks, split_stride=self.dots.stride(0)); self._k()
         self._prefetch(n, (), experts=(L.w2, n * k))
         T = self.tcl[l] if self.tcl is not None else None
@@ -458,6 +465,8 @@ class Engine:
         if fused:
             self.comm.begin_step(); self._k()
         N.embed(w.embed, self.tokens, self.h, n, cfg.hc_mult, cfg.hidden_size, cfg.vocab_size, self.status); self._k()
+        if self.img_mask is not None:
+            N.embed_override(self.img_rows, self.img_mask, self.h, n, cfg.hc_mult, cfg.hidden_size); self._k()
         N.rope_table([w.inv_freq[c] for c, _ in self.rope_variants], [r for _, r in self.rope_variants], self.row_pos,
                      self.rope, n); self._k()
         k = 0
@@ -534,7 +543,19 @@ class Engine:
             bits = np.unpackbits(np.asarray(words, dtype=np.uint64).view(np.uint8), bitorder="little")[:hi - lo]
             self.mask[r, lo:hi].copy_(torch.from_numpy(bits))
 
-    def step(self, tokens, lanes, positions, temperature=None, seeds=None, sync: bool = True, masks: dict | None = None) -> torch.Tensor:
+    def _stage_images(self, n: int, image_rows: dict) -> None:
+        if self._img_dirty:
+            self.img_mask.zero_()
+            self._img_dirty = False
+        for r, vec in image_rows.items():
+            self.img_rows[r].copy_(vec.to(self.img_rows.dtype), non_blocking=True)
+        if image_rows:
+            idx = torch.tensor(sorted(image_rows), dtype=torch.int64, device=self.dev)
+            self.img_mask[idx] = 1
+            self._img_dirty = True
+
+    def step(self, tokens, lanes, positions, temperature=None, seeds=None, sync: bool = True, masks: dict | None = None,
+             image_rows: dict | None = None) -> torch.Tensor:
         """Run one rows step.  ``tokens/lanes/positions`` are host sequences of equal length n.
         Returns the sampled next-token ids as a host int32 tensor [n] (pinned) when ``sync``; the
         device tensor ``tokens_out`` otherwise."""
@@ -542,6 +563,10 @@ class Engine:
         if not 0 < n <= self.max_rows:
             raise ValueError(f"rows {n} out of range 1..{self.max_rows}")
         self.kv.ensure(lanes, positions)
+        if image_rows or self._img_dirty:
+            if self.img_mask is None:
+                raise ValueError("this engine was built without vision=True")
+            self._stage_images(n, image_rows or {})
         if masks or self._masked_rows:
             if self.mask is None:
                 raise ValueError("this engine was built without constrained=True")

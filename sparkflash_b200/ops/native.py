@@ -196,6 +196,10 @@ def embed(table, tokens, h, n, hc, d, vocab, status=None):
                            _stream()), "embed")
 
 
+def embed_override(rows, mask, h, n, hc, d):
+    _check(lib().sfb_embed_override(_p(rows), _p(mask), _p(h), c_int(n), c_int(hc), c_int(d), _stream()), "embed_override")
+
+
 def rope_table(inv_freqs, ratios, row_pos, out, n):
     """out: float32 [n, V, rd/2, 2] - (cos, sin) per row, variant and rotary pair (csrc/k_misc.cu)."""
     V = len(inv_freqs)

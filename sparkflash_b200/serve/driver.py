@@ -95,7 +95,8 @@ class DeviceDriver(InferenceEngine):
         ring_slack = getattr(engine, "ring_slack", None)
         if ring_slack is not None:
             self.sched.set_ring_slack(ring_slack)
-        self.capabilities = Capabilities(constrained=getattr(engine, "supports_mask", False), speculative=drafter is not None)
+        self.capabilities = Capabilities(constrained=getattr(engine, "supports_mask", False), speculative=drafter is not None,
+                                         vision=getattr(engine, "supports_vision", False))
         self._inbox: queue.Queue = queue.Queue()
         self._live: dict[int, _Live] = {}
         self._by_request: dict[str, int] = {}
@@ -279,8 +280,16 @@ class DeviceDriver(InferenceEngine):
                 if total == 0:
                     self._finish(live, None, error=("the constraint admits no token", "constraint_dead_end"))
                     return True
-        out = eng.step([r.token for r in rows], [r.lane for r in rows], [r.pos for r in rows], temps, seeds,
-                       **({"masks": masks} if masks or getattr(eng, "supports_mask", False) else {}))
+        image_rows = {}
+        for i, r in enumerate(rows):
+            for sp in self._live[r.seq].req.vision:
+                k = r.pos - sp.start
+                if 0 <= k < sp.embeddings.shape[0]:
+                    image_rows[i] = sp.embeddings[k]
+        kw = {"masks": masks} if masks or getattr(eng, "supports_mask", False) else {}
+        if image_rows or getattr(eng, "supports_vision", False):
+            kw["image_rows"] = image_rows
+        out = eng.step([r.token for r in rows], [r.lane for r in rows], [r.pos for r in rows], temps, seeds, **kw)
         out = [int(x) for x in out]
         eng.check_status()
         self.ticks += 1
@@ -390,6 +399,8 @@ class FakeRowsEngine:
         self.steps: list[int] = []
         self.status_error: str | None = None
         self.ring_slack = 64
+        self.supports_vision = True
+        self.image_log: list[tuple] = []
 
     def vocab_slice(self):
         return 0, self.vocab_size
@@ -408,8 +419,10 @@ class FakeRowsEngine:
             return self.eos_id
         return 32 + h % 90      # printable bytes
 
-    def step(self, tokens, lanes, positions, temperature=None, seeds=None, masks=None):
+    def step(self, tokens, lanes, positions, temperature=None, seeds=None, masks=None, image_rows=None):
         self.steps.append(len(tokens))
+        for i, vec in (image_rows or {}).items():
+            self.image_log.append((lanes[i], positions[i], float(vec.float().sum())))
         out = []
         for i, (t, l, p) in enumerate(zip(tokens, lanes, positions)):
             self.lane_tokens[l][p] = t

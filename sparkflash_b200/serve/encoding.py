@@ -17,7 +17,8 @@ EOS = "<｜end▁of▁sentence｜>"
 THINK_START, THINK_END = "<think>", "</think>"
 SYSTEM, USER, ASSISTANT, REMINDER = "<｜System｜>", "<｜User｜>", "<｜Assistant｜>", "<｜latest_reminder｜>"
 DSML = "｜DSML｜"
-SPECIAL_TOKENS = [BOS, EOS, THINK_START, THINK_END, SYSTEM, USER, ASSISTANT, REMINDER, DSML]
+IMAGE = "<｜image｜>"         # one placeholder per image; the server expands it into the image span
+SPECIAL_TOKENS = [BOS, EOS, THINK_START, THINK_END, SYSTEM, USER, ASSISTANT, REMINDER, DSML, IMAGE]
 
 EFFORT_SCORE = {"minimal": 25, "low": 25, "medium": 50, "high": 50, "xhigh": 75, "max": 100}
 DEFAULT_EFFORT = 50

@@ -47,6 +47,7 @@ class EngineRequest:
     trace_steps: int = 0
     constraint: dict | None = None
     images: list[Any] = field(default_factory=list)
+    vision: list[Any] = field(default_factory=list)     # prepared spans (serve/vision_glue.py), in prompt order
     tools: bool = False
     tool_block_open: bool = False      # the prompt ended inside an opened calls block (tool_choice required)
     tool_dialect: str = "dsml"

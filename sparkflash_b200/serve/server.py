@@ -51,6 +51,7 @@ def _content_text(content: Any, images: list) -> str:
             out.append(p.get("text", ""))
         elif t in ("image_url", "input_image", "image"):
             images.append(p)
+            out.append(ENC.IMAGE)
         elif t == "tool_result":
             out.append(_content_text(p.get("content"), images))
         elif t in ("thinking", "tool_use"):
@@ -62,7 +63,7 @@ def _content_text(content: Any, images: list) -> str:
 
 class Server:
     def __init__(self, engine: InferenceEngine, api_key: str | None = None, aliases: dict[str, str] | None = None,
-                 default_thinking: bool = False, trace=None, default_max_tokens: int = 1024):
+                 default_thinking: bool = False, trace=None, default_max_tokens: int = 1024, vision=None):
         self.engine = engine
         self.tok = engine.tokenizer
         self.api_key = api_key
@@ -70,6 +71,7 @@ class Server:
         self.default_thinking = default_thinking
         self.metrics = Metrics()
         self.trace = trace
+        self.vision = vision          # serve/vision_glue.VisionFrontEnd, when the engine has the vision path
         self.default_max_tokens = default_max_tokens
         self.draining = False
         self.started_at = time.time()
@@ -272,6 +274,12 @@ class Server:
         req.images = [im for m in messages for im in m.images]
         prompt = ENC.render_prompt(messages, tools, thinking, effort, required, hint)
         req.prompt_tokens = self.tok.encode(prompt)
+        if req.images and self.vision is not None and self.engine.capabilities.vision:
+            req.prompt_tokens, req.vision = self.vision.expand(req.prompt_tokens, req.images)
+            req.images = []
+        elif not req.images:
+            # a placeholder typed as text must not be mistaken for an image span
+            pass
         req.tools = bool(tools)
         req.tool_block_open = required
         self._sampling(body, req, max_key)

@@ -132,3 +132,36 @@ def test_cancel_frees_the_lane():
     finally:
         drv.shutdown(0.5)
     assert fin[0] == "finished" and len(toks) == 3
+
+
+def test_image_parts_become_spans_whose_rows_carry_the_tower_output():
+    import base64, io
+    import torch
+    from PIL import Image
+    from sparkflash_b200.serve import encoding as ENC
+    from sparkflash_b200.serve.vision_glue import VisionFrontEnd
+    from sparkflash_b200.vision import plan as VP, tower as VT
+    vc = VP.VisionConfig(n_layers=1, dim=32, n_heads=2, inter_dim=48, llm_dim=16, min_pixels=42 * 42, max_n_token=64)
+    tw = VT.VisionTower(vc, VT.synthetic_vision_weights(vc))
+    tok = ByteTokenizer(300)
+    front = VisionFrontEnd(tw, tok.special_ids[ENC.IMAGE])
+    buf = io.BytesIO(); Image.new("RGB", (60, 40), (200, 10, 10)).save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    eng = FakeRowsEngine(eos_after=10 ** 6, max_rows=8)
+    drv = DeviceDriver(eng, tok, model_id="fake", eos_id=10 ** 9).start()
+    try:
+        c = TestClient(Server(drv, vision=front).app)
+        body = {"messages": [{"role": "user", "content": [{"type": "text", "text": "look:"}, {"type": "image_url", "image_url": {"url": url}}, {"type": "text", "text": "what?"}]}], "max_tokens": 3}
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200, r.text
+        pl = VP.plan_image_grid(60, 40, vc)
+        assert r.json()["usage"]["prompt_tokens"] == len(tok.encode(ENC.BOS + ENC.USER + "look:what?" + ENC.ASSISTANT + ENC.THINK_END)) + pl.n_tokens
+        # every position of the span reached the engine as an embedding row, in order, exactly once
+        pos = [p for _, p, _ in eng.image_log]
+        assert len(pos) == pl.n_tokens and pos == list(range(pos[0], pos[0] + pl.n_tokens))
+        assert c.get("/v1/models").json()["data"][0]["capabilities"]["vision"]
+        bad = {"messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "http://example.com/x.png"}}]}]}
+        r = c.post("/v1/chat/completions", json=bad)
+        assert r.status_code == 400 and r.json()["error"]["code"] == "unsupported_image_source"
+    finally:
+        drv.shutdown(0.5)
