@@ -127,7 +127,7 @@ class Engine:
         # serving-side contract (serve/driver.py): a byte mask per row over the whole vocabulary, all ones unless a
         # constrained sequence owns the row; each rank fills and reads only its own slice
         self.supports_mask = constrained
-        self.supports_filter = False
+        self.supports_filter = True      # top-k / top-p through the candidate filter below (rows that ask for it only)
         # image rows: input embedding supplied by the caller (vision tower output / delimiter vectors), routed with
         # the vision-language router bias
         self.supports_vision = vision
@@ -543,6 +543,44 @@ class Engine:
             bits = np.unpackbits(np.asarray(words, dtype=np.uint64).view(np.uint8), bitorder="little")[:hi - lo]
             self.mask[r, lo:hi].copy_(torch.from_numpy(bits))
 
+    CANDIDATES = 256
+
+    def filtered_sample(self, row: int, top_k: int, top_p: float, temperature: float, seed: int, pos: int) -> int:
+        """Candidate filter for one row of the step that just ran: every rank offers its CANDIDATES best logits
+        (after the row's constraint mask) and its slice's log-sum-exp; the union is cut by top-k, then by the
+        nucleus over the full-vocabulary softmax, and sampled with a generator keyed on (seed, position), so the
+        choice does not depend on batching or speculation.  Reference: candidate gather of the sampler,
+        crates/sparkflash-deepseek-forward/src/tp4_forward/sample.rs."""
+        lo, hi = self.vocab_slice()
+        lg = self.logits[row].float()
+        if self.mask is not None and row in self._masked_rows:
+            lg = lg.masked_fill(self.mask[row, lo:hi] == 0, float("-inf"))
+        T = max(temperature, 1e-5)
+        k = min(self.CANDIDATES, lg.numel())
+        val, idx = torch.topk(lg, k)
+        lse = torch.logsumexp(lg / T, 0, keepdim=True)
+        idx = idx + lo
+        if self.world > 1:
+            import torch.distributed as dist
+            vs = [torch.empty_like(val) for _ in range(self.world)]
+            ids = [torch.empty_like(idx) for _ in range(self.world)]
+            ls = [torch.empty_like(lse) for _ in range(self.world)]
+            dist.all_gather(vs, val); dist.all_gather(ids, idx); dist.all_gather(ls, lse)
+            val, idx, lse = torch.cat(vs), torch.cat(ids), torch.logsumexp(torch.cat(ls), 0, keepdim=True)
+        order = torch.argsort(val, descending=True, stable=True)
+        val, idx = val[order], idx[order]
+        if temperature < 1e-5:
+            return int(idx[0])
+        keep = val.numel() if top_k <= 0 else min(top_k, val.numel())
+        prob = torch.exp(val / T - lse)                      # probabilities under the full-vocabulary softmax
+        if top_p < 1.0:
+            before = torch.cumsum(prob, 0) - prob            # mass of the strictly better candidates
+            keep = min(keep, max(1, int((before < top_p).sum())))
+        prob = prob[:keep]
+        g = torch.Generator(device=prob.device)
+        g.manual_seed((seed * 0x9E3779B97F4A7C15 + (pos + 1) * 0xBF58476D1CE4E5B9) & 0x7FFFFFFFFFFFFFFF)
+        return int(idx[int(torch.multinomial(prob / prob.sum(), 1, generator=g))])
+
     def _stage_images(self, n: int, image_rows: dict) -> None:
         if self._img_dirty:
             self.img_mask.zero_()
@@ -555,7 +593,7 @@ class Engine:
             self._img_dirty = True
 
     def step(self, tokens, lanes, positions, temperature=None, seeds=None, sync: bool = True, masks: dict | None = None,
-             image_rows: dict | None = None) -> torch.Tensor:
+             image_rows: dict | None = None, filters: dict | None = None) -> torch.Tensor:
         """Run one rows step.  ``tokens/lanes/positions`` are host sequences of equal length n.
         Returns the sampled next-token ids as a host int32 tensor [n] (pinned) when ``sync``; the
         device tensor ``tokens_out`` otherwise."""
@@ -595,6 +633,9 @@ class Engine:
             return self.tokens_out[:n]
         io.out[:n].copy_(self.tokens_out[:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        if filters:
+            for r, (top_k, top_p) in filters.items():
+                io.out[r] = self.filtered_sample(r, top_k, top_p, float(io.temp[r]), int(io.seed[r]), int(io.pos[r]))
         return io.out[:n]
 
     def run_rows(self, n: int, len_bucket: int) -> None:

@@ -289,6 +289,13 @@ class DeviceDriver(InferenceEngine):
         kw = {"masks": masks} if masks or getattr(eng, "supports_mask", False) else {}
         if image_rows or getattr(eng, "supports_vision", False):
             kw["image_rows"] = image_rows
+        filters = {}
+        for i, r in enumerate(rows):
+            q = self._live[r.seq].req
+            if (q.top_p < 1.0 or q.top_k > 0) and q.temperature >= 1e-5:
+                filters[i] = (q.top_k, q.top_p)
+        if filters:
+            kw["filters"] = filters
         out = eng.step([r.token for r in rows], [r.lane for r in rows], [r.pos for r in rows], temps, seeds, **kw)
         out = [int(x) for x in out]
         eng.check_status()
@@ -389,7 +396,6 @@ class FakeRowsEngine:
     prefix reuse changes the output.  Used by the CPU tests of the driver."""
 
     supports_mask = True
-    supports_filter = False
 
     def __init__(self, vocab_size: int = 300, max_lanes: int = 4, max_context: int = 512, max_rows: int = 16, eos_id: int = 257,
                  eos_after: int | None = None, cycle: list[int] | None = None):
@@ -401,6 +407,8 @@ class FakeRowsEngine:
         self.ring_slack = 64
         self.supports_vision = True
         self.image_log: list[tuple] = []
+        self.filter_log: list[tuple] = []
+        self.supports_filter = True
 
     def vocab_slice(self):
         return 0, self.vocab_size
@@ -419,8 +427,9 @@ class FakeRowsEngine:
             return self.eos_id
         return 32 + h % 90      # printable bytes
 
-    def step(self, tokens, lanes, positions, temperature=None, seeds=None, masks=None, image_rows=None):
+    def step(self, tokens, lanes, positions, temperature=None, seeds=None, masks=None, image_rows=None, filters=None):
         self.steps.append(len(tokens))
+        self.filter_log += [(positions[i], f) for i, f in (filters or {}).items()]
         for i, vec in (image_rows or {}).items():
             self.image_log.append((lanes[i], positions[i], float(vec.float().sum())))
         out = []

@@ -165,3 +165,14 @@ def test_image_parts_become_spans_whose_rows_carry_the_tower_output():
         assert r.status_code == 400 and r.json()["error"]["code"] == "unsupported_image_source"
     finally:
         drv.shutdown(0.5)
+
+
+def test_top_p_top_k_reach_the_engine_only_for_sampling_rows():
+    eng = FakeRowsEngine()
+    drv = DeviceDriver(eng, TOK)
+    reqs = [EngineRequest("a", "m", [1, 2, 3], max_tokens=3, temperature=0.8, top_p=0.9, top_k=40),
+            EngineRequest("b", "m", [4, 5, 6], max_tokens=3, temperature=0.0, top_p=0.5),       # greedy: the filter is moot
+            EngineRequest("c", "m", [7, 8, 9], max_tokens=3, temperature=1.0)]
+    res = run(drv, reqs)
+    assert all(f[0] == "finished" for _, f in res)
+    assert eng.filter_log and all(f == (40, 0.9) for _, f in eng.filter_log)

@@ -90,3 +90,23 @@ def test_prefix_reuse_and_constraint_on_device(setup):
         assert 1 <= doc["n"] <= 9
     else:       # whitespace padding is bounded, so a random model still has to close the document eventually
         assert fin[1] == "length"
+
+
+def test_candidate_filter_top_k_top_p(setup):
+    cfg, tok, make = setup
+    eng = make()
+    prompt = list(range(30, 50))
+    eng.step(prompt[:16], [0] * 16, list(range(16)))
+    eng.step(prompt[16:], [0] * 4, list(range(16, 20)), temperature=[1.0] * 4, seeds=[7] * 4)
+    row = 3
+    lg = eng.logits[row].float()
+    best = int(lg.argmax())
+    assert eng.filtered_sample(row, 1, 1.0, 1.0, 7, 19) == best                    # top_k = 1 is the argmax
+    assert eng.filtered_sample(row, 0, 1e-6, 1.0, 7, 19) == best                   # a vanishing nucleus too
+    top5 = set(torch.topk(lg, 5).indices.tolist())
+    draws = {eng.filtered_sample(row, 5, 1.0, 5.0, s, 19) for s in range(40)}
+    assert draws <= top5 and len(draws) > 1                                        # hot temperature, still inside top-5
+    assert eng.filtered_sample(row, 5, 1.0, 5.0, 3, 19) == eng.filtered_sample(row, 5, 1.0, 5.0, 3, 19)
+    assert eng.filtered_sample(row, 0, 1.0, 0.0, 3, 19) == best                    # greedy
+    out = eng.step([1], [0], [20], temperature=[2.0], seeds=[5], filters={0: (3, 1.0)})
+    assert int(out[0]) in set(torch.topk(eng.logits[0].float(), 3).indices.tolist())
