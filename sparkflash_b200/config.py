@@ -247,7 +247,7 @@ ENV_OVERRIDES: dict[str, tuple[str, Any]] = {
 }
 # variables that are read elsewhere and are not settings of the engine
 _ENV_PASSTHROUGH = {"SFB_REBUILD", "SFB_NVCC", "SFB_LOG", "SFB_TRACE_SCOPES", "SFB_API_KEY",
-                    "SFB_MODEL_ALIASES", "SFB_DEBUG_BOUNDS"}
+                    "SFB_MODEL_ALIASES", "SFB_DEBUG_BOUNDS", "SFB_FUSED_SPLITS"}
 
 
 @dataclass

@@ -18,6 +18,7 @@ reduce-scatter / all-gather around cuBLAS-free GEMMs), tp4_forward.rs reduce_row
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_int64, c_uint32, c_uint64, c_void_p
 
 import torch
@@ -97,7 +98,8 @@ class RowParallelLinear(_Base):
         self.bytes = self.off_done + 256 - heap_offset
         tiles = ((self.N + 127) // 128) * ((M + self.NP - 1) // self.NP)
         ksteps = self.Kl // 128
-        self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles))) if M <= 128 else 1
+        self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles))) if M < 32 else 1     # measured: from 32 rows on, split-K only adds its reduce
+        self.splits = int(os.environ.get("SFB_FUSED_SPLITS", self.splits))
         self.scratch = torch.zeros((tiles * self.splits * 128 * self.NP,), dtype=torch.float32, device="cuda") if self.splits > 1 else None
         self.tickets = torch.zeros((max(tiles, 1),), dtype=torch.int32, device="cuda")
         self.norm_w, self.eps = norm_w, eps
@@ -183,7 +185,7 @@ class ColumnParallelLinear(_Base):
             self.local_atom[-1].fill_(127)
         tiles = ((self.Nl + 127) // 128) * ((M + self.NP - 1) // self.NP)
         ksteps = self.K // 128
-        self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles))) if M <= 128 else 1
+        self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles))) if M < 32 else 1     # measured: from 32 rows on, split-K only adds its reduce
         self.scratch = torch.zeros((tiles * self.splits * 128 * self.NP,), dtype=torch.float32, device="cuda") if self.splits > 1 else None
         self.tickets = torch.zeros((max(tiles, 1),), dtype=torch.int32, device="cuda")
         self.out = torch.empty((M, self.Nl), dtype=torch.bfloat16, device="cuda")
