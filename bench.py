@@ -109,6 +109,8 @@ def main() -> None:
     ap.add_argument("--collective", default=os.environ.get("SFB_COLLECTIVE", "fused"))
     ap.add_argument("--skip-extras", action="store_true")
     ap.add_argument("--arm", default=os.environ.get("SFB_ARM", "tc"), choices=["tc", "cuda"])
+    ap.add_argument("--moe-mode", default=os.environ.get("SFB_MOE_MODE", "tp"), choices=["tp", "ep"],
+                    help="tp: every expert sliced by width over the ranks; ep: whole experts per rank")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -136,7 +138,7 @@ def main() -> None:
 
     cfg, reduced = pick_config(world, args)
     t0 = time.time()
-    weights = P.prepare_synthetic(cfg, rank, world, device=f"cuda:{local}", seed=0)
+    weights = P.prepare_synthetic(cfg, rank, world, device=f"cuda:{local}", seed=0, moe_mode=args.moe_mode if world > 1 else "tp")
     torch.cuda.synchronize()
     t_init = time.time() - t0
     S = args.streams
@@ -260,7 +262,7 @@ def main() -> None:
             "impl": "ours",
             "config": {"model": cfg.name, "layers": cfg.n_layers, "resident_experts": cfg.n_routed_experts,
                        "reduced_expert_pool": reduced, "global_batch": 1, "seq_len": args.prompt,
-                       "parallelism": f"tp{world}", "collective": args.collective if world > 1 else "none",
+                       "parallelism": (f"tp{world}" if args.moe_mode == "tp" or world == 1 else f"tp{world} attention + ep{world} experts"), "collective": args.collective if world > 1 else "none",
                        "speculation": "off (one token per step)", "sampling": "greedy",
                        "arm": "tcgen05 block-scaled MMA for projections and experts" if args.arm == "tc" else "CUDA-core",
                        "l2": "inputs larger than L2 (every step streams the step's weights, >1 GB per GPU, from HBM)",

@@ -312,6 +312,15 @@ __global__ void __launch_bounds__(256) moe_down_kernel(DownArgs a) {
   }
 }
 
+
+// expert parallelism: global expert ids -> this rank's local ids, -1 for experts held elsewhere (the grouped GEMMs skip them)
+__global__ void expert_remap_kernel(int* ids, int n, int lo, int count) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) { const int e = ids[i] - lo; ids[i] = (e >= 0 && e < count) ? e : -1; }
+}
+
 }  // namespace sfb
 
 using namespace sfb;
@@ -356,3 +365,7 @@ int sfb_moe_down(const void* act_q, const void* act_s, const int* ids, const voi
 }
 
 }  // extern "C"
+
+extern "C" int sfb_expert_remap(void* ids, int n, int lo, int count, cudaStream_t stream) {
+  return (int)sfb::sfb_launch(sfb::expert_remap_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, (int*)ids, n, lo, count);
+}

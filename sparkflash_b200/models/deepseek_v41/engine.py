@@ -414,17 +414,26 @@ class Engine:
                       nsplit=ks, split_stride=self.dots.stride(0)); self._k()
         self._prefetch(n, (), experts=(L.w2, n * k))
         T = self.tcl[l] if self.tcl is not None else None
+        slots = k + 1
+        if self.w.moe_mode == "ep":
+            # whole experts per rank: ids become local (or -1 = held elsewhere, skipped inside the GEMMs); the replicated
+            # shared expert is run by one rank per layer so that its work is spread over the group
+            if T is None or T.w13 is None:
+                raise RuntimeError("expert parallelism runs on the tensor-core arm")
+            N.expert_remap(self.ids, n * k, self.w.expert_lo, self.w.experts_local); self._k()
+            if l % self.world != self.rank:
+                slots = k
         if T is not None and T.w13 is not None:
             tcb = self.tcb
             tbx = tcb.bmap(self.xq, self.max_rows, d, 16)
             N.umma_gate_up(T.w13.tmap, T.s13.tmap, tbx, T.w13.atoms, T.s13.atoms, tcb.xs_atom_tok, self.ids, self.wts,
-                           self.act_q, self.act_s, tcb.act_sf, n, k, k + 1, d, self.il, cfg.swiglu_limit,
+                           self.act_q, self.act_s, tcb.act_sf, n, k, slots, d, self.il, cfg.swiglu_limit,
                            status=self.status); self._k()
             self._prefetch(n, (self._next_wqkv,) if self._next_wqkv is not self.w.head else ())
             tba = tcb.bmap(self.act_q, self.max_rows * (k + 1), self.il, 16)
             self._pushed = self._arm_push(1, 2 * l + 1)
             N.umma_down(T.w2.tmap, T.s2.tmap, tba, T.w2.atoms, T.s2.atoms, tcb.act_sf, self.ids, self.y_ffn, None, d,
-                        tcb.scratch, tcb.tickets, n, k, k + 1, d, self.il, status=self.status); self._k()
+                        tcb.scratch, tcb.tickets, n, k, slots, d, self.il, status=self.status); self._k()
             return
         N.moe_gate_up(self.xq, self.xs, self.ids, self.wts, L.w13, L.w13_sf, L.s13, L.s13_sf, self.act_q, self.act_s,
                       n, k, d, self.il, cfg.swiglu_limit); self._k()

@@ -81,6 +81,9 @@ class DeviceWeights:
     layers: list[LayerW] = field(default_factory=list)
     onehot: torch.Tensor = None      # f32 [hc] = (1, 0, 0, ..)
     il: int = 0                      # stored local intermediate width (moe_inter / world, padded to 128)
+    moe_mode: str = "tp"             # "tp": every expert sliced by width; "ep": whole experts [expert_lo, expert_lo + experts_local)
+    expert_lo: int = 0
+    experts_local: int = 0
 
     def nbytes(self) -> int:
         n = 0
@@ -99,11 +102,11 @@ class DeviceWeights:
         return n
 
 
-def stored_inter(cfg: ModelConfig, world: int) -> int:
+def stored_inter(cfg: ModelConfig, world: int, moe_mode: str = "tp") -> int:
     """Local expert width as stored: the 1/world slice padded with zero rows / zero K to a multiple of 128
     (tensor-core tiles and the packed-FP4 TMA box want it; reference: the 576 -> 640 padded MoE layout,
     crates/sparkflash-deepseek-forward/src/tp4_operands.rs)."""
-    il = cfg.moe_inter // world
+    il = cfg.moe_inter if moe_mode == "ep" else cfg.moe_inter // world
     return (il + 127) // 128 * 128
 
 
@@ -127,7 +130,7 @@ def _prep_sf_block32(sc: torch.Tensor, rows: int) -> torch.Tensor:
     return sc.repeat_interleave(32, 0)[:rows].contiguous()
 
 
-def _layer_from_ckpt(ck: dict, cfg: ModelConfig, p: str, l: int, n_exp: int, rank: int, world: int, dev) -> LayerW:
+def _layer_from_ckpt(ck: dict, cfg: ModelConfig, p: str, l: int, n_exp: int, rank: int, world: int, dev, moe_mode: str = "tp") -> LayerW:
     d, h, hd, q = cfg.hidden_size, cfg.n_heads, cfg.head_dim, cfg.q_lora_rank
     og, ol, mi = cfg.o_groups, cfg.o_lora_rank, cfg.moe_inter
     hl, gl, il = h // world, og // world, mi // world
@@ -179,11 +182,16 @@ def _layer_from_ckpt(ck: dict, cfg: ModelConfig, p: str, l: int, n_exp: int, ran
     # router
     L.gate_w = ck[f"{p}.ffn.gate.weight"].to(torch.bfloat16).contiguous().to(dev)
     L.gate_bias, L.gate_bias_vl = f32(f"{p}.ffn.gate.bias"), f32(f"{p}.ffn.gate.bias_vl")
-    # shared expert
-    i0, i1 = rank * il, (rank + 1) * il
+    # shared expert.  Expert parallelism keeps whole experts: full width, this rank's range of expert ids; the
+    # shared expert is replicated at full width and run by one rank per layer (see Engine._ffn)
+    ep = moe_mode == "ep"
+    if ep:
+        il = mi
+    i0, i1 = (0, mi) if ep else (rank * il, (rank + 1) * il)
     kb_d, kb_i = d // 32, il // 32
+    e_lo, e_n = (rank * (n_exp // world), n_exp // world) if ep else (0, n_exp)
 
-    ils = stored_inter(cfg, world)
+    ils = stored_inter(cfg, world, moe_mode)
 
     def slice13(name):
         w = ck[f"{name}.weight"][i0:i1]
@@ -199,7 +207,7 @@ def _layer_from_ckpt(ck: dict, cfg: ModelConfig, p: str, l: int, n_exp: int, ran
                         ils // 32, 127).contiguous().to(dev)
     # routed experts (fp4, per-row scales)
     w13, w13sf, w2, w2sf = [], [], [], []
-    for e in range(n_exp):
+    for e in range(e_lo, e_lo + e_n):
         ws, ss = [], []
         for nm in ("w1", "w3"):
             ws.append(_pad_rows(ck[f"{p}.ffn.experts.{e}.{nm}.weight"][i0:i1], ils))
@@ -214,7 +222,7 @@ def _layer_from_ckpt(ck: dict, cfg: ModelConfig, p: str, l: int, n_exp: int, ran
     return L
 
 
-def prepare_from_checkpoint(ck: dict, cfg: ModelConfig, rank: int = 0, world: int = 1, device="cuda") -> DeviceWeights:
+def prepare_from_checkpoint(ck: dict, cfg: ModelConfig, rank: int = 0, world: int = 1, device="cuda", moe_mode: str = "tp") -> DeviceWeights:
     dev = torch.device(device)
     W = DeviceWeights(cfg, rank, world)
     V = cfg.vocab_size
@@ -226,14 +234,19 @@ def prepare_from_checkpoint(ck: dict, cfg: ModelConfig, rank: int = 0, world: in
     oh = torch.zeros(cfg.hc_mult, dtype=torch.float32)
     oh[0] = 1.0
     W.onehot = oh.to(dev)
-    W.il = stored_inter(cfg, world)
+    if moe_mode == "ep" and cfg.n_routed_experts % world:
+        raise ValueError("expert parallelism needs the expert count to divide by the world size")
+    W.il = stored_inter(cfg, world, moe_mode)
+    W.moe_mode = moe_mode
+    W.experts_local = cfg.n_routed_experts // world if moe_mode == "ep" else cfg.n_routed_experts
+    W.expert_lo = rank * W.experts_local if moe_mode == "ep" else 0
     for l in range(cfg.n_layers):
-        W.layers.append(_layer_from_ckpt(ck, cfg, f"layers.{l}", l, cfg.n_routed_experts, rank, world, dev))
+        W.layers.append(_layer_from_ckpt(ck, cfg, f"layers.{l}", l, cfg.n_routed_experts, rank, world, dev, moe_mode))
     return W
 
 
 # ---- synthetic, generated on the device -----------------------------------------------------------------
-def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="cuda", seed: int = 0) -> DeviceWeights:
+def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="cuda", seed: int = 0, moe_mode: str = "tp") -> DeviceWeights:
     """Random-init weights (~N(0, 0.02), norms ~1) written straight into the prepared layout.
 
     Payload bytes come from ``sfb_synth_fill`` (a hash of the tensor's seed and the element index);
@@ -245,8 +258,9 @@ def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="c
     d, h, hd, q = cfg.hidden_size, cfg.n_heads, cfg.head_dim, cfg.q_lora_rank
     og, ol, mi, hc = cfg.o_groups, cfg.o_lora_rank, cfg.moe_inter, cfg.hc_mult
     hl, gl = h // world, og // world
-    il = stored_inter(cfg, world)   # padding rows / K of a synthetic expert are ordinary random values
+    il = stored_inter(cfg, world, moe_mode)   # padding rows / K of a synthetic expert are ordinary random values
     E, V = cfg.n_routed_experts, cfg.vocab_size
+    El = E // world if moe_mode == "ep" else E     # experts held by this rank
     mix = (2 + hc) * hc
     FP8_CODE, FP4_CODE = 115, 120
     sig8 = 0.02 / 2.0 ** (FP8_CODE - 127)
@@ -280,6 +294,7 @@ def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="c
     oh[0] = 1.0
     W.onehot = oh.to(dev)
     W.il = il
+    W.moe_mode, W.experts_local, W.expert_lo = moe_mode, El, (rank * El if moe_mode == "ep" else 0)
     for l in range(cfg.n_layers):
         p = f"layers.{l}"
         L = LayerW()
@@ -318,11 +333,11 @@ def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="c
         N.synth_fill(0, L.s13, L.s13.numel(), sd(f"{p}.s13", True), sig8)
         L.s13_sf = torch.full((2, sfb13), FP8_CODE, dtype=torch.uint8, device=dev)
         L.s2, L.s2_sf = fp8(f"{p}.s2", d, il, shard=True)
-        L.w13 = torch.empty((E, 2, il, d // 2), dtype=torch.uint8, device=dev)
+        L.w13 = torch.empty((El, 2, il, d // 2), dtype=torch.uint8, device=dev)
         N.synth_fill(1, L.w13, L.w13.numel(), sd(f"{p}.w13", True), sig4)
-        L.w13_sf = torch.full((E, 2, sfb13), FP4_CODE, dtype=torch.uint8, device=dev)
-        L.w2 = torch.empty((E, d, il // 2), dtype=torch.uint8, device=dev)
+        L.w13_sf = torch.full((El, 2, sfb13), FP4_CODE, dtype=torch.uint8, device=dev)
+        L.w2 = torch.empty((El, d, il // 2), dtype=torch.uint8, device=dev)
         N.synth_fill(1, L.w2, L.w2.numel(), sd(f"{p}.w2", True), sig4)
-        L.w2_sf = torch.full((E, sfb2), FP4_CODE, dtype=torch.uint8, device=dev)
+        L.w2_sf = torch.full((El, sfb2), FP4_CODE, dtype=torch.uint8, device=dev)
         W.layers.append(L)
     return W

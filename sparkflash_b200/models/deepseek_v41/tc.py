@@ -59,7 +59,7 @@ def attach(weights: DeviceWeights, synthetic: bool = False) -> list[TcLayer]:
     d, q, hd = cfg.hidden_size, cfg.q_lora_rank, cfg.head_dim
     gl, il = cfg.o_groups // W, weights.il or cfg.moe_inter // W
     ol, gin = cfg.o_lora_rank, cfg.group_in
-    E = cfg.n_routed_experts
+    E = weights.experts_local or cfg.n_routed_experts        # experts held by this rank (expert parallelism keeps a range)
     c8 = 115 if synthetic else None
     c4 = 120 if synthetic else None
     out = []

@@ -177,6 +177,10 @@ def router_topk(dots, bias, bias_vl, is_image, ids, wts, n, E, k, route_scale, n
     _check(code, "router_topk")
 
 
+def expert_remap(ids, n, lo, count):
+    _check(lib().sfb_expert_remap(_p(ids), c_int(n), c_int(lo), c_int(count), _stream()), "expert_remap")
+
+
 def moe_gate_up(xq, xs, ids, wts, w13, w13_sf, s13, s13_sf, act_q, act_s, n, k, d, inter, limit):
     code = lib().sfb_moe_gate_up(_p(xq), _p(xs), _p(ids), _p(wts), _p(w13), _p(w13_sf), _p(s13), _p(s13_sf),
                                  _p(act_q), _p(act_s), c_int(n), c_int(k), c_int(d), c_int(inter), c_float(limit),
