@@ -109,6 +109,7 @@ def main() -> None:
     ap.add_argument("--collective", default=os.environ.get("SFB_COLLECTIVE", "fused"))
     ap.add_argument("--skip-extras", action="store_true")
     ap.add_argument("--arm", default=os.environ.get("SFB_ARM", "tc"), choices=["tc", "cuda"])
+    ap.add_argument("--mtp", action="store_true", help="also build the DSpark draft stages and report the per-forward latency of a draft block")
     ap.add_argument("--moe-mode", default=os.environ.get("SFB_MOE_MODE", "tp"), choices=["tp", "ep"],
                     help="tp: every expert sliced by width over the ranks; ep: whole experts per rank")
     args = ap.parse_args()
@@ -138,13 +139,13 @@ def main() -> None:
 
     cfg, reduced = pick_config(world, args)
     t0 = time.time()
-    weights = P.prepare_synthetic(cfg, rank, world, device=f"cuda:{local}", seed=0, moe_mode=args.moe_mode if world > 1 else "tp")
+    weights = P.prepare_synthetic(cfg, rank, world, device=f"cuda:{local}", seed=0, moe_mode=args.moe_mode if world > 1 else "tp", mtp=args.mtp)
     torch.cuda.synchronize()
     t_init = time.time() - t0
     S = args.streams
     max_ctx = args.prompt + args.steps * 2 + args.warmup * 2 + 1024
     eng = E.Engine(weights, max_lanes=max(S, 1), max_context=max_ctx, max_rows=64, comm=comm, arm=args.arm,
-                   synthetic_scales=True)
+                   synthetic_scales=True, drafter=args.mtp)
     if comm is not None:
         comm.attach(eng)
     b = 1024
@@ -240,6 +241,20 @@ def main() -> None:
                   "prefill_tok_s": prefill_tok_s, "prefill_prompt_tokens": len(prompt),
                   "prefill_note": "rows steps of 64 (CUDA-core arm)",
                   "vs_baseline_prefill": prefill_tok_s / BASELINE_PREFILL_TOK_S}
+    if args.mtp:
+        # DSpark on: cost of one draft block (3 stages x 5 positions + Markov chain) per forward; acceptance is meaningless
+        # with random weights, so only the latency is reported.  The timed single-stream figure above already includes the
+        # per-step seeding of the draft stages' window keys.
+        for _ in range(3):
+            eng.draft(0, pos - 1, nxt)
+        barrier()
+        ev0.record()
+        for _ in range(8):
+            eng.draft(0, pos - 1, nxt)
+        ev1.record()
+        barrier()
+        extras["dspark_draft_block_ms"] = ev0.elapsed_time(ev1) / 8
+        extras["dspark_block_positions"] = cfg.dspark_block
     eng.check_status()
 
     def maxr(x: float) -> float:

@@ -36,6 +36,10 @@ struct AttnArgs {
   uint8_t* out_atom;        // its scale atoms (rows = hi rows then lo rows)
   int n, heads, rd, window, ring;
   float scale;
+  // optional explicit window per row: positions [win_lo[row], win_hi[row]] of the ring instead of the causal window that
+  // ends at the row's own position (draft blocks attend their whole block: no causal mask inside it)
+  const int* win_lo;
+  const int* win_hi;
 };
 
 constexpr int AT_HPB = 4;       // heads per block = warps per block
@@ -84,8 +88,8 @@ __global__ void __cluster_dims__(AT_SPLITS, 1, 1) __launch_bounds__(AT_THREADS) 
 #pragma unroll
   for (int j = 0; j < EPL; ++j) ql[j] = qs[warp * HD + lane * EPL + j];
 
-  const int w_first = pos - a.window + 1 > 0 ? pos - a.window + 1 : 0;
-  const int n_win = pos - w_first + 1;
+  const int w_first = a.win_lo ? a.win_lo[row] : (pos - a.window + 1 > 0 ? pos - a.window + 1 : 0);
+  const int n_win = (a.win_hi ? a.win_hi[row] : pos) - w_first + 1;
   const int n_sel = a.ckv_q ? a.sel_count[row] : 0;
   const int total = n_win + n_sel;
   const int e_lo = (int)((int64_t)total * sp / AT_SPLITS), e_hi = (int)((int64_t)total * (sp + 1) / AT_SPLITS);
@@ -260,17 +264,35 @@ using namespace sfb;
 
 extern "C" {
 
+int sfb_attn_rows_range(const void* q, int64_t q_stride, const void* rope, int rope_stride, const int* row_lane,
+                        const int* row_pos, const void* win_q, const void* win_s, int64_t win_lane_q,
+                        int64_t win_lane_s, const void* ckv_q, const void* ckv_s, int64_t ckv_lane_q,
+                        int64_t ckv_lane_s, const int* sel, const int* sel_count, int K, const float* sink,
+                        void* out, void* out_q, void* out_atom, int n, int heads, int hd, int rd, int window, int ring,
+                        float scale, const int* win_lo, const int* win_hi, cudaStream_t stream);
+
 int sfb_attn_rows(const void* q, int64_t q_stride, const void* rope, int rope_stride, const int* row_lane,
                   const int* row_pos, const void* win_q, const void* win_s, int64_t win_lane_q,
                   int64_t win_lane_s, const void* ckv_q, const void* ckv_s, int64_t ckv_lane_q,
                   int64_t ckv_lane_s, const int* sel, const int* sel_count, int K, const float* sink,
                   void* out, void* out_q, void* out_atom, int n, int heads, int hd, int rd, int window, int ring,
                   float scale, cudaStream_t stream) {
+  return sfb_attn_rows_range(q, q_stride, rope, rope_stride, row_lane, row_pos, win_q, win_s, win_lane_q, win_lane_s, ckv_q, ckv_s,
+                             ckv_lane_q, ckv_lane_s, sel, sel_count, K, sink, out, out_q, out_atom, n, heads, hd, rd, window, ring,
+                             scale, nullptr, nullptr, stream);
+}
+
+int sfb_attn_rows_range(const void* q, int64_t q_stride, const void* rope, int rope_stride, const int* row_lane,
+                        const int* row_pos, const void* win_q, const void* win_s, int64_t win_lane_q,
+                        int64_t win_lane_s, const void* ckv_q, const void* ckv_s, int64_t ckv_lane_q,
+                        int64_t ckv_lane_s, const int* sel, const int* sel_count, int K, const float* sink,
+                        void* out, void* out_q, void* out_atom, int n, int heads, int hd, int rd, int window, int ring,
+                        float scale, const int* win_lo, const int* win_hi, cudaStream_t stream) {
   if ((hd / 32) % 2) return (int)cudaErrorInvalidValue;
   AttnArgs a{(const __nv_bfloat16*)q, q_stride, (const float2*)rope, rope_stride, row_lane, row_pos, (const uint8_t*)win_q,
              (const uint8_t*)win_s, win_lane_q, win_lane_s, (const uint8_t*)ckv_q, (const uint8_t*)ckv_s,
              ckv_lane_q, ckv_lane_s, sel, sel_count, K, sink, (__nv_bfloat16*)out, (uint8_t*)out_q, (uint8_t*)out_atom,
-             n, heads, rd, window, ring, scale};
+             n, heads, rd, window, ring, scale, win_lo, win_hi};
   dim3 grid(AT_SPLITS, (heads + AT_HPB - 1) / AT_HPB, n);
   const size_t smem = sizeof(float) * (size_t)(AT_HPB * hd + AT_THREADS * 32 + AT_HPB * (hd + 2));
   cudaError_t launch_rc = cudaSuccess;

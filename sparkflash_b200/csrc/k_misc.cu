@@ -30,6 +30,20 @@ __global__ void embed_override_kernel(const __nv_bfloat16* override_rows, const 
   for (int c = 0; c < hc; ++c) *reinterpret_cast<uint4*>(h + ((size_t)row * hc + c) * d + col) = v;
 }
 
+// Markov head of the draft block: logits[row, v] += dot(head[v, :], embed[prev, :]) with prev read from device memory
+// (the token sampled for the previous block position), one warp per vocabulary entry.
+__global__ void __launch_bounds__(256) markov_bias_kernel(float* logits, const __nv_bfloat16* head, const __nv_bfloat16* embed,
+                                                         const int* prev, int vl, int r, int vocab) {
+  const int v = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (v >= vl) return;
+  int p = *prev;
+  if (p < 0 || p >= vocab) p = 0;
+  float s = 0.f;
+  for (int i = lane; i < r; i += 32) s += bf16_to_f(head[(size_t)v * r + i]) * bf16_to_f(embed[(size_t)p * r + i]);
+  s = warp_sum(s);
+  if (lane == 0) logits[v] += s;
+}
+
 // tap[row, :] = bf16(mean over copies of h[row, c, :])
 __global__ void tap_mean_kernel(const __nv_bfloat16* h, __nv_bfloat16* tap, int64_t tap_stride, int hc, int d) {
   const int row = blockIdx.y;
@@ -230,6 +244,11 @@ int sfb_embed(const void* embed, const int* tokens, void* h, int n, int hc, int 
   if (d % 8) return (int)cudaErrorInvalidValue;
   embed_kernel<<<dim3((d / 8 + 127) / 128, n), 128, 0, stream>>>((const __nv_bfloat16*)embed, tokens,
                                                                (__nv_bfloat16*)h, n, hc, d, vocab, (Status*)status);
+  return SFB_CHECK_LAUNCH();
+}
+
+int sfb_markov_bias(void* logits_row, const void* head, const void* embed, const int* prev, int vl, int r, int vocab, cudaStream_t stream) {
+  markov_bias_kernel<<<(vl + 7) / 8, 256, 0, stream>>>((float*)logits_row, (const __nv_bfloat16*)head, (const __nv_bfloat16*)embed, prev, vl, r, vocab);
   return SFB_CHECK_LAUNCH();
 }
 

@@ -25,7 +25,8 @@ class KVCache:
     """Position-addressed caches for ``lanes`` sequences (fixed-capacity arm; the lazily backed arm
     lives in kv/lanes.py).  Window ring slots = position % ring; compressed entry = position // ratio."""
 
-    def __init__(self, cfg: ModelConfig, lanes: int, max_context: int, max_rows: int, device, lane_budget_bytes: int | None = None):
+    def __init__(self, cfg: ModelConfig, lanes: int, max_context: int, max_rows: int, device, lane_budget_bytes: int | None = None,
+                 draft_stages: bool = False):
         """``lane_budget_bytes``: back the per-position regions (compressed KV, index keys) lazily from a chunk
         pool of this size instead of allocating ``lanes * max_context`` up front (kv/lanes.py)."""
         self.cfg, self.lanes, self.max_context = cfg, lanes, max_context
@@ -43,10 +44,10 @@ class KVCache:
         u8 = dict(dtype=torch.uint8, device=device)
         self.win_q, self.win_s, self.cin, self.ckv_q, self.ckv_s, self.ik_q, self.ik_s = {}, {}, {}, {}, {}, {}, {}
         self.max_entries = {}
-        for l in range(cfg.n_layers):
+        for l in range(cfg.n_layers + (cfg.n_mtp_stages if draft_stages else 0)):
             self.win_q[l] = torch.zeros((lanes, ring, hd), **u8)
             self.win_s[l] = torch.zeros((lanes, ring, hd // 32), **u8)
-            if cfg.is_kv_source(l):
+            if l < cfg.n_layers and cfg.is_kv_source(l):
                 r = cfg.ratio(l)
                 me = max_context // r + 1
                 self.max_entries[l] = me
@@ -113,7 +114,7 @@ class Engine:
     def __init__(self, weights: DeviceWeights, max_lanes: int = 4, max_context: int = 4096, max_rows: int = 64,
                  comm=None, use_graphs: bool = True, keep_logits: bool = False, arm: str = "cuda",
                  synthetic_scales: bool = False, constrained: bool = False, lane_budget_bytes: int | None = None,
-                 vision: bool = False):
+                 vision: bool = False, drafter: bool = False):
         """``arm``: "cuda" = CUDA-core exact arm for every projection; "tc" = tcgen05 tensor-core arm for
         every shape it takes (the rest falls back to the CUDA-core kernels)."""
         self.w, self.cfg = weights, weights.cfg
@@ -131,7 +132,8 @@ class Engine:
         # image rows: input embedding supplied by the caller (vision tower output / delimiter vectors), routed with
         # the vision-language router bias
         self.supports_vision = vision
-        self.kv = KVCache(cfg, max_lanes, max_context, max_rows, self.dev, lane_budget_bytes)
+        self.drafter = bool(drafter and weights.mtp_layers)
+        self.kv = KVCache(cfg, max_lanes, max_context, max_rows, self.dev, lane_budget_bytes, draft_stages=self.drafter)
         R, d, hc, hd, q = max_rows, cfg.hidden_size, cfg.hc_mult, cfg.head_dim, cfg.q_lora_rank
         W = self.world
         self.hl, self.gl, self.vl = cfg.n_heads // W, cfg.o_groups // W, cfg.vocab_size // W
@@ -209,6 +211,27 @@ class Engine:
             self._splits = TC.pick_splits
         elif arm != "cuda":
             raise ValueError(f"unknown arm {arm!r}")
+        if self.drafter:
+            if arm != "tc":
+                raise ValueError("the DSpark drafter runs on the tensor-core arm")
+            from . import tc as TC
+            from ... import codecs as CC
+            K3 = len(cfg.dspark_taps) * d
+            self.tcl_mtp = TC.attach(weights, synthetic=synthetic_scales, layers=weights.mtp_layers, n_experts=cfg.dspark_n_experts)
+            self.T_main = TC._matrix(weights.mtp_main_proj, weights.mtp_main_proj_sf, d, K3, False, 115 if synthetic_scales else None)
+            u8 = dict(dtype=torch.uint8, device=dev)
+            self.taps_q = torch.zeros((R, K3), **u8)
+            self.taps_atom = torch.full((CC.sf_bytes(128, K3 // 32),), 127, **u8)
+            self.main_raw, self.main_x = e((R, d), bf), e((R, d), bf)
+            self.main_xq = torch.zeros((R, d), **u8)
+            self.main_atom = torch.full((CC.sf_bytes(128, d // 32),), 127, **u8)
+            self.rope_identity = torch.zeros((R, cfg.rope_dim // 2, 2), dtype=torch.float32, device=dev)
+            self.rope_identity[..., 0] = 1.0
+            self.draft_lo, self.draft_hi = e((R,), i32), e((R,), i32)
+            self.draft_tokens = torch.zeros((cfg.dspark_block + 1,), dtype=torch.int32, device=dev)
+            self.draft_conf = torch.zeros((cfg.dspark_block,), dtype=torch.float32, device=dev)
+            self._draft_bv = torch.zeros((max(1, self.world),), dtype=torch.float32, device=dev)
+            self._draft_bi = torch.zeros((max(1, self.world),), dtype=torch.int32, device=dev)
         self.graphs: dict[tuple[int, int], torch.cuda.CUDAGraph] = {}
         self.launches_per_step = 0
         self._counting = False
@@ -323,13 +346,15 @@ class Engine:
         v = self.rope_variants.index((compressed, ratio))
         return self.rope[:, v]
 
-    def _attention(self, n: int, l: int, L: LayerW, len_bucket: int):
+    def _attention(self, n: int, l: int, L: LayerW, len_bucket: int, T="auto", win=None, sub: int | None = None):
         cfg, kv = self.cfg, self.kv
         d, hd, q, rd = cfg.hidden_size, cfg.head_dim, cfg.q_lora_rank, cfg.rope_dim
         ratio = cfg.ratio(l)
         invf = self._rope_view(ratio > 0, 1)                     # at the row's own position
         invf_c = self._rope_view(True, ratio) if ratio > 0 else None   # at the compressed position
-        T = self.tcl[l] if self.tcl is not None else None
+        if T == "auto":
+            T = self.tcl[l] if self.tcl is not None else None
+        sub = 2 * l if sub is None else sub
         if T is not None and T.wqkv_a is not None:
             self._tc_dense(T.wqkv_a, self.xq, self.max_rows, self.tcb.xs_atom, n, q + hd, d, self.qkv_raw)
         else:
@@ -379,7 +404,8 @@ class Engine:
                     kv.ckv_q[owner] if has_c else None, kv.ckv_s[owner] if has_c else None,
                     self.sel if has_c else None, self.sel_cnt if has_c else None, cfg.index_topk, L.sink,
                     self.attn_out, n, self.hl, hd, rd, cfg.window, kv.ring, hd ** -0.5,
-                    out_q=self.tcb.ao_q if tc_wo_a else None, out_atom=self.tcb.ao_atom if tc_wo_a else None); self._k()
+                    out_q=self.tcb.ao_q if tc_wo_a else None, out_atom=self.tcb.ao_atom if tc_wo_a else None,
+                    win_lo=win[0] if win else None, win_hi=win[1] if win else None); self._k()
         ol, gin = cfg.o_lora_rank, cfg.group_in
         tc_wo_b = T is not None and T.wo_b is not None
         fused_oa_q = False
@@ -397,25 +423,28 @@ class Engine:
             tcb = self.tcb
             if not fused_oa_q:
                 N.quant_rows(self.oa, tcb.oa_q, None, tcb.oa_atom, n, self.gl * ol); self._k()
-            self._pushed = self._arm_push(0, 2 * l)
+            self._pushed = self._arm_push(0, sub)
             self._tc_dense(T.wo_b, tcb.oa_q, self.max_rows, tcb.oa_atom, n, d, self.gl * ol, self.y_attn)
         else:
             N.gemv(N.WF_FP8, L.wo_b, L.wo_b_sf, self.gl * ol, d, self.gl * ol, n, xb=self.oa, x_quant=True,
                    out_b=self.y_attn); self._k()
 
-    def _ffn(self, n: int, L: LayerW, l: int = 0):
+    def _ffn(self, n: int, L: LayerW, l: int = 0, T="auto", E: int | None = None, k: int | None = None, sub: int | None = None):
         cfg = self.cfg
         self._pushed = False
-        d, E, k = cfg.hidden_size, cfg.n_routed_experts, cfg.top_k
+        d, E, k = cfg.hidden_size, E or cfg.n_routed_experts, k or cfg.top_k
+        draft = T != "auto"
+        sub = 2 * l + 1 if sub is None else sub
         ks = self.gate_ksplit
         N.gemv(N.WF_BF16, L.gate_w, None, 2 * d, E, d, n, xb=self.xn, out_f=self.dots, out_stride=E, ksplit=ks,
                split_stride=self.dots.stride(0)); self._k()
         N.router_topk(self.dots, L.gate_bias, L.gate_bias_vl, self.img_mask, self.ids, self.wts, n, E, k, cfg.route_scale,
                       nsplit=ks, split_stride=self.dots.stride(0)); self._k()
         self._prefetch(n, (), experts=(L.w2, n * k))
-        T = self.tcl[l] if self.tcl is not None else None
+        if T == "auto":
+            T = self.tcl[l] if self.tcl is not None else None
         slots = k + 1
-        if self.w.moe_mode == "ep":
+        if self.w.moe_mode == "ep" and not draft:
             # whole experts per rank: ids become local (or -1 = held elsewhere, skipped inside the GEMMs); the replicated
             # shared expert is run by one rank per layer so that its work is spread over the group
             if T is None or T.w13 is None:
@@ -431,7 +460,7 @@ class Engine:
                            status=self.status); self._k()
             self._prefetch(n, (self._next_wqkv,) if self._next_wqkv is not self.w.head else ())
             tba = tcb.bmap(self.act_q, self.max_rows * (k + 1), self.il, 16)
-            self._pushed = self._arm_push(1, 2 * l + 1)
+            self._pushed = self._arm_push(1, sub)
             N.umma_down(T.w2.tmap, T.s2.tmap, tba, T.w2.atoms, T.s2.atoms, tcb.act_sf, self.ids, self.y_ffn, None, d,
                         tcb.scratch, tcb.tickets, n, k, slots, d, self.il, status=self.status); self._k()
             return
@@ -504,6 +533,8 @@ class Engine:
             self._dbg(f"L{l}.route_ids", self.ids, n); self._dbg(f"L{l}.route_w", self.wts, n)
             y_prev = self._reduce_parts(self.y_ffn, n, 1, 2 * l + 1, self._pushed)
             yield ("ffn", l)
+        if self.drafter:
+            self._dspark_seed(n)
         self._seam(n, k, y_prev, None, None, None, w.norm, quant=False)
         self._dbg("final_x", self.xn, n); self._dbg("final_h", self.h, n)
         N.gemv(N.WF_BF16, w.head, None, 2 * cfg.hidden_size, self.vl, cfg.hidden_size, n, xb=self.xn,
@@ -523,6 +554,105 @@ class Engine:
                 self.comm.gather_best(self.best_val, self.best_id, n)
             N.sample_fold(self.best_val, self.best_id, self.world if self.comm is not None else 1, n, R,
                           self.tokens_out); self._k()
+        self._join_prefetch()
+
+    # ---- DSpark draft stages ------------------------------------------------------------------------------
+    # Reference semantics: docs/architecture/05-dspark.md of the reference (taps of three block inputs -> main_proj -> main_norm;
+    # every backbone position leaves one un-rotated key per stage; a block of [anchor, noise x 4] runs the three stages with
+    # window attention over [128 main keys ; its own 5 keys] without a causal mask; shared head + Markov bias + sequential
+    # sampling; confidence logit per position).
+    def _dspark_seed(self, n: int) -> None:
+        cfg, w, kv = self.cfg, self.w, self.kv
+        d, q, hd = cfg.hidden_size, cfg.q_lora_rank, cfg.head_dim
+        K3 = len(cfg.dspark_taps) * d
+        R = self.max_rows
+        N.quant_rows(self.taps, self.taps_q, None, self.taps_atom, n, K3); self._k()
+        if self.T_main is not None:
+            self._tc_dense(self.T_main, self.taps_q, R, self.taps_atom, n, d, K3, self.main_raw)
+        else:
+            N.gemv(N.WF_FP8, w.mtp_main_proj, w.mtp_main_proj_sf, K3, d, K3, n, xb=self.taps, out_b=self.main_raw); self._k()
+        N.rmsnorm_quant(self.main_raw, w.mtp_main_norm, cfg.norm_eps, self.main_x, self.main_xq, self.main_atom, n=n); self._k()
+        for s_, L in enumerate(w.mtp_layers):
+            T = self.tcl_mtp[s_]
+            if T.wqkv_a is not None:
+                self._tc_dense(T.wqkv_a, self.main_xq, R, self.main_atom, n, q + hd, d, self.qkv_raw)
+            else:
+                N.gemv(N.WF_FP8, L.wqkv_a, L.wqkv_a_sf, d, q + hd, d, n, xb=self.main_x, out_b=self.qkv_raw); self._k()
+            # kv_norm + FP8 into the stage's own ring at the row's position, no rotation (identity table)
+            N.qkv_post(self.qkv_raw, L.q_norm, L.kv_norm, self.rope_identity, self.row_lane, self.row_pos, self.qr_q, self.qr_s,
+                       kv.win_q[cfg.n_layers + s_], kv.win_s[cfg.n_layers + s_], n, q, hd, cfg.rope_dim, kv.ring, cfg.norm_eps,
+                       qr_atom=self.tcb.qr_atom); self._k()
+
+    def draft(self, lane: int, pos: int, anchor: int, temperature: float = 0.0, seed: int = 0):
+        """One draft block after the backbone handled position ``pos`` of ``lane`` and ``anchor`` was sampled for pos + 1.
+        Returns (tokens proposed for positions pos + 2 .., confidence logits), both lists of ``dspark_block``."""
+        if not self.drafter:
+            raise RuntimeError("engine was built without drafter=True (or the weights carry no draft stages)")
+        if self.w.moe_mode == "ep":
+            raise NotImplementedError("the draft stages are width-sliced; run them with moe_mode='tp'")
+        cfg, w = self.cfg, self.w
+        B = cfg.dspark_block
+        noise = cfg.dspark_noise_token % cfg.vocab_size
+        io = self.io
+        io.tokens[:B] = torch.tensor([anchor] + [noise] * (B - 1), dtype=torch.int32)
+        io.lanes[:B] = lane
+        io.pos[:B] = torch.arange(pos + 1, pos + 1 + B, dtype=torch.int32)
+        io.temp[:B] = temperature
+        io.seed[:B] = seed
+        for dst, src in ((self.tokens, io.tokens), (self.row_lane, io.lanes), (self.row_pos, io.pos), (self.temp, io.temp), (self.seed, io.seed)):
+            dst[:B].copy_(src[:B], non_blocking=True)
+        self.draft_lo[:B] = max(0, pos - cfg.window + 1)
+        self.draft_hi[:B] = pos + B
+        for _ in self._draft_gen(B):
+            pass
+        out = self.draft_tokens[1:B + 1].tolist()
+        return out, self.draft_conf[:B].tolist()
+
+    def _draft_gen(self, n: int):
+        cfg, w = self.cfg, self.w
+        d = cfg.hidden_size
+        if self._fused():
+            self.comm.begin_step(); self._k()
+        N.embed(w.embed, self.tokens, self.h, n, cfg.hc_mult, d, cfg.vocab_size, self.status); self._k()
+        N.rope_table([w.inv_freq[c] for c, _ in self.rope_variants], [r for _, r in self.rope_variants], self.row_pos, self.rope, n); self._k()
+        k = 0
+        y_prev = None
+        win = (self.draft_lo, self.draft_hi)
+        for s_, L in enumerate(w.mtp_layers):
+            l = cfg.n_layers + s_
+            T = self.tcl_mtp[s_]
+            self._seam(n, k, y_prev, L.hc_attn_fn, L.hc_attn_base, L.hc_attn_scale, L.attn_norm); k += 1
+            self._attention(n, l, L, 1024, T=T, win=win, sub=2 * s_)
+            parts = self._reduce_parts(self.y_attn, n, 0, 2 * s_, self._pushed)
+            yield ("attn", l)
+            self._seam(n, k, parts, L.hc_ffn_fn, L.hc_ffn_base, L.hc_ffn_scale, L.ffn_norm, atoms=1); k += 1
+            self._next_wqkv = w.head
+            self._ffn(n, L, l, T=T, E=cfg.dspark_n_experts, k=cfg.dspark_top_k, sub=2 * s_ + 1)
+            y_prev = self._reduce_parts(self.y_ffn, n, 1, 2 * s_ + 1, self._pushed)
+            yield ("ffn", l)
+        self._seam(n, k, y_prev, None, None, None, w.mtp_norm, quant=False)
+        N.gemv(N.WF_BF16, w.head, None, 2 * d, self.vl, d, n, xb=self.xn, out_f=self.logits); self._k()
+        # Markov head: position i's logits get a bias that depends on the token chosen for position i - 1 (the anchor for
+        # i = 0), then position i is sampled; the chain runs on the device through draft_tokens
+        r = w.markov_embed.shape[1]
+        R = self.max_rows
+        self.draft_tokens[:1].copy_(self.tokens[:1])
+        sub = 2 * len(w.mtp_layers)
+        for i in range(n):
+            N.markov_bias(self.logits[i], w.markov_head, w.markov_embed, self.draft_tokens[i:i + 1], self.vl, r, cfg.vocab_size); self._k()
+            N.sample(self.logits[i:i + 1], self.row_pos[i:i + 1], self.temp[i:i + 1], self.seed[i:i + 1], None, self.best_val[self.rank][i:i + 1],
+                     self.best_id[self.rank][i:i + 1], 1, self.vl, self.rank * self.vl); self._k()
+            if self.world > 1 and self.comm is not None:
+                # winners of the vocabulary slices: exchanged with the baseline collective (a draft block is off the critical
+                # path of the verified step)
+                import torch.distributed as dist
+                dist.all_gather_into_tensor(self._draft_bv, self.best_val[self.rank][i:i + 1])
+                dist.all_gather_into_tensor(self._draft_bi, self.best_id[self.rank][i:i + 1])
+                N.sample_fold(self._draft_bv, self._draft_bi, self.world, 1, 1, self.draft_tokens[i + 1:i + 2]); self._k()
+            else:
+                N.sample_fold(self.best_val[:, i:], self.best_id[:, i:], 1, 1, R, self.draft_tokens[i + 1:i + 2]); self._k()
+        emb = w.markov_embed[self.draft_tokens[:n].long()].float()
+        self.draft_conf[:n] = self.xn[:n].float() @ w.conf_w[:d] + emb @ w.conf_w[d:]
         self._join_prefetch()
 
     # ---- public step -------------------------------------------------------------------------------------

@@ -81,6 +81,15 @@ class DeviceWeights:
     layers: list[LayerW] = field(default_factory=list)
     onehot: torch.Tensor = None      # f32 [hc] = (1, 0, 0, ..)
     il: int = 0                      # stored local intermediate width (moe_inter / world, padded to 128)
+    # DSpark draft stages (empty list = no drafter): blocks like the backbone's with ratio-0 attention and their own expert pool
+    mtp_layers: list = field(default_factory=list)
+    mtp_main_proj: torch.Tensor = None     # e4m3 [d, taps*d]
+    mtp_main_proj_sf: torch.Tensor = None
+    mtp_main_norm: torch.Tensor = None     # f32 [d]
+    mtp_norm: torch.Tensor = None          # f32 [d]
+    markov_embed: torch.Tensor = None      # bf16 [V, r] (replicated)
+    markov_head: torch.Tensor = None       # bf16 [V/W, r] (vocabulary slice)
+    conf_w: torch.Tensor = None            # f32 [d + r]
     moe_mode: str = "tp"             # "tp": every expert sliced by width; "ep": whole experts [expert_lo, expert_lo + experts_local)
     expert_lo: int = 0
     experts_local: int = 0
@@ -242,11 +251,24 @@ def prepare_from_checkpoint(ck: dict, cfg: ModelConfig, rank: int = 0, world: in
     W.expert_lo = rank * W.experts_local if moe_mode == "ep" else 0
     for l in range(cfg.n_layers):
         W.layers.append(_layer_from_ckpt(ck, cfg, f"layers.{l}", l, cfg.n_routed_experts, rank, world, dev, moe_mode))
+    if cfg.n_mtp_stages and "mtp.0.main_proj.weight" in ck:
+        last = cfg.n_mtp_stages - 1
+        for s_ in range(cfg.n_mtp_stages):       # the draft experts stay width-sliced (tensor parallel) in both modes
+            W.mtp_layers.append(_layer_from_ckpt(ck, cfg, f"mtp.{s_}", cfg.n_layers + s_, cfg.dspark_n_experts, rank, world, dev, "tp"))
+        d = cfg.hidden_size
+        W.mtp_main_proj = ck["mtp.0.main_proj.weight"].contiguous().to(dev)
+        W.mtp_main_proj_sf = _prep_sf_block32(ck["mtp.0.main_proj.scale"], d).to(dev)
+        W.mtp_main_norm = ck["mtp.0.main_norm.weight"].to(torch.float32).to(dev)
+        W.mtp_norm = ck[f"mtp.{last}.norm.weight"].to(torch.float32).to(dev)
+        W.markov_embed = ck[f"mtp.{last}.markov_head.embed.weight"].to(torch.bfloat16).contiguous().to(dev)
+        W.markov_head = ck[f"mtp.{last}.markov_head.head.weight"][rank * vl:(rank + 1) * vl].to(torch.bfloat16).contiguous().to(dev)
+        W.conf_w = ck[f"mtp.{last}.confidence_head.proj.weight"].to(torch.float32).flatten().contiguous().to(dev)
     return W
 
 
 # ---- synthetic, generated on the device -----------------------------------------------------------------
-def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="cuda", seed: int = 0, moe_mode: str = "tp") -> DeviceWeights:
+def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="cuda", seed: int = 0, moe_mode: str = "tp",
+                      mtp: bool = False) -> DeviceWeights:
     """Random-init weights (~N(0, 0.02), norms ~1) written straight into the prepared layout.
 
     Payload bytes come from ``sfb_synth_fill`` (a hash of the tensor's seed and the element index);
@@ -295,8 +317,11 @@ def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="c
     W.onehot = oh.to(dev)
     W.il = il
     W.moe_mode, W.experts_local, W.expert_lo = moe_mode, El, (rank * El if moe_mode == "ep" else 0)
-    for l in range(cfg.n_layers):
-        p = f"layers.{l}"
+    il_tp = stored_inter(cfg, world, "tp")
+    plan = [(f"layers.{l}", l, E, El, il, W.layers) for l in range(cfg.n_layers)]
+    if mtp and cfg.n_mtp_stages:          # draft stages: same block, ratio-0 attention, their own width-sliced expert pool
+        plan += [(f"mtp.{s_}", cfg.n_layers + s_, cfg.dspark_n_experts, cfg.dspark_n_experts, il_tp, W.mtp_layers) for s_ in range(cfg.n_mtp_stages)]
+    for p, l, E, El, il, dest in plan:
         L = LayerW()
         L.wqkv_a, L.wqkv_a_sf = fp8(f"{p}.wqkv_a", q + hd, d)
         L.q_norm, L.kv_norm = f32(f"{p}.q_norm", (q,), 0.05, 1.0), f32(f"{p}.kv_norm", (hd,), 0.05, 1.0)
@@ -339,5 +364,13 @@ def prepare_synthetic(cfg: ModelConfig, rank: int = 0, world: int = 1, device="c
         L.w2 = torch.empty((El, d, il // 2), dtype=torch.uint8, device=dev)
         N.synth_fill(1, L.w2, L.w2.numel(), sd(f"{p}.w2", True), sig4)
         L.w2_sf = torch.full((El, sfb2), FP4_CODE, dtype=torch.uint8, device=dev)
-        W.layers.append(L)
+        dest.append(L)
+    if W.mtp_layers:
+        K3 = len(cfg.dspark_taps) * d
+        r = cfg.dspark_markov_rank
+        W.mtp_main_proj, W.mtp_main_proj_sf = fp8("mtp.main_proj", d, K3)
+        W.mtp_main_norm, W.mtp_norm = f32("mtp.main_norm", (d,), 0.05, 1.0), f32("mtp.norm", (d,), 0.05, 1.0)
+        W.markov_embed = bf16("mtp.markov_embed", (V, r))
+        W.markov_head = bf16("mtp.markov_head", (V // world, r), shard=True)
+        W.conf_w = f32("mtp.conf", (d + r,), 0.02)
     return W

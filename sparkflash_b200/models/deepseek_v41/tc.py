@@ -51,7 +51,7 @@ class TcLayer:
     w2: TcMatrix | None = None
 
 
-def attach(weights: DeviceWeights, synthetic: bool = False) -> list[TcLayer]:
+def attach(weights: DeviceWeights, synthetic: bool = False, layers=None, n_experts: int | None = None) -> list[TcLayer]:
     """Build the tensor-core attachments for every layer.  ``synthetic``: scales are a constant fill
     (2^-12 for FP8 blocks, 2^-7 for FP4 groups), so atoms are filled instead of re-ordered."""
     cfg = weights.cfg
@@ -59,11 +59,13 @@ def attach(weights: DeviceWeights, synthetic: bool = False) -> list[TcLayer]:
     d, q, hd = cfg.hidden_size, cfg.q_lora_rank, cfg.head_dim
     gl, il = cfg.o_groups // W, weights.il or cfg.moe_inter // W
     ol, gin = cfg.o_lora_rank, cfg.group_in
-    E = weights.experts_local or cfg.n_routed_experts        # experts held by this rank (expert parallelism keeps a range)
+    E = n_experts or weights.experts_local or cfg.n_routed_experts   # experts held by this rank (expert parallelism keeps a range)
+    if n_experts:
+        il = -(-(cfg.moe_inter // W) // 128) * 128                    # draft stages stay width-sliced in both modes
     c8 = 115 if synthetic else None
     c4 = 120 if synthetic else None
     out = []
-    for L in weights.layers:
+    for L in (weights.layers if layers is None else layers):
         T = TcLayer()
         T.wqkv_a = _matrix(L.wqkv_a, L.wqkv_a_sf, q + hd, d, False, c8)
         T.wq_b = _matrix(L.wq_b, L.wq_b_sf, L.wq_b_rows, q, False, c8)

@@ -159,14 +159,15 @@ def select_topk(scores, row_pos, ratio, len_div, max_len, K, ids, count, n):
 
 # ---- attention ---------------------------------------------------------------------------------------------
 def attn_rows(q, q_stride, rope, row_lane, row_pos, win_q, win_s, ckv_q, ckv_s, sel, sel_count, K, sink,
-              out, n, heads, hd, rd, window, ring, scale, out_q=None, out_atom=None):
-    code = lib().sfb_attn_rows(
+              out, n, heads, hd, rd, window, ring, scale, out_q=None, out_atom=None, win_lo=None, win_hi=None):
+    """``win_lo`` / ``win_hi`` (int32 [n], optional): explicit inclusive position range of the window entries per row."""
+    code = lib().sfb_attn_rows_range(
         _p(q), c_int64(q_stride), _p(rope), c_int(rope.stride(0) // 2), _p(row_lane), _p(row_pos), _p(win_q), _p(win_s),
         c_int64(win_q.stride(0)), c_int64(win_s.stride(0)), _p(ckv_q), _p(ckv_s),
         c_int64(ckv_q.stride(0) if ckv_q is not None else 0), c_int64(ckv_s.stride(0) if ckv_s is not None else 0),
         _p(sel), _p(sel_count), c_int(K), _p(sink), _p(out), _p(out_q), _p(out_atom), c_int(n), c_int(heads),
         c_int(hd), c_int(rd),
-        c_int(window), c_int(ring), c_float(scale), _stream())
+        c_int(window), c_int(ring), c_float(scale), _p(win_lo), _p(win_hi), _stream())
     _check(code, "attn_rows")
 
 
@@ -198,6 +199,20 @@ def moe_down(act_q, act_s, ids, w2, w2_sf, s2, s2_sf, out, n, k, d, inter):
 def embed(table, tokens, h, n, hc, d, vocab, status=None):
     _check(lib().sfb_embed(_p(table), _p(tokens), _p(h), c_int(n), c_int(hc), c_int(d), c_int(vocab), _p(status),
                            _stream()), "embed")
+
+
+def rmsnorm_quant(x, norm_w, eps, out, out_q=None, out_atom=None, n=None, residual=None, out_sum=None):
+    """out = rmsnorm(x (+ residual)) * w in bf16, optionally re-quantised to FP8 with scale atoms (the consumer kernel of the
+    fused collectives with a single, local slot and no flags)."""
+    n = x.shape[0] if n is None else n
+    d = x.shape[1]
+    _check(lib().sfb_fold_slots(_ptr_array([x]), None, c_int(1), c_int(n), c_int(d), c_int64(x.stride(0)), None, c_uint32(0), c_uint64(0),
+                                _p(residual), _p(norm_w), c_float(eps), _p(out_sum), _p(out), _p(out_q), _p(out_atom), None, _stream()),
+           "rmsnorm_quant")
+
+
+def markov_bias(logits_row, head, embed, prev, vl, r, vocab):
+    _check(lib().sfb_markov_bias(_p(logits_row), _p(head), _p(embed), _p(prev), c_int(vl), c_int(r), c_int(vocab), _stream()), "markov_bias")
 
 
 def embed_override(rows, mask, h, n, hc, d):

@@ -76,6 +76,24 @@ class NgramDrafter:
         return [], []
 
 
+class DSparkDrafter:
+    """The model's own draft stages on the device (Engine.draft): one block of proposals per decoding sequence and step,
+    sampled with the verifier's (seed, position) noise so that a good draft is accepted at any temperature."""
+    device = True
+
+    def __init__(self, depth: int = 5, min_confidence: float | None = None):
+        self.depth, self.min_confidence = depth, min_confidence
+
+    def propose_device(self, eng, lane: int, pos: int, anchor: int, temperature: float, seed: int):
+        toks, conf = eng.draft(lane, pos, anchor, temperature, seed)
+        toks, conf = toks[:self.depth], conf[:self.depth]
+        if self.min_confidence is not None:          # adaptive depth: stop at the first position the head does not trust
+            for i, c in enumerate(conf):
+                if c < self.min_confidence:
+                    return toks[:i], conf[:i]
+        return toks, conf
+
+
 class DeviceDriver(InferenceEngine):
     def __init__(self, engine, tokenizer, model_id: str = "deepseek-v4.1-flash", channel=None, drafter=None,
                  max_lanes: int | None = None, queue_depth: int = 64, prefill_chunk: int | None = None,
@@ -255,7 +273,13 @@ class DeviceDriver(InferenceEngine):
             for live in self._live.values():
                 info = self.sched.info(live.seq)
                 if info and info["state"] == "decode" and live.constraint is None:
-                    toks, conf = self.drafter.propose(live.history)
+                    if getattr(self.drafter, "device", False):
+                        q = live.req
+                        seed = (q.seed if q.seed is not None else live.seq * 0x9E3779B1) & 0x7FFFFFFFFFFFFFFF
+                        toks, conf = self.drafter.propose_device(eng, info["lane"], info["computed"] - 1, live.history[-1],
+                                                                 0.0 if q.temperature < 1e-5 else q.temperature, seed)
+                    else:
+                        toks, conf = self.drafter.propose(live.history)
                     if toks:
                         self.sched.set_drafts(live.seq, toks, conf)
         phase, rows = self.sched.tick(eng.max_rows)

@@ -147,7 +147,7 @@ def _flatten(w) -> tuple[dict[str, torch.Tensor], dict]:
     tensors, scalars = {}, {}
     for f in dataclasses.fields(w):
         v = getattr(w, f.name)
-        if f.name in ("cfg", "layers"):
+        if f.name in ("cfg", "layers", "mtp_layers"):
             continue
         if isinstance(v, torch.Tensor):
             tensors[f.name] = v
@@ -156,13 +156,14 @@ def _flatten(w) -> tuple[dict[str, torch.Tensor], dict]:
                 tensors[f"{f.name}.{int(k)}"] = t
         elif isinstance(v, (int, float, bool, str)) or v is None:
             scalars[f.name] = v
-    for i, L in enumerate(w.layers):
-        for f in dataclasses.fields(L):
-            v = getattr(L, f.name)
-            if isinstance(v, torch.Tensor):
-                tensors[f"layers.{i}.{f.name}"] = v
-            elif isinstance(v, (int, float, bool)):
-                scalars[f"layers.{i}.{f.name}"] = v
+    for group, layers in (("layers", w.layers), ("mtp_layers", getattr(w, "mtp_layers", []))):
+        for i, L in enumerate(layers):
+            for f in dataclasses.fields(L):
+                v = getattr(L, f.name)
+                if isinstance(v, torch.Tensor):
+                    tensors[f"{group}.{i}.{f.name}"] = v
+                elif isinstance(v, (int, float, bool)):
+                    scalars[f"{group}.{i}.{f.name}"] = v
     return tensors, scalars
 
 
@@ -225,28 +226,32 @@ def load_rank_file(path: str, device="cuda", verify: bool = True, threads: int =
         t = stage[off:off + nb].view(_DT[dt]).reshape(shape)
         t = t.to(device, non_blocking=True) if on_gpu else t.clone()
         head, _, tail = name.partition(".")
-        if head != "layers" and tail.isdigit():
+        if head not in ("layers", "mtp_layers") and tail.isdigit():
             dicts.setdefault(head, {})[bool(int(tail))] = t
         else:
             tensors[name] = t
     if on_gpu:
         torch.cuda.synchronize()
     sc = meta["scalars"]
-    nl = 1 + max((int(k.split(".")[1]) for k in tensors if k.startswith("layers.")), default=-1)
-    layers = []
-    for i in range(nl):
-        Lw = LayerW()
-        pre = f"layers.{i}."
-        for k, v in tensors.items():
-            if k.startswith(pre):
-                setattr(Lw, k[len(pre):], v)
-        for k, v in sc.items():
-            if k.startswith(pre):
-                setattr(Lw, k[len(pre):], v)
-        layers.append(Lw)
-    kw = {f.name: tensors.get(f.name, sc.get(f.name)) for f in dataclasses.fields(DeviceWeights) if f.name not in ("cfg", "layers")}
+    groups = {}
+    for group in ("layers", "mtp_layers"):
+        nl = 1 + max((int(k.split(".")[1]) for k in tensors if k.startswith(group + ".")), default=-1)
+        layers = []
+        for i in range(nl):
+            Lw = LayerW()
+            pre = f"{group}.{i}."
+            for k, v in tensors.items():
+                if k.startswith(pre):
+                    setattr(Lw, k[len(pre):], v)
+            for k, v in sc.items():
+                if k.startswith(pre):
+                    setattr(Lw, k[len(pre):], v)
+            layers.append(Lw)
+        groups[group] = layers
+    kw = {f.name: tensors.get(f.name, sc.get(f.name)) for f in dataclasses.fields(DeviceWeights) if f.name not in ("cfg", "layers", "mtp_layers")}
+    kw = {k: v for k, v in kw.items() if v is not None or k in ("embed",)}
     kw.update(dicts)
-    kw.update(cfg=cfg, layers=layers)
+    kw.update(cfg=cfg, **groups)
     return DeviceWeights(**kw)
 
 

@@ -1,0 +1,85 @@
+"""DSpark draft stages on the device against the CPU oracle, and through the serving driver (speculation with the
+model's own drafter never changes the output)."""
+import asyncio
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def setup():
+    from sparkflash_b200.config import tiny_config
+    from sparkflash_b200.models.deepseek_v41 import oracle as O, prepare as P, weights as W
+    cfg = tiny_config()
+    ck = W.synthetic_checkpoint(cfg, 0)
+    return cfg, O.Oracle(cfg, W.dequantize_checkpoint(ck, cfg)), P.prepare_from_checkpoint(ck, cfg, 0, 1)
+
+
+def test_draft_block_matches_the_oracle(setup):
+    from sparkflash_b200.models.deepseek_v41 import engine as E
+    cfg, orc, dw = setup
+    assert len(dw.mtp_layers) == cfg.n_mtp_stages
+    eng = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, arm="tc", drafter=True, use_graphs=False, keep_logits=True)
+    prompt = torch.randint(0, cfg.vocab_size, (21,), generator=torch.Generator().manual_seed(4)).tolist()
+    st = orc.new_state()
+    ol = orc.prefill(st, prompt)
+    eng.step(prompt[:16], [1] * 16, list(range(16)))
+    r = eng.step(prompt[16:], [1] * 5, list(range(16, 21)))
+    anchor = int(ol.argmax())
+    P = len(prompt) - 1
+    want_t, want_c, want_l = orc.draft(st, anchor)
+    got_t, got_c = eng.draft(1, P, anchor)
+    eng.check_status()
+    B = cfg.dspark_block
+    gl = eng.logits[:B].float().cpu()
+    scale = want_l.abs().max().item()
+    err = [(gl[i] - want_l[i]).abs().mean().item() / scale for i in range(B)]
+    # position 0 sees only exactly reproduced inputs; later positions inherit the previous position's sampled token
+    assert err[0] < 0.03, err
+    assert sum(err) / B < 0.08, err
+    assert got_t[0] == want_t[0] or abs(float(want_l[0].topk(2).values.diff())) < 0.05 * scale
+    assert sum(a == b for a, b in zip(got_t, want_t)) >= 2, (got_t, want_t)
+    assert max(abs(a - b) for a, b in zip(got_c, want_c)) < 0.1 + 0.1 * max(abs(c) for c in want_c), (got_c, want_c)
+    # drafting must not disturb the sequence: the next backbone step gives the same logits as without the draft
+    eng2 = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, arm="tc", drafter=True, use_graphs=False, keep_logits=True)
+    eng2.step(prompt[:16], [1] * 16, list(range(16))); eng2.step(prompt[16:], [1] * 5, list(range(16, 21)))
+    a = eng.step([anchor], [1], [P + 1]); la = eng.logits[0].clone()
+    b = eng2.step([anchor], [1], [P + 1])
+    assert int(a[0]) == int(b[0]) and torch.equal(la, eng2.logits[0])
+
+
+def test_driver_with_the_device_drafter_keeps_the_output(setup):
+    from sparkflash_b200.models.deepseek_v41 import engine as E
+    from sparkflash_b200.serve.driver import DeviceDriver, DSparkDrafter
+    from sparkflash_b200.serve.engine_api import EngineRequest
+    from sparkflash_b200.serve.tokenizer import ByteTokenizer
+    cfg, orc, dw = setup
+    tok = ByteTokenizer(cfg.vocab_size)
+
+    async def collect(drv, req):
+        toks, fin = [], None
+        async for ev in drv.generate(req):
+            if ev[0] == "token":
+                toks.append(ev[1])
+            elif ev[0] in ("finished", "error"):
+                fin = ev
+        return toks, fin
+
+    def run(drafter, temperature):
+        eng = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, arm="tc", drafter=True)
+        drv = DeviceDriver(eng, tok, eos_id=10 ** 9, drafter=drafter, prefix_reuse_min=1000).start()
+        try:
+            reqs = [EngineRequest(f"r{i}", "m", list(range(30 + i, 50 + i)), max_tokens=8, temperature=temperature, seed=3) for i in range(2)]
+
+            async def go():
+                return await asyncio.gather(*[collect(drv, r) for r in reqs])
+            return asyncio.run(go())
+        finally:
+            drv.shutdown(1.0)
+    for T in (0.0, 0.8):
+        plain = run(None, T)
+        spec = run(DSparkDrafter(depth=4), T)
+        assert [t for t, _ in plain] == [t for t, _ in spec]
+        assert all(f[0] == "finished" for _, f in spec) and sum(f[2]["proposed"] for _, f in spec) > 0
