@@ -109,6 +109,8 @@ def main() -> None:
     ap.add_argument("--collective", default=os.environ.get("SFB_COLLECTIVE", "fused"))
     ap.add_argument("--skip-extras", action="store_true")
     ap.add_argument("--arm", default=os.environ.get("SFB_ARM", "tc"), choices=["tc", "cuda"])
+    ap.add_argument("--long-context", default="", help="comma-separated cached context lengths (e.g. 131072,1048576): decode tok/s with the KV "
+                    "caches of lane 0 filled with random entries up to that position")
     ap.add_argument("--mtp", action="store_true", help="also build the DSpark draft stages and report the per-forward latency of a draft block")
     ap.add_argument("--moe-mode", default=os.environ.get("SFB_MOE_MODE", "tp"), choices=["tp", "ep"],
                     help="tp: every expert sliced by width over the ranks; ep: whole experts per rank")
@@ -143,7 +145,8 @@ def main() -> None:
     torch.cuda.synchronize()
     t_init = time.time() - t0
     S = args.streams
-    max_ctx = args.prompt + args.steps * 2 + args.warmup * 2 + 1024
+    long_ctx = [int(x) for x in args.long_context.split(",") if x]
+    max_ctx = max([args.prompt + args.steps * 2 + args.warmup * 2 + 1024] + [c + args.steps + args.warmup + 64 for c in long_ctx])
     eng = E.Engine(weights, max_lanes=max(S, 1), max_context=max_ctx, max_rows=64, comm=comm, arm=args.arm,
                    synthetic_scales=True, drafter=args.mtp)
     if comm is not None:
@@ -241,6 +244,29 @@ def main() -> None:
                   "prefill_tok_s": prefill_tok_s, "prefill_prompt_tokens": len(prompt),
                   "prefill_note": "rows steps of 64 (CUDA-core arm)",
                   "vs_baseline_prefill": prefill_tok_s / BASELINE_PREFILL_TOK_S}
+    for ctx in long_ctx:
+        # decode against a long cached context: the caches of lane 0 are filled with random codes (a real prefill of a million
+        # tokens is out of a benchmark's time), every kernel of the step then runs at that context length
+        g2 = torch.Generator(device=eng.dev).manual_seed(ctx)
+        for dct in (eng.kv.win_q, eng.kv.ckv_q, eng.kv.ik_q):
+            for t in dct.values():
+                t[0].copy_(torch.randint(0, 120, t[0].shape, dtype=torch.uint8, device=eng.dev, generator=g2))
+        for dct, code in ((eng.kv.win_s, 122), (eng.kv.ckv_s, 0x38), (eng.kv.ik_s, 122)):
+            for t in dct.values():
+                t[0].fill_(code)
+        p_l, tok_l = ctx, 1
+        saved_bucket = eng.min_bucket
+        eng.min_bucket = max(saved_bucket, eng._bucket(ctx + args.steps + args.warmup + 8))
+        for _ in range(args.warmup):
+            r = eng.step([tok_l], [0], [p_l]); tok_l = int(r[0]); p_l += 1
+        barrier()
+        ev0.record()
+        for _ in range(args.steps):
+            r = eng.step([tok_l], [0], [p_l]); tok_l = int(r[0]); p_l += 1
+        ev1.record()
+        barrier()
+        extras[f"decode_tok_s_at_context_{ctx}"] = args.steps / (ev0.elapsed_time(ev1) / 1e3)
+        eng.min_bucket = saved_bucket
     if args.mtp:
         # DSpark on: cost of one draft block (3 stages x 5 positions + Markov chain) per forward; acceptance is meaningless
         # with random weights, so only the latency is reported.  The timed single-stream figure above already includes the

@@ -434,12 +434,30 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         }
       } else if (S.last_flag) {
         __threadfence();
+        const bool vec = a.pair == 0 || (a.pair & 3) == 0;     // four token columns per load when the layout allows it
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
         for (int tok = 0; tok < nv; ++tok) {
           float s = 0.f;
-          for (int sp = 0; sp < w.splits; ++sp) {
-            const float* pp = a.scratch + (size_t)sp * split_stride + lane_off;
-            s += __ldcg(pp + tok);
-            if (a.pair > 0) s += __ldcg(pp + tok + a.pair);
+          if (vec) {
+            if ((tok & 3) == 0) {
+              s4[0] = s4[1] = s4[2] = s4[3] = 0.f;
+              for (int sp = 0; sp < w.splits; ++sp) {          // split order, then the pair term: same sums as the scalar path
+                const float* pp = a.scratch + (size_t)sp * split_stride + lane_off;
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(pp + tok));
+                s4[0] += t.x; s4[1] += t.y; s4[2] += t.z; s4[3] += t.w;
+                if (a.pair > 0) {
+                  const float4 u = __ldcg(reinterpret_cast<const float4*>(pp + tok + a.pair));
+                  s4[0] += u.x; s4[1] += u.y; s4[2] += u.z; s4[3] += u.w;
+                }
+              }
+            }
+            s = s4[tok & 3];
+          } else {
+            for (int sp = 0; sp < w.splits; ++sp) {
+              const float* pp = a.scratch + (size_t)sp * split_stride + lane_off;
+              s += __ldcg(pp + tok);
+              if (a.pair > 0) s += __ldcg(pp + tok + a.pair);
+            }
           }
           if (!col_ok) s = 0.f;
           const int64_t o = (int64_t)(w.out_row0 + tok) * a.out_stride + col;
