@@ -46,6 +46,7 @@ struct Lane {
   int64_t owner = -1;            // sequence id, -1 = free
   std::vector<int32_t> held;     // tokens whose KV the lane still holds (valid prefix after the owner left)
   int64_t last_used = 0;
+  int full_from = 0;             // rows before this ran the cache-owning layers only (decoder-layer skip)
 };
 
 struct Config {
@@ -54,6 +55,7 @@ struct Config {
   int max_context = 1048576;
   int spec_depth = 5;
   int64_t ring_slack = (int64_t)1 << 40;
+  int decoder_tail = 0;     // > 0: prompt rows more than this far before the prompt's end run the cache-owning layers only
   int64_t lane_row_budget = -1;  // total rows all lanes may hold (-1: unlimited)
 };
 
@@ -113,6 +115,12 @@ void place_waiting(Scheduler& s) {
       s.prefix_rows += best_len;
     }
     Lane& L = s.lanes[best];
+    if (s.cfg.decoder_tail > 0 && best_len > 0 && L.full_from > 0 && best_len - s.cfg.decoder_tail < L.full_from) {
+      // the prefix forks inside rows whose upper layers were skipped: re-run one tail's worth of rows with every layer
+      // (they start cold and are exact again by the fork point)
+      best_len = std::max(0, best_len - s.cfg.decoder_tail);
+    }
+    if (best_len < L.full_from) L.full_from = best_len;      // rows kept are all before the old boundary: nothing upper-layer is kept
     L.owner = q.id;
     L.held.resize(best_len);
     L.last_used = s.tick_no;
@@ -168,6 +176,7 @@ void* sfb_sched_create(int max_lanes, int queue_depth, int max_rows, int prefill
   return s;
 }
 void sfb_sched_set_ring_slack(void* h, int64_t rows) { ((Scheduler*)h)->cfg.ring_slack = rows; }
+void sfb_sched_set_decoder_tail(void* h, int rows) { ((Scheduler*)h)->cfg.decoder_tail = rows; }
 void sfb_sched_destroy(void* h) { delete (Scheduler*)h; }
 
 // 0 = accepted, 1 = refused (lanes and queue full), 2 = prompt too long / invalid
@@ -235,10 +244,14 @@ int sfb_sched_tick(void* h, int64_t* out, int max_out, int* phase) {
     }
     int chunk = decoding.empty() ? s.cfg.prefill_chunk : s.cfg.prefill_chunk_busy;
     chunk = std::min(chunk, std::min(max_out, q->prompt_len - q->computed));
+    // decoder-layer skip: rows before prompt_len - tail form chunks of their own (kind 3) that stop at the boundary
+    const int skip_until = s.cfg.decoder_tail > 0 ? std::max(0, q->prompt_len - s.cfg.decoder_tail) : 0;
+    const bool skipping = q->computed < skip_until;
+    if (skipping) chunk = std::min(chunk, skip_until - q->computed);
     if (!make_room(s, chunk)) chunk = 0;
     if (q->state == PREFILL && q->lane >= 0) {
       for (int i = 0; i < chunk; ++i)
-        rows.push_back({q->id, q->lane, q->computed + i, q->tokens[q->computed + i], 0});
+        rows.push_back({q->id, q->lane, q->computed + i, q->tokens[q->computed + i], skipping ? 3 : 0});
       if (chunk > 0) *phase = 1;
     }
   } else if (!decoding.empty()) {
@@ -298,6 +311,10 @@ int sfb_sched_commit(void* h, int64_t id, int rows_done, const int32_t* new_toke
   Seq& q = it->second;
   Lane& L = s.lanes[q.lane];
   L.last_used = s.tick_no;
+  if (s.cfg.decoder_tail > 0 && q.state == PREFILL) {
+    const int skip_until = std::max(0, q.prompt_len - s.cfg.decoder_tail);
+    if (q.computed < skip_until) L.full_from = std::max(L.full_from, std::min(skip_until, q.computed + rows_done));
+  }
   q.computed += rows_done;
   q.spec_depth = 0;
   bool finished = false;

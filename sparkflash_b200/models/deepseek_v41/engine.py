@@ -491,11 +491,11 @@ class Engine:
         slots, flags = self.comm.slots(kind)
         return (slots, flags, sub + 1)
 
-    def _forward(self, n: int, len_bucket: int):
-        for _ in self._forward_gen(n, len_bucket):
+    def _forward(self, n: int, len_bucket: int, stop_after: int | None = None):
+        for _ in self._forward_gen(n, len_bucket, stop_after):
             pass
 
-    def _forward_gen(self, n: int, len_bucket: int):
+    def _forward_gen(self, n: int, len_bucket: int, stop_after: int | None = None):
         """The rows-step forward.  Yields after every point where this rank has published a partial result, so
         that a lockstep driver can interleave several ranks living in one process; a normal run just exhausts it."""
         cfg, w = self.cfg, self.w
@@ -511,6 +511,14 @@ class Engine:
         y_prev = None
         tap_i = 0
         for l, L in enumerate(w.layers):
+            if stop_after is not None and l > stop_after:
+                # decoder-layer skip: rows far before a prompt's end only have to leave the caches that later rows read, and
+                # the layers past the last cache owner keep nothing but their own short window
+                if self._coef_event is not None:      # join the side stream: a captured graph must end on one stream
+                    torch.cuda.current_stream().wait_event(self._coef_event)
+                    self._coef_event = None
+                self._join_prefetch()
+                return
             self._seam(n, k, y_prev, L.hc_attn_fn, L.hc_attn_base, L.hc_attn_scale, L.attn_norm); k += 1
             if l in cfg.dspark_taps and cfg.n_mtp_stages:
                 N.tap_mean(self.h, self.taps[:, tap_i * cfg.hidden_size:], self.taps.stride(0), n, cfg.hc_mult,
@@ -731,8 +739,24 @@ class Engine:
             self.img_mask[idx] = 1
             self._img_dirty = True
 
+    @property
+    def decoder_skip_layer(self) -> int:
+        """Last layer that owns a cache other layers read (compressed KV / index keys)."""
+        own = [l for l in self.cfg.kv_source_layers if l < self.cfg.n_layers]
+        return max(own) if own else self.cfg.n_layers - 1
+
+    @property
+    def decoder_tail(self) -> int:
+        """Rows before a prompt's end from which every layer must run so that the last window of every skipped layer is exact:
+        one window of reach per skipped layer, plus one window (reference: docs/design.md, 'the decoder layers only on a prompt's
+        tail': 19 windows + 1 for the released model = 2,541 rows)."""
+        skipped = self.cfg.n_layers - 1 - self.decoder_skip_layer
+        return (skipped * (self.cfg.window - 1) + self.cfg.window + skipped) if skipped > 0 else 0
+
     def step(self, tokens, lanes, positions, temperature=None, seeds=None, sync: bool = True, masks: dict | None = None,
-             image_rows: dict | None = None, filters: dict | None = None) -> torch.Tensor:
+             image_rows: dict | None = None, filters: dict | None = None, skip_decoder: bool = False) -> torch.Tensor:
+        """``skip_decoder``: run only the layers up to the last cache owner and no head (prefill rows far before the prompt's
+        end); the returned tokens are meaningless then."""
         """Run one rows step.  ``tokens/lanes/positions`` are host sequences of equal length n.
         Returns the sampled next-token ids as a host int32 tensor [n] (pinned) when ``sync``; the
         device tensor ``tokens_out`` otherwise."""
@@ -767,7 +791,7 @@ class Engine:
         self.row_pos[:n].copy_(io.pos[:n], non_blocking=True)
         self.temp[:n].copy_(io.temp[:n], non_blocking=True)
         self.seed[:n].copy_(io.seed[:n], non_blocking=True)
-        self.run_rows(n, self._bucket(int(max(positions))))
+        self.run_rows(n, self._bucket(int(max(positions))), self.decoder_skip_layer if skip_decoder else None)
         if not sync:
             return self.tokens_out[:n]
         io.out[:n].copy_(self.tokens_out[:n], non_blocking=True)
@@ -777,22 +801,22 @@ class Engine:
                 io.out[r] = self.filtered_sample(r, top_k, top_p, float(io.temp[r]), int(io.seed[r]), int(io.pos[r]))
         return io.out[:n]
 
-    def run_rows(self, n: int, len_bucket: int) -> None:
+    def run_rows(self, n: int, len_bucket: int, stop_after: int | None = None) -> None:
         """Launch (or replay) the forward for the rows already staged in the device input buffers."""
         if not self.use_graphs:
-            self._forward(n, len_bucket)
+            self._forward(n, len_bucket, stop_after)
             return
-        key = (n, len_bucket)
+        key = (n, len_bucket) if stop_after is None else (n, len_bucket, stop_after)
         g = self.graphs.get(key)
         if g is None:
             # warm-up run outside capture (first-call attribute set-up, lazy module loading)
             self._counting, self.launches_per_step = True, 0
-            self._forward(n, len_bucket)
+            self._forward(n, len_bucket, stop_after)
             self._counting = False
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                self._forward(n, len_bucket)
+                self._forward(n, len_bucket, stop_after)
             self.graphs[key] = g
             # the warm-up run already produced this step's result and advanced the caches; replaying
             # the same rows is idempotent (position-addressed writes), so fall through to one replay

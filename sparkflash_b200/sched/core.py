@@ -19,6 +19,7 @@ def _L():
         L.sfb_sched_create.argtypes = [c_int] * 8 + [c_int64]
         L.sfb_sched_destroy.argtypes = [c_void_p]
         L.sfb_sched_set_ring_slack.argtypes = [c_void_p, c_int64]
+        L.sfb_sched_set_decoder_tail.argtypes = [c_void_p, c_int]
         L.sfb_sched_submit.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int]
         L.sfb_sched_cancel.argtypes = [c_void_p, c_int64]
         L.sfb_sched_set_drafts.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int]
@@ -57,7 +58,7 @@ class PlanRow:
     lane: int
     pos: int
     token: int
-    kind: int  # 0 prefill, 1 decode anchor, 2 draft row
+    kind: int  # 0 prefill, 1 decode anchor, 2 draft row, 3 prefill row that runs the cache-owning layers only
 
 PHASE_IDLE, PHASE_PREFILL, PHASE_DECODE = 0, 1, 2
 STATE_NAMES = ["waiting", "prefill", "decode", "finished", "preempted"]
@@ -80,6 +81,10 @@ class Scheduler:
 
     def set_ring_slack(self, rows: int) -> None:
         _L().sfb_sched_set_ring_slack(self._h, rows)
+
+    def set_decoder_tail(self, rows: int) -> None:
+        """Prompt rows more than ``rows`` before the prompt's end are planned as kind-3 chunks (cache-owning layers only)."""
+        _L().sfb_sched_set_decoder_tail(self._h, rows)
 
     def submit(self, seq_id: int, prompt: list[int], max_new: int) -> int:
         return _L().sfb_sched_submit(self._h, seq_id, _i32(prompt), len(prompt), max_new)

@@ -97,7 +97,7 @@ class DSparkDrafter:
 class DeviceDriver(InferenceEngine):
     def __init__(self, engine, tokenizer, model_id: str = "deepseek-v4.1-flash", channel=None, drafter=None,
                  max_lanes: int | None = None, queue_depth: int = 64, prefill_chunk: int | None = None,
-                 prefix_reuse_min: int = 256, stall_seconds: float = 30.0, eos_id: int | None = None):
+                 prefix_reuse_min: int = 256, stall_seconds: float = 30.0, eos_id: int | None = None, decoder_skip: bool = True):
         self.engine = engine
         self.tokenizer = tokenizer
         self.model_id = model_id
@@ -110,6 +110,9 @@ class DeviceDriver(InferenceEngine):
         self.sched = Scheduler(max_lanes=lanes, queue_depth=queue_depth, max_rows=engine.max_rows, prefill_chunk=chunk,
                                prefill_chunk_busy=chunk, prefix_reuse_min=prefix_reuse_min, max_context=engine.max_context,
                                spec_depth=getattr(drafter, "depth", 0) or 0)
+        tail = getattr(engine, "decoder_tail", 0)
+        if decoder_skip and tail:
+            self.sched.set_decoder_tail(tail)
         ring_slack = getattr(engine, "ring_slack", None)
         if ring_slack is not None:
             self.sched.set_ring_slack(ring_slack)
@@ -320,6 +323,8 @@ class DeviceDriver(InferenceEngine):
                 filters[i] = (q.top_k, q.top_p)
         if filters:
             kw["filters"] = filters
+        if rows[0].kind == 3:
+            kw["skip_decoder"] = True
         out = eng.step([r.token for r in rows], [r.lane for r in rows], [r.pos for r in rows], temps, seeds, **kw)
         out = [int(x) for x in out]
         eng.check_status()
@@ -432,6 +437,8 @@ class FakeRowsEngine:
         self.supports_vision = True
         self.image_log: list[tuple] = []
         self.filter_log: list[tuple] = []
+        self.skipped_rows = 0
+        self.decoder_tail = 0
         self.supports_filter = True
 
     def vocab_slice(self):
@@ -451,8 +458,9 @@ class FakeRowsEngine:
             return self.eos_id
         return 32 + h % 90      # printable bytes
 
-    def step(self, tokens, lanes, positions, temperature=None, seeds=None, masks=None, image_rows=None, filters=None):
+    def step(self, tokens, lanes, positions, temperature=None, seeds=None, masks=None, image_rows=None, filters=None, skip_decoder=False):
         self.steps.append(len(tokens))
+        self.skipped_rows += len(tokens) if skip_decoder else 0
         self.filter_log += [(positions[i], f) for i, f in (filters or {}).items()]
         for i, vec in (image_rows or {}).items():
             self.image_log.append((lanes[i], positions[i], float(vec.float().sum())))

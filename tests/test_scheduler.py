@@ -138,3 +138,37 @@ def test_radix_cache_and_pager():
     x, y, z = p.alloc(), p.alloc(), p.alloc()
     assert p.alloc() == -1 and p.share(x) == 2
     assert p.release(x) == 1 and p.release(x) == 0 and p.free == 1
+
+
+def test_decoder_skip_chunks_stop_at_the_tail_and_forks_rerun_one_tail():
+    s = Scheduler(max_lanes=1, max_rows=16, prefill_chunk=16, prefix_reuse_min=4)
+    s.set_decoder_tail(10)
+    PROMPTS[1] = list(range(100, 140))                      # 40 rows: rows 0..29 skip the upper layers, 30..39 run everything
+    s.submit(1, PROMPTS[1], 1)
+    kinds = []
+    while True:
+        phase, rows = s.tick()
+        if phase != PHASE_PREFILL:
+            break
+        kinds.append((rows[0].pos, len(rows), rows[0].kind))
+        assert len({r.kind for r in rows}) == 1             # a chunk never straddles the boundary
+        done = rows[-1].pos + 1 == 40
+        s.commit(1, len(rows), [1] if done else [], 1)
+        if done:
+            break
+    assert kinds == [(0, 16, 3), (16, 14, 3), (30, 10, 0)]
+    # a prompt that forks at row 20 (inside the skipped rows) re-runs from row 10 with every layer
+    PROMPTS[2] = PROMPTS[1][:20] + [7] * 30
+    s.submit(2, PROMPTS[2], 1)
+    phase, rows = s.tick()
+    assert rows[0].pos == 10 and s.stats()["prefix_rows"] == 20
+    # a continuation of the whole first prompt (fork point inside the fully computed tail) keeps all of it
+    s2 = Scheduler(max_lanes=1, max_rows=16, prefill_chunk=64, prefix_reuse_min=4)
+    s2.set_decoder_tail(10)
+    s2.submit(1, PROMPTS[1], 1)
+    while s2.info(1)["state"] != "finished":
+        phase, rows = s2.tick()
+        s2.commit(1, len(rows), [1] if rows[-1].pos + 1 == 40 else [], 1)
+    s2.submit(2, PROMPTS[1] + [5, 6, 7], 1)
+    phase, rows = s2.tick()
+    assert rows[0].pos == 40

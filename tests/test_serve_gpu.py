@@ -110,3 +110,28 @@ def test_candidate_filter_top_k_top_p(setup):
     assert eng.filtered_sample(row, 0, 1.0, 0.0, 3, 19) == best                    # greedy
     out = eng.step([1], [0], [20], temperature=[2.0], seeds=[5], filters={0: (3, 1.0)})
     assert int(out[0]) in set(torch.topk(eng.logits[0].float(), 3).indices.tolist())
+
+
+def test_decoder_layer_skip_is_exact(setup):
+    """Prompt rows far before the end run only the cache-owning layers; the generated tokens and the final logits are
+    the ones a full run gives."""
+    from sparkflash_b200.serve.driver import DeviceDriver
+    from sparkflash_b200.serve.engine_api import EngineRequest
+    cfg, tok, make = setup
+    g = torch.Generator().manual_seed(21)
+    prompt = torch.randint(0, 256, (90,), generator=g).tolist()
+    outs = {}
+    for skip in (False, True):
+        eng = make(keep_logits=True)
+        assert eng.decoder_skip_layer == 3 and eng.decoder_tail == 24
+        calls = []
+        orig = eng.step
+        eng.step = lambda *a, **k: (calls.append((len(a[0]), k.get("skip_decoder", False))), orig(*a, **k))[1]
+        drv = DeviceDriver(eng, tok, eos_id=10 ** 9, prefix_reuse_min=1000, decoder_skip=skip).start()
+        try:
+            toks, fin = asyncio.run(_collect(drv, EngineRequest("r", "m", prompt, max_tokens=8, temperature=0.0)))
+        finally:
+            drv.shutdown(1.0)
+        outs[skip] = (toks, sum(n for n, s in calls if s))
+    assert outs[True][1] == 90 - 24 and outs[False][1] == 0
+    assert outs[True][0] == outs[False][0]
