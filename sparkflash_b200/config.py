@@ -61,6 +61,7 @@ class ModelConfig:
     engram_n_heads: int = 8
     engram_head_dim: int = 256
     engram_compressed_vocab: int = 99092
+    engram_vocab: int = 16000000          # bucket primes are drawn above this value
     engram_enabled: bool = False
     # DSpark / MTP drafter
     n_mtp_stages: int = 3
@@ -152,6 +153,10 @@ def tiny_config(**over: Any) -> ModelConfig:
         engram_rows=[], dspark_taps=[3, 4, 5], dspark_markov_rank=32, dspark_n_experts=4,
         dspark_top_k=2, dspark_noise_token=1000, image_token_id=1023, dspark_block=5,
     )
+    if over.pop("engram", False):
+        # small n-gram memory on two layers: bucket primes just above 2000, the released row width and head count
+        base.update(engram_enabled=True, engram_layers=[1, 3], engram_vocab=2000, engram_compressed_vocab=1024, engram_n_heads=8,
+                    engram_head_dim=256, engram_max_ngram=4)
     base.update(over)
     return dataclasses.replace(ModelConfig(), **base)
 

@@ -114,7 +114,7 @@ class Engine:
     def __init__(self, weights: DeviceWeights, max_lanes: int = 4, max_context: int = 4096, max_rows: int = 64,
                  comm=None, use_graphs: bool = True, keep_logits: bool = False, arm: str = "cuda",
                  synthetic_scales: bool = False, constrained: bool = False, lane_budget_bytes: int | None = None,
-                 vision: bool = False, drafter: bool = False):
+                 vision: bool = False, drafter: bool = False, engram=None):
         """``arm``: "cuda" = CUDA-core exact arm for every projection; "tc" = tcgen05 tensor-core arm for
         every shape it takes (the rest falls back to the CUDA-core kernels)."""
         self.w, self.cfg = weights, weights.cfg
@@ -211,6 +211,17 @@ class Engine:
             self._splits = TC.pick_splits
         elif arm != "cuda":
             raise ValueError(f"unknown arm {arm!r}")
+        self.engram = engram          # engram.runtime.EngramRuntime or None
+        if engram is not None:
+            from ... import codecs as CC
+            ne, cols = len(cfg.engram_layers), engram.layout.cols
+            Ke = cols * cfg.engram_head_dim
+            self.eg_ids = torch.zeros((ne, R, cols), dtype=torch.int64, device=dev)
+            self.eg_ids_host = torch.zeros((ne, R, cols), dtype=torch.int64).pin_memory()
+            self.eg_rows = e((R, Ke), bf)
+            self.eg_q = torch.zeros((R, Ke), dtype=torch.uint8, device=dev)
+            self.eg_atom = torch.full((CC.sf_bytes(128, Ke // 32),), 127, dtype=torch.uint8, device=dev)
+            self.eg_kv = e((R, (cfg.hc_mult + 1) * d), bf)
         if self.drafter:
             if arm != "tc":
                 raise ValueError("the DSpark drafter runs on the tensor-core arm")
@@ -262,7 +273,22 @@ class Engine:
             raise RuntimeError(f"device status code={st[0]} where={st[1]} detail=({st[2]}, {st[3]})")
 
     # ---- sublayers -------------------------------------------------------------------------------------
-    def _seam(self, n: int, k: int, y_parts, fn, base, scale, norm_w, quant: bool = True, atoms: int = 0):
+    def _engram_apply(self, n: int, j: int) -> None:
+        """Engram layer j on the residual copies of the step's rows: gather the hashed rows, project to keys and value, gate."""
+        cfg, eg = self.cfg, self.engram
+        Ke = self.eg_rows.shape[1]
+        Nkv = self.eg_kv.shape[1]
+        eg.shards[j].gather(self.eg_ids[j, :n], self.eg_rows); self._k()
+        q, sf, T = eg.wkv[j]
+        if T is not None and self.tcl is not None:
+            N.quant_rows(self.eg_rows, self.eg_q, None, self.eg_atom, n, Ke); self._k()
+            self._tc_dense(T, self.eg_q, self.max_rows, self.eg_atom, n, Nkv, Ke, self.eg_kv)
+        else:
+            N.gemv(N.WF_FP8, q, sf, Ke, Nkv, Ke, n, xb=self.eg_rows, out_b=self.eg_kv); self._k()
+        from ...engram.runtime import gate_bf16
+        gate_bf16(self.h, self.eg_kv, eg.gate_w[j], self.img_mask, n, cfg.norm_eps); self._k()
+
+    def _seam(self, n: int, k: int, y_parts, fn, base, scale, norm_w, quant: bool = True, atoms: int = 0, engram_j: int | None = None):
         """Seam number k (0-based over the whole forward).  The fold half (critical path) finishes the previous
         sublayer with coef[(k-1)%2]; the coefficient half runs on the side stream beside the sublayer's GEMMs
         and writes coef[k%2] for the next seam."""
@@ -285,6 +311,15 @@ class Engine:
                     xs_atom=None if (self.tcl is None or not quant) else (self.tcb.xs_atom if atoms == 0 else self.tcb.xs_atom_tok),
                     atom_mode=atoms)
         self._k()
+        if engram_j is not None:
+            # the memory writes into the block's input after the previous block's output has been folded in: apply it, then
+            # redo the collapse half of the seam on the updated copies (same coefficients, no fold)
+            self._engram_apply(n, engram_j)
+            N.seam_fold(self.h, None, None, prev, prev.stride(0), norm_w, self.xn, self.xq if quant else None,
+                        self.xs if quant else None, n, cfg.hc_mult, cfg.hidden_size, cfg.norm_eps, status=self.status,
+                        xs_atom=None if (self.tcl is None or not quant) else (self.tcb.xs_atom if atoms == 0 else self.tcb.xs_atom_tok),
+                        atom_mode=atoms)
+            self._k()
         if fn is not None:
             ev = torch.cuda.Event()
             ev.record(main)
@@ -519,7 +554,8 @@ class Engine:
                     self._coef_event = None
                 self._join_prefetch()
                 return
-            self._seam(n, k, y_prev, L.hc_attn_fn, L.hc_attn_base, L.hc_attn_scale, L.attn_norm); k += 1
+            eg_j = cfg.engram_layers.index(l) if (self.engram is not None and l in cfg.engram_layers) else None
+            self._seam(n, k, y_prev, L.hc_attn_fn, L.hc_attn_base, L.hc_attn_scale, L.attn_norm, engram_j=eg_j); k += 1
             if l in cfg.dspark_taps and cfg.n_mtp_stages:
                 N.tap_mean(self.h, self.taps[:, tap_i * cfg.hidden_size:], self.taps.stride(0), n, cfg.hc_mult,
                            cfg.hidden_size); self._k()
@@ -764,6 +800,10 @@ class Engine:
         if not 0 < n <= self.max_rows:
             raise ValueError(f"rows {n} out of range 1..{self.max_rows}")
         self.kv.ensure(lanes, positions)
+        if self.engram is not None:
+            ids = self.engram.ids_for_step(list(tokens), list(lanes), list(positions))
+            self.eg_ids_host[:, :n].copy_(torch.from_numpy(ids))
+            self.eg_ids[:, :n].copy_(self.eg_ids_host[:, :n], non_blocking=True)
         if image_rows or self._img_dirty:
             if self.img_mask is None:
                 raise ValueError("this engine was built without vision=True")

@@ -160,6 +160,11 @@ class Oracle:
         self.cfg, self.w, self.world = cfg, weights, world
         self.inv_freq = {False: rope_inv_freq(cfg, False), True: rope_inv_freq(cfg, True)}
         self.trace: dict[str, torch.Tensor] | None = None  # filled when a test asks for intermediates
+        self.engram = None
+        if cfg.engram_enabled and f"engram.{cfg.engram_layers[0]}.embed" in weights:
+            from ...engram.layout import EngramLayout
+            self.engram = EngramLayout.build(cfg.engram_layers, cfg.engram_max_ngram, cfg.engram_n_heads, cfg.engram_vocab,
+                                             cfg.engram_compressed_vocab)
 
     def new_state(self) -> SeqState:
         return SeqState([LayerState() for _ in range(self.cfg.n_layers + self.cfg.n_mtp_stages)])
@@ -341,6 +346,23 @@ class Oracle:
         self._t(f"L{l}.h", h)
         return h, f_pre
 
+    # ---- Engram n-gram memory (docs/architecture/04-engram.md of the reference, sections 5-6) ---------------------
+    def _engram(self, l: int, h: torch.Tensor, st: SeqState, token: int, pos: int) -> torch.Tensor:
+        """Before block ``l``: hash the last n-grams ending at ``pos``, fetch the rows (bf16 after dequantisation), project them to
+        one key per residual copy plus a value, and add the value through a signed-square-root gate."""
+        import numpy as np
+        from ...engram.store import gate_reference
+        cfg, w = self.cfg, self.w
+        j = cfg.engram_layers.index(l)
+        cv = cfg.engram_compressed_vocab
+        cache = np.array([t % cv for t in st.tokens] + [token % cv], dtype=np.int64)      # synthetic models: identity token map
+        ids = self.engram.hash_ids(j, cache, [pos], cfg.pad_id % cv)[0]
+        rows = bf(w[f"engram.{l}.embed"][torch.from_numpy(ids)]).flatten()
+        kv = bf(fp8_linear(rows, w[f"engram.{l}.wkv"]))
+        out = gate_reference(h.to(torch.float32).unsqueeze(0), kv.unsqueeze(0), w[f"engram.{l}.gate_w"], None, cfg.norm_eps)[0]
+        self._t(f"L{l}.engram_ids", torch.from_numpy(ids)); self._t(f"L{l}.engram_h", out)
+        return bf(out)
+
     # ---- whole forward for one token -------------------------------------------------------------------
     def step(self, st: SeqState, token: int) -> torch.Tensor:
         """Append ``token`` at position ``st.pos``; returns fp32 logits [vocab] for the next token."""
@@ -352,6 +374,8 @@ class Oracle:
         shared: dict = {}
         taps = []
         for l in range(cfg.n_layers):
+            if self.engram is not None and l in cfg.engram_layers:
+                h = self._engram(l, h, st, token, pos)
             if l in cfg.dspark_taps:
                 taps.append(bf(h.to(torch.float32).mean(0)))
             h, pre_mix = self._block(l, f"layers.{l}", h, pre_mix, st, pos, shared,

@@ -91,6 +91,14 @@ def tensor_specs(cfg: ModelConfig) -> list[TensorSpec]:
         out += _block_specs(cfg, f"layers.{l}", cfg.n_routed_experts, True, l)
     for s in range(cfg.n_mtp_stages):
         out += _block_specs(cfg, f"mtp.{s}", cfg.dspark_n_experts, False, cfg.n_layers + s)
+    if cfg.engram_enabled:
+        from ...engram.layout import EngramLayout
+        lay = EngramLayout.build(cfg.engram_layers, cfg.engram_max_ngram, cfg.engram_n_heads, cfg.engram_vocab, cfg.engram_compressed_vocab)
+        cols = (cfg.engram_max_ngram - 1) * cfg.engram_n_heads
+        for j, l in enumerate(cfg.engram_layers):
+            out += [S(f"engram.{l}.embed", (lay.rows[j], cfg.engram_head_dim), "fp8row", "unit"),
+                    S(f"engram.{l}.wkv", ((cfg.hc_mult + 1) * d, cols * cfg.engram_head_dim), "fp8"),
+                    S(f"engram.{l}.gate_w", (cfg.hc_mult, d), "f32", "ones")]      # q_weight * k_weight, folded
     if cfg.n_mtp_stages:
         r = cfg.dspark_markov_rank
         last = cfg.n_mtp_stages - 1
@@ -111,6 +119,8 @@ def _master(spec: TensorSpec, seed: int) -> torch.Tensor:
         return torch.zeros(spec.shape)
     if spec.init == "small":
         return 0.1 * torch.randn(spec.shape, generator=g)
+    if spec.init == "unit":
+        return torch.randn(spec.shape, generator=g)
     std = 0.02
     if spec.name.endswith(("hc_attn_fn", "hc_ffn_fn")):
         std = 0.05
@@ -128,6 +138,9 @@ def synthetic_checkpoint(cfg: ModelConfig, seed: int = 0) -> dict[str, torch.Ten
         elif sp.kind == "fp4":
             q, s = codecs.weight_quant_fp4_row32(w)
             ck[sp.name + ".weight"], ck[sp.name + ".scale"] = q, s
+        elif sp.kind == "fp8row":          # table rows: E4M3 codes with one UE8M0 scale per 32 values of the row
+            q, s = codecs.act_quant_fp8(w)
+            ck[sp.name + ".weight"], ck[sp.name + ".scale"] = q, s
         elif sp.kind == "bf16":
             ck[sp.name] = w.to(torch.bfloat16)
         else:
@@ -143,6 +156,9 @@ def dequantize_checkpoint(ck: dict[str, torch.Tensor], cfg: ModelConfig) -> dict
             out[sp.name] = codecs.weight_dequant_fp8_block32(ck[sp.name + ".weight"], ck[sp.name + ".scale"])
         elif sp.kind == "fp4":
             out[sp.name] = codecs.weight_dequant_fp4_row32(ck[sp.name + ".weight"], ck[sp.name + ".scale"])
+        elif sp.kind == "fp8row":
+            q, sc = ck[sp.name + ".weight"], ck[sp.name + ".scale"]
+            out[sp.name] = (codecs.e4m3_decode(q).reshape(q.shape[0], -1, 32) * codecs.ue8m0_decode(sc).unsqueeze(-1)).reshape(q.shape)
         else:
             out[sp.name] = ck[sp.name].to(torch.float32)
     return out

@@ -107,3 +107,40 @@ def test_device_gather_and_gate_match_the_reference():
     torch.cuda.synchronize()
     assert torch.equal(hd[2].cpu(), h[2])                       # a masked token keeps h exactly
     assert (hd.cpu() - want).abs().max() < 2e-3
+
+
+@pytest.mark.gpu
+def test_engine_with_engram_matches_the_oracle():
+    """The serving engine with the n-gram memory wired in before the Engram layers' blocks, against the CPU oracle:
+    the first positions to rounding, later ones statistically (cached low-precision values drift apart)."""
+    from sparkflash_b200.config import tiny_config
+    from sparkflash_b200.engram.runtime import EngramRuntime
+    from sparkflash_b200.models.deepseek_v41 import engine as E, oracle as O, prepare as P, weights as W
+    cfg = tiny_config(engram=True)
+    ck = W.synthetic_checkpoint(cfg, 0)
+    orc = O.Oracle(cfg, W.dequantize_checkpoint(ck, cfg))
+    base = O.Oracle(cfg, {k: v for k, v in W.dequantize_checkpoint(ck, cfg).items() if not k.startswith("engram.")})
+    eng = E.Engine(P.prepare_from_checkpoint(ck, cfg, 0, 1), max_lanes=2, max_context=256, max_rows=16, arm="tc", keep_logits=True,
+                   engram=EngramRuntime.from_checkpoint(ck, cfg))
+    prompt = torch.randint(0, cfg.vocab_size, (14,), generator=torch.Generator().manual_seed(8)).tolist()
+    st, st0 = orc.new_state(), base.new_state()
+    errs, agree, moved = [], 0, 0.0
+    for pos, tok in enumerate(prompt):
+        want = orc.step(st, tok)
+        plain = base.step(st0, tok)
+        out = eng.step([tok], [1], [pos])
+        got = eng.logits[0].float().cpu()
+        scale = want.abs().max().item()
+        if pos == 0:
+            assert (got - want).abs().max().item() < 0.03 * scale
+        errs.append((got - want).abs().mean().item() / scale)
+        moved = max(moved, (want - plain).abs().max().item() / scale)
+        agree += int(out[0]) == int(want.argmax())
+    eng.check_status()
+    assert moved > 0.05                       # the memory really changes the model's output ...
+    assert sum(errs) / len(errs) < 0.06       # ... and the engine follows the oracle with it
+    assert agree >= 0.6 * len(prompt)
+    # a multi-row chunk on another lane gives the rows the single-row steps gave (n-grams come from the lane's own history)
+    eng.step(prompt[:7], [0] * 7, list(range(7)))
+    eng.step(prompt[7:], [0] * 7, list(range(7, 14)))
+    assert torch.equal(eng.logits[6].float().cpu(), got) or (eng.logits[6].float().cpu() - got).abs().max() < 1e-3 * scale
