@@ -36,7 +36,7 @@ def _convert(args) -> int:
 
     def progress(done, total, detail):
         print("@progress " + json.dumps({"done": done, "total": total, "detail": detail}), flush=True)
-    man = C.convert(args.checkpoint, args.output_dir, args.tp_world_size, ranks, not args.no_verify, progress)
+    man = C.convert(args.checkpoint, args.output_dir, args.tp_world_size, ranks, not args.no_verify, progress, args.expert_split)
     print(f"convert: wrote {len(man['ranks'])} rank file(s) into {args.output_dir}")
     return 0
 
@@ -87,7 +87,7 @@ def main(argv=None) -> int:
     c = sub.add_parser("convert")
     c.add_argument("--checkpoint"); c.add_argument("--output-dir"); c.add_argument("--tp-world-size", type=int, default=1)
     c.add_argument("--ranks"); c.add_argument("--no-verify", action="store_true"); c.add_argument("--inspect")
-    c.add_argument("--verify-weights", action="store_true"); c.add_argument("--synthetic", choices=["tiny", "full"])
+    c.add_argument("--verify-weights", action="store_true"); c.add_argument("--expert-split", default="tp", choices=["tp", "ep"], help="tp: experts sliced by width; ep: whole experts per rank"); c.add_argument("--synthetic", choices=["tiny", "full"])
     c.set_defaults(fn=_convert)
     t = sub.add_parser("trace")
     t.add_argument("action", choices=["arm", "status", "dump"]); t.add_argument("--url", default="http://127.0.0.1:8000")
@@ -102,6 +102,7 @@ def main(argv=None) -> int:
     s.add_argument("--api-key", default=os.environ.get("SFB_API_KEY")); s.add_argument("--config", help="TOML settings file")
     s.add_argument("--model-id", default="deepseek-v4.1-flash"); s.add_argument("--control-port", type=int, default=29600)
     s.add_argument("--mock", action="store_true", help="serve the scripted mock engine (no GPU)")
+    s.add_argument("--lane-budget-gb", type=int, default=0, help="back the per-position KV regions lazily from a pool of this size")
     s.set_defaults(fn=_serve)
     b = sub.add_parser("bench-serving")
     b.add_argument("--url", default="http://127.0.0.1:8000"); b.add_argument("--concurrency", type=int, default=16)

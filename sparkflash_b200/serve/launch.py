@@ -28,20 +28,24 @@ def build_engine(args, settings, rank: int, world: int):
         from ..weights.convert import rank_path
         from ..weights.files import load_rank_file
         w = load_rank_file(rank_path(args.weights, rank, world), "cuda", expect_rank=rank, expect_world=world)
+        if w.moe_mode != settings.parallel.moe_mode:
+            raise SystemExit(f"rank files were converted for moe_mode={w.moe_mode!r}, the settings ask for {settings.parallel.moe_mode!r}")
         synthetic = False
     else:
         cfg = {"tiny": CF.tiny_config, "reduced": lambda: CF.reduced_config(128, 40), "full": CF.full_config}[args.synthetic or "tiny"]()
         if (args.synthetic or "tiny") == "tiny":
             from ..models.deepseek_v41 import weights as W
-            w = P.prepare_from_checkpoint(W.synthetic_checkpoint(cfg, 0), cfg, rank, world)
+            w = P.prepare_from_checkpoint(W.synthetic_checkpoint(cfg, 0), cfg, rank, world, moe_mode=settings.parallel.moe_mode)
             synthetic = False
         else:
-            w = P.prepare_synthetic(cfg, rank, world)
+            w = P.prepare_synthetic(cfg, rank, world, moe_mode=settings.parallel.moe_mode, mtp=settings.engine.speculation)
             synthetic = True
     comm = PC.make_comm(settings.parallel.collective, rank, world) if world > 1 else None
     ec = settings.engine
     eng = E.Engine(w, max_lanes=ec.max_lanes, max_context=min(ec.max_context, 1 << 16) if args.synthetic else ec.max_context,
-                   max_rows=ec.max_rows, comm=comm, use_graphs=ec.cuda_graphs, arm="tc", synthetic_scales=synthetic, constrained=True)
+                   max_rows=ec.max_rows, comm=comm, use_graphs=ec.cuda_graphs, arm="tc", synthetic_scales=synthetic, constrained=True,
+                   drafter=ec.speculation and bool(w.mtp_layers) and settings.parallel.moe_mode == "tp",
+                   lane_budget_bytes=getattr(args, "lane_budget_gb", 0) * (1 << 30) or None)
     if comm is not None:
         comm.attach(eng)
     return eng
@@ -79,9 +83,13 @@ def run(args) -> int:
         eng = build_engine(args, settings, rank, world)
         tok = load_tokenizer(args.tokenizer, eng.cfg.vocab_size)
         chan = ControlChannel(rank, world, addr=os.environ.get("MASTER_ADDR", "127.0.0.1"), port=args.control_port) if world > 1 else None
-        drafter = NgramDrafter(settings.engine.spec_depth) if settings.engine.speculation else None
+        from .driver import DSparkDrafter
+        drafter = None
+        if settings.engine.speculation:      # the model's own draft stages when the weights carry them, prompt look-up otherwise
+            drafter = DSparkDrafter(settings.engine.spec_depth) if eng.drafter else NgramDrafter(settings.engine.spec_depth)
         driver = DeviceDriver(eng, tok, model_id=args.model_id, channel=chan, drafter=drafter, queue_depth=settings.engine.queue_depth,
-                              prefix_reuse_min=settings.engine.prefix_reuse_min_rows, stall_seconds=settings.engine.stall_secs).start()
+                              prefix_reuse_min=settings.engine.prefix_reuse_min_rows, stall_seconds=settings.engine.stall_secs,
+                              decoder_skip=settings.engine.decoder_skip).start()
         engine = driver
         _boot("engine ready", rank=rank, weights_gb=round(eng.w.nbytes() / 1e9, 2), kv_gb=round(eng.kv.nbytes() / 1e9, 2))
         if rank != 0:

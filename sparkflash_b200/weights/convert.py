@@ -19,7 +19,7 @@ def rank_path(out_dir: str, rank: int, world: int) -> str:
 
 
 def convert(src_dir: str, out_dir: str, world: int = 1, ranks: list[int] | None = None, verify: bool = True,
-            progress=None) -> dict:
+            progress=None, moe_mode: str = "tp") -> dict:
     from ..models.deepseek_v41 import prepare as P
     with open(os.path.join(src_dir, "config.json")) as f:
         cfg = config_from_hf(json.load(f))
@@ -27,7 +27,7 @@ def convert(src_dir: str, out_dir: str, world: int = 1, ranks: list[int] | None 
     os.makedirs(out_dir, exist_ok=True)
     ranks = list(range(world)) if ranks is None else ranks
     man_path = os.path.join(out_dir, MANIFEST)
-    manifest = {"format": 1, "model": cfg.name, "world": world, "source": os.path.abspath(src_dir), "ranks": {}}
+    manifest = {"format": 1, "model": cfg.name, "world": world, "moe_mode": moe_mode, "source": os.path.abspath(src_dir), "ranks": {}}
     if os.path.exists(man_path):
         with open(man_path) as f:
             old = json.load(f)
@@ -35,7 +35,7 @@ def convert(src_dir: str, out_dir: str, world: int = 1, ranks: list[int] | None 
             manifest["ranks"] = old.get("ranks", {})
     for i, r in enumerate(ranks):
         t0 = time.time()
-        w = P.prepare_from_checkpoint(ck, cfg, r, world, device="cpu")
+        w = P.prepare_from_checkpoint(ck, cfg, r, world, device="cpu", moe_mode=moe_mode)
         path = rank_path(out_dir, r, world)
         info = F.write_rank_file(path, w, {"source": os.path.basename(os.path.abspath(src_dir))})
         if verify:
