@@ -313,6 +313,96 @@ __global__ void __launch_bounds__(256) moe_down_kernel(DownArgs a) {
 }
 
 
+// ---- grouped MoE plan: the (token, expert) pairs of a step sorted by expert, cut into segments of up to 16 pairs ----------
+// Every expert's weights are then read once per segment instead of once per pair, and the shared expert once per 16 tokens.
+// Reference behaviour: the MoE grouping / dedup plan built once per stage call (crates/sparkflash-kernels/src/moe_routed_device.rs:
+// 1568-2063; DECISIONS D102).  The arithmetic per pair is unchanged: one accumulator column per pair, summed per token in slot order.
+struct MoePlanArgs {
+  const int* ids;        // [n, k] expert id (local; < 0 = not on this rank)
+  const float* wts;      // [n, k]
+  int n, k, E, shared, S;          // S = segments launched (fixed per row count)
+  int* seg_expert;       // [S]  -1 unused, -2 shared expert
+  int* seg_count;        // [S]
+  float* seg_weight;     // [S*16]
+  int* seg_token;        // [S*16] token of the pair slot, -1 unused
+  int* pair_pos;         // [n, k+1] pair slot of (token, slot), -1 = skipped
+};
+
+__global__ void __launch_bounds__(512) moe_plan_kernel(MoePlanArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ int plan_sm[];     // cnt[E] | base[E + 1]
+  int* cnt = plan_sm; int* base = plan_sm + a.E;
+  const int P = a.n * a.k;
+  for (int i = threadIdx.x; i < a.E; i += blockDim.x) cnt[i] = 0;
+  for (int i = threadIdx.x; i < a.S; i += blockDim.x) { a.seg_expert[i] = -1; a.seg_count[i] = 0; }
+  for (int i = threadIdx.x; i < a.S * 16; i += blockDim.x) { a.seg_token[i] = -1; a.seg_weight[i] = 0.f; }
+  for (int i = threadIdx.x; i < a.n * (a.k + 1); i += blockDim.x) a.pair_pos[i] = -1;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) { const int e = a.ids[p]; if (e >= 0 && e < a.E) atomicAdd(&cnt[e], 1); }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int b = 0;
+    for (int e = 0; e < a.E; ++e) { base[e] = b; b += (cnt[e] + 15) / 16; }
+    base[a.E] = b;                     // first segment of the shared expert
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < a.E; e += blockDim.x)
+    for (int sgi = 0, c = cnt[e]; c > 0; ++sgi, c -= 16)
+      if (base[e] + sgi < a.S) { a.seg_expert[base[e] + sgi] = e; a.seg_count[base[e] + sgi] = c < 16 ? c : 16; }
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = a.ids[p];
+    if (e < 0 || e >= a.E) continue;
+    int r = 0;                          // rank among the earlier pairs of the same expert: the order inside a segment is the pair order
+    for (int q = 0; q < p; ++q) r += a.ids[q] == e;
+    const int seg = base[e] + r / 16, slot = seg * 16 + (r & 15);
+    if (seg < a.S) {
+      a.seg_token[slot] = p / a.k; a.seg_weight[slot] = a.wts[p];
+      a.pair_pos[(p / a.k) * (a.k + 1) + p % a.k] = slot;
+    }
+  }
+  if (a.shared) {
+    for (int t = threadIdx.x; t < a.n; t += blockDim.x) {
+      const int seg = base[a.E] + t / 16, slot = seg * 16 + (t & 15);
+      if (seg < a.S) { a.seg_token[slot] = t; a.seg_weight[slot] = 1.f; a.pair_pos[t * (a.k + 1) + a.k] = slot; }
+    }
+    for (int sgi = threadIdx.x; sgi * 16 < a.n; sgi += blockDim.x)
+      if (base[a.E] + sgi < a.S) { a.seg_expert[base[a.E] + sgi] = -2; a.seg_count[base[a.E] + sgi] = a.n - sgi * 16 < 16 ? a.n - sgi * 16 : 16; }
+  }
+}
+
+// one block per pair slot: the token's FP8 row and its scales (as row j of the segment's atom set)
+__global__ void __launch_bounds__(128) moe_permute_kernel(const uint8_t* xq, const uint8_t* xs, const int* seg_token, uint8_t* xperm,
+                                                         uint8_t* seg_atoms, int d, int atom_set_bytes) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int slot = blockIdx.x, tok = seg_token[slot];
+  if (tok < 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)tok * d);
+  uint4* dst = reinterpret_cast<uint4*>(xperm + (size_t)slot * d);
+  for (int i = threadIdx.x; i < d / 16; i += blockDim.x) dst[i] = src[i];
+  const int KB = d / 32, seg = slot >> 4, j = slot & 15;
+  for (int kb = threadIdx.x; kb < KB; kb += blockDim.x) seg_atoms[(size_t)seg * atom_set_bytes + sf_offset(j, kb, KB)] = xs[(size_t)tok * KB + kb];
+}
+
+// y[t, :] = bf16( sum over the token's pair slots, in slot order, of ypair[slot, :] )
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* ypair, const int* pair_pos, __nv_bfloat16* y, int k1, int d, int64_t y_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c >= d) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int sl = 0; sl < k1; ++sl) {
+    const int pos = pair_pos[t * k1 + sl];
+    if (pos < 0) continue;
+    const float4 v = *reinterpret_cast<const float4*>(ypair + (size_t)pos * d + c);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  __nv_bfloat16* o = y + (size_t)t * y_stride + c;
+  o[0] = __float2bfloat16_rn(acc.x); o[1] = __float2bfloat16_rn(acc.y); o[2] = __float2bfloat16_rn(acc.z); o[3] = __float2bfloat16_rn(acc.w);
+}
+
 // expert parallelism: global expert ids -> this rank's local ids, -1 for experts held elsewhere (the grouped GEMMs skip them)
 __global__ void expert_remap_kernel(int* ids, int n, int lo, int count) {
   pdl_launch_dependents();
@@ -368,4 +458,23 @@ int sfb_moe_down(const void* act_q, const void* act_s, const int* ids, const voi
 
 extern "C" int sfb_expert_remap(void* ids, int n, int lo, int count, cudaStream_t stream) {
   return (int)sfb::sfb_launch(sfb::expert_remap_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, (int*)ids, n, lo, count);
+}
+
+extern "C" int sfb_moe_plan(const void* ids, const void* wts, int n, int k, int E, int shared, int S, void* seg_expert, void* seg_count,
+                            void* seg_weight, void* seg_token, void* pair_pos, cudaStream_t stream) {
+  if (E > 4096) return (int)cudaErrorInvalidValue;
+  sfb::MoePlanArgs a{(const int*)ids, (const float*)wts, n, k, E, shared, S, (int*)seg_expert, (int*)seg_count, (float*)seg_weight,
+                     (int*)seg_token, (int*)pair_pos};
+  return (int)sfb::sfb_launch(sfb::moe_plan_kernel, dim3(1), dim3(512), (size_t)(2 * E + 1) * sizeof(int), stream, a);
+}
+extern "C" int sfb_moe_permute(const void* xq, const void* xs, const void* seg_token, void* xperm, void* seg_atoms, int slots, int d,
+                               int atom_set_bytes, cudaStream_t stream) {
+  if (d % 32) return (int)cudaErrorInvalidValue;
+  return (int)sfb::sfb_launch(sfb::moe_permute_kernel, dim3(slots), dim3(128), 0, stream, (const uint8_t*)xq, (const uint8_t*)xs,
+                              (const int*)seg_token, (uint8_t*)xperm, (uint8_t*)seg_atoms, d, atom_set_bytes);
+}
+extern "C" int sfb_moe_combine(const void* ypair, const void* pair_pos, void* y, int n, int k1, int d, int64_t y_stride, cudaStream_t stream) {
+  if (d % 4) return (int)cudaErrorInvalidValue;
+  return (int)sfb::sfb_launch(sfb::moe_combine_kernel, dim3((d / 4 + 255) / 256, n), dim3(256), 0, stream, (const float*)ypair,
+                              (const int*)pair_pos, (__nv_bfloat16*)y, k1, d, y_stride);
 }

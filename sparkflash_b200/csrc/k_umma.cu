@@ -137,7 +137,7 @@ __host__ __device__ inline uint32_t make_idesc(int a_fmt, int b_fmt, int M, int 
   return d;
 }
 
-enum UmmaMode : int { UM_DENSE = 0, UM_DOWN = 2 };
+enum UmmaMode : int { UM_DENSE = 0, UM_DOWN = 2, UM_DOWN_GROUPED = 3 };
 
 struct UmmaArgs {
   // A (weights): rows x K through tmapA (tmapA2 = the shared expert in MoE modes); scale atoms
@@ -191,6 +191,10 @@ struct UmmaArgs {
   uint8_t* act_s;             //              [n_tok, slots, inter/32] row-major
   uint8_t* act_sf;            //              one atom set per (token, slot), the row at atom row 0
   float limit;
+  // grouped MoE (rows of a step sorted by expert; one CTA column = one segment of up to 16 (token, expert) pairs)
+  const int* seg_expert;      // [segments] local expert id, -2 = the shared expert, -1 = unused segment
+  const int* seg_count;       // [segments] pairs in the segment (1..16)
+  const float* seg_weight;    // [segments * 16] routing weight of every pair slot
   Status* status;
 };
 
@@ -272,6 +276,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       w.n_valid = min(NP, a.n - tok_tile * NP);
       w.sfb = a.sfb + ((size_t)((tok_tile * NP) >> 7) * a.katoms_b + g * ksteps + w.ks0) * 512;
     }
+  } else if (a.mode == UM_DOWN_GROUPED) {   // x = column tile of d, y = segment: W2_e times the segment's activation rows
+    const int tile = blockIdx.x, seg = blockIdx.y;
+    const int ksteps = (a.inter + UM_BK - 1) / UM_BK;
+    int e = a.seg_expert[seg];
+    if (e == -1) { skip = true; e = 0; }
+    if (e >= 0) {
+      w.ma = &tmapA; w.a_fp4 = a.a_fp4;
+      w.a_row0 = e * a.d + tile * 128;
+      w.sfa = a.sfa + ((size_t)(w.a_row0 >> 7) * a.katoms_a) * 512;
+    } else {
+      w.ma = &tmapA2; w.a_fp4 = 0;
+      w.a_row0 = tile * 128;
+      w.sfa = a.sfa2 + ((size_t)tile * a.katoms_a) * 512;
+    }
+    w.ks0 = 0; w.nks = skip ? 0 : ksteps;
+    w.b_x0 = 0; w.b_row0 = seg * 16;
+    w.sfb = a.sfb + (size_t)seg * a.katoms_b * 512;
+    w.split = 0; w.splits = 1;
+    w.tile_id = seg * gridDim.x + tile; w.tiles_total = gridDim.x * gridDim.y;
+    w.out_row0 = seg * 16; w.n_valid = skip ? 0 : a.seg_count[seg]; w.col0 = tile * 128; w.col_limit = a.d;
   } else {  // UM_DOWN: x = column tile of d, y = slot, z = token
     const int tile = blockIdx.x, slot = blockIdx.y, tok = blockIdx.z;
     const int ksteps = (a.inter + UM_BK - 1) / UM_BK;
@@ -561,7 +585,24 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   const uint8_t *sf_g, *sf_u;
   float weight = 1.f;
   bool skip = false;
-  if (slot < a.top_k) {
+  const bool grouped = a.seg_expert != nullptr;     // blockIdx.y = segment, blockIdx.z = 0; tok = first pair slot of the segment
+  int count = 1;
+  if (grouped) {
+    int e = a.seg_expert[slot];
+    count = a.seg_count[slot];
+    if (e == -1) { skip = true; e = 0; count = 0; }
+    if (e >= 0) {
+      ma = &tmapA; a_fp4 = a.a_fp4;
+      row_g = (e * 2) * il + tile * 128; row_u = row_g + il;
+      sf_g = a.sfa + ((size_t)(row_g >> 7) * a.katoms_a) * 512;
+      sf_u = a.sfa + ((size_t)(row_u >> 7) * a.katoms_a) * 512;
+    } else {
+      ma = &tmapA2; a_fp4 = 0;
+      row_g = tile * 128; row_u = row_g + il;
+      sf_g = a.sfa2 + ((size_t)(row_g >> 7) * a.katoms_a) * 512;
+      sf_u = a.sfa2 + ((size_t)(row_u >> 7) * a.katoms_a) * 512;
+    }
+  } else if (slot < a.top_k) {
     int e = a.ids[(size_t)tok * a.top_k + slot];
     if (e < 0) { skip = true; e = 0; }         // not this rank's expert: nothing is loaded, multiplied or written
     weight = a.wts[(size_t)tok * a.top_k + slot];
@@ -575,7 +616,8 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
     sf_g = a.sfa2 + ((size_t)(row_g >> 7) * a.katoms_a) * 512;
     sf_u = a.sfa2 + ((size_t)(row_u >> 7) * a.katoms_a) * 512;
   }
-  const uint8_t* sfb = a.sfb + (size_t)tok * a.katoms_b * 512;
+  const int b_row = grouped ? slot * 16 : tok;
+  const uint8_t* sfb = a.sfb + (size_t)(grouped ? slot : tok) * a.katoms_b * 512;
   const uint32_t STAGE_TX = 2 * (a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 3 * 512;
   const uint32_t tmem = S.tmem_base;
   const uint32_t t_g = tmem, t_u = tmem + NP;
@@ -590,7 +632,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
         mbar_expect_tx(&S.full[s], STAGE_TX);
         tma_load_2d(S.a[s][0], ma, i * UM_BK, row_g, &S.full[s]);
         tma_load_2d(S.a[s][1], ma, i * UM_BK, row_u, &S.full[s]);
-        tma_load_2d(S.b[s], &tmapB, i * UM_BK, tok, &S.full[s]);
+        tma_load_2d(S.b[s], &tmapB, i * UM_BK, b_row, &S.full[s]);
         bulk_load(S.sfa[s][0], sf_g + (size_t)i * 512, 512, &S.full[s]);
         bulk_load(S.sfa[s][1], sf_u + (size_t)i * 512, 512, &S.full[s]);
         bulk_load(S.sfb[s], sfb + (size_t)i * 512, 512, &S.full[s]);
@@ -629,21 +671,27 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
     tc_ld16(t_u + ((uint32_t)(q * 32) << 16), vu);
     tc_wait_ld();
     const int col = tile * 128 + q * 32 + lane;   // column of the intermediate activation
-    float act = 0.f;
-    if (got && !S.fail && col < il) {
-      const float g = fminf(bfr(__uint_as_float(vg[0])), a.limit);
-      const float u = fminf(fmaxf(bfr(__uint_as_float(vu[0])), -a.limit), a.limit);
-      act = bfr(g / (1.f + expf(-g)) * u * weight);
-    }
-    uint8_t sc;
-    const uint8_t code = warp_quant_fp8(act, &sc);
-    if (got && !S.fail && col < il && !skip) {
-      const size_t row = (size_t)tok * a.slots + slot;
-      a.act_q[row * il + col] = code;
-      if (lane == 0) {
-        const int KBi = il / 32;
-        if (a.act_s) a.act_s[row * KBi + col / 32] = sc;
-        if (a.act_sf) a.act_sf[row * sf_bytes(1, KBi) + sf_offset(0, col / 32, KBi)] = sc;
+    const int KBi = il / 32;
+    for (int j = 0; j < (grouped ? count : 1); ++j) {     // accumulator column j = pair j of the segment (one column when ungrouped)
+      const float wj = grouped ? a.seg_weight[slot * 16 + j] : weight;
+      float act = 0.f;
+      if (got && !S.fail && col < il) {
+        const float g = fminf(bfr(__uint_as_float(vg[j])), a.limit);
+        const float u = fminf(fmaxf(bfr(__uint_as_float(vu[j])), -a.limit), a.limit);
+        act = bfr(g / (1.f + expf(-g)) * u * wj);
+      }
+      uint8_t sc;
+      const uint8_t code = warp_quant_fp8(act, &sc);
+      if (got && !S.fail && col < il && !skip) {
+        const size_t row = grouped ? (size_t)slot * 16 + j : (size_t)tok * a.slots + slot;
+        a.act_q[row * il + col] = code;
+        if (lane == 0) {
+          if (a.act_s) a.act_s[row * KBi + col / 32] = sc;
+          if (a.act_sf) {
+            if (grouped) a.act_sf[(size_t)slot * sf_bytes(16, KBi) + sf_offset(j, col / 32, KBi)] = sc;   // one atom set per segment, row j
+            else a.act_sf[row * sf_bytes(1, KBi) + sf_offset(0, col / 32, KBi)] = sc;
+          }
+        }
       }
     }
     if ((!got || S.fail) && lane == 0 && q == 0) status_set(a.status, ST_TIMEOUT, 20 + S.fail, blockIdx.x, blockIdx.y);
@@ -844,6 +892,40 @@ int sfb_umma_down(const void* tmapA, const void* tmapA2, const void* tmapB, cons
   a.slots = slots; a.inter = inter; a.d = d; a.scratch = scratch; a.tickets = tickets;
   a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f; a.out_stride = out_stride; a.status = (Status*)status;
   return launch_umma(tmapA, tmapA2, tmapB, a, dim3(d / 128, slots, n_tok), 16, stream);
+}
+
+}  // extern "C"
+
+extern "C" {
+
+// Grouped MoE (rows sorted by expert, see csrc/k_moe.cu moe_plan): gate/up over `segments` segments of up to 16 pairs.
+// tmapB = permuted activations [segments*16, d] (16-row box); sfb = one atom set per segment (rows = pair slots).
+int sfb_umma_gate_up_grouped(const void* tmapA, const void* tmapA2, const void* tmapB, const void* sfa, const void* sfa2, const void* sfb,
+                             const int* seg_expert, const int* seg_count, const float* seg_weight, void* act_q, void* act_sf, int segments,
+                             int d, int inter, float limit, void* status, cudaStream_t stream) {
+  if (inter % 128 || d % 32 || segments < 1) return (int)cudaErrorInvalidValue;
+  UmmaArgs a{};
+  a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (d / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
+  a.a_fp4 = 1; a.top_k = 0; a.slots = 1; a.inter = inter; a.d = d; a.act_q = (uint8_t*)act_q; a.act_sf = (uint8_t*)act_sf; a.limit = limit;
+  a.seg_expert = seg_expert; a.seg_count = seg_count; a.seg_weight = seg_weight; a.status = (Status*)status;
+  const size_t smem = sizeof(UmmaSmem<16, 2, UM_STAGES_GATEUP>) + 1024;
+  static bool done = false;
+  if (!done) { cudaFuncSetAttribute(umma_gateup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+  const CUtensorMap* mA = (const CUtensorMap*)tmapA;
+  const CUtensorMap* mA2 = (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA);
+  return (int)sfb_launch(umma_gateup_kernel, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem, stream, *mA, *mA2, *(const CUtensorMap*)tmapB, a);
+}
+
+// out_f [segments*16, d] fp32: one row per pair slot (the caller sums a token's pairs in slot order)
+int sfb_umma_down_grouped(const void* tmapA, const void* tmapA2, const void* tmapB, const void* sfa, const void* sfa2, const void* sfb,
+                          const int* seg_expert, const int* seg_count, float* out_f, int segments, int d, int inter, void* status,
+                          cudaStream_t stream) {
+  if (d % 128 || inter % 128 || segments < 1) return (int)cudaErrorInvalidValue;
+  UmmaArgs a{};
+  a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (inter / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
+  a.a_fp4 = 1; a.mode = UM_DOWN_GROUPED; a.inter = inter; a.d = d; a.out_f = out_f; a.out_stride = d; a.seg_expert = seg_expert;
+  a.seg_count = seg_count; a.status = (Status*)status; a.splits = 1;
+  return launch_umma(tmapA, tmapA2, tmapB, a, dim3(d / 128, segments, 1), 16, stream);
 }
 
 }  // extern "C"

@@ -132,6 +132,7 @@ class Engine:
         # image rows: input embedding supplied by the caller (vision tower output / delimiter vectors), routed with
         # the vision-language router bias
         self.supports_vision = vision
+        self.group_moe = True        # rows steps of 4+ rows run the experts grouped by expert (same bits, fewer weight reads)
         self.drafter = bool(drafter and weights.mtp_layers)
         self.kv = KVCache(cfg, max_lanes, max_context, max_rows, self.dev, lane_budget_bytes, draft_stages=self.drafter)
         R, d, hc, hd, q = max_rows, cfg.hidden_size, cfg.hc_mult, cfg.head_dim, cfg.q_lora_rank
@@ -464,6 +465,50 @@ class Engine:
             N.gemv(N.WF_FP8, L.wo_b, L.wo_b_sf, self.gl * ol, d, self.gl * ol, n, xb=self.oa, x_quant=True,
                    out_b=self.y_attn); self._k()
 
+    GROUP_MIN_ROWS = 4      # from this many rows on, the step's (token, expert) pairs are sorted by expert
+
+    def _group_segments(self, n: int, k: int, E_local: int) -> int:
+        """Segments launched for n rows: enough for every expert in use plus the experts with more than 16 pairs, plus the
+        shared expert's; fixed per row count so that a captured graph stays valid."""
+        P = n * k
+        return min(P, E_local + P // 16) + (n + 15) // 16
+
+    def _group_buffers(self):
+        if getattr(self, "_grp", None) is None:
+            from ... import codecs as CC
+            cfg, dev, R = self.cfg, self.dev, self.max_rows
+            d, il = cfg.hidden_size, self.il
+            S = self._group_segments(R, cfg.top_k, self.w.experts_local or cfg.n_routed_experts)
+            u8 = dict(dtype=torch.uint8, device=dev)
+            g = dict(S=S,
+                     seg_expert=torch.full((S,), -1, dtype=torch.int32, device=dev), seg_count=torch.zeros((S,), dtype=torch.int32, device=dev),
+                     seg_weight=torch.zeros((S * 16,), dtype=torch.float32, device=dev), seg_token=torch.full((S * 16,), -1, dtype=torch.int32, device=dev),
+                     pair_pos=torch.full((R * (cfg.top_k + 1),), -1, dtype=torch.int32, device=dev),
+                     xperm=torch.zeros((S * 16, d), **u8), x_atoms=torch.full((S, CC.sf_bytes(16, d // 32)), 127, **u8),
+                     act_q=torch.zeros((S * 16, il), **u8), act_sf=torch.full((S, CC.sf_bytes(16, il // 32)), 127, **u8),
+                     ypair=torch.zeros((S * 16, d), dtype=torch.float32, device=dev))
+            g["tmap_x"] = N.TensorMap(g["xperm"], S * 16, d, d, 16)
+            g["tmap_act"] = N.TensorMap(g["act_q"], S * 16, il, il, 16)
+            g["x_atom_bytes"] = CC.sf_bytes(16, d // 32)
+            self._grp = g
+        return self._grp
+
+    def _ffn_grouped(self, n: int, T, k: int, shared_here: bool) -> None:
+        """Routed + shared experts for n rows with each expert's weights read once per segment of 16 pairs (csrc/k_moe.cu moe_plan).
+        Per-pair arithmetic and the per-token slot-order sum are those of the ungrouped kernels: the bits do not change."""
+        cfg = self.cfg
+        d = cfg.hidden_size
+        g = self._group_buffers()
+        E_local = self.w.experts_local or cfg.n_routed_experts
+        S = self._group_segments(n, k, E_local)
+        N.moe_plan(self.ids, self.wts, n, k, E_local, shared_here, S, g["seg_expert"], g["seg_count"], g["seg_weight"], g["seg_token"], g["pair_pos"]); self._k()
+        N.moe_permute(self.xq, self.xs, g["seg_token"], g["xperm"], g["x_atoms"], S * 16, d, g["x_atom_bytes"]); self._k()
+        N.umma_gate_up_grouped(T.w13.tmap, T.s13.tmap, g["tmap_x"], T.w13.atoms, T.s13.atoms, g["x_atoms"], g["seg_expert"], g["seg_count"],
+                               g["seg_weight"], g["act_q"], g["act_sf"], S, d, self.il, cfg.swiglu_limit, status=self.status); self._k()
+        N.umma_down_grouped(T.w2.tmap, T.s2.tmap, g["tmap_act"], T.w2.atoms, T.s2.atoms, g["act_sf"], g["seg_expert"], g["seg_count"], g["ypair"],
+                            S, d, self.il, status=self.status); self._k()
+        N.moe_combine(g["ypair"], g["pair_pos"], self.y_ffn, n, k + 1, d, self.y_ffn.stride(0)); self._k()
+
     def _ffn(self, n: int, L: LayerW, l: int = 0, T="auto", E: int | None = None, k: int | None = None, sub: int | None = None):
         cfg = self.cfg
         self._pushed = False
@@ -487,6 +532,9 @@ class Engine:
             N.expert_remap(self.ids, n * k, self.w.expert_lo, self.w.experts_local); self._k()
             if l % self.world != self.rank:
                 slots = k
+        if T is not None and T.w13 is not None and not draft and n >= self.GROUP_MIN_ROWS and self.group_moe and k == cfg.top_k:
+            self._ffn_grouped(n, T, k, slots == k + 1)
+            return
         if T is not None and T.w13 is not None:
             tcb = self.tcb
             tbx = tcb.bmap(self.xq, self.max_rows, d, 16)

@@ -178,6 +178,32 @@ def router_topk(dots, bias, bias_vl, is_image, ids, wts, n, E, k, route_scale, n
     _check(code, "router_topk")
 
 
+def moe_plan(ids, wts, n, k, E, shared, S, seg_expert, seg_count, seg_weight, seg_token, pair_pos):
+    _check(lib().sfb_moe_plan(_p(ids), _p(wts), c_int(n), c_int(k), c_int(E), c_int(1 if shared else 0), c_int(S), _p(seg_expert), _p(seg_count),
+                              _p(seg_weight), _p(seg_token), _p(pair_pos), _stream()), "moe_plan")
+
+
+def moe_permute(xq, xs, seg_token, xperm, seg_atoms, slots, d, atom_set_bytes):
+    _check(lib().sfb_moe_permute(_p(xq), _p(xs), _p(seg_token), _p(xperm), _p(seg_atoms), c_int(slots), c_int(d), c_int(atom_set_bytes), _stream()),
+           "moe_permute")
+
+
+def moe_combine(ypair, pair_pos, y, n, k1, d, y_stride):
+    _check(lib().sfb_moe_combine(_p(ypair), _p(pair_pos), _p(y), c_int(n), c_int(k1), c_int(d), c_int64(y_stride), _stream()), "moe_combine")
+
+
+def umma_gate_up_grouped(tmap_a, tmap_a2, tmap_b, sfa, sfa2, sfb, seg_expert, seg_count, seg_weight, act_q, act_sf, segments, d, inter, limit, status=None):
+    _check(lib().sfb_umma_gate_up_grouped(c_void_p(tmap_a.ptr), c_void_p(tmap_a2.ptr) if tmap_a2 else None, c_void_p(tmap_b.ptr), _p(sfa), _p(sfa2),
+                                          _p(sfb), _p(seg_expert), _p(seg_count), _p(seg_weight), _p(act_q), _p(act_sf), c_int(segments), c_int(d),
+                                          c_int(inter), c_float(limit), _p(status), _stream()), "umma_gate_up_grouped")
+
+
+def umma_down_grouped(tmap_a, tmap_a2, tmap_b, sfa, sfa2, sfb, seg_expert, seg_count, out_f, segments, d, inter, status=None):
+    _check(lib().sfb_umma_down_grouped(c_void_p(tmap_a.ptr), c_void_p(tmap_a2.ptr) if tmap_a2 else None, c_void_p(tmap_b.ptr), _p(sfa), _p(sfa2),
+                                       _p(sfb), _p(seg_expert), _p(seg_count), _p(out_f), c_int(segments), c_int(d), c_int(inter), _p(status),
+                                       _stream()), "umma_down_grouped")
+
+
 def expert_remap(ids, n, lo, count):
     _check(lib().sfb_expert_remap(_p(ids), c_int(n), c_int(lo), c_int(count), _stream()), "expert_remap")
 

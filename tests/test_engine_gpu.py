@@ -437,3 +437,21 @@ def test_virtual_expert_parallel_ranks_match_the_single_rank_engine(tiny):
         assert toks[0] == toks[1] == int(logits.argmax())
         agree += toks[0] == int(ref.argmax())
     assert sum(errs) / len(errs) < 0.06 and agree >= 0.6 * len(prompt)
+
+
+def test_grouped_moe_gives_the_bits_of_the_ungrouped_kernels(tiny):
+    """Rows steps of 4+ rows sort their (token, expert) pairs by expert so that an expert is read once per segment; the per-pair
+    arithmetic and the slot-order sum per token are unchanged, so the logits are bit-identical."""
+    from sparkflash_b200.models.deepseek_v41 import engine as E
+    cfg, ck, w, orc, dw = tiny
+    prompt = _prompt(cfg, 48, seed=11)
+    outs = []
+    for grouped in (False, True):
+        e = E.Engine(dw, max_lanes=3, max_context=256, max_rows=16, arm="tc", use_graphs=False, keep_logits=True)
+        e.group_moe = grouped
+        e.step(prompt[:16], [0] * 16, list(range(16)))
+        e.step(prompt[16:21], [1] * 5, list(range(5)))                      # 5 rows: one short segment per expert
+        e.step(prompt[21:37], [0, 1, 2] * 5 + [2], [16, 5, 0, 17, 6, 1, 18, 7, 2, 19, 8, 3, 20, 9, 4, 5])   # three lanes in one step
+        e.check_status()
+        outs.append(e.logits[:16].clone())
+    assert torch.equal(outs[0], outs[1])
