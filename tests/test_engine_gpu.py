@@ -451,7 +451,7 @@ def test_grouped_moe_gives_the_bits_of_the_ungrouped_kernels(tiny):
         e.group_moe = grouped
         e.step(prompt[:16], [0] * 16, list(range(16)))
         e.step(prompt[16:21], [1] * 5, list(range(5)))                      # 5 rows: one short segment per expert
-        e.step(prompt[21:37], [0, 1, 2] * 5 + [2], [16, 5, 0, 17, 6, 1, 18, 7, 2, 19, 8, 3, 20, 9, 4, 5])   # three lanes in one step
+        e.step(prompt[21:37], [0] * 5 + [1] * 5 + [2] * 6, list(range(16, 21)) + list(range(5, 10)) + list(range(6)))   # three lanes in one step
         e.check_status()
         outs.append(e.logits[:16].clone())
     assert torch.equal(outs[0], outs[1])
