@@ -743,8 +743,12 @@ class Engine:
                 N.sample_fold(self._draft_bv, self._draft_bi, self.world, 1, 1, self.draft_tokens[i + 1:i + 2]); self._k()
             else:
                 N.sample_fold(self.best_val[:, i:], self.best_id[:, i:], 1, 1, R, self.draft_tokens[i + 1:i + 2]); self._k()
+        # confidence head: reads the collapsed residual before the final norm (pre coefficients of the last seam) and the Markov
+        # embedding of each position's input token
         emb = w.markov_embed[self.draft_tokens[:n].long()].float()
-        self.draft_conf[:n] = self.xn[:n].float() @ w.conf_w[:d] + emb @ w.conf_w[d:]
+        pre = self.coef[(k - 1) % 2][:n, :cfg.hc_mult]
+        x = (pre.unsqueeze(-1) * self.h[:n].float()).sum(1).to(torch.bfloat16).float()
+        self.draft_conf[:n] = x @ w.conf_w[:d] + emb @ w.conf_w[d:]
         self._join_prefetch()
 
     # ---- public step -------------------------------------------------------------------------------------
