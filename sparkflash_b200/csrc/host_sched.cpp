@@ -319,9 +319,7 @@ int sfb_sched_commit(void* h, int64_t id, int rows_done, const int32_t* new_toke
   q.spec_depth = 0;
   bool finished = false;
   for (int i = 0; i < n_new; ++i) {
-    // keep the token list consistent with what the KV holds: tokens past `computed` are pending inputs
-    if ((int)q.tokens.size() > q.computed + i) q.tokens.resize(q.computed + i);
-    q.tokens.push_back(new_tokens[i]);
+    q.tokens.push_back(new_tokens[i]);      // tokens past `computed` are pending inputs: the next anchor and nothing else
     q.generated++;
     if (new_tokens[i] == eos_id || q.generated >= q.max_new) { finished = true; break; }
   }

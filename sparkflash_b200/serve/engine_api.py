@@ -200,8 +200,6 @@ class Generation:
         self.t0 = time.monotonic()
         self.t_first: float | None = None
 
-    _MARKUP = None
-
     def _visible(self, token_id: int) -> str:
         piece = self.raw.push(token_id)
         if self.req.skip_special_tokens and self.tok.is_special(token_id):

@@ -227,7 +227,7 @@ class Server:
                     if ev[2] == "engine_failed":
                         self.metrics.set("sparkflash_serving", 0)
                         raise ApiError(503, ev[1], "engine_unavailable")
-                    raise ApiError(500 if first else 500, ev[1], ev[2])
+                    raise ApiError(500, ev[1], ev[2])
         finally:
             await agen.aclose()
         d = gen.flush()
@@ -277,9 +277,6 @@ class Server:
         if req.images and self.vision is not None and self.engine.capabilities.vision:
             req.prompt_tokens, req.vision = self.vision.expand(req.prompt_tokens, req.images)
             req.images = []
-        elif not req.images:
-            # a placeholder typed as text must not be mistaken for an image span
-            pass
         req.tools = bool(tools)
         req.tool_block_open = required
         self._sampling(body, req, max_key)
@@ -606,7 +603,7 @@ class Server:
         mid = "msg_" + uuid.uuid4().hex[:24]
 
         def stop_reason(r):
-            return {"stop": "end_turn", "length": "max_tokens", "tool_calls": "tool_use"}.get(r, "end_turn") if not (r == "stop" and False) else "end_turn"
+            return {"stop": "end_turn", "length": "max_tokens", "tool_calls": "tool_use"}.get(r, "end_turn")
 
         if body.get("stream"):
             async def stream():

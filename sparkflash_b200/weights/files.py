@@ -99,8 +99,8 @@ class SafeTensorsFile:
         buf = (ctypes.c_uint8 * nb.value).from_address(p)
         flat = torch.frombuffer(buf, dtype=torch.uint8)
         tdt = _DT[dt]
-        if dt == "F4":                       # two values per byte: the last dimension is halved
-            shape = shape[:-1] + [shape[-1] // 2] if shape and shape[-1] * 1 == nb.value * 2 // max(1, _prod(shape[:-1])) else shape
+        if dt == "F4" and shape and _prod(shape) == 2 * nb.value:      # two values per byte: the stored last dimension is half the logical one
+            shape = shape[:-1] + [shape[-1] // 2]
         return flat.view(tdt).reshape(shape)
 
 
