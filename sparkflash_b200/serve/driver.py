@@ -262,11 +262,13 @@ class DeviceDriver(InferenceEngine):
             self._fail(f"{type(e).__name__}: {e}")
 
     def _wire(self, inputs: dict) -> dict:
-        return {"subs": [(l.seq, l.req) for l in inputs["subs"]], "cancels": inputs["cancels"], "local": inputs["subs"]}
+        """What travels to the followers: sequence numbers and requests, nothing tied to this process's event loop."""
+        self._local_subs = inputs["subs"]
+        return {"subs": [(l.seq, l.req) for l in inputs["subs"]], "cancels": list(inputs["cancels"])}
 
     def _unwire(self, msg: dict) -> dict:
         if self.channel.rank == 0:
-            return {"subs": msg["local"], "cancels": msg["cancels"]}
+            return {"subs": self._local_subs, "cancels": msg["cancels"]}
         return {"subs": [_Live(req, seq, None, None) for seq, req in msg["subs"]], "cancels": msg["cancels"]}
 
     def _tick(self) -> bool:

@@ -84,3 +84,44 @@ def test_lost_heartbeats_time_out_without_any_socket_error():
     lead.close()
     th.join(5)
     assert "why" in res
+
+
+def _serve_rank(rank, world, port, q):
+    """One rank of a serving group on CPU: the driver over a fake rows engine, tick inputs replicated through the channel."""
+    import asyncio
+    from sparkflash_b200.serve.driver import DeviceDriver, FakeRowsEngine
+    from sparkflash_b200.serve.engine_api import EngineRequest
+    from sparkflash_b200.serve.tokenizer import ByteTokenizer
+    ch = ControlChannel(rank, world, port=port, heartbeat=0.05, timeout=3.0)
+    eng = FakeRowsEngine(max_rows=8)
+    drv = DeviceDriver(eng, ByteTokenizer(300), channel=ch, eos_id=10 ** 9, prefix_reuse_min=1000).start()
+    if rank == 0:
+        async def go():
+            async def one(i):
+                toks = []
+                async for ev in drv.generate(EngineRequest(f"r{i}", "m", list(range(40 + i, 60 + i)), max_tokens=6, temperature=0.0)):
+                    if ev[0] == "token":
+                        toks.append(ev[1])
+                return toks
+            return await asyncio.gather(*[one(i) for i in range(3)])
+        out = asyncio.run(go())
+        time.sleep(0.3)                       # let the followers run the last tick before the channel closes
+        q.put((0, out, list(eng.steps)))
+        drv.shutdown(0.5)
+    else:
+        while drv.failed is None and ch.alive()[0]:
+            time.sleep(0.05)
+        q.put((rank, None, list(eng.steps)))
+
+
+def test_followers_replay_the_leaders_ticks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_serve_rank, args=(r, 2, PORT + 5, q)) for r in range(2)]
+    [p.start() for p in ps]
+    got = sorted([q.get(timeout=60) for _ in ps], key=lambda t: t[0])
+    [p.join(10) for p in ps]
+    lead_steps, foll_steps = [s for s in got[0][2]], [s for s in got[1][2]]
+    assert all(len(t) == 6 for t in got[0][1])
+    # the follower ran the same rows steps in the same order (it may miss only ticks after the leader's last answer)
+    assert foll_steps[:len(lead_steps)] == lead_steps[:len(foll_steps)] and len(foll_steps) >= len(lead_steps) - 1 and len(foll_steps) > 5
