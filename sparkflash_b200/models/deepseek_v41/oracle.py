@@ -156,8 +156,11 @@ class SeqState:
 
 
 class Oracle:
-    def __init__(self, cfg: ModelConfig, weights: dict[str, torch.Tensor], world: int = 1):
-        self.cfg, self.w, self.world = cfg, weights, world
+    def __init__(self, cfg: ModelConfig, weights: dict[str, torch.Tensor], world: int = 1, moe_mode: str = "tp"):
+        """``moe_mode`` "ep": each simulated rank holds whole experts ``[r*E/W, (r+1)*E/W)`` of the main layers and rank
+        ``layer % W`` runs the shared expert; a rank's partial is its experts' sum rounded to bf16 (draft stages stay
+        width-sliced, as on the device)."""
+        self.cfg, self.w, self.world, self.moe_mode = cfg, weights, world, moe_mode
         self.inv_freq = {False: rope_inv_freq(cfg, False), True: rope_inv_freq(cfg, True)}
         self.trace: dict[str, torch.Tensor] | None = None  # filled when a test asks for intermediates
         self.engram = None
@@ -316,7 +319,7 @@ class Oracle:
         u = bf(fp8_linear(x, w3)).clamp(-lim, lim)
         return bf(torch.nn.functional.silu(g) * u * weight)
 
-    def _moe(self, p: str, x: torch.Tensor, n_exp: int, top_k: int) -> torch.Tensor:
+    def _moe(self, p: str, x: torch.Tensor, n_exp: int, top_k: int, layer: int | None = None) -> torch.Tensor:
         w = self.w
         pick, wt = self._route(p, x, n_exp, top_k)
         self._t(f"{p}.route_ids", torch.tensor(pick)); self._t(f"{p}.route_w", wt)
@@ -325,6 +328,15 @@ class Oracle:
         w2s = [w[f"{p}.ffn.experts.{e}.w2"] for e in pick]
         acts.append(self._expert_act(x, w[f"{p}.ffn.shared_experts.w1"], w[f"{p}.ffn.shared_experts.w3"], 1.0))
         w2s.append(w[f"{p}.ffn.shared_experts.w2"])
+        if self.moe_mode == "ep" and layer is not None and self.world > 1:
+            W, per = self.world, n_exp // self.world
+            owner = [e // per for e in pick] + [layer % W]
+            total = None
+            for r in range(W):
+                terms = [fp8_linear(a, w2) for a, w2, o in zip(acts, w2s, owner) if o == r]
+                part = bf(sum(terms)) if terms else torch.zeros(w2s[-1].shape[0])
+                total = part if total is None else total + part
+            return total
         return self._row_parallel(acts, w2s)
 
     # ---- one block -----------------------------------------------------------------------------------
@@ -340,7 +352,7 @@ class Oracle:
         f_pre, f_post, f_comb = hc_coeffs(h, w[f"{p}.hc_ffn_fn"], w[f"{p}.hc_ffn_scale"], w[f"{p}.hc_ffn_base"], cfg)
         x = rmsnorm(hc_pre(h, a_pre), w[f"{p}.ffn_norm.weight"], cfg.norm_eps)
         self._t(f"L{l}.ffn_in", x)
-        y = bf(self._moe(p, x, n_exp, top_k))
+        y = bf(self._moe(p, x, n_exp, top_k, layer=l if l < cfg.n_layers else None))
         self._t(f"L{l}.ffn_out", y)
         h = hc_post(y, h, f_post, f_comb)
         self._t(f"L{l}.h", h)

@@ -394,9 +394,9 @@ def test_virtual_tensor_parallel_ranks_match_oracle_seams(tiny, arm):
 
 def test_virtual_expert_parallel_ranks_match_the_single_rank_engine(tiny):
     """Expert parallelism (whole experts per rank, shared expert run by one rank per layer) on two virtual ranks in
-    lockstep: same tokens on both ranks, first position within rounding of the one-rank engine, later ones
+    lockstep: same tokens on both ranks, first position within rounding of the oracle's expert-parallel seams, later ones
     statistically (a different summation grouping than tensor parallelism, same arithmetic otherwise)."""
-    from sparkflash_b200.models.deepseek_v41 import engine as E, prepare as P
+    from sparkflash_b200.models.deepseek_v41 import engine as E, oracle as O, prepare as P
     from sparkflash_b200.parallel.fused import FusedComm
     cfg, ck, w, orc, dw = tiny
     W = 2
@@ -408,12 +408,12 @@ def test_virtual_expert_parallel_ranks_match_the_single_rank_engine(tiny):
         e = E.Engine(pw, max_lanes=2, max_context=256, max_rows=16, comm=comms[r], use_graphs=False, arm="tc")
         comms[r].attach_local(e)
         engs.append(e)
-    one = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, use_graphs=False, arm="tc", keep_logits=True)
+    orc_ep = O.Oracle(cfg, w, world=W, moe_mode="ep")
+    st = orc_ep.new_state()
     prompt = _prompt(cfg, 16, seed=7)
     agree, errs = 0, []
     for pos, tok in enumerate(prompt):
-        one.step([tok], [0], [pos])
-        ref = one.logits[0].float().cpu()
+        ref = orc_ep.step(st, tok)
         for e in engs:
             e.tokens[:1] = tok; e.row_lane[:1] = 0; e.row_pos[:1] = pos; e.temp[:1] = 0.0; e.seed[:1] = 0
         gens = [e._forward_gen(1, 1024) for e in engs]
@@ -431,7 +431,7 @@ def test_virtual_expert_parallel_ranks_match_the_single_rank_engine(tiny):
         logits = torch.cat([e.logits[0].cpu() for e in engs])
         scale = ref.abs().max().item()
         if pos == 0:
-            assert (logits - ref).abs().max().item() < 0.03 * scale
+            assert (logits - ref).abs().max().item() < 0.02 * scale, (logits - ref).abs().max().item() / scale
         errs.append((logits - ref).abs().mean().item() / scale)
         toks = [int(e.tokens_out[0]) for e in engs]
         assert toks[0] == toks[1] == int(logits.argmax())
