@@ -99,10 +99,16 @@ void place_waiting(Scheduler& s) {
     // longest reusable prefix among the free lanes (never the whole prompt: the last row must be computed)
     int best = -1, best_len = 0;
     for (int li : free_lanes) {
-      int c = common_prefix(s.lanes[li].held, q.tokens, (int)q.tokens.size() - 1);
+      const Lane& C = s.lanes[li];
+      int c = common_prefix(C.held, q.tokens, (int)q.tokens.size() - 1);
+      if (s.cfg.decoder_tail > 0 && c > 0 && C.full_from > 0 && c - s.cfg.decoder_tail < C.full_from) {
+        // the prefix forks inside rows whose upper layers were skipped: re-run one tail's worth of rows with every
+        // layer (they start cold and are exact again by the fork point)
+        c = std::max(0, c - s.cfg.decoder_tail);
+      }
       // the window ring is addressed by position modulo its size: rows the old sequence wrote far past the
-      // shared prefix have overwritten the prefix's own window tail, and then the prefix cannot be reused
-      if ((int64_t)s.lanes[li].held.size() - c > s.cfg.ring_slack) continue;
+      // kept prefix have overwritten the prefix's own window tail, and then the prefix cannot be reused
+      if ((int64_t)C.held.size() - c > s.cfg.ring_slack) continue;
       if (c >= s.cfg.prefix_reuse_min && c > best_len) { best = li; best_len = c; }
     }
     if (best < 0) {  // least recently used free lane (ties: lowest index)
@@ -115,11 +121,6 @@ void place_waiting(Scheduler& s) {
       s.prefix_rows += best_len;
     }
     Lane& L = s.lanes[best];
-    if (s.cfg.decoder_tail > 0 && best_len > 0 && L.full_from > 0 && best_len - s.cfg.decoder_tail < L.full_from) {
-      // the prefix forks inside rows whose upper layers were skipped: re-run one tail's worth of rows with every layer
-      // (they start cold and are exact again by the fork point)
-      best_len = std::max(0, best_len - s.cfg.decoder_tail);
-    }
     if (best_len < L.full_from) L.full_from = best_len;      // rows kept are all before the old boundary: nothing upper-layer is kept
     L.owner = q.id;
     L.held.resize(best_len);

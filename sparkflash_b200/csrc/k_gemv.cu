@@ -45,6 +45,10 @@ struct GemvArgs {
   // partial to out_f + z*split_stride; the consumer adds the slices in index order
   int ksplit;
   int64_t split_stride;
+  // blockIdx.x = row_group * tile_blocks + tile_block: each row group takes every row_groups-th set of R activation
+  // rows, so many-row launches spread over the machine instead of looping in one wave (same sums per row either way)
+  int tile_blocks;
+  int row_groups;
 };
 
 template <int R>
@@ -125,11 +129,12 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
   const int chunks = a.K / EPC;
   const int c_lo = (int)((int64_t)chunks * blockIdx.z / a.ksplit), c_hi = (int)((int64_t)chunks * (blockIdx.z + 1) / a.ksplit);
 
-  for (int r0 = 0; r0 < a.n; r0 += R) {
+  const int tile_block = blockIdx.x % a.tile_blocks, row_group = blockIdx.x / a.tile_blocks;
+  for (int r0 = row_group * R; r0 < a.n; r0 += R * a.row_groups) {
     __syncthreads();
     load_x<R>(a, r0, g * a.K, xs_sm);
     __syncthreads();
-   for (int tile = blockIdx.x; tile * GV_ROWS < a.N; tile += gridDim.x) {
+   for (int tile = tile_block; tile * GV_ROWS < a.N; tile += a.tile_blocks) {
     const int row0 = tile * GV_ROWS + warp * GV_RPW;
     float acc[GV_RPW][R];
 #pragma unroll
@@ -208,7 +213,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
 }
 
 template <int WF>
-static int launch_gemv(const GemvArgs& a, cudaStream_t stream) {
+static int launch_gemv(GemvArgs a, cudaStream_t stream) {
   const int64_t smem1 = (int64_t)sm_pad(a.K) * 4;
   int R = 1;
   if (a.n >= 4 && smem1 * 4 <= 96 * 1024) R = 4;
@@ -216,7 +221,11 @@ static int launch_gemv(const GemvArgs& a, cudaStream_t stream) {
   if (smem1 > 96 * 1024) return (int)cudaErrorInvalidValue;
   int tiles = (a.N + GV_ROWS - 1) / GV_ROWS;
   const int cap = (148 * 4 + a.groups - 1) / a.groups;  // a few resident blocks per SM; each loops over row tiles
-  dim3 grid(tiles < cap ? tiles : cap, a.groups, a.ksplit);
+  a.tile_blocks = tiles < cap ? tiles : cap;
+  const int passes = (a.n + R - 1) / R;
+  const int room = cap * 2 / (a.tile_blocks * a.ksplit);          // row groups while the grid stays within a couple of waves
+  a.row_groups = passes < room ? passes : (room < 1 ? 1 : room);
+  dim3 grid(a.tile_blocks * a.row_groups, a.groups, a.ksplit);
   const size_t smem = (size_t)smem1 * R;
   cudaError_t launch_rc = cudaSuccess;
 #define SFB_GV(RR)                                                                                   \

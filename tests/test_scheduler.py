@@ -161,7 +161,7 @@ def test_decoder_skip_chunks_stop_at_the_tail_and_forks_rerun_one_tail():
     PROMPTS[2] = PROMPTS[1][:20] + [7] * 30
     s.submit(2, PROMPTS[2], 1)
     phase, rows = s.tick()
-    assert rows[0].pos == 10 and s.stats()["prefix_rows"] == 20
+    assert rows[0].pos == 10 and s.stats()["prefix_rows"] == 10
     # a continuation of the whole first prompt (fork point inside the fully computed tail) keeps all of it
     s2 = Scheduler(max_lanes=1, max_rows=16, prefill_chunk=64, prefix_reuse_min=4)
     s2.set_decoder_tail(10)

@@ -75,11 +75,26 @@ def test_prefix_reuse_and_constraint_on_device(setup):
     base = torch.randint(0, 256, (40,), generator=g).tolist()
     second = base[:32] + [1, 2, 3]
     want = make().generate(second, 6)
+    third = base + [1, 2, 3]
+    want3 = make().generate(third, 6)
+    plain = DeviceDriver(make(), tok, eos_id=10 ** 9, prefix_reuse_min=8, max_lanes=1, decoder_skip=False).start()
+    try:
+        asyncio.run(_collect(plain, EngineRequest("a", "m", base, max_tokens=3, temperature=0.0)))
+        toks, fin = asyncio.run(_collect(plain, EngineRequest("b", "m", second, max_tokens=6, temperature=0.0)))
+        assert plain.sched.stats()["prefix_rows"] == 32 and toks == want
+    finally:
+        plain.shutdown(1.0)
+    # with the decoder-layer skip on, a fork inside the rows whose upper layers were skipped backs off one tail; the kept
+    # prefix would then lie behind rows that the first request's later positions overwrote in the window ring, so nothing
+    # is reused - and a continuation past the prompt's fully computed tail keeps everything
     drv = DeviceDriver(make(), tok, eos_id=10 ** 9, prefix_reuse_min=8, max_lanes=1).start()
     try:
         asyncio.run(_collect(drv, EngineRequest("a", "m", base, max_tokens=3, temperature=0.0)))
         toks, fin = asyncio.run(_collect(drv, EngineRequest("b", "m", second, max_tokens=6, temperature=0.0)))
-        assert drv.sched.stats()["prefix_rows"] == 32 and toks == want
+        assert drv.sched.stats()["prefix_rows"] == 0 and toks == want
+        asyncio.run(_collect(drv, EngineRequest("a2", "m", base, max_tokens=3, temperature=0.0)))
+        toks, fin = asyncio.run(_collect(drv, EngineRequest("d", "m", third, max_tokens=6, temperature=0.0)))
+        assert drv.sched.stats()["prefix_rows"] == 40 and toks == want3
         sc = {"type": "object", "properties": {"n": {"type": "integer", "minimum": 1, "maximum": 9}}, "required": ["n"], "additionalProperties": False}
         drv.eos_id = tok.eos_id
         toks, fin = asyncio.run(_collect(drv, EngineRequest("c", "m", base[:10], max_tokens=200, temperature=0.8, seed=3, constraint=sc)))
