@@ -465,13 +465,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           if (vec) {
             if ((tok & 3) == 0) {
               s4[0] = s4[1] = s4[2] = s4[3] = 0.f;
-              for (int sp = 0; sp < w.splits; ++sp) {          // split order, then the pair term: same sums as the scalar path
-                const float* pp = a.scratch + (size_t)sp * split_stride + lane_off;
-                const float4 t = __ldcg(reinterpret_cast<const float4*>(pp + tok));
-                s4[0] += t.x; s4[1] += t.y; s4[2] += t.z; s4[3] += t.w;
-                if (a.pair > 0) {
-                  const float4 u = __ldcg(reinterpret_cast<const float4*>(pp + tok + a.pair));
-                  s4[0] += u.x; s4[1] += u.y; s4[2] += u.z; s4[3] += u.w;
+              // split order, then the pair term: same sums as the scalar path.  Four splits' loads are issued before
+              // their (ordered) adds so that the reduce is not one L2 round trip per split
+              for (int sp0 = 0; sp0 < w.splits; sp0 += 4) {
+                float4 t[4], u[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int sp = sp0 + i < w.splits ? sp0 + i : w.splits - 1;
+                  const float* pp = a.scratch + (size_t)sp * split_stride + lane_off;
+                  t[i] = __ldcg(reinterpret_cast<const float4*>(pp + tok));
+                  u[i] = a.pair > 0 ? __ldcg(reinterpret_cast<const float4*>(pp + tok + a.pair)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  if (sp0 + i < w.splits) {
+                    s4[0] += t[i].x; s4[1] += t[i].y; s4[2] += t[i].z; s4[3] += t[i].w;
+                    if (a.pair > 0) { s4[0] += u[i].x; s4[1] += u[i].y; s4[2] += u[i].z; s4[3] += u[i].w; }
+                  }
                 }
               }
             }

@@ -132,6 +132,7 @@ class Engine:
         # image rows: input embedding supplied by the caller (vision tower output / delimiter vectors), routed with
         # the vision-language router bias
         self.supports_vision = vision
+        self.supports_headless = True    # step(head=False) for prompt chunks whose rows are not sampled
         self.group_moe = True        # rows steps of 4+ rows run the experts grouped by expert (same bits, fewer weight reads)
         self.drafter = bool(drafter and weights.mtp_layers)
         self.kv = KVCache(cfg, max_lanes, max_context, max_rows, self.dev, lane_budget_bytes, draft_stages=self.drafter)
@@ -627,6 +628,15 @@ class Engine:
             yield ("ffn", l)
         if self.drafter:
             self._dspark_seed(n)
+        if stop_after is not None:
+            # every layer ran and no row of the step is sampled (a prompt chunk that does not reach the prompt's end): the
+            # last seam still folds the final partials into the residual copies, but no head and no sampler run
+            self._seam(n, k, y_prev, None, None, None, w.norm, quant=False)
+            if self._coef_event is not None:
+                torch.cuda.current_stream().wait_event(self._coef_event)
+                self._coef_event = None
+            self._join_prefetch()
+            return
         self._seam(n, k, y_prev, None, None, None, w.norm, quant=False)
         self._dbg("final_x", self.xn, n); self._dbg("final_h", self.h, n)
         N.gemv(N.WF_BF16, w.head, None, 2 * cfg.hidden_size, self.vl, cfg.hidden_size, n, xb=self.xn,
@@ -842,12 +852,14 @@ class Engine:
         return (skipped * (self.cfg.window - 1) + self.cfg.window + skipped) if skipped > 0 else 0
 
     def step(self, tokens, lanes, positions, temperature=None, seeds=None, sync: bool = True, masks: dict | None = None,
-             image_rows: dict | None = None, filters: dict | None = None, skip_decoder: bool = False) -> torch.Tensor:
-        """``skip_decoder``: run only the layers up to the last cache owner and no head (prefill rows far before the prompt's
-        end); the returned tokens are meaningless then."""
+             image_rows: dict | None = None, filters: dict | None = None, skip_decoder: bool = False,
+             head: bool = True) -> torch.Tensor:
         """Run one rows step.  ``tokens/lanes/positions`` are host sequences of equal length n.
         Returns the sampled next-token ids as a host int32 tensor [n] (pinned) when ``sync``; the
-        device tensor ``tokens_out`` otherwise."""
+        device tensor ``tokens_out`` otherwise.
+        ``skip_decoder``: run only the layers up to the last cache owner and no head (prefill rows far before the prompt's
+        end).  ``head=False``: every layer, but no head and no sampler (a prompt chunk that stops short of the prompt's end).
+        The returned tokens are meaningless in both cases."""
         n = len(tokens)
         if not 0 < n <= self.max_rows:
             raise ValueError(f"rows {n} out of range 1..{self.max_rows}")
@@ -883,7 +895,8 @@ class Engine:
         self.row_pos[:n].copy_(io.pos[:n], non_blocking=True)
         self.temp[:n].copy_(io.temp[:n], non_blocking=True)
         self.seed[:n].copy_(io.seed[:n], non_blocking=True)
-        self.run_rows(n, self._bucket(int(max(positions))), self.decoder_skip_layer if skip_decoder else None)
+        stop_after = self.decoder_skip_layer if skip_decoder else (None if head else len(self.w.layers))
+        self.run_rows(n, self._bucket(int(max(positions))), stop_after)
         if not sync:
             return self.tokens_out[:n]
         io.out[:n].copy_(self.tokens_out[:n], non_blocking=True)

@@ -327,6 +327,9 @@ class DeviceDriver(InferenceEngine):
             kw["filters"] = filters
         if rows[0].kind == 3:
             kw["skip_decoder"] = True
+        elif phase == PHASE_PREFILL and getattr(eng, "supports_headless", False) and not any(
+                self._prefill_completes(self._live[r.seq], rows) for r in rows):
+            kw["head"] = False           # no row of this chunk is sampled: skip the vocabulary projection
         out = eng.step([r.token for r in rows], [r.lane for r in rows], [r.pos for r in rows], temps, seeds, **kw)
         out = [int(x) for x in out]
         eng.check_status()
