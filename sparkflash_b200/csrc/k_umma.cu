@@ -179,6 +179,7 @@ struct UmmaArgs {
   const uint8_t* sfb_maps[8]; //   scale atoms of each shard (katoms = b_k_per_map / 128 per row block)
   int force_bulk;             // entry point for bulk shapes: always the staged-epilogue instantiation
   int rs_rows;                // GEMM -> reduce-scatter: token row t goes only to rank t / rs_rows, at row t % rs_rows
+  int defer_reduce;           // split-K partials are left in scratch for splitk_reduce_kernel (many-row dense launches)
   uint8_t* out_q;             // optional: the bf16-rounded output re-quantised per 32 columns (E4M3)
   uint8_t* out_q_atom;        //           and its scale atoms (rows = tokens, kb = out_stride/32)
   // MoE
@@ -433,7 +434,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                               __uint_as_float(v[4 * j + 3]));
       }
     }
-    if (!(single && a.pair == 0)) {
+    if (!(single && a.pair == 0) && !a.defer_reduce) {
       // last-arriving split of this tile reduces all splits in index order
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -763,6 +764,54 @@ int sfb_tmap_encode(void* out_map /*128 bytes, 64-aligned*/, const void* base, i
 
 int sfb_umma_scratch_floats(int tiles_total, int splits, int NP) { return tiles_total * splits * 128 * NP; }
 
+}  // extern "C"
+
+namespace sfb {
+// Split-K reduce for many-row dense launches: the GEMM leaves its fp32 partials in scratch ([split][tile][128 cols][NP
+// tokens]) and this kernel adds them in split order - the order the in-kernel last-arriver uses, so a row's bits do not
+// depend on which path ran - with every (tile, four-token group) on its own CTA instead of one CTA per tile.
+struct SplitReduceArgs {
+  const float* scratch;
+  int splits, tiles_total, tiles_per_group, NP, n, N;
+  __nv_bfloat16* out_b;
+  float* out_f;
+  int64_t out_stride;
+};
+__global__ void __launch_bounds__(128) splitk_reduce_kernel(SplitReduceArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tile_id = blockIdx.x, tok0 = blockIdx.y * 4, c = threadIdx.x;
+  const int g = tile_id / a.tiles_per_group, tile = tile_id - g * a.tiles_per_group;
+  const int col = g * a.N + tile * 128 + c;
+  const size_t split_stride = (size_t)a.tiles_total * 128 * a.NP;
+  const float* pp = a.scratch + ((size_t)tile_id * 128 + c) * a.NP + tok0;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int sp0 = 0; sp0 < a.splits; sp0 += 8) {
+    float4 t[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int sp = sp0 + i < a.splits ? sp0 + i : a.splits - 1;
+      t[i] = __ldcg(reinterpret_cast<const float4*>(pp + (size_t)sp * split_stride));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (sp0 + i < a.splits) { acc.x += t[i].x; acc.y += t[i].y; acc.z += t[i].z; acc.w += t[i].w; }
+  }
+  if (col >= (g + 1) * a.N) return;
+  const float r[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (tok0 + j < a.n) {
+      const int64_t o = (int64_t)(tok0 + j) * a.out_stride + col;
+      if (a.out_b) a.out_b[o] = __float2bfloat16_rn(r[j]);
+      if (a.out_f) a.out_f[o] = r[j];
+    }
+  }
+}
+}  // namespace sfb
+
+extern "C" {
+
 // Peer table of the next launch (set by sfb_umma_set_push, consumed and cleared by the launch).
 struct PushSpec {
   void* out[8];
@@ -822,7 +871,15 @@ int sfb_umma_dense(const void* tmapA, const void* tmapB, const void* sfa, int ka
   a.n = n; a.K = K; a.a_fp4 = a_fp4; a.mode = UM_DENSE; a.N = N; a.groups = groups; a.splits = splits;
   a.scratch = scratch; a.tickets = tickets; a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f;
   a.out_stride = out_stride; a.status = (Status*)status;
-  return launch_umma(tmapA, nullptr, tmapB, a, dim3((N + 127) / 128, splits, groups), NP, stream);
+  const int tiles = (N + 127) / 128;
+  // many rows and many splits: one CTA per tile adding every split is the slow part, so the add runs as its own grid
+  a.defer_reduce = (splits > 1 && NP >= 32 && g_push.n == 0) ? 1 : 0;
+  const int rc = launch_umma(tmapA, nullptr, tmapB, a, dim3(tiles, splits, groups), NP, stream);
+  if (rc != 0 || !a.defer_reduce) return rc;
+  SplitReduceArgs r{};
+  r.scratch = scratch; r.splits = splits; r.tiles_total = tiles * groups; r.tiles_per_group = tiles; r.NP = NP; r.n = n;
+  r.N = N; r.out_b = (__nv_bfloat16*)out_b; r.out_f = out_f; r.out_stride = out_stride;
+  return (int)sfb_launch(splitk_reduce_kernel, dim3(tiles * groups, (n + 3) / 4), dim3(128), 0, stream, r);
 }
 
 // Bulk GEMM with the fused-collective options: any number of token rows (tiles of NP = 128 when n > 128),
