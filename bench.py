@@ -55,6 +55,14 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def mark(self) -> None:
+        """Samples written from here on belong to the timed window."""
+        try:
+            self.f.flush()
+            self.skip = sum(1 for _ in open(self.path))
+        except Exception:
+            self.skip = 0
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -64,9 +72,14 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         self.f.close()
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in open(self.path):
+        lines = open(self.path).read().splitlines()
+        skip = getattr(self, "skip", 0)
+        window = "timed regions"
+        if len(lines) - skip < 2:      # a run shorter than two sampling periods: fall back to every sample taken under load
+            skip, window = 0, "warm-up and timed regions"
+        sm, mx, reasons = [], [], set()
+        for line in lines[skip:]:
             p = [x.strip() for x in line.split(",")]
             if len(p) < 9:
                 continue
@@ -82,7 +95,7 @@ class ClockSampler:
         except OSError:
             pass
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 def pick_config(n_gpus: int, args):
@@ -164,6 +177,8 @@ def main() -> None:
     gen = torch.Generator().manual_seed(1234)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=gen).tolist()
 
+    sampler = ClockSampler(local)
+    sampler.start()                   # started early: nvidia-smi needs a second to come up on a multi-GPU box
     # ---- prefill of the prompt on lane 0 (rows steps of 64), timed as the prefill figure ----
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -191,9 +206,8 @@ def main() -> None:
     launches = eng.launches_per_step
     # device-timed: K replays of the captured step; positions advance on the device copy of row_pos
     one = torch.ones((), dtype=torch.int32, device=eng.dev)
-    sampler = ClockSampler(local)
     barrier()
-    sampler.start()
+    sampler.mark()
     ev0.record()
     bucket = eng._bucket(pos + args.steps)
     for _ in range(args.steps):
@@ -202,7 +216,6 @@ def main() -> None:
         eng.row_pos[:1].add_(one)
     ev1.record()
     barrier()
-    clocks = sampler.stop()
     dev_ms = ev0.elapsed_time(ev1)
     pos = pos + args.steps
     nxt = int(eng.tokens_out[0])
@@ -217,6 +230,7 @@ def main() -> None:
     barrier()
     e2e_ms = ev0.elapsed_time(ev1)
     t_wall = time.perf_counter() - t_wall0
+    clocks = sampler.stop()           # samples cover the device-timed and the end-to-end regions
 
     # ---- 16-stream decode (aggregate), device-timed ----
     extras = {}
@@ -283,6 +297,32 @@ def main() -> None:
         barrier()
         extras["dspark_draft_block_ms"] = ev0.elapsed_time(ev1) / 8
         extras["dspark_block_positions"] = cfg.dspark_block
+        # MTP on, end to end: draft a block, verify anchor + proposals as one rows step, keep the agreeing prefix.  With random
+        # weights the draft stages predict nothing, so the measured acceptance is the floor and the figure is the cost of
+        # speculation when it never pays; tokens/s at acceptance a scales as (1 + a * depth) times this step rate.
+        depth = min(4, cfg.dspark_block - 1)
+        tok_s, p_s, emitted, accepted = nxt, pos, 0, 0
+        for timed in (False, True):
+            iters = args.steps if timed else args.warmup
+            barrier()
+            ev0.record()
+            for _ in range(iters):
+                drafts, _conf = eng.draft(0, p_s - 1, tok_s)
+                rows = [tok_s] + drafts[:depth]
+                out = eng.step(rows, [0] * len(rows), list(range(p_s, p_s + len(rows))))
+                a = 0
+                while a < depth and int(out[a]) == rows[a + 1]:
+                    a += 1
+                tok_s, p_s = int(out[a]), p_s + a + 1
+                if timed:
+                    emitted += a + 1; accepted += a
+            ev1.record()
+            barrier()
+        ms_spec = ev0.elapsed_time(ev1)
+        extras["mtp_on_tok_s"] = emitted / (ms_spec / 1e3)
+        extras["mtp_on_ms_per_forward"] = ms_spec / args.steps
+        extras["mtp_on_draft_depth"] = depth
+        extras["mtp_on_accepted_per_forward"] = accepted / args.steps
     eng.check_status()
 
     def maxr(x: float) -> float:
