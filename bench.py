@@ -258,7 +258,7 @@ def main() -> None:
                   "decode_16streams_ms_per_step": ms16 / args.steps,
                   "vs_baseline_16streams": S * args.steps / (ms16 / 1e3) / BASELINE_16STREAM_TOK_S,
                   "prefill_tok_s": prefill_tok_s, "prefill_prompt_tokens": len(prompt),
-                  "prefill_note": "rows steps of 64 (CUDA-core arm)",
+                  "prefill_note": "rows steps of 64: tcgen05 projections and grouped experts, CUDA-core attention; chunks before the last skip the head",
                   "vs_baseline_prefill": prefill_tok_s / BASELINE_PREFILL_TOK_S}
     for ctx in long_ctx:
         # decode against a long cached context: the caches of lane 0 are filled with random codes (a real prefill of a million

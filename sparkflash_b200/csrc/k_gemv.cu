@@ -170,28 +170,36 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
         for (int u = 0; u < U; ++u) {
           const int c = cb + 32 * u;
           if (c >= c_hi) break;
+          // decode this chunk of every weight row first, then read each activation row's chunk from shared memory once
+          // and use it for all of them (the shared-memory reads, not the FMAs, bound many-row launches)
+          float f[GV_RPW][EPC];
 #pragma unroll
           for (int i = 0; i < GV_RPW; ++i) {
-            float f[EPC];
-            if (WF == 0) decode16_e4m3_raw(wv[u][i], f);
-            else if (WF == 1) decode32_e2m1_raw(wv[u][i], f);
+            if (WF == 0) decode16_e4m3_raw(wv[u][i], f[i]);
+            else if (WF == 1) decode32_e2m1_raw(wv[u][i], f[i]);
             else {
               const uint32_t* p = reinterpret_cast<const uint32_t*>(&wv[u][i]);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) { f[2 * j] = __uint_as_float(p[j] << 16); f[2 * j + 1] = __uint_as_float(p[j] & 0xffff0000u); }
+              for (int j = 0; j < 4; ++j) { f[i][2 * j] = __uint_as_float(p[j] << 16); f[i][2 * j + 1] = __uint_as_float(p[j] & 0xffff0000u); }
             }
+          }
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-              const float4* xp = reinterpret_cast<const float4*>(xs_sm + r * sm_pad(a.K) + sm_pad(c * EPC));
-              float s = 0.f;
+          for (int r = 0; r < R; ++r) {
+            const float4* xp = reinterpret_cast<const float4*>(xs_sm + r * sm_pad(a.K) + sm_pad(c * EPC));
+            float s[GV_RPW];
 #pragma unroll
-              for (int j = 0; j < EPC / 4; ++j) {
-                float4 xv = xp[j];
-                s = fmaf(f[4 * j], xv.x, s); s = fmaf(f[4 * j + 1], xv.y, s);
-                s = fmaf(f[4 * j + 2], xv.z, s); s = fmaf(f[4 * j + 3], xv.w, s);
+            for (int i = 0; i < GV_RPW; ++i) s[i] = 0.f;
+#pragma unroll
+            for (int j = 0; j < EPC / 4; ++j) {
+              const float4 xv = xp[j];
+#pragma unroll
+              for (int i = 0; i < GV_RPW; ++i) {
+                s[i] = fmaf(f[i][4 * j], xv.x, s[i]); s[i] = fmaf(f[i][4 * j + 1], xv.y, s[i]);
+                s[i] = fmaf(f[i][4 * j + 2], xv.z, s[i]); s[i] = fmaf(f[i][4 * j + 3], xv.w, s[i]);
               }
-              acc[i][r] = fmaf(s, sc[u][i], acc[i][r]);
             }
+#pragma unroll
+            for (int i = 0; i < GV_RPW; ++i) acc[i][r] = fmaf(s[i], sc[u][i], acc[i][r]);
           }
         }
       }

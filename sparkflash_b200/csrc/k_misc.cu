@@ -3,6 +3,8 @@
 // Reference behaviour: kernels/opt_rows_sm121.cu embed_own:2564 / argmax_fold:1810 / argmax_pick:1834,
 // kernels/opt_sample_sm121.cuh (noise keyed on seed, position, token id),
 // crates/sparkflash-model-deepseek-v41/src/synthetic.rs (weights from a hash of name and seed).
+#include <cooperative_groups.h>
+
 #include "k_common.cuh"
 
 namespace sfb {
@@ -114,16 +116,23 @@ struct SampleArgs {
   int V, vocab_offset;
 };
 
-__global__ void __launch_bounds__(1024) sample_kernel(SampleArgs a) {
+constexpr int SAMPLE_CLUSTER = 8;   // CTAs per row: each scans an eighth of the vocabulary slice, CTA 0 merges through DSMEM
+
+__global__ void __cluster_dims__(SAMPLE_CLUSTER, 1, 1) __launch_bounds__(1024) sample_kernel(SampleArgs a) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
   __shared__ float sv[32];
   __shared__ int si[32];
-  const int row = blockIdx.x;
+  __shared__ float cv[SAMPLE_CLUSTER];
+  __shared__ int ci[SAMPLE_CLUSTER];
+  const int row = blockIdx.y, part = blockIdx.x;   // part == rank in the cluster
   const float T = a.temperature[row];
   const bool greedy = T < 1e-5f;
   const uint64_t base = splitmix64(a.seed[row] ^ splitmix64((uint64_t)(a.row_pos[row] + 1)));
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < a.V; i += 1024) {
+  // (value, lowest id) is a total order, so the winner does not depend on how the slice is cut
+  for (int i = part * 1024 + threadIdx.x; i < a.V; i += 1024 * SAMPLE_CLUSTER) {
     const int id = a.vocab_offset + i;
     if (a.mask && a.mask[(size_t)row * a.mask_stride + id] == 0) continue;
     float v = a.logits[(size_t)row * a.stride + i];
@@ -141,6 +150,14 @@ __global__ void __launch_bounds__(1024) sample_kernel(SampleArgs a) {
   if (threadIdx.x == 0) {
     for (int w = 1; w < 32; ++w)
       if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    *cluster.map_shared_rank(&cv[part], 0) = bv;
+    *cluster.map_shared_rank(&ci[part], 0) = bi;
+  }
+  cluster.sync();
+  if (part == 0 && threadIdx.x == 0) {
+    bv = cv[0]; bi = ci[0];
+    for (int p = 1; p < SAMPLE_CLUSTER; ++p)
+      if (cv[p] > bv || (cv[p] == bv && ci[p] < bi)) { bv = cv[p]; bi = ci[p]; }
     a.best_val[row] = bv;
     a.best_id[row] = bi;
   }
@@ -296,7 +313,7 @@ int sfb_sample(const float* logits, int64_t stride, const int* row_pos, const fl
                int V, int vocab_offset, cudaStream_t stream) {
   SampleArgs a{logits, stride, row_pos, temperature, (const uint64_t*)seed, (const uint8_t*)mask, mask_stride,
                best_val, best_id, V, vocab_offset};
-  sample_kernel<<<n, 1024, 0, stream>>>(a);
+  sample_kernel<<<dim3(SAMPLE_CLUSTER, n), 1024, 0, stream>>>(a);
   return SFB_CHECK_LAUNCH();
 }
 
