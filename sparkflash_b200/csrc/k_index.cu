@@ -32,12 +32,14 @@ struct IndexQArgs {
   float wscale;
 };
 
-// grid n, block 256; one warp per (head, 32-group)
+// grid (n, IQ_SPLIT), block 256; one warp per (head, 32-group), the items dealt round-robin over the row's CTAs
 __global__ void __launch_bounds__(256) index_q_kernel(IndexQArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gph = a.idh / 32;
-  for (int item = warp; item < a.inh * gph; item += 8) {
+  for (int item = warp + 8 * blockIdx.y; item < a.inh * gph; item += 8 * gridDim.y) {
     const int h = item / gph, g = item % gph;
     const int e = g * 32 + lane;
     float v = bf16_to_f(a.qraw[(size_t)row * a.q_stride + a.q_off + (size_t)h * a.idh + e]);
@@ -58,6 +60,7 @@ __global__ void __launch_bounds__(256) index_q_kernel(IndexQArgs a) {
     float dq = e2m1_to_f32(f32_to_e2m1(v / s)) * s;
     a.qi[((size_t)row * a.idh + e) * a.inh + h] = dq;
   }
+  if (blockIdx.y != 0) return;
   for (int h = threadIdx.x; h < a.inh; h += 256)
     a.wt[(size_t)row * a.inh + h] = bfr(a.wraw[(size_t)row * a.w_stride + a.w_off + h]) * a.wscale;
 }
@@ -83,6 +86,8 @@ constexpr int IS_ENT_PER_BLOCK = 64;
 
 // grid (ceil(max_len/64), n), block 256: each warp scores 8 entries
 __global__ void __launch_bounds__(256) index_scores_kernel(IndexScoreArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float sm[];
   float* q = sm;                         // [idh * inh]
   float* kbuf = sm + a.idh * a.inh;      // [8 warps][idh]
@@ -178,6 +183,8 @@ constexpr int SEL_THREADS = 1024;
 
 // one block per row; 4 radix passes of 8 bits, then an ordered compaction
 __global__ void __launch_bounds__(SEL_THREADS) select_topk_kernel(SelectArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_need, s_total;
   __shared__ uint32_t wsum[32];
@@ -281,8 +288,7 @@ int sfb_index_q(const void* qraw, int64_t q_stride, int64_t q_off, const float* 
   IndexQArgs a{(const __nv_bfloat16*)qraw, q_stride, q_off, wraw, w_stride, w_off, (const float2*)rope, rope_stride,
                row_pos, qi, wt,
                n, inh, idh, rd, wscale};
-  index_q_kernel<<<n, 256, 0, stream>>>(a);
-  return SFB_CHECK_LAUNCH();
+  return (int)sfb_launch(index_q_kernel, dim3(n, n <= 16 ? 4 : 1), dim3(256), 0, stream, a);
 }
 
 int sfb_index_scores(const float* qi, const float* wt, const void* ik_q, const void* ik_s, int64_t ik_lane_q,
@@ -299,8 +305,7 @@ int sfb_index_scores(const float* qi, const float* wt, const void* ik_q, const v
     if (!done) { cudaFuncSetAttribute(index_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); done = true; }
   }
   dim3 grid((max_len + IS_ENT_PER_BLOCK - 1) / IS_ENT_PER_BLOCK, n);
-  index_scores_kernel<<<grid, 256, smem, stream>>>(a);
-  return SFB_CHECK_LAUNCH();
+  return (int)sfb_launch(index_scores_kernel, grid, dim3(256), smem, stream, a);
 }
 
 int sfb_hsi_blockmax(const float* scores, int64_t score_stride, const int* row_pos, int ratio, int bs,
@@ -325,8 +330,7 @@ int sfb_hsi_mark(const int* ids, int K, void* flags, int64_t f_stride, int max_b
 int sfb_select_topk(const float* scores, int64_t stride, const int* row_pos, int ratio, int len_div,
                     int max_len, int K, int* ids, int* count, int n, cudaStream_t stream) {
   SelectArgs a{scores, stride, row_pos, ratio, len_div, max_len, K, ids, count};
-  select_topk_kernel<<<n, SEL_THREADS, 0, stream>>>(a);
-  return SFB_CHECK_LAUNCH();
+  return (int)sfb_launch(select_topk_kernel, dim3(n), dim3(SEL_THREADS), 0, stream, a);
 }
 
 }  // extern "C"

@@ -117,6 +117,8 @@ struct CompressArgs {
 
 // one block per row, 256 threads. dynamic smem: (2*hd + idh) floats
 __global__ void __launch_bounds__(256) compress_append_kernel(CompressArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sh[32];
   extern __shared__ float buf[];
   float* lat = buf;            // [hd]
@@ -258,8 +260,7 @@ int sfb_compress_append(const float* raw, int64_t raw_stride, const float* norm_
                  (uint8_t*)ik_s, ckv_lane_q, ckv_lane_s, ik_lane_q, ik_lane_s, max_entries, n, hd, idh, rd,
                  ratio, eps, (Status*)status};
   const size_t smem = sizeof(float) * (size_t)(2 * hd + idh);
-  compress_append_kernel<<<n, 256, smem, stream>>>(a);
-  return SFB_CHECK_LAUNCH();
+  return (int)sfb_launch(compress_append_kernel, dim3(n), dim3(256), smem, stream, a);
 }
 
 }  // extern "C"

@@ -12,6 +12,8 @@ namespace sfb {
 // h[row, c, :] = embed[token[row], :] for every hc copy
 __global__ void embed_kernel(const __nv_bfloat16* embed, const int* tokens, __nv_bfloat16* h, int n, int hc,
                              int d, int vocab, Status* st) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.y;
   int tok = tokens[row];
   if (tok < 0 || tok >= vocab) { if (threadIdx.x == 0 && blockIdx.x == 0) status_set(st, ST_BOUNDS, 3, tok, vocab); tok = 0; }
@@ -48,6 +50,8 @@ __global__ void __launch_bounds__(256) markov_bias_kernel(float* logits, const _
 
 // tap[row, :] = bf16(mean over copies of h[row, c, :])
 __global__ void tap_mean_kernel(const __nv_bfloat16* h, __nv_bfloat16* tap, int64_t tap_stride, int hc, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.y;
   const int col = blockIdx.x * blockDim.x + threadIdx.x;
   if (col >= d) return;
@@ -66,6 +70,8 @@ struct RopeTableArgs {
   float2* out;  // [n, V, half]
 };
 __global__ void rope_table_kernel(RopeTableArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int pos = a.row_pos[row];
   for (int i = threadIdx.x; i < a.V * a.half; i += blockDim.x) {
@@ -121,6 +127,8 @@ constexpr int SAMPLE_CLUSTER = 8;   // CTAs per row: each scans an eighth of the
 __global__ void __cluster_dims__(SAMPLE_CLUSTER, 1, 1) __launch_bounds__(1024) sample_kernel(SampleArgs a) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ float cv[SAMPLE_CLUSTER];
@@ -283,8 +291,7 @@ int sfb_rope_table(const double* const* inv_freq, const int* ratio, int V, int h
   RopeTableArgs a{};
   for (int v = 0; v < V; ++v) { a.inv_freq[v] = inv_freq[v]; a.ratio[v] = ratio[v] > 0 ? ratio[v] : 1; }
   a.V = V; a.half = half; a.row_pos = row_pos; a.out = (float2*)out;
-  rope_table_kernel<<<n, 128, 0, stream>>>(a);
-  return SFB_CHECK_LAUNCH();
+  return (int)sfb_launch(rope_table_kernel, dim3(n), dim3(128), 0, stream, a);
 }
 
 int sfb_prefetch_l2(const void* p, int64_t bytes, cudaStream_t stream) {
@@ -303,9 +310,8 @@ int sfb_prefetch_experts(const void* base, int64_t stride, int64_t bytes, const 
 }
 
 int sfb_tap_mean(const void* h, void* tap, int64_t tap_stride, int n, int hc, int d, cudaStream_t stream) {
-  tap_mean_kernel<<<dim3((d + 255) / 256, n), 256, 0, stream>>>((const __nv_bfloat16*)h, (__nv_bfloat16*)tap,
-                                                               tap_stride, hc, d);
-  return SFB_CHECK_LAUNCH();
+  return (int)sfb_launch(tap_mean_kernel, dim3((d + 255) / 256, n), dim3(256), 0, stream, (const __nv_bfloat16*)h,
+                         (__nv_bfloat16*)tap, tap_stride, hc, d);
 }
 
 int sfb_sample(const float* logits, int64_t stride, const int* row_pos, const float* temperature,
@@ -313,8 +319,7 @@ int sfb_sample(const float* logits, int64_t stride, const int* row_pos, const fl
                int V, int vocab_offset, cudaStream_t stream) {
   SampleArgs a{logits, stride, row_pos, temperature, (const uint64_t*)seed, (const uint8_t*)mask, mask_stride,
                best_val, best_id, V, vocab_offset};
-  sample_kernel<<<dim3(SAMPLE_CLUSTER, n), 1024, 0, stream>>>(a);
-  return SFB_CHECK_LAUNCH();
+  return (int)sfb_launch(sample_kernel, dim3(SAMPLE_CLUSTER, n), dim3(1024), 0, stream, a);
 }
 
 int sfb_sample_fold(const void* vals, const void* ids, int W, int n, int stride, int* out_tokens,
