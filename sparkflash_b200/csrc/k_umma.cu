@@ -253,10 +253,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  pdl_wait();   // everything above is set-up; operands written by the previous kernel are read below
   UmmaWork w;
   int tok_tile = 0;
   bool skip = false;
+  int pre = 0;   // stages whose weight tile was requested before the dependency wait
   if (a.mode == UM_DENSE) {
     const int tile = blockIdx.x;
     int g = blockIdx.z;
@@ -277,6 +277,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       w.n_valid = min(NP, a.n - tok_tile * NP);
       w.sfb = a.sfb + ((size_t)((tok_tile * NP) >> 7) * a.katoms_b + g * ksteps + w.ks0) * 512;
     }
+    // dense weights and their scales do not depend on the previous kernel: request the first stages' weight tiles now, so
+    // that their fetch overlaps the predecessor's tail; the activation tiles follow after the wait
+    if (warp == 0 && lane == 0) {
+      const uint32_t stage_tx = (w.a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 1024;
+      pre = w.nks < UM_STAGES ? w.nks : UM_STAGES;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&S.full[i], stage_tx);
+        tma_load_2d(S.a[i][0], w.ma, (w.ks0 + i) * UM_BK, w.a_row0, &S.full[i]);
+        bulk_load(S.sfa[i][0], w.sfa + (size_t)i * 512, 512, &S.full[i]);
+      }
+    }
+  }
+  pdl_wait();   // operands written by the previous kernel (activations, expert ids) are read below
+  if (a.mode == UM_DENSE) {
   } else if (a.mode == UM_DOWN_GROUPED) {   // x = column tile of d, y = segment: W2_e times the segment's activation rows
     const int tile = blockIdx.x, seg = blockIdx.y;
     const int ksteps = (a.inter + UM_BK - 1) / UM_BK;
@@ -329,9 +343,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     if (lane == 0) {
       for (int i = 0; i < w.nks; ++i) {
         const int s = i % UM_STAGES;
-        if (i >= UM_STAGES && !mbar_wait(&S.empty[s], ((i / UM_STAGES) - 1) & 1)) { S.fail = 1; break; }
-        mbar_expect_tx(&S.full[s], STAGE_TX);
-        tma_load_2d(S.a[s][0], w.ma, (w.ks0 + i) * UM_BK, w.a_row0, &S.full[s]);
+        if (i >= pre) {
+          if (i >= UM_STAGES && !mbar_wait(&S.empty[s], ((i / UM_STAGES) - 1) & 1)) { S.fail = 1; break; }
+          mbar_expect_tx(&S.full[s], STAGE_TX);
+          tma_load_2d(S.a[s][0], w.ma, (w.ks0 + i) * UM_BK, w.a_row0, &S.full[s]);
+        }
         if (BULK && a.b_maps) {
           // the k-slab lives on the rank that owns this range of the hidden dimension: a plain (non-multicast)
           // TMA load from that rank's memory, and its scale atoms with a bulk copy
@@ -342,7 +358,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           tma_load_2d(S.b[s], &tmapB, w.b_x0 + i * UM_BK, w.b_row0, &S.full[s]);
           bulk_load(S.sfb[s], w.sfb + (size_t)i * 512, 512, &S.full[s]);
         }
-        bulk_load(S.sfa[s][0], w.sfa + (size_t)i * 512, 512, &S.full[s]);
+        if (i >= pre) bulk_load(S.sfa[s][0], w.sfa + (size_t)i * 512, 512, &S.full[s]);
       }
     }
   } else if (warp == 1) {
