@@ -57,6 +57,7 @@ class ControlChannel:
         self._lock = threading.Lock()
         self._closed = False
         self._failed: str | None = None
+        self.departed: set[int] = set()      # peers that said goodbye
         self._last_seen: dict[int, float] = {}
         self._ticks: list = []
         self._cv = threading.Condition()
@@ -110,6 +111,7 @@ class ControlChannel:
                         self._ticks.append(pickle.loads(payload))
                         self._cv.notify_all()
                 elif kind == GOODBYE:
+                    self.departed.add(peer)          # an orderly leave (drain), as opposed to a silent or broken peer
                     self._fail(f"rank {peer} left the group")
                     return
         except (ChannelClosed, OSError) as e:

@@ -15,7 +15,7 @@ import time
 
 
 def _boot(msg: str, **kw) -> None:
-    print(json.dumps({"ts": round(time.time(), 3), "boot": msg, **kw}), file=sys.stderr, flush=True)
+    print(json.dumps({"ts": round(time.time(), 3), "pid": os.getpid(), "boot": msg, **kw}), file=sys.stderr, flush=True)
 
 
 def build_engine(args, settings, rank: int, world: int):
@@ -96,8 +96,13 @@ def run(args) -> int:
             # followers have no HTTP surface: they serve ticks until the channel closes
             while driver.failed is None and chan.alive()[0]:
                 time.sleep(0.2)
-            _boot("follower leaving", rank=rank, reason=driver.failed or chan.alive()[1])
-            return 0 if driver.failed is None else 1
+            orderly = 0 in chan.departed           # the leader drained and said goodbye: not a failure
+            _boot("follower leaving", rank=rank, reason=driver.failed or chan.alive()[1], orderly=orderly)
+            driver.shutdown(1.0)
+            eng.close()
+            if world > 1:
+                dist.destroy_process_group()
+            return 0 if (driver.failed is None or orderly) else 1
     aliases = dict(kv.split("=", 1) for kv in os.environ.get("SFB_MODEL_ALIASES", "").split(",") if "=" in kv)
     srv = Server(engine, api_key=args.api_key, aliases=aliases, trace=trace)
     import uvicorn
@@ -112,4 +117,8 @@ def run(args) -> int:
     server.run()
     if driver is not None:
         driver.shutdown(30.0)
+        if world > 1:
+            import torch.distributed as dist
+            driver.engine.close()
+            dist.destroy_process_group()
     return 0

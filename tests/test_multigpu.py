@@ -76,3 +76,60 @@ def test_two_ranks_fused_and_nccl_agree(tmp_path, arm, collectives):
     if "nccl" in res:
         assert res["fused"][:2] == res["nccl"][:2], res
     assert len(res["fused"]) == 12
+
+
+def test_two_rank_server_answers_a_chat_request(tmp_path):
+    """The whole serving stack on two GPUs: torchrun starts ``serve`` on both ranks, rank 0 answers HTTP, the follower
+    replays the leader's ticks through the control channel, SIGTERM drains and both ranks leave with exit code 0."""
+    import time
+    import urllib.request
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    port, cport = 18431, 18432
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=repo + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29535", "-m", "sparkflash_b200", "serve", "--synthetic", "tiny", "--port", str(port),
+           "--control-port", str(cport)]
+    log = open(tmp_path / "serve.log", "w")
+    proc = subprocess.Popen(cmd, env=env, stdout=log, stderr=subprocess.STDOUT, start_new_session=True, cwd=repo)
+
+    def fail(msg):
+        os.killpg(proc.pid, signal.SIGKILL)
+        proc.wait()
+        pytest.fail(msg + "\n" + open(tmp_path / "serve.log").read()[-3000:])
+
+    try:
+        deadline = time.time() + 120
+        up = False
+        while time.time() < deadline and proc.poll() is None:
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/readyz", timeout=2) as r:
+                    up = r.status == 200
+                    if up:
+                        break
+            except Exception:
+                time.sleep(1.0)
+        if not up:
+            fail("server did not come up")
+        body = json.dumps({"model": "deepseek-v4.1-flash", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 8,
+                           "temperature": 0.0}).encode()
+        outs = []
+        for _ in range(2):
+            req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions", data=body,
+                                         headers={"Content-Type": "application/json"})
+            with urllib.request.urlopen(req, timeout=60) as r:
+                outs.append(json.loads(r.read()))
+        assert outs[0]["usage"]["completion_tokens"] >= 1
+        assert outs[0]["choices"][0]["message"]["content"] == outs[1]["choices"][0]["message"]["content"]      # greedy: repeatable
+        # SIGTERM to the leader alone: it drains, says goodbye on the control channel, and the follower leaves in order
+        boots = [json.loads(l) for l in open(tmp_path / "serve.log").read().splitlines() if l.startswith("{") and '"boot"' in l]
+        leader = [b["pid"] for b in boots if b["boot"] == "listening"][0]
+        os.kill(leader, signal.SIGTERM)
+        try:
+            rc = proc.wait(timeout=60)
+        except subprocess.TimeoutExpired:
+            fail("ranks did not leave after SIGTERM")
+        assert rc == 0, open(tmp_path / "serve.log").read()[-3000:]
+    finally:
+        if proc.poll() is None:
+            os.killpg(proc.pid, signal.SIGKILL)
+            proc.wait()
