@@ -5,13 +5,16 @@
 seams per layer plus the sampler); more than that means somebody added a hidden collective.  Reference:
 scripts/perf_regression_gate.py, scripts/check-collective-count.py.
 
-    python -m sparkflash_b200.gates.perf perf --result BENCH.json --baseline perf_baseline.json [--tolerance 0.03]
+    python -m sparkflash_b200.gates.perf perf --result BENCH.json [--baseline perf_baseline.json] [--tolerance 0.03]
+
+The default baseline is ``gates/perf_baseline.json`` (B200 figures of bench.py's defaults at 1, 2 and 8 GPUs).
     python -m sparkflash_b200.gates.perf collectives --layers 40 --counted 81
 """
 from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 
 
@@ -46,7 +49,7 @@ def check_perf(result: dict, baseline: dict, tolerance: float = 0.03) -> list[st
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
-    p = sub.add_parser("perf"); p.add_argument("--result", required=True); p.add_argument("--baseline", required=True); p.add_argument("--tolerance", type=float, default=0.03)
+    p = sub.add_parser("perf"); p.add_argument("--result", required=True); p.add_argument("--baseline", default=os.path.join(os.path.dirname(__file__), "perf_baseline.json")); p.add_argument("--tolerance", type=float, default=0.03)
     c = sub.add_parser("collectives"); c.add_argument("--layers", type=int, required=True); c.add_argument("--counted", type=int, required=True)
     a = ap.parse_args(argv)
     if a.cmd == "perf":
