@@ -19,6 +19,7 @@ constexpr int GV_THREADS = 256;
 constexpr int GV_WARPS = 8;
 constexpr int GV_RPW = 2;                    // output rows per warp, loaded together
 constexpr int GV_ROWS = GV_WARPS * GV_RPW;   // output rows per block
+__host__ __device__ constexpr int gv_rpw(int wf, int r) { return (wf == 2 && r >= 4) ? 4 : GV_RPW; }
 
 struct GemvArgs {
   const uint8_t* w;        // payload, row-major [groups*N, row_bytes]
@@ -126,6 +127,10 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
   const int g = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int EPC = WF == 0 ? 16 : (WF == 1 ? 32 : 8);  // elements per 16-byte chunk
+  // output rows per warp: many-row bf16 launches (head, router, auxiliary projections) take four, so that one read of an
+  // activation chunk from shared memory feeds four weight rows; a row's sum is the same either way
+  constexpr int RPW = gv_rpw(WF, R);
+  constexpr int ROWS = GV_WARPS * RPW;
   const int chunks = a.K / EPC;
   const int c_lo = (int)((int64_t)chunks * blockIdx.z / a.ksplit), c_hi = (int)((int64_t)chunks * (blockIdx.z + 1) / a.ksplit);
 
@@ -134,25 +139,25 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
     __syncthreads();
     load_x<R>(a, r0, g * a.K, xs_sm);
     __syncthreads();
-   for (int tile = tile_block; tile * GV_ROWS < a.N; tile += a.tile_blocks) {
-    const int row0 = tile * GV_ROWS + warp * GV_RPW;
-    float acc[GV_RPW][R];
+   for (int tile = tile_block; tile * ROWS < a.N; tile += a.tile_blocks) {
+    const int row0 = tile * ROWS + warp * RPW;
+    float acc[RPW][R];
 #pragma unroll
-    for (int i = 0; i < GV_RPW; ++i)
+    for (int i = 0; i < RPW; ++i)
 #pragma unroll
       for (int r = 0; r < R; ++r) acc[i][r] = 0.f;
 
     if (row0 < a.N) {
       const int64_t grow0 = (int64_t)g * a.N + row0;
-      constexpr int U = 4;  // chunks in flight per row per lane
+      constexpr int U = RPW == 4 ? 2 : 4;  // chunks in flight per row per lane
       for (int cb = c_lo + lane; cb < c_hi; cb += 32 * U) {
-        uint4 wv[U][GV_RPW];
-        float sc[U][GV_RPW];
+        uint4 wv[U][RPW];
+        float sc[U][RPW];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const int c = cb + 32 * u;
 #pragma unroll
-          for (int i = 0; i < GV_RPW; ++i) {
+          for (int i = 0; i < RPW; ++i) {
             const bool ok = row0 + i < a.N && c < c_hi;
             const int64_t gr = row0 + i < a.N ? grow0 + i : grow0;
             if (ok) {
@@ -172,9 +177,9 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
           if (c >= c_hi) break;
           // decode this chunk of every weight row first, then read each activation row's chunk from shared memory once
           // and use it for all of them (the shared-memory reads, not the FMAs, bound many-row launches)
-          float f[GV_RPW][EPC];
+          float f[RPW][EPC];
 #pragma unroll
-          for (int i = 0; i < GV_RPW; ++i) {
+          for (int i = 0; i < RPW; ++i) {
             if (WF == 0) decode16_e4m3_raw(wv[u][i], f[i]);
             else if (WF == 1) decode32_e2m1_raw(wv[u][i], f[i]);
             else {
@@ -186,26 +191,26 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvArgs a) {
 #pragma unroll
           for (int r = 0; r < R; ++r) {
             const float4* xp = reinterpret_cast<const float4*>(xs_sm + r * sm_pad(a.K) + sm_pad(c * EPC));
-            float s[GV_RPW];
+            float s[RPW];
 #pragma unroll
-            for (int i = 0; i < GV_RPW; ++i) s[i] = 0.f;
+            for (int i = 0; i < RPW; ++i) s[i] = 0.f;
 #pragma unroll
             for (int j = 0; j < EPC / 4; ++j) {
               const float4 xv = xp[j];
 #pragma unroll
-              for (int i = 0; i < GV_RPW; ++i) {
+              for (int i = 0; i < RPW; ++i) {
                 s[i] = fmaf(f[i][4 * j], xv.x, s[i]); s[i] = fmaf(f[i][4 * j + 1], xv.y, s[i]);
                 s[i] = fmaf(f[i][4 * j + 2], xv.z, s[i]); s[i] = fmaf(f[i][4 * j + 3], xv.w, s[i]);
               }
             }
 #pragma unroll
-            for (int i = 0; i < GV_RPW; ++i) acc[i][r] = fmaf(s[i], sc[u][i], acc[i][r]);
+            for (int i = 0; i < RPW; ++i) acc[i][r] = fmaf(s[i], sc[u][i], acc[i][r]);
           }
         }
       }
     }
 #pragma unroll
-    for (int i = 0; i < GV_RPW; ++i)
+    for (int i = 0; i < RPW; ++i)
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         float v = warp_sum(acc[i][r]);
@@ -227,7 +232,8 @@ static int launch_gemv(GemvArgs a, cudaStream_t stream) {
   if (a.n >= 4 && smem1 * 4 <= 96 * 1024) R = 4;
   else if (a.n >= 2 && smem1 * 2 <= 96 * 1024) R = 2;
   if (smem1 > 96 * 1024) return (int)cudaErrorInvalidValue;
-  int tiles = (a.N + GV_ROWS - 1) / GV_ROWS;
+  const int rows_per_block = GV_WARPS * gv_rpw(WF, R);
+  int tiles = (a.N + rows_per_block - 1) / rows_per_block;
   const int cap = (148 * 4 + a.groups - 1) / a.groups;  // a few resident blocks per SM; each loops over row tiles
   a.tile_blocks = tiles < cap ? tiles : cap;
   const int passes = (a.n + R - 1) / R;
