@@ -187,7 +187,8 @@ int sfb_push_rows(const void* src, const void* const* dst_ptrs, const void* cons
   a.W = W; a.n16 = bytes / 16; a.epoch_ptr = (const uint32_t*)epoch_ptr; a.epoch_add = epoch_add;
   a.done = (unsigned int*)done;
   int64_t blocks = (a.n16 + 255) / 256;
-  if (blocks > 64) blocks = 64;
+  const int64_t cap = bytes > (1 << 20) ? 148 * 4 : 64;     // megabytes need every SM's stores in flight to fill the links
+  if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return (int)sfb_launch(push_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, a);
 }

@@ -177,6 +177,10 @@ struct UmmaArgs {
   const CUtensorMap* b_maps;  // all-gather -> GEMM: activations sharded along K over the ranks; map r covers k in
   int b_k_per_map;            //   [r * b_k_per_map, (r+1) * b_k_per_map) and may point into rank r's memory
   const uint8_t* sfb_maps[8]; //   scale atoms of each shard (katoms = b_k_per_map / 128 per row block)
+  const uint32_t* gflag[8];   // optional arrival flag per map (null = that shard is already there): the producer warp waits
+  const uint32_t* gepoch_ptr; //   (bounded) for flag >= *gepoch_ptr + gepoch_add before the first load from that map, so the
+  uint32_t gepoch_add;        //   GEMM starts on the shards that have arrived while the others are still in flight
+  uint64_t gwait_ns;
   int force_bulk;             // entry point for bulk shapes: always the staged-epilogue instantiation
   int rs_rows;                // GEMM -> reduce-scatter: token row t goes only to rank t / rs_rows, at row t % rs_rows
   int defer_reduce;           // split-K partials are left in scratch for splitk_reduce_kernel (many-row dense launches)
@@ -341,6 +345,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
+      int gated = -1;
       for (int i = 0; i < w.nks; ++i) {
         const int s = i % UM_STAGES;
         if (i >= pre) {
@@ -349,9 +354,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           tma_load_2d(S.a[s][0], w.ma, (w.ks0 + i) * UM_BK, w.a_row0, &S.full[s]);
         }
         if (BULK && a.b_maps) {
-          // the k-slab lives on the rank that owns this range of the hidden dimension: a plain (non-multicast)
-          // TMA load from that rank's memory, and its scale atoms with a bulk copy
+          // the k-slab belongs to the rank that owns this range of the hidden dimension: a plain (non-multicast) TMA load
+          // from that rank's memory or from the local slot its owner pushed it into, and its scale atoms with a bulk copy
           const int k = (w.ks0 + i) * UM_BK, owner = k / a.b_k_per_map, kl = k - owner * a.b_k_per_map;
+          if (owner != gated && a.gflag[owner]) {
+            // a launch whose status word already holds an error (an earlier CTA ran out of time) does not wait again: the
+            // loads below still read valid local memory, the epilogue writes nothing, and the host sees the status
+            const bool dead = a.status && *reinterpret_cast<volatile int*>(&a.status->code) != 0;
+            if (dead || !wait_flag_ge(a.gflag[owner], *a.gepoch_ptr + a.gepoch_add, a.gwait_ns)) {
+              status_set(a.status, ST_TIMEOUT, 40, owner, (int)(*a.gepoch_ptr + a.gepoch_add));
+              S.fail = 1;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+          gated = owner;
           tma_load_2d(S.b[s], &a.b_maps[owner], kl, w.b_row0, &S.full[s]);
           bulk_load(S.sfb[s], a.sfb_maps[owner] + ((size_t)(w.b_row0 >> 7) * (a.b_k_per_map / UM_BK) + kl / UM_BK) * 512, 512, &S.full[s]);
         } else {
@@ -839,6 +855,23 @@ struct PushSpec {
 };
 static thread_local PushSpec g_push;
 
+// Arrival flags of the next all-gather -> GEMM launch (set by sfb_umma_set_gather, consumed and cleared by the launch).
+struct GatherSpec {
+  const void* flag[8];
+  int n = 0;
+  const void* epoch_ptr = nullptr;
+  uint32_t epoch_add = 0;
+  uint64_t wait_ns = 0;
+};
+static thread_local GatherSpec g_gather;
+
+static void apply_gather(UmmaArgs& a) {
+  for (int i = 0; i < 8; ++i) a.gflag[i] = i < g_gather.n ? (const uint32_t*)g_gather.flag[i] : nullptr;
+  a.gepoch_ptr = (const uint32_t*)g_gather.epoch_ptr; a.gepoch_add = g_gather.epoch_add;
+  a.gwait_ns = g_gather.wait_ns ? g_gather.wait_ns : 1000000000ull;
+  g_gather.n = 0;
+}
+
 static void apply_push(UmmaArgs& a) {
   a.n_peers = g_push.n;
   for (int i = 0; i < g_push.n; ++i) { a.peer_out[i] = (__nv_bfloat16*)g_push.out[i]; a.peer_flag[i] = (uint32_t*)g_push.flag[i]; }
@@ -854,6 +887,7 @@ static int launch_umma(const void* tmapA, const void* tmapA2, const void* tmapB,
   cudaError_t launch_rc = cudaSuccess;
   UmmaArgs a = a_in;
   apply_push(a);
+  apply_gather(a);
 const bool bulk = a.force_bulk || a.tok_tiles > 1 || a.b_maps != nullptr || a.rs_rows > 0;
   if (a.tok_tiles < 1) a.tok_tiles = 1;
 #define SFB_UM(NPV) { launch_rc = bulk ? launch_umma_t<NPV, true>(mA, mA2, mB, a, grid, stream) : launch_umma_t<NPV, false>(mA, mA2, mB, a, grid, stream); }
@@ -870,6 +904,15 @@ int sfb_umma_set_push(const void* const* out_ptrs, const void* const* flag_ptrs,
   if (W < 0 || W > 8) return (int)cudaErrorInvalidValue;
   for (int i = 0; i < W; ++i) { g_push.out[i] = (void*)out_ptrs[i]; g_push.flag[i] = (void*)flag_ptrs[i]; }
   g_push.n = W; g_push.epoch_ptr = epoch_ptr; g_push.epoch_add = epoch_add; g_push.done = done_counter;
+  return 0;
+}
+
+// Arm per-shard arrival flags for the next sfb_umma_bulk call with b_maps: flag_ptrs[r] (null = no wait) must reach
+// *epoch_ptr + epoch_add before the kernel reads map r.
+int sfb_umma_set_gather(const void* const* flag_ptrs, int W, const void* epoch_ptr, uint32_t epoch_add, uint64_t wait_ns) {
+  if (W < 0 || W > 8) return (int)cudaErrorInvalidValue;
+  for (int i = 0; i < W; ++i) g_gather.flag[i] = flag_ptrs[i];
+  g_gather.n = W; g_gather.epoch_ptr = epoch_ptr; g_gather.epoch_add = epoch_add; g_gather.wait_ns = wait_ns;
   return 0;
 }
 

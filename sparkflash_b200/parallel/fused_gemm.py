@@ -150,11 +150,21 @@ class RowParallelLinear(_Base):
 
 
 class ColumnParallelLinear(_Base):
-    """y_r = x @ W_r^T with x [M, K] held as W shards along K, one per rank, in symmetric memory (FP8 + atoms).
-    Weight shard: FP8 codes [N/W, K] with UE8M0 scales per 32x32 block."""
+    """y_r = x @ W_r^T with x [M, K] held as W shards along K, one per rank (FP8 + atoms).
+    Weight shard: FP8 codes [N/W, K] with UE8M0 scales per 32x32 block.
 
-    def __init__(self, heap: SymmHeap, w_q: torch.Tensor, w_sf: torch.Tensor, M: int, heap_offset: int = 0, **kw):
+    ``mode="gather"`` (default): every rank keeps W local slots; ``publish`` quantises this rank's shard into its own slot
+    and pushes it (codes and atoms, one contiguous block) into slot ``rank`` of every peer, then raises its flag there.
+    The GEMM reads local memory only, and its producer warp waits for a shard's flag just before the first load from it,
+    so the math on the shards that are there overlaps the transfers still in flight and every byte crosses NVLink once.
+    ``mode="remote"``: the shards stay where they are and the GEMM's TMA loads read them from the owners' memory (every
+    weight-tile CTA fetches the remote tile again: fine for a few rows, link-bound for thousands)."""
+
+    def __init__(self, heap: SymmHeap, w_q: torch.Tensor, w_sf: torch.Tensor, M: int, heap_offset: int = 0, mode: str = "gather", **kw):
         super().__init__(heap, M, **kw)
+        if mode not in ("gather", "remote"):
+            raise ValueError(f"unknown mode {mode!r}")
+        self.mode = mode
         self.Nl, self.K = w_q.shape
         W = self.world
         self.Kl = self.K // W
@@ -167,21 +177,31 @@ class ColumnParallelLinear(_Base):
         self.Mp = max(self.NP, (M + 127) // 128 * 128)
         self.xq_bytes = self.Mp * self.Kl
         self.atom_bytes = (C.sf_bytes(self.Mp, self.Kl // 32) + 255) // 256 * 256
-        # symmetric layout: [2 parities] (x_q shard | atoms) | flags [2][W] | dummy 16 B | done
+        self.slot_bytes = self.xq_bytes + self.atom_bytes
+        slots = W if mode == "gather" else 1
+        # symmetric layout: [2 parities][slots] (x_q shard | atoms) | flags [2][W] | dummy 16 B | done
         self.off_x = heap_offset
-        self.off_flags = heap_offset + 2 * (self.xq_bytes + self.atom_bytes)
+        self.off_flags = heap_offset + 2 * slots * self.slot_bytes
         self.off_dummy = self.off_flags + 2 * 256
         self.off_done = self.off_dummy + 256
         self.bytes = self.off_done + 256 - heap_offset
         h = heap
-        self.maps, self.sfb_ptrs, self.local_q, self.local_atom = [], [], [], []
+        self.maps, self.sfb_ptrs, self.local_q, self.local_atom, self.slot_off = [], [], [], [], []
         for par in range(2):
-            ms = [tensor_map_at(b + self.off_x + par * (self.xq_bytes + self.atom_bytes), self.Mp, self.Kl, self.NP) for b in h.bases]
+            base_par = self.off_x + par * slots * self.slot_bytes
+            if mode == "gather":      # slot r of THIS rank's memory holds rank r's shard
+                addrs = [h.base + base_par + r * self.slot_bytes for r in range(W)]
+                own = base_par + self.rank * self.slot_bytes
+            else:                     # the one slot of rank r's memory
+                addrs = [b + base_par for b in h.bases]
+                own = base_par
+            ms = [tensor_map_at(a, self.Mp, self.Kl, self.NP) for a in addrs]
             self._keep_maps = getattr(self, "_keep_maps", []) + ms
             self.maps.append(_maps_device(ms))
-            self.sfb_ptrs.append([b + self.off_x + par * (self.xq_bytes + self.atom_bytes) + self.xq_bytes for b in h.bases])
-            self.local_q.append(h.view(self.off_x + par * (self.xq_bytes + self.atom_bytes), (self.Mp, self.Kl), torch.uint8))
-            self.local_atom.append(h.view(self.off_x + par * (self.xq_bytes + self.atom_bytes) + self.xq_bytes, (self.atom_bytes,), torch.uint8))
+            self.sfb_ptrs.append([a + self.xq_bytes for a in addrs])
+            self.slot_off.append(own)
+            self.local_q.append(h.view(own, (self.Mp, self.Kl), torch.uint8))
+            self.local_atom.append(h.view(own + self.xq_bytes, (self.atom_bytes,), torch.uint8))
             self.local_atom[-1].fill_(127)
         tiles = ((self.Nl + 127) // 128) * ((M + self.NP - 1) // self.NP)
         ksteps = self.K // 128
@@ -189,31 +209,48 @@ class ColumnParallelLinear(_Base):
         self.scratch = torch.zeros((tiles * self.splits * 128 * self.NP,), dtype=torch.float32, device="cuda") if self.splits > 1 else None
         self.tickets = torch.zeros((max(tiles, 1),), dtype=torch.int32, device="cuda")
         self.out = torch.empty((M, self.Nl), dtype=torch.bfloat16, device="cuda")
-        self.flag_ptrs = [torch.tensor([b_ + self.off_flags + par * 256 + r * 4 for r in range(W)], dtype=torch.int64, device="cuda")
-                          for par in range(2) for b_ in [h.base]]
+        self.flag_addr = [[h.base + self.off_flags + par * 256 + r * 4 for r in range(W)] for par in range(2)]
+        self.flag_ptrs = [torch.tensor(self.flag_addr[par], dtype=torch.int64, device="cuda") for par in range(2)]
         self._dummy = torch.zeros(16, dtype=torch.uint8, device="cuda")
 
     @staticmethod
-    def heap_bytes(M: int, K: int, W: int) -> int:
+    def heap_bytes(M: int, K: int, W: int, mode: str = "gather") -> int:
         Mp = max(16, (M + 127) // 128 * 128)
-        return 2 * (Mp * (K // W) + (C.sf_bytes(Mp, K // W // 32) + 255) // 256 * 256) + 2 * 256 + 512
+        slots = W if mode == "gather" else 1
+        return 2 * slots * (Mp * (K // W) + (C.sf_bytes(Mp, K // W // 32) + 255) // 256 * 256) + 2 * 256 + 512
 
     def publish(self, x_shard: torch.Tensor) -> None:
-        """x_shard bf16 [M, K/W]: quantise into this rank's symmetric shard and tell every rank it is there."""
+        """x_shard bf16 [M, K/W]: quantise into this rank's slot, (gather mode) push the slot to every peer, and tell every
+        rank it is there."""
         self.step += 1
         par = self.step & 1
         self._bump()
         N.quant_rows(x_shard, self.local_q[par], None, self.local_atom[par], self.M, self.Kl)
         h = self.heap
-        dst = [b + self.off_dummy for b in h.bases]
         flags = [b + self.off_flags + par * 256 + self.rank * 4 for b in h.bases]
-        N._check(_L().sfb_push_rows(N._p(self._dummy), N._ptr_array(dst), N._ptr_array(flags), c_int(self.world), c_int64(16), N._p(self.epoch),
-                                    c_uint32(0), c_void_p(h.base + self.off_done), N._stream()), "push_rows")
+        if self.mode == "gather":
+            # own rank's entry copies the slot onto itself only for W == 1; otherwise the list holds the peers
+            peers = [r for r in range(self.world) if r != self.rank] or [self.rank]
+            dst = [h.bases[r] + self.slot_off[par] for r in peers]
+            src = h.view(self.slot_off[par], (self.slot_bytes,), torch.uint8)
+            N._check(_L().sfb_push_rows(N._p(src), N._ptr_array(dst), N._ptr_array([flags[r] for r in peers]), c_int(len(peers)),
+                                        c_int64(self.slot_bytes), N._p(self.epoch), c_uint32(0), c_void_p(h.base + self.off_done),
+                                        N._stream()), "push_rows")
+        else:
+            dst = [b + self.off_dummy for b in h.bases]
+            N._check(_L().sfb_push_rows(N._p(self._dummy), N._ptr_array(dst), N._ptr_array(flags), c_int(self.world), c_int64(16), N._p(self.epoch),
+                                        c_uint32(0), c_void_p(h.base + self.off_done), N._stream()), "push_rows")
 
     def gemm(self) -> torch.Tensor:
         par = self.step & 1
-        N._check(_L().sfb_wait_flags(N._p(self.flag_ptrs[par]), c_int(self.world), N._p(self.epoch), c_uint32(0), c_uint64(self.wait_ns),
-                                     N._p(self.status), N._stream()), "wait_flags")
+        if self.mode == "gather":
+            # no separate wait: the kernel's producer warp waits for shard r's flag right before it first reads slot r
+            gate = [0 if r == self.rank else self.flag_addr[par][r] for r in range(self.world)]
+            N._check(_L().sfb_umma_set_gather(N._ptr_array(gate), c_int(self.world), N._p(self.epoch), c_uint32(0), c_uint64(self.wait_ns)),
+                     "umma_set_gather")
+        else:
+            N._check(_L().sfb_wait_flags(N._p(self.flag_ptrs[par]), c_int(self.world), N._p(self.epoch), c_uint32(0), c_uint64(self.wait_ns),
+                                         N._p(self.status), N._stream()), "wait_flags")
         N._check(_L().sfb_umma_bulk(c_void_p(self.tmap_a.ptr), None, N._p(self.w_atoms), c_int(self.K // 128), None, c_int(self.Kl // 128),
                                     c_int(self.M), c_int(self.NP), c_int(self.Nl), c_int(self.K), c_int(self.splits), N._p(self.scratch),
                                     N._p(self.tickets), N._p(self.out), None, c_int64(self.Nl), N._p(self.maps[par]), c_int(self.Kl),

@@ -112,10 +112,14 @@ def main() -> None:
                          "frac_of_roofline": max(t_compute, link) / fused})
             del op; heap.close()
         # ---- all-gather -> GEMM ----------------------------------------------------------------------------------
-        heap = SymmHeap(rank, W, ColumnParallelLinear.heap_bytes(M, H, W)).attach()
-        op = ColumnParallelLinear(heap, qc.cuda(), sc, M)
-        fused = timed(lambda: op.forward(x_l), a.iters)
-        op.check()
+        fused_by_mode = {}
+        for mode in ("gather", "remote"):
+            heap = SymmHeap(rank, W, ColumnParallelLinear.heap_bytes(M, H, W, mode)).attach()
+            op = ColumnParallelLinear(heap, qc.cuda(), sc, M, mode=mode)
+            fused_by_mode[mode] = timed(lambda: op.forward(x_l), a.iters)
+            op.check()
+            del op; heap.close()
+        fused = fused_by_mode["gather"]
         gathered = torch.empty(W * M, Kl, dtype=torch.bfloat16, device="cuda")
         yc = torch.empty(M, H // W, dtype=torch.bfloat16, device="cuda")
 
@@ -126,8 +130,8 @@ def main() -> None:
         base = timed(base_ag, a.iters)
         link = M * H * (W - 1) / W / (a.link_gbs * 1e9) * 1e6          # FP8 activations cross once
         rows.append({"op": "allgather_gemm", "M": M, "fused_us": fused, "nccl_cublas_us": base, "roofline_us": max(t_compute, link),
-                     "frac_of_roofline": max(t_compute, link) / fused, "nvlink_reread_factor": max(1, (H // W) // 128)})
-        del op; heap.close()
+                     "frac_of_roofline": max(t_compute, link) / fused, "fused_remote_reads_us": fused_by_mode["remote"],
+                     "remote_reads_nvlink_reread_factor": max(1, (H // W) // 128)})
     if rank == 0:
         for r in rows:
             print(json.dumps({"world": W, "hidden": H, **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()}}))

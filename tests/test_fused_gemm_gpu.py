@@ -55,18 +55,19 @@ def test_row_parallel_gemm_then_reduce(M, mode):
             assert (out - wn).abs().max() < 0.03 * wn.abs().max() + 0.02
 
 
+@pytest.mark.parametrize("mode", ["gather", "remote"])
 @pytest.mark.parametrize("M", [1, 16, 128, 384])
-def test_all_gather_then_column_parallel_gemm(M):
+def test_all_gather_then_column_parallel_gemm(M, mode):
     from sparkflash_b200.parallel.fused_gemm import ColumnParallelLinear
     from sparkflash_b200.parallel.symm import SymmHeap
     W, N, K = 2, 512, 1024
     Nl, Kl = N // W, K // W
-    heaps = SymmHeap.local_group(W, ColumnParallelLinear.heap_bytes(M, K, W))
+    heaps = SymmHeap.local_group(W, ColumnParallelLinear.heap_bytes(M, K, W, mode))
     g = torch.Generator().manual_seed(1)
     ops, wds = [], []
     for r in range(W):
         q, sf, wd = _weights(Nl, K, 20 + r)
-        ops.append(ColumnParallelLinear(heaps[r], q.cuda(), sf, M, wait_ns=200_000_000))
+        ops.append(ColumnParallelLinear(heaps[r], q.cuda(), sf, M, mode=mode, wait_ns=200_000_000))
         wds.append(wd)
     for step in range(3):
         x = torch.randn(M, K, generator=g).to(torch.bfloat16)
@@ -79,6 +80,23 @@ def test_all_gather_then_column_parallel_gemm(M):
             ops[r].check()
             want = xr @ wds[r].t()
             assert (outs[r] - want).abs().max() < 0.02 * want.abs().max() + 0.01, (M, r, step)
+
+
+def test_a_gather_gemm_whose_peer_shard_never_arrives_times_out_with_a_status():
+    """The all-gather -> GEMM kernel waits for a shard inside its producer warp; the wait is bounded, later CTAs do not wait
+    again, nothing is written, and the context stays usable."""
+    from sparkflash_b200.parallel.fused_gemm import ColumnParallelLinear
+    from sparkflash_b200.parallel.symm import SymmHeap
+    W, N, K, M = 2, 512, 1024, 16
+    heaps = SymmHeap.local_group(W, ColumnParallelLinear.heap_bytes(M, K, W))
+    q, sf, _ = _weights(N // W, K, 5)
+    op = ColumnParallelLinear(heaps[0], q.cuda(), sf, M, wait_ns=50_000_000)           # 50 ms limit
+    op.publish(torch.randn(M, K // W).to(torch.bfloat16).cuda())                       # rank 1 never publishes
+    op.gemm()
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="device status"):
+        op.check()
+    assert torch.zeros(4, device="cuda").sum().item() == 0
 
 
 def test_a_consumer_whose_producer_never_arrives_times_out_with_a_status():
