@@ -97,31 +97,40 @@ __global__ void __launch_bounds__(128) fold_slots_kernel(FoldArgs a) {
   float vals[PASS][8];
   float ss = 0.f;
 #pragma unroll
+  for (int p = 0; p < PASS; ++p)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) vals[p][j] = 0.f;
+  // one round trip per source instead of one per (source, pass): all of a source's 16-byte loads of this row are issued
+  // before the first add.  Each element still adds slot 0, slot 1, ..., then the residual: same sums as before
+  for (int r = 0; r <= a.W; ++r) {
+    const __nv_bfloat16* src = r < a.W ? a.slot[r] + (int64_t)row * a.stride : (a.residual ? a.residual + (int64_t)row * a.d : nullptr);
+    if (!src) break;
+    uint4 u[PASS];
+#pragma unroll
+    for (int p = 0; p < PASS; ++p) {
+      const int c = (p * 128 + threadIdx.x) * 8;
+      u[p] = c < a.d ? *reinterpret_cast<const uint4*>(src + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int p = 0; p < PASS; ++p) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[p]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); vals[p][2 * j] += f.x; vals[p][2 * j + 1] += f.y; }
+    }
+  }
+#pragma unroll
   for (int p = 0; p < PASS; ++p) {
     const int c = (p * 128 + threadIdx.x) * 8;
     if (c >= a.d) break;
-    float s8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int r = 0; r < a.W; ++r) {      // rank order
-      const uint4 u = *reinterpret_cast<const uint4*>(a.slot[r] + (int64_t)row * a.stride + c);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); s8[2 * j] += f.x; s8[2 * j + 1] += f.y; }
-    }
-    if (a.residual) {
-      const uint4 u = *reinterpret_cast<const uint4*>(a.residual + (int64_t)row * a.d + c);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); s8[2 * j] += f.x; s8[2 * j + 1] += f.y; }
-    }
     if (a.out_sum) {
       uint4 o;
       __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(s8[2 * j], s8[2 * j + 1]);
+      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(vals[p][2 * j], vals[p][2 * j + 1]);
       *reinterpret_cast<uint4*>(a.out_sum + (int64_t)row * a.d + c) = o;
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { vals[p][j] = s8[j]; ss += s8[j] * s8[j]; }
+    for (int j = 0; j < 8; ++j) ss += vals[p][j] * vals[p][j];
   }
   float scale = 1.f;
   if (a.norm_w) scale = rsqrtf(block_sum(ss, red) / (float)a.d + a.eps);
