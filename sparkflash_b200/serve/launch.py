@@ -72,7 +72,10 @@ def run(args) -> int:
     else:
         import torch.distributed as dist
         if world > 1:
-            dist.init_process_group("nccl")
+            import torch
+            local = int(os.environ.get("LOCAL_RANK", rank))
+            torch.cuda.set_device(local)          # before the first collective: every rank on its own GPU
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
             # every rank must start from the same effective settings
             words = [None] * world
             dist.all_gather_object(words, settings.digest())
