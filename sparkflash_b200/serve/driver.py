@@ -248,6 +248,12 @@ class DeviceDriver(InferenceEngine):
 
     def _loop(self) -> None:
         try:
+            # CUDA's current device is per thread and starts at device 0: this thread must select the engine's GPU before
+            # its first launch, or rank r > 0 would launch on GPU 0 with pointers into GPU r's memory
+            dev = getattr(self.engine, "dev", None)
+            if dev is not None and getattr(dev, "type", None) == "cuda":
+                import torch
+                torch.cuda.set_device(dev)
             while not self._stop:
                 inputs = self._take_inputs() if self.channel.rank == 0 else None
                 # followers block here for rank 0's message; rank 0 sends one per tick

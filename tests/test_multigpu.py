@@ -136,3 +136,8 @@ def test_two_rank_server_answers_a_chat_request(tmp_path):
         if proc.poll() is None:
             os.killpg(proc.pid, signal.SIGKILL)
             proc.wait()
+        log.close()
+        keep = os.path.join(repo, "gpurun_out")          # the ranks' boot lines and any traceback, for a failed run
+        os.makedirs(keep, exist_ok=True)
+        with open(os.path.join(keep, "serve_two_ranks.log"), "w") as f:
+            f.write(open(tmp_path / "serve.log").read()[-20000:])
