@@ -124,6 +124,7 @@ def main() -> None:
     ap.add_argument("--arm", default=os.environ.get("SFB_ARM", "tc"), choices=["tc", "cuda"])
     ap.add_argument("--long-context", default="", help="comma-separated cached context lengths (e.g. 131072,1048576): decode tok/s with the KV "
                     "caches of lane 0 filled with random entries up to that position")
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="rows per prompt chunk (default 128 on one GPU, 64 with fused collectives)")
     ap.add_argument("--mtp", action="store_true", help="also build the DSpark draft stages and report the per-forward latency of a draft block")
     ap.add_argument("--moe-mode", default=os.environ.get("SFB_MOE_MODE", "tp"), choices=["tp", "ep"],
                     help="tp: every expert sliced by width over the ranks; ep: whole experts per rank")
@@ -160,7 +161,10 @@ def main() -> None:
     S = args.streams
     long_ctx = [int(x) for x in args.long_context.split(",") if x]
     max_ctx = max([args.prompt + args.steps * 2 + args.warmup * 2 + 1024] + [c + args.steps + args.warmup + 64 for c in long_ctx])
-    eng = E.Engine(weights, max_lanes=max(S, 1), max_context=max_ctx, max_rows=64, comm=comm, arm=args.arm,
+    # prompt chunk: 128 rows on one GPU (one read of the routed experts serves twice the rows); the fused collectives take
+    # steps of up to 64 rows
+    chunk = args.prefill_chunk or (128 if world == 1 else 64)
+    eng = E.Engine(weights, max_lanes=max(S, 1), max_context=max_ctx, max_rows=max(64, chunk), comm=comm, arm=args.arm,
                    synthetic_scales=True, drafter=args.mtp)
     if comm is not None:
         comm.attach(eng)
@@ -183,14 +187,14 @@ def main() -> None:
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     # warm the 64-row graph once on a scratch lane so capture cost is outside the timing
-    eng.step(prompt[:64], [S - 1] * 64, list(range(64)))
-    eng.step(prompt[:64], [S - 1] * 64, list(range(64)), head=False)
+    eng.step(prompt[:chunk], [S - 1] * chunk, list(range(chunk)))
+    eng.step(prompt[:chunk], [S - 1] * chunk, list(range(chunk)), head=False)
     barrier()
     ev0.record()
     pos = 0
     nxt = 0
     while pos < len(prompt):
-        c = prompt[pos:pos + 64]
+        c = prompt[pos:pos + chunk]
         last = pos + len(c) >= len(prompt)          # only the chunk that reaches the prompt's end is sampled
         r = eng.step(c, [0] * len(c), list(range(pos, pos + len(c))), head=last)
         nxt = int(r[len(c) - 1])
@@ -258,7 +262,7 @@ def main() -> None:
                   "decode_16streams_ms_per_step": ms16 / args.steps,
                   "vs_baseline_16streams": S * args.steps / (ms16 / 1e3) / BASELINE_16STREAM_TOK_S,
                   "prefill_tok_s": prefill_tok_s, "prefill_prompt_tokens": len(prompt),
-                  "prefill_note": "rows steps of 64: tcgen05 projections and grouped experts, CUDA-core attention; chunks before the last skip the head",
+                  "prefill_chunk_rows": chunk, "prefill_note": "rows steps: tcgen05 projections and grouped experts, CUDA-core attention; chunks before the last skip the head",
                   "vs_baseline_prefill": prefill_tok_s / BASELINE_PREFILL_TOK_S}
     for ctx in long_ctx:
         # decode against a long cached context: the caches of lane 0 are filled with random codes (a real prefill of a million

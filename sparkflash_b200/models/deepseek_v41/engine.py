@@ -206,6 +206,7 @@ class Engine:
         self.io = StepIO(pin(i32), pin(i32), pin(i32), pin(f32), pin(torch.int64), pin(i32))
         self.arm = arm
         self.tcl = None
+        self.tcb = None
         if arm == "tc":
             from . import tc as TC
             self.tcl = TC.attach(weights, synthetic=synthetic_scales)
@@ -436,35 +437,47 @@ class Engine:
             N.select_topk(self.scores, self.row_pos, ratio, 1, max_len, cfg.index_topk, self.sel, self.sel_cnt, n); self._k()
             self._dbg(f"L{l}.iscore", self.scores, n)
         has_c = ratio > 0
-        tc_wo_a = T is not None and T.wo_a is not None and 2 * n <= 128
-        N.attn_rows(self.qfull, self.qfull.stride(0), invf, self.row_lane, self.row_pos, kv.win_q[l], kv.win_s[l],
-                    kv.ckv_q[owner] if has_c else None, kv.ckv_s[owner] if has_c else None,
-                    self.sel if has_c else None, self.sel_cnt if has_c else None, cfg.index_topk, L.sink,
-                    self.attn_out, n, self.hl, hd, rd, cfg.window, kv.ring, hd ** -0.5,
-                    out_q=self.tcb.ao_q if tc_wo_a else None, out_atom=self.tcb.ao_atom if tc_wo_a else None,
-                    win_lo=win[0] if win else None, win_hi=win[1] if win else None); self._k()
-        ol, gin = cfg.o_lora_rank, cfg.group_in
+        tc_wo_a = T is not None and T.wo_a is not None
         tc_wo_b = T is not None and T.wo_b is not None
-        fused_oa_q = False
-        if tc_wo_a:
-            # bf16 activations through the FP8 tensor path as a two-term split (hi + lo, written by the
-            # attention kernel); the epilogue re-quantises its output for wo_b
-            tcb = self.tcb
-            fused_oa_q = tc_wo_b
-            self._tc_dense(T.wo_a, tcb.ao_q, 2 * self.max_rows, tcb.ao_atom, n, ol, gin, self.oa, groups=self.gl, pair=n,
-                           out_q=tcb.oa_q if fused_oa_q else None, out_q_atom=tcb.oa_atom if fused_oa_q else None)
-        else:
-            N.gemv(N.WF_FP8, L.wo_a, L.wo_a_sf, gin, ol, gin, n, groups=self.gl, xb=self.attn_out, out_b=self.oa); self._k()
+        ol, gin = cfg.o_lora_rank, cfg.group_in
         self._pushed = False
-        if tc_wo_b:
+        # The two-term (hi | lo) copy of the attention output fills a 128-row activation tile with 64 rows, so steps of more than
+        # 64 rows run the attention kernel and the two output projections once per block of 64 rows, each block with its own
+        # rows of the staging buffers and its own scale-atom block; everything before (and the expert pass after) sees all rows.
+        blocks = [(0, n)] if (n <= 64 or not tc_wo_a) else [(r0, min(64, n - r0)) for r0 in range(0, n, 64)]
+        if len(blocks) > 1 and self._fused():
+            raise ValueError("steps of more than 64 rows are not wired to the fused collectives yet")
+        for bj, (r0, m) in enumerate(blocks):
             tcb = self.tcb
-            if not fused_oa_q:
-                N.quant_rows(self.oa, tcb.oa_q, None, tcb.oa_atom, n, self.gl * ol); self._k()
-            self._pushed = self._arm_push(0, sub)
-            self._tc_dense(T.wo_b, tcb.oa_q, self.max_rows, tcb.oa_atom, n, d, self.gl * ol, self.y_attn)
-        else:
-            N.gemv(N.WF_FP8, L.wo_b, L.wo_b_sf, self.gl * ol, d, self.gl * ol, n, xb=self.oa, x_quant=True,
-                   out_b=self.y_attn); self._k()
+            ao_q = ao_atom = oa_q = oa_atom = None
+            if tc_wo_a:
+                ao_q, ao_atom = tcb.ao_q[2 * r0:], tcb.ao_atom[bj * tcb.ao_atom_block:]
+            if tc_wo_b:
+                oa_q, oa_atom = tcb.oa_q[r0:], tcb.oa_atom[bj * tcb.oa_atom_block:]
+            N.attn_rows(self.qfull[r0:], self.qfull.stride(0), invf[r0:], self.row_lane[r0:], self.row_pos[r0:], kv.win_q[l], kv.win_s[l],
+                        kv.ckv_q[owner] if has_c else None, kv.ckv_s[owner] if has_c else None,
+                        self.sel[r0:] if has_c else None, self.sel_cnt[r0:] if has_c else None, cfg.index_topk, L.sink,
+                        self.attn_out[r0:], m, self.hl, hd, rd, cfg.window, kv.ring, hd ** -0.5,
+                        out_q=ao_q, out_atom=ao_atom,
+                        win_lo=win[0][r0:] if win else None, win_hi=win[1][r0:] if win else None); self._k()
+            fused_oa_q = False
+            if tc_wo_a:
+                # bf16 activations through the FP8 tensor path as a two-term split (hi + lo, written by the
+                # attention kernel); the epilogue re-quantises its output for wo_b
+                fused_oa_q = tc_wo_b
+                self._tc_dense(T.wo_a, ao_q, min(128, 2 * (self.max_rows - r0)), ao_atom, m, ol, gin, self.oa[r0:], groups=self.gl, pair=m,
+                               out_q=oa_q if fused_oa_q else None, out_q_atom=oa_atom if fused_oa_q else None)
+            else:
+                N.gemv(N.WF_FP8, L.wo_a, L.wo_a_sf, gin, ol, gin, m, groups=self.gl, xb=self.attn_out[r0:], out_b=self.oa[r0:]); self._k()
+            if tc_wo_b:
+                if not fused_oa_q:
+                    N.quant_rows(self.oa[r0:], oa_q, None, oa_atom, m, self.gl * ol); self._k()
+                if len(blocks) == 1:
+                    self._pushed = self._arm_push(0, sub)
+                self._tc_dense(T.wo_b, oa_q, min(128, self.max_rows - r0), oa_atom, m, d, self.gl * ol, self.y_attn[r0:])
+            else:
+                N.gemv(N.WF_FP8, L.wo_b, L.wo_b_sf, self.gl * ol, d, self.gl * ol, m, xb=self.oa[r0:], x_quant=True,
+                       out_b=self.y_attn[r0:]); self._k()
 
     GROUP_MIN_ROWS = 4      # from this many rows on, the step's (token, expert) pairs are sorted by expert
 

@@ -96,10 +96,13 @@ class TcBuffers:
         self.qr_atom = torch.full((C.sf_bytes(128, q // 32),), 127, **u8)
         ao_k = eng.hl * cfg.head_dim
         self.ao_q = torch.zeros((2 * R, ao_k), **u8)                                  # attention out, hi | lo
-        self.ao_atom = torch.full((C.sf_bytes(128, ao_k // 32),), 127, **u8)
+        nblk = max(1, (R + 63) // 64)        # one 128-row scale-atom block per 64 rows of a step (hi | lo fill a block)
+        self.ao_atom_block = C.sf_bytes(128, ao_k // 32)
+        self.ao_atom = torch.full((nblk * self.ao_atom_block,), 127, **u8)
         oa_k = eng.gl * cfg.o_lora_rank
         self.oa_q = torch.zeros((R, oa_k), **u8)
-        self.oa_atom = torch.full((C.sf_bytes(128, max(1, oa_k // 32)),), 127, **u8)
+        self.oa_atom_block = C.sf_bytes(128, max(1, oa_k // 32))
+        self.oa_atom = torch.full((nblk * self.oa_atom_block,), 127, **u8)
         self.act_sf = torch.full((R * k, C.sf_bytes(1, max(1, eng.il // 32))), 127, **u8)
         tiles_down = R * ((d + 127) // 128)
         n_floats = max(tiles_down * k * 128 * 16, 64 * 16 * 128 * 128)

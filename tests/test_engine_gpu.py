@@ -455,3 +455,27 @@ def test_grouped_moe_gives_the_bits_of_the_ungrouped_kernels(tiny):
         e.check_status()
         outs.append(e.logits[:16].clone())
     assert torch.equal(outs[0], outs[1])
+
+
+def test_steps_of_more_than_64_rows_give_the_bits_of_small_steps(tiny):
+    """A 128-row step runs its attention and output projections per block of 64 rows (the two-term activation copy fills a
+    128-row tile with 64 rows) and everything else over all rows at once: same logits, bit for bit, as 16-row steps."""
+    from sparkflash_b200.models.deepseek_v41 import engine as E
+    cfg, ck, w, orc, dw = tiny
+    prompt = _prompt(cfg, 200, seed=11)
+    small = E.Engine(dw, max_lanes=1, max_context=256, max_rows=16, use_graphs=False, arm="tc", keep_logits=True)
+    big = E.Engine(dw, max_lanes=1, max_context=256, max_rows=128, use_graphs=True, arm="tc", keep_logits=True)
+    want, got = [], []
+    for pos in range(0, 200, 16):
+        c = prompt[pos:pos + 16]
+        small.step(c, [0] * len(c), list(range(pos, pos + len(c))))
+        want += [small.logits[i].clone() for i in range(len(c))]
+    pos = 0
+    for c_len in (128, 72):
+        c = prompt[pos:pos + c_len]
+        big.step(c, [0] * c_len, list(range(pos, pos + c_len)))
+        got += [big.logits[i].clone() for i in range(c_len)]
+        pos += c_len
+    small.check_status(); big.check_status()
+    for i, (x, y) in enumerate(zip(want, got)):
+        assert torch.equal(x, y), f"row {i} differs"
