@@ -594,11 +594,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
 
 // ---- MoE gate/up: two weight tiles (w1, w3) against one token, clamp-SwiGLU x route weight, FP8 re-quant ------
 // grid: x = 128-column tile of the intermediate width, y = slot (top_k routed + shared), z = token
-__global__ void __launch_bounds__(UM_THREADS, 1)
+// UM_STAGES = 6 fills one SM's shared memory with a single CTA (few CTAs: decode); 3 lets two CTAs share an SM, so that one's
+// prologue and epilogue hide behind the other's weight stream when a launch has many waves (grouped many-row steps)
+template <int UM_STAGES>
+__global__ void __launch_bounds__(UM_THREADS, UM_STAGES <= 3 ? 2 : 1)
 umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
                    const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
   constexpr int NP = 16;
-  constexpr int UM_STAGES = UM_STAGES_GATEUP;
   extern __shared__ uint8_t smem_raw[];
   using Smem = UmmaSmem<NP, 2, UM_STAGES>;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -995,12 +997,12 @@ int sfb_umma_gate_up(const void* tmapA, const void* tmapA2, const void* tmapB, c
   const size_t smem = sizeof(UmmaSmem<16, 2, UM_STAGES_GATEUP>) + 1024;
   static bool done = false;
   if (!done) {
-    cudaFuncSetAttribute(umma_gateup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(umma_gateup_kernel<UM_STAGES_GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     done = true;
   }
   const CUtensorMap* mA = (const CUtensorMap*)tmapA;
   const CUtensorMap* mA2 = (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA);
-  return (int)sfb_launch(umma_gateup_kernel, dim3(inter / 128, slots, n_tok), dim3(UM_THREADS), smem, stream, *mA, *mA2,
+  return (int)sfb_launch(umma_gateup_kernel<UM_STAGES_GATEUP>, dim3(inter / 128, slots, n_tok), dim3(UM_THREADS), smem, stream, *mA, *mA2,
                          *(const CUtensorMap*)tmapB, a);
 }
 
@@ -1034,12 +1036,19 @@ int sfb_umma_gate_up_grouped(const void* tmapA, const void* tmapA2, const void* 
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (d / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
   a.a_fp4 = 1; a.top_k = 0; a.slots = 1; a.inter = inter; a.d = d; a.act_q = (uint8_t*)act_q; a.act_sf = (uint8_t*)act_sf; a.limit = limit;
   a.seg_expert = seg_expert; a.seg_count = seg_count; a.seg_weight = seg_weight; a.status = (Status*)status;
-  const size_t smem = sizeof(UmmaSmem<16, 2, UM_STAGES_GATEUP>) + 1024;
-  static bool done = false;
-  if (!done) { cudaFuncSetAttribute(umma_gateup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
   const CUtensorMap* mA = (const CUtensorMap*)tmapA;
   const CUtensorMap* mA2 = (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA);
-  return (int)sfb_launch(umma_gateup_kernel, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem, stream, *mA, *mA2, *(const CUtensorMap*)tmapB, a);
+  if ((inter / 128) * segments > 2 * 148) {      // several waves: two half-depth CTAs per SM
+    const size_t smem3 = sizeof(UmmaSmem<16, 2, 3>) + 1024;
+    static bool done3 = false;
+    if (!done3) { cudaFuncSetAttribute(umma_gateup_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3); done3 = true; }
+    return (int)sfb_launch(umma_gateup_kernel<3>, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem3, stream, *mA, *mA2,
+                           *(const CUtensorMap*)tmapB, a);
+  }
+  const size_t smem = sizeof(UmmaSmem<16, 2, UM_STAGES_GATEUP>) + 1024;
+  static bool done = false;
+  if (!done) { cudaFuncSetAttribute(umma_gateup_kernel<UM_STAGES_GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+  return (int)sfb_launch(umma_gateup_kernel<UM_STAGES_GATEUP>, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem, stream, *mA, *mA2, *(const CUtensorMap*)tmapB, a);
 }
 
 // out_f [segments*16, d] fp32: one row per pair slot (the caller sums a token's pairs in slot order)

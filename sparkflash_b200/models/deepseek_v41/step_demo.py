@@ -26,7 +26,7 @@ def main() -> None:
     cfg = reduced_config(args.experts, args.layers)
     w = P.prepare_synthetic(cfg, 0, 1)
     rows = args.rows
-    eng = E.Engine(w, max_lanes=max(2, rows if args.decode else 2), max_context=2048, max_rows=64, arm="tc",
+    eng = E.Engine(w, max_lanes=max(2, rows if args.decode else 2), max_context=2048, max_rows=max(64, rows), arm="tc",
                    synthetic_scales=True, use_graphs=False)
     prompt = torch.randint(0, cfg.vocab_size, (2048,)).tolist()
     if args.decode:
