@@ -935,6 +935,9 @@ int sfb_umma_dense(const void* tmapA, const void* tmapB, const void* sfa, int ka
   const int tiles = (N + 127) / 128;
   // many rows and many splits: one CTA per tile adding every split is the slow part, so the add runs as its own grid
   a.defer_reduce = (splits > 1 && NP >= 32 && g_push.n == 0) ? 1 : 0;
+  // 64+ token rows: the staged epilogue (tile -> shared memory -> one 256-byte bulk store per token row) instead of one
+  // 2-byte store per element; the values written are the same
+  if (NP >= 64 && groups == 1 && out_b && !out_f && N % 128 == 0) a.force_bulk = 1;
   const int rc = launch_umma(tmapA, nullptr, tmapB, a, dim3(tiles, splits, groups), NP, stream);
   if (rc != 0 || !a.defer_reduce) return rc;
   SplitReduceArgs r{};
