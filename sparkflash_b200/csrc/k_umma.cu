@@ -230,13 +230,15 @@ struct UmmaWork {
   int out_row0, n_valid, col0, col_limit;
 };
 
-template <int NP, bool BULK>
-__global__ void __launch_bounds__(UM_THREADS, 1)
+// STO > 0 overrides the pipeline depth (and asks for three CTAs per SM): launches of many short-K CTAs, where a CTA's
+// prologue and epilogue are as long as its weight stream and only more resident CTAs keep the stream busy
+template <int NP, bool BULK, int STO = 0>
+__global__ void __launch_bounds__(UM_THREADS, STO ? 3 : 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
                  const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   // bulk tiles of 128 tokens run two CTAs per SM (3 stages = 99 KiB each): one CTA's epilogue hides behind the other's mainloop
-  constexpr int UM_STAGES = NP <= 32 ? UM_STAGES_DENSE : ((BULK && NP == 128) ? 3 : UM_STAGES_WIDE);
+  constexpr int UM_STAGES = STO ? STO : (NP <= 32 ? UM_STAGES_DENSE : ((BULK && NP == 128) ? 3 : UM_STAGES_WIDE));
   using Smem = UmmaSmem<NP, 1, UM_STAGES>;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -766,16 +768,16 @@ static EncodeTiledFn get_encode() {
 
 using namespace sfb;
 
-template <int NPV, bool BULK>
+template <int NPV, bool BULK, int STO = 0>
 static cudaError_t launch_umma_t(const CUtensorMap* mA, const CUtensorMap* mA2, const CUtensorMap* mB, const UmmaArgs& a, dim3 grid,
                                  cudaStream_t stream) {
-  const size_t smem = sizeof(UmmaSmem<NPV, 1, (NPV <= 32 ? UM_STAGES_DENSE : ((BULK && NPV == 128) ? 3 : UM_STAGES_WIDE))>) + 1024;
+  const size_t smem = sizeof(UmmaSmem<NPV, 1, (STO ? STO : (NPV <= 32 ? UM_STAGES_DENSE : ((BULK && NPV == 128) ? 3 : UM_STAGES_WIDE)))>) + 1024;
   static bool done = false;
   if (!done) {
-    cudaFuncSetAttribute(umma_gemm_kernel<NPV, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(umma_gemm_kernel<NPV, BULK, STO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     done = true;
   }
-  return sfb_launch(umma_gemm_kernel<NPV, BULK>, grid, dim3(UM_THREADS), smem, stream, *mA, *mA2, *mB, a);
+  return sfb_launch(umma_gemm_kernel<NPV, BULK, STO>, grid, dim3(UM_THREADS), smem, stream, *mA, *mA2, *mB, a);
 }
 
 extern "C" {
@@ -1063,6 +1065,12 @@ int sfb_umma_down_grouped(const void* tmapA, const void* tmapA2, const void* tma
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (inter / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
   a.a_fp4 = 1; a.mode = UM_DOWN_GROUPED; a.inter = inter; a.d = d; a.out_f = out_f; a.out_stride = d; a.seg_expert = seg_expert;
   a.seg_count = seg_count; a.status = (Status*)status; a.splits = 1;
+  if ((d / 128) * segments > 4 * 148) {      // many waves of 16-k-step CTAs: three 3-stage CTAs per SM
+    apply_push(a); apply_gather(a);
+    a.tok_tiles = 1;
+    return (int)launch_umma_t<16, false, 3>((const CUtensorMap*)tmapA, (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA),
+                                            (const CUtensorMap*)tmapB, a, dim3(d / 128, segments, 1), stream);
+  }
   return launch_umma(tmapA, tmapA2, tmapB, a, dim3(d / 128, segments, 1), 16, stream);
 }
 
