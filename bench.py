@@ -124,7 +124,7 @@ def main() -> None:
     ap.add_argument("--arm", default=os.environ.get("SFB_ARM", "tc"), choices=["tc", "cuda"])
     ap.add_argument("--long-context", default="", help="comma-separated cached context lengths (e.g. 131072,1048576): decode tok/s with the KV "
                     "caches of lane 0 filled with random entries up to that position")
-    ap.add_argument("--prefill-chunk", type=int, default=0, help="rows per prompt chunk (default 128 on one GPU, 64 with fused collectives)")
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="rows per prompt chunk (default 128)")
     ap.add_argument("--mtp", action="store_true", help="also build the DSpark draft stages and report the per-forward latency of a draft block")
     ap.add_argument("--moe-mode", default=os.environ.get("SFB_MOE_MODE", "tp"), choices=["tp", "ep"],
                     help="tp: every expert sliced by width over the ranks; ep: whole experts per rank")
@@ -161,9 +161,8 @@ def main() -> None:
     S = args.streams
     long_ctx = [int(x) for x in args.long_context.split(",") if x]
     max_ctx = max([args.prompt + args.steps * 2 + args.warmup * 2 + 1024] + [c + args.steps + args.warmup + 64 for c in long_ctx])
-    # prompt chunk: 128 rows on one GPU (one read of the routed experts serves twice the rows); the fused collectives take
-    # steps of up to 64 rows
-    chunk = args.prefill_chunk or (128 if world == 1 else 64)
+    # prompt chunk: 128 rows (one read of the routed experts serves twice the rows of a 64-row step)
+    chunk = args.prefill_chunk or 128
     eng = E.Engine(weights, max_lanes=max(S, 1), max_context=max_ctx, max_rows=max(64, chunk), comm=comm, arm=args.arm,
                    synthetic_scales=True, drafter=args.mtp)
     if comm is not None:

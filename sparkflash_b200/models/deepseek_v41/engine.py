@@ -445,8 +445,8 @@ class Engine:
         # 64 rows run the attention kernel and the two output projections once per block of 64 rows, each block with its own
         # rows of the staging buffers and its own scale-atom block; everything before (and the expert pass after) sees all rows.
         blocks = [(0, n)] if (n <= 64 or not tc_wo_a) else [(r0, min(64, n - r0)) for r0 in range(0, n, 64)]
-        if len(blocks) > 1 and self._fused():
-            raise ValueError("steps of more than 64 rows are not wired to the fused collectives yet")
+        # (with the fused collectives, a single block lets the last projection push its output from its epilogue; several
+        # blocks leave that to the generic push kernel after the last block, which raises the arrival flag once)
         for bj, (r0, m) in enumerate(blocks):
             tcb = self.tcb
             ao_q = ao_atom = oa_q = oa_atom = None

@@ -479,3 +479,59 @@ def test_steps_of_more_than_64_rows_give_the_bits_of_small_steps(tiny):
     small.check_status(); big.check_status()
     for i, (x, y) in enumerate(zip(want, got)):
         assert torch.equal(x, y), f"row {i} differs"
+
+
+def test_virtual_tensor_parallel_ranks_take_a_128_row_step(tiny):
+    """Two lockstep tensor-parallel ranks on the tensor-core arm: a 128-row prompt step (two 64-row blocks, partial outputs
+    exchanged by the generic push after the blocks) leaves the same caches as sixteen-row steps - the next decode rows sample
+    the same tokens on both ranks and in both runs."""
+    from sparkflash_b200.models.deepseek_v41 import engine as E, prepare as P
+    from sparkflash_b200.parallel.fused import FusedComm
+    cfg, ck, w, orc, dw = tiny
+    W = 2
+    prompt = _prompt(cfg, 128, seed=13)
+
+    def run(max_rows, chunks):
+        comms = FusedComm.local_group(W, max_rows, cfg.hidden_size)
+        engs = []
+        for r in range(W):
+            e = E.Engine(P.prepare_from_checkpoint(ck, cfg, r, W), max_lanes=1, max_context=256, max_rows=max_rows,
+                         comm=comms[r], use_graphs=False, arm="tc")
+            comms[r].attach_local(e)
+            engs.append(e)
+
+        def step(tokens, positions):
+            n = len(tokens)
+            for e in engs:
+                e.tokens[:n] = torch.tensor(tokens, dtype=torch.int32, device=e.dev)
+                e.row_lane[:n] = 0
+                e.row_pos[:n] = torch.tensor(positions, dtype=torch.int32, device=e.dev)
+                e.temp[:n] = 0.0; e.seed[:n] = 0
+            gens = [e._forward_gen(n, 1024) for e in engs]
+            live = True
+            while live:
+                live = False
+                for g in gens:
+                    try:
+                        next(g); live = True
+                    except StopIteration:
+                        pass
+            torch.cuda.synchronize()
+            for e in engs:
+                e.check_status()
+            outs = [e.tokens_out[:n].tolist() for e in engs]
+            assert outs[0] == outs[1]
+            return outs[0]
+        pos, last = 0, None
+        for c in chunks:
+            last = step(prompt[pos:pos + c], list(range(pos, pos + c)))
+            pos += c
+        toks, tok = [], last[-1]
+        for i in range(6):
+            tok = step([tok], [pos + i])[0]
+            toks.append(tok)
+        return last, toks
+
+    big_last, big_toks = run(128, [128])
+    small_last, small_toks = run(16, [16] * 8)
+    assert big_last[-16:] == small_last and big_toks == small_toks
