@@ -199,7 +199,7 @@ class ParallelConfig:
 class EngineConfig:
     max_lanes: int = 32
     queue_depth: int = 64
-    max_rows: int = 64            # verify rows per decode step (R_MAX)
+    max_rows: int = 128           # rows per step: prompt chunks and verify rows (64-row blocks inside the step above 64)
     prefill_chunk: int = 4096
     prefill_chunk_busy: int = 2048
     prefix_reuse_min_rows: int = 256
