@@ -128,9 +128,10 @@ bool parse_entry_fields(J& j, Entry& en, bool st_style) {
     } else if (k == "data_offsets" && st_style) {
       if (!j.eat('[')) return false;
       int64_t a = j.num(); if (!j.eat(',')) return false; int64_t b = j.num(); if (!j.eat(']')) return false;
-      en.offset = a; en.nbytes = b - a;
-    } else if (k == "offset") en.offset = j.num();
-    else if (k == "nbytes") en.nbytes = j.num();
+      if (a < 0 || b < a) return false;            // reversed or negative range: never wraps into a huge length
+      en.offset = (uint64_t)a; en.nbytes = (uint64_t)(b - a);
+    } else if (k == "offset") { int64_t v = j.num(); if (v < 0) return false; en.offset = (uint64_t)v; }
+    else if (k == "nbytes") { int64_t v = j.num(); if (v < 0) return false; en.nbytes = (uint64_t)v; }
     else if (k == "digest") { std::string d = j.str(); en.digest = strtoull(d.c_str(), nullptr, 16); }
     else j.skip();
   } while (j.ok && j.eat(','));
@@ -145,6 +146,33 @@ void json_escape(const std::string& s, std::string& out) {
 }
 
 thread_local std::string g_err;
+
+// [offset, offset + nbytes) inside a region of `size` bytes, compared without overflow
+bool range_inside(uint64_t offset, uint64_t nbytes, uint64_t size) { return offset <= size && nbytes <= size - offset; }
+
+// bits per element of a safetensors / rank-file dtype (0 = unknown: the size check is skipped)
+int dtype_bits(const std::string& d) {
+  if (d == "F64" || d == "I64" || d == "U64") return 64;
+  if (d == "F32" || d == "I32" || d == "U32") return 32;
+  if (d == "F16" || d == "BF16" || d == "I16" || d == "U16") return 16;
+  if (d == "F8_E4M3" || d == "F8_E5M2" || d == "F8_E8M0" || d == "I8" || d == "U8" || d == "BOOL") return 8;
+  if (d == "F4") return 4;
+  return 0;
+}
+
+// prod(shape) * element size == nbytes (packed 4-bit types count two elements per byte)
+bool shape_matches(const Entry& en) {
+  const int bits = dtype_bits(en.dtype);
+  if (!bits) return true;
+  unsigned __int128 n = 1;
+  for (int64_t s : en.shape) {
+    if (s < 0) return false;
+    n *= (unsigned __int128)s;
+    if (n > ((unsigned __int128)1 << 70)) return false;
+  }
+  const unsigned __int128 total_bits = n * (unsigned)bits;
+  return total_bits == (unsigned __int128)en.nbytes * 8 || (bits == 4 && ((total_bits + 4) / 8 == en.nbytes || n == en.nbytes));
+}
 
 }  // namespace
 
@@ -169,7 +197,8 @@ void* sfb_st_open(const char* path) {
       if (name == "__metadata__") { s->meta = j.raw_value(); continue; }
       Entry en; en.name = name;
       if (!parse_entry_fields(j, en, true)) { j.ok = false; break; }
-      if (s->data_start + en.offset + en.nbytes > s->m.size) { g_err = "tensor " + name + " lies beyond the file"; delete s; return nullptr; }
+      if (!range_inside(en.offset, en.nbytes, s->m.size - s->data_start)) { g_err = "tensor " + name + " lies beyond the file"; delete s; return nullptr; }
+      if (!shape_matches(en)) { g_err = "tensor " + name + ": shape and dtype do not give its byte length"; delete s; return nullptr; }
       s->t.push_back(en);
     } while (j.ok && j.eat(','));
   }
@@ -267,7 +296,7 @@ void* sfb_rank_open(const char* path) {
     if (!j.eat(',')) break;
   }
   if (!ok || !j.ok) { g_err = "malformed table"; close(fd); delete r; return nullptr; }
-  for (auto& e : r->t) if (e.offset + e.nbytes > off) { g_err = "tensor " + e.name + " overlaps the table"; close(fd); delete r; return nullptr; }
+  for (auto& e : r->t) if (!range_inside(e.offset, e.nbytes, off)) { g_err = "tensor " + e.name + " overlaps the table"; close(fd); delete r; return nullptr; }
   return r;
 }
 void sfb_rank_close(void* h) { RankReader* r = (RankReader*)h; if (r->fd >= 0) close(r->fd); delete r; }

@@ -869,6 +869,13 @@ struct GatherSpec {
 };
 static thread_local GatherSpec g_gather;
 
+// An entry point that refuses its arguments must not leave a push or gather armed for some later, unrelated launch.
+static int refuse_args() {
+  g_push.n = 0;
+  g_gather.n = 0;
+  return (int)cudaErrorInvalidValue;
+}
+
 static void apply_gather(UmmaArgs& a) {
   for (int i = 0; i < 8; ++i) a.gflag[i] = i < g_gather.n ? (const uint32_t*)g_gather.flag[i] : nullptr;
   a.gepoch_ptr = (const uint32_t*)g_gather.epoch_ptr; a.gepoch_add = g_gather.epoch_add;
@@ -896,7 +903,7 @@ const bool bulk = a.force_bulk || a.tok_tiles > 1 || a.b_maps != nullptr || a.rs
   if (a.tok_tiles < 1) a.tok_tiles = 1;
 #define SFB_UM(NPV) { launch_rc = bulk ? launch_umma_t<NPV, true>(mA, mA2, mB, a, grid, stream) : launch_umma_t<NPV, false>(mA, mA2, mB, a, grid, stream); }
   if (NP == 16) SFB_UM(16) else if (NP == 32) SFB_UM(32) else if (NP == 64) SFB_UM(64) else if (NP == 128) SFB_UM(128)
-  else return (int)cudaErrorInvalidValue;
+  else return refuse_args();
 #undef SFB_UM
   return (int)launch_rc;
 }
@@ -927,8 +934,8 @@ int sfb_umma_dense(const void* tmapA, const void* tmapB, const void* sfa, int ka
                    unsigned int* tickets, void* out_b, float* out_f, int64_t out_stride, void* status,
                    cudaStream_t stream) {
   if ((N % 128 && groups > 1) || K % UM_BK || n > NP || splits < 1 || splits > K / UM_BK)
-    return (int)cudaErrorInvalidValue;
-  if (splits > 1 && (!scratch || !tickets)) return (int)cudaErrorInvalidValue;
+    return refuse_args();
+  if (splits > 1 && (!scratch || !tickets)) return refuse_args();
   UmmaArgs a{};
   a.sfa = (const uint8_t*)sfa; a.katoms_a = katoms_a; a.sfb = (const uint8_t*)sfb; a.katoms_b = katoms_b;
   a.n = n; a.K = K; a.a_fp4 = a_fp4; a.mode = UM_DENSE; a.N = N; a.groups = groups; a.splits = splits;
@@ -958,9 +965,9 @@ int sfb_umma_bulk(const void* tmapA, const void* tmapB, const void* sfa, int kat
                   int64_t out_stride, const void* b_maps, int b_k_per_map, const void* const* sfb_maps, int n_maps,
                   int rs_rows, void* status, cudaStream_t stream) {
   const int tok_tiles = (n + NP - 1) / NP;
-  if (K % UM_BK || splits < 1 || splits > K / UM_BK || n < 1 || (tok_tiles > 1 && NP != 128)) return (int)cudaErrorInvalidValue;
-  if (splits > 1 && (!scratch || !tickets)) return (int)cudaErrorInvalidValue;
-  if (b_maps && (n_maps < 1 || n_maps > 8 || b_k_per_map % UM_BK || b_k_per_map * n_maps != K)) return (int)cudaErrorInvalidValue;
+  if (K % UM_BK || splits < 1 || splits > K / UM_BK || n < 1 || (tok_tiles > 1 && NP != 128)) return refuse_args();
+  if (splits > 1 && (!scratch || !tickets)) return refuse_args();
+  if (b_maps && (n_maps < 1 || n_maps > 8 || b_k_per_map % UM_BK || b_k_per_map * n_maps != K)) return refuse_args();
   UmmaArgs a{};
   a.sfa = (const uint8_t*)sfa; a.katoms_a = katoms_a; a.sfb = (const uint8_t*)sfb; a.katoms_b = katoms_b;
   a.n = n; a.K = K; a.mode = UM_DENSE; a.N = N; a.groups = 1; a.splits = splits; a.scratch = scratch; a.tickets = tickets;
@@ -978,7 +985,7 @@ int sfb_umma_dense_pair(const void* tmapA, const void* tmapB, const void* sfa, i
                         float* scratch, unsigned int* tickets, void* out_b, float* out_f, int64_t out_stride,
                         void* out_q, void* out_q_atom, void* status, cudaStream_t stream) {
   if (N % 128 || K % UM_BK || 2 * pair > NP || pair < 1 || splits < 1 || splits > K / UM_BK || !scratch || !tickets)
-    return (int)cudaErrorInvalidValue;
+    return refuse_args();
   UmmaArgs a{};
   a.sfa = (const uint8_t*)sfa; a.katoms_a = katoms_a; a.sfb = (const uint8_t*)sfb; a.katoms_b = katoms_b;
   a.n = 2 * pair; a.pair = pair; a.K = K; a.a_fp4 = a_fp4; a.mode = UM_DENSE; a.N = N; a.groups = groups;
@@ -993,7 +1000,7 @@ int sfb_umma_gate_up(const void* tmapA, const void* tmapA2, const void* tmapB, c
                      const void* sfb, const int* ids, const float* wts, void* act_q, void* act_s, void* act_sf,
                      int n_tok, int top_k, int slots, int d, int inter, float limit, void* status,
                      cudaStream_t stream) {
-  if (inter % 128 || d % 32 || slots < top_k || slots > top_k + 1) return (int)cudaErrorInvalidValue;
+  if (inter % 128 || d % 32 || slots < top_k || slots > top_k + 1) return refuse_args();
   UmmaArgs a{};
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (d / 32 + 3) / 4;
   a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a; a.a_fp4 = 1; a.ids = ids; a.wts = wts; a.top_k = top_k;
@@ -1018,7 +1025,7 @@ int sfb_umma_down(const void* tmapA, const void* tmapA2, const void* tmapB, cons
                   const void* sfb, const int* ids, void* out_b, float* out_f, int64_t out_stride, float* scratch,
                   unsigned int* tickets, int n_tok, int top_k, int slots, int d, int inter, void* status,
                   cudaStream_t stream) {
-  if (d % 128 || inter % 128 || !scratch || !tickets) return (int)cudaErrorInvalidValue;
+  if (d % 128 || inter % 128 || !scratch || !tickets) return refuse_args();
   UmmaArgs a{};
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (inter / 32 + 3) / 4;
   a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a; a.a_fp4 = 1; a.mode = UM_DOWN; a.ids = ids; a.top_k = top_k;
@@ -1036,7 +1043,7 @@ extern "C" {
 int sfb_umma_gate_up_grouped(const void* tmapA, const void* tmapA2, const void* tmapB, const void* sfa, const void* sfa2, const void* sfb,
                              const int* seg_expert, const int* seg_count, const float* seg_weight, void* act_q, void* act_sf, int segments,
                              int d, int inter, float limit, void* status, cudaStream_t stream) {
-  if (inter % 128 || d % 32 || segments < 1) return (int)cudaErrorInvalidValue;
+  if (inter % 128 || d % 32 || segments < 1) return refuse_args();
   UmmaArgs a{};
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (d / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
   a.a_fp4 = 1; a.top_k = 0; a.slots = 1; a.inter = inter; a.d = d; a.act_q = (uint8_t*)act_q; a.act_sf = (uint8_t*)act_sf; a.limit = limit;
@@ -1060,7 +1067,7 @@ int sfb_umma_gate_up_grouped(const void* tmapA, const void* tmapA2, const void* 
 int sfb_umma_down_grouped(const void* tmapA, const void* tmapA2, const void* tmapB, const void* sfa, const void* sfa2, const void* sfb,
                           const int* seg_expert, const int* seg_count, float* out_f, int segments, int d, int inter, void* status,
                           cudaStream_t stream) {
-  if (d % 128 || inter % 128 || segments < 1) return (int)cudaErrorInvalidValue;
+  if (d % 128 || inter % 128 || segments < 1) return refuse_args();
   UmmaArgs a{};
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (inter / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
   a.a_fp4 = 1; a.mode = UM_DOWN_GROUPED; a.inter = inter; a.d = d; a.out_f = out_f; a.out_stride = d; a.seg_expert = seg_expert;
@@ -1102,6 +1109,11 @@ int sfb_umma_dense_noalloc(const void* tmapA, const void* tmapB, const void* sfa
     snprintf(g_noalloc_err, sizeof g_noalloc_err, "bad shape: N=%d groups=%d splits=%d NP=%d", N, groups, splits, NP);
     return (int)cudaErrorInvalidValue;
   }
+  g_push.n = 0;      // this entry point never pushes to peers: a push armed for another call does not carry over
+  g_gather.n = 0;
+  if (splits == 1)   // a single split writes its output directly: no partial sums, no counters, no size limit
+    return sfb_umma_dense(tmapA, tmapB, sfa, katoms_a, sfb, katoms_b, n, NP, N, K, groups, a_fp4, 1, nullptr, nullptr,
+                          out_b, out_f, out_stride, status, stream);
   const long long tiles = (long long)groups * (N / 128);
   const long long floats = tiles * splits * 128 * NP;
   if (tiles > SFB_NOALLOC_MAX_TILES || floats > SFB_NOALLOC_MAX_FLOATS) {

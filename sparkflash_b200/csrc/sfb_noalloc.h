@@ -25,6 +25,14 @@
 //   * All calls share the arrays and find in them whatever the previous call left; the counters
 //     are cleared on the stream before each launch.  Two calls that overlap on the GPU (different
 //     streams, or the same stream with programmatic overlap) race on the arrays: serialise them.
+//   * With splits == 1 nothing is accumulated across CTAs, so the arrays are not touched and the
+//     size limits above do not apply.
+//   * The address lookup of the first call is not locked.  Two host threads that make their first
+//     call on the same device at the same time both run the lookup and store the same two
+//     addresses; that is harmless, but a caller that wants no such overlap makes one call per
+//     device from one thread during start-up.
+//   * A peer push armed with sfb_umma_set_push (or a gather armed with sfb_umma_set_gather) for
+//     some other call is discarded here, not inherited: this entry point writes only out_b / out_f.
 //   * The function calls no cudaMalloc, cudaFree or allocating library routine.
 #pragma once
 #include <cuda_runtime.h>

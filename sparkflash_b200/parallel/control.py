@@ -1,8 +1,11 @@
 """Control channel between the ranks of one serving group: rank 0 broadcasts the inputs of every tick, every
 rank sends heartbeats, and each side notices when the other stops.
 
-Wire: TCP, frames of ``u32 length | u8 kind | payload`` (kind 0 tick, 1 heartbeat, 2 goodbye).  The leader
-keeps one socket per follower.  Liveness is host-side only - a rank that stops answering is detected by a
+Wire: TCP, frames of ``u32 length | u8 kind | payload`` (kind 0 tick, 1 heartbeat, 2 goodbye).  Tick payloads
+are plain data in the tagged binary encoding of ``wire.py`` - nothing on this socket is ever unpickled.  The
+leader keeps one socket per follower; a connection is admitted only after it answers the leader's random
+challenge with an HMAC under the group's shared token and announces a rank in 1..world-1 that nobody holds
+yet.  Tick frames are accepted from the leader only: the leader drops any that a follower sends.  Liveness is host-side only - a rank that stops answering is detected by a
 missing heartbeat, never by waiting on the device.  Policy is fail-stop: when any rank is lost the group
 stops serving and an outside supervisor restarts it.
 
@@ -12,11 +15,15 @@ channel closes), crates/sparkflash-comm/src/tcp.rs.
 """
 from __future__ import annotations
 
-import pickle
+import hashlib
+import hmac
+import os
 import socket
 import struct
 import threading
 import time
+
+from . import wire
 
 TICK, HEARTBEAT, GOODBYE = 0, 1, 2
 
@@ -40,9 +47,27 @@ def _recv_exact(sock: socket.socket, n: int) -> bytes:
     return buf
 
 
+MAX_FRAME = 1 << 30
+
+
 def _recv(sock: socket.socket) -> tuple[int, bytes]:
     ln, kind = struct.unpack("<IB", _recv_exact(sock, 5))
+    if ln > MAX_FRAME:
+        raise ChannelClosed("oversized control frame")
     return kind, _recv_exact(sock, ln) if ln else b""
+
+
+def _default_token() -> bytes:
+    """Shared secret of the group: ``SFB_CONTROL_TOKEN`` when set (multi-node launches export the same value on
+    every node), else a value derived from the rendezvous address every rank already agrees on."""
+    t = os.environ.get("SFB_CONTROL_TOKEN")
+    if t:
+        return t.encode()
+    return f"sfb:{os.environ.get('MASTER_ADDR', '127.0.0.1')}:{os.environ.get('MASTER_PORT', '0')}".encode()
+
+
+def _answer(token: bytes, nonce: bytes, rank: int) -> bytes:
+    return hmac.new(token, nonce + struct.pack("<I", rank), hashlib.sha256).digest()
 
 
 class ControlChannel:
@@ -50,8 +75,10 @@ class ControlChannel:
     argument and returns the leader's next message (blocking, bounded by ``timeout``)."""
 
     def __init__(self, rank: int, world: int, addr: str = "127.0.0.1", port: int = 29600, heartbeat: float = 0.5,
-                 timeout: float = 5.0, connect_timeout: float = 60.0, drop=None):
+                 timeout: float = 5.0, connect_timeout: float = 60.0, drop=None, token: bytes | str | None = None):
         self.rank, self.world = rank, world
+        token = _default_token() if token is None else (token.encode() if isinstance(token, str) else token)
+        self.rejected = 0                      # connections the leader turned away (bad token, bad or duplicate rank)
         self.heartbeat, self.timeout = heartbeat, timeout
         self._drop = drop                      # test hook: drop(kind, direction) -> True to lose the frame
         self._lock = threading.Lock()
@@ -74,7 +101,21 @@ class ControlChannel:
                 while len(self._socks) < world - 1:
                     s, _ = srv.accept()
                     s.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
-                    r = struct.unpack("<I", _recv_exact(s, 4))[0]
+                    try:
+                        s.settimeout(5.0)
+                        nonce = os.urandom(16)
+                        s.sendall(nonce)
+                        hello = _recv_exact(s, 4 + 32)
+                        r = struct.unpack("<I", hello[:4])[0]
+                        good = 1 <= r < world and r not in self._socks and hmac.compare_digest(hello[4:], _answer(token, nonce, r))
+                        s.sendall(b"\x01" if good else b"\x00")
+                        s.settimeout(None)
+                    except (OSError, ChannelClosed):
+                        good = False
+                    if not good:
+                        self.rejected += 1
+                        s.close()
+                        continue
                     self._socks[r], self._locks[r] = s, threading.Lock()
                     self._last_seen[r] = time.monotonic()
             finally:
@@ -89,9 +130,14 @@ class ControlChannel:
                     if time.monotonic() - t0 > connect_timeout:
                         raise
                     time.sleep(0.05)
-            s.settimeout(None)
+            s.settimeout(10.0)
             s.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
-            s.sendall(struct.pack("<I", rank))
+            nonce = _recv_exact(s, 16)
+            s.sendall(struct.pack("<I", rank) + _answer(token, nonce, rank))
+            if _recv_exact(s, 1) != b"\x01":
+                s.close()
+                raise ChannelClosed("the leader refused this rank (token mismatch, or the rank is out of range or taken)")
+            s.settimeout(None)
             self._socks[0], self._locks[0] = s, threading.Lock()
             self._last_seen[0] = time.monotonic()
         for peer, s in self._socks.items():
@@ -107,8 +153,15 @@ class ControlChannel:
                     continue
                 self._last_seen[peer] = time.monotonic()
                 if kind == TICK:
+                    if self.rank == 0:
+                        continue                     # only the leader originates ticks
+                    try:
+                        msg = wire.loads(payload)
+                    except (wire.WireError, struct.error, UnicodeDecodeError, TypeError) as e:
+                        self._fail(f"rank {peer}: malformed tick ({e})")
+                        return
                     with self._cv:
-                        self._ticks.append(pickle.loads(payload))
+                        self._ticks.append(msg)
                         self._cv.notify_all()
                 elif kind == GOODBYE:
                     self.departed.add(peer)          # an orderly leave (drain), as opposed to a silent or broken peer
@@ -148,7 +201,7 @@ class ControlChannel:
         if self._failed:
             raise ChannelClosed(self._failed)
         if self.rank == 0:
-            payload = pickle.dumps(msg, protocol=pickle.HIGHEST_PROTOCOL)
+            payload = wire.dumps(msg)
             for peer, s in self._socks.items():
                 try:
                     if not (self._drop and self._drop(TICK, "out")):

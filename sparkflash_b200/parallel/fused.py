@@ -182,6 +182,24 @@ class FusedComm:
                 [lay.flag(self.base, BEST, s) for s in range(self.world)])
 
     def close(self) -> None:
+        """Unmap the peers' allocations and free this rank's own (idempotent).  Across processes every rank first
+        reaches a barrier, so that nobody frees memory a peer's kernel may still be storing into; a rank that finds
+        the process group gone already (fail-stop teardown) skips the barrier."""
+        if self._owned is None and not self._opened:
+            return
+        import torch
+        torch.cuda.synchronize()
+        if self._opened:
+            try:
+                import torch.distributed as dist
+                if dist.is_available() and dist.is_initialized():
+                    dist.barrier()
+            except Exception:
+                pass
         for p in self._opened:
             _L().sfb_ipc_close_handle(c_void_p(p))
         self._opened = []
+        if self._owned is not None:
+            _L().sfb_symm_free(c_void_p(self._owned))
+            self._owned = None
+        self.bases = []

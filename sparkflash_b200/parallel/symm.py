@@ -72,6 +72,23 @@ class SymmHeap:
         return t.view(dtype).reshape(shape)
 
     def close(self) -> None:
+        """Unmap the peers' heaps and free this rank's own (idempotent; a barrier first when peers are mapped)."""
+        if getattr(self, "_owned", None) is None and not self._opened:
+            return
+        import torch
+        torch.cuda.synchronize()
+        if self._opened:
+            try:
+                import torch.distributed as dist
+                if dist.is_available() and dist.is_initialized():
+                    dist.barrier()
+            except Exception:
+                pass
         for p in self._opened:
             _lib.cuda().sfb_ipc_close_handle(c_void_p(p))
         self._opened = []
+        self._keep = []
+        if getattr(self, "_owned", None) is not None:
+            _lib.cuda().sfb_symm_free(c_void_p(self._owned))
+            self._owned = None
+        self.bases = []

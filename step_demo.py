@@ -1,8 +1,8 @@
 """A few rows steps of a three-layer model at full per-token shapes, without CUDA graphs, for launch lists and
 single-kernel captures:
 
-    python -m sparkflash_b200.models.deepseek_v41.step_demo --rows 64            # prompt chunks of one sequence
-    python -m sparkflash_b200.models.deepseek_v41.step_demo --rows 16 --decode   # one row per sequence
+    python step_demo.py --rows 64            # prompt chunks of one sequence
+    python step_demo.py --rows 16 --decode   # one row per sequence
 
 Only the last step sits between cudaProfilerStart/Stop, so a profiler started with its collection off sees exactly one
 step (three layers: two window-only, one with the compressor, indexer and selection; plus the head when decoding).
@@ -21,8 +21,8 @@ def main() -> None:
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--layers", type=int, default=3)
     args = ap.parse_args()
-    from ...config import reduced_config
-    from . import engine as E, prepare as P
+    from sparkflash_b200.config import reduced_config
+    from sparkflash_b200.models.deepseek_v41 import engine as E, prepare as P
     cfg = reduced_config(args.experts, args.layers)
     w = P.prepare_synthetic(cfg, 0, 1)
     rows = args.rows

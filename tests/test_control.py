@@ -125,3 +125,64 @@ def test_followers_replay_the_leaders_ticks():
     assert all(len(t) == 6 for t in got[0][1])
     # the follower ran the same rows steps in the same order (it may miss only ticks after the leader's last answer)
     assert foll_steps[:len(lead_steps)] == lead_steps[:len(foll_steps)] and len(foll_steps) >= len(lead_steps) - 1 and len(foll_steps) > 5
+
+
+def test_wire_codec_round_trips_requests_and_refuses_unknown_types():
+    import dataclasses
+    import torch
+    from sparkflash_b200.parallel import wire
+    from sparkflash_b200.serve.engine_api import EngineRequest
+    req = EngineRequest("r1", "m", [1, 2, 3], temperature=0.5, stop=["x"], seed=2 ** 70, constraint={"a": [1, None, True]})
+    emb = torch.arange(12, dtype=torch.float32).reshape(3, 4).to(torch.bfloat16)
+    msg = {"subs": [(7, req)], "cancels": [3, 4], "emb": emb, "blob": b"\x00\x01", "t": (1.5, "s")}
+    back = wire.loads(wire.dumps(msg))
+    assert dataclasses.asdict(back["subs"][0][1]) == dataclasses.asdict(req) and back["subs"][0][0] == 7
+    assert torch.equal(back["emb"], emb) and back["blob"] == b"\x00\x01" and back["t"] == (1.5, "s") and back["cancels"] == [3, 4]
+
+    class Stranger:
+        pass
+    with pytest.raises(wire.WireError):
+        wire.dumps({"x": Stranger()})
+    for bad in (b"\xff", wire.dumps([1, 2])[:-1], wire.dumps(1) + b"\x00", bytes([12, 3]) + b"Foo" + bytes(4)):
+        with pytest.raises(wire.WireError):
+            wire.loads(bad)
+
+
+def test_leader_refuses_strangers_and_ignores_ticks_from_followers():
+    """A connection without the group's token, with an out-of-range rank or with a rank already taken is turned
+    away; a tick frame sent *to* the leader is dropped, never decoded."""
+    import socket
+    import struct
+    import threading
+    from sparkflash_b200.parallel import control as C
+    port = PORT + 7
+    box = {}
+    t = threading.Thread(target=lambda: box.setdefault("lead", ControlChannel(0, 2, port=port, heartbeat=0.05, timeout=5.0, token="secret")))
+    t.start()
+
+    def knock(rank, token):
+        for _ in range(200):
+            try:
+                s = socket.create_connection(("127.0.0.1", port), timeout=2.0)
+                break
+            except OSError:
+                time.sleep(0.02)
+        nonce = C._recv_exact(s, 16)
+        s.sendall(struct.pack("<I", rank) + C._answer(token, nonce, rank))
+        ok = C._recv_exact(s, 1)
+        return s, ok
+    s1, ok1 = knock(1, b"wrong")
+    s2, ok2 = knock(5, b"secret")
+    assert ok1 == b"\x00" and ok2 == b"\x00"
+    good = ControlChannel(1, 2, port=port, heartbeat=0.05, timeout=5.0, token="secret")
+    t.join(10)
+    lead = box["lead"]
+    assert lead.rejected == 2
+    # a follower-originated tick never reaches the leader's queue
+    C._send(good._socks[0], C.TICK, b"\x80\x04garbage-that-an-unpickler-would-run", good._locks[0])
+    time.sleep(0.3)
+    assert lead._ticks == [] and lead.alive()[0]
+    lead.broadcast({"tick": 1})
+    assert good.broadcast(None) == {"tick": 1}
+    good.close(); lead.close()
+    s1.close(); s2.close()

@@ -56,8 +56,7 @@ def test_two_ranks_fused_and_nccl_agree(tmp_path, arm, collectives):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    logdir = os.path.join(repo, "gpurun_out")
-    os.makedirs(logdir, exist_ok=True)
+    logdir = str(tmp_path)
     env = dict(os.environ, SFB_REPO=repo, NCCL_NVLS_ENABLE="0", SFB_TEST_ARM=arm, SFB_TEST_COLLECTIVES=collectives,
                SFB_WORKER_LOG=os.path.join(logdir, f"mgpu_worker_{arm}.log"))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
@@ -137,7 +136,3 @@ def test_two_rank_server_answers_a_chat_request(tmp_path):
             os.killpg(proc.pid, signal.SIGKILL)
             proc.wait()
         log.close()
-        keep = os.path.join(repo, "gpurun_out")          # the ranks' boot lines and any traceback, for a failed run
-        os.makedirs(keep, exist_ok=True)
-        with open(os.path.join(keep, "serve_two_ranks.log"), "w") as f:
-            f.write(open(tmp_path / "serve.log").read()[-20000:])

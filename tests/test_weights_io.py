@@ -32,6 +32,34 @@ def test_safetensors_roundtrip_and_views(tmp_path):
         F.SafeTensorsFile(str(bad))
 
 
+def _raw_safetensors(path, header: dict, payload: bytes) -> str:
+    import json
+    h = json.dumps(header).encode()
+    path.write_bytes(len(h).to_bytes(8, "little") + h + payload)
+    return str(path)
+
+
+def test_safetensors_rejects_crafted_offsets(tmp_path):
+    """A header whose byte ranges are reversed, negative, beyond the file or at odds with shape x dtype is refused at open
+    (the length b - a must never wrap into a huge unsigned value)."""
+    ok = {"t": {"dtype": "U8", "shape": [16], "data_offsets": [0, 16]}}
+    f = F.SafeTensorsFile(_raw_safetensors(tmp_path / "ok.safetensors", ok, bytes(16)))
+    assert f.tensor("t").numel() == 16
+    f.close()
+    cases = {
+        "reversed": {"t": {"dtype": "U8", "shape": [16], "data_offsets": [16, 0]}},
+        "negative": {"t": {"dtype": "U8", "shape": [16], "data_offsets": [-16, 0]}},
+        "huge": {"t": {"dtype": "U8", "shape": [16], "data_offsets": [0, 2 ** 62]}},
+        "huge_begin": {"t": {"dtype": "U8", "shape": [0], "data_offsets": [2 ** 62, 2 ** 62]}},
+        "beyond": {"t": {"dtype": "U8", "shape": [17], "data_offsets": [0, 17]}},
+        "shape_mismatch": {"t": {"dtype": "F32", "shape": [16], "data_offsets": [0, 16]}},
+        "negative_dim": {"t": {"dtype": "U8", "shape": [-16], "data_offsets": [0, 16]}},
+    }
+    for name, header in cases.items():
+        with pytest.raises(OSError):
+            F.SafeTensorsFile(_raw_safetensors(tmp_path / f"{name}.safetensors", header, bytes(16)))
+
+
 def test_digest_is_stable_and_sensitive():
     t = torch.arange(1000, dtype=torch.int32)
     d = F.digest64(t)
