@@ -1,0 +1,501 @@
+// CSA2 sparse-MLA attention on tcgen05 for steps of many rows (prompt chunks, wide verify steps).
+//
+// One CTA = one row x one group of NH heads.  The row's keys (the causal window from the FP8 ring, then the
+// selected compressed FP4 entries) are decoded once into a bf16 tile of 128 keys x 512 dims in shared memory,
+// laid out as eight slabs of [128 keys x 64 dims] with the 128-byte swizzle.  The one latent row is key and
+// value for every head, so the same tile feeds both contractions:
+//
+//   S^T[key, head] = K[key, :] . Q[head, :]      A = key tile, K-major (dims contiguous);  B = Q, K-major
+//   O^T[dim, head] += V^T[dim, key] P^T[key, head]   A = the same tile read MN-major (dims are M);  B = P, K-major
+//
+// Both run as tcgen05.mma kind::f16 (bf16 in, fp32 accumulators in TMEM): S^T is 128 lanes (keys) x NH columns,
+// O^T is four 128-dim tiles x NH columns.  FP8 x 2^k and FP4 x E4M3 products are exact in bf16, so QK^T sees the
+// cache's exact values; P is rounded to bf16 for the second contraction (the CUDA-core rows kernel keeps it in
+// fp32: this kernel is a tolerance arm, not a bit-exact one).  Softmax is online over tiles of 128 keys: the
+// score tile goes TMEM -> registers -> shared memory (transposed), threads then own heads, and the running
+// accumulator in TMEM is rescaled per column when a head's maximum moves.  The sink enters the denominator only.
+// Query RoPE on load, inverse RoPE on the output's rope slice, optional two-term FP8 copy for the wo_a GEMM.
+//
+// No cluster, no multicast; every mbarrier wait is bounded and reports through the status word.
+//
+// Reference behaviour replaced: kernels/opt_mma_sm121.cu:1243 (opt_bulk_attn: one block per row, heads as the MMA M),
+// kernels/flash_mla_csa2_common_sm121.cuh; docs/architecture/01-csa2-attention.md:98-104,212-229.
+#include <cuda.h>
+
+#include "k_common.cuh"
+
+namespace sfb {
+
+namespace atc {
+
+constexpr int HD = 512;            // latent width
+constexpr int KT = 128;            // keys per tile
+constexpr int SLABS = HD / 64;     // 64 bf16 = one 128-byte swizzle row
+constexpr int SLAB_BYTES = KT * 128;
+constexpr int THREADS = 128;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) __nanosleep(32);
+  }
+  return false;
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 version bit set), 128-byte swizzle.
+//   K-major operand:  rows of 128 bytes, 8-row groups `sbo` bytes apart (lbo unused).
+//   MN-major operand: 64 contiguous MN elements per 128-byte row, one row per k; 8-k groups `sbo` bytes apart,
+//                     64-element MN blocks `lbo` bytes apart.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t sbo_bytes, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fff);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+  return d;
+}
+// kind::f16, bf16 operands, fp32 accumulator; a_mn: A operand is MN-major
+__device__ __forceinline__ uint32_t make_idesc(int M, int N, int a_mn) {
+  uint32_t d = 0;
+  d |= 1u << 4;
+  d |= 1u << 7;
+  d |= 1u << 10;
+  d |= (uint32_t)(a_mn & 1) << 15;
+  d |= (uint32_t)((N >> 3) & 63) << 17;
+  d |= (uint32_t)((M >> 4) & 31) << 24;
+  return d;
+}
+// byte offset of 16-byte chunk `c16` (0..7) of row `r` inside a 128-byte-swizzled slab
+__device__ __forceinline__ uint32_t swz(int r, int c16) { return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c16 ^ (r & 7)) << 4)); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+}  // namespace atc
+
+struct AttnTcArgs {
+  const __nv_bfloat16* q;   // [n, q_stride]; head h at h*512
+  int64_t q_stride;
+  const float2* rope;       // [n, rope_stride]: (cos, sin) of the row's position
+  int rope_stride;
+  const int* row_lane;
+  const int* row_pos;
+  const uint8_t* win_q;     // [lanes, ring, 512]
+  const uint8_t* win_s;     // [lanes, ring, 16]
+  int64_t win_lane_q, win_lane_s;
+  const uint8_t* ckv_q;     // [lanes, max_entries, 256] (null: window only)
+  const uint8_t* ckv_s;     // [lanes, max_entries, 32]
+  int64_t ckv_lane_q, ckv_lane_s;
+  const int* sel;           // [n, K] ascending ids, -1 padded
+  const int* sel_count;     // [n]
+  int K;
+  const float* sink;        // [heads]
+  __nv_bfloat16* out;       // [n, heads*512]
+  uint8_t* out_q;           // optional two-term FP8 copy in blocks of 2*pair_block rows: hi rows then lo rows of each block
+  uint8_t* out_atom;        // its scale atoms (128 rows per atom block)
+  int pair_block;           // rows per block of the two-term copy (64), or 0: hi rows [0,n), lo rows [n,2n) as the rows kernel
+  int n, heads, rd, window, ring;
+  float scale;
+  const int* win_lo;        // optional explicit inclusive window range per row
+  const int* win_hi;
+  Status* status;
+};
+
+}  // namespace sfb
+
+namespace sfb {
+
+using namespace atc;
+
+template <int NH>
+struct AttnTcSmem {
+  alignas(1024) uint8_t kv[SLABS * SLAB_BYTES];   // 128 keys x 512 dims bf16, eight swizzled slabs
+  alignas(1024) uint8_t q[SLABS * NH * 128];      // NH heads x 512 dims bf16
+  alignas(1024) uint8_t p[2 * NH * 128];          // NH heads x 128 keys bf16 (two slabs of 64 keys)
+  float sbuf[NH][KT + 1];                         // scores of the tile, head-major
+  float red[THREADS];                             // per (key part, head) partial max / sum
+  float fac[NH];                                  // per-head rescale of the running accumulator; 1/denominator at the end
+  alignas(8) uint64_t bar;
+  uint32_t tmem_base;
+};
+
+// grid (head groups, rows), 128 threads.  Thread t owns key slot t of every tile (decode, TMEM lane of the score tile)
+// and dim 32*warp + lane of each 128-dim output tile; for the softmax it owns head t % NH over the key part t / NH.
+template <int NH>
+__global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = AttnTcSmem<NH>;
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr uint32_t TMEM_COLS = NH * 5 <= 128 ? 128 : 256;
+  constexpr int PARTS = THREADS / NH;      // key parts per head in the softmax
+  constexpr int KPP = KT / PARTS;          // keys per part
+  constexpr float LOG2E = 1.4426950408889634f;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int hg = blockIdx.x, row = blockIdx.y;
+
+  if (tid == 0) {
+    mbar_init(&S.bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    tmem_alloc(&S.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_wait();
+  const uint32_t tmem = S.tmem_base;
+  const uint32_t t_s = tmem, t_o = tmem + NH;
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+
+  const int pos = a.row_pos[row], L = a.row_lane[row];
+  const int r0 = HD - a.rd;
+  // ---- queries of the group's heads: rope on the last rd dims, bf16, swizzled K-major ----
+  for (int idx = tid; idx < NH * 64; idx += THREADS) {
+    const int hh = idx >> 6, c = idx & 63;          // head in group, 8-dim chunk
+    const int ghead = hg * NH + hh;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (ghead < a.heads) {
+      v = *reinterpret_cast<const uint4*>(a.q + (size_t)row * a.q_stride + (size_t)ghead * HD + c * 8);
+      if (c * 8 >= r0) {
+        __nv_bfloat162* pr = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 c2 = a.rope[(size_t)row * a.rope_stride + ((c * 8 - r0) >> 1) + j];
+          const float x = __bfloat162float(pr[j].x), y = __bfloat162float(pr[j].y);
+          pr[j] = __floats2bfloat162_rn(x * c2.x - y * c2.y, x * c2.y + y * c2.x);
+        }
+      }
+    }
+    *reinterpret_cast<uint4*>(S.q + (c >> 3) * (NH * 128) + swz(hh, c & 7)) = v;
+  }
+
+  const int w_first = a.win_lo ? a.win_lo[row] : (pos - a.window + 1 > 0 ? pos - a.window + 1 : 0);
+  const int n_win = (a.win_hi ? a.win_hi[row] : pos) - w_first + 1;
+  const int n_sel = a.ckv_q ? a.sel_count[row] : 0;
+  const int total = n_win + n_sel;
+  const int tiles = (total + KT - 1) / KT;
+  const int my_head = tid % NH, my_part = tid / NH;
+  float m_run = -1e30f, l_run = 0.f;       // identical in every thread that shares my_head
+  uint32_t parity = 0;
+  bool ok = true;
+  const float sl2 = a.scale * LOG2E;
+
+  for (int tile = 0; tile < tiles && ok; ++tile) {
+    // ---- decode key slot `tid` of the tile into the bf16 tile (exact: FP8 x 2^k, FP4 x E4M3) ----
+    {
+      const int e = tile * KT + tid;
+      uint8_t* rowp = S.kv;
+      if (e < n_win) {
+        const int slot = (w_first + e) % a.ring;
+        const uint8_t* kq = a.win_q + (size_t)L * a.win_lane_q + (size_t)slot * HD;
+        const uint8_t* ks = a.win_s + (size_t)L * a.win_lane_s + (size_t)slot * (HD / 32);
+        const uint4 sc4 = *reinterpret_cast<const uint4*>(ks);
+        const uint8_t* scb = reinterpret_cast<const uint8_t*>(&sc4);
+#pragma unroll 2
+        for (int prt = 0; prt < 16; ++prt) {
+          const uint4 raw0 = *reinterpret_cast<const uint4*>(kq + prt * 32);
+          const uint4 raw1 = *reinterpret_cast<const uint4*>(kq + prt * 32 + 16);
+          const float rs = ue8m0_to_f32(scb[prt]) * 1.152921504606847e18f;    // 2^60; the raw decode carries 2^-120
+          float f[32];
+          decode16_e4m3_raw(raw0, f); decode16_e4m3_raw(raw1, f + 16);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              ow[u] = pack_bf16((f[8 * j + 2 * u] * 1.152921504606847e18f) * rs, (f[8 * j + 2 * u + 1] * 1.152921504606847e18f) * rs);
+            const int c = prt * 4 + j;
+            *reinterpret_cast<uint4*>(rowp + (c >> 3) * SLAB_BYTES + swz(tid, c & 7)) = o;
+          }
+        }
+      } else if (e < total) {
+        const int id = a.sel[(size_t)row * a.K + (e - n_win)];
+        const uint8_t* kq = a.ckv_q + (size_t)L * a.ckv_lane_q + (size_t)id * (HD / 2);
+        const uint8_t* ks = a.ckv_s + (size_t)L * a.ckv_lane_s + (size_t)id * (HD / 16);
+        const uint4 sa = *reinterpret_cast<const uint4*>(ks), sb = *reinterpret_cast<const uint4*>(ks + 16);
+        uint8_t scb[32];
+        *reinterpret_cast<uint4*>(scb) = sa; *reinterpret_cast<uint4*>(scb + 16) = sb;
+#pragma unroll 2
+        for (int prt = 0; prt < 16; ++prt) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(kq + prt * 16);
+          const float rs0 = e4m3_to_f32(scb[2 * prt]) * 9.223372036854776e18f;       // 2^63; the raw decode carries 2^-126
+          const float rs1 = e4m3_to_f32(scb[2 * prt + 1]) * 9.223372036854776e18f;
+          float f[32];
+          decode32_e2m1_raw(raw, f);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float rs = j < 2 ? rs0 : rs1;
+            uint4 o;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              ow[u] = pack_bf16((f[8 * j + 2 * u] * 9.223372036854776e18f) * rs, (f[8 * j + 2 * u + 1] * 9.223372036854776e18f) * rs);
+            const int c = prt * 4 + j;
+            *reinterpret_cast<uint4*>(rowp + (c >> 3) * SLAB_BYTES + swz(tid, c & 7)) = o;
+          }
+        }
+      } else {
+        // past the row's last key: zeros, so that the value contraction adds 0 x 0 and never meets stale bits
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll 4
+        for (int c = 0; c < 64; ++c) *reinterpret_cast<uint4*>(rowp + (c >> 3) * SLAB_BYTES + swz(tid, c & 7)) = z;
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    // ---- S^T = K Q^T ----
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t idesc = make_idesc(128, NH, 0);
+      const uint32_t kvb = smem_u32(S.kv), qb = smem_u32(S.q);
+#pragma unroll
+      for (int s = 0; s < SLABS; ++s) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tc_mma_f16(t_s, make_desc(kvb + s * SLAB_BYTES + kk * 32, 1024, 16), make_desc(qb + s * (NH * 128) + kk * 32, 1024, 16), idesc,
+                     (s | kk) ? 1u : 0u);
+      }
+      tc_commit(&S.bar);
+    }
+    ok = mbar_wait(&S.bar, parity);
+    parity ^= 1;
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    if (!ok) break;
+    tc_fence_after();
+    // ---- scores: TMEM (lane = key) -> shared memory, head-major ----
+    {
+      const bool valid = tile * KT + tid < total;
+#pragma unroll
+      for (int c0 = 0; c0 < NH; c0 += 16) {
+        uint32_t v[16];
+        tc_ld16(t_s + lane_base + c0, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) S.sbuf[c0 + j][tid] = valid ? __uint_as_float(v[j]) * sl2 : -INFINITY;
+      }
+    }
+    __syncthreads();
+    // ---- online softmax: thread = (head, key part) ----
+    float mloc = -INFINITY;
+    const float* srow = &S.sbuf[my_head][my_part * KPP];
+#pragma unroll 8
+    for (int i = 0; i < KPP; ++i) mloc = fmaxf(mloc, srow[i]);
+    S.red[my_part * NH + my_head] = mloc;
+    __syncthreads();
+    float m_new = m_run;
+#pragma unroll
+    for (int pp = 0; pp < PARTS; ++pp) m_new = fmaxf(m_new, S.red[pp * NH + my_head]);
+    const float corr = exp2f(m_run - m_new);
+    __syncthreads();                 // everyone has read the maxima before the sums overwrite them
+    float lsum = 0.f;
+#pragma unroll 4
+    for (int i = 0; i < KPP; i += 2) {
+      const float p0 = exp2f(srow[i] - m_new), p1 = exp2f(srow[i + 1] - m_new);
+      const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+      lsum += __bfloat162float(pb.x) + __bfloat162float(pb.y);      // the denominator sums what the value contraction multiplies
+      const int key = my_part * KPP + i;
+      *reinterpret_cast<__nv_bfloat162*>(S.p + (key >> 6) * (NH * 128) + swz(my_head, (key & 63) >> 3) + (key & 7) * 2) = pb;
+    }
+    S.red[my_part * NH + my_head] = lsum;
+    if (my_part == 0) S.fac[my_head] = corr;
+    __syncthreads();
+    float lt = 0.f;
+#pragma unroll
+    for (int pp = 0; pp < PARTS; ++pp) lt += S.red[pp * NH + my_head];
+    l_run = l_run * corr + lt;
+    m_run = m_new;
+    // ---- rescale the running O^T (lane = dim, column = head) ----
+    if (tile > 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int c0 = 0; c0 < NH; c0 += 16) {
+          uint32_t v[16];
+          tc_ld16(t_o + lane_base + j * NH + c0, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * S.fac[c0 + i]);
+          tc_st16(t_o + lane_base + j * NH + c0, v);
+        }
+      }
+      tc_wait_st();
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    // ---- O^T += V^T P^T ----
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t idesc = make_idesc(128, NH, 1);
+      const uint32_t kvb = smem_u32(S.kv), pb = smem_u32(S.p);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int t8 = 0; t8 < KT / 16; ++t8)
+          tc_mma_f16(t_o + j * NH, make_desc(kvb + (2 * j) * SLAB_BYTES + t8 * 2048, 1024, SLAB_BYTES),
+                     make_desc(pb + (t8 >> 2) * (NH * 128) + (t8 & 3) * 32, 1024, 16), idesc, (tile > 0 || t8 > 0) ? 1u : 0u);
+      }
+      tc_commit(&S.bar);
+    }
+    ok = mbar_wait(&S.bar, parity);
+    parity ^= 1;
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    tc_fence_after();
+  }
+
+  // ---- epilogue: O^T / denominator (sink in the denominator only), inverse rope, bf16 (+ two-term FP8 copy) ----
+  if (ok) {
+    if (my_part == 0) {
+      const int ghead = hg * NH + my_head;
+      const float sk = ghead < a.heads ? a.sink[ghead] : 0.f;
+      S.fac[my_head] = 1.f / (l_run + exp2f(sk * LOG2E - m_run));
+    }
+    __syncthreads();
+    const size_t Wd = (size_t)a.heads * HD;
+    int row_hi = row, row_lo = a.n + row;
+    if (a.pair_block > 0) {
+      row_hi = (row / a.pair_block) * 2 * a.pair_block + row % a.pair_block;
+      row_lo = row_hi + a.pair_block;
+    }
+    const int KB = a.heads * (HD / 32);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int dim = j * 128 + warp * 32 + lane;
+      const bool roped = dim >= r0;                       // warp-uniform (r0 is a multiple of 32)
+      float2 c2 = make_float2(1.f, 0.f);
+      if (roped) c2 = a.rope[(size_t)row * a.rope_stride + ((dim - r0) >> 1)];
+#pragma unroll
+      for (int c0 = 0; c0 < NH; c0 += 16) {
+        uint32_t v[16];
+        tc_ld16(t_o + lane_base + j * NH + c0, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int ghead = hg * NH + c0 + i;
+          float o = bfr(__uint_as_float(v[i]) * S.fac[c0 + i]);
+          if (roped) {        // pairs (2p, 2p+1) sit in neighbouring lanes
+            const float other = __shfl_xor_sync(0xffffffffu, o, 1);
+            o = (lane & 1) ? bfr(-other * c2.y + o * c2.x) : bfr(o * c2.x + other * c2.y);
+          }
+          if (ghead >= a.heads) continue;                  // uniform over the CTA
+          a.out[((size_t)row * a.heads + ghead) * HD + dim] = __float2bfloat16_rn(o);
+          if (a.out_q) {
+            const float amax = warp_max(fabsf(o));
+            const uint8_t sc = act_scale_code_fp8(amax);
+            const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+            const uint8_t hi = enc_e4m3(o * inv);
+            const uint8_t lo = enc_e4m3((o * inv - e4m3_to_f32(hi)) * 16.f);
+            const size_t c = (size_t)ghead * HD + dim;
+            a.out_q[(size_t)row_hi * Wd + c] = hi;
+            a.out_q[(size_t)row_lo * Wd + c] = lo;
+            if (lane == 0) {
+              const int kb = ghead * (HD / 32) + (dim >> 5);
+              a.out_atom[sf_offset(row_hi, kb, KB)] = sc;
+              a.out_atom[sf_offset(row_lo, kb, KB)] = sc >= 4 ? (uint8_t)(sc - 4) : (uint8_t)0;
+            }
+          }
+        }
+      }
+    }
+  } else if (tid == 0) {
+    status_set(a.status, ST_TIMEOUT, 50, blockIdx.x, blockIdx.y);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+}  // namespace sfb
+
+using namespace sfb;
+
+extern "C" {
+
+// Same arguments as sfb_attn_rows_range plus the layout of the two-term copy (pair_block) and the status word.
+// hd must be 512; rd a multiple of 32.  Heads are processed in groups of 32 (16 when the rank holds at most 16).
+int sfb_attn_tc(const void* q, int64_t q_stride, const void* rope, int rope_stride, const int* row_lane, const int* row_pos,
+                const void* win_q, const void* win_s, int64_t win_lane_q, int64_t win_lane_s, const void* ckv_q, const void* ckv_s,
+                int64_t ckv_lane_q, int64_t ckv_lane_s, const int* sel, const int* sel_count, int K, const float* sink, void* out,
+                void* out_q, void* out_atom, int pair_block, int n, int heads, int hd, int rd, int window, int ring, float scale,
+                const int* win_lo, const int* win_hi, void* status, cudaStream_t stream) {
+  if (hd != atc::HD || rd % 32 || rd > hd || n < 1 || heads < 1 || (q_stride % 8)) return (int)cudaErrorInvalidValue;
+  AttnTcArgs a{};
+  a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride; a.rope = (const float2*)rope; a.rope_stride = rope_stride;
+  a.row_lane = row_lane; a.row_pos = row_pos; a.win_q = (const uint8_t*)win_q; a.win_s = (const uint8_t*)win_s;
+  a.win_lane_q = win_lane_q; a.win_lane_s = win_lane_s; a.ckv_q = (const uint8_t*)ckv_q; a.ckv_s = (const uint8_t*)ckv_s;
+  a.ckv_lane_q = ckv_lane_q; a.ckv_lane_s = ckv_lane_s; a.sel = sel; a.sel_count = sel_count; a.K = K; a.sink = sink;
+  a.out = (__nv_bfloat16*)out; a.out_q = (uint8_t*)out_q; a.out_atom = (uint8_t*)out_atom; a.pair_block = pair_block;
+  a.n = n; a.heads = heads; a.rd = rd; a.window = window; a.ring = ring; a.scale = scale; a.win_lo = win_lo; a.win_hi = win_hi;
+  a.status = (Status*)status;
+  cudaError_t rc;
+  if (heads <= 16) {
+    const size_t smem = sizeof(AttnTcSmem<16>) + 1024;
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(attn_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+    rc = sfb_launch(attn_tc_kernel<16>, dim3(1, n), dim3(atc::THREADS), smem, stream, a);
+  } else {
+    const size_t smem = sizeof(AttnTcSmem<32>) + 1024;
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(attn_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+    rc = sfb_launch(attn_tc_kernel<32>, dim3((heads + 31) / 32, n), dim3(atc::THREADS), smem, stream, a);
+  }
+  return (int)rc;
+}
+
+}  // extern "C"

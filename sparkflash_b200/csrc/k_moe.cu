@@ -331,10 +331,10 @@ struct MoePlanArgs {
 __global__ void __launch_bounds__(512) moe_plan_kernel(MoePlanArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ int plan_sm[];     // cnt[E] | base[E + 1]
-  int* cnt = plan_sm; int* base = plan_sm + a.E;
+  extern __shared__ int plan_sm[];     // cnt[E] | base[E + 1] | fill[E]
+  int* cnt = plan_sm; int* base = plan_sm + a.E; int* fill = plan_sm + 2 * a.E + 1;
   const int P = a.n * a.k;
-  for (int i = threadIdx.x; i < a.E; i += blockDim.x) cnt[i] = 0;
+  for (int i = threadIdx.x; i < a.E; i += blockDim.x) { cnt[i] = 0; fill[i] = 0; }
   for (int i = threadIdx.x; i < a.S; i += blockDim.x) { a.seg_expert[i] = -1; a.seg_count[i] = 0; }
   for (int i = threadIdx.x; i < a.S * 16; i += blockDim.x) { a.seg_token[i] = -1; a.seg_weight[i] = 0.f; }
   for (int i = threadIdx.x; i < a.n * (a.k + 1); i += blockDim.x) a.pair_pos[i] = -1;
@@ -353,8 +353,14 @@ __global__ void __launch_bounds__(512) moe_plan_kernel(MoePlanArgs a) {
   for (int p = threadIdx.x; p < P; p += blockDim.x) {
     const int e = a.ids[p];
     if (e < 0 || e >= a.E) continue;
-    int r = 0;                          // rank among the earlier pairs of the same expert: the order inside a segment is the pair order
-    for (int q = 0; q < p; ++q) r += a.ids[q] == e;
+    int r = 0;
+    if (P <= 1024) {                    // rank among the earlier pairs of the same expert: the order inside a segment is the pair order
+      for (int q = 0; q < p; ++q) r += a.ids[q] == e;
+    } else {
+      // many pairs: take the next free place of the expert instead of counting the earlier pairs.  A pair is its own
+      // accumulator column wherever it sits, so the place changes no result
+      r = cnt[e] - 1 - atomicAdd(&fill[e], 1);
+    }
     const int seg = base[e] + r / 16, slot = seg * 16 + (r & 15);
     if (seg < a.S) {
       a.seg_token[slot] = p / a.k; a.seg_weight[slot] = a.wts[p];
@@ -465,7 +471,7 @@ extern "C" int sfb_moe_plan(const void* ids, const void* wts, int n, int k, int 
   if (E > 4096) return (int)cudaErrorInvalidValue;
   sfb::MoePlanArgs a{(const int*)ids, (const float*)wts, n, k, E, shared, S, (int*)seg_expert, (int*)seg_count, (float*)seg_weight,
                      (int*)seg_token, (int*)pair_pos};
-  return (int)sfb::sfb_launch(sfb::moe_plan_kernel, dim3(1), dim3(512), (size_t)(2 * E + 1) * sizeof(int), stream, a);
+  return (int)sfb::sfb_launch(sfb::moe_plan_kernel, dim3(1), dim3(512), (size_t)(3 * E + 1) * sizeof(int), stream, a);
 }
 extern "C" int sfb_moe_permute(const void* xq, const void* xs, const void* seg_token, void* xperm, void* seg_atoms, int slots, int d,
                                int atom_set_bytes, cudaStream_t stream) {

@@ -176,10 +176,12 @@ struct CoefArgs {
   float* coef;                   // [n, coef_stride]
   int n, hc, d, mix, iters;
   float norm_eps, hc_eps;
+  int rb;                        // rows per block
 };
 
 __global__ void __launch_bounds__(COEF_THREADS) seam_coef_kernel(CoefArgs a) {
-  const int row = blockIdx.y;
+  // a block owns 32 columns of the flattened row for `rb` consecutive rows: its slice of the predictor matrix is loaded
+  // once and stays in registers while the rows stream through (many-row steps would otherwise re-read it per row)
   const int lcol = threadIdx.x & (COEF_COLS - 1);
   const int part = threadIdx.x / COEF_COLS;  // = warp
   const int col = blockIdx.x * COEF_COLS + lcol;
@@ -188,90 +190,98 @@ __global__ void __launch_bounds__(COEF_THREADS) seam_coef_kernel(CoefArgs a) {
   __shared__ float tot[1 + MAX_MIX];
   __shared__ int is_last;
   const bool live = col < d;
-  float x[MAX_HC];
-  float ss = 0.f;
-#pragma unroll
-  for (int c = 0; c < MAX_HC; ++c) {
-    x[c] = (live && c < hc) ? bf16_to_f(a.h[((size_t)row * hc + c) * d + col]) : 0.f;
-    ss += x[c] * x[c];
-  }
   const int mq = (a.mix + COEF_PARTS - 1) / COEF_PARTS;
-  float dots[MAX_MQ];
+  float fv[MAX_MQ][MAX_HC];
 #pragma unroll
   for (int i = 0; i < MAX_MQ; ++i) {
-    dots[i] = 0.f;
     const int m = part * mq + i;
-    if (i < mq && m < a.mix && live) {
-      const float* f = a.fn + (size_t)m * hc * d + col;
+#pragma unroll
+    for (int c = 0; c < MAX_HC; ++c)
+      fv[i][c] = (i < mq && m < a.mix && live && c < hc) ? a.fn[((size_t)m * hc + c) * d + col] : 0.f;
+  }
+  const int row_end = min(a.n, (int)(blockIdx.y + 1) * a.rb);
+  for (int row = blockIdx.y * a.rb; row < row_end; ++row) {
+    float x[MAX_HC];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAX_HC; ++c) {
+      x[c] = (live && c < hc) ? bf16_to_f(a.h[((size_t)row * hc + c) * d + col]) : 0.f;
+      ss += x[c] * x[c];
+    }
+    float dots[MAX_MQ];
+#pragma unroll
+    for (int i = 0; i < MAX_MQ; ++i) {
+      dots[i] = 0.f;
 #pragma unroll
       for (int c = 0; c < MAX_HC; ++c)
-        if (c < hc) dots[i] += f[(size_t)c * d] * x[c];
+        if (c < hc) dots[i] += fv[i][c] * x[c];
     }
-  }
 #pragma unroll
-  for (int i = 0; i < MAX_MQ; ++i) dots[i] = warp_sum(dots[i]);
-  ss = warp_sum(ss);
-  if (lane == 0) {
+    for (int i = 0; i < MAX_MQ; ++i) dots[i] = warp_sum(dots[i]);
+    ss = warp_sum(ss);
+    if (lane == 0) {
 #pragma unroll
-    for (int i = 0; i < MAX_MQ; ++i) red[part][i] = dots[i];
-    red[part][MAX_MQ] = ss;
-  }
-  __syncthreads();
-  const int nv = 1 + a.mix;
-  float* out = a.partials + ((size_t)row * gridDim.x + blockIdx.x) * nv;
-  if (threadIdx.x < a.mix) out[1 + threadIdx.x] = red[threadIdx.x / mq][threadIdx.x % mq];
-  if (threadIdx.x == 32) out[0] = red[0][MAX_MQ];
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int prev = atomicAdd(&a.tickets[row], 1u);
-    is_last = prev == gridDim.x - 1;
-    if (is_last) a.tickets[row] = 0;
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  {  // totals in a fixed order (independent of which block runs the tail)
-    const int w = threadIdx.x >> 5;
-    for (int v = w; v < nv; v += 8) {
-      const float* p = a.partials + (size_t)row * gridDim.x * nv + v;
-      float s = 0.f;
-      for (int b = lane; b < (int)gridDim.x; b += 32) s += __ldcg(p + (size_t)b * nv);
-      s = warp_sum(s);
-      if (lane == 0) tot[v] = s;
+      for (int i = 0; i < MAX_MQ; ++i) red[part][i] = dots[i];
+      red[part][MAX_MQ] = ss;
     }
-  }
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    // lanes 0..hc*hc-1 own comb[j][k]; lanes < hc also own pre/post
-    const float rs = rsqrtf(tot[0] / (float)(hc * d) + a.norm_eps);
-    float* cp = a.coef + (size_t)row * coef_stride(hc);
-    if (lane < hc) {
-      float m0 = tot[1 + lane] * rs, m1 = tot[1 + hc + lane] * rs;
-      cp[lane] = 1.f / (1.f + expf(-(m0 * a.hc_scale[0] + a.hc_base[lane]))) + a.hc_eps;
-      cp[hc + lane] = 2.f / (1.f + expf(-(m1 * a.hc_scale[1] + a.hc_base[hc + lane])));
+    __syncthreads();
+    const int nv = 1 + a.mix;
+    float* out = a.partials + ((size_t)row * gridDim.x + blockIdx.x) * nv;
+    if (threadIdx.x < a.mix) out[1 + threadIdx.x] = red[threadIdx.x / mq][threadIdx.x % mq];
+    if (threadIdx.x == 32) out[0] = red[0][MAX_MQ];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int prev = atomicAdd(&a.tickets[row], 1u);
+      is_last = prev == gridDim.x - 1;
+      if (is_last) a.tickets[row] = 0;
     }
-    const int nel = hc * hc;
-    const bool on = lane < nel;
-    float v = on ? tot[1 + 2 * hc + lane] * rs * a.hc_scale[2] + a.hc_base[2 * hc + lane] : -1e30f;
-    float mx = v;
-    for (int o = 1; o < hc; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float e = on ? expf(v - mx) : 0.f;
-    float rsum = e;
-    for (int o = 1; o < hc; o <<= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
-    float c = e / rsum + a.hc_eps;
-    float csum = c;
-    for (int o = hc; o < nel; o <<= 1) csum += __shfl_xor_sync(0xffffffffu, csum, o);
-    c = c / (csum + a.hc_eps);
-    for (int it = 1; it < a.iters; ++it) {
-      float r2 = c;
-      for (int o = 1; o < hc; o <<= 1) r2 += __shfl_xor_sync(0xffffffffu, r2, o);
-      c = c / (r2 + a.hc_eps);
-      float c2 = c;
-      for (int o = hc; o < nel; o <<= 1) c2 += __shfl_xor_sync(0xffffffffu, c2, o);
-      c = c / (c2 + a.hc_eps);
+    __syncthreads();
+    if (!is_last) continue;
+    __threadfence();
+    {  // totals in a fixed order (independent of which block runs the tail)
+      const int w = threadIdx.x >> 5;
+      for (int v = w; v < nv; v += 8) {
+        const float* p = a.partials + (size_t)row * gridDim.x * nv + v;
+        float s = 0.f;
+        for (int b = lane; b < (int)gridDim.x; b += 32) s += __ldcg(p + (size_t)b * nv);
+        s = warp_sum(s);
+        if (lane == 0) tot[v] = s;
+      }
     }
-    if (on) cp[2 * hc + lane] = c;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      // lanes 0..hc*hc-1 own comb[j][k]; lanes < hc also own pre/post
+      const float rs = rsqrtf(tot[0] / (float)(hc * d) + a.norm_eps);
+      float* cp = a.coef + (size_t)row * coef_stride(hc);
+      if (lane < hc) {
+        float m0 = tot[1 + lane] * rs, m1 = tot[1 + hc + lane] * rs;
+        cp[lane] = 1.f / (1.f + expf(-(m0 * a.hc_scale[0] + a.hc_base[lane]))) + a.hc_eps;
+        cp[hc + lane] = 2.f / (1.f + expf(-(m1 * a.hc_scale[1] + a.hc_base[hc + lane])));
+      }
+      const int nel = hc * hc;
+      const bool on = lane < nel;
+      float v = on ? tot[1 + 2 * hc + lane] * rs * a.hc_scale[2] + a.hc_base[2 * hc + lane] : -1e30f;
+      float mx = v;
+      for (int o = 1; o < hc; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float e = on ? expf(v - mx) : 0.f;
+      float rsum = e;
+      for (int o = 1; o < hc; o <<= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
+      float c = e / rsum + a.hc_eps;
+      float csum = c;
+      for (int o = hc; o < nel; o <<= 1) csum += __shfl_xor_sync(0xffffffffu, csum, o);
+      c = c / (csum + a.hc_eps);
+      for (int it = 1; it < a.iters; ++it) {
+        float r2 = c;
+        for (int o = 1; o < hc; o <<= 1) r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+        c = c / (r2 + a.hc_eps);
+        float c2 = c;
+        for (int o = hc; o < nel; o <<= 1) c2 += __shfl_xor_sync(0xffffffffu, c2, o);
+        c = c / (c2 + a.hc_eps);
+      }
+      if (on) cp[2 * hc + lane] = c;
+    }
+    __syncthreads();   // the tail's shared totals are not overwritten while a lane still reads them
   }
 }
 
@@ -310,9 +320,10 @@ int sfb_seam_coef(const void* h, const float* fn, const float* hc_scale, const f
                   unsigned int* tickets, float* coef_out, int n, int hc, int d, int iters, float norm_eps,
                   float hc_eps, cudaStream_t stream) {
   if (hc > MAX_HC || (hc & (hc - 1)) || !tickets) return (int)cudaErrorInvalidValue;
+  const int rb = n <= 32 ? 1 : (n <= 256 ? 4 : 16);
   CoefArgs a{(const __nv_bfloat16*)h, fn, hc_scale, hc_base, partials, tickets, coef_out, n, hc, d, (2 + hc) * hc,
-             iters, norm_eps, hc_eps};
-  seam_coef_kernel<<<dim3(sfb_seam_nblk(d), n), COEF_THREADS, 0, stream>>>(a);
+             iters, norm_eps, hc_eps, rb};
+  seam_coef_kernel<<<dim3(sfb_seam_nblk(d), (n + rb - 1) / rb), COEF_THREADS, 0, stream>>>(a);
   return SFB_CHECK_LAUNCH();
 }
 

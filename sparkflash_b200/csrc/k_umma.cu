@@ -104,6 +104,13 @@ __device__ __forceinline__ void tc_mma_bs(uint32_t d, uint64_t adesc, uint64_t b
       "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
 }
+// bf16 x bf16 -> fp32, operands from shared memory (no block scales)
+__device__ __forceinline__ void tc_mma_f16(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -137,6 +144,20 @@ __host__ __device__ inline uint32_t make_idesc(int a_fmt, int b_fmt, int M, int 
   return d;
 }
 
+// instruction descriptor for kind::f16 with bf16 operands and an fp32 accumulator: accumulator format F32 = 1 at bits 4-5,
+// operand formats BF16 = 1 at bits 7-9 / 10-12, both operands K-major (bits 15, 16 clear), N/8 at 17-22, M/16 at 24-28.
+// a_mn != 0 marks the A operand as MN-major (bit 15).
+__host__ __device__ inline uint32_t make_idesc_bf16(int M, int N, int a_mn = 0) {
+  uint32_t d = 0;
+  d |= 1u << 4;
+  d |= 1u << 7;
+  d |= 1u << 10;
+  d |= (uint32_t)(a_mn & 1) << 15;
+  d |= (uint32_t)((N >> 3) & 63) << 17;
+  d |= (uint32_t)((M >> 4) & 31) << 24;
+  return d;
+}
+
 enum UmmaMode : int { UM_DENSE = 0, UM_DOWN = 2, UM_DOWN_GROUPED = 3 };
 
 struct UmmaArgs {
@@ -151,6 +172,7 @@ struct UmmaArgs {
   int n;                      // valid token rows (dense); number of tokens = gridDim.z (MoE)
   int K;                      // reduction length per item
   int a_fp4;                  // format of tmapA (tmapA2 is always FP8)
+  int bf16;                   // dense mode: both operands are bf16 (K counts bytes: two per element), no block scales
   int mode;
   // dense / grouped
   int N;                      // output columns per group
@@ -276,22 +298,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     w.b_x0 = g * a.K + w.ks0 * UM_BK; w.b_row0 = 0;
     w.sfb = a.sfb + ((size_t)(g * ksteps + w.ks0)) * 512;
     w.split = blockIdx.y; w.splits = a.splits;
-    w.tile_id = g * gridDim.x + tile; w.tiles_total = gridDim.x * gridDim.z;
+    w.tile_id = blockIdx.z * gridDim.x + tile; w.tiles_total = gridDim.x * gridDim.z;
     w.out_row0 = 0; w.n_valid = a.n; w.col0 = w.a_row0; w.col_limit = (g + 1) * a.N;
     if (BULK) {
       w.b_row0 = tok_tile * NP; w.out_row0 = tok_tile * NP;
       w.n_valid = min(NP, a.n - tok_tile * NP);
       w.sfb = a.sfb + ((size_t)((tok_tile * NP) >> 7) * a.katoms_b + g * ksteps + w.ks0) * 512;
+      if (a.pair > 0) {   // two-term activations in blocks: tile = `pair` hi rows then `pair` lo rows; a.n counts logical rows
+        w.out_row0 = tok_tile * a.pair;
+        w.n_valid = min(a.pair, a.n - tok_tile * a.pair);
+      }
     }
     // dense weights and their scales do not depend on the previous kernel: request the first stages' weight tiles now, so
     // that their fetch overlaps the predecessor's tail; the activation tiles follow after the wait
     if (warp == 0 && lane == 0) {
-      const uint32_t stage_tx = (w.a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 1024;
+      const uint32_t stage_tx = (w.a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + (a.bf16 ? 0 : 1024);
       pre = w.nks < UM_STAGES ? w.nks : UM_STAGES;
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&S.full[i], stage_tx);
         tma_load_2d(S.a[i][0], w.ma, (w.ks0 + i) * UM_BK, w.a_row0, &S.full[i]);
-        bulk_load(S.sfa[i][0], w.sfa + (size_t)i * 512, 512, &S.full[i]);
+        if (!a.bf16) bulk_load(S.sfa[i][0], w.sfa + (size_t)i * 512, 512, &S.full[i]);
       }
     }
   }
@@ -339,7 +365,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     w.out_row0 = tok; w.n_valid = 1; w.col0 = tile * 128; w.col_limit = a.d;
   }
   // bytes TMA reports per stage: packed FP4 counts 4 bits per element although it lands in 8-bit containers
-  const uint32_t STAGE_TX = (w.a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 1024;
+  const uint32_t STAGE_TX = (w.a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + (a.bf16 ? 0 : 1024);
   const uint32_t tmem = S.tmem_base;
   const uint32_t t_acc = tmem;               // NP fp32 columns
   const uint32_t t_sfa = tmem + NP;          // 2 x 4 columns
@@ -374,9 +400,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           bulk_load(S.sfb[s], a.sfb_maps[owner] + ((size_t)(w.b_row0 >> 7) * (a.b_k_per_map / UM_BK) + kl / UM_BK) * 512, 512, &S.full[s]);
         } else {
           tma_load_2d(S.b[s], &tmapB, w.b_x0 + i * UM_BK, w.b_row0, &S.full[s]);
-          bulk_load(S.sfb[s], w.sfb + (size_t)i * 512, 512, &S.full[s]);
+          if (!a.bf16) bulk_load(S.sfb[s], w.sfb + (size_t)i * 512, 512, &S.full[s]);
         }
-        if (i >= pre) bulk_load(S.sfa[s][0], w.sfa + (size_t)i * 512, 512, &S.full[s]);
+        if (i >= pre && !a.bf16) bulk_load(S.sfa[s][0], w.sfa + (size_t)i * 512, 512, &S.full[s]);
       }
     }
   } else if (warp == 1) {
@@ -387,9 +413,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         if (!mbar_wait(&S.full[s], (i / UM_STAGES) & 1)) { S.fail = 2; break; }
         tc_fence_after();
         const uint32_t sf_slot = (uint32_t)(i & 1) * 4;
+        const uint32_t a_addr = smem_u32(S.a[s][0]), b_addr = smem_u32(S.b[s]);
+        if (a.bf16) {
+          // a 128-byte stage row holds 64 bf16 elements = four K = 16 steps of 32 bytes
+          const uint32_t idb = make_idesc_bf16(128, NP);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            tc_mma_f16(t_acc, make_desc(a_addr + kk * 32, 1024, 16, 2), make_desc(b_addr + kk * 32, 1024, 16, 2), idb,
+                       (i > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(&S.empty[s]);
+          continue;
+        }
         tc_cp_sf(t_sfa + sf_slot, make_desc(smem_u32(S.sfa[s][0]), 128, 0, 0));
         tc_cp_sf(t_sfb + sf_slot, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
-        const uint32_t a_addr = smem_u32(S.a[s][0]), b_addr = smem_u32(S.b[s]);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const uint64_t ad = make_desc(a_addr + kk * 32, 1024, 16, 2);
@@ -412,7 +448,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     const size_t lane_off = ((size_t)w.tile_id * 128 + q * 32 + lane) * NP;
     const size_t split_stride = (size_t)w.tiles_total * 128 * NP;
     float* part = a.scratch ? a.scratch + (size_t)w.split * split_stride + lane_off : nullptr;
-    const int nv = a.pair > 0 ? a.pair : w.n_valid;
+    const int nv = (a.pair > 0 && !BULK) ? a.pair : w.n_valid;
     // bulk shapes: the bf16 tile is staged token-major in the (now idle) operand stages and leaves the SM as
     // 256-byte bulk copies, one per token row and destination - element stores to a peer serialise on NVLink
     const bool staged = BULK && a.pair == 0 && !a.out_f && !a.out_q && (a.out_b || a.n_peers > 0) &&
@@ -992,6 +1028,48 @@ int sfb_umma_dense_pair(const void* tmapA, const void* tmapB, const void* sfa, i
   a.splits = splits; a.scratch = scratch; a.tickets = tickets; a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f;
   a.out_stride = out_stride; a.out_q = (uint8_t*)out_q; a.out_q_atom = (uint8_t*)out_q_atom; a.status = (Status*)status;
   return launch_umma(tmapA, nullptr, tmapB, a, dim3(N / 128, splits, groups), NP, stream);
+}
+
+// Two-term activations for any number of rows: the activation buffer holds blocks of 128 rows, each = 64 hi rows then 64 lo
+// rows of 64 consecutive logical rows (scale atoms: one 128-row atom block per block); out row = logical row.
+int sfb_umma_pair_bulk(const void* tmapA, const void* tmapB, const void* sfa, int katoms_a, const void* sfb, int katoms_b,
+                       int n_rows, int N, int K, int groups, int splits, float* scratch, unsigned int* tickets, void* out_b,
+                       float* out_f, int64_t out_stride, void* out_q, void* out_q_atom, void* status, cudaStream_t stream) {
+  if (N % 128 || K % UM_BK || n_rows < 1 || splits < 1 || splits > K / UM_BK || !scratch || !tickets) return refuse_args();
+  UmmaArgs a{};
+  a.sfa = (const uint8_t*)sfa; a.katoms_a = katoms_a; a.sfb = (const uint8_t*)sfb; a.katoms_b = katoms_b;
+  a.n = n_rows; a.pair = 64; a.K = K; a.mode = UM_DENSE; a.N = N; a.groups = groups; a.splits = splits;
+  a.scratch = scratch; a.tickets = tickets; a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f; a.out_stride = out_stride;
+  a.out_q = (uint8_t*)out_q; a.out_q_atom = (uint8_t*)out_q_atom; a.status = (Status*)status;
+  a.force_bulk = 1;
+  a.tok_tiles = (n_rows + 63) / 64;
+  return launch_umma(tmapA, nullptr, tmapB, a, dim3(N / 128, splits, groups * a.tok_tiles), 128, stream);
+}
+
+// bf16 x bf16 -> fp32 GEMM (kind::f16): out[token, col] = sum_k W[col, k] X[token, k], both operands bf16 row-major.  The
+// tensor maps are byte maps (sfb_tmap_encode with K = row_bytes = 2 * elements, fp4 = 0).  Any number of token rows
+// (tiles of 128 when n > NP); split-K partials are added in split order.
+int sfb_umma_bf16(const void* tmapA, const void* tmapB, int n, int NP, int N, int K_elems, int splits, float* scratch,
+                  unsigned int* tickets, void* out_b, float* out_f, int64_t out_stride, void* status, cudaStream_t stream) {
+  const int K = 2 * K_elems;
+  const int tok_tiles = (n + NP - 1) / NP;
+  if (K % UM_BK || n < 1 || splits < 1 || splits > K / UM_BK || (tok_tiles > 1 && NP != 128)) return refuse_args();
+  if (splits > 1 && (!scratch || !tickets)) return refuse_args();
+  UmmaArgs a{};
+  a.bf16 = 1; a.n = n; a.K = K; a.mode = UM_DENSE; a.N = N; a.groups = 1; a.splits = splits; a.scratch = scratch; a.tickets = tickets;
+  a.out_b = (__nv_bfloat16*)out_b; a.out_f = out_f; a.out_stride = out_stride; a.status = (Status*)status;
+  const int tiles = (N + 127) / 128;
+  if (tok_tiles > 1) {
+    a.force_bulk = 1; a.tok_tiles = tok_tiles;
+    return launch_umma(tmapA, nullptr, tmapB, a, dim3(tiles, splits, tok_tiles), NP, stream);
+  }
+  a.defer_reduce = (splits > 1 && NP >= 32 && g_push.n == 0) ? 1 : 0;
+  const int rc = launch_umma(tmapA, nullptr, tmapB, a, dim3(tiles, splits, 1), NP, stream);
+  if (rc != 0 || !a.defer_reduce) return rc;
+  SplitReduceArgs r{};
+  r.scratch = scratch; r.splits = splits; r.tiles_total = tiles; r.tiles_per_group = tiles; r.NP = NP; r.n = n;
+  r.N = N; r.out_b = (__nv_bfloat16*)out_b; r.out_f = out_f; r.out_stride = out_stride;
+  return (int)sfb_launch(splitk_reduce_kernel, dim3(tiles, (n + 3) / 4), dim3(128), 0, stream, r);
 }
 
 // MoE gate/up for n_tok tokens: tmapA = routed w13 [E*2*inter, d] (FP4), tmapA2 = shared [2*inter, d] (FP8, may be

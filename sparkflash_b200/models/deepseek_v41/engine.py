@@ -134,6 +134,7 @@ class Engine:
         self.supports_vision = vision
         self.supports_headless = True    # step(head=False) for prompt chunks whose rows are not sampled
         self.group_moe = True        # rows steps of 4+ rows run the experts grouped by expert (same bits, fewer weight reads)
+        self.bulk_attention = True   # rows steps of 65+ rows run attention on tcgen05 (csrc/k_attn_tc.cu)
         self.drafter = bool(drafter and weights.mtp_layers)
         self.kv = KVCache(cfg, max_lanes, max_context, max_rows, self.dev, lane_budget_bytes, draft_stages=self.drafter)
         R, d, hc, hd, q = max_rows, cfg.hidden_size, cfg.hc_mult, cfg.head_dim, cfg.q_lora_rank
@@ -212,6 +213,7 @@ class Engine:
             self.tcl = TC.attach(weights, synthetic=synthetic_scales)
             self.tcb = TC.TcBuffers(self)
             self._splits = TC.pick_splits
+            self._splits_bulk = TC.pick_splits_bulk
         elif arm != "cuda":
             raise ValueError(f"unknown arm {arm!r}")
         self.engram = engram          # engram.runtime.EngramRuntime or None
@@ -223,7 +225,7 @@ class Engine:
             self.eg_ids_host = torch.zeros((ne, R, cols), dtype=torch.int64).pin_memory()
             self.eg_rows = e((R, Ke), bf)
             self.eg_q = torch.zeros((R, Ke), dtype=torch.uint8, device=dev)
-            self.eg_atom = torch.full((CC.sf_bytes(128, Ke // 32),), 127, dtype=torch.uint8, device=dev)
+            self.eg_atom = torch.full((CC.sf_bytes(max(128, R), Ke // 32),), 127, dtype=torch.uint8, device=dev)
             self.eg_kv = e((R, (cfg.hc_mult + 1) * d), bf)
         if self.drafter:
             if arm != "tc":
@@ -235,10 +237,10 @@ class Engine:
             self.T_main = TC._matrix(weights.mtp_main_proj, weights.mtp_main_proj_sf, d, K3, False, 115 if synthetic_scales else None)
             u8 = dict(dtype=torch.uint8, device=dev)
             self.taps_q = torch.zeros((R, K3), **u8)
-            self.taps_atom = torch.full((CC.sf_bytes(128, K3 // 32),), 127, **u8)
+            self.taps_atom = torch.full((CC.sf_bytes(max(128, R), K3 // 32),), 127, **u8)
             self.main_raw, self.main_x = e((R, d), bf), e((R, d), bf)
             self.main_xq = torch.zeros((R, d), **u8)
-            self.main_atom = torch.full((CC.sf_bytes(128, d // 32),), 127, **u8)
+            self.main_atom = torch.full((CC.sf_bytes(max(128, R), d // 32),), 127, **u8)
             self.rope_identity = torch.zeros((R, cfg.rope_dim // 2, 2), dtype=torch.float32, device=dev)
             self.rope_identity[..., 0] = 1.0
             self.draft_lo, self.draft_hi = e((R,), i32), e((R,), i32)
@@ -340,6 +342,18 @@ class Engine:
                   out_q_atom=None):
         """One projection on the tensor-core arm: M = TcMatrix, xq_buf = FP8 activation codes [x_rows, K*groups]."""
         tcb = self.tcb
+        if n > 128 and not pair:
+            # many rows: tiles of 128 token rows through the staged-epilogue kernel; the activation scale atoms are in the
+            # standard layout (one 128-row atom block per 128 rows)
+            if groups != 1 or out_q is not None:
+                raise ValueError("grouped / re-quantising projections take at most 128 rows per launch")
+            tb = tcb.bmap(xq_buf, x_rows, K, 128)
+            tiles = ((N_ + 127) // 128) * ((n + 127) // 128)
+            splits = self._splits_bulk(tiles, K // 128)
+            N.umma_bulk(M.tmap, tb, M.atoms, atoms, n, N_, K, splits=splits, scratch=tcb.scratch, tickets=tcb.tickets,
+                        out_b=out_b, out_stride=out_stride if out_stride is not None else N_, status=self.status)
+            self._k()
+            return
         NP = N.umma_np(2 * pair if pair else n)
         tb = tcb.bmap(xq_buf, x_rows, K * groups, NP)
         tiles = groups * ((N_ + 127) // 128)
@@ -398,8 +412,14 @@ class Engine:
         else:
             N.gemv(N.WF_FP8, L.wqkv_a, L.wqkv_a_sf, d, q + hd, d, n, xq=self.xq, xs=self.xs, out_b=self.qkv_raw); self._k()
         if L.aux_w is not None:
-            N.gemv(N.WF_BF16, L.aux_w, None, 2 * d, L.aux_rows, d, n, xb=self.xn, out_f=self.aux_raw,
-                   out_stride=self.aux_raw.stride(0)); self._k()
+            if n > 128 and self.tcb is not None:
+                ta, tbx = self._bf16_map(L.aux_w, L.aux_rows, d), self._bf16_map(self.xn, self.max_rows, d)
+                tiles = ((L.aux_rows + 127) // 128) * ((n + 127) // 128)
+                N.umma_bf16(ta, tbx, n, L.aux_rows, d, splits=self._splits_bulk(tiles, d // 64), scratch=self.tcb.scratch,
+                            tickets=self.tcb.tickets, out_f=self.aux_raw, out_stride=self.aux_raw.stride(0), status=self.status); self._k()
+            else:
+                N.gemv(N.WF_BF16, L.aux_w, None, 2 * d, L.aux_rows, d, n, xb=self.xn, out_f=self.aux_raw,
+                       out_stride=self.aux_raw.stride(0)); self._k()
         N.qkv_post(self.qkv_raw, L.q_norm, L.kv_norm, invf, self.row_lane, self.row_pos, self.qr_q, self.qr_s,
                    kv.win_q[l], kv.win_s[l], n, q, hd, rd, kv.ring, cfg.norm_eps,
                    qr_atom=self.tcb.qr_atom if T is not None else None); self._k()
@@ -444,6 +464,22 @@ class Engine:
         # The two-term (hi | lo) copy of the attention output fills a 128-row activation tile with 64 rows, so steps of more than
         # 64 rows run the attention kernel and the two output projections once per block of 64 rows, each block with its own
         # rows of the staging buffers and its own scale-atom block; everything before (and the expert pass after) sees all rows.
+        if n > 64 and tc_wo_a and tc_wo_b and hd == 512 and self.bulk_attention:
+            # many rows: attention on tcgen05 (a tolerance arm: the probabilities enter the value contraction as bf16), its
+            # two-term FP8 copy in blocks of 64 hi | 64 lo rows, and one launch each for the two output projections
+            tcb = self.tcb
+            N.attn_tc(self.qfull, self.qfull.stride(0), invf, self.row_lane, self.row_pos, kv.win_q[l], kv.win_s[l],
+                      kv.ckv_q[owner] if has_c else None, kv.ckv_s[owner] if has_c else None,
+                      self.sel if has_c else None, self.sel_cnt if has_c else None, cfg.index_topk, L.sink,
+                      self.attn_out, n, self.hl, hd, rd, cfg.window, kv.ring, hd ** -0.5, out_q=tcb.ao_q, out_atom=tcb.ao_atom,
+                      pair_block=64, win_lo=win[0] if win else None, win_hi=win[1] if win else None, status=self.status); self._k()
+            tba = tcb.bmap(tcb.ao_q, 128 * tcb.nblk, self.hl * hd, 128)
+            N.umma_pair_bulk(T.wo_a.tmap, tba, T.wo_a.atoms, tcb.ao_atom, n, ol, gin, groups=self.gl, splits=1,
+                             scratch=tcb.scratch, tickets=tcb.tickets, out_b=self.oa, out_q=tcb.oa_q, out_q_atom=tcb.oa_atom,
+                             status=self.status); self._k()
+            self._pushed = self._arm_push(0, sub)
+            self._tc_dense(T.wo_b, tcb.oa_q, self.max_rows, tcb.oa_atom, n, d, self.gl * ol, self.y_attn)
+            return
         blocks = [(0, n)] if (n <= 64 or not tc_wo_a) else [(r0, min(64, n - r0)) for r0 in range(0, n, 64)]
         # (with the fused collectives, a single block lets the last projection push its output from its epilogue; several
         # blocks leave that to the generic push kernel after the last block, which raises the arrival flag once)
@@ -530,8 +566,17 @@ class Engine:
         draft = T != "auto"
         sub = 2 * l + 1 if sub is None else sub
         ks = self.gate_ksplit
-        N.gemv(N.WF_BF16, L.gate_w, None, 2 * d, E, d, n, xb=self.xn, out_f=self.dots, out_stride=E, ksplit=ks,
-               split_stride=self.dots.stride(0)); self._k()
+        if n > 128 and self.tcb is not None and E == cfg.n_routed_experts:
+            # many rows: the gate dots as a bf16 tensor-core GEMM (bf16 x bf16 products are exact in fp32; only the order of
+            # the fp32 sum differs from the CUDA-core kernel)
+            ks = 1
+            ta, tbx = self._bf16_map(L.gate_w, E, d), self._bf16_map(self.xn, self.max_rows, d)
+            tiles = ((E + 127) // 128) * ((n + 127) // 128)
+            N.umma_bf16(ta, tbx, n, E, d, splits=self._splits_bulk(tiles, d // 64), scratch=self.tcb.scratch,
+                        tickets=self.tcb.tickets, out_f=self.dots[0], out_stride=E, status=self.status); self._k()
+        else:
+            N.gemv(N.WF_BF16, L.gate_w, None, 2 * d, E, d, n, xb=self.xn, out_f=self.dots, out_stride=E, ksplit=ks,
+                   split_stride=self.dots.stride(0)); self._k()
         N.router_topk(self.dots, L.gate_bias, L.gate_bias_vl, self.img_mask, self.ids, self.wts, n, E, k, cfg.route_scale,
                       nsplit=ks, split_stride=self.dots.stride(0)); self._k()
         self._prefetch(n, (), experts=(L.w2, n * k))
@@ -565,6 +610,15 @@ class Engine:
                       n, k, d, self.il, cfg.swiglu_limit); self._k()
         N.moe_down(self.act_q, self.act_s, self.ids, L.w2, L.w2_sf, L.s2, L.s2_sf, self.y_ffn, n, k, d, self.il); self._k()
 
+    def _bf16_map(self, t: torch.Tensor, rows: int, K: int):
+        """Cached tensor map over a row-major bf16 matrix for the bf16 tensor-core GEMM."""
+        maps = self.__dict__.setdefault("_bf16_maps", {})
+        key = (t.data_ptr(), rows, K)
+        m = maps.get(key)
+        if m is None:
+            m = maps[key] = N.bf16_map(t, rows, K, 128)
+        return m
+
     def _fused(self) -> bool:
         return self.world > 1 and self.comm is not None and getattr(self.comm, "name", "") == "fused"
 
@@ -588,11 +642,11 @@ class Engine:
         slots, flags = self.comm.slots(kind)
         return (slots, flags, sub + 1)
 
-    def _forward(self, n: int, len_bucket: int, stop_after: int | None = None):
-        for _ in self._forward_gen(n, len_bucket, stop_after):
+    def _forward(self, n: int, len_bucket: int, stop_after: int | None = None, head_from: int = 0):
+        for _ in self._forward_gen(n, len_bucket, stop_after, head_from):
             pass
 
-    def _forward_gen(self, n: int, len_bucket: int, stop_after: int | None = None):
+    def _forward_gen(self, n: int, len_bucket: int, stop_after: int | None = None, head_from: int = 0):
         """The rows-step forward.  Yields after every point where this rank has published a partial result, so
         that a lockstep driver can interleave several ranks living in one process; a normal run just exhausts it."""
         cfg, w = self.cfg, self.w
@@ -652,10 +706,12 @@ class Engine:
             return
         self._seam(n, k, y_prev, None, None, None, w.norm, quant=False)
         self._dbg("final_x", self.xn, n); self._dbg("final_h", self.h, n)
-        N.gemv(N.WF_BF16, w.head, None, 2 * cfg.hidden_size, self.vl, cfg.hidden_size, n, xb=self.xn,
-               out_f=self.logits); self._k()
-        N.sample(self.logits, self.row_pos, self.temp, self.seed, self.mask, self.best_val[self.rank], self.best_id[self.rank],
-                 n, self.vl, self.rank * self.vl); self._k()
+        # the head and the sampler run on rows head_from .. n-1 only (a prompt's last chunk samples its last row alone)
+        hf, hn = head_from, n - head_from
+        N.gemv(N.WF_BF16, w.head, None, 2 * cfg.hidden_size, self.vl, cfg.hidden_size, hn, xb=self.xn[hf:],
+               out_f=self.logits[hf:]); self._k()
+        N.sample(self.logits[hf:], self.row_pos[hf:], self.temp[hf:], self.seed[hf:], self.mask[hf:] if self.mask is not None else None,
+                 self.best_val[self.rank][hf:], self.best_id[self.rank][hf:], hn, self.vl, self.rank * self.vl); self._k()
         R = self.max_rows
         if fused:
             sub = 2 * len(w.layers)
@@ -866,13 +922,14 @@ class Engine:
 
     def step(self, tokens, lanes, positions, temperature=None, seeds=None, sync: bool = True, masks: dict | None = None,
              image_rows: dict | None = None, filters: dict | None = None, skip_decoder: bool = False,
-             head: bool = True) -> torch.Tensor:
+             head: bool | str = True) -> torch.Tensor:
         """Run one rows step.  ``tokens/lanes/positions`` are host sequences of equal length n.
         Returns the sampled next-token ids as a host int32 tensor [n] (pinned) when ``sync``; the
         device tensor ``tokens_out`` otherwise.
         ``skip_decoder``: run only the layers up to the last cache owner and no head (prefill rows far before the prompt's
         end).  ``head=False``: every layer, but no head and no sampler (a prompt chunk that stops short of the prompt's end).
-        The returned tokens are meaningless in both cases."""
+        The returned tokens are meaningless in both cases.  ``head="last"``: the head and the sampler run on the last row only
+        (the last chunk of a prompt: only out[n-1] is meaningful)."""
         n = len(tokens)
         if not 0 < n <= self.max_rows:
             raise ValueError(f"rows {n} out of range 1..{self.max_rows}")
@@ -909,7 +966,7 @@ class Engine:
         self.temp[:n].copy_(io.temp[:n], non_blocking=True)
         self.seed[:n].copy_(io.seed[:n], non_blocking=True)
         stop_after = self.decoder_skip_layer if skip_decoder else (None if head else len(self.w.layers))
-        self.run_rows(n, self._bucket(int(max(positions))), stop_after)
+        self.run_rows(n, self._bucket(int(max(positions))), stop_after, head_from=n - 1 if head == "last" else 0)
         if not sync:
             return self.tokens_out[:n]
         io.out[:n].copy_(self.tokens_out[:n], non_blocking=True)
@@ -919,22 +976,24 @@ class Engine:
                 io.out[r] = self.filtered_sample(r, top_k, top_p, float(io.temp[r]), int(io.seed[r]), int(io.pos[r]))
         return io.out[:n]
 
-    def run_rows(self, n: int, len_bucket: int, stop_after: int | None = None) -> None:
+    def run_rows(self, n: int, len_bucket: int, stop_after: int | None = None, head_from: int = 0) -> None:
         """Launch (or replay) the forward for the rows already staged in the device input buffers."""
         if not self.use_graphs:
-            self._forward(n, len_bucket, stop_after)
+            self._forward(n, len_bucket, stop_after, head_from)
             return
         key = (n, len_bucket) if stop_after is None else (n, len_bucket, stop_after)
+        if head_from:
+            key = key + ("head_from", head_from)
         g = self.graphs.get(key)
         if g is None:
             # warm-up run outside capture (first-call attribute set-up, lazy module loading)
             self._counting, self.launches_per_step = True, 0
-            self._forward(n, len_bucket, stop_after)
+            self._forward(n, len_bucket, stop_after, head_from)
             self._counting = False
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                self._forward(n, len_bucket, stop_after)
+                self._forward(n, len_bucket, stop_after, head_from)
             self.graphs[key] = g
             # the warm-up run already produced this step's result and advanced the caches; replaying
             # the same rows is idempotent (position-addressed writes), so fall through to one replay
@@ -956,7 +1015,9 @@ class Engine:
         nxt = None
         while pos < len(prompt):
             c = prompt[pos:pos + chunk]
-            r = self.step(c, [lane] * len(c), list(range(pos, pos + len(c))), [temperature] * len(c), [seed] * len(c))
+            # chunks that stop short of the prompt's end are not sampled; the last one samples its last row only
+            r = self.step(c, [lane] * len(c), list(range(pos, pos + len(c))), [temperature] * len(c), [seed] * len(c),
+                          head="last" if pos + len(c) >= len(prompt) else False)
             nxt = int(r[len(c) - 1])
             self.check_status()
             if collect_logits:

@@ -91,12 +91,14 @@ class TcBuffers:
         R, d, q = eng.max_rows, cfg.hidden_size, cfg.q_lora_rank
         u8 = dict(dtype=torch.uint8, device=dev)
         k = cfg.top_k + 1
-        self.xs_atom = torch.full((C.sf_bytes(128, d // 32),), 127, **u8)            # rows = tokens
+        RA = max(128, R)                                                              # atom blocks cover 128 rows each
+        self.xs_atom = torch.full((C.sf_bytes(RA, d // 32),), 127, **u8)             # rows = tokens
         self.xs_atom_tok = torch.full((R, C.sf_bytes(1, d // 32)), 127, **u8)        # one set per token
-        self.qr_atom = torch.full((C.sf_bytes(128, q // 32),), 127, **u8)
+        self.qr_atom = torch.full((C.sf_bytes(RA, q // 32),), 127, **u8)
         ao_k = eng.hl * cfg.head_dim
-        self.ao_q = torch.zeros((2 * R, ao_k), **u8)                                  # attention out, hi | lo
         nblk = max(1, (R + 63) // 64)        # one 128-row scale-atom block per 64 rows of a step (hi | lo fill a block)
+        self.nblk = nblk
+        self.ao_q = torch.zeros((128 * nblk, ao_k), **u8)                             # attention out: per 64 rows, 64 hi | 64 lo
         self.ao_atom_block = C.sf_bytes(128, ao_k // 32)
         self.ao_atom = torch.full((nblk * self.ao_atom_block,), 127, **u8)
         oa_k = eng.gl * cfg.o_lora_rank
@@ -104,14 +106,21 @@ class TcBuffers:
         self.oa_atom_block = C.sf_bytes(128, max(1, oa_k // 32))
         self.oa_atom = torch.full((nblk * self.oa_atom_block,), 127, **u8)
         self.act_sf = torch.full((R * k, C.sf_bytes(1, max(1, eng.il // 32))), 127, **u8)
-        tiles_down = R * ((d + 127) // 128)
+        tiles_down = min(R, 128) * ((d + 127) // 128)
         n_floats = max(tiles_down * k * 128 * 16, 64 * 16 * 128 * 128)
+        pair_tiles = 0
+        if R > 128:
+            # many-row steps: the grouped output projection keeps one fp32 tile per (column tile, group, 64-row block), and
+            # a split dense projection one per (column tile, 128-row tile, split)
+            pair_tiles = ((cfg.o_lora_rank + 127) // 128) * max(1, eng.gl) * nblk
+            dense_tiles = 4 * ((max(d, eng.qfull_w) + 127) // 128) * ((R + 127) // 128)
+            n_floats = max(n_floats, pair_tiles * 128 * 128, dense_tiles * 128 * 128)
         self.scratch = torch.zeros((n_floats,), dtype=torch.float32, device=dev)
-        self.tickets = torch.zeros((max(tiles_down, 4096),), dtype=torch.int32, device=dev)
-        self._maps: dict[tuple[int, int], N.TensorMap] = {}
+        self.tickets = torch.zeros((max(tiles_down, 4096, pair_tiles),), dtype=torch.int32, device=dev)
+        self._maps: dict[tuple[int, int, int], N.TensorMap] = {}
 
     def bmap(self, t: torch.Tensor, rows: int, K: int, box_rows: int) -> N.TensorMap:
-        key = (t.data_ptr(), box_rows)
+        key = (t.data_ptr(), rows, box_rows)
         m = self._maps.get(key)
         if m is None:
             m = N.TensorMap(t, rows, K, K, box_rows)
@@ -122,3 +131,9 @@ class TcBuffers:
 def pick_splits(tiles: int, ksteps: int, target_ctas: int = 296) -> int:
     s = max(1, min(ksteps, target_ctas // max(1, tiles)))
     return s
+
+
+def pick_splits_bulk(tiles: int, ksteps: int) -> int:
+    """Many-row launches (tiles of 128 token rows, two CTAs per SM): split the reduction only while the grid is short of
+    one wave, and never below eight k-steps per CTA."""
+    return max(1, min(4, ksteps // 8, 296 // max(1, tiles)))

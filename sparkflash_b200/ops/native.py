@@ -371,3 +371,60 @@ def umma_down(tmap_a, tmap_a2, tmap_b, sfa, sfa2, sfb, ids, out_b, out_f, out_st
                                _p(scratch), _p(tickets), c_int(n_tok), c_int(top_k), c_int(slots), c_int(d),
                                c_int(inter), _p(status), _stream())
     _check(code, "umma_down")
+
+
+# ---- bulk (many-row) tensor-core paths ----------------------------------------------------------------------
+def umma_bulk(tmap_a, tmap_b, sfa, sfb, n, N, K, *, splits=1, scratch=None, tickets=None, out_b=None, out_f=None,
+              out_stride=None, status=None, NP=128, katoms_b=None):
+    """Block-scaled GEMM over any number of token rows (tiles of 128 rows).  ``sfb``: activation scale atoms in the
+    standard layout (one 128-row atom block per 128 rows, ``katoms_b`` k-atoms per block, default K / 128)."""
+    if out_stride is None:
+        out_stride = N
+    code = lib().sfb_umma_bulk(c_void_p(tmap_a.ptr), c_void_p(tmap_b.ptr), _p(sfa), c_int(K // 128), _p(sfb),
+                               c_int(katoms_b if katoms_b is not None else K // 128), c_int(n), c_int(NP), c_int(N), c_int(K),
+                               c_int(splits), _p(scratch), _p(tickets), _p(out_b), _p(out_f), c_int64(out_stride), None,
+                               c_int(0), None, c_int(0), c_int(0), _p(status), _stream())
+    _check(code, "umma_bulk")
+
+
+def umma_pair_bulk(tmap_a, tmap_b, sfa, sfb, n_rows, N, K, *, groups=1, splits=1, scratch=None, tickets=None, out_b=None,
+                   out_f=None, out_stride=None, out_q=None, out_q_atom=None, status=None):
+    """Two-term activations in blocks of 128 buffer rows (64 hi rows then 64 lo rows per 64 logical rows)."""
+    if out_stride is None:
+        out_stride = N * groups
+    code = lib().sfb_umma_pair_bulk(c_void_p(tmap_a.ptr), c_void_p(tmap_b.ptr), _p(sfa), c_int(K // 128), _p(sfb),
+                                    c_int(K * groups // 128), c_int(n_rows), c_int(N), c_int(K), c_int(groups), c_int(splits),
+                                    _p(scratch), _p(tickets), _p(out_b), _p(out_f), c_int64(out_stride), _p(out_q),
+                                    _p(out_q_atom), _p(status), _stream())
+    _check(code, "umma_pair_bulk")
+
+
+def bf16_map(t: torch.Tensor, rows: int, K: int, box_rows: int) -> TensorMap:
+    """Tensor map over a row-major bf16 matrix [rows, K] for the bf16 tensor-core GEMM (bytes as the element type)."""
+    return TensorMap(t, rows, 2 * K, 2 * K, box_rows)
+
+
+def umma_bf16(tmap_a, tmap_b, n, N, K, *, splits=1, scratch=None, tickets=None, out_b=None, out_f=None, out_stride=None,
+              status=None, NP=None):
+    """out[token, col] = sum_k W[col, k] X[token, k] with bf16 operands on tcgen05 kind::f16 (fp32 accumulate)."""
+    NP = NP or (128 if n > 128 else umma_np(n))
+    if out_stride is None:
+        out_stride = N
+    code = lib().sfb_umma_bf16(c_void_p(tmap_a.ptr), c_void_p(tmap_b.ptr), c_int(n), c_int(NP), c_int(N), c_int(K),
+                               c_int(splits), _p(scratch), _p(tickets), _p(out_b), _p(out_f), c_int64(out_stride), _p(status),
+                               _stream())
+    _check(code, "umma_bf16")
+
+
+def attn_tc(q, q_stride, rope, row_lane, row_pos, win_q, win_s, ckv_q, ckv_s, sel, sel_count, K, sink, out, n, heads,
+            hd, rd, window, ring, scale, out_q=None, out_atom=None, pair_block=0, win_lo=None, win_hi=None, status=None):
+    """Rows attention on tcgen05 (csrc/k_attn_tc.cu); arguments as ``attn_rows``.  ``pair_block`` > 0: the two-term FP8
+    copy is laid out in blocks of 2 * pair_block buffer rows (hi rows then lo rows of pair_block logical rows)."""
+    code = lib().sfb_attn_tc(
+        _p(q), c_int64(q_stride), _p(rope), c_int(rope.stride(0) // 2), _p(row_lane), _p(row_pos), _p(win_q), _p(win_s),
+        c_int64(win_q.stride(0)), c_int64(win_s.stride(0)), _p(ckv_q), _p(ckv_s),
+        c_int64(ckv_q.stride(0) if ckv_q is not None else 0), c_int64(ckv_s.stride(0) if ckv_s is not None else 0),
+        _p(sel), _p(sel_count), c_int(K), _p(sink), _p(out), _p(out_q), _p(out_atom), c_int(pair_block), c_int(n),
+        c_int(heads), c_int(hd), c_int(rd), c_int(window), c_int(ring), c_float(scale), _p(win_lo), _p(win_hi), _p(status),
+        _stream())
+    _check(code, "attn_tc")

@@ -1,0 +1,198 @@
+"""Many-row tensor-core kernels against plain fp32 references: the bf16 GEMM (kind::f16), the two-term block layout of
+the grouped output projection, and the tcgen05 rows attention.  Reference tests: crates/sparkflash-kernels/tests
+(decode_mma_device.rs), kernels/opt_mma_sm121.cu bulk paths."""
+import pytest
+import torch
+
+from sparkflash_b200 import codecs as C
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("N_,K,n,splits", [(128, 64, 1, 1), (256, 512, 5, 1), (384, 1024, 40, 4), (256, 320, 300, 1),
+                                            (128, 2048, 130, 2), (200, 256, 16, 1)])
+def test_umma_bf16_matches_fp32_reference(N_, K, n, splits):
+    from sparkflash_b200.ops import native as N
+    g = torch.Generator().manual_seed(N_ + K + n)
+    w = (torch.randn(N_, K, generator=g) * 0.1).to(torch.bfloat16)
+    x = torch.randn(n, K, generator=g).to(torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    dev = "cuda"
+    NP = 128 if n > 128 else N.umma_np(n)
+    rows_b = (n + NP - 1) // NP * NP
+    wd = w.to(dev).contiguous()
+    xd = torch.zeros(rows_b, K, dtype=torch.bfloat16, device=dev)
+    xd[:n] = x.to(dev)
+    ta = N.bf16_map(wd, N_, K, 128)
+    tb = N.bf16_map(xd, rows_b, K, NP)
+    tiles = (N_ + 127) // 128 * ((n + NP - 1) // NP)
+    scratch = torch.zeros(max(1, tiles * splits * 128 * NP), dtype=torch.float32, device=dev)
+    tickets = torch.zeros(max(1, tiles), dtype=torch.int32, device=dev)
+    out = torch.full((n, N_), float("nan"), dtype=torch.float32, device=dev)
+    out_b = torch.zeros((n, N_), dtype=torch.bfloat16, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    for _ in range(2):
+        N.umma_bf16(ta, tb, n, N_, K, splits=splits, scratch=scratch, tickets=tickets, out_f=out, status=status, NP=NP)
+        torch.cuda.synchronize()
+        assert status.tolist()[0] == 0, status.tolist()
+        err = (out.cpu() - ref).abs().max().item()
+        assert err <= 1e-4 * ref.abs().max().item() + 1e-5, (err, ref.abs().max().item())   # exact products, fp32 sums
+    if N_ % 128 == 0:
+        N.umma_bf16(ta, tb, n, N_, K, splits=splits, scratch=scratch, tickets=tickets, out_b=out_b, status=status, NP=NP)
+        torch.cuda.synchronize()
+        assert (out_b.cpu().float() - ref).abs().max() <= 2 ** -7 * ref.abs().max() + 1e-5
+
+
+def test_two_term_block_layout_matches_per_block_launches():
+    """150 rows through the grouped projection in one launch (blocks of 64 hi + 64 lo rows) give the bits of one launch per
+    block of 64 rows, and both stay within FP8 two-term precision of the fp32 product."""
+    from sparkflash_b200.ops import native as N
+    dev = "cuda"
+    groups, N_, K, n = 2, 128, 256, 150
+    g = torch.Generator().manual_seed(5)
+    w = torch.randn(groups * N_, K, generator=g) * 0.05
+    q, s = C.weight_quant_fp8_block32(w)
+    wd = C.weight_dequant_fp8_block32(q, s)
+    sfa = C.scales_to_prepared(s, groups * N_, 32).to(dev)
+    x = torch.randn(n, groups * K, generator=g).to(torch.bfloat16)
+    ref = torch.cat([x.float()[:, gi * K:(gi + 1) * K] @ wd[gi * N_:(gi + 1) * N_].t() for gi in range(groups)], 1)
+    nblk = (n + 63) // 64
+    KB = groups * K // 32
+    xq = torch.zeros(nblk * 128, groups * K, dtype=torch.uint8, device=dev)
+    atom = torch.full((C.sf_bytes(nblk * 128, KB),), 127, dtype=torch.uint8, device=dev)
+    block_bytes = C.sf_bytes(128, KB)
+    xdev = x.to(dev)
+    for b in range(nblk):
+        m = min(64, n - 64 * b)
+        N.quant_rows(xdev[64 * b:], xq[128 * b:], None, atom[b * block_bytes:], m, groups * K, split=True, split_off=64)
+    qd = q.to(dev).contiguous()
+    ta = N.TensorMap(qd, groups * N_, K, K, 128)
+    tb = N.TensorMap(xq, nblk * 128, groups * K, groups * K, 128)
+    tiles = (N_ // 128) * groups * nblk
+    scratch = torch.zeros(tiles * 128 * 128, dtype=torch.float32, device=dev)
+    tickets = torch.zeros(tiles, dtype=torch.int32, device=dev)
+    out = torch.full((n, groups * N_), float("nan"), dtype=torch.float32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    oq = torch.zeros(nblk * 64, groups * N_, dtype=torch.uint8, device=dev)
+    oq_atom = torch.full((C.sf_bytes(nblk * 64, groups * N_ // 32),), 127, dtype=torch.uint8, device=dev)
+    N.umma_pair_bulk(ta, tb, sfa, atom, n, N_, K, groups=groups, scratch=scratch, tickets=tickets, out_f=out, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0, status.tolist()
+    assert (out.cpu() - ref).abs().max() <= 4e-3 * ref.abs().max()
+    # per-block launches of the few-row entry point on the same buffers
+    for b in range(nblk):
+        m = min(64, n - 64 * b)
+        one = torch.zeros(64, groups * N_, dtype=torch.float32, device=dev)      # the few-row entry point writes all 64 rows
+        tb1 = N.TensorMap(xq[128 * b:], 128, groups * K, groups * K, 128)
+        N.umma_dense_pair(ta, tb1, sfa, atom[b * block_bytes:], 64, N_, K, groups=groups, scratch=scratch, tickets=tickets,
+                          out_f=one, status=status, NP=128)
+        torch.cuda.synchronize()
+        assert torch.equal(one[:m], out[64 * b:64 * b + m]), b
+    # re-quantised output for the next projection: codes and atoms decode to the bf16-rounded output
+    out_b = torch.zeros(n, groups * N_, dtype=torch.bfloat16, device=dev)
+    N.umma_pair_bulk(ta, tb, sfa, atom, n, N_, K, groups=groups, scratch=scratch, tickets=tickets, out_b=out_b, out_q=oq,
+                     out_q_atom=oq_atom, status=status)
+    torch.cuda.synchronize()
+    rq, rs = C.act_quant_fp8(out_b.cpu().float())
+    assert torch.equal(oq[:n].cpu(), rq)
+    assert torch.equal(C.prepared_to_scales(oq_atom.cpu(), n, groups * N_ // 32), rs)
+
+
+def _attention_case(heads, rows, with_compressed, seed):
+    from sparkflash_b200.models.deepseek_v41 import oracle as O
+    from sparkflash_b200.config import full_config
+    cfg = full_config()
+    hd, rd, window, ring, K = 512, 64, 128, 512, 512
+    g = torch.Generator().manual_seed(seed)
+    lanes = 2
+    pos = torch.tensor(rows, dtype=torch.int32)
+    n = len(rows)
+    lane = torch.tensor([i % lanes for i in range(n)], dtype=torch.int32)
+    invf = O.rope_inv_freq(cfg, True)
+    win = torch.randn(lanes, ring, hd, generator=g) * 0.7
+    wq, ws = C.act_quant_fp8(win)
+    entries = 900
+    ckv = torch.randn(lanes, entries, hd, generator=g) * 0.7
+    cq, cs = C.kv_quant_fp4(ckv)
+    sel = torch.full((n, K), -1, dtype=torch.int32)
+    cnt = torch.zeros(n, dtype=torch.int32)
+    if with_compressed:
+        for r in range(n):
+            clen = min(entries, int(pos[r]) + 1)
+            k = min(K, clen)
+            ids = torch.randperm(clen, generator=g)[:k].sort().values
+            sel[r, :k] = ids.int(); cnt[r] = k
+    q = (torch.randn(n, heads * hd, generator=g) * 0.5).to(torch.bfloat16)
+    sink = torch.randn(heads, generator=g)
+    return dict(cfg=cfg, hd=hd, rd=rd, window=window, ring=ring, K=K, pos=pos, lane=lane, invf=invf, wq=wq, ws=ws, cq=cq, cs=cs,
+                sel=sel, cnt=cnt, q=q, sink=sink, n=n, heads=heads)
+
+
+@pytest.mark.parametrize("heads,with_compressed", [(8, True), (40, True), (16, False), (64, True)])
+def test_attention_tc_matches_fp32_reference(heads, with_compressed):
+    from sparkflash_b200.models.deepseek_v41 import oracle as O
+    from sparkflash_b200.ops import native as N
+    rows = [700, 5, 131, 0, 127, 128, 400, 899, 64] if heads <= 16 else [700, 5, 131, 899]
+    c = _attention_case(heads, rows, with_compressed, seed=11 + heads)
+    dev = "cuda"
+    n, hd, rd = c["n"], c["hd"], c["rd"]
+    out = torch.zeros(n, heads * hd, dtype=torch.bfloat16, device=dev)
+    nblk = (n + 63) // 64
+    out_q = torch.zeros(nblk * 128, heads * hd, dtype=torch.uint8, device=dev)
+    KB = heads * hd // 32
+    out_atom = torch.full((C.sf_bytes(nblk * 128, KB),), 127, dtype=torch.uint8, device=dev)
+    rope = torch.zeros(n, 1, rd // 2, 2, dtype=torch.float32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    N.rope_table([c["invf"].to(dev)], [1], c["pos"].to(dev), rope, n)
+    ckq = C.pack_nibbles(c["cq"]).to(dev) if with_compressed else None
+    cks = c["cs"].to(dev) if with_compressed else None
+    N.attn_tc(c["q"].to(dev), heads * hd, rope[:, 0], c["lane"].to(dev), c["pos"].to(dev), c["wq"].to(dev), c["ws"].to(dev),
+              ckq, cks, c["sel"].to(dev) if with_compressed else None, c["cnt"].to(dev) if with_compressed else None, c["K"],
+              c["sink"].to(dev), out, n, heads, hd, rd, c["window"], c["ring"], hd ** -0.5, out_q=out_q, out_atom=out_atom,
+              pair_block=64, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0, status.tolist()
+    wd = C.act_dequant_fp8(c["wq"], c["ws"])
+    cd = C.kv_dequant_fp4(c["cq"], c["cs"])
+    invf = c["invf"]
+    for r in range(n):
+        p, L = int(c["pos"][r]), int(c["lane"][r])
+        keys = [wd[L, t % c["ring"]] for t in range(max(0, p - c["window"] + 1), p + 1)]
+        keys += [cd[L, j] for j in c["sel"][r, :int(c["cnt"][r])].tolist()]
+        Kmat = torch.stack(keys)
+        qq = O.apply_rope(c["q"][r].float().view(heads, hd), p, invf)
+        s = (qq @ Kmat.t()) * hd ** -0.5
+        m = s.max(-1, keepdim=True).values
+        e = torch.exp(s - m)
+        o = O.bf((e @ Kmat) / (e.sum(-1, keepdim=True) + torch.exp(c["sink"].view(heads, 1) - m)))
+        o = O.apply_rope(o, p, invf, inverse=True)
+        got = out[r].cpu().float().view(heads, hd)
+        assert (got - o).abs().max() <= 0.02 * o.abs().max() + 1e-4, (r, (got - o).abs().max(), o.abs().max())
+    # the two-term FP8 copy decodes back to the bf16 output (hi + lo / 16 under the hi scale)
+    oq = out_q.cpu()
+    for r in range(n):
+        hi_row, lo_row = (r // 64) * 128 + r % 64, (r // 64) * 128 + r % 64 + 64
+        _, sc = C.act_quant_fp8(out[r].cpu().float().view(1, -1))
+        scale = C.ue8m0_decode(sc).repeat_interleave(32, -1).view(-1)
+        val = (C.e4m3_decode(oq[hi_row]) + C.e4m3_decode(oq[lo_row]) / 16.0) * scale
+        ref = out[r].cpu().float()
+        assert (val - ref).abs().max() <= 2 ** -6 * ref.abs().max() + 1e-6, r
+
+
+def test_attention_tc_agrees_with_rows_kernel():
+    """Same inputs through the CUDA-core rows kernel (the exact arm) and the tcgen05 kernel."""
+    from sparkflash_b200.ops import native as N
+    heads = 32
+    c = _attention_case(heads, [300, 899, 17], True, seed=3)
+    dev = "cuda"
+    n, hd, rd = c["n"], c["hd"], c["rd"]
+    rope = torch.zeros(n, 1, rd // 2, 2, dtype=torch.float32, device=dev)
+    N.rope_table([c["invf"].to(dev)], [1], c["pos"].to(dev), rope, n)
+    args = (c["q"].to(dev), heads * hd, rope[:, 0], c["lane"].to(dev), c["pos"].to(dev), c["wq"].to(dev), c["ws"].to(dev),
+            C.pack_nibbles(c["cq"]).to(dev), c["cs"].to(dev), c["sel"].to(dev), c["cnt"].to(dev), c["K"], c["sink"].to(dev))
+    a = torch.zeros(n, heads * hd, dtype=torch.bfloat16, device=dev)
+    b = torch.zeros_like(a)
+    N.attn_rows(*args, a, n, heads, hd, rd, c["window"], c["ring"], hd ** -0.5)
+    N.attn_tc(*args, b, n, heads, hd, rd, c["window"], c["ring"], hd ** -0.5)
+    torch.cuda.synchronize()
+    assert (a.float() - b.float()).abs().max() <= 0.02 * a.float().abs().max()

@@ -28,7 +28,11 @@ def _case(N_, K, n, fp4, groups=1, seed=0):
 
 @pytest.mark.parametrize("N_,K,n,fp4,splits,groups", [
     (128, 128, 1, False, 1, 1), (256, 512, 5, False, 1, 1), (256, 512, 16, False, 2, 1), (384, 1024, 3, False, 4, 1),
-    (128, 256, 2, True, 1, 1), (256, 512, 9, True, 2, 1), (128, 256, 4, False, 1, 2), (256, 1280, 33, False, 1, 1)])
+    (128, 256, 2, True, 1, 1), (256, 512, 9, True, 2, 1), (128, 256, 4, False, 1, 2), (256, 1280, 33, False, 1, 1),
+    # production shapes: wo_b / expert down column count with 7-way split-K, wqkv_a with 21-way split-K, wq_b without a split,
+    # many rows with the separate split-K reduce grid, a grouped matrix with eight groups
+    (5120, 8192, 1, False, 7, 1), (1792, 5120, 1, False, 21, 1), (4096, 1280, 3, False, 1, 1), (5120, 5120, 40, False, 7, 1),
+    (1024, 4096, 6, False, 4, 8), (2304, 5120, 16, True, 2, 1)])
 def test_umma_dense_matches_reference(N_, K, n, fp4, splits, groups):
     from sparkflash_b200.ops import native as N
     q, sfa, xq, sfb, ref = _case(N_, K, n, fp4, groups, seed=N_ + K + n)
