@@ -21,6 +21,7 @@
 // Reference behaviour replaced: kernels/opt_mma_sm121.cu:1243 (opt_bulk_attn: one block per row, heads as the MMA M),
 // kernels/flash_mla_csa2_common_sm121.cuh; docs/architecture/01-csa2-attention.md:98-104,212-229.
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #include "k_common.cuh"
 
@@ -32,7 +33,7 @@ constexpr int HD = 512;            // latent width
 constexpr int KT = 128;            // keys per tile
 constexpr int SLABS = HD / 64;     // 64 bf16 = one 128-byte swizzle row
 constexpr int SLAB_BYTES = KT * 128;
-constexpr int THREADS = 128;
+constexpr int THREADS = 256;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -158,6 +159,60 @@ namespace sfb {
 
 using namespace atc;
 
+// ---- cache codes -> bf16 by bit placement ----------------------------------------------------------------------
+// An E4M3 byte shifted into a bf16 (sign to bit 15, the seven exponent|mantissa bits to bits 4..10) is the code's value
+// times 2^-120, subnormal codes included (they land on bf16 subnormals); an E2M1 nibble placed the same way (sign to bit
+// 15, three bits to 6..8) is its value times 2^-126.  Two exact bf16 multiplications by powers of two (the second one
+// carrying the block scale) undo the factor; every intermediate is representable, so the result is the exact product.
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2_raw(uint32_t two_bytes_in_high_halves) {
+  // input: byte a in bits 8..15, byte b in bits 24..31
+  const uint32_t t = two_bytes_in_high_halves;
+  return (t & 0x80008000u) | ((t >> 4) & 0x07f007f0u);
+}
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf16x2_splat(float f) {
+  __nv_bfloat162 r = __float2bfloat162_rn(f);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+// 16 E4M3 codes (one uint4) with one power-of-two scale -> two uint4 of bf16; m1, m2: splatted bf16 multipliers
+__device__ __forceinline__ void fp8x16_to_bf16(const uint4& v, uint32_t m1, uint32_t m2, uint4& o0, uint4& o1) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t r[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t lo = __byte_perm(w[i], 0u, 0x1404);   // bytes: [0, b0, 0, b1] -> b0 in bits 8..15, b1 in bits 24..31
+    const uint32_t hi = __byte_perm(w[i], 0u, 0x3424);   // b2, b3
+    r[2 * i] = bf16x2_mul(bf16x2_mul(e4m3x2_to_bf16x2_raw(lo), m1), m2);
+    r[2 * i + 1] = bf16x2_mul(bf16x2_mul(e4m3x2_to_bf16x2_raw(hi), m1), m2);
+  }
+  o0 = make_uint4(r[0], r[1], r[2], r[3]);
+  o1 = make_uint4(r[4], r[5], r[6], r[7]);
+}
+// 8 E2M1 codes (one 32-bit word, element i in nibble i) -> one uint4 of bf16
+__device__ __forceinline__ uint4 fp4x8_to_bf16(uint32_t w, uint32_t m1, uint32_t m2) {
+  uint32_t r[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t x = (w >> (8 * i)) & 0xffu;
+    const uint32_t lanes = (x & 0xfu) | ((x & 0xf0u) << 12);          // nibble 0 in bits 0..3, nibble 1 in bits 16..19
+    const uint32_t raw = ((lanes & 0x00080008u) << 12) | ((lanes & 0x00070007u) << 6);
+    r[i] = bf16x2_mul(bf16x2_mul(raw, m1), m2);
+  }
+  return make_uint4(r[0], r[1], r[2], r[3]);
+}
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t* v) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+
 template <int NH>
 struct AttnTcSmem {
   alignas(1024) uint8_t kv[SLABS * SLAB_BYTES];   // 128 keys x 512 dims bf16, eight swizzled slabs
@@ -170,8 +225,10 @@ struct AttnTcSmem {
   uint32_t tmem_base;
 };
 
-// grid (head groups, rows), 128 threads.  Thread t owns key slot t of every tile (decode, TMEM lane of the score tile)
-// and dim 32*warp + lane of each 128-dim output tile; for the softmax it owns head t % NH over the key part t / NH.
+// grid (head groups, rows), 256 threads = two halves of four warps.  Half h of thread pair (key slot = tid % 128) decodes
+// dims [256 h, 256 h + 256) of its key; in TMEM accesses warp w and warp w + 4 share lanes 32 (w % 4).. and split the
+// columns (score tile) or the 128-dim output tiles (half h owns tiles 2h, 2h + 1).  For the softmax a thread owns head
+// tid % NH over the key part tid / NH.
 template <int NH>
 __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -180,8 +237,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   constexpr uint32_t TMEM_COLS = NH * 5 <= 128 ? 128 : 256;
   constexpr int PARTS = THREADS / NH;      // key parts per head in the softmax
   constexpr int KPP = KT / PARTS;          // keys per part
+  constexpr int CH = NH / 2;               // score columns per half
   constexpr float LOG2E = 1.4426950408889634f;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int half = tid >> 7, key_slot = tid & 127;
   const int hg = blockIdx.x, row = blockIdx.y;
 
   if (tid == 0) {
@@ -199,11 +258,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   pdl_wait();
   const uint32_t tmem = S.tmem_base;
   const uint32_t t_s = tmem, t_o = tmem + NH;
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
   const int pos = a.row_pos[row], L = a.row_lane[row];
   const int r0 = HD - a.rd;
   // ---- queries of the group's heads: rope on the last rd dims, bf16, swizzled K-major ----
+#pragma unroll 2
   for (int idx = tid; idx < NH * 64; idx += THREADS) {
     const int hh = idx >> 6, c = idx & 63;          // head in group, 8-dim chunk
     const int ghead = hg * NH + hh;
@@ -233,67 +293,62 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   uint32_t parity = 0;
   bool ok = true;
   const float sl2 = a.scale * LOG2E;
+  const uint32_t M60 = bf16x2_splat(1.152921504606847e18f);      // 2^60
+  const uint32_t M100 = bf16x2_splat(1.2676506002282294e30f);    // 2^100
 
+#pragma unroll 1
   for (int tile = 0; tile < tiles && ok; ++tile) {
-    // ---- decode key slot `tid` of the tile into the bf16 tile (exact: FP8 x 2^k, FP4 x E4M3) ----
+    // ---- decode dims [256 half, +256) of key slot `key_slot` into the bf16 tile ----
     {
-      const int e = tile * KT + tid;
+      const int e = tile * KT + key_slot;
       uint8_t* rowp = S.kv;
       if (e < n_win) {
         const int slot = (w_first + e) % a.ring;
-        const uint8_t* kq = a.win_q + (size_t)L * a.win_lane_q + (size_t)slot * HD;
-        const uint8_t* ks = a.win_s + (size_t)L * a.win_lane_s + (size_t)slot * (HD / 32);
-        const uint4 sc4 = *reinterpret_cast<const uint4*>(ks);
-        const uint8_t* scb = reinterpret_cast<const uint8_t*>(&sc4);
-#pragma unroll 2
-        for (int prt = 0; prt < 16; ++prt) {
-          const uint4 raw0 = *reinterpret_cast<const uint4*>(kq + prt * 32);
-          const uint4 raw1 = *reinterpret_cast<const uint4*>(kq + prt * 32 + 16);
-          const float rs = ue8m0_to_f32(scb[prt]) * 1.152921504606847e18f;    // 2^60; the raw decode carries 2^-120
-          float f[32];
-          decode16_e4m3_raw(raw0, f); decode16_e4m3_raw(raw1, f + 16);
+        const uint8_t* kq = a.win_q + (size_t)L * a.win_lane_q + (size_t)slot * HD + half * 256;
+        const uint8_t* ks = a.win_s + (size_t)L * a.win_lane_s + (size_t)slot * (HD / 32) + half * 8;
+        const uint2 sc2 = *reinterpret_cast<const uint2*>(ks);
+        const uint8_t* scb = reinterpret_cast<const uint8_t*>(&sc2);
+#pragma unroll 1
+        for (int b = 0; b < 2; ++b) {          // two batches of eight 16-byte loads in flight
+          uint4 raw[8];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 o;
-            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+          for (int i = 0; i < 8; ++i) raw[i] = *reinterpret_cast<const uint4*>(kq + (b * 8 + i) * 16);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              ow[u] = pack_bf16((f[8 * j + 2 * u] * 1.152921504606847e18f) * rs, (f[8 * j + 2 * u + 1] * 1.152921504606847e18f) * rs);
-            const int c = prt * 4 + j;
-            *reinterpret_cast<uint4*>(rowp + (c >> 3) * SLAB_BYTES + swz(tid, c & 7)) = o;
+          for (int i = 0; i < 8; ++i) {
+            // block scale 2^(code - 127) times the 2^60 left over from the raw placement (2^-120 = 2^-60 2^-60)
+            const uint32_t m2 = bf16x2_splat(ue8m0_shifted(scb[(b * 8 + i) >> 1], 60));
+            uint4 o0, o1;
+            fp8x16_to_bf16(raw[i], M60, m2, o0, o1);
+            const int c = half * 32 + (b * 8 + i) * 2;
+            *reinterpret_cast<uint4*>(rowp + (c >> 3) * SLAB_BYTES + swz(key_slot, c & 7)) = o0;
+            *reinterpret_cast<uint4*>(rowp + ((c + 1) >> 3) * SLAB_BYTES + swz(key_slot, (c + 1) & 7)) = o1;
           }
         }
       } else if (e < total) {
         const int id = a.sel[(size_t)row * a.K + (e - n_win)];
-        const uint8_t* kq = a.ckv_q + (size_t)L * a.ckv_lane_q + (size_t)id * (HD / 2);
-        const uint8_t* ks = a.ckv_s + (size_t)L * a.ckv_lane_s + (size_t)id * (HD / 16);
-        const uint4 sa = *reinterpret_cast<const uint4*>(ks), sb = *reinterpret_cast<const uint4*>(ks + 16);
-        uint8_t scb[32];
-        *reinterpret_cast<uint4*>(scb) = sa; *reinterpret_cast<uint4*>(scb + 16) = sb;
-#pragma unroll 2
-        for (int prt = 0; prt < 16; ++prt) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(kq + prt * 16);
-          const float rs0 = e4m3_to_f32(scb[2 * prt]) * 9.223372036854776e18f;       // 2^63; the raw decode carries 2^-126
-          const float rs1 = e4m3_to_f32(scb[2 * prt + 1]) * 9.223372036854776e18f;
-          float f[32];
-          decode32_e2m1_raw(raw, f);
+        const uint8_t* kq = a.ckv_q + (size_t)L * a.ckv_lane_q + (size_t)id * (HD / 2) + half * 128;
+        const uint8_t* ks = a.ckv_s + (size_t)L * a.ckv_lane_s + (size_t)id * (HD / 16) + half * 16;
+        uint4 raw[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) raw[i] = *reinterpret_cast<const uint4*>(kq + i * 16);
+        const uint4 sc4 = *reinterpret_cast<const uint4*>(ks);
+        const uint8_t* scb = reinterpret_cast<const uint8_t*>(&sc4);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {          // 32 codes per uint4, two E4M3 scales
+          const uint32_t w4[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float rs = j < 2 ? rs0 : rs1;
-            uint4 o;
-            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              ow[u] = pack_bf16((f[8 * j + 2 * u] * 9.223372036854776e18f) * rs, (f[8 * j + 2 * u + 1] * 9.223372036854776e18f) * rs);
-            const int c = prt * 4 + j;
-            *reinterpret_cast<uint4*>(rowp + (c >> 3) * SLAB_BYTES + swz(tid, c & 7)) = o;
+            // E4M3 scale (exact in bf16) times the 2^26 left over: 2^-126 = 2^-100 2^-26
+            const uint32_t m2 = bf16x2_splat(e4m3_to_f32(scb[2 * i + (j >> 1)]) * 67108864.f);
+            const int c = half * 32 + i * 4 + j;
+            *reinterpret_cast<uint4*>(rowp + (c >> 3) * SLAB_BYTES + swz(key_slot, c & 7)) = fp4x8_to_bf16(w4[j], M100, m2);
           }
         }
       } else {
         // past the row's last key: zeros, so that the value contraction adds 0 x 0 and never meets stale bits
         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll 4
-        for (int c = 0; c < 64; ++c) *reinterpret_cast<uint4*>(rowp + (c >> 3) * SLAB_BYTES + swz(tid, c & 7)) = z;
+        for (int c = half * 32; c < half * 32 + 32; ++c) *reinterpret_cast<uint4*>(rowp + (c >> 3) * SLAB_BYTES + swz(key_slot, c & 7)) = z;
       }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -304,7 +359,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
       tc_fence_after();
       const uint32_t idesc = make_idesc(128, NH, 0);
       const uint32_t kvb = smem_u32(S.kv), qb = smem_u32(S.q);
-#pragma unroll
+#pragma unroll 1
       for (int s = 0; s < SLABS; ++s) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
@@ -318,23 +373,28 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
     if (!ok) break;
     tc_fence_after();
-    // ---- scores: TMEM (lane = key) -> shared memory, head-major ----
+    // ---- scores: TMEM (lane = key) -> shared memory, head-major; each half takes half of the head columns ----
     {
-      const bool valid = tile * KT + tid < total;
-#pragma unroll
-      for (int c0 = 0; c0 < NH; c0 += 16) {
+      const bool valid = tile * KT + key_slot < total;
+      if constexpr (CH == 16) {
         uint32_t v[16];
-        tc_ld16(t_s + lane_base + c0, v);
+        tc_ld16(t_s + lane_base + half * CH, v);
         tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) S.sbuf[c0 + j][tid] = valid ? __uint_as_float(v[j]) * sl2 : -INFINITY;
+        for (int j = 0; j < 16; ++j) S.sbuf[half * CH + j][key_slot] = valid ? __uint_as_float(v[j]) * sl2 : -INFINITY;
+      } else {
+        uint32_t v[8];
+        tc_ld8(t_s + lane_base + half * CH, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) S.sbuf[half * CH + j][key_slot] = valid ? __uint_as_float(v[j]) * sl2 : -INFINITY;
       }
     }
     __syncthreads();
     // ---- online softmax: thread = (head, key part) ----
     float mloc = -INFINITY;
     const float* srow = &S.sbuf[my_head][my_part * KPP];
-#pragma unroll 8
+#pragma unroll
     for (int i = 0; i < KPP; ++i) mloc = fmaxf(mloc, srow[i]);
     S.red[my_part * NH + my_head] = mloc;
     __syncthreads();
@@ -344,7 +404,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     const float corr = exp2f(m_run - m_new);
     __syncthreads();                 // everyone has read the maxima before the sums overwrite them
     float lsum = 0.f;
-#pragma unroll 4
+#pragma unroll
     for (int i = 0; i < KPP; i += 2) {
       const float p0 = exp2f(srow[i] - m_new), p1 = exp2f(srow[i + 1] - m_new);
       const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
@@ -360,11 +420,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     for (int pp = 0; pp < PARTS; ++pp) lt += S.red[pp * NH + my_head];
     l_run = l_run * corr + lt;
     m_run = m_new;
-    // ---- rescale the running O^T (lane = dim, column = head) ----
+    // ---- rescale the running O^T (lane = dim, column = head): half h owns the 128-dim tiles 2h and 2h + 1 ----
     if (tile > 0) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-#pragma unroll
+#pragma unroll 1
+      for (int jj = 0; jj < 2; ++jj) {
+        const int j = half * 2 + jj;
+#pragma unroll 1
         for (int c0 = 0; c0 < NH; c0 += 16) {
           uint32_t v[16];
           tc_ld16(t_o + lane_base + j * NH + c0, v);
@@ -384,7 +445,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
       tc_fence_after();
       const uint32_t idesc = make_idesc(128, NH, 1);
       const uint32_t kvb = smem_u32(S.kv), pb = smem_u32(S.p);
-#pragma unroll
+#pragma unroll 1
       for (int j = 0; j < 4; ++j) {
 #pragma unroll
         for (int t8 = 0; t8 < KT / 16; ++t8)
@@ -414,18 +475,19 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
       row_lo = row_hi + a.pair_block;
     }
     const int KB = a.heads * (HD / 32);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int dim = j * 128 + warp * 32 + lane;
+#pragma unroll 1
+    for (int jj = 0; jj < 2; ++jj) {
+      const int j = half * 2 + jj;
+      const int dim = j * 128 + (warp & 3) * 32 + lane;
       const bool roped = dim >= r0;                       // warp-uniform (r0 is a multiple of 32)
       float2 c2 = make_float2(1.f, 0.f);
       if (roped) c2 = a.rope[(size_t)row * a.rope_stride + ((dim - r0) >> 1)];
-#pragma unroll
+#pragma unroll 1
       for (int c0 = 0; c0 < NH; c0 += 16) {
         uint32_t v[16];
         tc_ld16(t_o + lane_base + j * NH + c0, v);
         tc_wait_ld();
-#pragma unroll
+#pragma unroll 4
         for (int i = 0; i < 16; ++i) {
           const int ghead = hg * NH + c0 + i;
           float o = bfr(__uint_as_float(v[i]) * S.fac[c0 + i]);

@@ -181,25 +181,22 @@ struct SelectArgs {
 
 constexpr int SEL_THREADS = 1024;
 
-// one block per row; 4 radix passes of 8 bits, then an ordered compaction
-__global__ void __launch_bounds__(SEL_THREADS) select_topk_kernel(SelectArgs a) {
-  pdl_launch_dependents();
-  pdl_wait();
+// One block selects the top K of `len` elements: 4 radix passes of 8 bits, then an ordered compaction.  Element i is
+// sc[i] (IND = false; the id written is base + i) or sc[list[i]] with `list` ascending (IND = true; the id written is
+// list[i]), so "ties go to the lowest index" holds in both forms.
+template <bool IND>
+__device__ __forceinline__ void select_run(const float* sc, const int* list, int len, int base, int K, int* out, int* count_out) {
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_need, s_total;
   __shared__ uint32_t wsum[32];
-  const int row = blockIdx.x;
-  int len = (a.row_pos[row] + 1) / a.ratio;
-  len = (len + a.len_div - 1) / a.len_div;
-  if (len > a.max_len) len = a.max_len;
-  const float* sc = a.scores + (size_t)row * a.stride;
-  int* out = a.ids + (size_t)row * a.K;
+  struct { int K; } a{K};
   const uint32_t NEG_INF_KEY = order_key(-INFINITY);
+  auto at = [&](int i) -> float { return IND ? sc[list[i]] : sc[i]; };
   // count finite candidates (key > key(-inf))
   if (threadIdx.x == 0) s_total = 0;
   __syncthreads();
   uint32_t cnt = 0;
-  for (int i = threadIdx.x; i < len; i += SEL_THREADS) cnt += order_key(sc[i]) > NEG_INF_KEY;
+  for (int i = threadIdx.x; i < len; i += SEL_THREADS) cnt += order_key(at(i)) > NEG_INF_KEY;
   cnt = (uint32_t)__reduce_add_sync(0xffffffffu, cnt);
   if ((threadIdx.x & 31) == 0 && cnt) atomicAdd(&s_total, cnt);
   __syncthreads();
@@ -214,7 +211,7 @@ __global__ void __launch_bounds__(SEL_THREADS) select_topk_kernel(SelectArgs a) 
       for (int i = threadIdx.x; i < 256; i += SEL_THREADS) hist[i] = 0;
       __syncthreads();
       for (int i = threadIdx.x; i < len; i += SEL_THREADS) {
-        uint32_t key = order_key(sc[i]);
+        uint32_t key = order_key(at(i));
         if (key > NEG_INF_KEY && (key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
       }
       __syncthreads();
@@ -243,7 +240,7 @@ __global__ void __launch_bounds__(SEL_THREADS) select_topk_kernel(SelectArgs a) 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int c0 = 0; c0 < len && k > 0; c0 += SEL_THREADS) {
     const int i = c0 + threadIdx.x;
-    uint32_t key = i < len ? order_key(sc[i]) : 0u;
+    uint32_t key = i < len ? order_key(at(i)) : 0u;
     const bool gt = i < len && key > thr_key;
     const bool eq = i < len && key == thr_key && need_eq > 0 && key > NEG_INF_KEY;
     // eq entries are admitted in index order until need_eq is used up, so rank them first
@@ -265,15 +262,66 @@ __global__ void __launch_bounds__(SEL_THREADS) select_topk_kernel(SelectArgs a) 
     for (int w = 0; w < warp; ++w) before += wsum[w];
     uint32_t chunk = 0;
     for (int w = 0; w < SEL_THREADS / 32; ++w) chunk += wsum[w];
-    if (take && before + tk_rank_w < (uint32_t)a.K) out[before + tk_rank_w] = i;
+    if (take && before + tk_rank_w < (uint32_t)a.K) out[before + tk_rank_w] = IND ? list[i] : base + i;
     __syncthreads();
     if (threadIdx.x == 0) { s_base_gt += chunk; s_base_eq += eq_chunk; }
     __syncthreads();
   }
   for (int i = threadIdx.x; i < a.K; i += SEL_THREADS)
     if ((uint32_t)i >= k) out[i] = -1;
-  if (threadIdx.x == 0) a.count[row] = (int)k;
+  if (threadIdx.x == 0) *count_out = (int)k;
+  __syncthreads();
 }
+
+__device__ __forceinline__ int select_len(const SelectArgs& a, int row) {
+  int len = (a.row_pos[row] + 1) / a.ratio;
+  len = (len + a.len_div - 1) / a.len_div;
+  return len > a.max_len ? a.max_len : len;
+}
+
+// one block per row
+__global__ void __launch_bounds__(SEL_THREADS) select_topk_kernel(SelectArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  select_run<false>(a.scores + (size_t)row * a.stride, nullptr, select_len(a, row), 0, a.K, a.ids + (size_t)row * a.K, a.count + row);
+}
+
+// Long rows, stage 1: grid (chunks, rows); block (c, row) selects the top K of its chunk of the row into
+// tmp_ids[row, c, :] (ascending ids) and tmp_cnt[row, c].  The top K of the row is a subset of the union of the chunks'
+// top K (with the same order on (value, index)), which stage 2 selects from.
+__global__ void __launch_bounds__(SEL_THREADS) select_chunks_kernel(SelectArgs a, int chunk, int* tmp_ids, int* tmp_cnt) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = blockIdx.x, row = blockIdx.y, nch = gridDim.x;
+  const int len = select_len(a, row), base = c * chunk;
+  int lc = len - base;
+  lc = lc < 0 ? 0 : (lc > chunk ? chunk : lc);
+  select_run<false>(a.scores + (size_t)row * a.stride + base, nullptr, lc, base, a.K, tmp_ids + ((size_t)row * nch + c) * a.K,
+                    tmp_cnt + (size_t)row * nch + c);
+}
+
+// stage 2: one block per row gathers the chunks' winners (ascending by construction) and selects among them
+__global__ void __launch_bounds__(SEL_THREADS) select_merge_kernel(SelectArgs a, int nch, const int* tmp_ids, const int* tmp_cnt, int* tmp_list) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int off[257];
+  const int row = blockIdx.x;
+  if (threadIdx.x == 0) {
+    int o = 0;
+    for (int c = 0; c < nch; ++c) { off[c] = o; o += tmp_cnt[(size_t)row * nch + c]; }
+    off[nch] = o;
+  }
+  __syncthreads();
+  int* list = tmp_list + (size_t)row * nch * a.K;
+  for (int c = 0; c < nch; ++c) {
+    const int cnt = off[c + 1] - off[c];
+    for (int i = threadIdx.x; i < cnt; i += SEL_THREADS) list[off[c] + i] = tmp_ids[((size_t)row * nch + c) * a.K + i];
+  }
+  __syncthreads();
+  select_run<true>(a.scores + (size_t)row * a.stride, list, off[nch], 0, a.K, a.ids + (size_t)row * a.K, a.count + row);
+}
+
 
 }  // namespace sfb
 
@@ -324,6 +372,19 @@ int sfb_hsi_mark(const int* ids, int K, void* flags, int64_t f_stride, int max_b
   hsi_mark_kernel<<<dim3(gb, n), 256, 0, stream>>>(ids, K, (uint8_t*)flags, f_stride, max_blocks);
   hsi_mark2_kernel<<<dim3((K + 255) / 256, n), 256, 0, stream>>>(ids, K, (uint8_t*)flags, f_stride);
   return SFB_CHECK_LAUNCH();
+}
+
+// Long rows: the row cut into `chunk`-sized pieces selected by separate blocks, then merged.  tmp_ids [n, chunks, K],
+// tmp_cnt [n, chunks], tmp_list [n, chunks * K] are caller-provided int32 scratch; chunks = ceil(max_len / chunk) <= 256.
+int sfb_select_topk_long(const float* scores, int64_t stride, const int* row_pos, int ratio, int len_div, int max_len, int K,
+                         int* ids, int* count, int n, int chunk, int* tmp_ids, int* tmp_cnt, int* tmp_list, cudaStream_t stream) {
+  const int nch = (max_len + chunk - 1) / chunk;
+  if (chunk < 1 || nch < 1 || nch > 256) return (int)cudaErrorInvalidValue;
+  SelectArgs a{scores, stride, row_pos, ratio, len_div, max_len, K, ids, count};
+  cudaError_t e = sfb_launch(select_chunks_kernel, dim3(nch, n), dim3(SEL_THREADS), 0, stream, a, chunk, tmp_ids, tmp_cnt);
+  if (e != cudaSuccess) return (int)e;
+  return (int)sfb_launch(select_merge_kernel, dim3(n), dim3(SEL_THREADS), 0, stream, a, nch, (const int*)tmp_ids, (const int*)tmp_cnt,
+                         tmp_list);
 }
 
 // length of row = ceil(((row_pos+1)/ratio) / len_div), capped at max_len

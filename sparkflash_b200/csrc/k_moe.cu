@@ -321,6 +321,7 @@ struct MoePlanArgs {
   const int* ids;        // [n, k] expert id (local; < 0 = not on this rank)
   const float* wts;      // [n, k]
   int n, k, E, shared, S;          // S = segments launched (fixed per row count)
+  int seg;                         // pair slots per segment (16, or 64 for many-row steps)
   int* seg_expert;       // [S]  -1 unused, -2 shared expert
   int* seg_count;        // [S]
   float* seg_weight;     // [S*16]
@@ -336,20 +337,20 @@ __global__ void __launch_bounds__(512) moe_plan_kernel(MoePlanArgs a) {
   const int P = a.n * a.k;
   for (int i = threadIdx.x; i < a.E; i += blockDim.x) { cnt[i] = 0; fill[i] = 0; }
   for (int i = threadIdx.x; i < a.S; i += blockDim.x) { a.seg_expert[i] = -1; a.seg_count[i] = 0; }
-  for (int i = threadIdx.x; i < a.S * 16; i += blockDim.x) { a.seg_token[i] = -1; a.seg_weight[i] = 0.f; }
+  for (int i = threadIdx.x; i < a.S * a.seg; i += blockDim.x) { a.seg_token[i] = -1; a.seg_weight[i] = 0.f; }
   for (int i = threadIdx.x; i < a.n * (a.k + 1); i += blockDim.x) a.pair_pos[i] = -1;
   __syncthreads();
   for (int p = threadIdx.x; p < P; p += blockDim.x) { const int e = a.ids[p]; if (e >= 0 && e < a.E) atomicAdd(&cnt[e], 1); }
   __syncthreads();
   if (threadIdx.x == 0) {
     int b = 0;
-    for (int e = 0; e < a.E; ++e) { base[e] = b; b += (cnt[e] + 15) / 16; }
+    for (int e = 0; e < a.E; ++e) { base[e] = b; b += (cnt[e] + a.seg - 1) / a.seg; }
     base[a.E] = b;                     // first segment of the shared expert
   }
   __syncthreads();
   for (int e = threadIdx.x; e < a.E; e += blockDim.x)
-    for (int sgi = 0, c = cnt[e]; c > 0; ++sgi, c -= 16)
-      if (base[e] + sgi < a.S) { a.seg_expert[base[e] + sgi] = e; a.seg_count[base[e] + sgi] = c < 16 ? c : 16; }
+    for (int sgi = 0, c = cnt[e]; c > 0; ++sgi, c -= a.seg)
+      if (base[e] + sgi < a.S) { a.seg_expert[base[e] + sgi] = e; a.seg_count[base[e] + sgi] = c < a.seg ? c : a.seg; }
   for (int p = threadIdx.x; p < P; p += blockDim.x) {
     const int e = a.ids[p];
     if (e < 0 || e >= a.E) continue;
@@ -361,7 +362,7 @@ __global__ void __launch_bounds__(512) moe_plan_kernel(MoePlanArgs a) {
       // accumulator column wherever it sits, so the place changes no result
       r = cnt[e] - 1 - atomicAdd(&fill[e], 1);
     }
-    const int seg = base[e] + r / 16, slot = seg * 16 + (r & 15);
+    const int seg = base[e] + r / a.seg, slot = seg * a.seg + (r % a.seg);
     if (seg < a.S) {
       a.seg_token[slot] = p / a.k; a.seg_weight[slot] = a.wts[p];
       a.pair_pos[(p / a.k) * (a.k + 1) + p % a.k] = slot;
@@ -369,17 +370,17 @@ __global__ void __launch_bounds__(512) moe_plan_kernel(MoePlanArgs a) {
   }
   if (a.shared) {
     for (int t = threadIdx.x; t < a.n; t += blockDim.x) {
-      const int seg = base[a.E] + t / 16, slot = seg * 16 + (t & 15);
+      const int seg = base[a.E] + t / a.seg, slot = seg * a.seg + (t % a.seg);
       if (seg < a.S) { a.seg_token[slot] = t; a.seg_weight[slot] = 1.f; a.pair_pos[t * (a.k + 1) + a.k] = slot; }
     }
-    for (int sgi = threadIdx.x; sgi * 16 < a.n; sgi += blockDim.x)
-      if (base[a.E] + sgi < a.S) { a.seg_expert[base[a.E] + sgi] = -2; a.seg_count[base[a.E] + sgi] = a.n - sgi * 16 < 16 ? a.n - sgi * 16 : 16; }
+    for (int sgi = threadIdx.x; sgi * a.seg < a.n; sgi += blockDim.x)
+      if (base[a.E] + sgi < a.S) { a.seg_expert[base[a.E] + sgi] = -2; a.seg_count[base[a.E] + sgi] = a.n - sgi * a.seg < a.seg ? a.n - sgi * a.seg : a.seg; }
   }
 }
 
 // one block per pair slot: the token's FP8 row and its scales (as row j of the segment's atom set)
 __global__ void __launch_bounds__(128) moe_permute_kernel(const uint8_t* xq, const uint8_t* xs, const int* seg_token, uint8_t* xperm,
-                                                         uint8_t* seg_atoms, int d, int atom_set_bytes) {
+                                                         uint8_t* seg_atoms, int d, int atom_set_bytes, int seg_size) {
   pdl_launch_dependents();
   pdl_wait();
   const int slot = blockIdx.x, tok = seg_token[slot];
@@ -387,7 +388,7 @@ __global__ void __launch_bounds__(128) moe_permute_kernel(const uint8_t* xq, con
   const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)tok * d);
   uint4* dst = reinterpret_cast<uint4*>(xperm + (size_t)slot * d);
   for (int i = threadIdx.x; i < d / 16; i += blockDim.x) dst[i] = src[i];
-  const int KB = d / 32, seg = slot >> 4, j = slot & 15;
+  const int KB = d / 32, seg = slot / seg_size, j = slot % seg_size;
   for (int kb = threadIdx.x; kb < KB; kb += blockDim.x) seg_atoms[(size_t)seg * atom_set_bytes + sf_offset(j, kb, KB)] = xs[(size_t)tok * KB + kb];
 }
 
@@ -466,18 +467,18 @@ extern "C" int sfb_expert_remap(void* ids, int n, int lo, int count, cudaStream_
   return (int)sfb::sfb_launch(sfb::expert_remap_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, (int*)ids, n, lo, count);
 }
 
-extern "C" int sfb_moe_plan(const void* ids, const void* wts, int n, int k, int E, int shared, int S, void* seg_expert, void* seg_count,
+extern "C" int sfb_moe_plan(const void* ids, const void* wts, int n, int k, int E, int shared, int S, int seg, void* seg_expert, void* seg_count,
                             void* seg_weight, void* seg_token, void* pair_pos, cudaStream_t stream) {
-  if (E > 4096) return (int)cudaErrorInvalidValue;
-  sfb::MoePlanArgs a{(const int*)ids, (const float*)wts, n, k, E, shared, S, (int*)seg_expert, (int*)seg_count, (float*)seg_weight,
+  if (E > 4096 || (seg != 16 && seg != 64)) return (int)cudaErrorInvalidValue;
+  sfb::MoePlanArgs a{(const int*)ids, (const float*)wts, n, k, E, shared, S, seg, (int*)seg_expert, (int*)seg_count, (float*)seg_weight,
                      (int*)seg_token, (int*)pair_pos};
   return (int)sfb::sfb_launch(sfb::moe_plan_kernel, dim3(1), dim3(512), (size_t)(3 * E + 1) * sizeof(int), stream, a);
 }
 extern "C" int sfb_moe_permute(const void* xq, const void* xs, const void* seg_token, void* xperm, void* seg_atoms, int slots, int d,
-                               int atom_set_bytes, cudaStream_t stream) {
-  if (d % 32) return (int)cudaErrorInvalidValue;
+                               int atom_set_bytes, int seg_size, cudaStream_t stream) {
+  if (d % 32 || seg_size < 1) return (int)cudaErrorInvalidValue;
   return (int)sfb::sfb_launch(sfb::moe_permute_kernel, dim3(slots), dim3(128), 0, stream, (const uint8_t*)xq, (const uint8_t*)xs,
-                              (const int*)seg_token, (uint8_t*)xperm, (uint8_t*)seg_atoms, d, atom_set_bytes);
+                              (const int*)seg_token, (uint8_t*)xperm, (uint8_t*)seg_atoms, d, atom_set_bytes, seg_size);
 }
 extern "C" int sfb_moe_combine(const void* ypair, const void* pair_pos, void* y, int n, int k1, int d, int64_t y_stride, cudaStream_t stream) {
   if (d % 4) return (int)cudaErrorInvalidValue;

@@ -52,6 +52,8 @@ struct FoldArgs {
   __nv_bfloat16* xn;             // [n, d] normalised bf16 (may be null)
   uint8_t* xq;                   // [n, d] e4m3 (may be null)
   uint8_t* xs;                   // [n, d/32] ue8m0, row-major
+  float* hss;                    // optional [n]: sum of squares of the row's new residual copies (all hc*d values), for the
+                                 //   many-row coefficient path
   uint8_t* xs_atom;              // optional scale atoms for the tensor-core arm (see atom_mode)
   int atom_mode;                 // 0: rows of one atom set = tokens; 1: one atom set per token, token at row 0
   Status* status;
@@ -67,10 +69,11 @@ __global__ void __cluster_dims__(FOLD_CLUSTER, 1, 1) __launch_bounds__(FOLD_THRE
   const int hc = a.hc, d = a.d;
   const int cpc = d / FOLD_CLUSTER;            // columns of this CTA (multiple of 32)
   const int c_lo = rank * cpc;
-  __shared__ float part_ss;
+  __shared__ float part_ss, part_hss;
   __shared__ float sh[32];
   pdl_launch_dependents();
   pdl_wait();
+  float hsq = 0.f;
 
   if (a.has_post && a.flags[0] != nullptr) {
     const uint32_t want = (a.epoch_ptr ? *a.epoch_ptr : 0u) + a.epoch_add;
@@ -127,17 +130,23 @@ __global__ void __cluster_dims__(FOLD_CLUSTER, 1, 1) __launch_bounds__(FOLD_THRE
       float v = 0.f;
 #pragma unroll
       for (int c = 0; c < MAX_HC; ++c)
-        if (c < hc) v += ap[c] * x[c];
+        if (c < hc) { v += ap[c] * x[c]; hsq += x[c] * x[c]; }
       v = bfr(v);
       xh[it] = v;
       ss += v * v;
     }
   }
   ss = block_sum(ss, sh);
-  if (threadIdx.x == 0) part_ss = ss;
+  if (a.hss) hsq = block_sum(hsq, sh);
+  if (threadIdx.x == 0) { part_ss = ss; part_hss = hsq; }
   cluster.sync();
   float total = 0.f;
   for (int r = 0; r < FOLD_CLUSTER; ++r) total += *cluster.map_shared_rank(&part_ss, r);
+  if (a.hss && rank == 0 && threadIdx.x == 0) {
+    float t2 = 0.f;
+    for (int r = 0; r < FOLD_CLUSTER; ++r) t2 += *cluster.map_shared_rank(&part_hss, r);
+    a.hss[row] = t2;
+  }
   cluster.sync();  // nobody leaves while its shared memory may still be read
   const float rsx = rsqrtf(total / (float)d + a.norm_eps);
   const int KB = d / 32;
@@ -285,6 +294,58 @@ __global__ void __launch_bounds__(COEF_THREADS) seam_coef_kernel(CoefArgs a) {
   }
 }
 
+// Many-row coefficient path, last step: the predictor dots come from a bf16 tensor-core GEMM of the flattened residual
+// rows against the predictor matrix split in two bf16 terms (rows 0..mix-1 = high parts, mix..2*mix-1 = low parts), the
+// sum of squares from seam_fold.  One warp per row adds the two terms and runs the sigmoid / softmax / Sinkhorn tail.
+struct CoefFinishArgs {
+  const float* acc;              // [n, acc_stride]: column m = high-term dot of mix m, column mix + m = low-term dot
+  int acc_stride;
+  const float* hss;              // [n]
+  const float* hc_scale;
+  const float* hc_base;
+  float* coef;                   // [n, coef_stride]
+  int n, hc, d, mix, iters;
+  float norm_eps, hc_eps;
+};
+
+__global__ void __launch_bounds__(128) seam_coef_finish_kernel(CoefFinishArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= a.n) return;
+  const int hc = a.hc;
+  const float* ac = a.acc + (size_t)row * a.acc_stride;
+  auto tot = [&](int m) { return ac[m] + ac[a.mix + m]; };
+  const float rs = rsqrtf(a.hss[row] / (float)(hc * a.d) + a.norm_eps);
+  float* cp = a.coef + (size_t)row * coef_stride(hc);
+  if (lane < hc) {
+    const float m0 = tot(lane) * rs, m1 = tot(hc + lane) * rs;
+    cp[lane] = 1.f / (1.f + expf(-(m0 * a.hc_scale[0] + a.hc_base[lane]))) + a.hc_eps;
+    cp[hc + lane] = 2.f / (1.f + expf(-(m1 * a.hc_scale[1] + a.hc_base[hc + lane])));
+  }
+  const int nel = hc * hc;
+  const bool on = lane < nel;
+  float v = on ? tot(2 * hc + lane) * rs * a.hc_scale[2] + a.hc_base[2 * hc + lane] : -1e30f;
+  float mx = v;
+  for (int o = 1; o < hc; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float e = on ? expf(v - mx) : 0.f;
+  float rsum = e;
+  for (int o = 1; o < hc; o <<= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
+  float c = e / rsum + a.hc_eps;
+  float csum = c;
+  for (int o = hc; o < nel; o <<= 1) csum += __shfl_xor_sync(0xffffffffu, csum, o);
+  c = c / (csum + a.hc_eps);
+  for (int it = 1; it < a.iters; ++it) {
+    float r2 = c;
+    for (int o = 1; o < hc; o <<= 1) r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+    c = c / (r2 + a.hc_eps);
+    float c2 = c;
+    for (int o = hc; o < nel; o <<= 1) c2 += __shfl_xor_sync(0xffffffffu, c2, o);
+    c = c / (c2 + a.hc_eps);
+  }
+  if (on) cp[2 * hc + lane] = c;
+}
+
 }  // namespace sfb
 
 using namespace sfb;
@@ -299,7 +360,7 @@ int sfb_seam_fold(void* h, const void* const* y_ptrs, const void* const* flag_pt
                   uint32_t epoch_add, uint64_t wait_ns, int W,
                   int has_post, const float* coef_prev, const float* a_pre, int a_stride, void* ysum,
                   const float* norm_w, void* xn, void* xq, void* xs, void* xs_atom, int atom_mode, void* status,
-                  int n, int hc, int d, float norm_eps, cudaStream_t stream) {
+                  int n, int hc, int d, float norm_eps, float* hss, cudaStream_t stream) {
   if (hc > MAX_HC || W > 8 || (hc & (hc - 1)) || d % (32 * FOLD_CLUSTER) || d > FOLD_CLUSTER * FOLD_THREADS * FOLD_MAX_IT)
     return (int)cudaErrorInvalidValue;
   FoldArgs a{};
@@ -311,7 +372,7 @@ int sfb_seam_fold(void* h, const void* const* y_ptrs, const void* const* flag_pt
   a.epoch_ptr = (const uint32_t*)epoch_ptr; a.epoch_add = epoch_add; a.wait_ns = wait_ns ? wait_ns : 2000000000ull; a.W = W; a.has_post = has_post; a.coef_prev = coef_prev; a.a_pre = a_pre; a.a_stride = a_stride;
   a.ysum = (__nv_bfloat16*)ysum; a.norm_w = norm_w; a.xn = (__nv_bfloat16*)xn; a.xq = (uint8_t*)xq;
   a.xs = (uint8_t*)xs; a.xs_atom = (uint8_t*)xs_atom; a.atom_mode = atom_mode; a.status = (Status*)status;
-  a.n = n; a.hc = hc; a.d = d; a.norm_eps = norm_eps;
+  a.n = n; a.hc = hc; a.d = d; a.norm_eps = norm_eps; a.hss = hss;
   return (int)sfb_launch(seam_fold_kernel, dim3(FOLD_CLUSTER, n), dim3(FOLD_THREADS), 0, stream, a);
 }
 
@@ -325,6 +386,13 @@ int sfb_seam_coef(const void* h, const float* fn, const float* hc_scale, const f
              iters, norm_eps, hc_eps, rb};
   seam_coef_kernel<<<dim3(sfb_seam_nblk(d), (n + rb - 1) / rb), COEF_THREADS, 0, stream>>>(a);
   return SFB_CHECK_LAUNCH();
+}
+
+int sfb_seam_coef_finish(const float* acc, int acc_stride, const float* hss, const float* hc_scale, const float* hc_base,
+                         float* coef_out, int n, int hc, int d, int iters, float norm_eps, float hc_eps, cudaStream_t stream) {
+  if (hc > MAX_HC || (hc & (hc - 1)) || hc * hc > 32) return (int)cudaErrorInvalidValue;
+  CoefFinishArgs a{acc, acc_stride, hss, hc_scale, hc_base, coef_out, n, hc, d, (2 + hc) * hc, iters, norm_eps, hc_eps};
+  return (int)sfb_launch(seam_coef_finish_kernel, dim3((n + 3) / 4), dim3(128), 0, stream, a);
 }
 
 }  // extern "C"

@@ -338,11 +338,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       w.sfa = a.sfa2 + ((size_t)tile * a.katoms_a) * 512;
     }
     w.ks0 = 0; w.nks = skip ? 0 : ksteps;
-    w.b_x0 = 0; w.b_row0 = seg * 16;
+    w.b_x0 = 0; w.b_row0 = seg * NP;
     w.sfb = a.sfb + (size_t)seg * a.katoms_b * 512;
     w.split = 0; w.splits = 1;
     w.tile_id = seg * gridDim.x + tile; w.tiles_total = gridDim.x * gridDim.y;
-    w.out_row0 = seg * 16; w.n_valid = skip ? 0 : a.seg_count[seg]; w.col0 = tile * 128; w.col_limit = a.d;
+    w.out_row0 = seg * NP; w.n_valid = skip ? 0 : a.seg_count[seg]; w.col0 = tile * 128; w.col_limit = a.d;
   } else {  // UM_DOWN: x = column tile of d, y = slot, z = token
     const int tile = blockIdx.x, slot = blockIdx.y, tok = blockIdx.z;
     const int ksteps = (a.inter + UM_BK - 1) / UM_BK;
@@ -634,11 +634,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
 // grid: x = 128-column tile of the intermediate width, y = slot (top_k routed + shared), z = token
 // UM_STAGES = 6 fills one SM's shared memory with a single CTA (few CTAs: decode); 3 lets two CTAs share an SM, so that one's
 // prologue and epilogue hide behind the other's weight stream when a launch has many waves (grouped many-row steps)
-template <int UM_STAGES>
+// NP = token columns: 16 (a token, or a segment of up to 16 pairs) or 64 (many-row steps: segments of up to 64 pairs)
+template <int UM_STAGES, int NP = 16>
 __global__ void __launch_bounds__(UM_THREADS, UM_STAGES <= 3 ? 2 : 1)
 umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
                    const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
-  constexpr int NP = 16;
   extern __shared__ uint8_t smem_raw[];
   using Smem = UmmaSmem<NP, 2, UM_STAGES>;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -646,7 +646,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   const int tile = blockIdx.x, slot = blockIdx.y, tok = blockIdx.z;
   const int il = a.inter;
   const int nks = (a.d + UM_BK - 1) / UM_BK;
-  constexpr uint32_t TMEM_COLS = 64;
+  constexpr uint32_t TMEM_COLS = 2 * NP + 24 <= 64 ? 64 : 256;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
@@ -699,7 +699,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
     sf_g = a.sfa2 + ((size_t)(row_g >> 7) * a.katoms_a) * 512;
     sf_u = a.sfa2 + ((size_t)(row_u >> 7) * a.katoms_a) * 512;
   }
-  const int b_row = grouped ? slot * 16 : tok;
+  const int b_row = grouped ? slot * NP : tok;
   const uint8_t* sfb = a.sfb + (size_t)(grouped ? slot : tok) * a.katoms_b * 512;
   const uint32_t STAGE_TX = 2 * (a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 3 * 512;
   const uint32_t tmem = S.tmem_base;
@@ -749,30 +749,37 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
     const int q = warp & 3;
     const bool got = mbar_wait(&S.acc_full, 0);
     tc_fence_after();
-    uint32_t vg[16], vu[16];
-    tc_ld16(t_g + ((uint32_t)(q * 32) << 16), vg);
-    tc_ld16(t_u + ((uint32_t)(q * 32) << 16), vu);
-    tc_wait_ld();
     const int col = tile * 128 + q * 32 + lane;   // column of the intermediate activation
     const int KBi = il / 32;
-    for (int j = 0; j < (grouped ? count : 1); ++j) {     // accumulator column j = pair j of the segment (one column when ungrouped)
-      const float wj = grouped ? a.seg_weight[slot * 16 + j] : weight;
-      float act = 0.f;
-      if (got && !S.fail && col < il) {
-        const float g = fminf(bfr(__uint_as_float(vg[j])), a.limit);
-        const float u = fminf(fmaxf(bfr(__uint_as_float(vu[j])), -a.limit), a.limit);
-        act = bfr(g / (1.f + expf(-g)) * u * wj);
-      }
-      uint8_t sc;
-      const uint8_t code = warp_quant_fp8(act, &sc);
-      if (got && !S.fail && col < il && !skip) {
-        const size_t row = grouped ? (size_t)slot * 16 + j : (size_t)tok * a.slots + slot;
-        a.act_q[row * il + col] = code;
-        if (lane == 0) {
-          if (a.act_s) a.act_s[row * KBi + col / 32] = sc;
-          if (a.act_sf) {
-            if (grouped) a.act_sf[(size_t)slot * sf_bytes(16, KBi) + sf_offset(j, col / 32, KBi)] = sc;   // one atom set per segment, row j
-            else a.act_sf[row * sf_bytes(1, KBi) + sf_offset(0, col / 32, KBi)] = sc;
+    const int ncol = grouped ? count : 1;         // accumulator column j = pair j of the segment (one column when ungrouped)
+#pragma unroll 1
+    for (int c0 = 0; c0 < NP && c0 < ncol; c0 += 16) {
+      uint32_t vg[16], vu[16];
+      tc_ld16(t_g + ((uint32_t)(q * 32) << 16) + c0, vg);
+      tc_ld16(t_u + ((uint32_t)(q * 32) << 16) + c0, vu);
+      tc_wait_ld();
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        const int j = c0 + jj;
+        if (j >= ncol) break;                     // warp-uniform
+        const float wj = grouped ? a.seg_weight[slot * NP + j] : weight;
+        float act = 0.f;
+        if (got && !S.fail && col < il) {
+          const float g = fminf(bfr(__uint_as_float(vg[jj])), a.limit);
+          const float u = fminf(fmaxf(bfr(__uint_as_float(vu[jj])), -a.limit), a.limit);
+          act = bfr(g / (1.f + expf(-g)) * u * wj);
+        }
+        uint8_t sc;
+        const uint8_t code = warp_quant_fp8(act, &sc);
+        if (got && !S.fail && col < il && !skip) {
+          const size_t row = grouped ? (size_t)slot * NP + j : (size_t)tok * a.slots + slot;
+          a.act_q[row * il + col] = code;
+          if (lane == 0) {
+            if (a.act_s) a.act_s[row * KBi + col / 32] = sc;
+            if (a.act_sf) {
+              if (grouped) a.act_sf[(size_t)slot * sf_bytes(NP, KBi) + sf_offset(j, col / 32, KBi)] = sc;   // one atom set per segment, row j
+              else a.act_sf[row * sf_bytes(1, KBi) + sf_offset(0, col / 32, KBi)] = sc;
+            }
           }
         }
       }
@@ -1120,14 +1127,21 @@ extern "C" {
 // tmapB = permuted activations [segments*16, d] (16-row box); sfb = one atom set per segment (rows = pair slots).
 int sfb_umma_gate_up_grouped(const void* tmapA, const void* tmapA2, const void* tmapB, const void* sfa, const void* sfa2, const void* sfb,
                              const int* seg_expert, const int* seg_count, const float* seg_weight, void* act_q, void* act_sf, int segments,
-                             int d, int inter, float limit, void* status, cudaStream_t stream) {
-  if (inter % 128 || d % 32 || segments < 1) return refuse_args();
+                             int d, int inter, float limit, int seg_size, void* status, cudaStream_t stream) {
+  if (inter % 128 || d % 32 || segments < 1 || (seg_size != 16 && seg_size != 64)) return refuse_args();
   UmmaArgs a{};
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (d / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
   a.a_fp4 = 1; a.top_k = 0; a.slots = 1; a.inter = inter; a.d = d; a.act_q = (uint8_t*)act_q; a.act_sf = (uint8_t*)act_sf; a.limit = limit;
   a.seg_expert = seg_expert; a.seg_count = seg_count; a.seg_weight = seg_weight; a.status = (Status*)status;
   const CUtensorMap* mA = (const CUtensorMap*)tmapA;
   const CUtensorMap* mA2 = (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA);
+  if (seg_size == 64) {      // segments of up to 64 pairs: two 2-stage CTAs per SM (a stage holds 32 KiB of weights and 8 KiB of tokens)
+    const size_t smem64 = sizeof(UmmaSmem<64, 2, 2>) + 1024;
+    static bool done64 = false;
+    if (!done64) { cudaFuncSetAttribute(umma_gateup_kernel<2, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem64); done64 = true; }
+    return (int)sfb_launch(umma_gateup_kernel<2, 64>, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem64, stream, *mA, *mA2,
+                           *(const CUtensorMap*)tmapB, a);
+  }
   if ((inter / 128) * segments > 2 * 148) {      // several waves: two half-depth CTAs per SM
     const size_t smem3 = sizeof(UmmaSmem<16, 2, 3>) + 1024;
     static bool done3 = false;
@@ -1143,13 +1157,19 @@ int sfb_umma_gate_up_grouped(const void* tmapA, const void* tmapA2, const void* 
 
 // out_f [segments*16, d] fp32: one row per pair slot (the caller sums a token's pairs in slot order)
 int sfb_umma_down_grouped(const void* tmapA, const void* tmapA2, const void* tmapB, const void* sfa, const void* sfa2, const void* sfb,
-                          const int* seg_expert, const int* seg_count, float* out_f, int segments, int d, int inter, void* status,
-                          cudaStream_t stream) {
-  if (d % 128 || inter % 128 || segments < 1) return refuse_args();
+                          const int* seg_expert, const int* seg_count, float* out_f, int segments, int d, int inter, int seg_size,
+                          void* status, cudaStream_t stream) {
+  if (d % 128 || inter % 128 || segments < 1 || (seg_size != 16 && seg_size != 64)) return refuse_args();
   UmmaArgs a{};
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (inter / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
   a.a_fp4 = 1; a.mode = UM_DOWN_GROUPED; a.inter = inter; a.d = d; a.out_f = out_f; a.out_stride = d; a.seg_expert = seg_expert;
   a.seg_count = seg_count; a.status = (Status*)status; a.splits = 1;
+  if (seg_size == 64) {
+    apply_push(a); apply_gather(a);
+    a.tok_tiles = 1;
+    return (int)launch_umma_t<64, false, 3>((const CUtensorMap*)tmapA, (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA),
+                                            (const CUtensorMap*)tmapB, a, dim3(d / 128, segments, 1), stream);
+  }
   if ((d / 128) * segments > 4 * 148) {      // many waves of 16-k-step CTAs: three 3-stage CTAs per SM
     apply_push(a); apply_gather(a);
     a.tok_tiles = 1;

@@ -135,6 +135,8 @@ class Engine:
         self.supports_headless = True    # step(head=False) for prompt chunks whose rows are not sampled
         self.group_moe = True        # rows steps of 4+ rows run the experts grouped by expert (same bits, fewer weight reads)
         self.bulk_attention = True   # rows steps of 65+ rows run attention on tcgen05 (csrc/k_attn_tc.cu)
+        self.index_tc = arm == "tc"  # indexer scores on tcgen05 (csrc/k_index_tc.cu); the CUDA-core kernel otherwise
+        self._uniform_lane = False   # set per step: every row belongs to one lane (rows of one sequence)
         self.drafter = bool(drafter and weights.mtp_layers)
         self.kv = KVCache(cfg, max_lanes, max_context, max_rows, self.dev, lane_budget_bytes, draft_stages=self.drafter)
         R, d, hc, hd, q = max_rows, cfg.hidden_size, cfg.hc_mult, cfg.head_dim, cfg.q_lora_rank
@@ -308,13 +310,14 @@ class Engine:
         if isinstance(y_parts, tuple):      # fused collective: (slots, flags, epoch_add)
             y_parts, flags, epoch_add = y_parts
             epoch_ptr = self.comm.epoch_ptr
+        bulk_coef = n > 128 and self.tcb is not None and fn is not None and engram_j is None
         N.seam_fold(self.h, y_parts, None if first else prev, self.w.onehot if first else prev,
                     0 if first else prev.stride(0), norm_w, self.xn, self.xq if quant else None,
                     self.xs if quant else None, n, cfg.hc_mult, cfg.hidden_size, cfg.norm_eps, status=self.status,
                     flags=flags, epoch_ptr=epoch_ptr, epoch_add=epoch_add,
                     wait_ns=self.comm.wait_ns if flags is not None else 0,
                     xs_atom=None if (self.tcl is None or not quant) else (self.tcb.xs_atom if atoms == 0 else self.tcb.xs_atom_tok),
-                    atom_mode=atoms)
+                    atom_mode=atoms, hss=self._coef_bulk()["hss"] if bulk_coef else None)
         self._k()
         if engram_j is not None:
             # the memory writes into the block's input after the previous block's output has been folded in: apply it, then
@@ -331,12 +334,51 @@ class Engine:
             side = self._side_stream
             side.wait_event(ev)
             with torch.cuda.stream(side):
-                N.seam_coef(self.h, fn, scale, base, self.partials, self.seam_tickets, self.coef[k % 2], n, cfg.hc_mult,
-                            cfg.hidden_size, cfg.hc_sinkhorn_iters, cfg.norm_eps, cfg.hc_eps)
+                if bulk_coef:
+                    # many rows: the predictor dots as one bf16 tensor-core GEMM over the flattened residual rows (the fp32
+                    # predictor matrix enters as a high and a low bf16 term), then one warp per row for the Sinkhorn tail
+                    cb = self._coef_bulk()
+                    hcd = cfg.hc_mult * cfg.hidden_size
+                    N.umma_bf16(self._fn2_map(fn), self._bf16_map(self.h, self.max_rows, hcd), n, 2 * self.mix, hcd, splits=cb["splits"],
+                                scratch=cb["scratch"], tickets=cb["tickets"], out_f=cb["acc"], out_stride=cb["acc"].stride(0),
+                                status=self.status)
+                    N.seam_coef_finish(cb["acc"], cb["hss"], scale, base, self.coef[k % 2], n, cfg.hc_mult, cfg.hidden_size,
+                                       cfg.hc_sinkhorn_iters, cfg.norm_eps, cfg.hc_eps)
+                    self._k()
+                else:
+                    N.seam_coef(self.h, fn, scale, base, self.partials, self.seam_tickets, self.coef[k % 2], n, cfg.hc_mult,
+                                cfg.hidden_size, cfg.hc_sinkhorn_iters, cfg.norm_eps, cfg.hc_eps)
                 done = torch.cuda.Event()
                 done.record(side)
             self._coef_event = done
             self._k()
+
+    def _coef_bulk(self) -> dict:
+        """Buffers of the many-row coefficient path (own split-K scratch: it runs on the side stream beside the main GEMMs)."""
+        cb = self.__dict__.get("_coef_bulk_buf")
+        if cb is None:
+            R, dev = self.max_rows, self.dev
+            splits = 16
+            tok_tiles = (R + 127) // 128
+            cb = self._coef_bulk_buf = dict(
+                splits=splits, hss=torch.zeros((R,), dtype=torch.float32, device=dev),
+                acc=torch.zeros((R, 64), dtype=torch.float32, device=dev),
+                scratch=torch.zeros((splits * tok_tiles * 128 * 128,), dtype=torch.float32, device=dev),
+                tickets=torch.zeros((tok_tiles,), dtype=torch.int32, device=dev))
+        return cb
+
+    def _fn2_map(self, fn: torch.Tensor):
+        """Tensor map over the predictor matrix [mix, hc*d] (fp32) as two bf16 terms stacked: rows [0, mix) high, [mix, 2 mix) low."""
+        cache = self.__dict__.setdefault("_fn2", {})
+        key = fn.data_ptr()
+        ent = cache.get(key)
+        if ent is None:
+            fn = fn.reshape(fn.shape[0], -1)
+            hi = fn.to(torch.bfloat16)
+            lo = (fn - hi.float()).to(torch.bfloat16)
+            fn2 = torch.cat([hi, lo], 0).contiguous()
+            ent = cache[key] = (fn2, N.bf16_map(fn2, fn2.shape[0], fn2.shape[1], 128))
+        return ent[1]
 
     def _tc_dense(self, M, xq_buf, x_rows, atoms, n, N_, K, out_b, out_stride=None, groups=1, pair=0, out_q=None,
                   out_q_atom=None):
@@ -438,23 +480,34 @@ class Engine:
         owner = cfg.kv_owner(l)
         if ratio > 0 and cfg.is_index_source(l):
             inh, idh = cfg.index_n_heads, cfg.index_head_dim
-            N.index_q(self.qfull, self.qfull.stride(0), self.hl * hd, self.aux_raw, self.aux_raw.stride(0),
-                      L.aux_off_wproj, invf, self.row_pos, self.qi, self.wt, n, inh, idh, rd,
-                      idh ** -0.5 * inh ** -0.5); self._k()
             max_len = min(len_bucket // ratio + 1, kv.max_entries[owner])
             use_cand = cfg.uses_candidates(l)
-            N.index_scores(self.qi, self.wt, kv.ik_q[owner], kv.ik_s[owner], self.row_lane, self.row_pos,
-                           self.cand if use_cand else None, cfg.candidate_block_size, self.scores, n, inh, idh,
-                           ratio, max_len); self._k()
+            tc_index = self.index_tc and self.tcb is not None and inh == 32 and idh == 128
+            if tc_index:
+                # scores on tensor cores: MXFP4 queries (packed, with scale atoms) against the MXFP4 index keys; four consecutive
+                # rows of one sequence share a key tile when the whole step belongs to one lane
+                ib = self._index_bufs()
+                rpg = 4 if (self._uniform_lane and n >= 4) else 1
+                N.index_q4(self.qfull, self.qfull.stride(0), self.hl * hd, self.aux_raw, self.aux_raw.stride(0), L.aux_off_wproj,
+                           invf, ib["q4"], ib["q_atoms"], self.wt, n, inh, idh, rd, rpg, idh ** -0.5 * inh ** -0.5); self._k()
+                N.index_scores_tc(self._index_kmap(owner), ib["tq4"] if rpg == 4 else ib["tq1"], kv.ik_s[owner], kv.max_entries[owner],
+                                  ib["q_atoms"], self.wt, self.row_lane, self.row_pos, self.cand if use_cand else None,
+                                  cfg.candidate_block_size, self.scores, n, ratio, max_len, rpg, status=self.status); self._k()
+            else:
+                N.index_q(self.qfull, self.qfull.stride(0), self.hl * hd, self.aux_raw, self.aux_raw.stride(0),
+                          L.aux_off_wproj, invf, self.row_pos, self.qi, self.wt, n, inh, idh, rd,
+                          idh ** -0.5 * inh ** -0.5); self._k()
+                N.index_scores(self.qi, self.wt, kv.ik_q[owner], kv.ik_s[owner], self.row_lane, self.row_pos,
+                               self.cand if use_cand else None, cfg.candidate_block_size, self.scores, n, inh, idh,
+                               ratio, max_len); self._k()
             if l == cfg.candidate_source_layer:
                 bs = cfg.candidate_block_size
                 mb = min((max_len + bs - 1) // bs, self.max_blocks)
                 N.hsi_blockmax(self.scores, self.row_pos, ratio, bs, self.bscore, mb, n); self._k()
-                N.select_topk(self.bscore, self.row_pos, ratio, bs, mb, cfg.candidate_topk_blocks, self.cand_ids,
-                              self.cand_cnt, n); self._k()
+                self._select(self.bscore, ratio, bs, mb, cfg.candidate_topk_blocks, self.cand_ids, self.cand_cnt, n)
                 N.hsi_mark(self.cand_ids, cfg.candidate_topk_blocks, self.cand, mb, n)
                 self.launches_per_step += 2 if self._counting else 0
-            N.select_topk(self.scores, self.row_pos, ratio, 1, max_len, cfg.index_topk, self.sel, self.sel_cnt, n); self._k()
+            self._select(self.scores, ratio, 1, max_len, cfg.index_topk, self.sel, self.sel_cnt, n)
             self._dbg(f"L{l}.iscore", self.scores, n)
         has_c = ratio > 0
         tc_wo_a = T is not None and T.wo_a is not None
@@ -515,48 +568,92 @@ class Engine:
                 N.gemv(N.WF_FP8, L.wo_b, L.wo_b_sf, self.gl * ol, d, self.gl * ol, m, xb=self.oa[r0:], x_quant=True,
                        out_b=self.y_attn[r0:]); self._k()
 
+    SELECT_CHUNK = 16384    # entries per block of the long-row select
+
+    def _select(self, scores, ratio, len_div, max_len, K, ids, cnt, n) -> None:
+        """Top-K per row: one block per row, or - for few rows over a long context - several blocks per row and a merge."""
+        if max_len > 2 * self.SELECT_CHUNK and n <= 64:
+            sb = self.__dict__.setdefault("_select_bufs", {})
+            nch = (max_len + self.SELECT_CHUNK - 1) // self.SELECT_CHUNK
+            key = (nch, K)
+            if key not in sb:
+                R = min(self.max_rows, 64)
+                i32 = dict(dtype=torch.int32, device=self.dev)
+                sb[key] = (torch.zeros((R, nch, K), **i32), torch.zeros((R, nch), **i32), torch.zeros((R, nch * K), **i32))
+            t_ids, t_cnt, t_list = sb[key]
+            N.select_topk_long(scores, self.row_pos, ratio, len_div, max_len, K, ids, cnt, n, self.SELECT_CHUNK, t_ids, t_cnt, t_list)
+            self._k(); self._k()
+            return
+        N.select_topk(scores, self.row_pos, ratio, len_div, max_len, K, ids, cnt, n); self._k()
+
+    def _index_bufs(self) -> dict:
+        ib = self.__dict__.get("_index_buf")
+        if ib is None:
+            cfg, R, dev = self.cfg, self.max_rows, self.dev
+            inh, idh = cfg.index_n_heads, cfg.index_head_dim
+            q4 = torch.zeros((R * inh, idh // 2), dtype=torch.uint8, device=dev)
+            ib = self._index_buf = dict(q4=q4, q_atoms=torch.full((R * 512,), 127, dtype=torch.uint8, device=dev),
+                                        tq1=N.TensorMap(q4, R * inh, idh, idh // 2, 32, fp4=True),
+                                        tq4=N.TensorMap(q4, R * inh, idh, idh // 2, 128, fp4=True), kmaps={})
+        return ib
+
+    def _index_kmap(self, owner: int):
+        """FP4 tensor map over the index keys of every lane of one cache owner, as [lanes * entries, 128]."""
+        ib = self._index_bufs()
+        m = ib["kmaps"].get(owner)
+        if m is None:
+            t = self.kv.ik_q[owner]
+            rows = t.shape[0] * t.shape[1]
+            m = ib["kmaps"][owner] = N.TensorMap(t, rows, self.cfg.index_head_dim, self.cfg.index_head_dim // 2, 128, fp4=True)
+        return m
+
     GROUP_MIN_ROWS = 4      # from this many rows on, the step's (token, expert) pairs are sorted by expert
 
-    def _group_segments(self, n: int, k: int, E_local: int) -> int:
-        """Segments launched for n rows: enough for every expert in use plus the experts with more than 16 pairs, plus the
-        shared expert's; fixed per row count so that a captured graph stays valid."""
+    def _group_segments(self, n: int, k: int, E_local: int, seg: int = 16) -> int:
+        """Segments launched for n rows: enough for every expert in use plus the experts with more than one segment's worth of
+        pairs, plus the shared expert's; fixed per row count so that a captured graph stays valid."""
         P = n * k
-        return min(P, E_local + P // 16) + (n + 15) // 16
+        return min(P, E_local + P // seg) + (n + seg - 1) // seg
 
-    def _group_buffers(self):
-        if getattr(self, "_grp", None) is None:
+    GROUP_WIDE_ROWS = 512   # from this many rows on, segments hold up to 64 pairs (an expert's weights serve four times the rows)
+
+    def _group_buffers(self, seg: int = 16):
+        grp = self.__dict__.setdefault("_grp", {})
+        if seg not in grp:
             from ... import codecs as CC
             cfg, dev, R = self.cfg, self.dev, self.max_rows
             d, il = cfg.hidden_size, self.il
-            S = self._group_segments(R, cfg.top_k, self.w.experts_local or cfg.n_routed_experts)
+            S = self._group_segments(R, cfg.top_k, self.w.experts_local or cfg.n_routed_experts, seg)
             u8 = dict(dtype=torch.uint8, device=dev)
             g = dict(S=S,
                      seg_expert=torch.full((S,), -1, dtype=torch.int32, device=dev), seg_count=torch.zeros((S,), dtype=torch.int32, device=dev),
-                     seg_weight=torch.zeros((S * 16,), dtype=torch.float32, device=dev), seg_token=torch.full((S * 16,), -1, dtype=torch.int32, device=dev),
+                     seg_weight=torch.zeros((S * seg,), dtype=torch.float32, device=dev), seg_token=torch.full((S * seg,), -1, dtype=torch.int32, device=dev),
                      pair_pos=torch.full((R * (cfg.top_k + 1),), -1, dtype=torch.int32, device=dev),
-                     xperm=torch.zeros((S * 16, d), **u8), x_atoms=torch.full((S, CC.sf_bytes(16, d // 32)), 127, **u8),
-                     act_q=torch.zeros((S * 16, il), **u8), act_sf=torch.full((S, CC.sf_bytes(16, il // 32)), 127, **u8),
-                     ypair=torch.zeros((S * 16, d), dtype=torch.float32, device=dev))
-            g["tmap_x"] = N.TensorMap(g["xperm"], S * 16, d, d, 16)
-            g["tmap_act"] = N.TensorMap(g["act_q"], S * 16, il, il, 16)
-            g["x_atom_bytes"] = CC.sf_bytes(16, d // 32)
-            self._grp = g
-        return self._grp
+                     xperm=torch.zeros((S * seg, d), **u8), x_atoms=torch.full((S, CC.sf_bytes(seg, d // 32)), 127, **u8),
+                     act_q=torch.zeros((S * seg, il), **u8), act_sf=torch.full((S, CC.sf_bytes(seg, il // 32)), 127, **u8),
+                     ypair=torch.zeros((S * seg, d), dtype=torch.float32, device=dev))
+            g["tmap_x"] = N.TensorMap(g["xperm"], S * seg, d, d, seg)
+            g["tmap_act"] = N.TensorMap(g["act_q"], S * seg, il, il, seg)
+            g["x_atom_bytes"] = CC.sf_bytes(seg, d // 32)
+            grp[seg] = g
+        return grp[seg]
 
     def _ffn_grouped(self, n: int, T, k: int, shared_here: bool) -> None:
-        """Routed + shared experts for n rows with each expert's weights read once per segment of 16 pairs (csrc/k_moe.cu moe_plan).
+        """Routed + shared experts for n rows with each expert's weights read once per segment of pairs (csrc/k_moe.cu moe_plan).
         Per-pair arithmetic and the per-token slot-order sum are those of the ungrouped kernels: the bits do not change."""
         cfg = self.cfg
         d = cfg.hidden_size
-        g = self._group_buffers()
+        seg = 64 if n >= self.GROUP_WIDE_ROWS else 16
+        g = self._group_buffers(seg)
         E_local = self.w.experts_local or cfg.n_routed_experts
-        S = self._group_segments(n, k, E_local)
-        N.moe_plan(self.ids, self.wts, n, k, E_local, shared_here, S, g["seg_expert"], g["seg_count"], g["seg_weight"], g["seg_token"], g["pair_pos"]); self._k()
-        N.moe_permute(self.xq, self.xs, g["seg_token"], g["xperm"], g["x_atoms"], S * 16, d, g["x_atom_bytes"]); self._k()
+        S = self._group_segments(n, k, E_local, seg)
+        N.moe_plan(self.ids, self.wts, n, k, E_local, shared_here, S, g["seg_expert"], g["seg_count"], g["seg_weight"], g["seg_token"], g["pair_pos"],
+                   seg=seg); self._k()
+        N.moe_permute(self.xq, self.xs, g["seg_token"], g["xperm"], g["x_atoms"], S * seg, d, g["x_atom_bytes"], seg=seg); self._k()
         N.umma_gate_up_grouped(T.w13.tmap, T.s13.tmap, g["tmap_x"], T.w13.atoms, T.s13.atoms, g["x_atoms"], g["seg_expert"], g["seg_count"],
-                               g["seg_weight"], g["act_q"], g["act_sf"], S, d, self.il, cfg.swiglu_limit, status=self.status); self._k()
+                               g["seg_weight"], g["act_q"], g["act_sf"], S, d, self.il, cfg.swiglu_limit, status=self.status, seg=seg); self._k()
         N.umma_down_grouped(T.w2.tmap, T.s2.tmap, g["tmap_act"], T.w2.atoms, T.s2.atoms, g["act_sf"], g["seg_expert"], g["seg_count"], g["ypair"],
-                            S, d, self.il, status=self.status); self._k()
+                            S, d, self.il, status=self.status, seg=seg); self._k()
         N.moe_combine(g["ypair"], g["pair_pos"], self.y_ffn, n, k + 1, d, self.y_ffn.stride(0)); self._k()
 
     def _ffn(self, n: int, L: LayerW, l: int = 0, T="auto", E: int | None = None, k: int | None = None, sub: int | None = None):
@@ -966,6 +1063,7 @@ class Engine:
         self.temp[:n].copy_(io.temp[:n], non_blocking=True)
         self.seed[:n].copy_(io.seed[:n], non_blocking=True)
         stop_after = self.decoder_skip_layer if skip_decoder else (None if head else len(self.w.layers))
+        self._uniform_lane = n >= 4 and len(set(lanes)) == 1
         self.run_rows(n, self._bucket(int(max(positions))), stop_after, head_from=n - 1 if head == "last" else 0)
         if not sync:
             return self.tokens_out[:n]
@@ -984,6 +1082,8 @@ class Engine:
         key = (n, len_bucket) if stop_after is None else (n, len_bucket, stop_after)
         if head_from:
             key = key + ("head_from", head_from)
+        if self._uniform_lane:
+            key = key + ("one_lane",)
         g = self.graphs.get(key)
         if g is None:
             # warm-up run outside capture (first-call attribute set-up, lazy module loading)

@@ -61,7 +61,7 @@ def coef_stride(hc: int) -> int:
 
 
 def seam_fold(h, y_parts, coef_prev, a_pre, a_stride, norm_w, xn, xq, xs, n, hc, d, norm_eps, ysum=None,
-              flags=None, epoch_ptr=None, epoch_add=0, wait_ns=0, status=None, xs_atom=None, atom_mode=0):
+              flags=None, epoch_ptr=None, epoch_add=0, wait_ns=0, status=None, xs_atom=None, atom_mode=0, hss=None):
     """Critical-path half of an mHC seam (see csrc/k_seam.cu).  ``y_parts``: list of W partial outputs
     (tensors or raw device addresses) or None for the first seam of a forward."""
     has_post = y_parts is not None
@@ -71,7 +71,7 @@ def seam_fold(h, y_parts, coef_prev, a_pre, a_stride, norm_w, xn, xq, xs, n, hc,
     ep = c_void_p(epoch_ptr) if isinstance(epoch_ptr, int) else _p(epoch_ptr)
     code = lib().sfb_seam_fold(_p(h), yp, fp, ep, c_uint32(epoch_add), c_uint64(wait_ns), c_int(W), c_int(1 if has_post else 0), _p(coef_prev),
                                _p(a_pre), c_int(a_stride), _p(ysum), _p(norm_w), _p(xn), _p(xq), _p(xs), _p(xs_atom),
-                               c_int(atom_mode), _p(status), c_int(n), c_int(hc), c_int(d), c_float(norm_eps),
+                               c_int(atom_mode), _p(status), c_int(n), c_int(hc), c_int(d), c_float(norm_eps), _p(hss),
                                _stream())
     _check(code, "seam_fold")
 
@@ -81,6 +81,13 @@ def seam_coef(h, fn, hc_scale, hc_base, partials, tickets, coef_out, n, hc, d, i
                                c_int(n), c_int(hc), c_int(d), c_int(iters), c_float(norm_eps), c_float(hc_eps),
                                _stream())
     _check(code, "seam_coef")
+
+
+def seam_coef_finish(acc, hss, hc_scale, hc_base, coef_out, n, hc, d, iters, norm_eps, hc_eps):
+    """Tail of the many-row coefficient path: ``acc`` [n, stride] holds the high- and low-term predictor dots."""
+    _check(lib().sfb_seam_coef_finish(_p(acc), c_int(acc.stride(0)), _p(hss), _p(hc_scale), _p(hc_base), _p(coef_out), c_int(n),
+                                      c_int(hc), c_int(d), c_int(iters), c_float(norm_eps), c_float(hc_eps), _stream()),
+           "seam_coef_finish")
 
 
 # ---- gemv -----------------------------------------------------------------------------------------------
@@ -178,13 +185,13 @@ def router_topk(dots, bias, bias_vl, is_image, ids, wts, n, E, k, route_scale, n
     _check(code, "router_topk")
 
 
-def moe_plan(ids, wts, n, k, E, shared, S, seg_expert, seg_count, seg_weight, seg_token, pair_pos):
-    _check(lib().sfb_moe_plan(_p(ids), _p(wts), c_int(n), c_int(k), c_int(E), c_int(1 if shared else 0), c_int(S), _p(seg_expert), _p(seg_count),
+def moe_plan(ids, wts, n, k, E, shared, S, seg_expert, seg_count, seg_weight, seg_token, pair_pos, seg=16):
+    _check(lib().sfb_moe_plan(_p(ids), _p(wts), c_int(n), c_int(k), c_int(E), c_int(1 if shared else 0), c_int(S), c_int(seg), _p(seg_expert), _p(seg_count),
                               _p(seg_weight), _p(seg_token), _p(pair_pos), _stream()), "moe_plan")
 
 
-def moe_permute(xq, xs, seg_token, xperm, seg_atoms, slots, d, atom_set_bytes):
-    _check(lib().sfb_moe_permute(_p(xq), _p(xs), _p(seg_token), _p(xperm), _p(seg_atoms), c_int(slots), c_int(d), c_int(atom_set_bytes), _stream()),
+def moe_permute(xq, xs, seg_token, xperm, seg_atoms, slots, d, atom_set_bytes, seg=16):
+    _check(lib().sfb_moe_permute(_p(xq), _p(xs), _p(seg_token), _p(xperm), _p(seg_atoms), c_int(slots), c_int(d), c_int(atom_set_bytes), c_int(seg), _stream()),
            "moe_permute")
 
 
@@ -192,16 +199,17 @@ def moe_combine(ypair, pair_pos, y, n, k1, d, y_stride):
     _check(lib().sfb_moe_combine(_p(ypair), _p(pair_pos), _p(y), c_int(n), c_int(k1), c_int(d), c_int64(y_stride), _stream()), "moe_combine")
 
 
-def umma_gate_up_grouped(tmap_a, tmap_a2, tmap_b, sfa, sfa2, sfb, seg_expert, seg_count, seg_weight, act_q, act_sf, segments, d, inter, limit, status=None):
+def umma_gate_up_grouped(tmap_a, tmap_a2, tmap_b, sfa, sfa2, sfb, seg_expert, seg_count, seg_weight, act_q, act_sf, segments, d, inter, limit, status=None,
+                         seg=16):
     _check(lib().sfb_umma_gate_up_grouped(c_void_p(tmap_a.ptr), c_void_p(tmap_a2.ptr) if tmap_a2 else None, c_void_p(tmap_b.ptr), _p(sfa), _p(sfa2),
                                           _p(sfb), _p(seg_expert), _p(seg_count), _p(seg_weight), _p(act_q), _p(act_sf), c_int(segments), c_int(d),
-                                          c_int(inter), c_float(limit), _p(status), _stream()), "umma_gate_up_grouped")
+                                          c_int(inter), c_float(limit), c_int(seg), _p(status), _stream()), "umma_gate_up_grouped")
 
 
-def umma_down_grouped(tmap_a, tmap_a2, tmap_b, sfa, sfa2, sfb, seg_expert, seg_count, out_f, segments, d, inter, status=None):
+def umma_down_grouped(tmap_a, tmap_a2, tmap_b, sfa, sfa2, sfb, seg_expert, seg_count, out_f, segments, d, inter, status=None, seg=16):
     _check(lib().sfb_umma_down_grouped(c_void_p(tmap_a.ptr), c_void_p(tmap_a2.ptr) if tmap_a2 else None, c_void_p(tmap_b.ptr), _p(sfa), _p(sfa2),
-                                       _p(sfb), _p(seg_expert), _p(seg_count), _p(out_f), c_int(segments), c_int(d), c_int(inter), _p(status),
-                                       _stream()), "umma_down_grouped")
+                                       _p(sfb), _p(seg_expert), _p(seg_count), _p(out_f), c_int(segments), c_int(d), c_int(inter), c_int(seg),
+                                       _p(status), _stream()), "umma_down_grouped")
 
 
 def expert_remap(ids, n, lo, count):
@@ -428,3 +436,28 @@ def attn_tc(q, q_stride, rope, row_lane, row_pos, win_q, win_s, ckv_q, ckv_s, se
         c_int(heads), c_int(hd), c_int(rd), c_int(window), c_int(ring), c_float(scale), _p(win_lo), _p(win_hi), _p(status),
         _stream())
     _check(code, "attn_tc")
+
+
+# ---- indexer on tensor cores ---------------------------------------------------------------------------------
+def index_q4(qraw, q_stride, q_off, wraw, w_stride, w_off, rope, q4, q_atoms, wt, n, inh, idh, rd, rows_per_group, wscale):
+    _check(lib().sfb_index_q4(_p(qraw), c_int64(q_stride), c_int64(q_off), _p(wraw), c_int64(w_stride), c_int64(w_off), _p(rope),
+                              c_int(rope.stride(0) // 2), _p(q4), _p(q_atoms), _p(wt), c_int(n), c_int(inh), c_int(idh), c_int(rd),
+                              c_int(rows_per_group), c_float(wscale), _stream()), "index_q4")
+
+
+def index_scores_tc(tmap_k, tmap_q, ik_s, lane_rows, q_atoms, wt, row_lane, row_pos, cand, cand_block, scores, n, ratio, max_len,
+                    rows_per_group, status=None):
+    """``tmap_k``: FP4 map over the index keys of every lane as [lanes * lane_rows, 128]; ``tmap_q``: FP4 map over the packed
+    queries [n * 32, 128] with a box of 32 * rows_per_group rows."""
+    _check(lib().sfb_index_scores_tc(c_void_p(tmap_k.ptr), c_void_p(tmap_q.ptr), _p(ik_s), c_int64(ik_s.stride(0)), c_int64(lane_rows),
+                                     _p(q_atoms), _p(wt), _p(row_lane), _p(row_pos), _p(cand),
+                                     c_int64(cand.stride(0) if cand is not None else 0), c_int(cand_block), _p(scores),
+                                     c_int64(scores.stride(0)), c_int(n), c_int(ratio), c_int(max_len), c_int(rows_per_group),
+                                     _p(status), _stream()), "index_scores_tc")
+
+
+def select_topk_long(scores, row_pos, ratio, len_div, max_len, K, ids, count, n, chunk, tmp_ids, tmp_cnt, tmp_list):
+    """Top-K of long rows: chunks of ``chunk`` entries selected by separate blocks, then merged (same result as select_topk)."""
+    _check(lib().sfb_select_topk_long(_p(scores), c_int64(scores.stride(0)), _p(row_pos), c_int(ratio), c_int(len_div), c_int(max_len),
+                                      c_int(K), _p(ids), _p(count), c_int(n), c_int(chunk), _p(tmp_ids), _p(tmp_cnt), _p(tmp_list),
+                                      _stream()), "select_topk_long")

@@ -20,15 +20,18 @@ def main() -> None:
     ap.add_argument("--decode", action="store_true", help="one row per sequence at the same position instead of a prompt chunk")
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--layers", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=12, help="prompt chunks to run (the last one is the profiled / timed one)")
     args = ap.parse_args()
     from sparkflash_b200.config import reduced_config
     from sparkflash_b200.models.deepseek_v41 import engine as E, prepare as P
     cfg = reduced_config(args.experts, args.layers)
     w = P.prepare_synthetic(cfg, 0, 1)
     rows = args.rows
-    eng = E.Engine(w, max_lanes=max(2, rows if args.decode else 2), max_context=2048, max_rows=max(64, rows), arm="tc",
+    ctx = max(2048, rows * args.steps + 64)
+    eng = E.Engine(w, max_lanes=max(2, rows if args.decode else 2), max_context=ctx, max_rows=max(64, rows), arm="tc",
                    synthetic_scales=True, use_graphs=False)
-    prompt = torch.randint(0, cfg.vocab_size, (2048,)).tolist()
+    prompt = torch.randint(0, cfg.vocab_size, (ctx,)).tolist()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if args.decode:
         for s in range(rows):
             eng.step(prompt[:64], [s] * 64, list(range(64)), head=False)
@@ -38,12 +41,15 @@ def main() -> None:
             eng.step(prompt[:rows], list(range(rows)), [64 + i] * rows)
     else:
         pos = 0
-        for i in range(12):
-            if i == 11:
-                torch.cuda.synchronize(); torch.cuda.profiler.start()
-            eng.step(prompt[pos:pos + rows], [0] * rows, list(range(pos, pos + rows)), head=False); pos += rows
+        for i in range(args.steps):
+            if i == args.steps - 1:
+                torch.cuda.synchronize(); torch.cuda.profiler.start(); ev0.record()
+            eng.step(prompt[pos:pos + rows], [0] * rows, list(range(pos, pos + rows)), head=False, sync=False); pos += rows
+        ev1.record()
     torch.cuda.synchronize(); torch.cuda.profiler.stop()
     eng.check_status()
+    if not args.decode:
+        print(f"last chunk: {rows} rows at context {pos} in {ev0.elapsed_time(ev1):.3f} ms ({args.layers} layers)")
     print("ok")
 
 

@@ -196,3 +196,98 @@ def test_attention_tc_agrees_with_rows_kernel():
     N.attn_tc(*args, b, n, heads, hd, rd, c["window"], c["ring"], hd ** -0.5)
     torch.cuda.synchronize()
     assert (a.float() - b.float()).abs().max() <= 0.02 * a.float().abs().max()
+
+
+def _index_case(n, entries, lanes, seed):
+    g = torch.Generator().manual_seed(seed)
+    inh, idh, rd = 32, 128, 64
+    keys = torch.randn(lanes, entries, idh, generator=g)
+    kq, ks = C.act_quant_fp4(keys)                       # MXFP4: codes + one UE8M0 scale per 32
+    qraw = (torch.randn(n, inh * idh, generator=g) * 0.8).to(torch.bfloat16)
+    wraw = torch.randn(n, inh, generator=g)
+    return dict(inh=inh, idh=idh, rd=rd, kq=kq, ks=ks, qraw=qraw, wraw=wraw)
+
+
+@pytest.mark.parametrize("n,rpg,same_lane", [(3, 1, False), (9, 4, True), (1, 1, True)])
+def test_index_scores_on_tensor_cores_match_cuda_core_kernel(n, rpg, same_lane):
+    """Same quantised queries and keys through the CUDA-core scores kernel and the tcgen05 one; the candidate-block
+    filter and the per-row compressed length mask the same entries."""
+    from sparkflash_b200.models.deepseek_v41 import oracle as O
+    from sparkflash_b200.config import full_config
+    from sparkflash_b200.ops import native as N
+    dev = "cuda"
+    lanes, entries, ratio = 2, 1000, 2
+    c = _index_case(n, entries, lanes, seed=21 + n)
+    inh, idh, rd = c["inh"], c["idh"], c["rd"]
+    pos = torch.tensor([1999, 300, 777, 5, 1200, 64, 1, 1500, 900][:n], dtype=torch.int32)
+    lane = torch.zeros(n, dtype=torch.int32) if same_lane else torch.tensor([i % lanes for i in range(n)], dtype=torch.int32)
+    invf = O.rope_inv_freq(full_config(), True)
+    rope = torch.zeros(n, 1, rd // 2, 2, dtype=torch.float32, device=dev)
+    N.rope_table([invf.to(dev)], [1], pos.to(dev), rope, n)
+    ik_q = C.pack_nibbles(c["kq"]).to(dev).contiguous()      # [lanes, entries, 64]
+    ik_s = c["ks"].to(dev).contiguous()                       # [lanes, entries, 4]
+    qraw, wraw = c["qraw"].to(dev), c["wraw"].to(dev)
+    wscale = idh ** -0.5 * inh ** -0.5
+    bs = 8
+    cand = (torch.rand(n, (entries + bs - 1) // bs, generator=torch.Generator().manual_seed(1)) > 0.3).to(torch.uint8).to(dev)
+    # CUDA-core arm
+    qi = torch.zeros(n, idh, inh, dtype=torch.float32, device=dev)
+    wt = torch.zeros(n, inh, dtype=torch.float32, device=dev)
+    ref = torch.full((n, entries), float("nan"), dtype=torch.float32, device=dev)
+    N.index_q(qraw, inh * idh, 0, wraw, inh, 0, rope[:, 0], pos.to(dev), qi, wt, n, inh, idh, rd, wscale)
+    N.index_scores(qi, wt, ik_q, ik_s, lane.to(dev), pos.to(dev), cand, bs, ref, n, inh, idh, ratio, entries)
+    # tensor-core arm
+    q4 = torch.zeros(n * inh, idh // 2, dtype=torch.uint8, device=dev)
+    q_atoms = torch.full((n * 512,), 127, dtype=torch.uint8, device=dev)
+    wt2 = torch.zeros(n, inh, dtype=torch.float32, device=dev)
+    out = torch.full((n, entries), float("nan"), dtype=torch.float32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    N.index_q4(qraw, inh * idh, 0, wraw, inh, 0, rope[:, 0], q4, q_atoms, wt2, n, inh, idh, rd, rpg, wscale)
+    tk = N.TensorMap(ik_q.view(lanes * entries, idh // 2), lanes * entries, idh, idh // 2, 128, fp4=True)
+    tq = N.TensorMap(q4, n * inh, idh, idh // 2, 32 * rpg, fp4=True)
+    N.index_scores_tc(tk, tq, ik_s, entries, q_atoms, wt2, lane.to(dev), pos.to(dev), cand, bs, out, n, ratio, entries, rpg, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0, status.tolist()
+    assert torch.equal(wt, wt2)
+    for r in range(n):
+        clen = (int(pos[r]) + 1) // ratio
+        a, b = ref[r, :clen].cpu(), out[r, :clen].cpu()
+        assert torch.equal(torch.isinf(a), torch.isinf(b)), r
+        fin = ~torch.isinf(a)
+        if fin.any():
+            # the two query kernels may round a rotated element to neighbouring bf16 values (fused vs separate multiply-add),
+            # which moves one FP4 code: nearly every score agrees to fp32 summation order, none is far off
+            err, scale = (a[fin] - b[fin]).abs(), a[fin].abs().max() + 1e-6
+            assert (err <= 1e-4 * scale).float().mean() >= 0.98 and err.max() <= 5e-2 * scale, (r, err.max(), scale)
+        assert torch.isinf(out[r, clen:]).all()
+
+
+def test_select_long_rows_matches_single_block_select():
+    """The chunked select (several blocks per row, then a merge) returns exactly the ids of the one-block select, ties
+    included (a quantised score column makes many ties; the lowest indices must win)."""
+    from sparkflash_b200.ops import native as N
+    dev = "cuda"
+    n, L, K, chunk = 3, 70000, 512, 16384
+    g = torch.Generator().manual_seed(4)
+    sc = torch.randn(n, L, generator=g)
+    sc[1] = (sc[1] * 4).round() / 4                 # heavy ties
+    sc[2, 1000:] = float("-inf")                    # fewer finite entries than a chunk, more than K
+    sc[0, ::7] = float("-inf")
+    pos = torch.tensor([L - 1, L - 1, 50000], dtype=torch.int32)
+    scd = sc.to(dev)
+    ids1 = torch.zeros(n, K, dtype=torch.int32, device=dev); cnt1 = torch.zeros(n, dtype=torch.int32, device=dev)
+    ids2 = torch.zeros(n, K, dtype=torch.int32, device=dev); cnt2 = torch.zeros(n, dtype=torch.int32, device=dev)
+    nch = (L + chunk - 1) // chunk
+    tmp_ids = torch.zeros(n, nch, K, dtype=torch.int32, device=dev)
+    tmp_cnt = torch.zeros(n, nch, dtype=torch.int32, device=dev)
+    tmp_list = torch.zeros(n, nch * K, dtype=torch.int32, device=dev)
+    N.select_topk(scd, pos.to(dev), 1, 1, L, K, ids1, cnt1, n)
+    N.select_topk_long(scd, pos.to(dev), 1, 1, L, K, ids2, cnt2, n, chunk, tmp_ids, tmp_cnt, tmp_list)
+    torch.cuda.synchronize()
+    assert torch.equal(cnt1, cnt2) and torch.equal(ids1, ids2)
+    # and both follow the rule: value descending, index ascending among equals
+    for r in range(n):
+        ln = int(pos[r]) + 1
+        order = sorted(range(ln), key=lambda i: (-sc[r, i].item(), i))
+        want = sorted(i for i in order[:K] if sc[r, i] > float("-inf"))
+        assert ids1[r, :int(cnt1[r])].tolist() == want
