@@ -394,7 +394,7 @@ def phase_mtp(B: Bench, cfg, extras: dict) -> None:
     finally:
         eng.close()
         del eng, weights
-        torch.cuda.empty_cache()
+        release(torch)
 
 
 def phase_long(B: Bench, weights, cfg, extras: dict) -> None:
@@ -439,7 +439,7 @@ def phase_long(B: Bench, weights, cfg, extras: dict) -> None:
     finally:
         eng.close()
         del eng
-        torch.cuda.empty_cache()
+        release(torch)
 
 
 def phase_ep(B: Bench, cfg, extras: dict) -> None:
@@ -461,7 +461,15 @@ def phase_ep(B: Bench, cfg, extras: dict) -> None:
     finally:
         eng.close()
         del eng, weights
-        torch.cuda.empty_cache()
+        release(torch)
+
+
+def release(torch) -> None:
+    """Give a finished section's device memory back: engines and communicators reference each other, so the cycle
+    collector runs before the caching allocator is emptied."""
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
 
 
 def main() -> None:
@@ -520,15 +528,14 @@ def main() -> None:
     weights_gb, kv_gb = weights.nbytes() / 1e9, eng.kv.nbytes() / 1e9
     eng.close()
     del eng
-    torch.cuda.empty_cache()
+    release(torch)
     if not args.skip_extras:
-        for name, fn in (("long_context", lambda: phase_long(B, weights, cfg, extras)),):
-            try:
-                fn()
-            except Exception as e:
-                extras[f"{name}_error"] = f"{type(e).__name__}: {e}"[:300]
+        try:
+            phase_long(B, weights, cfg, extras)
+        except Exception as e:
+            extras["long_context_error"] = f"{type(e).__name__}: {e}"[:300]
     del weights
-    torch.cuda.empty_cache()
+    release(torch)
     if not args.skip_extras:
         if not args.no_mtp and cfg.n_mtp_stages:
             try:

@@ -175,6 +175,156 @@ __global__ void __cluster_dims__(FOLD_CLUSTER, 1, 1) __launch_bounds__(FOLD_THRE
   }
 }
 
+// Many-row variant of seam_fold: one block per row, no cluster.  A thread owns groups of four consecutive columns, eight
+// lanes share a 32-column scale group; the row sums go through one block reduction.  Same arithmetic per element as the
+// cluster kernel (the sums of squares are added in a different order, so the normalised values may differ in the last bit).
+constexpr int FOLDR_THREADS = 256;
+constexpr int FOLDR_MAX_IT = 8;      // d <= 256 * 4 * 8
+
+__global__ void __launch_bounds__(FOLDR_THREADS) seam_fold_rows_kernel(FoldArgs a) {
+  const int row = blockIdx.x;
+  const int hc = a.hc, d = a.d;
+  __shared__ float sh[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  if (a.has_post && a.flags[0] != nullptr) {
+    const uint32_t want = (a.epoch_ptr ? *a.epoch_ptr : 0u) + a.epoch_add;
+    if (threadIdx.x < a.W && !wait_flag_ge(a.flags[threadIdx.x], want, a.wait_ns))
+      status_set(a.status, ST_TIMEOUT, 2, threadIdx.x, (int)want);
+    __syncthreads();
+  }
+  float post[MAX_HC], comb[MAX_HC * MAX_HC], ap[MAX_HC];
+#pragma unroll
+  for (int c = 0; c < MAX_HC; ++c) {
+    ap[c] = c < hc ? a.a_pre[(size_t)row * a.a_stride + c] : 0.f;
+    post[c] = 0.f;
+  }
+  if (a.has_post) {
+    const float* cp = a.coef_prev + (size_t)row * coef_stride(hc);
+#pragma unroll
+    for (int c = 0; c < MAX_HC; ++c)
+      if (c < hc) post[c] = cp[hc + c];
+#pragma unroll
+    for (int i = 0; i < MAX_HC * MAX_HC; ++i)
+      if (i < hc * hc) comb[i] = cp[2 * hc + i];
+  }
+  float xh[FOLDR_MAX_IT][4];
+  float ss = 0.f, hsq = 0.f;
+#pragma unroll
+  for (int it = 0; it < FOLDR_MAX_IT; ++it) {
+    const int col = (it * FOLDR_THREADS + threadIdx.x) * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) xh[it][e] = 0.f;
+    if (col < d) {
+      float x[MAX_HC][4];
+      __nv_bfloat16* hp = a.h + (size_t)row * hc * d + col;
+#pragma unroll
+      for (int c = 0; c < MAX_HC; ++c) {
+        if (c < hc) {
+          const uint2 u = *reinterpret_cast<const uint2*>(hp + (size_t)c * d);
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+          const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
+          x[c][0] = f0.x; x[c][1] = f0.y; x[c][2] = f1.x; x[c][3] = f1.y;
+        } else {
+          x[c][0] = x[c][1] = x[c][2] = x[c][3] = 0.f;
+        }
+      }
+      if (a.has_post) {
+        float y[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < a.W; ++r) {
+          const uint2 u = *reinterpret_cast<const uint2*>(a.y[r] + (size_t)row * d + col);
+          const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+          const float2 f0 = __bfloat1622float2(y2[0]), f1 = __bfloat1622float2(y2[1]);
+          y[0] += f0.x; y[1] += f0.y; y[2] += f1.x; y[3] += f1.y;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[e] = bfr(y[e]);
+        if (a.ysum) {
+          __nv_bfloat16* yo = a.ysum + (size_t)row * d + col;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) yo[e] = __float2bfloat16_rn(y[e]);
+        }
+        float nx[MAX_HC][4];
+#pragma unroll
+        for (int k = 0; k < MAX_HC; ++k) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float v = post[k] * y[e];
+#pragma unroll
+            for (int j = 0; j < MAX_HC; ++j)
+              if (j < hc && k < hc) v += comb[j * hc + k] * x[j][e];
+            nx[k][e] = bfr(v);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < MAX_HC; ++c) {
+          if (c < hc) {
+            __nv_bfloat162 o2[2] = {__floats2bfloat162_rn(nx[c][0], nx[c][1]), __floats2bfloat162_rn(nx[c][2], nx[c][3])};
+            *reinterpret_cast<uint2*>(hp + (size_t)c * d) = *reinterpret_cast<uint2*>(o2);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[c][e] = nx[c][e];
+          }
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = 0.f;
+#pragma unroll
+        for (int c = 0; c < MAX_HC; ++c)
+          if (c < hc) { v += ap[c] * x[c][e]; hsq += x[c][e] * x[c][e]; }
+        v = bfr(v);
+        xh[it][e] = v;
+        ss += v * v;
+      }
+    }
+  }
+  ss = block_sum(ss, sh);
+  if (a.hss) {
+    hsq = block_sum(hsq, sh);
+    if (threadIdx.x == 0) a.hss[row] = hsq;
+  }
+  const float rsx = rsqrtf(ss / (float)d + a.norm_eps);
+  const int KB = d / 32;
+#pragma unroll
+  for (int it = 0; it < FOLDR_MAX_IT; ++it) {
+    const int col = (it * FOLDR_THREADS + threadIdx.x) * 4;
+    // whole warps are in or out of range (d is a multiple of 128)
+    if (col - (int)(threadIdx.x & 31) * 4 < d) {
+      float v[4];
+      float amax = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[e] = col < d ? bfr(xh[it][e] * rsx * a.norm_w[col + e]) : 0.f;
+        amax = fmaxf(amax, fabsf(v[e]));
+      }
+      if (a.xn && col < d) {
+        __nv_bfloat162 o2[2] = {__floats2bfloat162_rn(v[0], v[1]), __floats2bfloat162_rn(v[2], v[3])};
+        *reinterpret_cast<uint2*>(a.xn + (size_t)row * d + col) = *reinterpret_cast<uint2*>(o2);
+      }
+      if (a.xq) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        if (col < d) {
+          const uint8_t sc = act_scale_code_fp8(amax);
+          const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+          uint32_t q4 = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) q4 |= (uint32_t)enc_e4m3(v[e] * inv) << (8 * e);
+          *reinterpret_cast<uint32_t*>(a.xq + (size_t)row * d + col) = q4;
+          if ((threadIdx.x & 7) == 0) {
+            a.xs[(size_t)row * KB + col / 32] = sc;
+            if (a.xs_atom) {
+              if (a.atom_mode == 0) a.xs_atom[sf_offset(row, col / 32, KB)] = sc;
+              else a.xs_atom[(size_t)row * sf_bytes(1, KB) + sf_offset(0, col / 32, KB)] = sc;
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
 struct CoefArgs {
   const __nv_bfloat16* h;        // [n, hc, d] (already folded)
   const float* fn;               // [mix, hc*d]
@@ -373,6 +523,8 @@ int sfb_seam_fold(void* h, const void* const* y_ptrs, const void* const* flag_pt
   a.ysum = (__nv_bfloat16*)ysum; a.norm_w = norm_w; a.xn = (__nv_bfloat16*)xn; a.xq = (uint8_t*)xq;
   a.xs = (uint8_t*)xs; a.xs_atom = (uint8_t*)xs_atom; a.atom_mode = atom_mode; a.status = (Status*)status;
   a.n = n; a.hc = hc; a.d = d; a.norm_eps = norm_eps; a.hss = hss;
+  if (n > 128 && d % 128 == 0 && d <= FOLDR_THREADS * 4 * FOLDR_MAX_IT)       // many rows: one block per row
+    return (int)sfb_launch(seam_fold_rows_kernel, dim3(n), dim3(FOLDR_THREADS), 0, stream, a);
   return (int)sfb_launch(seam_fold_kernel, dim3(FOLD_CLUSTER, n), dim3(FOLD_THREADS), 0, stream, a);
 }
 

@@ -251,6 +251,14 @@ class Engine:
             self._draft_bv = torch.zeros((max(1, self.world),), dtype=torch.float32, device=dev)
             self._draft_bi = torch.zeros((max(1, self.world),), dtype=torch.int32, device=dev)
         self.graphs: dict[tuple[int, int], torch.cuda.CUDAGraph] = {}
+        # runtime bookkeeping: an optional per-step ledger (runtime/ledger.py) and the launch list every graph was captured from
+        self.ledger = None
+        self.ledger_strict = True
+        self.last_ledger = None
+        self._capturing = False
+        self._graph_counts: dict[tuple, tuple[int, int]] = {}
+        from ...runtime.segments import SegmentCache
+        self.segments = SegmentCache()
         self.launches_per_step = 0
         self._counting = False
         self.min_bucket = 1024
@@ -260,6 +268,8 @@ class Engine:
     def _k(self):
         if self._counting:
             self.launches_per_step += 1
+        if self.ledger is not None and not self._capturing:
+            self.ledger.count("launch")
 
     def _dbg(self, key: str, t: torch.Tensor, n: int) -> None:
         if self.debug is not None:
@@ -273,6 +283,8 @@ class Engine:
         self.graphs.clear()
         if self.comm is not None and hasattr(self.comm, "close"):
             self.comm.close()
+        if self.comm is not None and getattr(self.comm, "engine", None) is self:
+            self.comm.engine = None      # the communicator points back at its engine: break the cycle so both are freed promptly
 
     def check_status(self) -> None:
         st = self.status.tolist()
@@ -707,13 +719,36 @@ class Engine:
                       n, k, d, self.il, cfg.swiglu_limit); self._k()
         N.moe_down(self.act_q, self.act_s, self.ids, L.w2, L.w2_sf, L.s2, L.s2_sf, self.y_ffn, n, k, d, self.il); self._k()
 
-    def _bf16_map(self, t: torch.Tensor, rows: int, K: int):
-        """Cached tensor map over a row-major bf16 matrix for the bf16 tensor-core GEMM."""
+    HEAD_TC_MIN_ROWS = 1 << 30     # rows from which the vocabulary projection runs on the bf16 tensor-core GEMM (off: the
+                                   # CUDA-core kernel keeps a row's logits independent of the step's row count and measured faster)
+
+    def _head(self, hf: int, hn: int) -> None:
+        """Vocabulary-slice logits of rows hf .. hf + hn - 1 (fp32).  One row: the CUDA-core GEMV, which streams the bf16
+        matrix at memory speed.  More rows: the bf16 tensor-core GEMM, every row its own accumulator column (a row's logits
+        do not depend on how many rows share the launch)."""
+        cfg, w = self.cfg, self.w
+        d = cfg.hidden_size
+        if self.tcb is None or hn < self.HEAD_TC_MIN_ROWS or hn > 128 or d % 64:
+            N.gemv(N.WF_BF16, w.head, None, 2 * d, self.vl, d, hn, xb=self.xn[hf:], out_f=self.logits[hf:]); self._k()
+            return
+        x = self.xn
+        if hf:
+            x = self.__dict__.get("_xn_head")
+            if x is None:
+                x = self._xn_head = torch.zeros((128, d), dtype=torch.bfloat16, device=self.dev)
+            x[:hn].copy_(self.xn[hf:hf + hn]); self._k()
+        NP = N.umma_np(hn)
+        N.umma_bf16(self._bf16_map(w.head, self.vl, d), self._bf16_map(x, x.shape[0], d, NP), hn, self.vl, d, out_f=self.logits[hf:],
+                    out_stride=self.logits.stride(0), status=self.status, NP=NP); self._k()
+
+    def _bf16_map(self, t: torch.Tensor, rows: int, K: int, box: int = 128):
+        """Cached tensor map over a row-major bf16 matrix for the bf16 tensor-core GEMM (``box`` rows per tile: 128 for
+        weights, the launch's token-column count for activations)."""
         maps = self.__dict__.setdefault("_bf16_maps", {})
-        key = (t.data_ptr(), rows, K)
+        key = (t.data_ptr(), rows, K, box)
         m = maps.get(key)
         if m is None:
-            m = maps[key] = N.bf16_map(t, rows, K, 128)
+            m = maps[key] = N.bf16_map(t, rows, K, box)
         return m
 
     def _fused(self) -> bool:
@@ -732,6 +767,8 @@ class Engine:
         pushed already when ``pushed``; otherwise the generic push kernel does)."""
         if self.world == 1 or self.comm is None:
             return [y]
+        if self.ledger is not None and not self._capturing:
+            self.ledger.count("collective")
         if not self._fused():
             return self.comm.parts(y, n)
         if not pushed:
@@ -805,11 +842,12 @@ class Engine:
         self._dbg("final_x", self.xn, n); self._dbg("final_h", self.h, n)
         # the head and the sampler run on rows head_from .. n-1 only (a prompt's last chunk samples its last row alone)
         hf, hn = head_from, n - head_from
-        N.gemv(N.WF_BF16, w.head, None, 2 * cfg.hidden_size, self.vl, cfg.hidden_size, hn, xb=self.xn[hf:],
-               out_f=self.logits[hf:]); self._k()
+        self._head(hf, hn)
         N.sample(self.logits[hf:], self.row_pos[hf:], self.temp[hf:], self.seed[hf:], self.mask[hf:] if self.mask is not None else None,
                  self.best_val[self.rank][hf:], self.best_id[self.rank][hf:], hn, self.vl, self.rank * self.vl); self._k()
         R = self.max_rows
+        if self.world > 1 and self.comm is not None and self.ledger is not None and not self._capturing:
+            self.ledger.count("collective")
         if fused:
             sub = 2 * len(w.layers)
             self.comm.push_best(self.best_val, self.best_id, n, sub + 1); self._k(); self._k()
@@ -899,7 +937,7 @@ class Engine:
             y_prev = self._reduce_parts(self.y_ffn, n, 1, 2 * s_ + 1, self._pushed)
             yield ("ffn", l)
         self._seam(n, k, y_prev, None, None, None, w.mtp_norm, quant=False)
-        N.gemv(N.WF_BF16, w.head, None, 2 * d, self.vl, d, n, xb=self.xn, out_f=self.logits); self._k()
+        self._head(0, n)
         # Markov head: position i's logits get a bias that depends on the token chosen for position i - 1 (the anchor for
         # i = 0), then position i is sampled; the chain runs on the device through draft_tokens
         r = w.markov_embed.shape[1]
@@ -1030,6 +1068,9 @@ class Engine:
         n = len(tokens)
         if not 0 < n <= self.max_rows:
             raise ValueError(f"rows {n} out of range 1..{self.max_rows}")
+        if self.ledger is not None:
+            self.ledger.begin()
+            self.ledger.count("h2d", 5)
         self.kv.ensure(lanes, positions)
         if self.engram is not None:
             ids = self.engram.ids_for_step(list(tokens), list(lanes), list(positions))
@@ -1066,9 +1107,14 @@ class Engine:
         self._uniform_lane = n >= 4 and len(set(lanes)) == 1
         self.run_rows(n, self._bucket(int(max(positions))), stop_after, head_from=n - 1 if head == "last" else 0)
         if not sync:
+            if self.ledger is not None:
+                self.last_ledger = self.ledger.end(strict=self.ledger_strict)
             return self.tokens_out[:n]
         io.out[:n].copy_(self.tokens_out[:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        if self.ledger is not None:
+            self.ledger.count("d2h"); self.ledger.count("host_sync")
+            self.last_ledger = self.ledger.end(strict=self.ledger_strict)
         if filters:
             for r, (top_k, top_p) in filters.items():
                 io.out[r] = self.filtered_sample(r, top_k, top_p, float(io.temp[r]), int(io.seed[r]), int(io.pos[r]))
@@ -1086,18 +1132,52 @@ class Engine:
             key = key + ("one_lane",)
         g = self.graphs.get(key)
         if g is None:
-            # warm-up run outside capture (first-call attribute set-up, lazy module loading)
+            # warm-up run outside capture (first-call attribute set-up, lazy module loading); its launch list is kept with the
+            # graph so that a later recording of the same step can be compared with what was captured
+            from ...runtime.segments import recording
+            led, self.ledger = self.ledger, None
             self._counting, self.launches_per_step = True, 0
-            self._forward(n, len_bucket, stop_after, head_from)
+            with recording() as log:
+                self._forward(n, len_bucket, stop_after, head_from)
             self._counting = False
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self._forward(n, len_bucket, stop_after, head_from)
+            self._capturing = True
+            try:
+                with torch.cuda.graph(g):
+                    self._forward(n, len_bucket, stop_after, head_from)
+            finally:
+                self._capturing = False
+                self.ledger = led
             self.graphs[key] = g
+            self.segments.put(key, log, g)
+            colls = 0
+            if self.world > 1 and self.comm is not None:     # two reductions per layer run, plus the winners' exchange when sampled
+                colls = 2 * (len(self.w.layers) if stop_after is None else min(len(self.w.layers), stop_after + 1)) + (stop_after is None)
+            self._graph_counts[key] = (self.launches_per_step, colls)
+        if self.ledger is not None:
+            L, C = self._graph_counts[key]
+            self.ledger.count("launch", L); self.ledger.count("collective", C)
             # the warm-up run already produced this step's result and advanced the caches; replaying
             # the same rows is idempotent (position-addressed writes), so fall through to one replay
         g.replay()
+
+    def verify_segment(self, n: int, len_bucket: int, stop_after: int | None = None, head_from: int = 0) -> None:
+        """Run the step for the staged rows eagerly with the launch recorder on and compare its launch list with the one the
+        captured graph of the same key was recorded from (raises when they differ, or when nothing was captured)."""
+        from ...runtime.segments import recording
+        key = (n, len_bucket) if stop_after is None else (n, len_bucket, stop_after)
+        if head_from:
+            key = key + ("head_from", head_from)
+        if self._uniform_lane:
+            key = key + ("one_lane",)
+        led, self.ledger = self.ledger, None
+        try:
+            with recording() as log:
+                self._forward(n, len_bucket, stop_after, head_from)
+        finally:
+            self.ledger = led
+        self.segments.check(key, log)
 
     # ---- convenience -------------------------------------------------------------------------------------
     def h2d_bytes(self, n: int) -> int:

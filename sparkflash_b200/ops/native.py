@@ -12,6 +12,7 @@ from ctypes import c_float, c_int, c_int64, c_uint32, c_uint64, c_void_p
 import torch
 
 from .. import _lib
+from ..runtime import segments as _segments
 
 
 class NativeError(RuntimeError):
@@ -29,6 +30,7 @@ def _stream():
 def _check(code: int, what: str) -> None:
     if code != 0:
         raise NativeError(f"{what}: CUDA error {code}")
+    _segments.note(what)
 
 
 _declared = False

@@ -291,3 +291,59 @@ def test_select_long_rows_matches_single_block_select():
         order = sorted(range(ln), key=lambda i: (-sc[r, i].item(), i))
         want = sorted(i for i in order[:K] if sc[r, i] > float("-inf"))
         assert ids1[r, :int(cnt1[r])].tolist() == want
+
+
+def test_many_row_seam_matches_the_cluster_kernel_and_bf16_coefficients():
+    """Steps of 129+ rows fold with one block per row and take the predictor dots from the bf16 tensor-core GEMM: residual
+    copies, normalised rows and FP8 codes agree with the few-row kernels, coefficients to the two-term precision."""
+    from sparkflash_b200.ops import native as N
+    dev = "cuda"
+    d, hc, mix, W, n = 5120, 4, 24, 2, 150
+    g = torch.Generator().manual_seed(17)
+    h = (torch.randn(n, hc, d, generator=g) * 0.5).to(torch.bfloat16)
+    ys = [(torch.randn(n, d, generator=g) * 0.3).to(torch.bfloat16).to(dev) for _ in range(W)]
+    fn = (torch.randn(mix, hc * d, generator=g) * 0.05).to(dev)
+    base = (torch.randn(mix, generator=g) * 0.1).to(dev)
+    scale = torch.tensor([1.0, 0.9, 1.1]).to(dev)
+    norm_w = (1 + 0.05 * torch.randn(d, generator=g)).to(dev)
+    cs = N.coef_stride(hc)
+    prev = torch.rand(n, cs, generator=g).to(dev)
+
+    def run(rows: slice, hss=None):
+        m = rows.stop - rows.start
+        hh = h[rows].clone().to(dev)
+        xn = torch.zeros(m, d, dtype=torch.bfloat16, device=dev)
+        xq = torch.zeros(m, d, dtype=torch.uint8, device=dev)
+        xs = torch.zeros(m, d // 32, dtype=torch.uint8, device=dev)
+        pv = prev[rows].contiguous()
+        N.seam_fold(hh, [y[rows].contiguous() for y in ys], pv, pv, pv.stride(0), norm_w, xn, xq, xs, m, hc, d, 1e-20, hss=hss)
+        return hh, xn, xq, xs
+    hss = torch.zeros(n, dtype=torch.float32, device=dev)
+    big = run(slice(0, n), hss)                       # one block per row
+    parts = [run(slice(0, 75)), run(slice(75, n))]    # cluster kernel
+    torch.cuda.synchronize()
+    hh = torch.cat([p[0] for p in parts]); xn = torch.cat([p[1] for p in parts]); xq = torch.cat([p[2] for p in parts])
+    assert torch.equal(big[0], hh)                                      # residual copies: same arithmetic per element
+    assert (big[1].float() - xn.float()).abs().max() <= 2 ** -7 * xn.float().abs().max()
+    assert (big[2] != xq).float().mean() < 0.01                          # codes may move where the row sum's order differs
+    assert torch.allclose(hss.cpu(), hh.float().pow(2).sum((1, 2)).cpu(), rtol=1e-4)
+    # coefficients: few-row kernel vs bf16 GEMM + finish
+    nblk = N.seam_nblk(d)
+    partials = torch.zeros(n, nblk, 1 + mix, device=dev)
+    tickets = torch.zeros(n, dtype=torch.int32, device=dev)
+    ref = torch.zeros(n, cs, device=dev)
+    N.seam_coef(hh, fn, scale, base, partials, tickets, ref, n, hc, d, 20, 1e-20, 1e-6)
+    hi = fn.to(torch.bfloat16); lo = (fn - hi.float()).to(torch.bfloat16)
+    fn2 = torch.cat([hi, lo], 0).contiguous()
+    R = 256
+    hpad = torch.zeros(R, hc, d, dtype=torch.bfloat16, device=dev); hpad[:n] = hh
+    ta, tb = N.bf16_map(fn2, 2 * mix, hc * d, 128), N.bf16_map(hpad, R, hc * d, 128)
+    splits, tt = 16, R // 128
+    scratch = torch.zeros(splits * tt * 128 * 128, dtype=torch.float32, device=dev)
+    tk = torch.zeros(tt, dtype=torch.int32, device=dev)
+    acc = torch.zeros(R, 64, dtype=torch.float32, device=dev)
+    out = torch.zeros(n, cs, device=dev)
+    N.umma_bf16(ta, tb, n, 2 * mix, hc * d, splits=splits, scratch=scratch, tickets=tk, out_f=acc, out_stride=64)
+    N.seam_coef_finish(acc, hss, scale, base, out, n, hc, d, 20, 1e-20, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.allclose(out.cpu(), ref.cpu(), rtol=2e-3, atol=2e-4), (out.cpu() - ref.cpu()).abs().max()

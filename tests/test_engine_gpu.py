@@ -535,3 +535,30 @@ def test_virtual_tensor_parallel_ranks_take_a_128_row_step(tiny):
     big_last, big_toks = run(128, [128])
     small_last, small_toks = run(16, [16] * 8)
     assert big_last[-16:] == small_last and big_toks == small_toks
+
+
+def test_step_ledger_and_segment_identity(tiny):
+    """The engine counts launches, collectives and host<->device crossings per step against a budget, and a captured
+    graph is tied to the launch list it was recorded from."""
+    from sparkflash_b200.models.deepseek_v41 import engine as E
+    from sparkflash_b200.runtime.ledger import Budget, LedgerError, StepLedger
+    cfg, ck, w, orc, dw = tiny
+    eng = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, use_graphs=True)
+    eng.ledger = StepLedger(Budget.for_rows_step(cfg.n_layers, 1, False))
+    prompt = _prompt(cfg, 12, seed=3)
+    eng.step(prompt[:8], [0] * 8, list(range(8)))              # captures
+    eng.step(prompt[:8], [0] * 8, list(range(8)))              # replays
+    got = eng.last_ledger
+    assert got["problems"] == [] and got["collective"] == 0 and got["h2d"] == 5 and got["d2h"] == 1 and got["host_sync"] == 1
+    assert got["launch"] == eng.launches_per_step > 0
+    # the launch list of the captured 8-row step is what an eager run of the same step issues now
+    eng.verify_segment(8, eng._bucket(7))
+    eng.group_moe = False                                       # the experts would now run ungrouped: another launch list
+    with pytest.raises(RuntimeError, match="changed since capture"):
+        eng.verify_segment(8, eng._bucket(7))
+    eng.group_moe = True
+    # a budget that allows no result copy refuses the sampled step
+    eng.ledger = StepLedger(Budget(max_d2h=0))
+    with pytest.raises(LedgerError):
+        eng.step(prompt[:8], [0] * 8, list(range(8)))
+    eng.check_status()

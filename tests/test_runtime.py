@@ -1,0 +1,81 @@
+"""Runtime bookkeeping on the host: ledger budgets, launch-list identity of captured segments, in-step agreement.
+Reference tests: crates/sparkflash-deepseek-forward device_counters / tp4_graph unit tests, crates/sparkflash-runtime."""
+import pytest
+
+from sparkflash_b200.runtime import group as G, ledger as L, segments as S
+
+
+def test_ledger_accepts_a_step_within_budget_and_refuses_a_stray_collective():
+    b = L.Budget.for_rows_step(n_layers=40, world=8, fused=True)
+    assert b.collectives == 81 and b.max_d2h == 1
+    led = L.StepLedger(b)
+    led.begin()
+    led.count("launch", 620); led.count("collective", 81); led.count("h2d", 5); led.count("d2h"); led.count("host_sync")
+    assert led.end()["problems"] == []
+    led.begin()
+    led.count("launch", 620); led.count("collective", 82); led.count("h2d", 5)
+    with pytest.raises(L.LedgerError, match="collectives 82 != 81"):
+        led.end()
+    led.begin()
+    led.count("collective", 81); led.count("d2h", 2); led.count("alloc")
+    got = led.end(strict=False)
+    assert any("d2h" in p for p in got["problems"]) and any("alloc" in p for p in got["problems"])
+    assert led.snapshot()["steps"] == 3
+    assert L.Budget.for_rows_step(40, 1, False).collectives == 0
+    assert L.Budget.for_rows_step(40, 4, True, sampled=False).collectives == 80
+    with pytest.raises(KeyError):
+        led.count("nonsense")
+
+
+def test_launch_log_identity_of_a_segment():
+    with S.recording() as a:
+        for name in ("seam_fold", "umma_dense", "attn_rows", "umma_dense"):
+            S.note(name)
+    cache = S.SegmentCache()
+    cache.put((1, 1024), a)
+    with S.recording() as same:
+        for name in ("seam_fold", "umma_dense", "attn_rows", "umma_dense"):
+            S.note(name)
+    cache.check((1, 1024), same)
+    with S.recording() as other:          # one kernel swapped for another: same count, different list
+        for name in ("seam_fold", "umma_dense", "attn_tc", "umma_dense"):
+            S.note(name)
+    with pytest.raises(RuntimeError, match="changed since capture"):
+        cache.check((1, 1024), other)
+    with pytest.raises(KeyError):
+        cache.check((2, 1024), same)
+    S.note("outside any recording")         # a no-op without an installed log
+    assert len(a) == 4
+
+
+def test_native_wrappers_feed_the_launch_log():
+    """A wrapper that returns success notes its name; a failing one raises before anything is noted."""
+    from sparkflash_b200.ops import native as N
+    with S.recording() as log:
+        N._check(0, "some_kernel")
+        with pytest.raises(N.NativeError):
+            N._check(700, "bad_kernel")
+    assert log.items == ["some_kernel"]
+
+
+def test_group_lanes_detect_a_rank_that_took_another_branch():
+    W = 4
+    ranks = [G.GroupLanes(r, W) for r in range(W)]
+    lead = ranks[0]
+    for t in range(1, 4):
+        for r in ranks:
+            d = r.record([11, 12], [0, 1], [t, t], [5, 6])
+            lead.report(r.rank, t, d)
+        assert lead.in_step(t) is True
+        lead.check(t)
+    # rank 2 runs a different row list at tick 4
+    for r in ranks:
+        rows = [11, 12] if r.rank != 2 else [11, 13]
+        lead.report(r.rank, 4, r.record(rows, [0, 1], [4, 4], [5, 6]))
+    assert lead.in_step(4) is False
+    with pytest.raises(G.GroupOutOfStep, match="tick 4"):
+        lead.check(4)
+    # a tick with a missing report is undecided, not wrong
+    lead.report(0, 5, "x")
+    assert lead.in_step(5) is None
+    lead.check(5)
