@@ -246,8 +246,9 @@ class Engine:
             self.rope_identity = torch.zeros((R, cfg.rope_dim // 2, 2), dtype=torch.float32, device=dev)
             self.rope_identity[..., 0] = 1.0
             self.draft_lo, self.draft_hi = e((R,), i32), e((R,), i32)
-            self.draft_tokens = torch.zeros((cfg.dspark_block + 1,), dtype=torch.int32, device=dev)
-            self.draft_conf = torch.zeros((cfg.dspark_block,), dtype=torch.float32, device=dev)
+            s_max = max(1, R // cfg.dspark_block)
+            self.draft_tokens = torch.zeros((s_max * (cfg.dspark_block + 1),), dtype=torch.int32, device=dev)
+            self.draft_conf = torch.zeros((s_max * cfg.dspark_block,), dtype=torch.float32, device=dev)
             self._draft_bv = torch.zeros((max(1, self.world),), dtype=torch.float32, device=dev)
             self._draft_bi = torch.zeros((max(1, self.world),), dtype=torch.int32, device=dev)
         self.graphs: dict[tuple[int, int], torch.cuda.CUDAGraph] = {}
@@ -892,29 +893,46 @@ class Engine:
     def draft(self, lane: int, pos: int, anchor: int, temperature: float = 0.0, seed: int = 0):
         """One draft block after the backbone handled position ``pos`` of ``lane`` and ``anchor`` was sampled for pos + 1.
         Returns (tokens proposed for positions pos + 2 .., confidence logits), both lists of ``dspark_block``."""
+        return self.draft_many([(lane, pos, anchor, temperature, seed)])[0]
+
+    def draft_many(self, items):
+        """Draft blocks of several sequences in one pass: ``items`` = [(lane, pos, anchor, temperature, seed), ...], at most
+        ``max_rows // dspark_block`` of them.  A block's rows attend only their own sequence's window, so the result of a
+        sequence does not depend on which others share the pass.  Returns [(tokens, confidences), ...] in order.
+        Reference: crates/sparkflash-deepseek-forward/src/tp4_forward/draft.rs:904 (draft_blocks)."""
         if not self.drafter:
             raise RuntimeError("engine was built without drafter=True (or the weights carry no draft stages)")
         if self.w.moe_mode == "ep":
             raise NotImplementedError("the draft stages are width-sliced; run them with moe_mode='tp'")
-        cfg, w = self.cfg, self.w
+        cfg = self.cfg
         B = cfg.dspark_block
+        S = len(items)
+        if not 0 < S * B <= self.max_rows:
+            raise ValueError(f"{S} draft blocks of {B} rows do not fit a step of {self.max_rows} rows")
         noise = cfg.dspark_noise_token % cfg.vocab_size
         io = self.io
-        io.tokens[:B] = torch.tensor([anchor] + [noise] * (B - 1), dtype=torch.int32)
-        io.lanes[:B] = lane
-        io.pos[:B] = torch.arange(pos + 1, pos + 1 + B, dtype=torch.int32)
-        io.temp[:B] = temperature
-        io.seed[:B] = seed
+        n = S * B
+        lo, hi = [], []
+        for s_, (lane, pos, anchor, temperature, seed) in enumerate(items):
+            r0 = s_ * B
+            io.tokens[r0:r0 + B] = torch.tensor([anchor] + [noise] * (B - 1), dtype=torch.int32)
+            io.lanes[r0:r0 + B] = lane
+            io.pos[r0:r0 + B] = torch.arange(pos + 1, pos + 1 + B, dtype=torch.int32)
+            io.temp[r0:r0 + B] = temperature
+            io.seed[r0:r0 + B] = seed
+            lo += [max(0, pos - cfg.window + 1)] * B
+            hi += [pos + B] * B
         for dst, src in ((self.tokens, io.tokens), (self.row_lane, io.lanes), (self.row_pos, io.pos), (self.temp, io.temp), (self.seed, io.seed)):
-            dst[:B].copy_(src[:B], non_blocking=True)
-        self.draft_lo[:B] = max(0, pos - cfg.window + 1)
-        self.draft_hi[:B] = pos + B
-        for _ in self._draft_gen(B):
+            dst[:n].copy_(src[:n], non_blocking=True)
+        self.draft_lo[:n].copy_(torch.tensor(lo, dtype=torch.int32), non_blocking=False)
+        self.draft_hi[:n].copy_(torch.tensor(hi, dtype=torch.int32), non_blocking=False)
+        for _ in self._draft_gen(n, S):
             pass
-        out = self.draft_tokens[1:B + 1].tolist()
-        return out, self.draft_conf[:B].tolist()
+        toks = self.draft_tokens[:S * (B + 1)].view(S, B + 1)[:, 1:].tolist()
+        conf = self.draft_conf[:n].view(S, B).tolist()
+        return [(toks[s_], conf[s_]) for s_ in range(S)]
 
-    def _draft_gen(self, n: int):
+    def _draft_gen(self, n: int, S: int = 1):
         cfg, w = self.cfg, self.w
         d = cfg.hidden_size
         if self._fused():
@@ -942,24 +960,28 @@ class Engine:
         # i = 0), then position i is sampled; the chain runs on the device through draft_tokens
         r = w.markov_embed.shape[1]
         R = self.max_rows
-        self.draft_tokens[:1].copy_(self.tokens[:1])
+        B = n // S
+        dt = self.draft_tokens[:S * (B + 1)].view(S, B + 1)        # per sequence: anchor, then the B sampled tokens
+        dt[:, 0].copy_(self.tokens[:n].view(S, B)[:, 0])
         sub = 2 * len(w.mtp_layers)
-        for i in range(n):
-            N.markov_bias(self.logits[i], w.markov_head, w.markov_embed, self.draft_tokens[i:i + 1], self.vl, r, cfg.vocab_size); self._k()
-            N.sample(self.logits[i:i + 1], self.row_pos[i:i + 1], self.temp[i:i + 1], self.seed[i:i + 1], None, self.best_val[self.rank][i:i + 1],
-                     self.best_id[self.rank][i:i + 1], 1, self.vl, self.rank * self.vl); self._k()
-            if self.world > 1 and self.comm is not None:
-                # winners of the vocabulary slices: exchanged with the baseline collective (a draft block is off the critical
-                # path of the verified step)
-                import torch.distributed as dist
-                dist.all_gather_into_tensor(self._draft_bv, self.best_val[self.rank][i:i + 1])
-                dist.all_gather_into_tensor(self._draft_bi, self.best_id[self.rank][i:i + 1])
-                N.sample_fold(self._draft_bv, self._draft_bi, self.world, 1, 1, self.draft_tokens[i + 1:i + 2]); self._k()
-            else:
-                N.sample_fold(self.best_val[:, i:], self.best_id[:, i:], 1, 1, R, self.draft_tokens[i + 1:i + 2]); self._k()
+        for i in range(B):
+            for s_ in range(S):
+                row = s_ * B + i
+                N.markov_bias(self.logits[row], w.markov_head, w.markov_embed, dt[s_, i:i + 1], self.vl, r, cfg.vocab_size); self._k()
+                N.sample(self.logits[row:row + 1], self.row_pos[row:row + 1], self.temp[row:row + 1], self.seed[row:row + 1], None,
+                         self.best_val[self.rank][row:row + 1], self.best_id[self.rank][row:row + 1], 1, self.vl, self.rank * self.vl); self._k()
+                if self.world > 1 and self.comm is not None:
+                    # winners of the vocabulary slices: exchanged with the baseline collective (a draft block is off the critical
+                    # path of the verified step)
+                    import torch.distributed as dist
+                    dist.all_gather_into_tensor(self._draft_bv, self.best_val[self.rank][row:row + 1])
+                    dist.all_gather_into_tensor(self._draft_bi, self.best_id[self.rank][row:row + 1])
+                    N.sample_fold(self._draft_bv, self._draft_bi, self.world, 1, 1, dt[s_, i + 1:i + 2]); self._k()
+                else:
+                    N.sample_fold(self.best_val[:, row:], self.best_id[:, row:], 1, 1, R, dt[s_, i + 1:i + 2]); self._k()
         # confidence head: reads the collapsed residual before the final norm (pre coefficients of the last seam) and the Markov
         # embedding of each position's input token
-        emb = w.markov_embed[self.draft_tokens[:n].long()].float()
+        emb = w.markov_embed[dt[:, :B].reshape(-1).long()].float()
         pre = self.coef[(k - 1) % 2][:n, :cfg.hc_mult]
         x = (pre.unsqueeze(-1) * self.h[:n].float()).sum(1).to(torch.bfloat16).float()
         self.draft_conf[:n] = x @ w.conf_w[:d] + emb @ w.conf_w[d:]

@@ -81,8 +81,22 @@ class DSparkDrafter:
     sampled with the verifier's (seed, position) noise so that a good draft is accepted at any temperature."""
     device = True
 
-    def __init__(self, depth: int = 5, min_confidence: float | None = None):
-        self.depth, self.min_confidence = depth, min_confidence
+    def __init__(self, depth: int = 5, min_confidence: float | None = None, policy=None, passes_of: int = 16):
+        """``policy``: a sched.spec.SpecPolicy choosing every sequence's depth from the step-cost model (None keeps every
+        proposal up to ``depth``, or up to the first one below ``min_confidence``)."""
+        self.depth, self.min_confidence, self.policy, self.passes_of = depth, min_confidence, policy, passes_of
+
+    def _trim(self, toks, conf):
+        toks, conf = toks[:self.depth], conf[:self.depth]
+        if self.min_confidence is not None:          # stop at the first position the head does not trust
+            for i, c in enumerate(conf):
+                if c < self.min_confidence:
+                    return toks[:i], conf[:i]
+        return toks, conf
+
+    def propose_many(self, eng, items):
+        """Draft blocks of several sequences in one device pass (Engine.draft_many)."""
+        return [self._trim(t, c) for t, c in eng.draft_many(items)]
 
     def propose_device(self, eng, lane: int, pos: int, anchor: int, temperature: float, seed: int):
         toks, conf = eng.draft(lane, pos, anchor, temperature, seed)
@@ -277,22 +291,49 @@ class DeviceDriver(InferenceEngine):
             return {"subs": self._local_subs, "cancels": msg["cancels"]}
         return {"subs": [_Live(req, seq, None, None) for seq, req in msg["subs"]], "cancels": msg["cancels"]}
 
+    def _collect_drafts(self) -> None:
+        """Drafts of every decoding sequence for the coming step.  The device drafter runs the sequences' blocks in passes of
+        several sequences each; the depth policy then keeps, per sequence, the prefix of drafts that raises the shared verify
+        step's expected tokens per millisecond (anchors come first, then the likeliest drafts)."""
+        eng = self.engine
+        cand = []
+        for live in self._live.values():
+            info = self.sched.info(live.seq)
+            if info and info["state"] == "decode" and live.constraint is None:
+                cand.append((live, info))
+        if not cand:
+            return
+        proposals: list[tuple] = []
+        if getattr(self.drafter, "device", False):
+            items = []
+            for live, info in cand:
+                q = live.req
+                seed = (q.seed if q.seed is not None else live.seq * 0x9E3779B1) & 0x7FFFFFFFFFFFFFFF
+                items.append((info["lane"], info["computed"] - 1, live.history[-1], 0.0 if q.temperature < 1e-5 else q.temperature, seed))
+            per_pass = max(1, min(getattr(self.drafter, "passes_of", 16), eng.max_rows // max(1, eng.cfg.dspark_block)))
+            out = []
+            for p0 in range(0, len(items), per_pass):
+                out += self.drafter.propose_many(eng, items[p0:p0 + per_pass])
+            proposals = [(live, toks, conf) for (live, _), (toks, conf) in zip(cand, out)]
+        else:
+            proposals = [(live, *self.drafter.propose(live.history)) for live, _ in cand]
+        policy = getattr(self.drafter, "policy", None)
+        if policy is not None and proposals:
+            from ..sched.spec import calibrate
+            # more decoding sequences than half a step's rows take plain rows (the scheduler's rule): nothing to allocate then
+            if len(proposals) <= policy.max_rows:
+                alloc = policy.allocate([[calibrate(c) for c in conf] for _, _, conf in proposals])
+                proposals = [(live, toks[:k], conf[:k]) for (live, toks, conf), k in zip(proposals, alloc.keep)]
+                self.last_allocation = alloc
+        for live, toks, conf in proposals:
+            if toks:
+                self.sched.set_drafts(live.seq, toks, conf)
+
     def _tick(self) -> bool:
         eng = self.engine
         # drafts for the coming decode step
         if self.drafter is not None:
-            for live in self._live.values():
-                info = self.sched.info(live.seq)
-                if info and info["state"] == "decode" and live.constraint is None:
-                    if getattr(self.drafter, "device", False):
-                        q = live.req
-                        seed = (q.seed if q.seed is not None else live.seq * 0x9E3779B1) & 0x7FFFFFFFFFFFFFFF
-                        toks, conf = self.drafter.propose_device(eng, info["lane"], info["computed"] - 1, live.history[-1],
-                                                                 0.0 if q.temperature < 1e-5 else q.temperature, seed)
-                    else:
-                        toks, conf = self.drafter.propose(live.history)
-                    if toks:
-                        self.sched.set_drafts(live.seq, toks, conf)
+            self._collect_drafts()
         phase, rows = self.sched.tick(eng.max_rows)
         if phase == PHASE_IDLE or not rows:
             return False

@@ -176,3 +176,33 @@ def test_top_p_top_k_reach_the_engine_only_for_sampling_rows():
     res = run(drv, reqs)
     assert all(f[0] == "finished" for _, f in res)
     assert eng.filter_log and all(f == (40, 0.9) for _, f in eng.filter_log)
+
+
+def test_eight_sequences_share_one_verify_step_under_the_depth_policy():
+    """Eight decoding sequences with a host drafter that is always right: the depth policy gives every sequence drafts
+    while the step stays within its row cap, all of them ride in one verify step per tick, and the output is the
+    sequential one (speculation invisible)."""
+    from sparkflash_b200.sched.spec import SpecPolicy, StepCost
+    cycle = [65, 66, 67, 68, 69, 70, 71]
+    eng = FakeRowsEngine(max_rows=64, max_lanes=8, cycle=cycle)
+
+    class OracleDrafter:
+        """Knows the fake model's cycle: proposes the true continuation with high confidence."""
+        depth = 5
+        policy = SpecPolicy(StepCost(a0=5.0, b0=0.2, a1=5.0, b1=0.2, band=5), max_rows=64, max_depth=5)
+
+        def propose(self, history):
+            p = len(history) - 1          # position of the last token
+            toks = [cycle[(p + 1 + i) % len(cycle)] for i in range(5)]
+            return toks, [6.0] * 5
+    drv = DeviceDriver(eng, TOK, drafter=OracleDrafter(), prefix_reuse_min=1000, eos_id=10 ** 9)
+    prompts = [[40 + i, 41 + i, 42 + i] for i in range(8)]
+    res = run(drv, [EngineRequest(f"r{i}", "m", p, max_tokens=24, temperature=0.0) for i, p in enumerate(prompts)])
+    for (toks, fin), p in zip(res, prompts):
+        assert fin[0] == "finished" and toks == reference_tokens(p, 24, cycle=cycle)
+    assert max(eng.steps) <= 64
+    # a shared speculative step: eight anchors plus drafts of several sequences in one rows step
+    assert any(s > 16 for s in eng.steps), eng.steps
+    assert drv.last_allocation.rows <= 64 and sum(drv.last_allocation.keep) > 0
+    # 192 tokens in a few dozen steps (prompt steps included): the drafts were accepted
+    assert len(eng.steps) < 60

@@ -83,3 +83,24 @@ def test_driver_with_the_device_drafter_keeps_the_output(setup):
         spec = run(DSparkDrafter(depth=4), T)
         assert [t for t, _ in plain] == [t for t, _ in spec]
         assert all(f[0] == "finished" for _, f in spec) and sum(f[2]["proposed"] for _, f in spec) > 0
+
+
+def test_draft_blocks_of_several_sequences_in_one_pass(setup):
+    """Two sequences drafted in one pass give exactly the tokens and confidences of two separate passes (a block's rows
+    only see their own sequence), and three blocks of five rows do not fit a 12-row engine."""
+    from sparkflash_b200.models.deepseek_v41 import engine as E
+    cfg, orc, dw = setup
+    B = cfg.dspark_block
+    eng = E.Engine(dw, max_lanes=3, max_context=256, max_rows=2 * B + 2, arm="tc", drafter=True, use_graphs=False)
+    g = torch.Generator().manual_seed(6)
+    items = []
+    for lane, plen in ((0, 9), (2, 12)):
+        prompt = torch.randint(0, cfg.vocab_size, (plen,), generator=g).tolist()
+        r = eng.step(prompt, [lane] * plen, list(range(plen)))
+        items.append((lane, plen - 1, int(r[plen - 1]), 0.0 if lane == 0 else 0.8, 3 + lane))
+    separate = [eng.draft(*it) for it in items]
+    together = eng.draft_many(items)
+    eng.check_status()
+    assert together == separate
+    with pytest.raises(ValueError):
+        eng.draft_many(items + [items[0]])

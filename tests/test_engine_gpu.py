@@ -543,7 +543,7 @@ def test_step_ledger_and_segment_identity(tiny):
     from sparkflash_b200.models.deepseek_v41 import engine as E
     from sparkflash_b200.runtime.ledger import Budget, LedgerError, StepLedger
     cfg, ck, w, orc, dw = tiny
-    eng = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, use_graphs=True)
+    eng = E.Engine(dw, max_lanes=2, max_context=256, max_rows=16, use_graphs=True, arm="tc")
     eng.ledger = StepLedger(Budget.for_rows_step(cfg.n_layers, 1, False))
     prompt = _prompt(cfg, 12, seed=3)
     eng.step(prompt[:8], [0] * 8, list(range(8)))              # captures
