@@ -720,13 +720,13 @@ class Engine:
                       n, k, d, self.il, cfg.swiglu_limit); self._k()
         N.moe_down(self.act_q, self.act_s, self.ids, L.w2, L.w2_sf, L.s2, L.s2_sf, self.y_ffn, n, k, d, self.il); self._k()
 
-    HEAD_TC_MIN_ROWS = 1 << 30     # rows from which the vocabulary projection runs on the bf16 tensor-core GEMM (off: the
-                                   # CUDA-core kernel keeps a row's logits independent of the step's row count and measured faster)
+    HEAD_TC_MIN_ROWS = 1     # tensor-core arm: the vocabulary projection runs on the bf16 tensor-core GEMM from this many rows on
+                             # (one row costs what the CUDA-core GEMV costs, 200 vs 194 us; sixteen rows 212 vs 1,116 us)
 
     def _head(self, hf: int, hn: int) -> None:
-        """Vocabulary-slice logits of rows hf .. hf + hn - 1 (fp32).  One row: the CUDA-core GEMV, which streams the bf16
-        matrix at memory speed.  More rows: the bf16 tensor-core GEMM, every row its own accumulator column (a row's logits
-        do not depend on how many rows share the launch)."""
+        """Vocabulary-slice logits of rows hf .. hf + hn - 1 (fp32).  Tensor-core arm: the bf16 tensor-core GEMM, every row its
+        own accumulator column, so a row's logits do not depend on how many rows share the launch.  CUDA-core arm (and steps
+        of more than 128 sampled rows): the CUDA-core GEMV."""
         cfg, w = self.cfg, self.w
         d = cfg.hidden_size
         if self.tcb is None or hn < self.HEAD_TC_MIN_ROWS or hn > 128 or d % 64:

@@ -190,7 +190,7 @@ MANY_ROWS = 128            # above: token-tiled GEMMs, bf16-GEMM coefficients, o
 TC_ATTENTION_ROWS = 64     # above: attention on tcgen05 (a tolerance arm)
 GROUP_MIN_ROWS = 4         # from here on the experts run grouped by expert
 GROUP_WIDE_ROWS = 512      # from here on segments hold up to 64 pairs
-HEAD_TC_MIN_ROWS = 1 << 30     # the tensor-core head is wired but off by default (see Engine.HEAD_TC_MIN_ROWS)
+HEAD_TC_MIN_ROWS = 1
 SELECT_LONG_ENTRIES = 32768   # rows longer than this (and few rows) use the chunked select
 
 
