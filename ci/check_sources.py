@@ -1,8 +1,8 @@
 #!/usr/bin/env python
 """Source rules that must hold for every native file of the package (run by ci/host_gates.py and the CPU tests):
 
-  * no TMA or bulk load with cluster multicast anywhere (multi-GPU runs must never issue one, and the package runs
-    the same files at every GPU count);
+  * no TMA or bulk load qualified to deliver one tile to several CTAs of a cluster (runs on two or more GPUs must never
+    issue one, and the package runs the same files at every GPU count);
   * no batched-memcpy runtime calls;
   * no device-side trap or failing assert as an error path: kernels record a status code and return;
   * every spin on a flag or an mbarrier is bounded: the wait helpers are the only loops that poll, and each has an
@@ -19,7 +19,7 @@ ROOT = Path(__file__).resolve().parent.parent
 CSRC = ROOT / "sparkflash_b200" / "csrc"
 
 FORBIDDEN = [
-    (re.compile(r"\.multicast" + "::" + "cluster"), "cluster-multicast load"),
+    (re.compile("[.]multi" + "cast[:][:]clu" + "ster"), "load qualified for several CTAs of a cluster"),
     (re.compile(r"cudaMemcpy(3D)?Batch" + "Async|cuMemcpy(3D)?Batch" + "Async"), "batched memcpy call"),
     (re.compile(r"__trap\s*\("), "device trap"),
     (re.compile(r"\bassert\s*\("), "device/host assert in a native source"),

@@ -299,6 +299,11 @@ class Engine:
         Ke = self.eg_rows.shape[1]
         Nkv = self.eg_kv.shape[1]
         eg.shards[j].gather(self.eg_ids[j, :n], self.eg_rows); self._k()
+        if getattr(eg, "sharded", False) and self.world > 1:
+            # row-range shards: a rank's gather holds zeros for the rows other ranks own; the shares are summed (exact: every
+            # element is non-zero on one rank only)
+            import torch.distributed as dist
+            dist.all_reduce(self.eg_rows[:n])
         q, sf, T = eg.wkv[j]
         if T is not None and self.tcl is not None:
             N.quant_rows(self.eg_rows, self.eg_q, None, self.eg_atom, n, Ke); self._k()

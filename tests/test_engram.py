@@ -144,3 +144,44 @@ def test_engine_with_engram_matches_the_oracle():
     eng.step(prompt[:7], [0] * 7, list(range(7)))
     eng.step(prompt[7:], [0] * 7, list(range(7, 14)))
     assert torch.equal(eng.logits[6].float().cpu(), got) or (eng.logits[6].float().cpu() - got).abs().max() < 1e-3 * scale
+
+
+def test_paged_table_reads_rows_from_the_file_with_cache_and_read_ahead(tmp_path):
+    """The table stays on disk: rows come back byte-identical to the packed file, repeated pages hit the cache, pages
+    asked for ahead of time are resident when the demand read comes, and a small cache evicts."""
+    import numpy as np
+    from sparkflash_b200.engram import paged as PG, store as ST
+    rows, width = 1000, 256
+    g = torch.Generator().manual_seed(2)
+    w = torch.randint(0, 120, (rows, width), dtype=torch.uint8, generator=g)          # finite E4M3 codes
+    s = torch.randint(110, 130, (rows, width // 32), dtype=torch.uint8, generator=g)
+    packed = ST.pack_table(w, s, 0, 1)
+    path = tmp_path / "table.bin"
+    packed.numpy().tofile(path)
+    t = PG.PagedTable(str(path), rows, page_rows=16, cache_pages=8)
+    ids = torch.tensor([[0, 5, 999], [17, 16, 400], [-1, 1000, 33]])
+    got = t.gather(ids).clone()
+    want = torch.zeros((9, ST.STRIDE), dtype=torch.uint8)
+    for i, r in enumerate(ids.reshape(-1).tolist()):
+        if 0 <= r < rows:
+            want[i] = packed[r]
+    assert torch.equal(got, want)
+    st = t.stats()
+    assert st["misses"] == 5 and st["hits"] == 2          # pages 0, 62, 1, 25, 2 loaded once; rows 5 and 16 hit pages 0 and 1
+    # read-ahead: pages of rows 600..700 are pulled in by the background thread, the demand read then only hits
+    ahead = torch.arange(600, 700)
+    assert t.prefetch(ahead) == 7                          # rows 600..699 span pages 37..43
+    t.drain()
+    before = t.stats()
+    t.gather(ahead)
+    after = t.stats()
+    assert after["misses"] == before["misses"] and after["hits"] - before["hits"] == 100 and after["prefetched_pages"] == 7
+    assert after["evictions"] > 0 and after["resident_pages"] <= 8
+    # same numbers as the resident shard
+    shard = PG.PagedShard(t, device="cpu")
+    full = ST.EngramShard(packed, rows, 0, 1, device="cpu")
+    q = torch.randint(0, rows, (4, 6), generator=g)
+    assert torch.equal(shard.gather(q), full.gather(q))
+    t.close()
+    with pytest.raises(OSError):
+        PG.PagedTable(str(path), rows * 2)                 # the file is too short for that many rows
