@@ -21,7 +21,7 @@ from sparkflash_b200.parallel import comm as PC
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
 dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
-cfg = tiny_config()
+cfg = tiny_config(**json.loads(os.environ.get("SFB_TEST_CFG", "{}")))
 ck = W.synthetic_checkpoint(cfg, 0)
 out = {}
 log = open(os.environ["SFB_WORKER_LOG"] + f".{rank}", "w")
@@ -38,6 +38,34 @@ for arm in os.environ["SFB_TEST_COLLECTIVES"].split(","):
     print("generated", arm, toks, file=log, flush=True)
     eng.check_status()
     out[arm] = toks
+    if os.environ.get("SFB_TEST_ORACLE") == "1":
+        # teacher-forced pass over the prompt on lane 1: every rank's vocabulary slice of the logits is gathered and rank 0
+        # compares the whole row with the CPU oracle's simulation of the same tensor-parallel seams
+        from sparkflash_b200.models.deepseek_v41 import oracle as O
+        rows = []
+        for pos, tok in enumerate(prompt):
+            r = eng.step([tok], [1], [pos])
+            parts = [torch.empty_like(eng.logits[0]) for _ in range(world)]
+            dist.all_gather(parts, eng.logits[0].contiguous())
+            rows.append((int(r[0]), torch.cat(parts).cpu()))
+        eng.check_status()
+        same = torch.tensor([t for t, _ in rows], device="cuda")
+        every = [torch.empty_like(same) for _ in range(world)]
+        dist.all_gather(every, same)
+        assert all(torch.equal(e, same) for e in every), "ranks sampled different tokens"
+        if rank == 0:
+            orc = O.Oracle(cfg, W.dequantize_checkpoint(ck, cfg), world=world)
+            st = orc.new_state()
+            errs, agree = [], 0
+            for pos, tok in enumerate(prompt):
+                ol = orc.step(st, tok)
+                scale = ol.abs().max().item()
+                e = (rows[pos][1] - ol).abs()
+                if pos == 0:
+                    assert e.max().item() < 0.02 * scale, ("first position", e.max().item(), scale)
+                errs.append(e.mean().item() / scale)
+                agree += rows[pos][0] == int(ol.argmax())
+            out[arm + "_oracle"] = {"mean_err": sum(errs) / len(errs), "agree": agree, "n": len(prompt)}
     torch.cuda.synchronize()
     dist.barrier()
     print("barrier", arm, file=log, flush=True)
@@ -49,6 +77,39 @@ if rank == 0:
 dist.destroy_process_group()
 print('destroyed', file=log, flush=True)
 '''
+
+
+def _gpus() -> int:
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_real_ranks_match_the_oracle_seams(tmp_path, world):
+    """One process per GPU over the fused collectives: every position's full logits row (gathered from the ranks'
+    vocabulary slices) against the CPU oracle's simulation of the same tensor-parallel seams, and the same sampled tokens
+    on every rank.  Skipped where the box has fewer GPUs."""
+    if _gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    # four and eight ranks need as many heads, output groups and 32-wide expert slices as ranks
+    over = {} if world == 2 else {"n_heads": 8, "o_groups": 8, "moe_inter": 256}
+    env = dict(os.environ, SFB_REPO=repo, NCCL_NVLS_ENABLE="0", SFB_TEST_ARM="tc", SFB_TEST_COLLECTIVES="fused", SFB_TEST_ORACLE="1",
+               SFB_TEST_CFG=json.dumps(over), SFB_WORKER_LOG=os.path.join(str(tmp_path), "oracle_worker.log"))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
+           "127.0.0.1", "--master-port", str(29540 + world), str(script)]
+    proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, start_new_session=True)
+    try:
+        stdout, stderr = proc.communicate(timeout=240)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)
+        stdout, stderr = proc.communicate()
+        pytest.fail(f"{world}-rank worker timed out\n" + stdout[-2000:] + stderr[-2000:])
+    assert proc.returncode == 0, stdout[-3000:] + stderr[-3000:]
+    res = json.loads([l for l in stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    o = res["fused_oracle"]
+    assert o["mean_err"] < 0.06 and o["agree"] >= 0.6 * o["n"], o
 
 
 @pytest.mark.parametrize("arm,collectives", [("tc", "fused"), ("cuda", "fused,nccl")])
@@ -123,8 +184,18 @@ def test_two_rank_server_answers_a_chat_request(tmp_path):
         assert outs[0]["usage"]["completion_tokens"] >= 1
         assert outs[0]["choices"][0]["message"]["content"] == outs[1]["choices"][0]["message"]["content"]      # greedy: repeatable
         # SIGTERM to the leader alone: it drains, says goodbye on the control channel, and the follower leaves in order
-        boots = [json.loads(l) for l in open(tmp_path / "serve.log").read().splitlines() if l.startswith("{") and '"boot"' in l]
-        leader = [b["pid"] for b in boots if b["boot"] == "listening"][0]
+        # both ranks write boot lines to one log; two of them can land on one line
+        boots, dec = [], json.JSONDecoder()
+        for l in open(tmp_path / "serve.log").read().splitlines():
+            p = l.find('{"ts"')
+            while p >= 0:
+                try:
+                    obj, end = dec.raw_decode(l, p)
+                    boots.append(obj)
+                    p = l.find('{"ts"', end)
+                except ValueError:
+                    p = l.find('{"ts"', p + 1)
+        leader = [b["pid"] for b in boots if b.get("boot") == "listening"][0]
         os.kill(leader, signal.SIGTERM)
         try:
             rc = proc.wait(timeout=60)
