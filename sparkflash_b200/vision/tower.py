@@ -1,8 +1,10 @@
 """DeepSeek-ViT tower and the 3x3 aligner: bf16 end to end with fp32 norm weights, replicated on every rank.
 
-Plain dense GEMMs go to cuBLAS through torch (they are library-shaped); attention over one image is a single
-unmasked SDPA call; the rotary and the aligner's unfold are this framework's kernels (csrc/k_vision.cu) with
-torch twins used on the CPU.  Reference: docs/architecture/06-vision.md sections 1, 3, 4.
+On the GPU every projection whose reduction length is a multiple of 64 runs on this framework's bf16 tensor-core GEMM
+(csrc/k_umma.cu, kind::f16: the tower's weights are the M operand, the image's patches the token columns); the patch
+embedding (K = 588) and the CPU path use torch.  Attention over one image is a single unmasked SDPA call; the rotary and
+the aligner's unfold are this framework's kernels (csrc/k_vision.cu) with torch twins used on the CPU.
+Reference: docs/architecture/06-vision.md sections 1, 3, 4; kernels/opt_vision_sm121.cu:172 (the reference's own bf16 GEMM).
 """
 from __future__ import annotations
 
@@ -83,6 +85,26 @@ def _unfold3(x, n_h, n_w):
 class VisionTower:
     def __init__(self, cfg: VisionConfig, weights: dict[str, torch.Tensor]):
         self.c, self.w = cfg, weights
+        self._maps: dict[int, object] = {}
+        self.tc_gemms = 0                 # projections that ran on the tensor-core GEMM (tests look at it)
+
+    def _linear(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+        """x bf16 [N, K] times weight bf16 [out, K] (+ bias): tcgen05 on the GPU when K is a multiple of 64."""
+        K = weight.shape[1]
+        if not x.is_cuda or K % 64 or weight.dtype != torch.bfloat16:
+            return F.linear(x, weight, bias)
+        from ..ops import native as N
+        x = x.to(torch.bfloat16).contiguous()
+        n, out_dim = x.shape[0], weight.shape[0]
+        ta = self._maps.get(weight.data_ptr())
+        if ta is None:
+            ta = self._maps[weight.data_ptr()] = N.bf16_map(weight.contiguous(), out_dim, K, 128)
+        NP = 128 if n > 128 else N.umma_np(n)
+        tb = N.bf16_map(x, n, K, NP)
+        y = torch.empty((n, out_dim), dtype=torch.bfloat16, device=x.device)
+        N.umma_bf16(ta, tb, n, out_dim, K, out_b=y, out_stride=out_dim, NP=NP)
+        self.tc_gemms += 1
+        return y if bias is None else y + bias
 
     @torch.no_grad()
     def encode(self, patches: torch.Tensor, plan: ImagePlan) -> torch.Tensor:
@@ -92,17 +114,17 @@ class VisionTower:
         x = F.linear(patches, w["patch_embed.weight"], w["patch_embed.bias"])
         for l in range(c.n_layers):
             p = f"blocks.{l}."
-            qkv = F.linear(_rms(x, w[p + "attn_norm.weight"], c.norm_eps), w[p + "wqkv.weight"], w[p + "wqkv.bias"])
+            qkv = self._linear(_rms(x, w[p + "attn_norm.weight"], c.norm_eps), w[p + "wqkv.weight"], w[p + "wqkv.bias"])
             q, k, v = qkv.reshape(N, 3, H, hd).unbind(1)
             q, k = _rope(q, plan.n_vit_w, c.rope_theta), _rope(k, plan.n_vit_w, c.rope_theta)
             o = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0), v.transpose(0, 1).unsqueeze(0))
-            x = x + F.linear(o[0].transpose(0, 1).reshape(N, c.dim), w[p + "wo.weight"], w[p + "wo.bias"])
-            gu = F.linear(_rms(x, w[p + "ffn_norm.weight"], c.norm_eps), w[p + "w1.weight"])
+            x = x + self._linear(o[0].transpose(0, 1).reshape(N, c.dim), w[p + "wo.weight"], w[p + "wo.bias"])
+            gu = self._linear(_rms(x, w[p + "ffn_norm.weight"], c.norm_eps), w[p + "w1.weight"])
             gate, up = gu.chunk(2, -1)
-            x = x + F.linear(F.silu(gate) * up, w[p + "w2.weight"])
+            x = x + self._linear(F.silu(gate) * up, w[p + "w2.weight"])
         x = _rms(x, w["norm.weight"], c.norm_eps)
         u = _unfold3(x, plan.n_vit_h, plan.n_vit_w)
-        return F.linear(F.gelu(F.linear(u, w["aligner.w1.weight"], w["aligner.w1.bias"])), w["aligner.w2.weight"], w["aligner.w2.bias"])
+        return self._linear(F.gelu(self._linear(u, w["aligner.w1.weight"], w["aligner.w1.bias"])), w["aligner.w2.weight"], w["aligner.w2.bias"])
 
     def span_embeddings(self, image_tokens: torch.Tensor, plan: ImagePlan) -> torch.Tensor:
         """Rows of the whole span in prompt order: start, (n_llm_w image rows + newline) * n_llm_h, end."""

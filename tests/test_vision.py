@@ -91,5 +91,7 @@ def test_device_kernels_match_their_twins():
     pl = VP.ImagePlan(84, 84, 6, 6, 2, 2)
     patches = (torch.randn(36, 588, generator=g) * 0.5).to(torch.bfloat16)
     cpu = VT.VisionTower(c, w).encode(patches, pl).float()
-    gpu = VT.VisionTower(c, {k: v.cuda() for k, v in w.items()}).encode(patches.cuda(), pl).float().cpu()
+    tower = VT.VisionTower(c, {k: v.cuda() for k, v in w.items()})
+    gpu = tower.encode(patches.cuda(), pl).float().cpu()
     assert (cpu - gpu).abs().max() < 0.05 * cpu.abs().max() + 1e-3
+    assert tower.tc_gemms >= 4 * c.n_layers          # the blocks' projections ran on the tensor-core GEMM
