@@ -1,4 +1,5 @@
-"""Command line: ``python -m sparkflash_b200 <models|doctor|trace|convert|pack-engram|serve|bench-serving>``.
+"""Command line: ``python -m sparkflash_b200 <models|doctor|trace|convert|pack-engram|serve|bench-serving|web|device-chain|
+inkling-tp4|plan|gates|served-gate>``.
 Reference: crates/sparkflash-cli/src/main.rs:50-76 (subcommand table), convert.rs:76 (convert usage),
 serve.rs:6418-6590 (serve orchestration)."""
 from __future__ import annotations
@@ -63,7 +64,7 @@ def _trace(args) -> int:
 
 
 def _pack_engram(args) -> int:
-    from .engram import packer
+    from .engram import store as packer
     rep = packer.pack(args.source, args.output_dir, world=args.world, dry_run=args.dry_run)
     print(f"pack-engram: wrote {len(rep['files'])} file(s), {rep['bytes']} bytes, into {args.output_dir}")
     return 0
@@ -77,6 +78,96 @@ def _serve(args) -> int:
 def _bench_serving(args) -> int:
     from .serve import bench_client
     return bench_client.run(args)
+
+
+def _web(args) -> int:
+    from .web import app
+    return app.main(["--host", args.host, "--port", str(args.port), "--server", args.server_url])
+
+
+def _device_chain(args) -> int:
+    """The engine loop without HTTP: prefill a synthetic prompt in chunks, decode, print one JSON line with the rates
+    (reference: crates/sparkflash-cli/src/device_chain.rs:351-383, tp4_chain.rs run_loop)."""
+    import time
+
+    import torch
+    from . import config as CF
+    from .models.deepseek_v41 import engine as E, prepare as P
+    from .utils.evidence import run_header
+    cfg = {"tiny": CF.tiny_config, "reduced": lambda: CF.reduced_config(args.experts, args.layers), "full": CF.full_config}[args.synthetic]()
+    if args.synthetic == "tiny":
+        from .models.deepseek_v41 import weights as W
+        w = P.prepare_from_checkpoint(W.synthetic_checkpoint(cfg, 0), cfg)
+    else:
+        w = P.prepare_synthetic(cfg, 0, 1)
+    eng = E.Engine(w, max_lanes=2, max_context=args.prompt + args.tokens + 64, max_rows=args.chunk, arm=args.arm,
+                   synthetic_scales=args.synthetic != "tiny")
+    prompt = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=torch.Generator().manual_seed(0)).tolist()
+    eng.generate(prompt[:min(len(prompt), args.chunk)], 2, lane=1, chunk=args.chunk)         # graphs and lazy set-up
+    torch.cuda.synchronize(); t0 = time.perf_counter()
+    pos, nxt = 0, 0
+    while pos < len(prompt):
+        c = prompt[pos:pos + args.chunk]
+        r = eng.step(c, [0] * len(c), list(range(pos, pos + len(c))), head="last" if pos + len(c) >= len(prompt) else False)
+        nxt, pos = int(r[len(c) - 1]), pos + len(c)
+    t1 = time.perf_counter()
+    out = []
+    for _ in range(args.tokens):
+        out.append(nxt)
+        nxt = int(eng.step([nxt], [0], [pos])[0]); pos += 1
+    t2 = time.perf_counter()
+    eng.check_status()
+    print(json.dumps({"header": run_header(eng), "prefill_tok_s": len(prompt) / (t1 - t0), "decode_tok_s": args.tokens / (t2 - t1),
+                      "launches_per_step": eng.launches_per_step, "tokens": out[:16]}))
+    return 0
+
+
+def _inkling_tp4(args) -> int:
+    """Inkling-2 under its three expert splits on ``world`` simulated ranks: the logits of every split against the unsplit
+    model (reference: crates/sparkflash-cli inkling-tp4, crates/sparkflash-model-inkling2/src/tensor.rs:49-78)."""
+    import torch
+    from .models import inkling as IK
+    c = IK.InklingConfig()
+    w = IK.init_weights(c, 0)
+    toks = torch.randint(0, c.vocab, (args.tokens,), generator=torch.Generator().manual_seed(1)).tolist()
+    base = IK.reference_logits(c, w, toks)
+    rep = {}
+    for split in ("experts", "intermediate", "rows"):
+        got = IK.reference_logits(c, w, toks, world=args.world, split=split)
+        rep[split] = float((got - base).abs().max())
+    print(json.dumps({"world": args.world, "max_abs_vs_unsplit": rep}))
+    return 0 if max(rep.values()) < 1e-3 else 1
+
+
+def _plan(args) -> int:
+    from . import config as CF
+    from .models import tp_plan as TP
+    from .ops import plan as OP
+    cfg = CF.full_config()
+    tp = TP.plan(cfg, args.world, args.moe_mode)
+    steps = {str(n): OP.plan_step(n, "tc", args.world).__dict__ | {"collective": OP.plan_step(n, "tc", args.world).collective.kind.value}
+             for n in (1, 5, 16, 64, 128, 1024)}
+    print(json.dumps({"world": args.world, "moe_mode": args.moe_mode, "gb_per_rank": round(tp.bytes_per_rank() / 1e9, 2),
+                      "heads_per_rank": tp.heads_per_rank, "inter_per_rank": tp.inter_per_rank, "vocab_per_rank": tp.vocab_per_rank,
+                      "experts_per_rank": tp.experts_per_rank, "collectives_per_step": tp.collectives_per_step(), "tensors": tp.table(),
+                      "step_plans": steps}, indent=1, default=str))
+    return 0
+
+
+def _gates(args) -> int:
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "ci", "host_gates.py")
+    if not os.path.exists(script):
+        print("gates: ci/host_gates.py is not part of this installation")
+        return 2
+    return subprocess.call([sys.executable, script] + (["--skip-tests"] if args.skip_tests else []))
+
+
+def _served_gate(args) -> int:
+    from .gates import served
+    return served.main(["--url", args.url, "--tokens", str(args.tokens), "--concurrency", str(args.concurrency)] +
+                       (["--api-key", args.api_key] if args.api_key else []))
 
 
 def main(argv=None) -> int:
@@ -108,6 +199,19 @@ def main(argv=None) -> int:
     b.add_argument("--url", default="http://127.0.0.1:8000"); b.add_argument("--concurrency", type=int, default=16)
     b.add_argument("--requests", type=int, default=32); b.add_argument("--prompt-tokens", type=int, default=512)
     b.add_argument("--max-tokens", type=int, default=128); b.add_argument("--api-key"); b.set_defaults(fn=_bench_serving)
+    wb = sub.add_parser("web"); wb.add_argument("--host", default="127.0.0.1"); wb.add_argument("--port", type=int, default=8080)
+    wb.add_argument("--server-url", default="http://127.0.0.1:8000"); wb.set_defaults(fn=_web)
+    dc = sub.add_parser("device-chain")
+    dc.add_argument("--synthetic", default="reduced", choices=["tiny", "reduced", "full"]); dc.add_argument("--experts", type=int, default=32)
+    dc.add_argument("--layers", type=int, default=8); dc.add_argument("--prompt", type=int, default=2048); dc.add_argument("--tokens", type=int, default=64)
+    dc.add_argument("--chunk", type=int, default=1024); dc.add_argument("--arm", default="tc", choices=["tc", "cuda"]); dc.set_defaults(fn=_device_chain)
+    ik = sub.add_parser("inkling-tp4"); ik.add_argument("--world", type=int, default=4); ik.add_argument("--tokens", type=int, default=12)
+    ik.set_defaults(fn=_inkling_tp4)
+    pl = sub.add_parser("plan"); pl.add_argument("--world", type=int, default=8); pl.add_argument("--moe-mode", default="tp", choices=["tp", "ep"])
+    pl.set_defaults(fn=_plan)
+    gt = sub.add_parser("gates"); gt.add_argument("--skip-tests", action="store_true"); gt.set_defaults(fn=_gates)
+    sg = sub.add_parser("served-gate"); sg.add_argument("--url", default="http://127.0.0.1:8000"); sg.add_argument("--tokens", type=int, default=48)
+    sg.add_argument("--concurrency", type=int, default=4); sg.add_argument("--api-key"); sg.set_defaults(fn=_served_gate)
     args = ap.parse_args(argv)
     if not getattr(args, "fn", None):
         ap.print_help()

@@ -41,6 +41,7 @@ class _Live:
     verify_steps: int = 0
     generated: int = 0
     history: list[int] = field(default_factory=list)
+    choices: list[int] = field(default_factory=list)      # the model's own picks under teacher forcing
 
 
 class LocalChannel:
@@ -410,12 +411,20 @@ class DeviceDriver(InferenceEngine):
                 cached = getattr(live, "_cached", 0)
             self._emit(live, ("started", len(live.req.prompt_tokens), cached))
 
+    def _force(self, live: _Live, index: int, sampled: int) -> int:
+        """Teacher forcing: remember the model's own choice for generation index ``index`` and emit the forced token."""
+        f = live.req.forced_tokens
+        if not f:
+            return sampled
+        live.choices.append(int(sampled))
+        return f[index] if index < len(f) else sampled
+
     def _commit_prefill(self, live: _Live, rows, out) -> None:
         if not live.started:
             live._cached = rows[0].pos if rows[0].pos > 0 else 0
             self._start(live)
         done = rows[-1].pos + 1 >= len(live.req.prompt_tokens)
-        new = [out[-1]] if done else []
+        new = [self._force(live, 0, out[-1])] if done else []
         fin = self.sched.commit(live.seq, len(rows), new, self.eos_id)
         if done:
             self._deliver(live, new, fin)
@@ -423,16 +432,20 @@ class DeviceDriver(InferenceEngine):
     def _commit_decode(self, live: _Live, rows, out) -> None:
         self._start(live)
         # row 0 is the anchor; rows 1.. are drafts: draft k is accepted when it equals the token sampled at row k-1
+        # (under teacher forcing the token that is fed next is the forced one, so that is what a draft has to match)
         accepted = 0
         drafts = rows[1:]
-        for k, d in enumerate(drafts):
-            if d.token == out[k]:
+        new = []
+        base = live.generated
+        while True:
+            t = self._force(live, base + accepted, out[accepted])
+            new.append(t)
+            if accepted < len(drafts) and drafts[accepted].token == t:
                 accepted += 1
             else:
                 break
         if drafts:
             live.proposed += len(drafts); live.accepted += accepted; live.verify_steps += 1
-        new = [d.token for d in drafts[:accepted]] + [out[accepted]]
         # end-of-sequence inside the accepted run cuts it there
         for k, t in enumerate(new):
             if t == self.eos_id:
@@ -467,8 +480,11 @@ class DeviceDriver(InferenceEngine):
             return
         self.sched.release(live.seq)
         dt = max(1e-9, time.monotonic() - (live.t_first or live.t_submit))
-        self._emit(live, ("finished", reason, {"decode_tokens": live.generated, "proposed": live.proposed, "accepted": live.accepted,
-                                               "verify_steps": live.verify_steps, "decode_tok_s": live.generated / dt}))
+        stats = {"decode_tokens": live.generated, "proposed": live.proposed, "accepted": live.accepted,
+                 "verify_steps": live.verify_steps, "decode_tok_s": live.generated / dt}
+        if live.req.forced_tokens:
+            stats["model_choices"] = list(live.choices[:live.generated])
+        self._emit(live, ("finished", reason, stats))
 
 
 class FakeRowsEngine:

@@ -51,6 +51,9 @@ class EngineRequest:
     tools: bool = False
     tool_block_open: bool = False      # the prompt ended inside an opened calls block (tool_choice required)
     tool_dialect: str = "dsml"
+    # teacher forcing (numerics / identity gates): generation index i emits forced_tokens[i] whatever the model chose; the
+    # model's own choices come back with the result, so two runs of one forced sequence compare position by position
+    forced_tokens: list[int] = field(default_factory=list)
 
 
 @dataclass
@@ -194,6 +197,7 @@ class Generation:
         self.tools = (DsmlToolParser(req.tool_block_open) if req.tool_dialect == "dsml" else XmlToolParser()) if req.tools else None
         self.loop = LoopAbortDetector()
         self.completion_tokens = 0
+        self.model_choices: list[int] | None = None     # filled from the engine's result when the request was teacher-forced
         self.finish: str | None = None
         self.text = ""
         self.reasoning_text = ""

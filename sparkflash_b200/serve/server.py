@@ -211,6 +211,8 @@ class Server:
                 elif ev[0] == "finished":
                     reason = ev[1]
                     st = ev[2] or {}
+                    if "model_choices" in st:
+                        gen.model_choices = list(st["model_choices"])
                     if st.get("proposed"):
                         self.metrics.inc("sparkflash_draft_tokens_proposed_total", st["proposed"])
                         self.metrics.inc("vllm:spec_decode_num_draft_tokens_total", st["proposed"])
@@ -420,6 +422,13 @@ class Server:
                     r.seed += j
                 self._response_format(body, r)
                 self._trace_header(request, r)
+                forced = body.get("forced_tokens")
+                if forced is not None:
+                    # gate extension: emit exactly these tokens and report what the model would have chosen at each position
+                    if not isinstance(forced, list) or any((not isinstance(t, int)) or t < 0 or t >= self.tok.vocab_size for t in forced):
+                        raise ApiError(400, "forced_tokens must be a list of token ids inside the vocabulary", param="forced_tokens")
+                    r.forced_tokens = list(forced)
+                    r.max_tokens = len(forced)
                 self.engine.validate(r)
                 reqs.append(r)
         cid, created = "cmpl-" + uuid.uuid4().hex[:24], int(time.time())
@@ -444,7 +453,10 @@ class Server:
             async for ev in self._run(r):
                 if ev[0] == "done":
                     text = (self.tok.decode(r.prompt_tokens) if echo else "") + ev[2].text
-                    return {"index": i, "text": text, "finish_reason": _finish(ev[1]), "logprobs": None}, ev[2].completion_tokens
+                    choice = {"index": i, "text": text, "finish_reason": _finish(ev[1]), "logprobs": None}
+                    if ev[2].model_choices is not None:
+                        choice["model_choices"] = ev[2].model_choices
+                    return choice, ev[2].completion_tokens
         results = await asyncio.gather(*[collect(i, r) for i, r in enumerate(reqs)])
         pt = sum(len(p) for p in prompts)
         ct = sum(c for _, c in results)

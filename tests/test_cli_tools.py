@@ -114,3 +114,21 @@ def test_fit_estimator_and_control_panel(tmp_path):
         _t.sleep(0.1)
     assert j["state"] == "done" and j["progress"]["done"] == 1
     assert c.post("/api/jobs", json={"kind": "rm -rf"}).status_code == 400
+
+
+def test_plan_and_inkling_subcommands(capsys):
+    assert cli.main(["plan", "--world", "4", "--moe-mode", "ep"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["world"] == 4 and rep["heads_per_rank"] == 16 and rep["gb_per_rank"] > 10
+    assert set(rep["step_plans"]) >= {"1", "16", "1024"}
+    assert cli.main(["inkling-tp4", "--world", "4", "--tokens", "5"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert set(rep["max_abs_vs_unsplit"]) == {"experts", "intermediate", "rows"}
+
+
+def test_pack_engram_subcommand_resolves_its_packer():
+    import inspect
+    src = inspect.getsource(cli._pack_engram)
+    assert "engram import store" in src
+    from sparkflash_b200.engram import store
+    assert hasattr(store, "pack")

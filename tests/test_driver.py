@@ -206,3 +206,42 @@ def test_eight_sequences_share_one_verify_step_under_the_depth_policy():
     assert drv.last_allocation.rows <= 64 and sum(drv.last_allocation.keep) > 0
     # 192 tokens in a few dozen steps (prompt steps included): the drafts were accepted
     assert len(eng.steps) < 60
+
+
+def test_teacher_forcing_reports_the_models_choices_and_speculation_does_not_change_them():
+    """Forced tokens are what gets emitted and fed back; the model's own choice per position is reported, and it is the same
+    with and without a drafter, alone and beside other sequences (the served identity gate's property)."""
+    from sparkflash_b200.gates import served
+    forced = [70, 71, 33, 90, 91, 92, 40, 41, 42, 43, 60, 61]
+    prompt = [50, 51, 52, 53]
+
+    def server(drafter):
+        eng = FakeRowsEngine(max_rows=16, max_lanes=6)
+        drv = DeviceDriver(eng, TOK, drafter=drafter, prefix_reuse_min=1000, eos_id=10 ** 9, model_id="m").start()
+        return TestClient(Server(drv).app), drv
+
+    def fetch_with(client):
+        def fetch(p, f):
+            r = client.post("/v1/completions", json={"model": "m", "prompt": p, "forced_tokens": f, "temperature": 0.0})
+            assert r.status_code == 200, r.text
+            ch = r.json()["choices"][0]
+            return ch["model_choices"]
+        return fetch
+    results = {}
+    for name, drafter in (("plain", None), ("ngram", NgramDrafter(depth=4))):
+        client, drv = server(drafter)
+        try:
+            with client:
+                res = served.run(fetch_with(client), prompt, forced, concurrency=3)
+                assert res["identical"] and res["positions"] == len(forced), res
+                results[name] = res["alone"]
+        finally:
+            drv.shutdown(1.0)
+    assert results["plain"] == results["ngram"]
+    # the reported choices are the fake model's picks along the *forced* history
+    eng = FakeRowsEngine()
+    hist = prompt + forced
+    for p, t in enumerate(hist):
+        eng.lane_tokens[0][p] = t
+    want = [eng._next(0, len(prompt) - 1 + i) for i in range(len(forced))]
+    assert results["plain"] == want
