@@ -139,7 +139,9 @@ class ControlChannel:
                 raise ChannelClosed("the leader refused this rank (token mismatch, or the rank is out of range or taken)")
             s.settimeout(None)
             self._socks[0], self._locks[0] = s, threading.Lock()
-            self._last_seen[0] = time.monotonic()
+            # the leader only starts beating once every rank has joined: until its first frame arrives the silence is
+            # bounded by the connect timeout, not by the heartbeat timeout
+            self._last_seen[0] = time.monotonic() + connect_timeout - timeout
         for peer, s in self._socks.items():
             threading.Thread(target=self._reader, args=(peer, s), daemon=True).start()
         threading.Thread(target=self._beater, daemon=True).start()
