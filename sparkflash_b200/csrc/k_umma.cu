@@ -454,8 +454,44 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     const bool staged = BULK && a.pair == 0 && !a.out_f && !a.out_q && (a.out_b || a.n_peers > 0) &&
                         w.col0 + 128 <= w.col_limit && (a.out_stride & 7) == 0;
     __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(&S.a[0][0][0]);
+    // two-term activations in blocks, one split: the hi and lo accumulator columns of a token are added straight out of
+    // TMEM (the same sum, 0 + hi + lo, that the scratch path forms), without the round trip through global memory
+    const bool pair_direct = BULK && a.pair > 0 && single && 2 * a.pair <= NP && (a.pair & 15) == 0;
+    if (pair_direct) {
+      for (int c0 = 0; c0 < a.pair; c0 += 16) {
+        uint32_t v[16], u[16];
+        tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0, v);
+        tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0 + a.pair, u);
+        tc_wait_ld();
+        if (!got || S.fail) continue;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int tok = c0 + j;
+          if (tok < nv) {   // warp-uniform
+            float sum = 0.f;
+            sum += __uint_as_float(v[j]);
+            sum += __uint_as_float(u[j]);
+            if (!col_ok) sum = 0.f;
+            const int64_t o = (int64_t)(w.out_row0 + tok) * a.out_stride + col;
+            if (col_ok) {
+              if (a.out_b) a.out_b[o] = __float2bfloat16_rn(sum);
+              if (a.out_f) a.out_f[o] = sum;
+            }
+            if (a.out_q) {
+              uint8_t sc;
+              const uint8_t code = warp_quant_fp8(bfr(sum), &sc);
+              if (col_ok) {
+                a.out_q[o] = code;
+                if (lane == 0) a.out_q_atom[sf_offset(w.out_row0 + tok, col >> 5, (int)(a.out_stride >> 5))] = sc;
+              }
+            }
+          }
+        }
+      }
+    }
 #pragma unroll
     for (int c0 = 0; c0 < NP; c0 += 16) {
+      if (pair_direct) break;
       uint32_t v[16];
       tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0, v);
       tc_wait_ld();
@@ -504,7 +540,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                               __uint_as_float(v[4 * j + 3]));
       }
     }
-    if (!(single && a.pair == 0) && !a.defer_reduce) {
+    if (!(single && a.pair == 0) && !a.defer_reduce && !pair_direct) {
       // last-arriving split of this tile reduces all splits in index order
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -608,7 +644,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     if (a.n_peers > 0) {
       // this CTA finalised its tile (directly, or as the last split): count it; the CTA that completes the
       // kernel's last tile raises this rank's arrival flag on every rank
-      const bool finalised = (single && a.pair == 0) || S.last_flag;
+      const bool finalised = (single && a.pair == 0) || pair_direct || S.last_flag;
       if (finalised) {
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -852,6 +888,7 @@ namespace sfb {
 struct SplitReduceArgs {
   const float* scratch;
   int splits, tiles_total, tiles_per_group, NP, n, N;
+  int tok_tiles;              // > 1: tile ids run over (group, token tile, column tile); output row = token tile * NP + token
   __nv_bfloat16* out_b;
   float* out_f;
   int64_t out_stride;
@@ -859,11 +896,14 @@ struct SplitReduceArgs {
 __global__ void __launch_bounds__(128) splitk_reduce_kernel(SplitReduceArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  const int tile_id = blockIdx.x, tok0 = blockIdx.y * 4, c = threadIdx.x;
-  const int g = tile_id / a.tiles_per_group, tile = tile_id - g * a.tiles_per_group;
+  const int tile_id = blockIdx.x, c = threadIdx.x;
+  const int z = tile_id / a.tiles_per_group, tile = tile_id - z * a.tiles_per_group;
+  const int tt = a.tok_tiles > 1 ? a.tok_tiles : 1;
+  const int g = z / tt, tok_tile = z - g * tt;
+  const int tok_in = blockIdx.y * 4, tok0 = tok_tile * a.NP + tok_in;
   const int col = g * a.N + tile * 128 + c;
   const size_t split_stride = (size_t)a.tiles_total * 128 * a.NP;
-  const float* pp = a.scratch + ((size_t)tile_id * 128 + c) * a.NP + tok0;
+  const float* pp = a.scratch + ((size_t)tile_id * 128 + c) * a.NP + tok_in;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int sp0 = 0; sp0 < a.splits; sp0 += 8) {
     float4 t[8];
@@ -1018,8 +1058,16 @@ int sfb_umma_bulk(const void* tmapA, const void* tmapB, const void* sfa, int kat
   a.force_bulk = 1;
   a.tok_tiles = tok_tiles; a.b_maps = (const CUtensorMap*)b_maps; a.b_k_per_map = b_k_per_map; a.rs_rows = rs_rows;
   for (int i = 0; i < n_maps && b_maps; ++i) a.sfb_maps[i] = (const uint8_t*)sfb_maps[i];
-  const int rc = launch_umma(tmapA, nullptr, tmapB ? tmapB : tmapA, a, dim3((N + 127) / 128, splits, tok_tiles), NP, stream);
-  return rc;
+  const int tiles = (N + 127) / 128;
+  // many token tiles and several splits: the add of the partials runs as its own grid (one CTA per tile adding every split
+  // is latency-bound); not with an armed push, whose epilogue needs the finished tile
+  a.defer_reduce = (splits > 1 && NP >= 32 && g_push.n == 0) ? 1 : 0;
+  const int rc = launch_umma(tmapA, nullptr, tmapB ? tmapB : tmapA, a, dim3(tiles, splits, tok_tiles), NP, stream);
+  if (rc != 0 || !a.defer_reduce) return rc;
+  SplitReduceArgs r{};
+  r.scratch = scratch; r.splits = splits; r.tiles_total = tiles * tok_tiles; r.tiles_per_group = tiles; r.NP = NP; r.n = n;
+  r.N = N; r.tok_tiles = tok_tiles; r.out_b = (__nv_bfloat16*)out_b; r.out_f = out_f; r.out_stride = out_stride;
+  return (int)sfb_launch(splitk_reduce_kernel, dim3(tiles * tok_tiles, ((n < NP ? n : NP) + 3) / 4), dim3(128), 0, stream, r);
 }
 
 // Same with two-term activations (see k_quant.cu): rows [0, pair) are the hi terms, [pair, 2*pair) the lo terms.
@@ -1068,7 +1116,13 @@ int sfb_umma_bf16(const void* tmapA, const void* tmapB, int n, int NP, int N, in
   const int tiles = (N + 127) / 128;
   if (tok_tiles > 1) {
     a.force_bulk = 1; a.tok_tiles = tok_tiles;
-    return launch_umma(tmapA, nullptr, tmapB, a, dim3(tiles, splits, tok_tiles), NP, stream);
+    a.defer_reduce = (splits > 1 && g_push.n == 0) ? 1 : 0;
+    const int rc = launch_umma(tmapA, nullptr, tmapB, a, dim3(tiles, splits, tok_tiles), NP, stream);
+    if (rc != 0 || !a.defer_reduce) return rc;
+    SplitReduceArgs r{};
+    r.scratch = scratch; r.splits = splits; r.tiles_total = tiles * tok_tiles; r.tiles_per_group = tiles; r.NP = NP; r.n = n;
+    r.N = N; r.tok_tiles = tok_tiles; r.out_b = (__nv_bfloat16*)out_b; r.out_f = out_f; r.out_stride = out_stride;
+    return (int)sfb_launch(splitk_reduce_kernel, dim3(tiles * tok_tiles, (NP + 3) / 4), dim3(128), 0, stream, r);
   }
   a.defer_reduce = (splits > 1 && NP >= 32 && g_push.n == 0) ? 1 : 0;
   const int rc = launch_umma(tmapA, nullptr, tmapB, a, dim3(tiles, splits, 1), NP, stream);
