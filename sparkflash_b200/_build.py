@@ -30,6 +30,8 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--expt-relaxed-constexpr",
     "-Xcompiler", "-Wno-unused-function",
 ]
+if os.environ.get("SFB_KERNEL_MARKS") == "1":      # in-kernel phase marks (utils/kernel_marks.py): a measurement build
+    NVCC_FLAGS.append("-DSFB_KERNEL_MARKS")
 GXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", "-pthread"]
 
 

@@ -251,7 +251,7 @@ ENV_OVERRIDES: dict[str, tuple[str, Any]] = {
     "SFB_COLLECTIVE": ("parallel.collective", _choice("fused", "nccl")),
 }
 # variables that are read elsewhere and are not settings of the engine
-_ENV_PASSTHROUGH = {"SFB_REBUILD", "SFB_NVCC", "SFB_LOG", "SFB_TRACE_SCOPES", "SFB_API_KEY",
+_ENV_PASSTHROUGH = {"SFB_REBUILD", "SFB_KERNEL_MARKS", "SFB_NVCC", "SFB_LOG", "SFB_TRACE_SCOPES", "SFB_API_KEY",
                     "SFB_MODEL_ALIASES", "SFB_DEBUG_BOUNDS", "SFB_FUSED_SPLITS", "SFB_ARM", "SFB_CONTROL_TOKEN"}
 # names the host gates use (ci/host_gates.py checks that every SFB_* variable the sources read is in one of the two)
 ENV_TABLE = ENV_OVERRIDES

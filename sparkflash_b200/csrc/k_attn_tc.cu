@@ -37,6 +37,14 @@ constexpr int THREADS = 256;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// shared -> global bulk copy; the commit waits only until the copy has read its shared-memory source
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_store_commit_wait_read() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
@@ -475,6 +483,14 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
       row_lo = row_hi + a.pair_block;
     }
     const int KB = a.heads * (HD / 32);
+    // The row's outputs are collected in the (now idle) KV tile buffer - bf16 [NH][512], the two FP8 terms [NH][512] each and
+    // their scale bytes - and leave the SM as three bulk copies plus one 4-byte word of scales per thread: the head groups
+    // are contiguous in every output.  (Element stores from inside the column loop dominated the kernel.)
+    __nv_bfloat16* st_o = reinterpret_cast<__nv_bfloat16*>(S.kv);
+    uint8_t* st_hi = S.kv + NH * HD * 2;
+    uint8_t* st_lo = st_hi + NH * HD;
+    uint8_t* st_sh = st_lo + NH * HD;          // [NH * 16] scale codes of the hi term
+    uint8_t* st_sl = st_sh + NH * (HD / 32);   // and of the lo term
 #pragma unroll 1
     for (int jj = 0; jj < 2; ++jj) {
       const int j = half * 2 + jj;
@@ -487,31 +503,60 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
         uint32_t v[16];
         tc_ld16(t_o + lane_base + j * NH + c0, v);
         tc_wait_ld();
-#pragma unroll 4
+        float o[16];
+#pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const int ghead = hg * NH + c0 + i;
-          float o = bfr(__uint_as_float(v[i]) * S.fac[c0 + i]);
+          o[i] = bfr(__uint_as_float(v[i]) * S.fac[c0 + i]);
           if (roped) {        // pairs (2p, 2p+1) sit in neighbouring lanes
-            const float other = __shfl_xor_sync(0xffffffffu, o, 1);
-            o = (lane & 1) ? bfr(-other * c2.y + o * c2.x) : bfr(o * c2.x + other * c2.y);
+            const float other = __shfl_xor_sync(0xffffffffu, o[i], 1);
+            o[i] = (lane & 1) ? bfr(-other * c2.y + o[i] * c2.x) : bfr(o[i] * c2.x + other * c2.y);
           }
-          if (ghead >= a.heads) continue;                  // uniform over the CTA
-          a.out[((size_t)row * a.heads + ghead) * HD + dim] = __float2bfloat16_rn(o);
-          if (a.out_q) {
-            const float amax = warp_max(fabsf(o));
-            const uint8_t sc = act_scale_code_fp8(amax);
+          st_o[(c0 + i) * HD + dim] = __float2bfloat16_rn(o[i]);
+        }
+        if (a.out_q) {
+          uint32_t amax_bits[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float ax = (o[i] == o[i]) ? fabsf(o[i]) : 0.f;        // a NaN lane counts as 0, as under fmaxf
+            amax_bits[i] = __reduce_max_sync(0xffffffffu, __float_as_uint(ax));
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const uint8_t sc = act_scale_code_fp8(__uint_as_float(amax_bits[i]));
             const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
-            const uint8_t hi = enc_e4m3(o * inv);
-            const uint8_t lo = enc_e4m3((o * inv - e4m3_to_f32(hi)) * 16.f);
-            const size_t c = (size_t)ghead * HD + dim;
-            a.out_q[(size_t)row_hi * Wd + c] = hi;
-            a.out_q[(size_t)row_lo * Wd + c] = lo;
+            const uint8_t hi = enc_e4m3(o[i] * inv);
+            const uint8_t lo = enc_e4m3((o[i] * inv - e4m3_to_f32(hi)) * 16.f);
+            st_hi[(c0 + i) * HD + dim] = hi;
+            st_lo[(c0 + i) * HD + dim] = lo;
             if (lane == 0) {
-              const int kb = ghead * (HD / 32) + (dim >> 5);
-              a.out_atom[sf_offset(row_hi, kb, KB)] = sc;
-              a.out_atom[sf_offset(row_lo, kb, KB)] = sc >= 4 ? (uint8_t)(sc - 4) : (uint8_t)0;
+              st_sh[(c0 + i) * (HD / 32) + (dim >> 5)] = sc;
+              st_sl[(c0 + i) * (HD / 32) + (dim >> 5)] = sc >= 4 ? (uint8_t)(sc - 4) : (uint8_t)0;
             }
           }
+        }
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    const int head0 = hg * NH;
+    const int nvalid = a.heads - head0 < NH ? a.heads - head0 : NH;        // heads of this group that exist
+    if (nvalid > 0) {
+      if (tid == 0) {
+        bulk_store(a.out + ((size_t)row * a.heads + head0) * HD, smem_u32(st_o), (uint32_t)nvalid * HD * 2);
+        bulk_store_commit_wait_read();
+      } else if (tid == 32 && a.out_q) {
+        bulk_store(a.out_q + (size_t)row_hi * Wd + (size_t)head0 * HD, smem_u32(st_hi), (uint32_t)nvalid * HD);
+        bulk_store_commit_wait_read();
+      } else if (tid == 64 && a.out_q) {
+        bulk_store(a.out_q + (size_t)row_lo * Wd + (size_t)head0 * HD, smem_u32(st_lo), (uint32_t)nvalid * HD);
+        bulk_store_commit_wait_read();
+      }
+      if (a.out_q) {
+        // scale bytes: four k-blocks (one k-atom) of a row are four consecutive bytes of the atom layout
+        for (int wd = tid; wd < nvalid * (HD / 128); wd += THREADS) {
+          const int kb = head0 * (HD / 32) + wd * 4;
+          *reinterpret_cast<uint32_t*>(a.out_atom + sf_offset(row_hi, kb, KB)) = reinterpret_cast<const uint32_t*>(st_sh)[wd];
+          *reinterpret_cast<uint32_t*>(a.out_atom + sf_offset(row_lo, kb, KB)) = reinterpret_cast<const uint32_t*>(st_sl)[wd];
         }
       }
     }

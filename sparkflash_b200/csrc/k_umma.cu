@@ -80,6 +80,12 @@ __device__ __forceinline__ void bulk_store_commit_wait() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
+// commit and wait only until the copies have READ their shared-memory source (the CTA may then reuse or leave it; the
+// global writes complete on their own before the grid counts as finished)
+__device__ __forceinline__ void bulk_store_commit_wait_read() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
 }
@@ -222,8 +228,30 @@ struct UmmaArgs {
   const int* seg_expert;      // [segments] local expert id, -2 = the shared expert, -1 = unused segment
   const int* seg_count;       // [segments] pairs in the segment (1..16)
   const float* seg_weight;    // [segments * 16] routing weight of every pair slot
+  unsigned long long* marks;  // optional phase marks: sixteen %globaltimer words per CTA (see um_mark), for the first marks_cap CTAs
+  int marks_cap;
+  int swap_xy;                // grouped modes: blockIdx.x = segment, blockIdx.y = column tile (CTAs that run together work on
+                              // different segments, so one activation tile is not fetched by every SM at the same moment)
   Status* status;
 };
+
+// Phase marks inside a kernel (sixteen words per CTA; 8 = the epilogue's first accumulator read is in registers): slot 0 entry, 1 set-up done (barriers, TMEM), 2 producer about to issue its first load,
+// 3 first stage landed, 4 last MMA issued, 5 accumulator complete (epilogue starts), 6 epilogue done (stores issued and
+// waited for), 7 exit.  One word per slot and CTA, written by one thread of the role that reaches the point.
+// Compiled in only with -DSFB_KERNEL_MARKS (SFB_KERNEL_MARKS=1 at build time): with the marks present but unarmed a decode
+// step measured 3.5 % slower, so the shipped kernels carry none.
+#ifdef SFB_KERNEL_MARKS
+#define SFB_MARKS_ON 1
+__device__ __forceinline__ void um_mark(const UmmaArgs& a, int slot) {
+  if (a.marks) {
+    const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    if (cta < a.marks_cap) a.marks[(size_t)cta * 16 + slot] = globaltimer_ns();
+  }
+}
+#else
+#define SFB_MARKS_ON 0
+__device__ __forceinline__ void um_mark(const UmmaArgs&, int) {}
+#endif
 
 template <int NP, int NA, int ST>  // token columns; weight tiles per stage (2 for gate|up); stages
 struct UmmaSmem {
@@ -267,6 +295,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   constexpr uint32_t TMEM_COLS = NP + 16 <= 32 ? 32 : (NP + 16 <= 64 ? 64 : (NP + 16 <= 128 ? 128 : 256));
 
   if (threadIdx.x == 0) {
+    um_mark(a, 0);
     for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
     mbar_init(&S.acc_full, 1);
     S.fail = 0;
@@ -281,6 +310,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (threadIdx.x == 0) um_mark(a, 1);
   UmmaWork w;
   int tok_tile = 0;
   bool skip = false;
@@ -324,7 +354,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   pdl_wait();   // operands written by the previous kernel (activations, expert ids) are read below
   if (a.mode == UM_DENSE) {
   } else if (a.mode == UM_DOWN_GROUPED) {   // x = column tile of d, y = segment: W2_e times the segment's activation rows
-    const int tile = blockIdx.x, seg = blockIdx.y;
+    const int tile = a.swap_xy ? blockIdx.y : blockIdx.x, seg = a.swap_xy ? blockIdx.x : blockIdx.y;
+    const int n_tiles = a.swap_xy ? gridDim.y : gridDim.x;
     const int ksteps = (a.inter + UM_BK - 1) / UM_BK;
     int e = a.seg_expert[seg];
     if (e == -1) { skip = true; e = 0; }
@@ -341,7 +372,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     w.b_x0 = 0; w.b_row0 = seg * NP;
     w.sfb = a.sfb + (size_t)seg * a.katoms_b * 512;
     w.split = 0; w.splits = 1;
-    w.tile_id = seg * gridDim.x + tile; w.tiles_total = gridDim.x * gridDim.y;
+    w.tile_id = seg * n_tiles + tile; w.tiles_total = gridDim.x * gridDim.y;
     w.out_row0 = seg * NP; w.n_valid = skip ? 0 : a.seg_count[seg]; w.col0 = tile * 128; w.col_limit = a.d;
   } else {  // UM_DOWN: x = column tile of d, y = slot, z = token
     const int tile = blockIdx.x, slot = blockIdx.y, tok = blockIdx.z;
@@ -374,6 +405,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   if (warp == 0) {
     if (lane == 0) {
       int gated = -1;
+      um_mark(a, 2);
       for (int i = 0; i < w.nks; ++i) {
         const int s = i % UM_STAGES;
         if (i >= pre) {
@@ -412,6 +444,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         const int s = i % UM_STAGES;
         if (!mbar_wait(&S.full[s], (i / UM_STAGES) & 1)) { S.fail = 2; break; }
         tc_fence_after();
+        if (i == 0) um_mark(a, 3);
         const uint32_t sf_slot = (uint32_t)(i & 1) * 4;
         const uint32_t a_addr = smem_u32(S.a[s][0]), b_addr = smem_u32(S.b[s]);
         if (a.bf16) {
@@ -436,12 +469,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         tc_commit(&S.empty[s]);   // frees this stage's shared memory once the MMAs have read it
       }
       tc_commit(&S.acc_full);     // arrives even after a failed wait so the epilogue never hangs
+      um_mark(a, 4);
     }
   } else {
     // ---- epilogue: warp w owns TMEM lanes 32*(w%4) .. +31 = weight rows of the tile ----
     const int q = warp & 3;
     const bool got = mbar_wait(&S.acc_full, 0);
     tc_fence_after();
+    if (warp == 2 && lane == 0) um_mark(a, 5);
     const int col = w.col0 + q * 32 + lane;     // output column (row of A)
     const bool col_ok = col < w.col_limit;
     const bool single = w.splits == 1;
@@ -454,38 +489,84 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     const bool staged = BULK && a.pair == 0 && !a.out_f && !a.out_q && (a.out_b || a.n_peers > 0) &&
                         w.col0 + 128 <= w.col_limit && (a.out_stride & 7) == 0;
     __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(&S.a[0][0][0]);
+    // grouped down projection with wide segments: the fp32 tile is staged token-major in the idle operand stages and leaves
+    // as one 512-byte bulk copy per pair row (one element store per pair and thread took twice the main loop's time)
+    constexpr bool STAGE_F_FITS = NP >= 32 && NP * 512 <= UM_STAGES * UM_A_BYTES;
+    const bool stagedf = STAGE_F_FITS && !BULK && a.mode == UM_DOWN_GROUPED && a.out_f && !a.out_b && !a.out_q && single &&
+                         a.pair == 0 && a.n_peers == 0 && w.col0 + 128 <= w.col_limit && (a.out_stride & 3) == 0;
+    float* stagef = reinterpret_cast<float*>(&S.a[0][0][0]);
     // two-term activations in blocks, one split: the hi and lo accumulator columns of a token are added straight out of
     // TMEM (the same sum, 0 + hi + lo, that the scratch path forms), without the round trip through global memory
     const bool pair_direct = BULK && a.pair > 0 && single && 2 * a.pair <= NP && (a.pair & 15) == 0;
+    // ... staged: bf16 rows, FP8 codes and the rows' scale bytes are collected in the idle operand stages and leave as one
+    // bulk copy per token row (element stores from inside the column loop cost more than the main loop)
+    const bool pd_stage = pair_direct && a.out_b && !a.out_f && w.col0 + 128 <= w.col_limit && (a.out_stride & 15) == 0 &&
+                          a.pair * 384 <= UM_STAGES * UM_A_BYTES;
     if (pair_direct) {
+      __nv_bfloat16* st_b = stage;                                                      // [pair][128] bf16
+      uint8_t* st_q = reinterpret_cast<uint8_t*>(&S.a[0][0][0]) + (size_t)a.pair * 256;  // [pair][128] codes
+      uint8_t* st_sf = &S.sfa[0][0][0];                                                  // [pair][4] scale bytes (pair <= 128)
       for (int c0 = 0; c0 < a.pair; c0 += 16) {
         uint32_t v[16], u[16];
         tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0, v);
         tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0 + a.pair, u);
         tc_wait_ld();
         if (!got || S.fail) continue;
+        float sum[16];
+        uint32_t amax_bits[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float t = 0.f;
+          t += __uint_as_float(v[j]);
+          t += __uint_as_float(u[j]);
+          sum[j] = col_ok ? t : 0.f;
+        }
+        if (a.out_q) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float r = bfr(sum[j]);
+            const float ax = (r == r) ? fabsf(r) : 0.f;
+            amax_bits[j] = __reduce_max_sync(0xffffffffu, __float_as_uint(ax));
+          }
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int tok = c0 + j;
           if (tok < nv) {   // warp-uniform
-            float sum = 0.f;
-            sum += __uint_as_float(v[j]);
-            sum += __uint_as_float(u[j]);
-            if (!col_ok) sum = 0.f;
             const int64_t o = (int64_t)(w.out_row0 + tok) * a.out_stride + col;
-            if (col_ok) {
-              if (a.out_b) a.out_b[o] = __float2bfloat16_rn(sum);
-              if (a.out_f) a.out_f[o] = sum;
+            if (pd_stage) {
+              st_b[tok * 128 + q * 32 + lane] = __float2bfloat16_rn(sum[j]);
+            } else if (col_ok) {
+              if (a.out_b) a.out_b[o] = __float2bfloat16_rn(sum[j]);
+              if (a.out_f) a.out_f[o] = sum[j];
             }
             if (a.out_q) {
-              uint8_t sc;
-              const uint8_t code = warp_quant_fp8(bfr(sum), &sc);
-              if (col_ok) {
+              const uint8_t sc = act_scale_code_fp8(__uint_as_float(amax_bits[j]));
+              const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+              const uint8_t code = enc_e4m3(bfr(sum[j]) * inv);
+              if (pd_stage) {
+                st_q[tok * 128 + q * 32 + lane] = code;
+                if (lane == 0) st_sf[tok * 4 + q] = sc;
+              } else if (col_ok) {
                 a.out_q[o] = code;
                 if (lane == 0) a.out_q_atom[sf_offset(w.out_row0 + tok, col >> 5, (int)(a.out_stride >> 5))] = sc;
               }
             }
           }
+        }
+      }
+      if (pd_stage) {       // CTA-uniform
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int tok = q * 32 + lane;
+        if (tok < nv && got && !S.fail) {
+          const int64_t row = w.out_row0 + tok;
+          bulk_store(a.out_b + row * a.out_stride + w.col0, smem_u32(st_b + tok * 128), 256);
+          if (a.out_q) bulk_store(a.out_q + row * a.out_stride + w.col0, smem_u32(st_q + tok * 128), 128);
+          bulk_store_commit_wait_read();
+          if (a.out_q)
+            *reinterpret_cast<uint32_t*>(a.out_q_atom + sf_offset(row, w.col0 >> 5, (int)(a.out_stride >> 5))) =
+                *reinterpret_cast<const uint32_t*>(st_sf + tok * 4);
         }
       }
     }
@@ -495,6 +576,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       uint32_t v[16];
       tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0, v);
       tc_wait_ld();
+      if (c0 == 0 && warp == 2 && lane == 0) um_mark(a, 8);
       if (!got || S.fail) continue;
       if (skip) {
 #pragma unroll
@@ -504,6 +586,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
 #pragma unroll
         for (int j = 0; j < 16; ++j)
           if (c0 + j < nv) stage[(c0 + j) * 128 + q * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[j]));
+      } else if (stagedf) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (c0 + j < nv) stagef[(c0 + j) * 128 + q * 32 + lane] = __uint_as_float(v[j]);
       } else if (single && a.pair == 0) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -624,6 +710,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         }
       }
     }
+    if (stagedf) {        // CTA-uniform, so every epilogue warp reaches the barrier whatever its own wait returned
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int tok = q * 32 + lane;
+      if (tok < nv && got && !S.fail) {
+        bulk_store(a.out_f + (int64_t)(w.out_row0 + tok) * a.out_stride + w.col0, smem_u32(stagef + tok * 128), 512);
+        bulk_store_commit_wait_read();
+      }
+    }
     if (staged && got && !S.fail && (single || S.last_flag)) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -660,9 +755,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       }
     }
     if ((!got || S.fail) && lane == 0 && q == 0) status_set(a.status, ST_TIMEOUT, 10 + S.fail, blockIdx.x, blockIdx.y);
+    if (warp == 2 && lane == 0) um_mark(a, 6);
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) um_mark(a, 7);
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
@@ -679,12 +776,13 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   using Smem = UmmaSmem<NP, 2, UM_STAGES>;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, slot = blockIdx.y, tok = blockIdx.z;
+  const int tile = a.swap_xy ? blockIdx.y : blockIdx.x, slot = a.swap_xy ? blockIdx.x : blockIdx.y, tok = blockIdx.z;
   const int il = a.inter;
   const int nks = (a.d + UM_BK - 1) / UM_BK;
   constexpr uint32_t TMEM_COLS = 2 * NP + 24 <= 64 ? 64 : 256;
 
   if (threadIdx.x == 0) {
+    um_mark(a, 0);
     for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
     mbar_init(&S.acc_full, 1);
     S.fail = 0;
@@ -698,6 +796,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (threadIdx.x == 0) um_mark(a, 1);
   pdl_wait();
   const CUtensorMap* ma;
   int a_fp4, row_g, row_u;
@@ -745,6 +844,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {
+      um_mark(a, 2);
       for (int i = 0; i < nks_run; ++i) {
         const int s = i % UM_STAGES;
         if (i >= UM_STAGES && !mbar_wait(&S.empty[s], ((i / UM_STAGES) - 1) & 1)) { S.fail = 1; break; }
@@ -762,12 +862,16 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
       const uint32_t idesc = make_idesc(a_fp4 ? 5 : 0, 0, 128, NP);
       for (int i = 0; i < nks_run; ++i) {
         const int s = i % UM_STAGES;
+        const long long tw0 = (SFB_MARKS_ON && a.marks && i == 8) ? clock64() : 0;
         if (!mbar_wait(&S.full[s], (i / UM_STAGES) & 1)) { S.fail = 2; break; }
         tc_fence_after();
+        if (i == 0) um_mark(a, 3);
+        const long long tw1 = (SFB_MARKS_ON && a.marks && i == 8) ? clock64() : 0;
         const uint32_t sl = (uint32_t)(i & 1) * 4;
         tc_cp_sf(t_sfg + sl, make_desc(smem_u32(S.sfa[s][0]), 128, 0, 0));
         tc_cp_sf(t_sfu + sl, make_desc(smem_u32(S.sfa[s][1]), 128, 0, 0));
         tc_cp_sf(t_sfb + sl, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
+        const long long tw2 = (SFB_MARKS_ON && a.marks && i == 8) ? clock64() : 0;
         const uint32_t g_addr = smem_u32(S.a[s][0]), u_addr = smem_u32(S.a[s][1]), b_addr = smem_u32(S.b[s]);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
@@ -778,52 +882,145 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
           tc_mma_bs(t_u, make_desc(u_addr + kk * 32, 1024, 16, 2), bd, id, t_sfu + sl, t_sfb + sl, acc);
         }
         tc_commit(&S.empty[s]);
+        if (SFB_MARKS_ON && a.marks && i == 8) {      // cycle counts of one steady-state k-step of the issuing thread: wait, scale copies, MMAs + commit
+          const long long tw3 = clock64();
+          const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+          if (cta < a.marks_cap) {
+            a.marks[(size_t)cta * 16 + 13] = (unsigned long long)(tw1 - tw0);
+            a.marks[(size_t)cta * 16 + 14] = (unsigned long long)(tw2 - tw1);
+            a.marks[(size_t)cta * 16 + 15] = (unsigned long long)(tw3 - tw2);
+          }
+        }
       }
       tc_commit(&S.acc_full);
+      um_mark(a, 4);
     }
   } else {
     const int q = warp & 3;
     const bool got = mbar_wait(&S.acc_full, 0);
     tc_fence_after();
+    if (warp == 2 && lane == 0) um_mark(a, 5);
     const int col = tile * 128 + q * 32 + lane;   // column of the intermediate activation
     const int KBi = il / 32;
     const int ncol = grouped ? count : 1;         // accumulator column j = pair j of the segment (one column when ungrouped)
+    const bool live = got && !S.fail && col < il;
+    // segments: the FP8 codes of the tile are staged pair-major in the idle operand stages and leave as one 128-byte bulk
+    // copy per pair row; the routing weights of a 16-pair chunk come in with one load (a load per pair inside the loop made
+    // every pair wait for a trip to L2)
+    // (16-pair segments keep their direct stores: one chunk of columns, and the barriers and the copy's latency cost more)
+    const bool stq_cta = NP >= 32 && grouped && !skip && (tile + 1) * 128 <= il;      // CTA-uniform
+    const bool stq = stq_cta && live;
+    uint8_t* sq = &S.a[0][0][0];
+    // the tile's scale bytes are one whole 512-byte atom of the segment's atom set (k-atom = tile): staged too
+    uint8_t* ssf = &S.sfa[0][0][0];
+    const bool stsf = stq_cta && a.act_sf && !a.act_s;
+    if (stsf) {
+      reinterpret_cast<uint32_t*>(ssf)[q * 32 + lane] = 0x7f7f7f7fu;      // rows past the segment's pairs: scale 1
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+    const float limit = a.limit;
+    if (!grouped) {
+      // one token per CTA: a single accumulator column, quantised and stored directly
+      uint32_t vg[16], vu[16];
+      tc_ld16(t_g + ((uint32_t)(q * 32) << 16), vg);
+      tc_ld16(t_u + ((uint32_t)(q * 32) << 16), vu);
+      tc_wait_ld();
+      float act = 0.f;
+      if (live) {
+        const float g = fminf(bfr(__uint_as_float(vg[0])), limit);
+        const float u = fminf(fmaxf(bfr(__uint_as_float(vu[0])), -limit), limit);
+        act = bfr(g / (1.f + expf(-g)) * u * weight);
+      }
+      uint8_t sc;
+      const uint8_t code = warp_quant_fp8(act, &sc);
+      if (live && !skip) {
+        const size_t row = (size_t)tok * a.slots + slot;
+        a.act_q[row * il + col] = code;
+        if (lane == 0) {
+          if (a.act_s) a.act_s[row * KBi + col / 32] = sc;
+          if (a.act_sf) a.act_sf[row * sf_bytes(1, KBi) + sf_offset(0, col / 32, KBi)] = sc;
+        }
+      }
+    }
 #pragma unroll 1
-    for (int c0 = 0; c0 < NP && c0 < ncol; c0 += 16) {
+    for (int c0 = 0; grouped && c0 < NP && c0 < ncol; c0 += 16) {
       uint32_t vg[16], vu[16];
       tc_ld16(t_g + ((uint32_t)(q * 32) << 16) + c0, vg);
       tc_ld16(t_u + ((uint32_t)(q * 32) << 16) + c0, vu);
+      float wv = weight;
+      if (grouped) {
+        const int jx = c0 + (lane & 15);
+        wv = jx < ncol ? a.seg_weight[slot * NP + jx] : 0.f;
+      }
       tc_wait_ld();
+      if (c0 == 0 && warp == 2 && lane == 0) um_mark(a, 8);
+      if (c0 == 16 && warp == 2 && lane == 0) um_mark(a, 12);
+      // three passes over the chunk so that the sixteen columns' chains (exp, divide; reduction; encode) overlap instead
+      // of running one after the other; per column the arithmetic is unchanged
+      float act[16];
+      const int nb = ncol - c0;                   // columns of this chunk that exist (warp-uniform); the passes skip the rest
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        act[jj] = 0.f;
+        if (jj >= nb) continue;
+        const float wj = grouped ? __shfl_sync(0xffffffffu, wv, jj) : weight;
+        if (live) {
+          const float g = fminf(bfr(__uint_as_float(vg[jj])), limit);
+          const float u = fminf(fmaxf(bfr(__uint_as_float(vu[jj])), -limit), limit);
+          act[jj] = bfr(g / (1.f + expf(-g)) * u * wj);
+        }
+      }
+      uint32_t amax_bits[16];
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        amax_bits[jj] = 0u;
+        if (jj >= nb) continue;
+        const float ax = (act[jj] == act[jj]) ? fabsf(act[jj]) : 0.f;
+        amax_bits[jj] = __reduce_max_sync(0xffffffffu, __float_as_uint(ax));
+      }
 #pragma unroll
       for (int jj = 0; jj < 16; ++jj) {
         const int j = c0 + jj;
-        if (j >= ncol) break;                     // warp-uniform
-        const float wj = grouped ? a.seg_weight[slot * NP + j] : weight;
-        float act = 0.f;
-        if (got && !S.fail && col < il) {
-          const float g = fminf(bfr(__uint_as_float(vg[jj])), a.limit);
-          const float u = fminf(fmaxf(bfr(__uint_as_float(vu[jj])), -a.limit), a.limit);
-          act = bfr(g / (1.f + expf(-g)) * u * wj);
-        }
-        uint8_t sc;
-        const uint8_t code = warp_quant_fp8(act, &sc);
-        if (got && !S.fail && col < il && !skip) {
-          const size_t row = grouped ? (size_t)slot * NP + j : (size_t)tok * a.slots + slot;
-          a.act_q[row * il + col] = code;
-          if (lane == 0) {
-            if (a.act_s) a.act_s[row * KBi + col / 32] = sc;
-            if (a.act_sf) {
-              if (grouped) a.act_sf[(size_t)slot * sf_bytes(NP, KBi) + sf_offset(j, col / 32, KBi)] = sc;   // one atom set per segment, row j
-              else a.act_sf[row * sf_bytes(1, KBi) + sf_offset(0, col / 32, KBi)] = sc;
+        if (j < ncol) {                           // warp-uniform
+          const uint8_t sc = act_scale_code_fp8(__uint_as_float(amax_bits[jj]));
+          const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+          const uint8_t code = enc_e4m3(act[jj] * inv);
+          if (live && !skip) {
+            const size_t row = grouped ? (size_t)slot * NP + j : (size_t)tok * a.slots + slot;
+            if (stq) sq[j * 128 + q * 32 + lane] = code;
+            else a.act_q[row * il + col] = code;
+            if (lane == 0) {
+              if (a.act_s) a.act_s[row * KBi + col / 32] = sc;
+              if (stsf) {
+                ssf[(j & 31) * 16 + (j >> 5) * 4 + q] = sc;
+              } else if (a.act_sf) {
+                if (grouped) a.act_sf[(size_t)slot * sf_bytes(NP, KBi) + sf_offset(j, col / 32, KBi)] = sc;   // one atom set per segment, row j
+                else a.act_sf[row * sf_bytes(1, KBi) + sf_offset(0, col / 32, KBi)] = sc;
+              }
             }
           }
         }
       }
     }
+    if (warp == 2 && lane == 0) um_mark(a, 9);
+    if (stq_cta) {        // CTA-uniform, so every epilogue warp reaches the barrier whatever its own wait returned
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) um_mark(a, 10);
+      const int j = q * 32 + lane;
+      if (got && !S.fail) {
+        bool any = false;
+        if (j < ncol) { bulk_store(a.act_q + ((size_t)slot * NP + j) * il + tile * 128, smem_u32(sq + j * 128), 128); any = true; }
+        if (stsf && j == 0) { bulk_store(a.act_sf + (size_t)slot * sf_bytes(NP, KBi) + (size_t)tile * 512, smem_u32(ssf), 512); any = true; }
+        if (any) bulk_store_commit_wait_read();
+      }
+    }
     if ((!got || S.fail) && lane == 0 && q == 0) status_set(a.status, ST_TIMEOUT, 20 + S.fail, blockIdx.x, blockIdx.y);
+    if (warp == 2 && lane == 0) um_mark(a, 6);
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) um_mark(a, 7);
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
@@ -952,6 +1149,28 @@ struct GatherSpec {
 };
 static thread_local GatherSpec g_gather;
 
+// Tuning switches for measurements (0 = the shipped choice): [1] stages of the 64-pair down projection (2 shipped; 3, 4),
+// [2] stages of the 64-pair gate/up (2 = two CTAs per SM; 3, 5 = one CTA per SM).
+static int g_tune[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+// Phase marks (um_mark) of the NEXT launch of a tensor-core GEMM of this library: cleared by that launch.
+static thread_local unsigned long long* g_marks = nullptr;
+static thread_local int g_marks_cap = 0;
+int sfb_umma_set_marks(void* buf, int cap_ctas) {
+  if (buf && !SFB_MARKS_ON) return (int)cudaErrorNotSupported;     // this library was built without the marks
+  g_marks = (unsigned long long*)buf; g_marks_cap = buf ? cap_ctas : 0;
+  return 0;
+}
+int sfb_umma_has_marks(void) { return SFB_MARKS_ON; }
+static void apply_marks(UmmaArgs& a) {
+  a.marks = g_marks; a.marks_cap = g_marks_cap;
+  g_marks = nullptr; g_marks_cap = 0;
+}
+int sfb_umma_tune(int key, int value) {
+  if (key < 0 || key >= 8) return (int)cudaErrorInvalidValue;
+  g_tune[key] = value;
+  return 0;
+}
+
 // An entry point that refuses its arguments must not leave a push or gather armed for some later, unrelated launch.
 static int refuse_args() {
   g_push.n = 0;
@@ -966,7 +1185,9 @@ static void apply_gather(UmmaArgs& a) {
   g_gather.n = 0;
 }
 
+static void apply_marks(UmmaArgs& a);
 static void apply_push(UmmaArgs& a) {
+  apply_marks(a);
   a.n_peers = g_push.n;
   for (int i = 0; i < g_push.n; ++i) { a.peer_out[i] = (__nv_bfloat16*)g_push.out[i]; a.peer_flag[i] = (uint32_t*)g_push.flag[i]; }
   a.epoch_ptr = (const uint32_t*)g_push.epoch_ptr; a.epoch_add = g_push.epoch_add; a.done_counter = (unsigned int*)g_push.done;
@@ -1187,13 +1408,30 @@ int sfb_umma_gate_up_grouped(const void* tmapA, const void* tmapA2, const void* 
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (d / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
   a.a_fp4 = 1; a.top_k = 0; a.slots = 1; a.inter = inter; a.d = d; a.act_q = (uint8_t*)act_q; a.act_sf = (uint8_t*)act_sf; a.limit = limit;
   a.seg_expert = seg_expert; a.seg_count = seg_count; a.seg_weight = seg_weight; a.status = (Status*)status;
+  apply_marks(a);
   const CUtensorMap* mA = (const CUtensorMap*)tmapA;
   const CUtensorMap* mA2 = (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA);
+  if (seg_size == 64 && g_tune[2] == 3) {      // tuning arm: one 3-stage CTA per SM
+    const size_t smem = sizeof(UmmaSmem<64, 2, 3>) + 1024;
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(umma_gateup_kernel<3, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+    return (int)sfb_launch(umma_gateup_kernel<3, 64>, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem, stream, *mA, *mA2,
+                           *(const CUtensorMap*)tmapB, a);
+  }
+  if (seg_size == 64 && g_tune[2] == 5) {      // tuning arm: one 5-stage CTA per SM
+    const size_t smem = sizeof(UmmaSmem<64, 2, 5>) + 1024;
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(umma_gateup_kernel<5, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+    return (int)sfb_launch(umma_gateup_kernel<5, 64>, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem, stream, *mA, *mA2,
+                           *(const CUtensorMap*)tmapB, a);
+  }
   if (seg_size == 64) {      // segments of up to 64 pairs: two 2-stage CTAs per SM (a stage holds 32 KiB of weights and 8 KiB of tokens)
     const size_t smem64 = sizeof(UmmaSmem<64, 2, 2>) + 1024;
     static bool done64 = false;
     if (!done64) { cudaFuncSetAttribute(umma_gateup_kernel<2, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem64); done64 = true; }
-    return (int)sfb_launch(umma_gateup_kernel<2, 64>, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem64, stream, *mA, *mA2,
+    a.swap_xy = g_tune[4] ? 1 : 0;
+    const dim3 grid = a.swap_xy ? dim3(segments, inter / 128, 1) : dim3(inter / 128, segments, 1);
+    return (int)sfb_launch(umma_gateup_kernel<2, 64>, grid, dim3(UM_THREADS), smem64, stream, *mA, *mA2,
                            *(const CUtensorMap*)tmapB, a);
   }
   if ((inter / 128) * segments > 2 * 148) {      // several waves: two half-depth CTAs per SM
@@ -1218,11 +1456,22 @@ int sfb_umma_down_grouped(const void* tmapA, const void* tmapA2, const void* tma
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (inter / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
   a.a_fp4 = 1; a.mode = UM_DOWN_GROUPED; a.inter = inter; a.d = d; a.out_f = out_f; a.out_stride = d; a.seg_expert = seg_expert;
   a.seg_count = seg_count; a.status = (Status*)status; a.splits = 1;
+  if (seg_size == 64 && g_tune[1] != 3) {      // shipped: 2 stages, so that three CTAs share an SM (measured best); tuning arm 4 stages
+    apply_push(a); apply_gather(a);
+    a.tok_tiles = 1;
+    a.swap_xy = g_tune[3] ? 1 : 0;
+    if (g_tune[1] != 4)
+      return (int)launch_umma_t<64, false, 2>((const CUtensorMap*)tmapA, (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA),
+                                              (const CUtensorMap*)tmapB, a, a.swap_xy ? dim3(segments, d / 128, 1) : dim3(d / 128, segments, 1), stream);
+    return (int)launch_umma_t<64, false, 4>((const CUtensorMap*)tmapA, (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA),
+                                            (const CUtensorMap*)tmapB, a, dim3(d / 128, segments, 1), stream);
+  }
   if (seg_size == 64) {
     apply_push(a); apply_gather(a);
     a.tok_tiles = 1;
+    a.swap_xy = g_tune[3] ? 1 : 0;
     return (int)launch_umma_t<64, false, 3>((const CUtensorMap*)tmapA, (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA),
-                                            (const CUtensorMap*)tmapB, a, dim3(d / 128, segments, 1), stream);
+                                            (const CUtensorMap*)tmapB, a, a.swap_xy ? dim3(segments, d / 128, 1) : dim3(d / 128, segments, 1), stream);
   }
   if ((d / 128) * segments > 4 * 148) {      // many waves of 16-k-step CTAs: three 3-stage CTAs per SM
     apply_push(a); apply_gather(a);

@@ -410,11 +410,13 @@ class Engine:
             tb = tcb.bmap(xq_buf, x_rows, K, 128)
             tiles = ((N_ + 127) // 128) * ((n + 127) // 128)
             splits = self._splits_bulk(tiles, K // 128)
+            self._arm_marks(f"dense_bulk_{N_}x{K}")
             N.umma_bulk(M.tmap, tb, M.atoms, atoms, n, N_, K, splits=splits, scratch=tcb.scratch, tickets=tcb.tickets,
                         out_b=out_b, out_stride=out_stride if out_stride is not None else N_, status=self.status)
             self._k()
             return
         NP = N.umma_np(2 * pair if pair else n)
+        self._arm_marks(f"dense_{N_}x{K}")
         tb = tcb.bmap(xq_buf, x_rows, K * groups, NP)
         tiles = groups * ((N_ + 127) // 128)
         splits = self._splits(tiles, K // 128)
@@ -656,6 +658,13 @@ class Engine:
             grp[seg] = g
         return grp[seg]
 
+    def _arm_marks(self, name: str) -> None:
+        """In-kernel phase marks for the next tensor-core launch when ``self.kernel_marks[name]`` holds a buffer (int64, eight
+        words per CTA): entry, set-up, first load, first stage landed, last MMA, accumulator complete, epilogue done, exit."""
+        buf = self.__dict__.get("kernel_marks", {}).get(name)
+        if buf is not None:
+            N.umma_set_marks(buf)
+
     def _ffn_grouped(self, n: int, T, k: int, shared_here: bool) -> None:
         """Routed + shared experts for n rows with each expert's weights read once per segment of pairs (csrc/k_moe.cu moe_plan).
         Per-pair arithmetic and the per-token slot-order sum are those of the ungrouped kernels: the bits do not change."""
@@ -668,8 +677,10 @@ class Engine:
         N.moe_plan(self.ids, self.wts, n, k, E_local, shared_here, S, g["seg_expert"], g["seg_count"], g["seg_weight"], g["seg_token"], g["pair_pos"],
                    seg=seg); self._k()
         N.moe_permute(self.xq, self.xs, g["seg_token"], g["xperm"], g["x_atoms"], S * seg, d, g["x_atom_bytes"], seg=seg); self._k()
+        self._arm_marks("moe_gate_up")
         N.umma_gate_up_grouped(T.w13.tmap, T.s13.tmap, g["tmap_x"], T.w13.atoms, T.s13.atoms, g["x_atoms"], g["seg_expert"], g["seg_count"],
                                g["seg_weight"], g["act_q"], g["act_sf"], S, d, self.il, cfg.swiglu_limit, status=self.status, seg=seg); self._k()
+        self._arm_marks("moe_down")
         N.umma_down_grouped(T.w2.tmap, T.s2.tmap, g["tmap_act"], T.w2.atoms, T.s2.atoms, g["act_sf"], g["seg_expert"], g["seg_count"], g["ypair"],
                             S, d, self.il, status=self.status, seg=seg); self._k()
         N.moe_combine(g["ypair"], g["pair_pos"], self.y_ffn, n, k + 1, d, self.y_ffn.stride(0)); self._k()

@@ -414,6 +414,22 @@ def bf16_map(t: torch.Tensor, rows: int, K: int, box_rows: int) -> TensorMap:
     return TensorMap(t, rows, 2 * K, 2 * K, box_rows)
 
 
+def umma_tune(key: int, value: int) -> None:
+    """Measurement switch of the MoE launchers (csrc/k_umma.cu g_tune); 0 restores the shipped choice."""
+    _check(lib().sfb_umma_tune(c_int(key), c_int(value)), "umma_tune")
+
+
+def umma_set_marks(buf, ctas: int | None = None) -> None:
+    """Arm phase marks for the next tensor-core GEMM launch of this thread: ``buf`` is an int64 device tensor with sixteen
+    words per CTA (csrc/k_umma.cu um_mark); None disarms."""
+    if buf is not None and not lib().sfb_umma_has_marks():
+        raise RuntimeError("this library was built without in-kernel marks: rebuild with SFB_KERNEL_MARKS=1 SFB_REBUILD=1")
+    if buf is None:
+        _check(lib().sfb_umma_set_marks(None, c_int(0)), "umma_set_marks")
+    else:
+        _check(lib().sfb_umma_set_marks(_p(buf), c_int(buf.numel() // 16 if ctas is None else ctas)), "umma_set_marks")
+
+
 def umma_bf16(tmap_a, tmap_b, n, N, K, *, splits=1, scratch=None, tickets=None, out_b=None, out_f=None, out_stride=None,
               status=None, NP=None):
     """out[token, col] = sum_k W[col, k] X[token, k] with bf16 operands on tcgen05 kind::f16 (fp32 accumulate)."""

@@ -21,9 +21,15 @@ def main() -> None:
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--layers", type=int, default=3)
     ap.add_argument("--steps", type=int, default=12, help="prompt chunks to run (the last one is the profiled / timed one)")
+    ap.add_argument("--marks", default="", help="kernels whose in-kernel phase marks are printed for the last step, e.g. moe_down,moe_gate_up")
+    ap.add_argument("--tune", default="", help="measurement switches of the MoE launchers, key=value[,key=value]")
     args = ap.parse_args()
     from sparkflash_b200.config import reduced_config
     from sparkflash_b200.models.deepseek_v41 import engine as E, prepare as P
+    from sparkflash_b200.ops import native as N
+    for kv in filter(None, args.tune.split(",")):
+        k, v = kv.split("=")
+        N.umma_tune(int(k), int(v))
     cfg = reduced_config(args.experts, args.layers)
     w = P.prepare_synthetic(cfg, 0, 1)
     rows = args.rows
@@ -43,11 +49,15 @@ def main() -> None:
         pos = 0
         for i in range(args.steps):
             if i == args.steps - 1:
+                eng.kernel_marks = {k: torch.zeros(16 * 16384, dtype=torch.int64, device="cuda") for k in filter(None, args.marks.split(","))}
                 torch.cuda.synchronize(); torch.cuda.profiler.start(); ev0.record()
             eng.step(prompt[pos:pos + rows], [0] * rows, list(range(pos, pos + rows)), head=False, sync=False); pos += rows
         ev1.record()
     torch.cuda.synchronize(); torch.cuda.profiler.stop()
     eng.check_status()
+    for name, buf in getattr(eng, "kernel_marks", {}).items():
+        from sparkflash_b200.utils.kernel_marks import summarize
+        print(name, summarize(buf))
     if not args.decode:
         print(f"last chunk: {rows} rows at context {pos} in {ev0.elapsed_time(ev1):.3f} ms ({args.layers} layers)")
     print("ok")

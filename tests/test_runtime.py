@@ -79,3 +79,27 @@ def test_group_lanes_detect_a_rank_that_took_another_branch():
     lead.report(0, 5, "x")
     assert lead.in_step(5) is None
     lead.check(5)
+
+
+def test_kernel_marks_summary_separates_idle_ctas_and_old_launches():
+    """Phase marks: the summary uses the CTAs of the newest launch, tells idle CTAs (no stage ever landed) from working ones
+    and reports the phases in microseconds."""
+    import torch
+    from sparkflash_b200.utils.kernel_marks import summarize
+    m = torch.zeros(6, 16, dtype=torch.int64)
+    base = 1_000_000_000
+    # two working CTAs of the newest launch
+    for i, life in enumerate((20_000, 24_000)):
+        t0 = base + i * 1000
+        m[i, :8] = torch.tensor([t0, t0 + 250, t0 + 1250, t0 + 2250, t0 + 10_250, t0 + 10_300, t0 + life - 200, t0 + life])
+        m[i, 8] = t0 + 10_400
+    # an idle CTA of the newest launch: its "first stage landed" mark is left over from an older launch
+    m[2, :8] = torch.tensor([base + 50, base + 300, base + 700, base - 500_000, base + 800, base + 900, base + 1900, base + 2000])
+    # a CTA slot only an older launch touched (a second earlier)
+    m[3, :8] = torch.tensor([base - 10**9 + k for k in range(8)])
+    rep = summarize(m.view(-1))
+    assert rep["ctas"] == 3 and rep["ctas_with_work"] == 2
+    assert rep["idle_cta_us"] == pytest.approx(1.95, abs=0.01)
+    assert rep["setup_us"] == pytest.approx(0.25) and rep["mainloop_us"] == pytest.approx(8.0) and rep["first_stage_latency_us"] == pytest.approx(1.0)
+    assert rep["epilogue_first_read_us"] == pytest.approx(0.1)
+    assert summarize(torch.zeros(32, dtype=torch.int64)) == {"ctas": 0}
