@@ -175,7 +175,7 @@ def test_supervisor_records_the_group_and_signals_exactly_it(tmp_path):
     started = []
 
     class P:
-        pid = os.getpid()                                                    # a process group that is certainly alive: ours
+        pid = os.getpgid(0)                                                  # a process group that is certainly alive: ours
 
     def popen(argv, **kw):
         started.append((argv, kw))
@@ -186,7 +186,7 @@ def test_supervisor_records_the_group_and_signals_exactly_it(tmp_path):
     assert supervisor.status(pidf)["alive"] is True
     sent = []
     rep = supervisor.stop(pidf, wait_s=0.3, kill=lambda pg, sig: sent.append((pg, sig)))
-    assert sent == [(os.getpgid(0) if False else P.pid, signal.SIGTERM)] and rep["ok"] is False   # our own group does not exit
+    assert sent == [(P.pid, signal.SIGTERM)] and rep["ok"] is False         # our own group does not exit
     pidf.write_text(json.dumps({"pgid": 2 ** 22 - 3}))                       # a group that does not exist
     assert "stale" in supervisor.stop(pidf)["state"] and not pidf.exists()
     assert supervisor.command_line(1, 1, ["--mock"])[1:4] == ["-m", "sparkflash_b200", "serve"]
