@@ -768,8 +768,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
 // UM_STAGES = 6 fills one SM's shared memory with a single CTA (few CTAs: decode); 3 lets two CTAs share an SM, so that one's
 // prologue and epilogue hide behind the other's weight stream when a launch has many waves (grouped many-row steps)
 // NP = token columns: 16 (a token, or a segment of up to 16 pairs) or 64 (many-row steps: segments of up to 64 pairs)
+// Warps: 0 = TMA producer, 1 = MMA issue for the gate tile, 2..5 = epilogue, 6 = MMA issue for the up tile.  One thread
+// issues a tcgen05 operation about every 75 cycles whatever its size, and with 16-column tiles that - not the data - paced
+// the main loop; the two accumulators are independent, so each gets its own issuing thread (and its own copy of the
+// activation scales in TMEM, because copies and MMAs of different threads are not ordered against each other).
+constexpr int GU_THREADS = UM_THREADS + 32;
 template <int UM_STAGES, int NP = 16>
-__global__ void __launch_bounds__(UM_THREADS, UM_STAGES <= 3 ? 2 : 1)
+__global__ void __launch_bounds__(GU_THREADS, UM_STAGES <= 3 ? 2 : 1)
 umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
                    const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -779,12 +784,12 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   const int tile = a.swap_xy ? blockIdx.y : blockIdx.x, slot = a.swap_xy ? blockIdx.x : blockIdx.y, tok = blockIdx.z;
   const int il = a.inter;
   const int nks = (a.d + UM_BK - 1) / UM_BK;
-  constexpr uint32_t TMEM_COLS = 2 * NP + 24 <= 64 ? 64 : 256;
+  constexpr uint32_t TMEM_COLS = 2 * NP + 32 <= 64 ? 64 : 256;
 
   if (threadIdx.x == 0) {
     um_mark(a, 0);
-    for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
-    mbar_init(&S.acc_full, 1);
+    for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 2); }   // both issuing threads free a stage
+    mbar_init(&S.acc_full, 2);
     S.fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -839,7 +844,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   const uint32_t STAGE_TX = 2 * (a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 3 * 512;
   const uint32_t tmem = S.tmem_base;
   const uint32_t t_g = tmem, t_u = tmem + NP;
-  const uint32_t t_sfg = tmem + 2 * NP, t_sfu = tmem + 2 * NP + 8, t_sfb = tmem + 2 * NP + 16;
+  const uint32_t t_sfg = tmem + 2 * NP, t_sfu = tmem + 2 * NP + 8, t_sfb = tmem + 2 * NP + 16, t_sfb2 = tmem + 2 * NP + 24;
   const int nks_run = skip ? 0 : nks;
 
   if (warp == 0) {
@@ -857,32 +862,32 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
         bulk_load(S.sfb[s], sfb + (size_t)i * 512, 512, &S.full[s]);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 6) {
     if (lane == 0) {
+      const int h = warp == 1 ? 0 : 1;           // 0: gate tile, 1: up tile
       const uint32_t idesc = make_idesc(a_fp4 ? 5 : 0, 0, 128, NP);
+      const uint32_t t_d = h ? t_u : t_g, t_sa = h ? t_sfu : t_sfg, t_sb = h ? t_sfb2 : t_sfb;
       for (int i = 0; i < nks_run; ++i) {
         const int s = i % UM_STAGES;
-        const long long tw0 = (SFB_MARKS_ON && a.marks && i == 8) ? clock64() : 0;
+        const long long tw0 = (SFB_MARKS_ON && a.marks && i == 8 && h == 0) ? clock64() : 0;
         if (!mbar_wait(&S.full[s], (i / UM_STAGES) & 1)) { S.fail = 2; break; }
         tc_fence_after();
-        if (i == 0) um_mark(a, 3);
-        const long long tw1 = (SFB_MARKS_ON && a.marks && i == 8) ? clock64() : 0;
+        if (i == 0 && h == 0) um_mark(a, 3);
+        const long long tw1 = (SFB_MARKS_ON && a.marks && i == 8 && h == 0) ? clock64() : 0;
         const uint32_t sl = (uint32_t)(i & 1) * 4;
-        tc_cp_sf(t_sfg + sl, make_desc(smem_u32(S.sfa[s][0]), 128, 0, 0));
-        tc_cp_sf(t_sfu + sl, make_desc(smem_u32(S.sfa[s][1]), 128, 0, 0));
-        tc_cp_sf(t_sfb + sl, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
-        const long long tw2 = (SFB_MARKS_ON && a.marks && i == 8) ? clock64() : 0;
-        const uint32_t g_addr = smem_u32(S.a[s][0]), u_addr = smem_u32(S.a[s][1]), b_addr = smem_u32(S.b[s]);
+        tc_cp_sf(t_sa + sl, make_desc(smem_u32(S.sfa[s][h]), 128, 0, 0));
+        tc_cp_sf(t_sb + sl, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
+        const long long tw2 = (SFB_MARKS_ON && a.marks && i == 8 && h == 0) ? clock64() : 0;
+        const uint32_t w_addr = smem_u32(S.a[s][h]), b_addr = smem_u32(S.b[s]);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const uint64_t bd = make_desc(b_addr + kk * 32, 1024, 16, 2);
           const uint32_t id = idesc | ((uint32_t)kk << 29) | ((uint32_t)kk << 4);
           const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-          tc_mma_bs(t_g, make_desc(g_addr + kk * 32, 1024, 16, 2), bd, id, t_sfg + sl, t_sfb + sl, acc);
-          tc_mma_bs(t_u, make_desc(u_addr + kk * 32, 1024, 16, 2), bd, id, t_sfu + sl, t_sfb + sl, acc);
+          tc_mma_bs(t_d, make_desc(w_addr + kk * 32, 1024, 16, 2), bd, id, t_sa + sl, t_sb + sl, acc);
         }
         tc_commit(&S.empty[s]);
-        if (SFB_MARKS_ON && a.marks && i == 8) {      // cycle counts of one steady-state k-step of the issuing thread: wait, scale copies, MMAs + commit
+        if (SFB_MARKS_ON && a.marks && i == 8 && h == 0) {      // cycle counts of one steady-state k-step of the issuing thread: wait, scale copies, MMAs + commit
           const long long tw3 = clock64();
           const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
           if (cta < a.marks_cap) {
@@ -892,8 +897,8 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
           }
         }
       }
-      tc_commit(&S.acc_full);
-      um_mark(a, 4);
+      tc_commit(&S.acc_full);     // arrives even after a failed wait so the epilogue never hangs
+      if (h == 0) um_mark(a, 4);
     }
   } else {
     const int q = warp & 3;
@@ -1366,6 +1371,7 @@ int sfb_umma_gate_up(const void* tmapA, const void* tmapA2, const void* tmapB, c
   a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a; a.a_fp4 = 1; a.ids = ids; a.wts = wts; a.top_k = top_k;
   a.slots = slots; a.inter = inter; a.d = d; a.act_q = (uint8_t*)act_q; a.act_s = (uint8_t*)act_s;
   a.act_sf = (uint8_t*)act_sf; a.limit = limit; a.status = (Status*)status;
+  apply_marks(a);
   const size_t smem = sizeof(UmmaSmem<16, 2, UM_STAGES_GATEUP>) + 1024;
   static bool done = false;
   if (!done) {
@@ -1374,7 +1380,7 @@ int sfb_umma_gate_up(const void* tmapA, const void* tmapA2, const void* tmapB, c
   }
   const CUtensorMap* mA = (const CUtensorMap*)tmapA;
   const CUtensorMap* mA2 = (const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA);
-  return (int)sfb_launch(umma_gateup_kernel<UM_STAGES_GATEUP>, dim3(inter / 128, slots, n_tok), dim3(UM_THREADS), smem, stream, *mA, *mA2,
+  return (int)sfb_launch(umma_gateup_kernel<UM_STAGES_GATEUP>, dim3(inter / 128, slots, n_tok), dim3(GU_THREADS), smem, stream, *mA, *mA2,
                          *(const CUtensorMap*)tmapB, a);
 }
 
@@ -1415,14 +1421,14 @@ int sfb_umma_gate_up_grouped(const void* tmapA, const void* tmapA2, const void* 
     const size_t smem = sizeof(UmmaSmem<64, 2, 3>) + 1024;
     static bool done = false;
     if (!done) { cudaFuncSetAttribute(umma_gateup_kernel<3, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
-    return (int)sfb_launch(umma_gateup_kernel<3, 64>, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem, stream, *mA, *mA2,
+    return (int)sfb_launch(umma_gateup_kernel<3, 64>, dim3(inter / 128, segments, 1), dim3(GU_THREADS), smem, stream, *mA, *mA2,
                            *(const CUtensorMap*)tmapB, a);
   }
   if (seg_size == 64 && g_tune[2] == 5) {      // tuning arm: one 5-stage CTA per SM
     const size_t smem = sizeof(UmmaSmem<64, 2, 5>) + 1024;
     static bool done = false;
     if (!done) { cudaFuncSetAttribute(umma_gateup_kernel<5, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
-    return (int)sfb_launch(umma_gateup_kernel<5, 64>, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem, stream, *mA, *mA2,
+    return (int)sfb_launch(umma_gateup_kernel<5, 64>, dim3(inter / 128, segments, 1), dim3(GU_THREADS), smem, stream, *mA, *mA2,
                            *(const CUtensorMap*)tmapB, a);
   }
   if (seg_size == 64) {      // segments of up to 64 pairs: two 2-stage CTAs per SM (a stage holds 32 KiB of weights and 8 KiB of tokens)
@@ -1431,20 +1437,20 @@ int sfb_umma_gate_up_grouped(const void* tmapA, const void* tmapA2, const void* 
     if (!done64) { cudaFuncSetAttribute(umma_gateup_kernel<2, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem64); done64 = true; }
     a.swap_xy = g_tune[4] ? 1 : 0;
     const dim3 grid = a.swap_xy ? dim3(segments, inter / 128, 1) : dim3(inter / 128, segments, 1);
-    return (int)sfb_launch(umma_gateup_kernel<2, 64>, grid, dim3(UM_THREADS), smem64, stream, *mA, *mA2,
+    return (int)sfb_launch(umma_gateup_kernel<2, 64>, grid, dim3(GU_THREADS), smem64, stream, *mA, *mA2,
                            *(const CUtensorMap*)tmapB, a);
   }
   if ((inter / 128) * segments > 2 * 148) {      // several waves: two half-depth CTAs per SM
     const size_t smem3 = sizeof(UmmaSmem<16, 2, 3>) + 1024;
     static bool done3 = false;
     if (!done3) { cudaFuncSetAttribute(umma_gateup_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3); done3 = true; }
-    return (int)sfb_launch(umma_gateup_kernel<3>, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem3, stream, *mA, *mA2,
+    return (int)sfb_launch(umma_gateup_kernel<3>, dim3(inter / 128, segments, 1), dim3(GU_THREADS), smem3, stream, *mA, *mA2,
                            *(const CUtensorMap*)tmapB, a);
   }
   const size_t smem = sizeof(UmmaSmem<16, 2, UM_STAGES_GATEUP>) + 1024;
   static bool done = false;
   if (!done) { cudaFuncSetAttribute(umma_gateup_kernel<UM_STAGES_GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
-  return (int)sfb_launch(umma_gateup_kernel<UM_STAGES_GATEUP>, dim3(inter / 128, segments, 1), dim3(UM_THREADS), smem, stream, *mA, *mA2, *(const CUtensorMap*)tmapB, a);
+  return (int)sfb_launch(umma_gateup_kernel<UM_STAGES_GATEUP>, dim3(inter / 128, segments, 1), dim3(GU_THREADS), smem, stream, *mA, *mA2, *(const CUtensorMap*)tmapB, a);
 }
 
 // out_f [segments*16, d] fp32: one row per pair slot (the caller sums a token's pairs in slot order)

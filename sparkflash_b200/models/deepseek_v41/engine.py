@@ -723,12 +723,14 @@ class Engine:
         if T is not None and T.w13 is not None:
             tcb = self.tcb
             tbx = tcb.bmap(self.xq, self.max_rows, d, 16)
+            self._arm_marks("moe_gate_up")
             N.umma_gate_up(T.w13.tmap, T.s13.tmap, tbx, T.w13.atoms, T.s13.atoms, tcb.xs_atom_tok, self.ids, self.wts,
                            self.act_q, self.act_s, tcb.act_sf, n, k, slots, d, self.il, cfg.swiglu_limit,
                            status=self.status); self._k()
             self._prefetch(n, (self._next_wqkv,) if self._next_wqkv is not self.w.head else ())
             tba = tcb.bmap(self.act_q, self.max_rows * (k + 1), self.il, 16)
             self._pushed = self._arm_push(1, sub)
+            self._arm_marks("moe_down")
             N.umma_down(T.w2.tmap, T.s2.tmap, tba, T.w2.atoms, T.s2.atoms, tcb.act_sf, self.ids, self.y_ffn, None, d,
                         tcb.scratch, tcb.tickets, n, k, slots, d, self.il, status=self.status); self._k()
             return

@@ -43,6 +43,7 @@ def main() -> None:
             eng.step(prompt[:64], [s] * 64, list(range(64)), head=False)
         for i in range(3):
             if i == 2:
+                eng.kernel_marks = {k: torch.zeros(16 * 16384, dtype=torch.int64, device="cuda") for k in filter(None, args.marks.split(","))}
                 torch.cuda.synchronize(); torch.cuda.profiler.start()
             eng.step(prompt[:rows], list(range(rows)), [64 + i] * rows)
     else:
