@@ -102,20 +102,32 @@ __global__ void __launch_bounds__(128) fold_slots_kernel(FoldArgs a) {
     for (int j = 0; j < 8; ++j) vals[p][j] = 0.f;
   // one round trip per source instead of one per (source, pass): all of a source's 16-byte loads of this row are issued
   // before the first add.  Each element still adds slot 0, slot 1, ..., then the residual: same sums as before
-  for (int r = 0; r <= a.W; ++r) {
-    const __nv_bfloat16* src = r < a.W ? a.slot[r] + (int64_t)row * a.stride : (a.residual ? a.residual + (int64_t)row * a.d : nullptr);
-    if (!src) break;
-    uint4 u[PASS];
+  // two sources per round trip: both sources' loads are issued before either is added (slot order of the adds unchanged)
+  for (int r = 0; r <= a.W; r += 2) {
+    const __nv_bfloat16* src0 = r < a.W ? a.slot[r] + (int64_t)row * a.stride : (a.residual ? a.residual + (int64_t)row * a.d : nullptr);
+    const __nv_bfloat16* src1 = r + 1 < a.W ? a.slot[r + 1] + (int64_t)row * a.stride
+                                            : (r + 1 == a.W && a.residual ? a.residual + (int64_t)row * a.d : nullptr);
+    if (!src0) break;
+    uint4 u[PASS], u1[PASS];
 #pragma unroll
     for (int p = 0; p < PASS; ++p) {
       const int c = (p * 128 + threadIdx.x) * 8;
-      u[p] = c < a.d ? *reinterpret_cast<const uint4*>(src + c) : make_uint4(0, 0, 0, 0);
+      u[p] = c < a.d ? *reinterpret_cast<const uint4*>(src0 + c) : make_uint4(0, 0, 0, 0);
+      u1[p] = (src1 && c < a.d) ? *reinterpret_cast<const uint4*>(src1 + c) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int p = 0; p < PASS; ++p) {
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[p]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); vals[p][2 * j] += f.x; vals[p][2 * j + 1] += f.y; }
+    }
+    if (src1) {
+#pragma unroll
+      for (int p = 0; p < PASS; ++p) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u1[p]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); vals[p][2 * j] += f.x; vals[p][2 * j + 1] += f.y; }
+      }
     }
   }
 #pragma unroll

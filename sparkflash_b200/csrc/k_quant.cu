@@ -15,10 +15,13 @@ struct QuantArgs {
   uint8_t* s;               // optional row-major scales [rows_out, K/32]
   uint8_t* atom;            // optional atoms (rows = output rows)
   int n, K, split, split_off;
+  uint32_t* epoch;          // optional step counter of a fused collective, advanced by `epoch_add` by one thread of the launch
+  uint32_t epoch_add;       // (saves the one-thread launch that did nothing else)
 };
 
 // grid (K/256 rounded up, n), block 256: one 32-group per warp
 __global__ void __launch_bounds__(256) quant_rows_kernel(QuantArgs a) {
+  if (a.epoch && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *a.epoch += a.epoch_add;
   const int row = blockIdx.y;
   const int col = blockIdx.x * 256 + threadIdx.x;
   const int lane = threadIdx.x & 31;
@@ -54,6 +57,7 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(QuantArgs a) {
 // Bulk variant (many rows): a thread owns 8 consecutive columns (one 16-byte load, one 8-byte store), four lanes
 // share a 32-column scale group.  grid (ceil(K / 1024), n), block 128.
 __global__ void __launch_bounds__(128) quant_rows_vec_kernel(QuantArgs a) {
+  if (a.epoch && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *a.epoch += a.epoch_add;
   const int row = blockIdx.y;
   const int col = (blockIdx.x * 128 + threadIdx.x) * 8;
   const int KB = a.K / 32;
@@ -87,10 +91,25 @@ __global__ void __launch_bounds__(128) quant_rows_vec_kernel(QuantArgs a) {
 
 using namespace sfb;
 
+static int quant_rows_launch(const QuantArgs& a, cudaStream_t stream);
+
 extern "C" int sfb_quant_rows(const void* x, void* q, void* s, void* atom, int n, int K, int split, int split_off,
                               cudaStream_t stream) {
   if (K % 32) return (int)cudaErrorInvalidValue;
-  QuantArgs a{(const __nv_bfloat16*)x, (uint8_t*)q, (uint8_t*)s, (uint8_t*)atom, n, K, split, split_off};
+  QuantArgs a{(const __nv_bfloat16*)x, (uint8_t*)q, (uint8_t*)s, (uint8_t*)atom, n, K, split, split_off, nullptr, 0u};
+  return quant_rows_launch(a, stream);
+}
+
+// The same, and *epoch += epoch_add inside the launch (the fused collectives count their steps on the device).
+extern "C" int sfb_quant_rows_bump(const void* x, void* q, void* s, void* atom, int n, int K, void* epoch, uint32_t epoch_add,
+                                   cudaStream_t stream) {
+  if (K % 32 || !epoch) return (int)cudaErrorInvalidValue;
+  QuantArgs a{(const __nv_bfloat16*)x, (uint8_t*)q, (uint8_t*)s, (uint8_t*)atom, n, K, 0, 0, (uint32_t*)epoch, epoch_add};
+  return quant_rows_launch(a, stream);
+}
+
+static int quant_rows_launch(const QuantArgs& a, cudaStream_t stream) {
+  const int n = a.n, K = a.K, split = a.split;
   if (!split && n >= 32) {      // same arithmetic, wider accesses
     quant_rows_vec_kernel<<<dim3((K + 1023) / 1024, n), 128, 0, stream>>>(a);
     return SFB_CHECK_LAUNCH();

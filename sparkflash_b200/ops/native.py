@@ -350,6 +350,12 @@ def quant_rows(x, q, s, atom, n, K, split=False, split_off=0):
                                 c_int(split_off), _stream()), "quant_rows")
 
 
+def quant_rows_bump(x, q, s, atom, n, K, epoch, add: int = 1):
+    """quant_rows, and ``epoch += add`` inside the same launch (step counter of a fused collective)."""
+    _check(lib().sfb_quant_rows_bump(_p(x), _p(q), _p(s), _p(atom), c_int(n), c_int(K), _p(epoch), c_uint32(add), _stream()),
+           "quant_rows_bump")
+
+
 def umma_dense_pair(tmap_a, tmap_b, sfa, sfb, pair, N, K, *, groups=1, a_fp4=False, splits=1, scratch=None,
                     tickets=None, out_b=None, out_f=None, out_stride=None, status=None, NP=None, out_q=None,
                     out_q_atom=None):

@@ -77,8 +77,14 @@ class RowParallelLinear(_Base):
                  norm_w: torch.Tensor | None = None, eps: float = 1e-6, **kw):
         super().__init__(heap, M, **kw)
         self.N, self.Kl = w_q.shape
-        self.mode = mode
         W = self.world
+        # all-reduce of many rows: two shots - every row goes to one owner (reduce-scatter), the owner folds it and
+        # sends the folded row to everyone (all-gather): 2 (W - 1) / W of the data crosses the links instead of W - 1
+        self.two_shot = mode == "ar" and W > 1 and M >= self.TWO_SHOT_ROWS and M % W == 0
+        self.ar_rows = M
+        if self.two_shot:
+            mode = "rs"
+        self.mode = mode
         if mode == "rs" and M % W:
             raise ValueError("reduce-scatter needs M divisible by the world size")
         self.rows_out = M // W if mode == "rs" else M
@@ -96,9 +102,22 @@ class RowParallelLinear(_Base):
         self.off_flags = heap_offset + 2 * W * self.slot_bytes
         self.off_done = self.off_flags + 2 * 256
         self.bytes = self.off_done + 256 - heap_offset
+        if self.two_shot:      # | gathered rows [2][M, N] bf16 | gather flags [2][W] | done
+            self.off_gather = self.off_done + 256
+            self.off_gflags = self.off_gather + 2 * M * self.N * 2
+            self.off_gdone = self.off_gflags + 2 * 256
+            self.bytes = self.off_gdone + 256 - heap_offset
+            self.gflag_ptrs = [torch.tensor([heap.base + self.off_gflags + par * 256 + r * 4 for r in range(W) if r != self.rank],
+                                            dtype=torch.int64, device="cuda") for par in range(2)]
         tiles = ((self.N + 127) // 128) * ((M + self.NP - 1) // self.NP)
         ksteps = self.Kl // 128
-        self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles))) if M < 32 else 1     # measured: from 32 rows on, split-K only adds its reduce
+        # few rows: split K until every SM has a CTA or two; 32..128 rows: only while the tiles alone leave most SMs idle
+        if M < 32:
+            self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles)))
+        elif M <= 128:
+            self.splits = max(1, min(ksteps // 3, 148 // max(1, tiles)))
+        else:
+            self.splits = 1
         self.splits = int(os.environ.get("SFB_FUSED_SPLITS", self.splits))
         self.scratch = torch.zeros((tiles * self.splits * 128 * self.NP,), dtype=torch.float32, device="cuda") if self.splits > 1 else None
         self.tickets = torch.zeros((max(tiles, 1),), dtype=torch.int32, device="cuda")
@@ -106,10 +125,13 @@ class RowParallelLinear(_Base):
         self.out = torch.empty((self.rows_out, self.N), dtype=torch.bfloat16, device="cuda")
         self.out_sum = torch.empty_like(self.out)
 
-    @staticmethod
-    def heap_bytes(M: int, Nn: int, W: int, mode: str) -> int:
-        rows = M // W if mode == "rs" else M
-        return 2 * W * rows * Nn * 2 + 2 * 256 + 256
+    TWO_SHOT_ROWS = 512
+
+    @classmethod
+    def heap_bytes(cls, M: int, Nn: int, W: int, mode: str) -> int:
+        two = mode == "ar" and W > 1 and M >= cls.TWO_SHOT_ROWS and M % W == 0
+        rows = M // W if (mode == "rs" or two) else M
+        return 2 * W * rows * Nn * 2 + 2 * 256 + 256 + (2 * M * Nn * 2 + 2 * 256 + 256 if two else 0)
 
     def _slot(self, base: int, parity: int, r: int) -> int:
         return base + self.off_slots + (parity * self.world + r) * self.slot_bytes
@@ -121,8 +143,7 @@ class RowParallelLinear(_Base):
         """x bf16 [M, K/W]: quantise, multiply, push the partial to the consumers, raise the flags."""
         self.step += 1
         par = self.step & 1
-        self._bump()
-        N.quant_rows(x, self.x_q, None, self.x_atom, self.M, self.Kl)
+        N.quant_rows_bump(x, self.x_q, None, self.x_atom, self.M, self.Kl, self.epoch)      # quantise and count the step in one launch
         h = self.heap
         outs = [self._slot(b, par, self.rank) for b in h.bases]
         flags = [self._flag(b, par, self.rank) for b in h.bases]
@@ -133,16 +154,46 @@ class RowParallelLinear(_Base):
                                     c_int(self.splits), N._p(self.scratch), N._p(self.tickets), None, None, c_int64(self.N), None, c_int(0),
                                     None, c_int(0), c_int(self.rows_out if self.mode == "rs" else 0), N._p(self.status), N._stream()), "umma_bulk")
 
-    def consume(self, residual: torch.Tensor | None = None, out_q: torch.Tensor | None = None, out_atom: torch.Tensor | None = None) -> torch.Tensor:
+    def consume(self, residual: torch.Tensor | None = None, out_q: torch.Tensor | None = None, out_atom: torch.Tensor | None = None,
+                wait: bool = True) -> torch.Tensor:
         par = self.step & 1
         b = self.heap.base
         slots = [self._slot(b, par, r) for r in range(self.world)]
         flags = [self._flag(b, par, r) for r in range(self.world)]
+        out = self.out
+        if self.two_shot:
+            # fold this rank's rows straight into its part of the gathered buffer, send that part to every peer, wait for theirs
+            h, W, rows = self.heap, self.world, self.rows_out
+            g_off = self.off_gather + par * self.ar_rows * self.N * 2
+            own_off = g_off + self.rank * rows * self.N * 2
+            out = h.view(own_off, (rows, self.N), torch.bfloat16)
+            if residual is not None and residual.shape[0] == self.ar_rows:
+                residual = residual[self.rank * rows:(self.rank + 1) * rows]
         N._check(_L().sfb_fold_slots(N._ptr_array(slots), N._ptr_array(flags), c_int(self.world), c_int(self.rows_out), c_int(self.N),
                                      c_int64(self.N), N._p(self.epoch), c_uint32(0), c_uint64(self.wait_ns), N._p(residual), N._p(self.norm_w),
-                                     c_float(self.eps), N._p(self.out_sum), N._p(self.out), N._p(out_q), N._p(out_atom), N._p(self.status),
+                                     c_float(self.eps), N._p(self.out_sum), N._p(out), N._p(out_q), N._p(out_atom), N._p(self.status),
                                      N._stream()), "fold_slots")
-        return self.out
+        if not self.two_shot:
+            return self.out
+        self._gather_push(out, own_off, par)
+        return self.gathered() if wait else None
+
+    def _gather_push(self, out, own_off, par):
+        h, W, rows = self.heap, self.world, self.rows_out
+        peers = [r for r in range(W) if r != self.rank]
+        dst = [h.bases[r] + own_off for r in peers]
+        gfl = [h.bases[r] + self.off_gflags + par * 256 + self.rank * 4 for r in peers]
+        N._check(_L().sfb_push_rows(N._p(out), N._ptr_array(dst), N._ptr_array(gfl), c_int(len(peers)), c_int64(rows * self.N * 2),
+                                    N._p(self.epoch), c_uint32(0), c_void_p(h.base + self.off_gdone), N._stream()), "push_rows")
+
+    def gathered(self) -> torch.Tensor:
+        """Second half of the two-shot all-reduce: wait (bounded) for every peer's folded rows; returns all M rows.  Separate
+        from ``consume(wait=False)`` so that ranks emulated on one GPU can all push before anyone waits."""
+        par = self.step & 1
+        W = self.world
+        N._check(_L().sfb_wait_flags(N._p(self.gflag_ptrs[par]), c_int(W - 1), N._p(self.epoch), c_uint32(0), c_uint64(self.wait_ns),
+                                     N._p(self.status), N._stream()), "wait_flags")
+        return self.heap.view(self.off_gather + par * self.ar_rows * self.N * 2, (self.ar_rows, self.N), torch.bfloat16)
 
     def forward(self, x, residual=None):
         self.produce(x)
@@ -205,7 +256,12 @@ class ColumnParallelLinear(_Base):
             self.local_atom[-1].fill_(127)
         tiles = ((self.Nl + 127) // 128) * ((M + self.NP - 1) // self.NP)
         ksteps = self.K // 128
-        self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles))) if M < 32 else 1     # measured: from 32 rows on, split-K only adds its reduce
+        if M < 32:
+            self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles)))
+        elif M <= 128:
+            self.splits = max(1, min(ksteps // 3, 148 // max(1, tiles)))
+        else:
+            self.splits = 1
         self.scratch = torch.zeros((tiles * self.splits * 128 * self.NP,), dtype=torch.float32, device="cuda") if self.splits > 1 else None
         self.tickets = torch.zeros((max(tiles, 1),), dtype=torch.int32, device="cuda")
         self.out = torch.empty((M, self.Nl), dtype=torch.bfloat16, device="cuda")
@@ -224,8 +280,7 @@ class ColumnParallelLinear(_Base):
         rank it is there."""
         self.step += 1
         par = self.step & 1
-        self._bump()
-        N.quant_rows(x_shard, self.local_q[par], None, self.local_atom[par], self.M, self.Kl)
+        N.quant_rows_bump(x_shard, self.local_q[par], None, self.local_atom[par], self.M, self.Kl, self.epoch)
         h = self.heap
         flags = [b + self.off_flags + par * 256 + self.rank * 4 for b in h.bases]
         if self.mode == "gather":
@@ -290,7 +345,10 @@ def _demo(argv=None) -> None:
         for o in rows:
             o.produce(x)
         for o in rows:
-            o.consume()
+            o.consume(wait=False)
+        for o in rows:
+            if o.two_shot:
+                o.gathered()
         for o in cols:
             o.publish(x)
         for o in cols:

@@ -88,9 +88,12 @@ def main() -> None:
             z = y + res
             torch.nn.functional.rms_norm(z, (H,), eps=1e-6)
         base = timed(base_ar, a.iters)
-        link = M * H * 2 * (W - 1) / (a.link_gbs * 1e9) * 1e6
+        # bytes every rank must send: one shot = its whole partial to each peer; two shots (reduce-scatter + all-gather of the
+        # folded rows, the form used from RowParallelLinear.TWO_SHOT_ROWS rows on) = 2 (W - 1) / W of the partial
+        two = op.two_shot
+        link = M * H * 2 * ((2 * (W - 1) / W) if two else (W - 1)) / (a.link_gbs * 1e9) * 1e6
         rows.append({"op": "gemm_allreduce", "M": M, "fused_us": fused, "nccl_cublas_us": base, "roofline_us": max(t_compute, link),
-                     "frac_of_roofline": max(t_compute, link) / fused})
+                     "frac_of_roofline": max(t_compute, link) / fused, "form": "two_shot" if two else "one_shot"})
         del op; heap.close()
         # ---- GEMM -> reduce-scatter ----------------------------------------------------------------------------
         if M % W == 0:
@@ -136,7 +139,7 @@ def main() -> None:
     # twice that, and no FP8 rate was measured on this pool: a second fraction against 2 x the bf16 figure is printed too.
     for r in rows:
         t_c8 = 2.0 * r["M"] * H * H / W / (2 * a.peak_tflops * 1e12) * 1e6
-        link_us = {"gemm_allreduce": r["M"] * H * 2 * (W - 1), "gemm_reducescatter": r["M"] * H * 2 * (W - 1) / W,
+        link_us = {"gemm_allreduce": r["M"] * H * 2 * ((2 * (W - 1) / W) if r.get("form") == "two_shot" else (W - 1)), "gemm_reducescatter": r["M"] * H * 2 * (W - 1) / W,
                    "allgather_gemm": r["M"] * H * (W - 1) / W}[r["op"]] / (a.link_gbs * 1e9) * 1e6
         r["roofline_fp8peak_us"] = max(t_c8, link_us)
         r["frac_of_roofline_fp8peak"] = max(t_c8, link_us) / r["fused_us"]

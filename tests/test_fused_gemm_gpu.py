@@ -55,6 +55,39 @@ def test_row_parallel_gemm_then_reduce(M, mode):
             assert (out - wn).abs().max() < 0.03 * wn.abs().max() + 0.02
 
 
+def test_two_shot_all_reduce_of_many_rows():
+    """From 512 rows on the all-reduce runs as reduce-scatter + fold on the owner + all-gather of the folded rows; every rank
+    ends with all rows.  (Emulated ranks: all produce, all fold and push, then all wait.)"""
+    from sparkflash_b200.parallel.fused_gemm import RowParallelLinear
+    from sparkflash_b200.parallel.symm import SymmHeap
+    W, N, K, M = 2, 512, 1024, 640
+    Kl = K // W
+    heaps = SymmHeap.local_group(W, RowParallelLinear.heap_bytes(M, N, W, "ar"))
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    res = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    norm_w = (1 + 0.1 * torch.randn(N, generator=g)).cuda()
+    ops, ref = [], torch.zeros(M, N)
+    for r in range(W):
+        q, sf, wd = _weights(N, Kl, 20 + r)
+        ops.append(RowParallelLinear(heaps[r], q.cuda(), sf, M, "ar", norm_w=norm_w, eps=1e-6, wait_ns=200_000_000))
+        assert ops[-1].two_shot
+        ref += (_ref_act(x[:, r * Kl:(r + 1) * Kl]) @ wd.t()).to(torch.bfloat16).float()
+    want = ref + res.float()
+    want = want * torch.rsqrt(want.pow(2).mean(-1, keepdim=True) + 1e-6) * norm_w.cpu()
+    for step in range(3):
+        for r in range(W):
+            ops[r].produce(x[:, r * Kl:(r + 1) * Kl].cuda().contiguous())
+        for r in range(W):
+            ops[r].consume(res.cuda(), wait=False)
+        outs = [ops[r].gathered().float().cpu() for r in range(W)]
+        torch.cuda.synchronize()
+        for r in range(W):
+            ops[r].check()
+            assert (outs[r] - want).abs().max() < 0.03 * want.abs().max() + 0.02
+        assert torch.equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("mode", ["gather", "remote"])
 @pytest.mark.parametrize("M", [1, 16, 128, 384])
 def test_all_gather_then_column_parallel_gemm(M, mode):
