@@ -763,6 +763,189 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// ---- persistent many-row dense GEMM ---------------------------------------------------------------------------------
+// One CTA per SM walks over (weight tile, token tile) pairs.  The producer and the MMA thread run ahead into the next tile
+// while the four epilogue warps drain the previous accumulator (two accumulator sets in TMEM), so a tile's epilogue - TMEM ->
+// bf16 -> shared memory -> one 256-byte bulk copy per token row and destination, peer memory included - and the wait for
+// those copies hide behind the next main loop.  Same arithmetic and the same output bits as umma_gemm_kernel<128, true>.
+constexpr int PS_STAGES = 5;
+struct UmmaPersistSmem {
+  alignas(1024) uint8_t a[PS_STAGES][UM_A_BYTES];
+  alignas(1024) uint8_t b[PS_STAGES][128 * UM_BK];
+  alignas(1024) __nv_bfloat16 out[128 * 128];     // the tile on its way out, token-major
+  alignas(128) uint8_t sfa[PS_STAGES][512];
+  alignas(128) uint8_t sfb[PS_STAGES][512];
+  alignas(8) uint64_t full[PS_STAGES];
+  alignas(8) uint64_t empty[PS_STAGES];
+  alignas(8) uint64_t acc_full[2];
+  alignas(8) uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  volatile int fail;
+  volatile int ep_ok;
+};
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(UM_THREADS, 1)
+umma_bulk_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, UmmaArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  UmmaPersistSmem& S = *reinterpret_cast<UmmaPersistSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PS_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], 1); }
+    S.fail = 0;
+    S.ep_ok = 1;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, 512);
+    tmem_relinquish();
+  }
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_wait();
+  const int n_w = (a.N + 127) / 128, total = n_w * a.tok_tiles, ksteps = a.K / UM_BK;
+  const uint32_t tmem = S.tmem_base;
+  const uint32_t t_sfa = tmem + 256, t_sfb = tmem + 264;
+  constexpr uint32_t STAGE_TX = UM_A_BYTES + 128 * UM_BK + 1024;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
+        const int wt = t % n_w, tt = t / n_w;
+        const uint8_t* sfa = a.sfa + ((size_t)wt * a.katoms_a) * 512;
+        const uint8_t* sfb = a.sfb + ((size_t)tt * a.katoms_b) * 512;
+        for (int i = 0; i < ksteps; ++i, ++it) {
+          const int s = it % PS_STAGES;
+          if (it >= PS_STAGES && !mbar_wait(&S.empty[s], ((it / PS_STAGES) - 1) & 1)) { S.fail = 1; break; }
+          mbar_expect_tx(&S.full[s], STAGE_TX);
+          tma_load_2d(S.a[s], &tmapA, i * UM_BK, wt * 128, &S.full[s]);
+          tma_load_2d(S.b[s], &tmapB, i * UM_BK, tt * 128, &S.full[s]);
+          bulk_load(S.sfa[s], sfa + (size_t)i * 512, 512, &S.full[s]);
+          bulk_load(S.sfb[s], sfb + (size_t)i * 512, 512, &S.full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(0, 0, 128, 128);
+      uint32_t it = 0;
+      int lt = 0;
+      for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x, ++lt) {
+        const int buf = lt & 1;
+        // the accumulator set is free once the epilogue of the tile before last has read it
+        if (lt >= 2 && !mbar_wait(&S.acc_empty[buf], ((lt >> 1) - 1) & 1)) { S.fail = 3; break; }
+        tc_fence_after();
+        const uint32_t t_acc = tmem + (uint32_t)buf * 128;
+        bool ok = true;
+        for (int i = 0; i < ksteps; ++i, ++it) {
+          const int s = it % PS_STAGES;
+          if (!mbar_wait(&S.full[s], (it / PS_STAGES) & 1)) { S.fail = 2; ok = false; break; }
+          tc_fence_after();
+          const uint32_t sf_slot = (it & 1u) * 4;
+          tc_cp_sf(t_sfa + sf_slot, make_desc(smem_u32(S.sfa[s]), 128, 0, 0));
+          tc_cp_sf(t_sfb + sf_slot, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
+          const uint32_t a_addr = smem_u32(S.a[s]), b_addr = smem_u32(S.b[s]);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t id = idesc | ((uint32_t)kk << 29) | ((uint32_t)kk << 4);
+            tc_mma_bs(t_acc, make_desc(a_addr + kk * 32, 1024, 16, 2), make_desc(b_addr + kk * 32, 1024, 16, 2), id, t_sfa + sf_slot,
+                      t_sfb + sf_slot, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&S.empty[s]);
+        }
+        tc_commit(&S.acc_full[buf]);      // arrives even after a failed wait, so the epilogue never waits for its limit
+        if (!ok) break;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    bool pending = false;      // this thread has bulk copies of the previous tile in flight
+    int lt = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x, ++lt) {
+      const int buf = lt & 1, wt = t % n_w, tt = t / n_w;
+      // one warp waits for the accumulator and tells the others through the barrier, so that all four take the same path
+      if (warp == 2) {
+        bool got = true;
+        if (lane == 0) got = mbar_wait(&S.acc_full[buf], (lt >> 1) & 1) && !S.fail;
+        got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+        if (lane == 0 && !got) S.ep_ok = 0;
+      }
+      if (pending) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // the staging tile has been read out (the
+                                                                                      // plain loads of the peer stores are done when their loop ends)
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!S.ep_ok) break;
+      tc_fence_after();
+      const int nv = min(128, a.n - tt * 128);
+      const uint32_t t_acc = tmem + (uint32_t)buf * 128;
+#pragma unroll
+      for (int c0 = 0; c0 < 128; c0 += 16) {
+        uint32_t v[16];
+        tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (c0 + j < nv) S.out[(c0 + j) * 128 + q * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[j]));
+      }
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) mbar_arrive(&S.acc_empty[buf]);       // every warp's TMEM reads of this set are done
+      const int tok = q * 32 + lane;
+      pending = false;
+      if (a.out_b && tok < nv) {
+        bulk_store(a.out_b + (int64_t)(tt * 128 + tok) * a.out_stride + wt * 128, smem_u32(S.out + tok * 128), 256);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        pending = true;
+      }
+      if (a.n_peers > 0) {
+        // rows on their way to other GPUs go out as plain 16-byte stores, half a warp per 256-byte row segment (the form
+        // NVLink moves best; one small bulk copy per row reached a quarter of the link rate)
+        const int hw = lane >> 4, c8 = (lane & 15) * 8;
+#pragma unroll 4
+        for (int r0 = q * 32; r0 < q * 32 + 32; r0 += 2) {
+          const int r = r0 + hw;
+          if (r < nv) {
+            const uint4 v = *reinterpret_cast<const uint4*>(S.out + r * 128 + c8);
+            const int row = tt * 128 + r;
+            if (a.rs_rows > 0) {
+              const int pr = row / a.rs_rows;
+              *reinterpret_cast<uint4*>(a.peer_out[pr] + (int64_t)(row - pr * a.rs_rows) * a.out_stride + wt * 128 + c8) = v;
+            } else {
+              for (int pr = 0; pr < a.n_peers; ++pr)
+                *reinterpret_cast<uint4*>(a.peer_out[pr] + (int64_t)row * a.out_stride + wt * 128 + c8) = v;
+            }
+          }
+        }
+      }
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // every copy of this thread has been written
+    if (a.n_peers > 0) {
+      // this CTA's tiles are out: count the CTA; the last one raises this rank's arrival flag on every rank
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        const unsigned int prev = atomicAdd(a.done_counter, 1u);
+        if (prev == gridDim.x - 1) {
+          *a.done_counter = 0;
+          __threadfence_system();
+          const uint32_t ep = *a.epoch_ptr + a.epoch_add;
+          for (int pr = 0; pr < a.n_peers; ++pr) st_release_sys(a.peer_flag[pr], ep);
+        }
+      }
+    }
+    if ((S.fail || !S.ep_ok) && lane == 0 && q == 0) status_set(a.status, ST_TIMEOUT, 60 + S.fail, blockIdx.x, lt);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
 // ---- MoE gate/up: two weight tiles (w1, w3) against one token, clamp-SwiGLU x route weight, FP8 re-quant ------
 // grid: x = 128-column tile of the intermediate width, y = slot (top_k routed + shared), z = token
 // UM_STAGES = 6 fills one SM's shared memory with a single CTA (few CTAs: decode); 3 lets two CTAs share an SM, so that one's
@@ -1155,7 +1338,8 @@ struct GatherSpec {
 static thread_local GatherSpec g_gather;
 
 // Tuning switches for measurements (0 = the shipped choice): [1] stages of the 64-pair down projection (2 shipped; 3, 4),
-// [2] stages of the 64-pair gate/up (2 = two CTAs per SM; 3, 5 = one CTA per SM).
+// [2] stages of the 64-pair gate/up (2 = two CTAs per SM; 3, 5 = one CTA per SM), [3] / [4] segment-major grid order of the
+// grouped down / gate-up kernels, [5] persistent many-row dense kernel (1 = never, 2 = whenever the shape allows).
 static int g_tune[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 // Phase marks (um_mark) of the NEXT launch of a tensor-core GEMM of this library: cleared by that launch.
 static thread_local unsigned long long* g_marks = nullptr;
@@ -1285,6 +1469,23 @@ int sfb_umma_bulk(const void* tmapA, const void* tmapB, const void* sfa, int kat
   a.tok_tiles = tok_tiles; a.b_maps = (const CUtensorMap*)b_maps; a.b_k_per_map = b_k_per_map; a.rs_rows = rs_rows;
   for (int i = 0; i < n_maps && b_maps; ++i) a.sfb_maps[i] = (const uint8_t*)sfb_maps[i];
   const int tiles = (N + 127) / 128;
+  // many tiles of 128 x 128, one split, bf16 out (local and / or pushed): the persistent kernel, whose epilogues and copies
+  // run under the next tile's main loop.  g_tune[5]: 1 = never, 2 = whenever the shape allows
+  const bool can_persist = NP == 128 && splits == 1 && !b_maps && !out_f && (out_b || g_push.n > 0) && N % 128 == 0 &&
+                           (out_stride % 8) == 0 && K >= UM_BK;
+  // (one issuing thread per SM paces its main loop, so for long reductions two one-tile CTAs per SM stay faster: measured
+  // 1.23 vs 1.11 PFLOP/s at K = 1280 and 1.38 vs 1.57 at K = 2560; with a push the copies' latency decides)
+  if (can_persist && g_tune[5] != 1 && (g_tune[5] == 2 || (tiles * tok_tiles >= 296 && (K <= 1536 || g_push.n > 0)))) {
+    apply_push(a); apply_gather(a);
+    static int sms = 0;
+    if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+    const size_t smem = sizeof(UmmaPersistSmem) + 1024;
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(umma_bulk_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+    const int total = tiles * tok_tiles;
+    return (int)sfb_launch(umma_bulk_persistent_kernel, dim3(total < sms ? total : sms), dim3(UM_THREADS), smem, stream,
+                           *(const CUtensorMap*)tmapA, *(const CUtensorMap*)tmapB, a);
+  }
   // many token tiles and several splits: the add of the partials runs as its own grid (one CTA per tile adding every split
   // is latency-bound); not with an armed push, whose epilogue needs the finished tile
   a.defer_reduce = (splits > 1 && NP >= 32 && g_push.n == 0) ? 1 : 0;

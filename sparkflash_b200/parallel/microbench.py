@@ -50,7 +50,7 @@ def timed(fn, iters, warm=4):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--hidden", type=int, default=5120)
-    ap.add_argument("--m", default="1,8,64,512,8192")
+    ap.add_argument("--m", "--rows", dest="m", default="1,8,64,512,8192", help="row counts (use --rows under torch.distributed.run, which claims --m)")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--peak-tflops", type=float, default=1376.0)     # sustained cuBLAS bf16 of this pool
     ap.add_argument("--link-gbs", type=float, default=770.0)

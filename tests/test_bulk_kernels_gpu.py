@@ -347,3 +347,42 @@ def test_many_row_seam_matches_the_cluster_kernel_and_bf16_coefficients():
     N.seam_coef_finish(acc, hss, scale, base, out, n, hc, d, 20, 1e-20, 1e-6)
     torch.cuda.synchronize()
     assert torch.allclose(out.cpu(), ref.cpu(), rtol=2e-3, atol=2e-4), (out.cpu() - ref.cpu()).abs().max()
+
+
+@pytest.mark.parametrize("N_,K,n", [(512, 256, 300), (2048, 512, 1024), (4096, 256, 2500)])
+def test_persistent_bulk_gemm_gives_the_bits_of_the_tile_per_cta_kernel(N_, K, n):
+    """The persistent many-row kernel (one CTA per SM walking over tiles, epilogue under the next main loop) against the
+    one-tile-per-CTA kernel: same bf16 bits, and both within FP8 precision of the fp32 product.  The last shape gives
+    every CTA several tiles (both accumulator sets and every barrier phase are used) and a partial last token tile."""
+    from sparkflash_b200.ops import native as N
+    dev = "cuda"
+    g = torch.Generator().manual_seed(N_ + n)
+    w = torch.randn(N_, K, generator=g) * 0.05
+    x = torch.randn(n, K, generator=g)
+    q, s = C.weight_quant_fp8_block32(w)
+    wd = C.weight_dequant_fp8_block32(q, s)
+    sfa = C.scales_to_prepared(s, N_, 32).to(dev)
+    xq, xs = C.act_quant_fp8(x)
+    ref = C.act_dequant_fp8(xq, xs) @ wd.t()
+    rows = (n + 127) // 128 * 128
+    xpad = torch.zeros(rows, K, dtype=torch.uint8, device=dev)
+    xpad[:n] = xq.to(dev)
+    sfb = C.scales_to_prepared(xs, n, 1).to(dev)
+    qd = q.to(dev).contiguous()
+    ta = N.TensorMap(qd, N_, K, K, 128)
+    tb = N.TensorMap(xpad, rows, K, K, 128)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    outs = []
+    try:
+        for arm in (1, 2):            # 1: never persistent, 2: persistent whenever the shape allows
+            N.umma_tune(5, arm)
+            out = torch.zeros(n, N_, dtype=torch.bfloat16, device=dev)
+            for _ in range(2):
+                N.umma_bulk(ta, tb, sfa, sfb, n, N_, K, out_b=out, status=status)
+            torch.cuda.synchronize()
+            assert status.tolist()[0] == 0, status.tolist()
+            outs.append(out.float().cpu())
+    finally:
+        N.umma_tune(5, 0)
+    assert torch.equal(outs[0], outs[1])
+    assert (outs[1] - ref).abs().max() <= 1e-2 * ref.abs().max()
