@@ -1212,6 +1212,264 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// ---- persistent grouped gate/up for wide (64-pair) segments --------------------------------------------------------------
+// One CTA per SM walks over (column tile of the intermediate width, segment) pairs.  While the four epilogue warps turn one
+// tile's accumulators into FP8 activations (SwiGLU, routing weight, re-quantisation: 14 of a one-tile CTA's 48 us), the
+// producer and the two MMA-issuing threads are already in the next tile's main loop on the other accumulator set.  The
+// arithmetic, its order and the output bits are those of umma_gateup_kernel<2, 64>.
+constexpr int PG_STAGES = 5;
+constexpr int PG_NP = 64;
+struct UmmaGateupPersistSmem {
+  alignas(1024) uint8_t a[PG_STAGES][2][UM_A_BYTES];
+  alignas(1024) uint8_t b[PG_STAGES][PG_NP * UM_BK];
+  alignas(1024) uint8_t sq[PG_NP * 128];          // the tile's FP8 codes on their way out, pair-major
+  alignas(128) uint8_t ssf[512];                  // and its scale atom
+  alignas(128) uint8_t sfa[PG_STAGES][2][512];
+  alignas(128) uint8_t sfb[PG_STAGES][512];
+  alignas(8) uint64_t full[PG_STAGES];
+  alignas(8) uint64_t empty[PG_STAGES];
+  alignas(8) uint64_t sfready[PG_STAGES][2];      // the stage's scale factors are in TMEM (one barrier per accumulator)
+  alignas(8) uint64_t acc_full[2];
+  alignas(8) uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  volatile int fail;
+  volatile int ep_ok;
+};
+// warps: 0 TMA producer, 1 / 6 MMA issue (gate / up), 2..5 epilogue, 7 / 8 scale-factor copies (gate / up).  A thread issues
+// one tcgen05 operation per ~80 cycles; with the copies on their own threads an MMA thread issues five per k-step, not seven.
+constexpr int PG_THREADS = 288;
+
+__global__ void __launch_bounds__(PG_THREADS, 1)
+umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
+                              const __grid_constant__ CUtensorMap tmapB, UmmaArgs a, int n_tiles, int n_segs) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = UmmaGateupPersistSmem;
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int NP = PG_NP;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int il = a.inter;
+  const int nks = (a.d + UM_BK - 1) / UM_BK;
+  const int total = n_tiles * n_segs;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PG_STAGES; ++s) {
+      mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 2);
+      mbar_init(&S.sfready[s][0], 1); mbar_init(&S.sfready[s][1], 1);
+    }
+    for (int b = 0; b < 2; ++b) { mbar_init(&S.acc_full[b], 2); mbar_init(&S.acc_empty[b], 1); }
+    S.fail = 0;
+    S.ep_ok = 1;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, 512);
+    tmem_relinquish();
+  }
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_wait();
+  const uint32_t tmem = S.tmem_base;
+  // scale factors: one 4-column slot per stage and operand, so a slot is rewritten only after the MMAs of the stage's previous
+  // use are done (the producer refills the stage only then): gate weights 256.., gate's activation copy 276.., up 296.., 316..
+  const uint32_t t_sfg = tmem + 256, t_sfb = tmem + 276, t_sfu = tmem + 296, t_sfb2 = tmem + 316;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
+        const int tile = t % n_tiles, seg = t / n_tiles;
+        const int e = a.seg_expert[seg];
+        if (e == -1) continue;                                   // an unused segment: no role touches a barrier for it
+        const CUtensorMap* ma;
+        int a_fp4, row_g;
+        const uint8_t *sf_g, *sf_u;
+        if (e >= 0) {
+          ma = &tmapA; a_fp4 = a.a_fp4;
+          row_g = (e * 2) * il + tile * 128;
+          sf_g = a.sfa + ((size_t)(row_g >> 7) * a.katoms_a) * 512;
+          sf_u = a.sfa + ((size_t)((row_g + il) >> 7) * a.katoms_a) * 512;
+        } else {
+          ma = &tmapA2; a_fp4 = 0;
+          row_g = tile * 128;
+          sf_g = a.sfa2 + ((size_t)(row_g >> 7) * a.katoms_a) * 512;
+          sf_u = a.sfa2 + ((size_t)((row_g + il) >> 7) * a.katoms_a) * 512;
+        }
+        const int row_u = row_g + il;
+        const uint8_t* sfb = a.sfb + (size_t)seg * a.katoms_b * 512;
+        const uint32_t stage_tx = 2 * (a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 3 * 512;
+        for (int i = 0; i < nks; ++i, ++it) {
+          const int s = it % PG_STAGES;
+          if (it >= PG_STAGES && !mbar_wait(&S.empty[s], ((it / PG_STAGES) - 1) & 1)) { S.fail = 1; break; }
+          mbar_expect_tx(&S.full[s], stage_tx);
+          tma_load_2d(S.a[s][0], ma, i * UM_BK, row_g, &S.full[s]);
+          tma_load_2d(S.a[s][1], ma, i * UM_BK, row_u, &S.full[s]);
+          tma_load_2d(S.b[s], &tmapB, i * UM_BK, seg * NP, &S.full[s]);
+          bulk_load(S.sfa[s][0], sf_g + (size_t)i * 512, 512, &S.full[s]);
+          bulk_load(S.sfa[s][1], sf_u + (size_t)i * 512, 512, &S.full[s]);
+          bulk_load(S.sfb[s], sfb + (size_t)i * 512, 512, &S.full[s]);
+        }
+      }
+    }
+  } else if (warp == 1 || warp == 6) {
+    if (lane == 0) {
+      const int h = warp == 1 ? 0 : 1;           // 0: gate tile, 1: up tile
+      const uint32_t t_sa = h ? t_sfu : t_sfg, t_sb = h ? t_sfb2 : t_sfb;
+      uint32_t it = 0;
+      int lt = 0;
+      long long c_acc = 0, c_full = 0, c_all0 = SFB_MARKS_ON ? clock64() : 0;      // cycles waiting for a free accumulator set / for data
+      for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
+        const int seg = t / n_tiles;
+        const int e = a.seg_expert[seg];
+        if (e == -1) continue;
+        const uint32_t idesc = make_idesc((e >= 0 && a.a_fp4) ? 5 : 0, 0, 128, NP);
+        const int buf = lt & 1;
+        const long long w0 = SFB_MARKS_ON ? clock64() : 0;
+        if (lt >= 2 && !mbar_wait(&S.acc_empty[buf], ((lt >> 1) - 1) & 1)) { S.fail = 3; break; }
+        if (SFB_MARKS_ON) c_acc += clock64() - w0;
+        tc_fence_after();
+        const uint32_t t_d = tmem + (uint32_t)buf * 128 + (h ? NP : 0);
+        bool ok = true;
+        for (int i = 0; i < nks; ++i, ++it) {
+          const int s = it % PG_STAGES;
+          const long long w1 = SFB_MARKS_ON ? clock64() : 0;
+          if (!mbar_wait(&S.sfready[s][h], (it / PG_STAGES) & 1)) { S.fail = 2; ok = false; break; }
+          if (SFB_MARKS_ON) c_full += clock64() - w1;
+          tc_fence_after();
+          const uint32_t sl = (uint32_t)s * 4;
+          const uint32_t w_addr = smem_u32(S.a[s][h]), b_addr = smem_u32(S.b[s]);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t id = idesc | ((uint32_t)kk << 29) | ((uint32_t)kk << 4);
+            tc_mma_bs(t_d, make_desc(w_addr + kk * 32, 1024, 16, 2), make_desc(b_addr + kk * 32, 1024, 16, 2), id, t_sa + sl, t_sb + sl,
+                      (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&S.empty[s]);
+        }
+        tc_commit(&S.acc_full[buf]);
+        if (!ok) break;
+        ++lt;
+      }
+      if (SFB_MARKS_ON && a.marks && h == 0 && (int)blockIdx.x < a.marks_cap) {      // per CTA: tiles, total, waiting-for-set, waiting-for-data cycles
+        a.marks[(size_t)blockIdx.x * 16 + 0] = (unsigned long long)lt;
+        a.marks[(size_t)blockIdx.x * 16 + 1] = (unsigned long long)(clock64() - c_all0);
+        a.marks[(size_t)blockIdx.x * 16 + 2] = (unsigned long long)c_acc;
+        a.marks[(size_t)blockIdx.x * 16 + 3] = (unsigned long long)c_full;
+      }
+    }
+  } else if (warp == 7 || warp == 8) {
+    if (lane == 0) {
+      const int h = warp == 7 ? 0 : 1;
+      const uint32_t t_sa = h ? t_sfu : t_sfg, t_sb = h ? t_sfb2 : t_sfb;
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
+        if (a.seg_expert[t / n_tiles] == -1) continue;
+        bool ok = true;
+        for (int i = 0; i < nks; ++i, ++it) {
+          const int s = it % PG_STAGES;
+          if (!mbar_wait(&S.full[s], (it / PG_STAGES) & 1)) { S.fail = 4; ok = false; break; }
+          tc_fence_after();
+          tc_cp_sf(t_sa + (uint32_t)s * 4, make_desc(smem_u32(S.sfa[s][h]), 128, 0, 0));
+          tc_cp_sf(t_sb + (uint32_t)s * 4, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
+          tc_commit(&S.sfready[s][h]);
+        }
+        if (!ok) break;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int KBi = il / 32;
+    const float limit = a.limit;
+    bool pending = false;
+    int lt = 0;
+    long long c_wait = 0;                          // cycles the epilogue waited for an accumulator (marks builds)
+    const long long c_ep0 = SFB_MARKS_ON ? clock64() : 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x) {
+      const int tile = t % n_tiles, seg = t / n_tiles;
+      const int e = a.seg_expert[seg];
+      if (e == -1) continue;                       // CTA-uniform (every thread reads the same word)
+      const int ncol = a.seg_count[seg];
+      const int buf = lt & 1;
+      if (warp == 2) {
+        bool got = true;
+        const long long w2 = SFB_MARKS_ON ? clock64() : 0;
+        if (lane == 0) got = mbar_wait(&S.acc_full[buf], (lt >> 1) & 1) && !S.fail;
+        if (SFB_MARKS_ON && lane == 0) c_wait += clock64() - w2;
+        got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+        if (lane == 0 && !got) S.ep_ok = 0;
+      }
+      if (pending) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!S.ep_ok) break;
+      tc_fence_after();
+      reinterpret_cast<uint32_t*>(S.ssf)[q * 32 + lane] = 0x7f7f7f7fu;      // rows past the segment's pairs: scale 1
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const uint32_t t_g = tmem + (uint32_t)buf * 128, t_u = t_g + NP;
+      const int col = tile * 128 + q * 32 + lane;
+      const bool live = col < il;
+#pragma unroll 1
+      for (int c0 = 0; c0 < NP && c0 < ncol; c0 += 16) {
+        uint32_t vg[16], vu[16];
+        tc_ld16(t_g + ((uint32_t)(q * 32) << 16) + c0, vg);
+        tc_ld16(t_u + ((uint32_t)(q * 32) << 16) + c0, vu);
+        const int jx = c0 + (lane & 15);
+        const float wv = jx < ncol ? a.seg_weight[seg * NP + jx] : 0.f;
+        tc_wait_ld();
+        float act[16];
+        const int nb = ncol - c0;
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+          act[jj] = 0.f;
+          if (jj >= nb) continue;
+          const float wj = __shfl_sync(0xffffffffu, wv, jj);
+          if (live) {
+            const float g = fminf(bfr(__uint_as_float(vg[jj])), limit);
+            const float u = fminf(fmaxf(bfr(__uint_as_float(vu[jj])), -limit), limit);
+            act[jj] = bfr(g / (1.f + expf(-g)) * u * wj);
+          }
+        }
+        uint32_t amax_bits[16];
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+          amax_bits[jj] = 0u;
+          if (jj >= nb) continue;
+          const float ax = (act[jj] == act[jj]) ? fabsf(act[jj]) : 0.f;
+          amax_bits[jj] = __reduce_max_sync(0xffffffffu, __float_as_uint(ax));
+        }
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+          const int j = c0 + jj;
+          if (j < ncol) {                           // warp-uniform
+            const uint8_t sc = act_scale_code_fp8(__uint_as_float(amax_bits[jj]));
+            const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+            S.sq[j * 128 + q * 32 + lane] = enc_e4m3(act[jj] * inv);
+            if (lane == 0) S.ssf[(j & 31) * 16 + (j >> 5) * 4 + q] = sc;
+          }
+        }
+      }
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) mbar_arrive(&S.acc_empty[buf]);
+      const int j = q * 32 + lane;
+      pending = false;
+      if (j < ncol) { bulk_store(a.act_q + ((size_t)seg * NP + j) * il + tile * 128, smem_u32(S.sq + j * 128), 128); pending = true; }
+      if (j == 0) { bulk_store(a.act_sf + (size_t)seg * sf_bytes(NP, KBi) + (size_t)tile * 512, smem_u32(S.ssf), 512); pending = true; }
+      if (pending) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      ++lt;
+    }
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    if (SFB_MARKS_ON && a.marks && warp == 2 && lane == 0 && (int)blockIdx.x < a.marks_cap) {
+      a.marks[(size_t)blockIdx.x * 16 + 4] = (unsigned long long)(clock64() - c_ep0);
+      a.marks[(size_t)blockIdx.x * 16 + 5] = (unsigned long long)c_wait;
+    }
+    if ((S.fail || !S.ep_ok) && lane == 0 && q == 0) status_set(a.status, ST_TIMEOUT, 70 + S.fail, blockIdx.x, lt);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1339,7 +1597,7 @@ static thread_local GatherSpec g_gather;
 
 // Tuning switches for measurements (0 = the shipped choice): [1] stages of the 64-pair down projection (2 shipped; 3, 4),
 // [2] stages of the 64-pair gate/up (2 = two CTAs per SM; 3, 5 = one CTA per SM), [3] / [4] segment-major grid order of the
-// grouped down / gate-up kernels, [5] persistent many-row dense kernel (1 = never, 2 = whenever the shape allows).
+// grouped down / gate-up kernels, [5] persistent many-row dense kernel, [6] persistent 64-pair gate/up kernel (1 = never, 2 = whenever the shape allows).
 static int g_tune[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 // Phase marks (um_mark) of the NEXT launch of a tensor-core GEMM of this library: cleared by that launch.
 static thread_local unsigned long long* g_marks = nullptr;
@@ -1631,6 +1889,17 @@ int sfb_umma_gate_up_grouped(const void* tmapA, const void* tmapA2, const void* 
     if (!done) { cudaFuncSetAttribute(umma_gateup_kernel<5, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
     return (int)sfb_launch(umma_gateup_kernel<5, 64>, dim3(inter / 128, segments, 1), dim3(GU_THREADS), smem, stream, *mA, *mA2,
                            *(const CUtensorMap*)tmapB, a);
+  }
+  // many wide segments: the persistent kernel (g_tune[6]: 1 = never, 2 = whenever the shape allows)
+  if (seg_size == 64 && inter % 128 == 0 && act_sf && g_tune[6] != 1 && (g_tune[6] == 2 || (inter / 128) * segments >= 296)) {
+    static int sms = 0;
+    if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+    const size_t smem = sizeof(UmmaGateupPersistSmem) + 1024;
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(umma_gateup_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+    const int total = (inter / 128) * segments;
+    return (int)sfb_launch(umma_gateup_persistent_kernel, dim3(total < sms ? total : sms), dim3(PG_THREADS), smem, stream, *mA, *mA2,
+                           *(const CUtensorMap*)tmapB, a, inter / 128, segments);
   }
   if (seg_size == 64) {      // segments of up to 64 pairs: two 2-stage CTAs per SM (a stage holds 32 KiB of weights and 8 KiB of tokens)
     const size_t smem64 = sizeof(UmmaSmem<64, 2, 2>) + 1024;
