@@ -229,7 +229,8 @@ struct AttnTcSmem {
   float sbuf[NH][KT + 1];                         // scores of the tile, head-major
   float red[THREADS];                             // per (key part, head) partial max / sum
   float fac[NH];                                  // per-head rescale of the running accumulator; 1/denominator at the end
-  alignas(8) uint64_t bar;
+  alignas(8) uint64_t bar;                        // score MMAs done (two issuing threads)
+  alignas(8) uint64_t bar_pv;                     // value MMAs done (four issuing threads)
   uint32_t tmem_base;
 };
 
@@ -242,7 +243,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   extern __shared__ uint8_t smem_raw[];
   using Smem = AttnTcSmem<NH>;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  constexpr uint32_t TMEM_COLS = NH * 5 <= 128 ? 128 : 256;
+  // scores: two partial accumulators (latent dims 0..255 and 256..511, one issuing thread each, added when they are read);
+  // output: four 128-dim tiles (one issuing thread each).  A thread issues one tcgen05 operation per ~80 cycles whatever its
+  // size, and with 32-column MMAs that paced the tile.
+  constexpr uint32_t TMEM_COLS = NH * 6 <= 128 ? 128 : 256;
   constexpr int PARTS = THREADS / NH;      // key parts per head in the softmax
   constexpr int KPP = KT / PARTS;          // keys per part
   constexpr int CH = NH / 2;               // score columns per half
@@ -252,7 +256,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   const int hg = blockIdx.x, row = blockIdx.y;
 
   if (tid == 0) {
-    mbar_init(&S.bar, 1);
+    mbar_init(&S.bar, 2);
+    mbar_init(&S.bar_pv, 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -265,7 +270,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   tc_fence_after();
   pdl_wait();
   const uint32_t tmem = S.tmem_base;
-  const uint32_t t_s = tmem, t_o = tmem + NH;
+  const uint32_t t_s = tmem, t_o = tmem + 2 * NH;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
   const int pos = a.row_pos[row], L = a.row_lane[row];
@@ -363,21 +368,21 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     tc_fence_before();
     __syncthreads();
     // ---- S^T = K Q^T ----
-    if (tid == 0) {
+    if (lane == 0 && warp < 2) {      // warp 0: slabs 0..3 into S0, warp 1: slabs 4..7 into S1
       tc_fence_after();
       const uint32_t idesc = make_idesc(128, NH, 0);
       const uint32_t kvb = smem_u32(S.kv), qb = smem_u32(S.q);
+      const int s0 = warp * (SLABS / 2);
 #pragma unroll 1
-      for (int s = 0; s < SLABS; ++s) {
+      for (int s = s0; s < s0 + SLABS / 2; ++s) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          tc_mma_f16(t_s, make_desc(kvb + s * SLAB_BYTES + kk * 32, 1024, 16), make_desc(qb + s * (NH * 128) + kk * 32, 1024, 16), idesc,
-                     (s | kk) ? 1u : 0u);
+          tc_mma_f16(t_s + warp * NH, make_desc(kvb + s * SLAB_BYTES + kk * 32, 1024, 16), make_desc(qb + s * (NH * 128) + kk * 32, 1024, 16),
+                     idesc, ((s - s0) | kk) ? 1u : 0u);
       }
       tc_commit(&S.bar);
     }
     ok = mbar_wait(&S.bar, parity);
-    parity ^= 1;
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
     if (!ok) break;
     tc_fence_after();
@@ -385,17 +390,21 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     {
       const bool valid = tile * KT + key_slot < total;
       if constexpr (CH == 16) {
-        uint32_t v[16];
+        uint32_t v[16], v1[16];
         tc_ld16(t_s + lane_base + half * CH, v);
+        tc_ld16(t_s + NH + lane_base + half * CH, v1);
         tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) S.sbuf[half * CH + j][key_slot] = valid ? __uint_as_float(v[j]) * sl2 : -INFINITY;
+        for (int j = 0; j < 16; ++j)
+          S.sbuf[half * CH + j][key_slot] = valid ? (__uint_as_float(v[j]) + __uint_as_float(v1[j])) * sl2 : -INFINITY;
       } else {
-        uint32_t v[8];
+        uint32_t v[8], v1[8];
         tc_ld8(t_s + lane_base + half * CH, v);
+        tc_ld8(t_s + NH + lane_base + half * CH, v1);
         tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 8; ++j) S.sbuf[half * CH + j][key_slot] = valid ? __uint_as_float(v[j]) * sl2 : -INFINITY;
+        for (int j = 0; j < 8; ++j)
+          S.sbuf[half * CH + j][key_slot] = valid ? (__uint_as_float(v[j]) + __uint_as_float(v1[j])) * sl2 : -INFINITY;
       }
     }
     __syncthreads();
@@ -449,20 +458,18 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     tc_fence_before();
     __syncthreads();
     // ---- O^T += V^T P^T ----
-    if (tid == 0) {
+    if (lane == 0 && warp < 4) {      // warp j issues the 128-dim output tile j
       tc_fence_after();
       const uint32_t idesc = make_idesc(128, NH, 1);
       const uint32_t kvb = smem_u32(S.kv), pb = smem_u32(S.p);
-#pragma unroll 1
-      for (int j = 0; j < 4; ++j) {
+      const int j = warp;
 #pragma unroll
-        for (int t8 = 0; t8 < KT / 16; ++t8)
-          tc_mma_f16(t_o + j * NH, make_desc(kvb + (2 * j) * SLAB_BYTES + t8 * 2048, 1024, SLAB_BYTES),
-                     make_desc(pb + (t8 >> 2) * (NH * 128) + (t8 & 3) * 32, 1024, 16), idesc, (tile > 0 || t8 > 0) ? 1u : 0u);
-      }
-      tc_commit(&S.bar);
+      for (int t8 = 0; t8 < KT / 16; ++t8)
+        tc_mma_f16(t_o + j * NH, make_desc(kvb + (2 * j) * SLAB_BYTES + t8 * 2048, 1024, SLAB_BYTES),
+                   make_desc(pb + (t8 >> 2) * (NH * 128) + (t8 & 3) * 32, 1024, 16), idesc, (tile > 0 || t8 > 0) ? 1u : 0u);
+      tc_commit(&S.bar_pv);
     }
-    ok = mbar_wait(&S.bar, parity);
+    ok = mbar_wait(&S.bar_pv, parity);
     parity ^= 1;
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
     tc_fence_after();

@@ -261,6 +261,7 @@ struct UmmaSmem {
   alignas(128) uint8_t sfb[ST][512];
   alignas(8) uint64_t full[ST];
   alignas(8) uint64_t empty[ST];
+  alignas(8) uint64_t sfready[ST][2];     // gate/up kernel: the stage's scale factors are in TMEM (one barrier per accumulator)
   alignas(8) uint64_t acc_full;
   uint32_t tmem_base;
   int last_flag;
@@ -955,7 +956,7 @@ umma_bulk_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const __g
 // issues a tcgen05 operation about every 75 cycles whatever its size, and with 16-column tiles that - not the data - paced
 // the main loop; the two accumulators are independent, so each gets its own issuing thread (and its own copy of the
 // activation scales in TMEM, because copies and MMAs of different threads are not ordered against each other).
-constexpr int GU_THREADS = UM_THREADS + 32;
+constexpr int GU_THREADS = UM_THREADS + 96;      // + warp 6 (up MMAs), warps 7 / 8 (scale-factor copies for gate / up)
 template <int UM_STAGES, int NP = 16>
 __global__ void __launch_bounds__(GU_THREADS, UM_STAGES <= 3 ? 2 : 1)
 umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
@@ -967,11 +968,17 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   const int tile = a.swap_xy ? blockIdx.y : blockIdx.x, slot = a.swap_xy ? blockIdx.x : blockIdx.y, tok = blockIdx.z;
   const int il = a.inter;
   const int nks = (a.d + UM_BK - 1) / UM_BK;
-  constexpr uint32_t TMEM_COLS = 2 * NP + 32 <= 64 ? 64 : 256;
+  // accumulators 2 NP columns; scale factors one 4-column slot per stage and operand (gate weights, gate's copy of the
+  // activation scales, up weights, up's copy): a slot is rewritten only when its stage's previous MMAs are done
+  constexpr uint32_t TMEM_NEED = 2 * NP + 16 * UM_STAGES;
+  constexpr uint32_t TMEM_COLS = TMEM_NEED <= 64 ? 64 : (TMEM_NEED <= 128 ? 128 : 256);
 
   if (threadIdx.x == 0) {
     um_mark(a, 0);
-    for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 2); }   // both issuing threads free a stage
+    for (int s = 0; s < UM_STAGES; ++s) {      // both issuing threads free a stage
+      mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 2);
+      mbar_init(&S.sfready[s][0], 1); mbar_init(&S.sfready[s][1], 1);
+    }
     mbar_init(&S.acc_full, 2);
     S.fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1027,7 +1034,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   const uint32_t STAGE_TX = 2 * (a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 3 * 512;
   const uint32_t tmem = S.tmem_base;
   const uint32_t t_g = tmem, t_u = tmem + NP;
-  const uint32_t t_sfg = tmem + 2 * NP, t_sfu = tmem + 2 * NP + 8, t_sfb = tmem + 2 * NP + 16, t_sfb2 = tmem + 2 * NP + 24;
+  const uint32_t t_sfg = tmem + 2 * NP, t_sfb = t_sfg + 4 * UM_STAGES, t_sfu = t_sfb + 4 * UM_STAGES, t_sfb2 = t_sfu + 4 * UM_STAGES;
   const int nks_run = skip ? 0 : nks;
 
   if (warp == 0) {
@@ -1053,13 +1060,11 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
       for (int i = 0; i < nks_run; ++i) {
         const int s = i % UM_STAGES;
         const long long tw0 = (SFB_MARKS_ON && a.marks && i == 8 && h == 0) ? clock64() : 0;
-        if (!mbar_wait(&S.full[s], (i / UM_STAGES) & 1)) { S.fail = 2; break; }
+        if (!mbar_wait(&S.sfready[s][h], (i / UM_STAGES) & 1)) { S.fail = 2; break; }      // data landed and scales copied
         tc_fence_after();
         if (i == 0 && h == 0) um_mark(a, 3);
         const long long tw1 = (SFB_MARKS_ON && a.marks && i == 8 && h == 0) ? clock64() : 0;
-        const uint32_t sl = (uint32_t)(i & 1) * 4;
-        tc_cp_sf(t_sa + sl, make_desc(smem_u32(S.sfa[s][h]), 128, 0, 0));
-        tc_cp_sf(t_sb + sl, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
+        const uint32_t sl = (uint32_t)s * 4;
         const long long tw2 = (SFB_MARKS_ON && a.marks && i == 8 && h == 0) ? clock64() : 0;
         const uint32_t w_addr = smem_u32(S.a[s][h]), b_addr = smem_u32(S.b[s]);
 #pragma unroll
@@ -1082,6 +1087,19 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
       }
       tc_commit(&S.acc_full);     // arrives even after a failed wait so the epilogue never hangs
       if (h == 0) um_mark(a, 4);
+    }
+  } else if (warp == 7 || warp == 8) {
+    if (lane == 0) {      // scale-factor copies of one accumulator's operands, a thread of their own
+      const int h = warp == 7 ? 0 : 1;
+      const uint32_t t_sa = h ? t_sfu : t_sfg, t_sb = h ? t_sfb2 : t_sfb;
+      for (int i = 0; i < nks_run; ++i) {
+        const int s = i % UM_STAGES;
+        if (!mbar_wait(&S.full[s], (i / UM_STAGES) & 1)) { S.fail = 4; break; }
+        tc_fence_after();
+        tc_cp_sf(t_sa + (uint32_t)s * 4, make_desc(smem_u32(S.sfa[s][h]), 128, 0, 0));
+        tc_cp_sf(t_sb + (uint32_t)s * 4, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
+        tc_commit(&S.sfready[s][h]);
+      }
     }
   } else {
     const int q = warp & 3;
