@@ -276,7 +276,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   const int pos = a.row_pos[row], L = a.row_lane[row];
   const int r0 = HD - a.rd;
   // ---- queries of the group's heads: rope on the last rd dims, bf16, swizzled K-major ----
-#pragma unroll 2
+#pragma unroll 8      // NH * 64 / THREADS loads per thread, all in flight at once
   for (int idx = tid; idx < NH * 64; idx += THREADS) {
     const int hh = idx >> 6, c = idx & 63;          // head in group, 8-dim chunk
     const int ghead = hg * NH + hh;
@@ -309,6 +309,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   const uint32_t M60 = bf16x2_splat(1.152921504606847e18f);      // 2^60
   const uint32_t M100 = bf16x2_splat(1.2676506002282294e30f);    // 2^100
 
+  // the FP4 codes and scales of the NEXT tile's compressed entry are requested while the current tile is multiplied and
+  // normalised, so that the gather's trip to L2 / HBM is not on the tile's critical path
+  uint4 nraw[8], nsc4;
+  bool have_next = false;
 #pragma unroll 1
   for (int tile = 0; tile < tiles && ok; ++tile) {
     // ---- decode dims [256 half, +256) of key slot `key_slot` into the bf16 tile ----
@@ -338,13 +342,19 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
           }
         }
       } else if (e < total) {
-        const int id = a.sel[(size_t)row * a.K + (e - n_win)];
-        const uint8_t* kq = a.ckv_q + (size_t)L * a.ckv_lane_q + (size_t)id * (HD / 2) + half * 128;
-        const uint8_t* ks = a.ckv_s + (size_t)L * a.ckv_lane_s + (size_t)id * (HD / 16) + half * 16;
-        uint4 raw[8];
+        uint4 raw[8], sc4;
+        if (have_next) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) raw[i] = *reinterpret_cast<const uint4*>(kq + i * 16);
-        const uint4 sc4 = *reinterpret_cast<const uint4*>(ks);
+          for (int i = 0; i < 8; ++i) raw[i] = nraw[i];
+          sc4 = nsc4;
+        } else {
+          const int id = a.sel[(size_t)row * a.K + (e - n_win)];
+          const uint8_t* kq = a.ckv_q + (size_t)L * a.ckv_lane_q + (size_t)id * (HD / 2) + half * 128;
+          const uint8_t* ks = a.ckv_s + (size_t)L * a.ckv_lane_s + (size_t)id * (HD / 16) + half * 16;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) raw[i] = *reinterpret_cast<const uint4*>(kq + i * 16);
+          sc4 = *reinterpret_cast<const uint4*>(ks);
+        }
         const uint8_t* scb = reinterpret_cast<const uint8_t*>(&sc4);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {          // 32 codes per uint4, two E4M3 scales
@@ -362,6 +372,18 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll 4
         for (int c = half * 32; c < half * 32 + 32; ++c) *reinterpret_cast<uint4*>(rowp + (c >> 3) * SLAB_BYTES + swz(key_slot, c & 7)) = z;
+      }
+    }
+    {
+      const int en = (tile + 1) * KT + key_slot;      // this thread's entry of the next tile
+      have_next = en >= n_win && en < total;
+      if (have_next) {
+        const int id = a.sel[(size_t)row * a.K + (en - n_win)];
+        const uint8_t* kq = a.ckv_q + (size_t)L * a.ckv_lane_q + (size_t)id * (HD / 2) + half * 128;
+        const uint8_t* ks = a.ckv_s + (size_t)L * a.ckv_lane_s + (size_t)id * (HD / 16) + half * 16;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) nraw[i] = *reinterpret_cast<const uint4*>(kq + i * 16);
+        nsc4 = *reinterpret_cast<const uint4*>(ks);
       }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
