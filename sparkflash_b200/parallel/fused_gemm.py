@@ -253,7 +253,14 @@ class ColumnParallelLinear(_Base):
             self.local_atom[-1].fill_(127)
         tiles = ((self.Nl + 127) // 128) * ((M + self.NP - 1) // self.NP)
         ksteps = self.K // 128
-        self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles))) if M < 32 else 1
+        # few tiles and a long reduction: split K (this GEMM has no push, so from 32 rows on the partials are added by the
+        # separate reduce grid, which is cheap; the row-parallel operator's in-kernel reduce is not, see above)
+        if M < 32:
+            self.splits = max(1, min(ksteps // 4, 296 // max(1, tiles)))
+        elif M <= 128:
+            self.splits = max(1, min(ksteps // 4, 148 // max(1, tiles)))
+        else:
+            self.splits = 1
         self.scratch = torch.zeros((tiles * self.splits * 128 * self.NP,), dtype=torch.float32, device="cuda") if self.splits > 1 else None
         self.tickets = torch.zeros((max(tiles, 1),), dtype=torch.int32, device="cuda")
         self.out = torch.empty((M, self.Nl), dtype=torch.bfloat16, device="cuda")
