@@ -1,5 +1,5 @@
 """Command line: ``python -m sparkflash_b200 <models|doctor|trace|convert|pack-engram|serve|bench-serving|web|device-chain|
-inkling-tp4|plan|gates|served-gate>``.
+inkling-tp4|plan|roofline|gates|served-gate>``.
 Reference: crates/sparkflash-cli/src/main.rs:50-76 (subcommand table), convert.rs:76 (convert usage),
 serve.rs:6418-6590 (serve orchestration)."""
 from __future__ import annotations
@@ -154,6 +154,43 @@ def _plan(args) -> int:
     return 0
 
 
+def _roofline(args) -> int:
+    """Per-kernel-class roofline table of one rows step at the flagship's per-token shapes (utils/roofline.py)."""
+    import torch
+    from . import config as CF
+    from .models.deepseek_v41 import engine as E, prepare as P
+    from .utils import roofline as R
+    cfg = CF.reduced_config(args.experts, args.layers)
+    eng = E.Engine(P.prepare_synthetic(cfg, 0, 1), max_lanes=max(2, args.rows if args.decode else 2), max_context=args.context + 2 * args.rows + 64,
+                   max_rows=max(64, args.rows), arm="tc", synthetic_scales=True, use_graphs=False)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (args.context + 2 * args.rows,), generator=g).tolist()
+    n = args.rows
+    if args.decode:
+        for s_ in range(n):
+            eng.step(ids[:64], [s_] * 64, list(range(64)), head=False)
+        call = (ids[:n], list(range(n)), [64] * n)
+        eng.step(*call)
+        ctx = 64
+    else:
+        pos = 0
+        while pos < args.context:
+            c = min(n, args.context - pos)
+            eng.step(ids[pos:pos + c], [0] * c, list(range(pos, pos + c)), head=False)
+            pos += c
+        call = (ids[pos:pos + n], [0] * n, list(range(pos, pos + n)))
+        eng.step(*call, head=False)                  # warm every lazily built buffer of this shape
+        call = (ids[pos + n:pos + 2 * n], [0] * n, list(range(pos + n, pos + 2 * n)))
+        ctx = pos + n
+    timings = R.timed_step(eng, *call, **({} if args.decode else {"head": False}))
+    eng.check_status()
+    rows = R.account(timings, R.work_model(eng, n, ctx, head_rows=n if args.decode else 0))
+    print(R.format_table(rows))
+    print(json.dumps({"rows": n, "context": ctx, "layers": args.layers, "experts": args.experts, "launches": len(timings),
+                      "step_us": round(sum(t for _, t in timings), 1), "peaks": R.peaks()}))
+    return 0
+
+
 def _gates(args) -> int:
     import subprocess
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -209,6 +246,9 @@ def main(argv=None) -> int:
     ik.set_defaults(fn=_inkling_tp4)
     pl = sub.add_parser("plan"); pl.add_argument("--world", type=int, default=8); pl.add_argument("--moe-mode", default="tp", choices=["tp", "ep"])
     pl.set_defaults(fn=_plan)
+    rf = sub.add_parser("roofline"); rf.add_argument("--rows", type=int, default=1024); rf.add_argument("--context", type=int, default=4096)
+    rf.add_argument("--layers", type=int, default=3); rf.add_argument("--experts", type=int, default=128)
+    rf.add_argument("--decode", action="store_true", help="one row per sequence instead of a prompt chunk"); rf.set_defaults(fn=_roofline)
     gt = sub.add_parser("gates"); gt.add_argument("--skip-tests", action="store_true"); gt.set_defaults(fn=_gates)
     sg = sub.add_parser("served-gate"); sg.add_argument("--url", default="http://127.0.0.1:8000"); sg.add_argument("--tokens", type=int, default=48)
     sg.add_argument("--concurrency", type=int, default=4); sg.add_argument("--api-key"); sg.set_defaults(fn=_served_gate)

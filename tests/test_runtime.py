@@ -103,3 +103,22 @@ def test_kernel_marks_summary_separates_idle_ctas_and_old_launches():
     assert rep["setup_us"] == pytest.approx(0.25) and rep["mainloop_us"] == pytest.approx(8.0) and rep["first_stage_latency_us"] == pytest.approx(1.0)
     assert rep["epilogue_first_read_us"] == pytest.approx(0.1)
     assert summarize(torch.zeros(32, dtype=torch.int64)) == {"ctas": 0}
+
+
+def test_roofline_accounting_groups_launches_and_uses_the_measured_peaks(tmp_path):
+    from sparkflash_b200.utils import roofline as R
+    assert R.classify("umma_gate_up_grouped") == "moe_gate_up" and R.classify("umma_down_grouped") == "moe_down"
+    assert R.classify("umma_bulk") == "dense" and R.classify("attn_tc") == "attention" and R.classify("seam_fold") == "seams"
+    assert R.classify("index_scores_tc") == "indexer" and R.classify("something_else") == "rest"
+    (tmp_path / "MEASURED_PEAKS.json").write_text('{"hbm_gbs": 5000.0, "bf16_tflops": 1500.0, "bf16_tflops_sustained": 1000.0}')
+    pk = R.peaks(tmp_path)
+    assert pk == {"hbm_gbs": 5000.0, "bf16_tflops_sustained": 1000.0, "source": "measured"}
+    assert R.peaks(tmp_path / "nowhere")["source"] == "fallback"
+    work = {"moe_gate_up": R.ClassWork(bytes=1e9, flops=1e11), "dense": R.ClassWork(bytes=1e8, flops=4e11)}
+    rows = R.account([("umma_gate_up_grouped", 400.0), ("umma_bulk", 300.0), ("umma_bulk", 200.0), ("moe_plan", 30.0)], work, pk)
+    by = {r["class"]: r for r in rows}
+    assert by["moe_gate_up"]["roofline_us"] == 200.0 and by["moe_gate_up"]["bound"] == "memory" and by["moe_gate_up"]["fraction_of_measured"] == 0.5
+    assert by["dense"]["launches"] == 2 and by["dense"]["bound"] == "compute" and by["dense"]["fraction_of_measured"] == 0.8
+    assert by["moe_plan"]["fraction_of_measured"] is None
+    assert rows[0]["class"] == "dense"                       # sorted by measured time
+    assert "| class |" in R.format_table(rows)
