@@ -226,7 +226,7 @@ struct AttnTcSmem {
   alignas(1024) uint8_t kv[SLABS * SLAB_BYTES];   // 128 keys x 512 dims bf16, eight swizzled slabs
   alignas(1024) uint8_t q[SLABS * NH * 128];      // NH heads x 512 dims bf16
   alignas(1024) uint8_t p[2 * NH * 128];          // NH heads x 128 keys bf16 (two slabs of 64 keys)
-  float sbuf[NH][KT + 1];                         // scores of the tile, head-major
+  float sbuf[(NH < 32 ? NH : 32)][KT + 1];        // scores of the tile, head-major: 32 heads per softmax pass
   float red[THREADS];                             // per (key part, head) partial max / sum
   float fac[NH];                                  // per-head rescale of the running accumulator; 1/denominator at the end
   alignas(8) uint64_t bar;                        // score MMAs done (two issuing threads)
@@ -246,10 +246,14 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   // scores: two partial accumulators (latent dims 0..255 and 256..511, one issuing thread each, added when they are read);
   // output: four 128-dim tiles (one issuing thread each).  A thread issues one tcgen05 operation per ~80 cycles whatever its
   // size, and with 32-column MMAs that paced the tile.
-  constexpr uint32_t TMEM_COLS = NH * 6 <= 128 ? 128 : 256;
-  constexpr int PARTS = THREADS / NH;      // key parts per head in the softmax
+  constexpr uint32_t TMEM_COLS = NH * 6 <= 128 ? 128 : (NH * 6 <= 256 ? 256 : 512);
+  // the softmax runs over SH heads at a time (all of them up to 32; two passes for a 64-head group, which halves the
+  // conversions of the key tiles per row against two 32-head CTAs)
+  constexpr int SH = NH < 32 ? NH : 32;
+  constexpr int NPASS = NH / SH;
+  constexpr int PARTS = THREADS / SH;      // key parts per head in the softmax
   constexpr int KPP = KT / PARTS;          // keys per part
-  constexpr int CH = NH / 2;               // score columns per half
+  constexpr int CH = SH / 2;               // score columns per half and pass
   constexpr float LOG2E = 1.4426950408889634f;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int half = tid >> 7, key_slot = tid & 127;
@@ -301,8 +305,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   const int n_sel = a.ckv_q ? a.sel_count[row] : 0;
   const int total = n_win + n_sel;
   const int tiles = (total + KT - 1) / KT;
-  const int my_head = tid % NH, my_part = tid / NH;
-  float m_run = -1e30f, l_run = 0.f;       // identical in every thread that shares my_head
+  const int my_head = tid % SH, my_part = tid / SH;
+  float m_run[NPASS], l_run[NPASS];        // identical in every thread that shares my_head
+#pragma unroll
+  for (int ps = 0; ps < NPASS; ++ps) { m_run[ps] = -1e30f; l_run[ps] = 0.f; }
   uint32_t parity = 0;
   bool ok = true;
   const float sl2 = a.scale * LOG2E;
@@ -408,57 +414,62 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
     if (!ok) break;
     tc_fence_after();
-    // ---- scores: TMEM (lane = key) -> shared memory, head-major; each half takes half of the head columns ----
-    {
-      const bool valid = tile * KT + key_slot < total;
-      if constexpr (CH == 16) {
-        uint32_t v[16], v1[16];
-        tc_ld16(t_s + lane_base + half * CH, v);
-        tc_ld16(t_s + NH + lane_base + half * CH, v1);
-        tc_wait_ld();
+    // ---- scores: TMEM (lane = key) -> shared memory, head-major; each half takes half of the pass's head columns ----
+#pragma unroll 1
+    for (int ps = 0; ps < NPASS; ++ps) {
+      {
+        const bool valid = tile * KT + key_slot < total;
+        if constexpr (CH == 16) {
+          uint32_t v[16], v1[16];
+          tc_ld16(t_s + lane_base + ps * SH + half * CH, v);
+          tc_ld16(t_s + NH + lane_base + ps * SH + half * CH, v1);
+          tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          S.sbuf[half * CH + j][key_slot] = valid ? (__uint_as_float(v[j]) + __uint_as_float(v1[j])) * sl2 : -INFINITY;
-      } else {
-        uint32_t v[8], v1[8];
-        tc_ld8(t_s + lane_base + half * CH, v);
-        tc_ld8(t_s + NH + lane_base + half * CH, v1);
-        tc_wait_ld();
+          for (int j = 0; j < 16; ++j)
+            S.sbuf[half * CH + j][key_slot] = valid ? (__uint_as_float(v[j]) + __uint_as_float(v1[j])) * sl2 : -INFINITY;
+        } else {
+          uint32_t v[8], v1[8];
+          tc_ld8(t_s + lane_base + ps * SH + half * CH, v);
+          tc_ld8(t_s + NH + lane_base + ps * SH + half * CH, v1);
+          tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          S.sbuf[half * CH + j][key_slot] = valid ? (__uint_as_float(v[j]) + __uint_as_float(v1[j])) * sl2 : -INFINITY;
+          for (int j = 0; j < 8; ++j)
+            S.sbuf[half * CH + j][key_slot] = valid ? (__uint_as_float(v[j]) + __uint_as_float(v1[j])) * sl2 : -INFINITY;
+        }
       }
+      __syncthreads();
+      // ---- online softmax: thread = (head of the pass, key part) ----
+      float mloc = -INFINITY;
+      const float* srow = &S.sbuf[my_head][my_part * KPP];
+#pragma unroll
+      for (int i = 0; i < KPP; ++i) mloc = fmaxf(mloc, srow[i]);
+      S.red[my_part * SH + my_head] = mloc;
+      __syncthreads();
+      float m_new = m_run[ps];
+#pragma unroll
+      for (int pp = 0; pp < PARTS; ++pp) m_new = fmaxf(m_new, S.red[pp * SH + my_head]);
+      const float corr = exp2f(m_run[ps] - m_new);
+      __syncthreads();                 // everyone has read the maxima before the sums overwrite them
+      float lsum = 0.f;
+      const int gh = ps * SH + my_head;            // head inside the CTA's group
+#pragma unroll
+      for (int i = 0; i < KPP; i += 2) {
+        const float p0 = exp2f(srow[i] - m_new), p1 = exp2f(srow[i + 1] - m_new);
+        const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+        lsum += __bfloat162float(pb.x) + __bfloat162float(pb.y);      // the denominator sums what the value contraction multiplies
+        const int key = my_part * KPP + i;
+        *reinterpret_cast<__nv_bfloat162*>(S.p + (key >> 6) * (NH * 128) + swz(gh, (key & 63) >> 3) + (key & 7) * 2) = pb;
+      }
+      S.red[my_part * SH + my_head] = lsum;
+      if (my_part == 0) S.fac[gh] = corr;
+      __syncthreads();
+      float lt = 0.f;
+#pragma unroll
+      for (int pp = 0; pp < PARTS; ++pp) lt += S.red[pp * SH + my_head];
+      l_run[ps] = l_run[ps] * corr + lt;
+      m_run[ps] = m_new;
+      if (NPASS > 1) __syncthreads();    // the next pass overwrites sbuf and red
     }
-    __syncthreads();
-    // ---- online softmax: thread = (head, key part) ----
-    float mloc = -INFINITY;
-    const float* srow = &S.sbuf[my_head][my_part * KPP];
-#pragma unroll
-    for (int i = 0; i < KPP; ++i) mloc = fmaxf(mloc, srow[i]);
-    S.red[my_part * NH + my_head] = mloc;
-    __syncthreads();
-    float m_new = m_run;
-#pragma unroll
-    for (int pp = 0; pp < PARTS; ++pp) m_new = fmaxf(m_new, S.red[pp * NH + my_head]);
-    const float corr = exp2f(m_run - m_new);
-    __syncthreads();                 // everyone has read the maxima before the sums overwrite them
-    float lsum = 0.f;
-#pragma unroll
-    for (int i = 0; i < KPP; i += 2) {
-      const float p0 = exp2f(srow[i] - m_new), p1 = exp2f(srow[i + 1] - m_new);
-      const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-      lsum += __bfloat162float(pb.x) + __bfloat162float(pb.y);      // the denominator sums what the value contraction multiplies
-      const int key = my_part * KPP + i;
-      *reinterpret_cast<__nv_bfloat162*>(S.p + (key >> 6) * (NH * 128) + swz(my_head, (key & 63) >> 3) + (key & 7) * 2) = pb;
-    }
-    S.red[my_part * NH + my_head] = lsum;
-    if (my_part == 0) S.fac[my_head] = corr;
-    __syncthreads();
-    float lt = 0.f;
-#pragma unroll
-    for (int pp = 0; pp < PARTS; ++pp) lt += S.red[pp * NH + my_head];
-    l_run = l_run * corr + lt;
-    m_run = m_new;
     // ---- rescale the running O^T (lane = dim, column = head): half h owns the 128-dim tiles 2h and 2h + 1 ----
     if (tile > 0) {
 #pragma unroll 1
@@ -500,9 +511,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   // ---- epilogue: O^T / denominator (sink in the denominator only), inverse rope, bf16 (+ two-term FP8 copy) ----
   if (ok) {
     if (my_part == 0) {
-      const int ghead = hg * NH + my_head;
-      const float sk = ghead < a.heads ? a.sink[ghead] : 0.f;
-      S.fac[my_head] = 1.f / (l_run + exp2f(sk * LOG2E - m_run));
+#pragma unroll
+      for (int ps = 0; ps < NPASS; ++ps) {
+        const int ghead = hg * NH + ps * SH + my_head;
+        const float sk = ghead < a.heads ? a.sink[ghead] : 0.f;
+        S.fac[ps * SH + my_head] = 1.f / (l_run[ps] + exp2f(sk * LOG2E - m_run[ps]));
+      }
     }
     __syncthreads();
     const size_t Wd = (size_t)a.heads * HD;
@@ -518,8 +532,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     __nv_bfloat16* st_o = reinterpret_cast<__nv_bfloat16*>(S.kv);
     uint8_t* st_hi = S.kv + NH * HD * 2;
     uint8_t* st_lo = st_hi + NH * HD;
-    uint8_t* st_sh = st_lo + NH * HD;          // [NH * 16] scale codes of the hi term
-    uint8_t* st_sl = st_sh + NH * (HD / 32);   // and of the lo term
+    // scale codes of the hi term [NH * 16] and of the lo term: in the query buffer, which nothing reads any more (for a
+    // 64-head group the three staged outputs fill the KV buffer exactly)
+    uint8_t* st_sh = S.q;
+    uint8_t* st_sl = st_sh + NH * (HD / 32);
 #pragma unroll 1
     for (int jj = 0; jj < 2; ++jj) {
       const int j = half * 2 + jj;
@@ -604,7 +620,7 @@ using namespace sfb;
 extern "C" {
 
 // Same arguments as sfb_attn_rows_range plus the layout of the two-term copy (pair_block) and the status word.
-// hd must be 512; rd a multiple of 32.  Heads are processed in groups of 32 (16 when the rank holds at most 16).
+// hd must be 512; rd a multiple of 32.  Heads are processed in groups of 64 (16 or 32 when the rank holds at most that many).
 int sfb_attn_tc(const void* q, int64_t q_stride, const void* rope, int rope_stride, const int* row_lane, const int* row_pos,
                 const void* win_q, const void* win_s, int64_t win_lane_q, int64_t win_lane_s, const void* ckv_q, const void* ckv_s,
                 int64_t ckv_lane_q, int64_t ckv_lane_s, const int* sel, const int* sel_count, int K, const float* sink, void* out,
@@ -625,11 +641,16 @@ int sfb_attn_tc(const void* q, int64_t q_stride, const void* rope, int rope_stri
     static bool done = false;
     if (!done) { cudaFuncSetAttribute(attn_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
     rc = sfb_launch(attn_tc_kernel<16>, dim3(1, n), dim3(atc::THREADS), smem, stream, a);
-  } else {
+  } else if (heads <= 32) {
     const size_t smem = sizeof(AttnTcSmem<32>) + 1024;
     static bool done = false;
     if (!done) { cudaFuncSetAttribute(attn_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
-    rc = sfb_launch(attn_tc_kernel<32>, dim3((heads + 31) / 32, n), dim3(atc::THREADS), smem, stream, a);
+    rc = sfb_launch(attn_tc_kernel<32>, dim3(1, n), dim3(atc::THREADS), smem, stream, a);
+  } else {       // 64 heads per CTA: a row's key tiles are converted once for all of them
+    const size_t smem = sizeof(AttnTcSmem<64>) + 1024;
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(attn_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+    rc = sfb_launch(attn_tc_kernel<64>, dim3((heads + 63) / 64, n), dim3(atc::THREADS), smem, stream, a);
   }
   return (int)rc;
 }
