@@ -291,6 +291,22 @@ class Engine:
         st = self.status.tolist()
         if st[0] != 0:
             raise RuntimeError(f"device status code={st[0]} where={st[1]} detail=({st[2]}, {st[3]})")
+        arena = self.__dict__.get("guard_arena")
+        if arena is not None:
+            bad = arena.check()
+            if bad:
+                raise RuntimeError("guard bands overwritten: " + "; ".join(bad[:4]))
+
+    @classmethod
+    def with_guards(cls, *args, **kw) -> "Engine":
+        """An engine whose device buffers sit between guard bands (utils/canary.py); ``check_status`` then also reports any
+        buffer a kernel wrote past.  Buffers created on first use are guarded when the step runs inside
+        ``engine.guard_arena.active()``.  ``SFB_DEBUG_BOUNDS=1`` selects this in the serving launcher."""
+        from ...utils import canary
+        with canary.guarded() as arena:
+            eng = cls(*args, **kw)
+        eng.guard_arena = arena
+        return eng
 
     # ---- sublayers -------------------------------------------------------------------------------------
     def _engram_apply(self, n: int, j: int) -> None:

@@ -42,7 +42,8 @@ def build_engine(args, settings, rank: int, world: int):
             synthetic = True
     comm = PC.make_comm(settings.parallel.collective, rank, world) if world > 1 else None
     ec = settings.engine
-    eng = E.Engine(w, max_lanes=ec.max_lanes, max_context=min(ec.max_context, 1 << 16) if args.synthetic else ec.max_context,
+    make = E.Engine.with_guards if os.environ.get("SFB_DEBUG_BOUNDS") == "1" else E.Engine
+    eng = make(w, max_lanes=ec.max_lanes, max_context=min(ec.max_context, 1 << 16) if args.synthetic else ec.max_context,
                    max_rows=ec.max_rows, comm=comm, use_graphs=ec.cuda_graphs, arm="tc", synthetic_scales=synthetic, constrained=True,
                    drafter=ec.speculation and bool(w.mtp_layers) and settings.parallel.moe_mode == "tp",
                    lane_budget_bytes=getattr(args, "lane_budget_gb", 0) * (1 << 30) or None)

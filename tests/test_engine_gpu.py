@@ -586,3 +586,47 @@ def test_wide_moe_segments_and_the_persistent_kernels_give_the_bits_of_16_pair_s
         N.umma_tune(6, 0)
     assert torch.equal(outs[0], outs[1])
     assert torch.equal(outs[1], outs[2])
+
+
+def test_guard_bands_stay_intact_over_decode_and_chunk_steps_and_report_a_changed_band(tiny):
+    """Every device buffer of a guarded engine sits between two 256-byte bands of a fixed pattern: steps of every kind leave
+    them intact (no kernel writes outside its buffers), and a band changed from the host is reported with the allocation's
+    source line."""
+    from sparkflash_b200.models.deepseek_v41 import engine as E
+    cfg, ck, w, orc, dw = tiny
+    prompt = _prompt(cfg, 150, seed=5)
+    plain = E.Engine(dw, max_lanes=2, max_context=256, max_rows=128, arm="tc", use_graphs=False, keep_logits=True)
+    eng = E.Engine.with_guards(dw, max_lanes=2, max_context=256, max_rows=128, arm="tc", use_graphs=False, keep_logits=True)
+    assert len(eng.guard_arena.records) > 20
+    with eng.guard_arena.active():
+        for e in (plain, eng):
+            e.step(prompt[:128], [0] * 128, list(range(128)))
+            e.step(prompt[128:140], [0] * 12, list(range(128, 140)))
+            e.step(prompt[140:145], [1] * 5, list(range(5)))
+            e.step(prompt[145:146], [0], [140])
+    eng.check_status()
+    assert torch.equal(plain.logits[:1], eng.logits[:1])              # the bands change nothing in the results
+    rec = eng.guard_arena.records[3]
+    rec.raw[-1] = 0
+    with pytest.raises(RuntimeError, match="written after its bounds"):
+        eng.check_status()
+    rec.raw[-1] = 0xA5
+    rec.raw[0] = 1
+    assert "before" in eng.guard_arena.check()[0] and ".py:" in eng.guard_arena.check()[0]
+
+
+def test_guard_bands_stay_intact_over_a_many_row_step_at_full_per_token_shapes():
+    """The many-row path (tcgen05 attention with its staged epilogue, persistent GEMMs, 64-pair expert segments, bulk stores)
+    under guard bands: a 600-row chunk whose last token tile is partial, then a decode step on the cache it filled."""
+    from sparkflash_b200.config import reduced_config
+    from sparkflash_b200.models.deepseek_v41 import engine as E, prepare as P
+    cfg = reduced_config(8, 3)
+    eng = E.Engine.with_guards(P.prepare_synthetic(cfg, 0, 1), max_lanes=2, max_context=2048, max_rows=640, arm="tc", synthetic_scales=True,
+                               use_graphs=False)
+    ids = torch.randint(0, cfg.vocab_size, (1300,), generator=torch.Generator().manual_seed(9)).tolist()
+    with eng.guard_arena.active():
+        eng.step(ids[:600], [0] * 600, list(range(600)), head="last")
+        eng.step(ids[600:1200], [0] * 600, list(range(600, 1200)), head="last")
+        tok = eng.step(ids[1200:1201], [0], [1200])
+    eng.check_status()
+    assert 0 <= int(tok[0]) < cfg.vocab_size and len(eng.guard_arena.records) > 40

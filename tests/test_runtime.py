@@ -122,3 +122,16 @@ def test_roofline_accounting_groups_launches_and_uses_the_measured_peaks(tmp_pat
     assert by["moe_plan"]["fraction_of_measured"] is None
     assert rows[0]["class"] == "dense"                       # sorted by measured time
     assert "| class |" in R.format_table(rows)
+
+
+def test_guard_arena_leaves_host_allocations_alone_and_restores_torch():
+    import torch
+    from sparkflash_b200.utils import canary
+    z, e = torch.zeros, torch.empty
+    with canary.guarded() as arena:
+        t = torch.zeros(4, 3)                       # a host tensor: not guarded
+        assert t.shape == (4, 3) and not arena.records
+        with arena.active():                        # nesting keeps the outer patch
+            assert torch.zeros is not z
+        assert torch.zeros is not z
+    assert torch.zeros is z and torch.empty is e
