@@ -207,3 +207,26 @@ def test_two_rank_server_answers_a_chat_request(tmp_path):
             os.killpg(proc.pid, signal.SIGKILL)
             proc.wait()
         log.close()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_token_sharded_expert_parallel_layer_on_real_ranks_matches_one_rank_bit_for_bit(tmp_path, world):
+    """The all-to-all dispatch, the experts on the received rows, the combine and the fold over one process per GPU: every
+    rank's output equals, bit for bit, what one rank holding every expert computes for the same tokens."""
+    if _gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=repo + os.pathsep + os.environ.get("PYTHONPATH", ""), NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr", "127.0.0.1",
+           "--master-port", str(29560 + world), "-m", "sparkflash_b200.parallel.ep_bench", "--tokens", "1,5", "--experts", "16",
+           "--hidden", "512", "--inter", "256", "--top-k", "3", "--iters", "4", "--check"]
+    proc = subprocess.Popen(cmd, env=env, cwd=repo, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, start_new_session=True)
+    try:
+        stdout, stderr = proc.communicate(timeout=240)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)
+        stdout, stderr = proc.communicate()
+        pytest.fail(f"{world}-rank expert-parallel run timed out\n" + stdout[-2000:] + stderr[-2000:])
+    assert proc.returncode == 0, stdout[-3000:] + stderr[-3000:]
+    recs = [json.loads(l) for l in stdout.splitlines() if l.startswith("{")]
+    assert len(recs) == 2 and all(r["matches_single_rank_bits"] is True and r["world"] == world for r in recs), recs
