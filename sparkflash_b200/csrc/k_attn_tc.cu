@@ -415,6 +415,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     if (!ok) break;
     tc_fence_after();
     // ---- scores: TMEM (lane = key) -> shared memory, head-major; each half takes half of the pass's head columns ----
+    int any_rescale = 0;
 #pragma unroll 1
     for (int ps = 0; ps < NPASS; ++ps) {
       {
@@ -448,7 +449,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
       float m_new = m_run[ps];
 #pragma unroll
       for (int pp = 0; pp < PARTS; ++pp) m_new = fmaxf(m_new, S.red[pp * SH + my_head]);
+      // the reference exponent moves only when the maximum grew by more than 2^8: probabilities up to 256 are as exact in
+      // bf16 as probabilities up to 1, numerator and denominator use the same reference, and the running output then
+      // rarely needs rescaling (a read-modify-write of the whole TMEM accumulator per tile)
+      if (m_new - m_run[ps] <= 8.f) m_new = m_run[ps];
       const float corr = exp2f(m_run[ps] - m_new);
+      if (corr != 1.f) any_rescale = 1;
       __syncthreads();                 // everyone has read the maxima before the sums overwrite them
       float lsum = 0.f;
       const int gh = ps * SH + my_head;            // head inside the CTA's group
@@ -471,7 +477,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
       if (NPASS > 1) __syncthreads();    // the next pass overwrites sbuf and red
     }
     // ---- rescale the running O^T (lane = dim, column = head): half h owns the 128-dim tiles 2h and 2h + 1 ----
-    if (tile > 0) {
+    any_rescale = __syncthreads_or(any_rescale);      // CTA-uniform: did any head's reference exponent move?
+    if (tile > 0 && any_rescale) {
 #pragma unroll 1
       for (int jj = 0; jj < 2; ++jj) {
         const int j = half * 2 + jj;
