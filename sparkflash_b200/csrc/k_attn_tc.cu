@@ -22,6 +22,7 @@
 // kernels/flash_mla_csa2_common_sm121.cuh; docs/architecture/01-csa2-attention.md:98-104,212-229.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "k_common.cuh"
 
@@ -159,6 +160,8 @@ struct AttnTcArgs {
   const int* win_lo;        // optional explicit inclusive window range per row
   const int* win_hi;
   Status* status;
+  unsigned long long* marks;  // optional phase marks (builds with -DSFB_KERNEL_MARKS): sixteen %globaltimer words per CTA
+  int marks_cap;
 };
 
 }  // namespace sfb
@@ -166,6 +169,21 @@ struct AttnTcArgs {
 namespace sfb {
 
 using namespace atc;
+
+// slots: 0 entry, 1 set-up done, 2 queries staged, 3 first tile decoded, 4 its scores done, 5 its softmax done, 6 its value
+// MMAs done, 7 exit, 8 epilogue starts (last tile done), 9 outputs staged, 10 copies issued
+#ifdef SFB_KERNEL_MARKS
+#define SFB_ATTN_MARKS_ON 1
+__device__ __forceinline__ void at_mark(const AttnTcArgs& a, int slot) {
+  if (a.marks && threadIdx.x == 0) {
+    const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+    if (cta < a.marks_cap) a.marks[(size_t)cta * 16 + slot] = globaltimer_ns();
+  }
+}
+#else
+#define SFB_ATTN_MARKS_ON 0
+__device__ __forceinline__ void at_mark(const AttnTcArgs&, int) {}
+#endif
 
 // ---- cache codes -> bf16 by bit placement ----------------------------------------------------------------------
 // An E4M3 byte shifted into a bf16 (sign to bit 15, the seven exponent|mantissa bits to bits 4..10) is the code's value
@@ -210,6 +228,9 @@ __device__ __forceinline__ uint4 fp4x8_to_bf16(uint32_t w, uint32_t m1, uint32_t
     r[i] = bf16x2_mul(bf16x2_mul(raw, m1), m2);
   }
   return make_uint4(r[0], r[1], r[2], r[3]);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t* v) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -259,6 +280,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   const int half = tid >> 7, key_slot = tid & 127;
   const int hg = blockIdx.x, row = blockIdx.y;
 
+  at_mark(a, 0);
   if (tid == 0) {
     mbar_init(&S.bar, 2);
     mbar_init(&S.bar_pv, 4);
@@ -273,33 +295,25 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   __syncthreads();
   tc_fence_after();
   pdl_wait();
+  at_mark(a, 1);
   const uint32_t tmem = S.tmem_base;
   const uint32_t t_s = tmem, t_o = tmem + 2 * NH;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
   const int pos = a.row_pos[row], L = a.row_lane[row];
   const int r0 = HD - a.rd;
-  // ---- queries of the group's heads: rope on the last rd dims, bf16, swizzled K-major ----
-#pragma unroll 8      // NH * 64 / THREADS loads per thread, all in flight at once
+  // ---- queries of the group's heads: asynchronous 16-byte copies into the swizzled K-major tile; they land while the
+  // first key tile is decoded, and the rope of the last rd dims is applied in place after that ----
   for (int idx = tid; idx < NH * 64; idx += THREADS) {
     const int hh = idx >> 6, c = idx & 63;          // head in group, 8-dim chunk
     const int ghead = hg * NH + hh;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (ghead < a.heads) {
-      v = *reinterpret_cast<const uint4*>(a.q + (size_t)row * a.q_stride + (size_t)ghead * HD + c * 8);
-      if (c * 8 >= r0) {
-        __nv_bfloat162* pr = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 c2 = a.rope[(size_t)row * a.rope_stride + ((c * 8 - r0) >> 1) + j];
-          const float x = __bfloat162float(pr[j].x), y = __bfloat162float(pr[j].y);
-          pr[j] = __floats2bfloat162_rn(x * c2.x - y * c2.y, x * c2.y + y * c2.x);
-        }
-      }
-    }
-    *reinterpret_cast<uint4*>(S.q + (c >> 3) * (NH * 128) + swz(hh, c & 7)) = v;
+    uint8_t* dst = S.q + (c >> 3) * (NH * 128) + swz(hh, c & 7);
+    if (ghead < a.heads) cp_async16(smem_u32(dst), a.q + (size_t)row * a.q_stride + (size_t)ghead * HD + c * 8);
+    else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
   }
+  asm volatile("cp.async.commit_group;" ::: "memory");
 
+  at_mark(a, 2);
   const int w_first = a.win_lo ? a.win_lo[row] : (pos - a.window + 1 > 0 ? pos - a.window + 1 : 0);
   const int n_win = (a.win_hi ? a.win_hi[row] : pos) - w_first + 1;
   const int n_sel = a.ckv_q ? a.sel_count[row] : 0;
@@ -392,9 +406,30 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
         nsc4 = *reinterpret_cast<const uint4*>(ks);
       }
     }
+    if (tile == 0) {
+      // the queries have landed: rope on dims [r0, 512) of every head, in place (one 8-dim chunk per thread and turn)
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncthreads();
+      const int rc = a.rd >> 3;                     // roped chunks per head
+      for (int idx = tid; idx < NH * rc; idx += THREADS) {
+        const int hh = idx / rc, c = (r0 >> 3) + idx % rc;
+        if (hg * NH + hh >= a.heads) continue;
+        uint4* qp = reinterpret_cast<uint4*>(S.q + (c >> 3) * (NH * 128) + swz(hh, c & 7));
+        uint4 v = *qp;
+        __nv_bfloat162* pr = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 c2 = a.rope[(size_t)row * a.rope_stride + ((c * 8 - r0) >> 1) + j];
+          const float x = __bfloat162float(pr[j].x), y = __bfloat162float(pr[j].y);
+          pr[j] = __floats2bfloat162_rn(x * c2.x - y * c2.y, x * c2.y + y * c2.x);
+        }
+        *qp = v;
+      }
+    }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
     __syncthreads();
+    if (tile == 0) at_mark(a, 3);
     // ---- S^T = K Q^T ----
     if (lane == 0 && warp < 2) {      // warp 0: slabs 0..3 into S0, warp 1: slabs 4..7 into S1
       tc_fence_after();
@@ -414,6 +449,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
     if (!ok) break;
     tc_fence_after();
+    if (tile == 0) at_mark(a, 4);
     // ---- scores: TMEM (lane = key) -> shared memory, head-major; each half takes half of the pass's head columns ----
     int any_rescale = 0;
 #pragma unroll 1
@@ -478,6 +514,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     }
     // ---- rescale the running O^T (lane = dim, column = head): half h owns the 128-dim tiles 2h and 2h + 1 ----
     any_rescale = __syncthreads_or(any_rescale);      // CTA-uniform: did any head's reference exponent move?
+    if (tile == 0) at_mark(a, 5);
     if (tile > 0 && any_rescale) {
 #pragma unroll 1
       for (int jj = 0; jj < 2; ++jj) {
@@ -513,7 +550,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     parity ^= 1;
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
     tc_fence_after();
+    if (tile == 0) at_mark(a, 6);
   }
+  at_mark(a, 8);
 
   // ---- epilogue: O^T / denominator (sink in the denominator only), inverse rope, bf16 (+ two-term FP8 copy) ----
   if (ok) {
@@ -543,6 +582,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     // 64-head group the three staged outputs fill the KV buffer exactly)
     uint8_t* st_sh = S.q;
     uint8_t* st_sl = st_sh + NH * (HD / 32);
+    // pass 1: TMEM (lane = dim, column = head) -> bf16 [head][dim] in shared memory
 #pragma unroll 1
     for (int jj = 0; jj < 2; ++jj) {
       const int j = half * 2 + jj;
@@ -555,41 +595,63 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
         uint32_t v[16];
         tc_ld16(t_o + lane_base + j * NH + c0, v);
         tc_wait_ld();
-        float o[16];
+        if (roped) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          o[i] = bfr(__uint_as_float(v[i]) * S.fac[c0 + i]);
-          if (roped) {        // pairs (2p, 2p+1) sit in neighbouring lanes
-            const float other = __shfl_xor_sync(0xffffffffu, o[i], 1);
-            o[i] = (lane & 1) ? bfr(-other * c2.y + o[i] * c2.x) : bfr(o[i] * c2.x + other * c2.y);
+          for (int i = 0; i < 16; ++i) {        // pairs (2p, 2p+1) sit in neighbouring lanes
+            const float o = bfr(__uint_as_float(v[i]) * S.fac[c0 + i]);
+            const float other = __shfl_xor_sync(0xffffffffu, o, 1);
+            st_o[(c0 + i) * HD + dim] = __float2bfloat16_rn((lane & 1) ? -other * c2.y + o * c2.x : o * c2.x + other * c2.y);
           }
-          st_o[(c0 + i) * HD + dim] = __float2bfloat16_rn(o[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) st_o[(c0 + i) * HD + dim] = __float2bfloat16_rn(__uint_as_float(v[i]) * S.fac[c0 + i]);
         }
-        if (a.out_q) {
-          uint32_t amax_bits[16];
+      }
+    }
+    // pass 2: the two-term FP8 copy from the staged bf16 rows, sixteen consecutive dims of one head per thread and turn
+    // (two neighbouring lanes share a 32-dim scale block), packed conversions, 16-byte stores.  (Quantising straight
+    // from the TMEM layout - one dim per lane, one warp reduction per head - took 55 % of the CTA's life.)
+    if (a.out_q) {
+      __syncthreads();
+      for (int sgm = tid; sgm < NH * 32; sgm += THREADS) {
+        const int hh = sgm >> 5, seg = sgm & 31;
+        const uint4* src = reinterpret_cast<const uint4*>(st_o + hh * HD + seg * 16);
+        const uint4 a0 = src[0], a1 = src[1];
+        const uint32_t w[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        float o[16];
+        float amax = 0.f;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float ax = (o[i] == o[i]) ? fabsf(o[i]) : 0.f;        // a NaN lane counts as 0, as under fmaxf
-            amax_bits[i] = __reduce_max_sync(0xffffffffu, __float_as_uint(ax));
-          }
+        for (int k = 0; k < 8; ++k) {
+          o[2 * k] = __uint_as_float(w[k] << 16);
+          o[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+          amax = fmaxf(amax, fmaxf(fabsf(o[2 * k]), fabsf(o[2 * k + 1])));      // fmaxf drops a NaN operand: it counts as 0
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        const uint8_t sc = act_scale_code_fp8(amax);
+        const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+        uint32_t hw[4], lw[4];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const uint8_t sc = act_scale_code_fp8(__uint_as_float(amax_bits[i]));
-            const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
-            const uint8_t hi = enc_e4m3(o[i] * inv);
-            const uint8_t lo = enc_e4m3((o[i] * inv - e4m3_to_f32(hi)) * 16.f);
-            st_hi[(c0 + i) * HD + dim] = hi;
-            st_lo[(c0 + i) * HD + dim] = lo;
-            if (lane == 0) {
-              st_sh[(c0 + i) * (HD / 32) + (dim >> 5)] = sc;
-              st_sl[(c0 + i) * (HD / 32) + (dim >> 5)] = sc >= 4 ? (uint8_t)(sc - 4) : (uint8_t)0;
-            }
-          }
+        for (int k = 0; k < 8; ++k) {
+          const float x0 = o[2 * k] * inv, x1 = o[2 * k + 1] * inv;
+          const uint16_t h2 = enc_e4m3x2(x0, x1);
+          uint32_t hf;
+          asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hf) : "h"(h2));
+          const float2 dq = __half22float2(*reinterpret_cast<const __half2*>(&hf));
+          const uint16_t l2 = enc_e4m3x2((x0 - dq.x) * 16.f, (x1 - dq.y) * 16.f);
+          if (k & 1) { hw[k >> 1] |= (uint32_t)h2 << 16; lw[k >> 1] |= (uint32_t)l2 << 16; }
+          else { hw[k >> 1] = h2; lw[k >> 1] = l2; }
+        }
+        *reinterpret_cast<uint4*>(st_hi + hh * HD + seg * 16) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        *reinterpret_cast<uint4*>(st_lo + hh * HD + seg * 16) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+        if (!(tid & 1)) {
+          st_sh[hh * (HD / 32) + (seg >> 1)] = sc;
+          st_sl[hh * (HD / 32) + (seg >> 1)] = sc >= 4 ? (uint8_t)(sc - 4) : (uint8_t)0;
         }
       }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
+    at_mark(a, 9);
     const int head0 = hg * NH;
     const int nvalid = a.heads - head0 < NH ? a.heads - head0 : NH;        // heads of this group that exist
     if (nvalid > 0) {
@@ -615,8 +677,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
   } else if (tid == 0) {
     status_set(a.status, ST_TIMEOUT, 50, blockIdx.x, blockIdx.y);
   }
+  at_mark(a, 10);
   tc_fence_before();
   __syncthreads();
+  at_mark(a, 7);
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
@@ -625,6 +689,15 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
 using namespace sfb;
 
 extern "C" {
+
+// Phase marks of the NEXT sfb_attn_tc launch of this thread (measurement builds only).
+static thread_local unsigned long long* g_attn_marks = nullptr;
+static thread_local int g_attn_marks_cap = 0;
+int sfb_attn_set_marks(void* buf, int cap_ctas) {
+  if (buf && !SFB_ATTN_MARKS_ON) return (int)cudaErrorNotSupported;
+  g_attn_marks = (unsigned long long*)buf; g_attn_marks_cap = buf ? cap_ctas : 0;
+  return 0;
+}
 
 // Same arguments as sfb_attn_rows_range plus the layout of the two-term copy (pair_block) and the status word.
 // hd must be 512; rd a multiple of 32.  Heads are processed in groups of 64 (16 or 32 when the rank holds at most that many).
@@ -642,6 +715,8 @@ int sfb_attn_tc(const void* q, int64_t q_stride, const void* rope, int rope_stri
   a.out = (__nv_bfloat16*)out; a.out_q = (uint8_t*)out_q; a.out_atom = (uint8_t*)out_atom; a.pair_block = pair_block;
   a.n = n; a.heads = heads; a.rd = rd; a.window = window; a.ring = ring; a.scale = scale; a.win_lo = win_lo; a.win_hi = win_hi;
   a.status = (Status*)status;
+  a.marks = g_attn_marks; a.marks_cap = g_attn_marks_cap;
+  g_attn_marks = nullptr; g_attn_marks_cap = 0;
   cudaError_t rc;
   if (heads <= 16) {
     const size_t smem = sizeof(AttnTcSmem<16>) + 1024;

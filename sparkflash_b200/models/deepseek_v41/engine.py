@@ -557,6 +557,7 @@ class Engine:
             # many rows: attention on tcgen05 (a tolerance arm: the probabilities enter the value contraction as bf16), its
             # two-term FP8 copy in blocks of 64 hi | 64 lo rows, and one launch each for the two output projections
             tcb = self.tcb
+            self._arm_marks("attn")
             N.attn_tc(self.qfull, self.qfull.stride(0), invf, self.row_lane, self.row_pos, kv.win_q[l], kv.win_s[l],
                       kv.ckv_q[owner] if has_c else None, kv.ckv_s[owner] if has_c else None,
                       self.sel if has_c else None, self.sel_cnt if has_c else None, cfg.index_topk, L.sink,
@@ -679,7 +680,7 @@ class Engine:
         words per CTA): entry, set-up, first load, first stage landed, last MMA, accumulator complete, epilogue done, exit."""
         buf = self.__dict__.get("kernel_marks", {}).get(name)
         if buf is not None:
-            N.umma_set_marks(buf)
+            (N.attn_set_marks if name == "attn" else N.umma_set_marks)(buf)
 
     def _ffn_grouped(self, n: int, T, k: int, shared_here: bool) -> None:
         """Routed + shared experts for n rows with each expert's weights read once per segment of pairs (csrc/k_moe.cu moe_plan).

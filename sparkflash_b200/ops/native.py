@@ -436,6 +436,13 @@ def umma_set_marks(buf, ctas: int | None = None) -> None:
         _check(lib().sfb_umma_set_marks(_p(buf), c_int(buf.numel() // 16 if ctas is None else ctas)), "umma_set_marks")
 
 
+def attn_set_marks(buf) -> None:
+    """Arm phase marks for the next ``attn_tc`` launch (int64 device tensor, sixteen words per CTA; measurement builds)."""
+    if buf is not None and not lib().sfb_umma_has_marks():
+        raise RuntimeError("this library was built without in-kernel marks: rebuild with SFB_KERNEL_MARKS=1 SFB_REBUILD=1")
+    _check(lib().sfb_attn_set_marks(_p(buf), c_int(0 if buf is None else buf.numel() // 16)), "attn_set_marks")
+
+
 def umma_bf16(tmap_a, tmap_b, n, N, K, *, splits=1, scratch=None, tickets=None, out_b=None, out_f=None, out_stride=None,
               status=None, NP=None):
     """out[token, col] = sum_k W[col, k] X[token, k] with bf16 operands on tcgen05 kind::f16 (fp32 accumulate)."""
