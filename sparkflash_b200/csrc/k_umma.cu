@@ -95,6 +95,13 @@ __device__ __forceinline__ void tmem_relinquish() {
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
+// One lane of a converged warp.  Unlike a test of the lane index, the election tells the compiler that exactly one thread
+// runs the guarded code, so the operands of the TMA / tcgen05 instructions in it can stay in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
@@ -1488,6 +1495,224 @@ umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const _
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
+// ---- persistent grouped down projection for wide (64-pair) segments ---------------------------------------------------------
+// One CTA per SM walks over (column tile of the model width, segment) pairs with seven operand stages in flight; the
+// epilogue of one tile (TMEM -> fp32 tile in shared memory -> one 512-byte bulk copy per pair row) runs under the next
+// tile's main loop on the other accumulator set.  One-tile CTAs spent a third of their life outside the main loop and, at
+// three per SM with two stages each, kept too few bytes in flight for the weight stream.  The scale-factor copies have
+// their own issuing thread (a thread issues one tcgen05 operation per ~80 cycles, and seven per k-step would pace the
+// loop).  Arithmetic, order and output bits are those of umma_gemm_kernel<64, false, 2> in UM_DOWN_GROUPED mode.
+constexpr int PD_STAGES = 7;
+constexpr int PD_NP = 64;
+constexpr int PD_THREADS = 224;      // warps: 0 TMA producer, 1 MMA issue, 2..5 epilogue, 6 scale-factor copies
+struct UmmaDownPersistSmem {
+  alignas(1024) uint8_t a[PD_STAGES][UM_A_BYTES];
+  alignas(1024) uint8_t b[PD_STAGES][PD_NP * UM_BK];
+  alignas(1024) float outf[PD_NP * 128];           // the tile on its way out, pair-major
+  alignas(128) uint8_t sfa[PD_STAGES][512];
+  alignas(128) uint8_t sfb[PD_STAGES][512];
+  alignas(8) uint64_t full[PD_STAGES];
+  alignas(8) uint64_t empty[PD_STAGES];
+  alignas(8) uint64_t sfready[PD_STAGES];
+  alignas(8) uint64_t acc_full[2];
+  alignas(8) uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  volatile int fail;
+  volatile int ep_ok;
+};
+
+__global__ void __launch_bounds__(PD_THREADS, 1)
+umma_down_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
+                            const __grid_constant__ CUtensorMap tmapB, UmmaArgs a, int n_tiles, int n_segs) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = UmmaDownPersistSmem;
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int NP = PD_NP;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nks = (a.inter + UM_BK - 1) / UM_BK;
+  const int total = n_tiles * n_segs;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PD_STAGES; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); mbar_init(&S.sfready[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], 1); }
+    S.fail = 0;
+    S.ep_ok = 1;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, 256);
+    tmem_relinquish();
+  }
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_wait();
+  const uint32_t tmem = S.tmem_base;
+  // accumulator sets at columns 0 and 64; one 4-column scale-factor slot per stage and operand (a slot is rewritten only
+  // after the MMAs of the stage's previous use are done, because the producer refills the stage only then)
+  const uint32_t t_sfa = tmem + 128, t_sfb = tmem + 160;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      uint32_t it = 0;
+      long long c_empty = 0;                                     // cycles the producer waited for a free stage (marks builds)
+      const long long c_p0 = SFB_MARKS_ON ? clock64() : 0;
+      for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
+        const int tile = t % n_tiles, seg = t / n_tiles;
+        const int e = a.seg_expert[seg];
+        if (e == -1) continue;                                   // an unused segment: no role touches a barrier for it
+        const CUtensorMap* ma;
+        int a_fp4, row0;
+        const uint8_t* sfa;
+        if (e >= 0) {
+          ma = &tmapA; a_fp4 = a.a_fp4;
+          row0 = e * a.d + tile * 128;
+          sfa = a.sfa + ((size_t)(row0 >> 7) * a.katoms_a) * 512;
+        } else {
+          ma = &tmapA2; a_fp4 = 0;
+          row0 = tile * 128;
+          sfa = a.sfa2 + ((size_t)tile * a.katoms_a) * 512;
+        }
+        const uint8_t* sfb = a.sfb + (size_t)seg * a.katoms_b * 512;
+        const uint32_t stage_tx = (a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 1024;
+        for (int i = 0; i < nks; ++i, ++it) {
+          const int s = it % PD_STAGES;
+          const long long w0 = SFB_MARKS_ON ? clock64() : 0;
+          if (it >= PD_STAGES && !mbar_wait(&S.empty[s], ((it / PD_STAGES) - 1) & 1)) { S.fail = 1; break; }
+          if (SFB_MARKS_ON) c_empty += clock64() - w0;
+          mbar_expect_tx(&S.full[s], stage_tx);
+          tma_load_2d(S.a[s], ma, i * UM_BK, row0, &S.full[s]);
+          tma_load_2d(S.b[s], &tmapB, i * UM_BK, seg * NP, &S.full[s]);
+          bulk_load(S.sfa[s], sfa + (size_t)i * 512, 512, &S.full[s]);
+          bulk_load(S.sfb[s], sfb + (size_t)i * 512, 512, &S.full[s]);
+        }
+      }
+      if (SFB_MARKS_ON && a.marks && (int)blockIdx.x < a.marks_cap) {      // per CTA: k-steps, producer cycles, of which waiting
+        a.marks[(size_t)blockIdx.x * 16 + 6] = (unsigned long long)it;
+        a.marks[(size_t)blockIdx.x * 16 + 7] = (unsigned long long)(clock64() - c_p0);
+        a.marks[(size_t)blockIdx.x * 16 + 8] = (unsigned long long)c_empty;
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      uint32_t it = 0;
+      int lt = 0;
+      long long c_acc = 0, c_sf = 0;               // cycles waiting for a free accumulator set / for the stage's scale factors
+      const long long c_m0 = SFB_MARKS_ON ? clock64() : 0;
+      for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
+        const int e = a.seg_expert[t / n_tiles];
+        if (e == -1) continue;
+        const uint32_t idesc = make_idesc((e >= 0 && a.a_fp4) ? 5 : 0, 0, 128, NP);
+        const int buf = lt & 1;
+        const long long w0 = SFB_MARKS_ON ? clock64() : 0;
+        if (lt >= 2 && !mbar_wait(&S.acc_empty[buf], ((lt >> 1) - 1) & 1)) { S.fail = 3; break; }
+        if (SFB_MARKS_ON) c_acc += clock64() - w0;
+        tc_fence_after();
+        const uint32_t t_acc = tmem + (uint32_t)buf * NP;
+        bool ok = true;
+        for (int i = 0; i < nks; ++i, ++it) {
+          const int s = it % PD_STAGES;
+          const long long w1 = SFB_MARKS_ON ? clock64() : 0;
+          if (!mbar_wait(&S.sfready[s], (it / PD_STAGES) & 1)) { S.fail = 2; ok = false; break; }
+          if (SFB_MARKS_ON) c_sf += clock64() - w1;
+          tc_fence_after();
+          const uint32_t sl = (uint32_t)s * 4;
+          const uint32_t a_addr = smem_u32(S.a[s]), b_addr = smem_u32(S.b[s]);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t id = idesc | ((uint32_t)kk << 29) | ((uint32_t)kk << 4);
+            tc_mma_bs(t_acc, make_desc(a_addr + kk * 32, 1024, 16, 2), make_desc(b_addr + kk * 32, 1024, 16, 2), id, t_sfa + sl,
+                      t_sfb + sl, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&S.empty[s]);
+        }
+        tc_commit(&S.acc_full[buf]);      // arrives even after a failed wait, so the epilogue never waits for its limit
+        if (!ok) break;
+        ++lt;
+      }
+      if (SFB_MARKS_ON && a.marks && (int)blockIdx.x < a.marks_cap) {      // per CTA: tiles, MMA-thread cycles, waiting for a set / for data
+        a.marks[(size_t)blockIdx.x * 16 + 0] = (unsigned long long)lt;
+        a.marks[(size_t)blockIdx.x * 16 + 1] = (unsigned long long)(clock64() - c_m0);
+        a.marks[(size_t)blockIdx.x * 16 + 2] = (unsigned long long)c_acc;
+        a.marks[(size_t)blockIdx.x * 16 + 3] = (unsigned long long)c_sf;
+      }
+    }
+  } else if (warp == 6) {
+    if (elect_one()) {
+      uint32_t it = 0;
+      long long c_full = 0;                        // cycles the copier waited for a stage to land
+      const long long c_c0 = SFB_MARKS_ON ? clock64() : 0;
+      for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
+        if (a.seg_expert[t / n_tiles] == -1) continue;
+        bool ok = true;
+        for (int i = 0; i < nks; ++i, ++it) {
+          const int s = it % PD_STAGES;
+          const long long w0 = SFB_MARKS_ON ? clock64() : 0;
+          if (!mbar_wait(&S.full[s], (it / PD_STAGES) & 1)) { S.fail = 4; ok = false; break; }
+          if (SFB_MARKS_ON) c_full += clock64() - w0;
+          tc_fence_after();
+          tc_cp_sf(t_sfa + (uint32_t)s * 4, make_desc(smem_u32(S.sfa[s]), 128, 0, 0));
+          tc_cp_sf(t_sfb + (uint32_t)s * 4, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
+          tc_commit(&S.sfready[s]);
+        }
+        if (!ok) break;
+      }
+      if (SFB_MARKS_ON && a.marks && (int)blockIdx.x < a.marks_cap) {
+        a.marks[(size_t)blockIdx.x * 16 + 4] = (unsigned long long)(clock64() - c_c0);
+        a.marks[(size_t)blockIdx.x * 16 + 5] = (unsigned long long)c_full;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    bool pending = false;
+    int lt = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x) {
+      const int tile = t % n_tiles, seg = t / n_tiles;
+      if (a.seg_expert[seg] == -1) continue;       // CTA-uniform (every thread reads the same word)
+      const int nv = a.seg_count[seg];
+      const int buf = lt & 1;
+      if (warp == 2) {
+        bool got = true;
+        if (lane == 0) got = mbar_wait(&S.acc_full[buf], (lt >> 1) & 1) && !S.fail;
+        got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+        if (lane == 0 && !got) S.ep_ok = 0;
+      }
+      if (pending) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the staging tile has been read out
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!S.ep_ok) break;
+      tc_fence_after();
+      const uint32_t t_acc = tmem + (uint32_t)buf * NP;
+#pragma unroll
+      for (int c0 = 0; c0 < NP; c0 += 16) {
+        if (c0 >= nv) break;                       // warp-uniform
+        uint32_t v[16];
+        tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (c0 + j < nv) S.outf[(c0 + j) * 128 + q * 32 + lane] = __uint_as_float(v[j]);
+      }
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) mbar_arrive(&S.acc_empty[buf]);       // every warp's TMEM reads of this set are done
+      const int tok = q * 32 + lane;
+      pending = false;
+      if (tok < nv) {
+        bulk_store(a.out_f + (int64_t)(seg * NP + tok) * a.out_stride + tile * 128, smem_u32(S.outf + tok * 128), 512);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        pending = true;
+      }
+      ++lt;
+    }
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    if ((S.fail || !S.ep_ok) && lane == 0 && q == 0) status_set(a.status, ST_TIMEOUT, 80 + S.fail, blockIdx.x, lt);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 256);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1615,7 +1840,7 @@ static thread_local GatherSpec g_gather;
 
 // Tuning switches for measurements (0 = the shipped choice): [1] stages of the 64-pair down projection (2 shipped; 3, 4),
 // [2] stages of the 64-pair gate/up (2 = two CTAs per SM; 3, 5 = one CTA per SM), [3] / [4] segment-major grid order of the
-// grouped down / gate-up kernels, [5] persistent many-row dense kernel, [6] persistent 64-pair gate/up kernel (1 = never, 2 = whenever the shape allows).
+// grouped down / gate-up kernels, [5] persistent many-row dense kernel, [6] persistent 64-pair gate/up kernel, [7] = 2: persistent 64-pair down kernel (1 = never, 2 = whenever the shape allows for [5] and [6]).
 static int g_tune[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 // Phase marks (um_mark) of the NEXT launch of a tensor-core GEMM of this library: cleared by that launch.
 static thread_local unsigned long long* g_marks = nullptr;
@@ -1950,6 +2175,19 @@ int sfb_umma_down_grouped(const void* tmapA, const void* tmapA2, const void* tma
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (inter / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
   a.a_fp4 = 1; a.mode = UM_DOWN_GROUPED; a.inter = inter; a.d = d; a.out_f = out_f; a.out_stride = d; a.seg_expert = seg_expert;
   a.seg_count = seg_count; a.status = (Status*)status; a.splits = 1;
+  // tuning arm [7] = 2: one persistent CTA per SM (measured slower than three 2-stage CTAs per SM at 1,024 rows)
+  if (seg_size == 64 && g_push.n == 0 && g_gather.n == 0 && g_tune[7] == 2) {
+    apply_marks(a);
+    static int sms = 0;
+    if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+    const int total = (d / 128) * segments;
+    const size_t smem = sizeof(UmmaDownPersistSmem) + 1024;
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(umma_down_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+    return (int)sfb_launch(umma_down_persistent_kernel, dim3(total < sms ? total : sms), dim3(PD_THREADS), smem, stream,
+                           *(const CUtensorMap*)tmapA, *(const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA), *(const CUtensorMap*)tmapB, a,
+                           d / 128, segments);
+  }
   if (seg_size == 64 && g_tune[1] != 3) {      // shipped: 2 stages, so that three CTAs share an SM (measured best); tuning arm 4 stages
     apply_push(a); apply_gather(a);
     a.tok_tiles = 1;

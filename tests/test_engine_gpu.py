@@ -566,8 +566,8 @@ def test_step_ledger_and_segment_identity(tiny):
 
 def test_wide_moe_segments_and_the_persistent_kernels_give_the_bits_of_16_pair_segments(tiny):
     """Many-row steps cut the sorted (token, expert) pairs into segments of 64 instead of 16, and large launches run the
-    persistent gate/up kernel: per-pair arithmetic and the per-token slot-order sum are unchanged, so the logits of a step
-    are bit-identical under all three forms."""
+    persistent gate/up and down kernels: per-pair arithmetic and the per-token slot-order sum are unchanged, so the logits
+    of a step are bit-identical under all three forms."""
     from sparkflash_b200.models.deepseek_v41 import engine as E
     from sparkflash_b200.ops import native as N
     cfg, ck, w, orc, dw = tiny
@@ -576,6 +576,7 @@ def test_wide_moe_segments_and_the_persistent_kernels_give_the_bits_of_16_pair_s
     try:
         for wide_rows, persistent in ((10 ** 6, 1), (4, 1), (4, 2)):
             N.umma_tune(6, persistent)
+            N.umma_tune(7, persistent)
             e = E.Engine(dw, max_lanes=2, max_context=256, max_rows=64, arm="tc", use_graphs=False, keep_logits=True)
             e.GROUP_WIDE_ROWS = wide_rows
             e.step(prompt[:40], [0] * 40, list(range(40)))
@@ -584,6 +585,7 @@ def test_wide_moe_segments_and_the_persistent_kernels_give_the_bits_of_16_pair_s
             outs.append(e.logits[:20].clone())
     finally:
         N.umma_tune(6, 0)
+        N.umma_tune(7, 0)
     assert torch.equal(outs[0], outs[1])
     assert torch.equal(outs[1], outs[2])
 
