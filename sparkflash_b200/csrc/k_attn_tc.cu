@@ -431,7 +431,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     __syncthreads();
     if (tile == 0) at_mark(a, 3);
     // ---- S^T = K Q^T ----
-    if (lane == 0 && warp < 2) {      // warp 0: slabs 0..3 into S0, warp 1: slabs 4..7 into S1
+    if (warp < 2 && elect_one()) {      // warp 0: slabs 0..3 into S0, warp 1: slabs 4..7 into S1
       tc_fence_after();
       const uint32_t idesc = make_idesc(128, NH, 0);
       const uint32_t kvb = smem_u32(S.kv), qb = smem_u32(S.q);
@@ -535,7 +535,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     tc_fence_before();
     __syncthreads();
     // ---- O^T += V^T P^T ----
-    if (lane == 0 && warp < 4) {      // warp j issues the 128-dim output tile j
+    if (warp < 4 && elect_one()) {      // warp j issues the 128-dim output tile j
       tc_fence_after();
       const uint32_t idesc = make_idesc(128, NH, 1);
       const uint32_t kvb = smem_u32(S.kv), pb = smem_u32(S.p);

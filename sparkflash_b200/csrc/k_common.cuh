@@ -107,6 +107,15 @@ __device__ __forceinline__ uint4 ldg_nc(const void* p) {
   return v;
 }
 
+// ---- one thread of a warp ----------------------------------------------------------------------------------
+// One lane of a converged warp.  Unlike a test of the lane index, the election tells the compiler that exactly one thread
+// runs the guarded code, so the operands of the TMA / tcgen05 instructions in it can stay in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- reductions -------------------------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(itc::THREADS) index_scores_tc_kernel(const __g
   const bool work = e0 < clen_max;
   bool ok = true;
   if (work) {
-    if (tid == 0) {
+    if (warp == 0 && elect_one()) {
       mbar_expect_tx(&S.full, 128 * 64 + NP * 64 + 512);
       tma_load_2d(S.a, &tmapK, 0, (int)(L * a.lane_rows) + e0, &S.full);
       tma_load_2d(S.b, &tmapQ, 0, row0 * 32, &S.full);
@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(itc::THREADS) index_scores_tc_kernel(const __g
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
-    if (tid == 0) {
+    if (warp == 0 && elect_one()) {
       ok = mbar_wait(&S.full, 0);
       tc_fence_after();
       tc_cp_sf(t_sfa, make_desc(smem_u32(S.sfa), 128, 0, 0));

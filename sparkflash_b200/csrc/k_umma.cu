@@ -95,13 +95,6 @@ __device__ __forceinline__ void tmem_relinquish() {
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
-// One lane of a converged warp.  Unlike a test of the lane index, the election tells the compiler that exactly one thread
-// runs the guarded code, so the operands of the TMA / tcgen05 instructions in it can stay in uniform registers.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-  return pred != 0;
-}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
@@ -349,13 +342,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     }
     // dense weights and their scales do not depend on the previous kernel: request the first stages' weight tiles now, so
     // that their fetch overlaps the predecessor's tail; the activation tiles follow after the wait
-    if (warp == 0 && lane == 0) {
-      const uint32_t stage_tx = (w.a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + (a.bf16 ? 0 : 1024);
-      pre = w.nks < UM_STAGES ? w.nks : UM_STAGES;
-      for (int i = 0; i < pre; ++i) {
-        mbar_expect_tx(&S.full[i], stage_tx);
-        tma_load_2d(S.a[i][0], w.ma, (w.ks0 + i) * UM_BK, w.a_row0, &S.full[i]);
-        if (!a.bf16) bulk_load(S.sfa[i][0], w.sfa + (size_t)i * 512, 512, &S.full[i]);
+    if (warp == 0) {
+      pre = w.nks < UM_STAGES ? w.nks : UM_STAGES;      // in every lane: whichever lane is elected below and later knows it
+      if (elect_one()) {
+        const uint32_t stage_tx = (w.a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + (a.bf16 ? 0 : 1024);
+        for (int i = 0; i < pre; ++i) {
+          mbar_expect_tx(&S.full[i], stage_tx);
+          tma_load_2d(S.a[i][0], w.ma, (w.ks0 + i) * UM_BK, w.a_row0, &S.full[i]);
+          if (!a.bf16) bulk_load(S.sfa[i][0], w.sfa + (size_t)i * 512, 512, &S.full[i]);
+        }
       }
     }
   }
@@ -411,7 +406,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
   const uint32_t t_sfb = tmem + NP + 8;      // 2 x 4 columns
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {
       int gated = -1;
       um_mark(a, 2);
       for (int i = 0; i < w.nks; ++i) {
@@ -446,7 +441,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (elect_one()) {
       const uint32_t idesc = make_idesc(w.a_fp4 ? 5 : 0, 0, 128, NP);
       for (int i = 0; i < w.nks; ++i) {
         const int s = i % UM_STAGES;
@@ -822,7 +817,7 @@ umma_bulk_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const __g
   constexpr uint32_t STAGE_TX = UM_A_BYTES + 128 * UM_BK + 1024;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {
       uint32_t it = 0;
       for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
         const int wt = t % n_w, tt = t / n_w;
@@ -840,7 +835,7 @@ umma_bulk_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const __g
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (elect_one()) {
       const uint32_t idesc = make_idesc(0, 0, 128, 128);
       uint32_t it = 0;
       int lt = 0;
@@ -1045,7 +1040,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
   const int nks_run = skip ? 0 : nks;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {
       um_mark(a, 2);
       for (int i = 0; i < nks_run; ++i) {
         const int s = i % UM_STAGES;
@@ -1060,7 +1055,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
       }
     }
   } else if (warp == 1 || warp == 6) {
-    if (lane == 0) {
+    if (elect_one()) {
       const int h = warp == 1 ? 0 : 1;           // 0: gate tile, 1: up tile
       const uint32_t idesc = make_idesc(a_fp4 ? 5 : 0, 0, 128, NP);
       const uint32_t t_d = h ? t_u : t_g, t_sa = h ? t_sfu : t_sfg, t_sb = h ? t_sfb2 : t_sfb;
@@ -1096,7 +1091,7 @@ umma_gateup_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_const
       if (h == 0) um_mark(a, 4);
     }
   } else if (warp == 7 || warp == 8) {
-    if (lane == 0) {      // scale-factor copies of one accumulator's operands, a thread of their own
+    if (elect_one()) {      // scale-factor copies of one accumulator's operands, a thread of their own
       const int h = warp == 7 ? 0 : 1;
       const uint32_t t_sa = h ? t_sfu : t_sfg, t_sb = h ? t_sfb2 : t_sfb;
       for (int i = 0; i < nks_run; ++i) {
@@ -1300,7 +1295,7 @@ umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const _
   const uint32_t t_sfg = tmem + 256, t_sfb = tmem + 276, t_sfu = tmem + 296, t_sfb2 = tmem + 316;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {
       uint32_t it = 0;
       for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
         const int tile = t % n_tiles, seg = t / n_tiles;
@@ -1337,7 +1332,7 @@ umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const _
       }
     }
   } else if (warp == 1 || warp == 6) {
-    if (lane == 0) {
+    if (elect_one()) {
       const int h = warp == 1 ? 0 : 1;           // 0: gate tile, 1: up tile
       const uint32_t t_sa = h ? t_sfu : t_sfg, t_sb = h ? t_sfb2 : t_sfb;
       uint32_t it = 0;
@@ -1383,7 +1378,7 @@ umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const _
       }
     }
   } else if (warp == 7 || warp == 8) {
-    if (lane == 0) {
+    if (elect_one()) {
       const int h = warp == 7 ? 0 : 1;
       const uint32_t t_sa = h ? t_sfu : t_sfg, t_sb = h ? t_sfb2 : t_sfb;
       uint32_t it = 0;
@@ -1840,7 +1835,7 @@ static thread_local GatherSpec g_gather;
 
 // Tuning switches for measurements (0 = the shipped choice): [1] stages of the 64-pair down projection (2 shipped; 3, 4),
 // [2] stages of the 64-pair gate/up (2 = two CTAs per SM; 3, 5 = one CTA per SM), [3] / [4] segment-major grid order of the
-// grouped down / gate-up kernels, [5] persistent many-row dense kernel, [6] persistent 64-pair gate/up kernel, [7] = 2: persistent 64-pair down kernel (1 = never, 2 = whenever the shape allows for [5] and [6]).
+// grouped down / gate-up kernels, [5] persistent many-row dense kernel, [6] persistent 64-pair gate/up kernel, [7] persistent 64-pair down kernel (1 = never, 2 = whenever the shape allows).
 static int g_tune[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 // Phase marks (um_mark) of the NEXT launch of a tensor-core GEMM of this library: cleared by that launch.
 static thread_local unsigned long long* g_marks = nullptr;
@@ -2175,8 +2170,8 @@ int sfb_umma_down_grouped(const void* tmapA, const void* tmapA2, const void* tma
   a.sfa = (const uint8_t*)sfa; a.sfa2 = (const uint8_t*)sfa2; a.katoms_a = (inter / 32 + 3) / 4; a.sfb = (const uint8_t*)sfb; a.katoms_b = a.katoms_a;
   a.a_fp4 = 1; a.mode = UM_DOWN_GROUPED; a.inter = inter; a.d = d; a.out_f = out_f; a.out_stride = d; a.seg_expert = seg_expert;
   a.seg_count = seg_count; a.status = (Status*)status; a.splits = 1;
-  // tuning arm [7] = 2: one persistent CTA per SM (measured slower than three 2-stage CTAs per SM at 1,024 rows)
-  if (seg_size == 64 && g_push.n == 0 && g_gather.n == 0 && g_tune[7] == 2) {
+  // many (column tile, segment) pairs: one persistent CTA per SM ([7]: 0 this rule, 1 never, 2 whenever the shape allows)
+  if (seg_size == 64 && g_push.n == 0 && g_gather.n == 0 && g_tune[7] != 1 && (g_tune[7] == 2 || (d / 128) * segments >= 296)) {
     apply_marks(a);
     static int sms = 0;
     if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
