@@ -58,7 +58,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < UM_SPIN_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > 64) __nanosleep(64);
+    if (i > 4096) __nanosleep(64);      // a poll suspends the thread for a while by itself; sleeping early delayed every hand-over
   }
   return false;
 }
@@ -524,7 +524,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
           t += __uint_as_float(u[j]);
           sum[j] = col_ok ? t : 0.f;
         }
-        if (a.out_q) {
+        if (a.out_q && !pd_stage) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float r = bfr(sum[j]);
@@ -543,19 +543,51 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
               if (a.out_b) a.out_b[o] = __float2bfloat16_rn(sum[j]);
               if (a.out_f) a.out_f[o] = sum[j];
             }
-            if (a.out_q) {
+            if (a.out_q && !pd_stage) {
               const uint8_t sc = act_scale_code_fp8(__uint_as_float(amax_bits[j]));
               const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
               const uint8_t code = enc_e4m3(bfr(sum[j]) * inv);
-              if (pd_stage) {
-                st_q[tok * 128 + q * 32 + lane] = code;
-                if (lane == 0) st_sf[tok * 4 + q] = sc;
-              } else if (col_ok) {
+              if (col_ok) {
                 a.out_q[o] = code;
                 if (lane == 0) a.out_q_atom[sf_offset(w.out_row0 + tok, col >> 5, (int)(a.out_stride >> 5))] = sc;
               }
             }
           }
+        }
+      }
+      if (pd_stage && a.out_q) {       // CTA-uniform
+        // the FP8 copy from the staged bf16 rows: sixteen consecutive columns of one token per thread and turn (two
+        // neighbouring lanes share a 32-column scale block), packed conversions, 16-byte stores.  (Quantising from the TMEM
+        // layout - one column per lane, one warp reduction per token - was most of this kernel's epilogue.)
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int tid = q * 32 + lane;
+        for (int base = 0; base < nv * 8; base += 128) {      // the same trip count in every thread: the shuffle below is warp-wide
+          const int sg = base + tid;
+          const bool live = sg < nv * 8;
+          const int tok = live ? sg >> 3 : 0, seg = sg & 7;
+          const uint4* src = reinterpret_cast<const uint4*>(st_b + tok * 128 + seg * 16);
+          const uint4 a0 = src[0], a1 = src[1];
+          const uint32_t wv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+          float o[16];
+          float amax = 0.f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            o[2 * k] = __uint_as_float(wv[k] << 16);
+            o[2 * k + 1] = __uint_as_float(wv[k] & 0xffff0000u);
+            amax = fmaxf(amax, fmaxf(fabsf(o[2 * k]), fabsf(o[2 * k + 1])));      // fmaxf drops a NaN operand: it counts as 0
+          }
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+          if (!live) continue;
+          const uint8_t sc = act_scale_code_fp8(amax);
+          const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+          uint32_t cw[4];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t c2 = enc_e4m3x2(o[2 * k] * inv, o[2 * k + 1] * inv);
+            if (k & 1) cw[k >> 1] |= c2 << 16; else cw[k >> 1] = c2;
+          }
+          *reinterpret_cast<uint4*>(st_q + tok * 128 + seg * 16) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+          if (!(seg & 1)) st_sf[tok * 4 + (seg >> 1)] = sc;
         }
       }
       if (pd_stage) {       // CTA-uniform
@@ -736,7 +768,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         } else {
           for (int pr = 0; pr < a.n_peers; ++pr) bulk_store(a.peer_out[pr] + (int64_t)row * a.out_stride + w.col0, src, 256);
         }
-        bulk_store_commit_wait();
+        if (a.n_peers > 0) bulk_store_commit_wait();      // the arrival flag below follows the writes
+        else bulk_store_commit_wait_read();               // local rows: the grid's end orders them for the next kernel
       }
     }
     if (a.n_peers > 0) {
@@ -1969,9 +2002,8 @@ int sfb_umma_bulk(const void* tmapA, const void* tmapB, const void* sfa, int kat
   // run under the next tile's main loop.  g_tune[5]: 1 = never, 2 = whenever the shape allows
   const bool can_persist = NP == 128 && splits == 1 && !b_maps && !out_f && (out_b || g_push.n > 0) && N % 128 == 0 &&
                            (out_stride % 8) == 0 && K >= UM_BK;
-  // (one issuing thread per SM paces its main loop, so for long reductions two one-tile CTAs per SM stay faster: measured
-  // 1.23 vs 1.11 PFLOP/s at K = 1280 and 1.38 vs 1.57 at K = 2560; with a push the copies' latency decides)
-  if (can_persist && g_tune[5] != 1 && (g_tune[5] == 2 || (tiles * tok_tiles >= 296 && (K <= 1536 || g_push.n > 0)))) {
+  // (for any reduction length: 320 tiles of K = 8192 on 296 one-tile CTA slots left a nearly empty second wave)
+  if (can_persist && g_tune[5] != 1 && (g_tune[5] == 2 || tiles * tok_tiles >= 296)) {
     apply_push(a); apply_gather(a);
     static int sms = 0;
     if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }

@@ -564,6 +564,7 @@ class Engine:
                       self.attn_out, n, self.hl, hd, rd, cfg.window, kv.ring, hd ** -0.5, out_q=tcb.ao_q, out_atom=tcb.ao_atom,
                       pair_block=64, win_lo=win[0] if win else None, win_hi=win[1] if win else None, status=self.status); self._k()
             tba = tcb.bmap(tcb.ao_q, 128 * tcb.nblk, self.hl * hd, 128)
+            self._arm_marks("wo_a")
             N.umma_pair_bulk(T.wo_a.tmap, tba, T.wo_a.atoms, tcb.ao_atom, n, ol, gin, groups=self.gl, splits=1,
                              scratch=tcb.scratch, tickets=tcb.tickets, out_b=self.oa, out_q=tcb.oa_q, out_q_atom=tcb.oa_atom,
                              status=self.status); self._k()
