@@ -33,6 +33,8 @@ constexpr int COEF_THREADS = 256;  // 8 predictor parts x 32 columns (one warp p
 constexpr int COEF_PARTS = 8;
 constexpr int MAX_MQ = 3;
 
+// The fold's sums are written with explicit multiply-add intrinsics: the compiler may contract `a * b + c * d` either way
+// round, and the three fold kernels (cluster, rows, rows through bulk copies) must produce the same bits for a row.
 // coefficient record per row: pre[hc] | post[hc] | comb[hc*hc]
 __host__ __device__ inline int coef_stride(int hc) { return 2 * hc + hc * hc; }
 
@@ -62,11 +64,14 @@ struct FoldArgs {
   float norm_eps;
 };
 
+// HC > 0 fixes the number of residual copies at compile time (the coefficient arrays then live in registers; indexed with a
+// run-time hc they sat in local memory and the fold of a row took three times as long); HC = 0 reads it from the arguments.
+template <int HC>
 __global__ void __cluster_dims__(FOLD_CLUSTER, 1, 1) __launch_bounds__(FOLD_THREADS) seam_fold_kernel(FoldArgs a) {
   cg::cluster_group cluster = cg::this_cluster();
   const int row = blockIdx.y;
   const int rank = blockIdx.x;  // == cluster rank
-  const int hc = a.hc, d = a.d;
+  const int hc = HC > 0 ? HC : a.hc, d = a.d;
   const int cpc = d / FOLD_CLUSTER;            // columns of this CTA (multiple of 32)
   const int c_lo = rank * cpc;
   __shared__ float part_ss, part_hss;
@@ -116,10 +121,10 @@ __global__ void __cluster_dims__(FOLD_CLUSTER, 1, 1) __launch_bounds__(FOLD_THRE
         float nx[MAX_HC];
 #pragma unroll
         for (int k = 0; k < MAX_HC; ++k) {
-          float v = post[k] * y;
+          float v = __fmul_rn(post[k], y);
 #pragma unroll
           for (int j = 0; j < MAX_HC; ++j)
-            if (j < hc && k < hc) v += comb[j * hc + k] * x[j];
+            if (j < hc && k < hc) v = __fmaf_rn(comb[j * hc + k], x[j], v);
           nx[k] = bfr(v);
         }
 #pragma unroll
@@ -130,10 +135,10 @@ __global__ void __cluster_dims__(FOLD_CLUSTER, 1, 1) __launch_bounds__(FOLD_THRE
       float v = 0.f;
 #pragma unroll
       for (int c = 0; c < MAX_HC; ++c)
-        if (c < hc) { v += ap[c] * x[c]; hsq += x[c] * x[c]; }
+        if (c < hc) { v = __fmaf_rn(ap[c], x[c], v); hsq = __fmaf_rn(x[c], x[c], hsq); }
       v = bfr(v);
       xh[it] = v;
-      ss += v * v;
+      ss = __fmaf_rn(v, v, ss);
     }
   }
   ss = block_sum(ss, sh);
@@ -181,9 +186,10 @@ __global__ void __cluster_dims__(FOLD_CLUSTER, 1, 1) __launch_bounds__(FOLD_THRE
 constexpr int FOLDR_THREADS = 256;
 constexpr int FOLDR_MAX_IT = 8;      // d <= 256 * 4 * 8
 
+template <int HC>
 __global__ void __launch_bounds__(FOLDR_THREADS) seam_fold_rows_kernel(FoldArgs a) {
   const int row = blockIdx.x;
-  const int hc = a.hc, d = a.d;
+  const int hc = HC > 0 ? HC : a.hc, d = a.d;
   __shared__ float sh[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -249,10 +255,10 @@ __global__ void __launch_bounds__(FOLDR_THREADS) seam_fold_rows_kernel(FoldArgs 
         for (int k = 0; k < MAX_HC; ++k) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            float v = post[k] * y[e];
+            float v = __fmul_rn(post[k], y[e]);
 #pragma unroll
             for (int j = 0; j < MAX_HC; ++j)
-              if (j < hc && k < hc) v += comb[j * hc + k] * x[j][e];
+              if (j < hc && k < hc) v = __fmaf_rn(comb[j * hc + k], x[j][e], v);
             nx[k][e] = bfr(v);
           }
         }
@@ -271,10 +277,10 @@ __global__ void __launch_bounds__(FOLDR_THREADS) seam_fold_rows_kernel(FoldArgs 
         float v = 0.f;
 #pragma unroll
         for (int c = 0; c < MAX_HC; ++c)
-          if (c < hc) { v += ap[c] * x[c][e]; hsq += x[c][e] * x[c][e]; }
+          if (c < hc) { v = __fmaf_rn(ap[c], x[c][e], v); hsq = __fmaf_rn(x[c][e], x[c][e], hsq); }
         v = bfr(v);
         xh[it][e] = v;
-        ss += v * v;
+        ss = __fmaf_rn(v, v, ss);
       }
     }
   }
@@ -323,6 +329,229 @@ __global__ void __launch_bounds__(FOLDR_THREADS) seam_fold_rows_kernel(FoldArgs 
       }
     }
   }
+}
+
+// Many-row seam with the row moved by bulk copies: the row's residual copies (hc x d bf16, contiguous) and the W partial
+// outputs arrive in shared memory as one asynchronous copy each, the fold and the normalisation run from there, and the new
+// residual, the folded output, the normalised row, its FP8 codes and scale bytes leave as one bulk copy each.  With 8-byte
+// loads per thread and the in-place stores between them the register version kept too few bytes in flight (a third of the
+// copy bandwidth).  Same arithmetic, in the same order, as seam_fold_rows_kernel: the outputs are bit-identical.
+__device__ __forceinline__ uint32_t fold_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool fold_mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (1u << 22); ++i) {      // bounded: several hundred milliseconds
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(fold_smem_u32(bar)), "r"(parity) : "memory");
+    if (ok) return true;
+    if (i > 4096) __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void fold_bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(fold_smem_u32(dst)), "l"(src), "r"(bytes), "r"(fold_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void fold_bulk_store(void* dst, const void* src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(fold_smem_u32(src_smem)), "r"(bytes) : "memory");
+}
+
+// phase marks of the bulk-copy fold (measurement builds): eight %globaltimer words per row of the last launch -
+// entry, dependencies met, row landed, fold done, sums done, outputs staged, copies read
+#ifdef SFB_KERNEL_MARKS
+__device__ unsigned long long g_fold_marks[4096 * 8];
+#define FOLD_MARK(slot) do { if (threadIdx.x == 0 && blockIdx.x < 4096) g_fold_marks[blockIdx.x * 8 + (slot)] = globaltimer_ns(); } while (0)
+#else
+#define FOLD_MARK(slot) do { } while (0)
+#endif
+
+template <int HC>
+__global__ void __launch_bounds__(FOLDR_THREADS) seam_fold_rows_bulk_kernel(FoldArgs a) {
+  extern __shared__ __align__(128) uint8_t fold_sm[];
+  FOLD_MARK(0);
+  const int row = blockIdx.x;
+  const int hc = HC > 0 ? HC : a.hc, d = a.d;
+  const int W = a.has_post ? a.W : 0;
+  const int KB = d / 32;
+  __nv_bfloat16* sh_h = reinterpret_cast<__nv_bfloat16*>(fold_sm);
+  __nv_bfloat16* sh_y = sh_h + (size_t)hc * d;
+  __nv_bfloat16* sh_xn = sh_y + (size_t)W * d;
+  uint8_t* sh_xq = reinterpret_cast<uint8_t*>(sh_xn + d);
+  uint8_t* sh_xs = sh_xq + d;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(sh_xs + ((KB + 15) & ~15));
+  __shared__ float sh[32];
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(fold_smem_u32(bar)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+  if (a.has_post && a.flags[0] != nullptr) {
+    const uint32_t want = (a.epoch_ptr ? *a.epoch_ptr : 0u) + a.epoch_add;
+    if (threadIdx.x < a.W && !wait_flag_ge(a.flags[threadIdx.x], want, a.wait_ns))
+      status_set(a.status, ST_TIMEOUT, 2, threadIdx.x, (int)want);
+  }
+  __syncthreads();
+  FOLD_MARK(1);
+  if (threadIdx.x < 32 && elect_one()) {
+    asm volatile("fence.proxy.async;" ::: "memory");      // the partials were published to the generic proxy; the copies read them
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fold_smem_u32(bar)), "r"((uint32_t)((hc + W) * d * 2)) : "memory");
+    fold_bulk_load(sh_h, a.h + (size_t)row * hc * d, (uint32_t)(hc * d * 2), bar);
+    for (int r = 0; r < W; ++r) fold_bulk_load(sh_y + (size_t)r * d, a.y[r] + (size_t)row * d, (uint32_t)(d * 2), bar);
+  }
+  float post[MAX_HC], comb[MAX_HC * MAX_HC], ap[MAX_HC];
+#pragma unroll
+  for (int c = 0; c < MAX_HC; ++c) {
+    ap[c] = c < hc ? a.a_pre[(size_t)row * a.a_stride + c] : 0.f;
+    post[c] = 0.f;
+  }
+  if (a.has_post) {
+    const float* cp = a.coef_prev + (size_t)row * coef_stride(hc);
+#pragma unroll
+    for (int c = 0; c < MAX_HC; ++c)
+      if (c < hc) post[c] = cp[hc + c];
+#pragma unroll
+    for (int i = 0; i < MAX_HC * MAX_HC; ++i)
+      if (i < hc * hc) comb[i] = cp[2 * hc + i];
+  }
+  const bool landed = __syncthreads_and(fold_mbar_wait(bar, 0) ? 1 : 0) != 0;
+  if (!landed) {
+    if (threadIdx.x == 0) status_set(a.status, ST_TIMEOUT, 3, row, 0);
+    return;
+  }
+  FOLD_MARK(2);
+  float xh[FOLDR_MAX_IT][4];
+  float ss = 0.f, hsq = 0.f;
+#pragma unroll
+  for (int it = 0; it < FOLDR_MAX_IT; ++it) {
+    const int col = (it * FOLDR_THREADS + threadIdx.x) * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) xh[it][e] = 0.f;
+    if (col < d) {
+      float x[MAX_HC][4];
+      __nv_bfloat16* hp = sh_h + col;
+#pragma unroll
+      for (int c = 0; c < MAX_HC; ++c) {
+        if (c < hc) {
+          const uint2 u = *reinterpret_cast<const uint2*>(hp + (size_t)c * d);
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+          const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
+          x[c][0] = f0.x; x[c][1] = f0.y; x[c][2] = f1.x; x[c][3] = f1.y;
+        } else {
+          x[c][0] = x[c][1] = x[c][2] = x[c][3] = 0.f;
+        }
+      }
+      if (a.has_post) {
+        float y[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < W; ++r) {
+          const uint2 u = *reinterpret_cast<const uint2*>(sh_y + (size_t)r * d + col);
+          const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+          const float2 f0 = __bfloat1622float2(y2[0]), f1 = __bfloat1622float2(y2[1]);
+          y[0] += f0.x; y[1] += f0.y; y[2] += f1.x; y[3] += f1.y;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[e] = bfr(y[e]);
+        if (a.ysum) {      // into the first partial's place: this thread alone reads and writes these four columns
+          __nv_bfloat162 o2[2] = {__floats2bfloat162_rn(y[0], y[1]), __floats2bfloat162_rn(y[2], y[3])};
+          *reinterpret_cast<uint2*>(sh_y + col) = *reinterpret_cast<uint2*>(o2);
+        }
+        float nx[MAX_HC][4];
+#pragma unroll
+        for (int k = 0; k < MAX_HC; ++k) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float v = __fmul_rn(post[k], y[e]);
+#pragma unroll
+            for (int j = 0; j < MAX_HC; ++j)
+              if (j < hc && k < hc) v = __fmaf_rn(comb[j * hc + k], x[j][e], v);
+            nx[k][e] = bfr(v);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < MAX_HC; ++c) {
+          if (c < hc) {
+            __nv_bfloat162 o2[2] = {__floats2bfloat162_rn(nx[c][0], nx[c][1]), __floats2bfloat162_rn(nx[c][2], nx[c][3])};
+            *reinterpret_cast<uint2*>(hp + (size_t)c * d) = *reinterpret_cast<uint2*>(o2);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[c][e] = nx[c][e];
+          }
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = 0.f;
+#pragma unroll
+        for (int c = 0; c < MAX_HC; ++c)
+          if (c < hc) { v = __fmaf_rn(ap[c], x[c][e], v); hsq = __fmaf_rn(x[c][e], x[c][e], hsq); }
+        v = bfr(v);
+        xh[it][e] = v;
+        ss = __fmaf_rn(v, v, ss);
+      }
+    }
+  }
+  FOLD_MARK(3);
+  ss = block_sum(ss, sh);
+  if (a.hss) {
+    hsq = block_sum(hsq, sh);
+    if (threadIdx.x == 0) a.hss[row] = hsq;
+  }
+  FOLD_MARK(4);
+  const float rsx = rsqrtf(ss / (float)d + a.norm_eps);
+#pragma unroll
+  for (int it = 0; it < FOLDR_MAX_IT; ++it) {
+    const int col = (it * FOLDR_THREADS + threadIdx.x) * 4;
+    // whole warps are in or out of range (d is a multiple of 128)
+    if (col - (int)(threadIdx.x & 31) * 4 < d) {
+      float v[4];
+      float amax = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[e] = col < d ? bfr(xh[it][e] * rsx * a.norm_w[col + e]) : 0.f;
+        amax = fmaxf(amax, fabsf(v[e]));
+      }
+      if (a.xn && col < d) {
+        __nv_bfloat162 o2[2] = {__floats2bfloat162_rn(v[0], v[1]), __floats2bfloat162_rn(v[2], v[3])};
+        *reinterpret_cast<uint2*>(sh_xn + col) = *reinterpret_cast<uint2*>(o2);
+      }
+      if (a.xq) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        if (col < d) {
+          const uint8_t sc = act_scale_code_fp8(amax);
+          const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+          uint32_t q4 = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) q4 |= (uint32_t)enc_e4m3(v[e] * inv) << (8 * e);
+          *reinterpret_cast<uint32_t*>(sh_xq + col) = q4;
+          if ((threadIdx.x & 7) == 0) {
+            sh_xs[col / 32] = sc;
+            if (a.xs_atom) {
+              if (a.atom_mode == 0) a.xs_atom[sf_offset(row, col / 32, KB)] = sc;
+              else a.xs_atom[(size_t)row * sf_bytes(1, KB) + sf_offset(0, col / 32, KB)] = sc;
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+  FOLD_MARK(5);
+  if (threadIdx.x < 32 && elect_one()) {
+    if (a.has_post) {
+      fold_bulk_store(a.h + (size_t)row * hc * d, sh_h, (uint32_t)(hc * d * 2));
+      if (a.ysum) fold_bulk_store(a.ysum + (size_t)row * d, sh_y, (uint32_t)(d * 2));
+    }
+    if (a.xn) fold_bulk_store(a.xn + (size_t)row * d, sh_xn, (uint32_t)(d * 2));
+    if (a.xq) {
+      fold_bulk_store(a.xq + (size_t)row * d, sh_xq, (uint32_t)d);
+      fold_bulk_store(a.xs + (size_t)row * KB, sh_xs, (uint32_t)KB);
+    }
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the block may leave once its shared memory has been read
+  }
+  __syncwarp();
+  FOLD_MARK(6);
 }
 
 struct CoefArgs {
@@ -502,6 +731,17 @@ using namespace sfb;
 
 extern "C" {
 
+// copies the phase marks of the last bulk-copy fold (rows x 8 words) to host memory; -1 when the library has none
+int sfb_seam_read_marks(unsigned long long* dst, int rows) {
+#ifdef SFB_KERNEL_MARKS
+  return (int)cudaMemcpyFromSymbol(dst, g_fold_marks, (size_t)(rows < 4096 ? rows : 4096) * 8 * sizeof(unsigned long long));
+#else
+  (void)dst; (void)rows;
+  return -1;
+#endif
+}
+static int g_seam_tune = 0;      // 1: the many-row fold never takes the bulk-copy kernel (measurements, equality tests)
+int sfb_seam_tune(int v) { g_seam_tune = v; return 0; }
 int sfb_seam_nblk(int d) { return (d + COEF_COLS - 1) / COEF_COLS; }
 int sfb_coef_stride(int hc) { return coef_stride(hc); }
 
@@ -523,9 +763,29 @@ int sfb_seam_fold(void* h, const void* const* y_ptrs, const void* const* flag_pt
   a.ysum = (__nv_bfloat16*)ysum; a.norm_w = norm_w; a.xn = (__nv_bfloat16*)xn; a.xq = (uint8_t*)xq;
   a.xs = (uint8_t*)xs; a.xs_atom = (uint8_t*)xs_atom; a.atom_mode = atom_mode; a.status = (Status*)status;
   a.n = n; a.hc = hc; a.d = d; a.norm_eps = norm_eps; a.hss = hss;
-  if (n > 128 && d % 128 == 0 && d <= FOLDR_THREADS * 4 * FOLDR_MAX_IT)       // many rows: one block per row
-    return (int)sfb_launch(seam_fold_rows_kernel, dim3(n), dim3(FOLDR_THREADS), 0, stream, a);
-  return (int)sfb_launch(seam_fold_kernel, dim3(FOLD_CLUSTER, n), dim3(FOLD_THREADS), 0, stream, a);
+  if (n > 128 && d % 128 == 0 && d <= FOLDR_THREADS * 4 * FOLDR_MAX_IT) {     // many rows: one block per row
+    // rows through bulk copies when every row of every buffer starts on a 16-byte boundary and a row's buffers fit in
+    // shared memory (g_seam_tune: 1 = never)
+    const int Wp = has_post ? W : 0;
+    const size_t smem = (size_t)(hc + Wp + 1) * d * 2 + d + ((d / 32 + 15) & ~15) + 16;
+    uintptr_t bits = (uintptr_t)h | (uintptr_t)ysum | (uintptr_t)xn | (uintptr_t)xq | (uintptr_t)xs;
+    for (int r = 0; r < Wp; ++r) bits |= (uintptr_t)y_ptrs[r];
+    if (g_seam_tune != 1 && d % 512 == 0 && (bits & 15) == 0 && smem <= 200 * 1024 && (xq == nullptr || xs != nullptr)) {
+      static bool attr = false;
+      if (!attr) {
+        cudaError_t rc = cudaFuncSetAttribute(seam_fold_rows_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+        if (rc == cudaSuccess) rc = cudaFuncSetAttribute(seam_fold_rows_bulk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+        if (rc != cudaSuccess) return (int)rc;
+        attr = true;
+      }
+      if (hc == 4) return (int)sfb_launch(seam_fold_rows_bulk_kernel<4>, dim3(n), dim3(FOLDR_THREADS), smem, stream, a);
+      return (int)sfb_launch(seam_fold_rows_bulk_kernel<0>, dim3(n), dim3(FOLDR_THREADS), smem, stream, a);
+    }
+    if (hc == 4) return (int)sfb_launch(seam_fold_rows_kernel<4>, dim3(n), dim3(FOLDR_THREADS), 0, stream, a);
+    return (int)sfb_launch(seam_fold_rows_kernel<0>, dim3(n), dim3(FOLDR_THREADS), 0, stream, a);
+  }
+  if (hc == 4) return (int)sfb_launch(seam_fold_kernel<4>, dim3(FOLD_CLUSTER, n), dim3(FOLD_THREADS), 0, stream, a);
+  return (int)sfb_launch(seam_fold_kernel<0>, dim3(FOLD_CLUSTER, n), dim3(FOLD_THREADS), 0, stream, a);
 }
 
 // Coefficient half: reads the folded residual, writes (pre, post, comb) for the next seam.

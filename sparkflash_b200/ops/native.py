@@ -58,6 +58,11 @@ def seam_nblk(d: int) -> int:
     return int(lib().sfb_seam_nblk(c_int(d)))
 
 
+def seam_tune(value: int) -> None:
+    """Measurement switch of the many-row fold (csrc/k_seam.cu): 1 = never the bulk-copy kernel, 0 = the shipped choice."""
+    _check(lib().sfb_seam_tune(c_int(value)), "seam_tune")
+
+
 def coef_stride(hc: int) -> int:
     return 2 * hc + hc * hc
 

@@ -293,6 +293,42 @@ def test_select_long_rows_matches_single_block_select():
         assert ids1[r, :int(cnt1[r])].tolist() == want
 
 
+@pytest.mark.parametrize("W,with_post", [(1, True), (2, True), (1, False)])
+def test_many_row_seam_through_bulk_copies_gives_the_bits_of_the_register_kernel(W, with_post):
+    """The many-row fold moves a row through shared memory with bulk copies (residual copies and partial outputs in, new
+    residual, folded output, normalised row, codes and scale bytes out): every output matches the kernel that loads and
+    stores from registers bit for bit, scale atoms included."""
+    from sparkflash_b200 import codecs as CC
+    from sparkflash_b200.ops import native as N
+    dev = "cuda"
+    d, hc, n = 5120, 4, 300
+    g = torch.Generator().manual_seed(31 + W)
+    h = (torch.randn(n, hc, d, generator=g) * 0.5).to(torch.bfloat16)
+    ys = [(torch.randn(n, d, generator=g) * 0.3).to(torch.bfloat16).to(dev) for _ in range(W)]
+    norm_w = (1 + 0.05 * torch.randn(d, generator=g)).to(dev)
+    prev = torch.rand(n, N.coef_stride(hc), generator=g).to(dev)
+    outs = []
+    try:
+        for arm in (1, 0):
+            N.seam_tune(arm)
+            hh = h.clone().to(dev)
+            xn = torch.zeros(n, d, dtype=torch.bfloat16, device=dev)
+            xq = torch.zeros(n, d, dtype=torch.uint8, device=dev)
+            xs = torch.zeros(n, d // 32, dtype=torch.uint8, device=dev)
+            atom = torch.zeros(CC.sf_bytes(n, d // 32), dtype=torch.uint8, device=dev)
+            ysum = torch.zeros(n, d, dtype=torch.bfloat16, device=dev)
+            hss = torch.zeros(n, dtype=torch.float32, device=dev)
+            N.seam_fold(hh, ys if with_post else None, prev, prev, prev.stride(0), norm_w, xn, xq, xs, n, hc, d, 1e-20,
+                        ysum=ysum if with_post else None, hss=hss, xs_atom=atom)
+            torch.cuda.synchronize()
+            outs.append((hh, xn, xq, xs, atom, ysum, hss))
+    finally:
+        N.seam_tune(0)
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    assert outs[0][1].float().abs().sum() > 0 and outs[0][2].any()
+
+
 def test_many_row_seam_matches_the_cluster_kernel_and_bf16_coefficients():
     """Steps of 129+ rows fold with one block per row and take the predictor dots from the bf16 tensor-core GEMM: residual
     copies, normalised rows and FP8 codes agree with the few-row kernels, coefficients to the two-term precision."""
