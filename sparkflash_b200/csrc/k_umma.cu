@@ -1459,7 +1459,6 @@ umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const _
       asm volatile("bar.sync 1, 128;" ::: "memory");
       const uint32_t t_g = tmem + (uint32_t)buf * 128, t_u = t_g + NP;
       const int col = tile * 128 + q * 32 + lane;
-      const bool live = col < il;
 #pragma unroll 1
       for (int c0 = 0; c0 < NP && c0 < ncol; c0 += 16) {
         uint32_t vg[16], vu[16];
@@ -1468,34 +1467,31 @@ umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const _
         const int jx = c0 + (lane & 15);
         const float wv = jx < ncol ? a.seg_weight[seg * NP + jx] : 0.f;
         tc_wait_ld();
+        // sixteen independent chains without branches (one warp per scheduler runs the epilogue: only instruction-level
+        // parallelism hides the latency of the exponential and the division); pair slots past the segment's count carry
+        // weight 0 and are never stored
         float act[16];
-        const int nb = ncol - c0;
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) {
-          act[jj] = 0.f;
-          if (jj >= nb) continue;
           const float wj = __shfl_sync(0xffffffffu, wv, jj);
-          if (live) {
-            const float g = fminf(bfr(__uint_as_float(vg[jj])), limit);
-            const float u = fminf(fmaxf(bfr(__uint_as_float(vu[jj])), -limit), limit);
-            act[jj] = bfr(g / (1.f + expf(-g)) * u * wj);
-          }
+          const float g = fminf(bfr(__uint_as_float(vg[jj])), limit);
+          const float u = fminf(fmaxf(bfr(__uint_as_float(vu[jj])), -limit), limit);
+          act[jj] = bfr(g / (1.f + expf(-g)) * u * wj);
         }
         uint32_t amax_bits[16];
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) {
-          amax_bits[jj] = 0u;
-          if (jj >= nb) continue;
           const float ax = (act[jj] == act[jj]) ? fabsf(act[jj]) : 0.f;
           amax_bits[jj] = __reduce_max_sync(0xffffffffu, __float_as_uint(ax));
         }
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) {
           const int j = c0 + jj;
+          const uint8_t sc = act_scale_code_fp8(__uint_as_float(amax_bits[jj]));
+          const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
+          const uint8_t code = enc_e4m3(act[jj] * inv);
           if (j < ncol) {                           // warp-uniform
-            const uint8_t sc = act_scale_code_fp8(__uint_as_float(amax_bits[jj]));
-            const float inv = bits_f32(((uint32_t)(254 - sc)) << 23);
-            S.sq[j * 128 + q * 32 + lane] = enc_e4m3(act[jj] * inv);
+            S.sq[j * 128 + q * 32 + lane] = code;
             if (lane == 0) S.ssf[(j & 31) * 16 + (j >> 5) * 4 + q] = sc;
           }
         }
