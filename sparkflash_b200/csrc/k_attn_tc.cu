@@ -171,7 +171,8 @@ namespace sfb {
 using namespace atc;
 
 // slots: 0 entry, 1 set-up done, 2 queries staged, 3 first tile decoded, 4 its scores done, 5 its softmax done, 6 its value
-// MMAs done, 7 exit, 8 epilogue starts (last tile done), 9 outputs staged, 10 copies issued
+// MMAs done, 7 exit, 8 epilogue starts (last tile done), 9 outputs staged, 10 copies issued, 11 / 12 thread 0 done with the
+// bf16 pass / every thread done with it
 #ifdef SFB_KERNEL_MARKS
 #define SFB_ATTN_MARKS_ON 1
 __device__ __forceinline__ void at_mark(const AttnTcArgs& a, int slot) {
@@ -248,7 +249,7 @@ struct AttnTcSmem {
   alignas(1024) uint8_t q[SLABS * NH * 128];      // NH heads x 512 dims bf16
   alignas(1024) uint8_t p[2 * NH * 128];          // NH heads x 128 keys bf16 (two slabs of 64 keys)
   float sbuf[(NH < 32 ? NH : 32)][KT + 1];        // scores of the tile, head-major: 32 heads per softmax pass
-  float red[THREADS];                             // per (key part, head) partial max / sum
+  alignas(8) float red[THREADS];                  // per (key part, head) partial max / sum; outside the softmax: the row's rope table
   float fac[NH];                                  // per-head rescale of the running accumulator; 1/denominator at the end
   alignas(8) uint64_t bar;                        // score MMAs done (two issuing threads)
   alignas(8) uint64_t bar_pv;                     // value MMAs done (four issuing threads)
@@ -302,6 +303,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
 
   const int pos = a.row_pos[row], L = a.row_lane[row];
   const int r0 = HD - a.rd;
+  // (cos, sin) of the row's position for the rd / 2 roped pairs, kept in the softmax scratch while no softmax runs: for the
+  // queries before the first tile's scores, again for the outputs after the last tile (rd <= THREADS)
+  float2* rope_tab = reinterpret_cast<float2*>(S.red);
+  if (tid < (a.rd >> 1)) rope_tab[tid] = a.rope[(size_t)row * a.rope_stride + tid];      // visible after the first barrier below
   // ---- queries of the group's heads: asynchronous 16-byte copies into the swizzled K-major tile; they land while the
   // first key tile is decoded, and the rope of the last rd dims is applied in place after that ----
   for (int idx = tid; idx < NH * 64; idx += THREADS) {
@@ -419,7 +424,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
         __nv_bfloat162* pr = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float2 c2 = a.rope[(size_t)row * a.rope_stride + ((c * 8 - r0) >> 1) + j];
+          const float2 c2 = rope_tab[((c * 8 - r0) >> 1) + j];
           const float x = __bfloat162float(pr[j].x), y = __bfloat162float(pr[j].y);
           pr[j] = __floats2bfloat162_rn(x * c2.x - y * c2.y, x * c2.y + y * c2.x);
         }
@@ -556,6 +561,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
 
   // ---- epilogue: O^T / denominator (sink in the denominator only), inverse rope, bf16 (+ two-term FP8 copy) ----
   if (ok) {
+    if (tid < (a.rd >> 1)) rope_tab[tid] = a.rope[(size_t)row * a.rope_stride + tid];      // the last softmax is done with the scratch
     if (my_part == 0) {
 #pragma unroll
       for (int ps = 0; ps < NPASS; ++ps) {
@@ -587,37 +593,47 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_kernel(AttnTcArgs a) {
     for (int jj = 0; jj < 2; ++jj) {
       const int j = half * 2 + jj;
       const int dim = j * 128 + (warp & 3) * 32 + lane;
-      const bool roped = dim >= r0;                       // warp-uniform (r0 is a multiple of 32)
-      float2 c2 = make_float2(1.f, 0.f);
-      if (roped) c2 = a.rope[(size_t)row * a.rope_stride + ((dim - r0) >> 1)];
-#pragma unroll 1
-      for (int c0 = 0; c0 < NH; c0 += 16) {
-        uint32_t v[16];
-        tc_ld16(t_o + lane_base + j * NH + c0, v);
-        tc_wait_ld();
-        if (roped) {
+      // every 16-head chunk of the tile is requested before the one wait: a load's round trip (several hundred cycles) was
+      // paid once per chunk
+      constexpr int NCH = NH / 16;
+      uint32_t v[NCH][16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {        // pairs (2p, 2p+1) sit in neighbouring lanes
-            const float o = bfr(__uint_as_float(v[i]) * S.fac[c0 + i]);
-            const float other = __shfl_xor_sync(0xffffffffu, o, 1);
-            st_o[(c0 + i) * HD + dim] = __float2bfloat16_rn((lane & 1) ? -other * c2.y + o * c2.x : o * c2.x + other * c2.y);
-          }
-        } else {
+      for (int ch = 0; ch < NCH; ++ch) tc_ld16(t_o + lane_base + j * NH + ch * 16, v[ch]);
+      tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) st_o[(c0 + i) * HD + dim] = __float2bfloat16_rn(__uint_as_float(v[i]) * S.fac[c0 + i]);
-        }
+      for (int ch = 0; ch < NCH; ++ch) {
+        const int c0 = ch * 16;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) st_o[(c0 + i) * HD + dim] = __float2bfloat16_rn(__uint_as_float(v[ch][i]) * S.fac[c0 + i]);
       }
     }
-    // pass 2: the two-term FP8 copy from the staged bf16 rows, sixteen consecutive dims of one head per thread and turn
+    // pass 2: inverse rope on the last rd dims and the two-term FP8 copy, both from the staged bf16 rows: sixteen consecutive dims of one head per thread and turn
     // (two neighbouring lanes share a 32-dim scale block), packed conversions, 16-byte stores.  (Quantising straight
     // from the TMEM layout - one dim per lane, one warp reduction per head - took 55 % of the CTA's life.)
-    if (a.out_q) {
+    at_mark(a, 11);
+    {
       __syncthreads();
+      at_mark(a, 12);
+      const int seg0 = r0 >> 4;                     // first 16-dim segment that carries rope (rd is a multiple of 32)
       for (int sgm = tid; sgm < NH * 32; sgm += THREADS) {
         const int hh = sgm >> 5, seg = sgm & 31;
-        const uint4* src = reinterpret_cast<const uint4*>(st_o + hh * HD + seg * 16);
+        if (!a.out_q && seg < seg0) continue;
+        uint4* src = reinterpret_cast<uint4*>(st_o + hh * HD + seg * 16);
         const uint4 a0 = src[0], a1 = src[1];
-        const uint32_t w[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        uint32_t w[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        if (seg >= seg0) {
+          // inverse rope on the segment's eight (even, odd) pairs, one word each; written back for the bf16 output
+          const float2* rt = &rope_tab[(seg * 16 - r0) >> 1];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float x = __uint_as_float(w[k] << 16), y = __uint_as_float(w[k] & 0xffff0000u);
+            const float2 c2 = rt[k];
+            w[k] = pack_bf16(__fmaf_rn(x, c2.x, __fmul_rn(y, c2.y)), __fmaf_rn(y, c2.x, -__fmul_rn(x, c2.y)));
+          }
+          src[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          src[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+        if (!a.out_q) continue;
         float o[16];
         float amax = 0.f;
 #pragma unroll
@@ -706,7 +722,7 @@ int sfb_attn_tc(const void* q, int64_t q_stride, const void* rope, int rope_stri
                 int64_t ckv_lane_q, int64_t ckv_lane_s, const int* sel, const int* sel_count, int K, const float* sink, void* out,
                 void* out_q, void* out_atom, int pair_block, int n, int heads, int hd, int rd, int window, int ring, float scale,
                 const int* win_lo, const int* win_hi, void* status, cudaStream_t stream) {
-  if (hd != atc::HD || rd % 32 || rd > hd || n < 1 || heads < 1 || (q_stride % 8)) return (int)cudaErrorInvalidValue;
+  if (hd != atc::HD || rd % 32 || rd > 256 || n < 1 || heads < 1 || (q_stride % 8)) return (int)cudaErrorInvalidValue;
   AttnTcArgs a{};
   a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride; a.rope = (const float2*)rope; a.rope_stride = rope_stride;
   a.row_lane = row_lane; a.row_pos = row_pos; a.win_q = (const uint8_t*)win_q; a.win_s = (const uint8_t*)win_s;
