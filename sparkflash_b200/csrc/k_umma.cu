@@ -919,14 +919,20 @@ umma_bulk_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const __g
       tc_fence_after();
       const int nv = min(128, a.n - tt * 128);
       const uint32_t t_acc = tmem + (uint32_t)buf * 128;
+      // four 16-token chunks are requested before each wait (a load's round trip was paid once per chunk)
 #pragma unroll
-      for (int c0 = 0; c0 < 128; c0 += 16) {
-        uint32_t v[16];
-        tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0, v);
+      for (int b0 = 0; b0 < 128; b0 += 64) {
+        uint32_t v[4][16];
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + b0 + ch * 16, v[ch]);
         tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (c0 + j < nv) S.out[(c0 + j) * 128 + q * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[j]));
+        for (int ch = 0; ch < 4; ++ch) {
+          const int c0 = b0 + ch * 16;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < nv) S.out[(c0 + j) * 128 + q * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[ch][j]));
+        }
       }
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1706,15 +1712,17 @@ umma_down_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const __g
       if (!S.ep_ok) break;
       tc_fence_after();
       const uint32_t t_acc = tmem + (uint32_t)buf * NP;
+      {
+        uint32_t v[NP / 16][16];      // every chunk requested before the one wait
 #pragma unroll
-      for (int c0 = 0; c0 < NP; c0 += 16) {
-        if (c0 >= nv) break;                       // warp-uniform
-        uint32_t v[16];
-        tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + c0, v);
+        for (int ch = 0; ch < NP / 16; ++ch) tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + ch * 16, v[ch]);
         tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (c0 + j < nv) S.outf[(c0 + j) * 128 + q * 32 + lane] = __uint_as_float(v[j]);
+        for (int ch = 0; ch < NP / 16; ++ch) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (ch * 16 + j < nv) S.outf[(ch * 16 + j) * 128 + q * 32 + lane] = __uint_as_float(v[ch][j]);
+        }
       }
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

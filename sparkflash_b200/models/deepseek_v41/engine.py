@@ -680,6 +680,10 @@ class Engine:
         """In-kernel phase marks for the next tensor-core launch when ``self.kernel_marks[name]`` holds a buffer (int64, eight
         words per CTA): entry, set-up, first load, first stage landed, last MMA, accumulator complete, epilogue done, exit."""
         buf = self.__dict__.get("kernel_marks", {}).get(name)
+        if isinstance(buf, list):       # one buffer per launch of the step, in launch order (one per layer)
+            turn = self.__dict__.setdefault("_marks_turn", {})
+            turn[name] = turn.get(name, -1) + 1
+            buf = buf[turn[name] % len(buf)]
         if buf is not None:
             (N.attn_set_marks if name == "attn" else N.umma_set_marks)(buf)
 

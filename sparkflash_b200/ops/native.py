@@ -63,6 +63,12 @@ def seam_tune(value: int) -> None:
     _check(lib().sfb_seam_tune(c_int(value)), "seam_tune")
 
 
+def seam_read_marks(rows: int):
+    """Phase marks of the last bulk-copy seam fold (eight words per row), or None when the library carries none."""
+    buf = (ctypes.c_ulonglong * (rows * 8))()
+    return buf if lib().sfb_seam_read_marks(buf, c_int(rows)) == 0 else None
+
+
 def coef_stride(hc: int) -> int:
     return 2 * hc + hc * hc
 

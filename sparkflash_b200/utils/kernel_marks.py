@@ -47,3 +47,46 @@ def summarize(buf: torch.Tensor) -> dict:
         c = worked[worked[:, 15] > 0].double()
         out["kstep_cycles_wait_copies_mmas"] = [round(float(c[:, k].mean())) for k in (13, 14, 15)]
     return out
+
+
+def summarize_attention(buf: torch.Tensor) -> dict:
+    """Phases of the tensor-core attention kernel (csrc/k_attn_tc.cu ``at_mark``; one launch per buffer): mean microseconds
+    over the CTAs - 0 entry, 1 set-up, 2 query copies issued, 3 first tile decoded (queries landed, rope applied), 4 its
+    scores, 5 its softmax, 6 its value MMAs, 8 last tile done, 11 / 12 accumulator pass done by thread 0 / by every thread,
+    9 outputs staged, 10 copies issued and read, 7 exit."""
+    m = buf.detach().cpu().view(-1, 16).double()
+    m = m[m[:, 7] > 0]
+    if not m.shape[0]:
+        return {"ctas": 0}
+
+    def d(hi: int, lo: int) -> float:
+        return round(float((m[:, hi] - m[:, lo]).mean()) / 1e3, 2)
+    return {"ctas": int(m.shape[0]), "kernel_span_us": round(float(m[:, 7].max() - m[:, 0].min()) / 1e3, 1), "cta_life_us": d(7, 0),
+            "setup_us": d(1, 0), "queries_issued_us": d(2, 1), "first_tile_decoded_us": d(3, 2), "first_tile_scores_us": d(4, 3),
+            "first_tile_softmax_us": d(5, 4), "first_tile_values_us": d(6, 5), "further_tiles_us": d(8, 6),
+            "epilogue_accumulator_pass_us": d(12, 8), "epilogue_rope_quant_pass_us": d(9, 12), "copies_us": d(10, 9), "teardown_us": d(7, 10)}
+
+
+def summarize_persistent(buf: torch.Tensor, kind: str) -> dict:
+    """Cycle counters of the persistent MoE kernels (one record per CTA).  ``gate_up``: tiles, MMA thread total / waiting for a
+    free accumulator set / waiting for data, epilogue total / waiting for an accumulator.  ``down``: the same three of the MMA
+    thread, the scale-copy thread's total / waiting for a stage, k-steps, the producer's total / waiting for a free stage."""
+    m = buf.detach().cpu().view(-1, 16).double()
+    m = m[m[:, 0] > 0]
+    if not m.shape[0]:
+        return {"ctas": 0}
+    names = {"gate_up": ("tiles", "mma_cycles", "mma_wait_set", "mma_wait_data", "epilogue_cycles", "epilogue_wait_acc"),
+             "down": ("tiles", "mma_cycles", "mma_wait_set", "mma_wait_scales", "copier_cycles", "copier_wait_stage", "ksteps",
+                      "producer_cycles", "producer_wait_free")}[kind]
+    return {"ctas": int(m.shape[0]), **{n: round(float(m[:, i].mean()), 1) for i, n in enumerate(names)}}
+
+
+def summarize_seam(words, rows: int) -> dict:
+    """Phases of the bulk-copy seam fold (csrc/k_seam.cu FOLD_MARK; eight words per row of the last launch)."""
+    m = torch.as_tensor(list(words), dtype=torch.float64).view(rows, 8)
+
+    def d(hi: int, lo: int) -> float:
+        return round(float((m[:, hi] - m[:, lo]).mean()) / 1e3, 2)
+    return {"rows": rows, "kernel_span_us": round(float(m[:, 6].max() - m[:, 0].min()) / 1e3, 1), "block_life_us": d(6, 0),
+            "dependencies_us": d(1, 0), "row_landed_us": d(2, 1), "fold_us": d(3, 2), "sums_us": d(4, 3), "norm_quant_us": d(5, 4),
+            "copies_out_us": d(6, 5)}

@@ -21,6 +21,7 @@ def main() -> None:
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--layers", type=int, default=3)
     ap.add_argument("--steps", type=int, default=12, help="prompt chunks to run (the last one is the profiled / timed one)")
+    ap.add_argument("--persistent-counters", action="store_true", help="read moe_gate_up / moe_down marks as the persistent kernels' cycle counters")
     ap.add_argument("--marks", default="", help="kernels whose in-kernel phase marks are printed for the last step, e.g. moe_down,moe_gate_up")
     ap.add_argument("--tune", default="", help="measurement switches of the MoE launchers, key=value[,key=value]")
     args = ap.parse_args()
@@ -43,22 +44,33 @@ def main() -> None:
             eng.step(prompt[:64], [s] * 64, list(range(64)), head=False)
         for i in range(3):
             if i == 2:
-                eng.kernel_marks = {k: torch.zeros(16 * 16384, dtype=torch.int64, device="cuda") for k in filter(None, args.marks.split(","))}
+                eng.kernel_marks = {k: ([torch.zeros(16 * 4096, dtype=torch.int64, device="cuda") for _ in range(args.layers)] if k == "attn" else
+                                        torch.zeros(16 * 16384, dtype=torch.int64, device="cuda")) for k in filter(None, args.marks.split(","))}
                 torch.cuda.synchronize(); torch.cuda.profiler.start()
             eng.step(prompt[:rows], list(range(rows)), [64 + i] * rows)
     else:
         pos = 0
         for i in range(args.steps):
             if i == args.steps - 1:
-                eng.kernel_marks = {k: torch.zeros(16 * 16384, dtype=torch.int64, device="cuda") for k in filter(None, args.marks.split(","))}
+                eng.kernel_marks = {k: ([torch.zeros(16 * 4096, dtype=torch.int64, device="cuda") for _ in range(args.layers)] if k == "attn" else
+                                        torch.zeros(16 * 16384, dtype=torch.int64, device="cuda")) for k in filter(None, args.marks.split(","))}
                 torch.cuda.synchronize(); torch.cuda.profiler.start(); ev0.record()
             eng.step(prompt[pos:pos + rows], [0] * rows, list(range(pos, pos + rows)), head=False, sync=False); pos += rows
         ev1.record()
     torch.cuda.synchronize(); torch.cuda.profiler.stop()
     eng.check_status()
     for name, buf in getattr(eng, "kernel_marks", {}).items():
-        from sparkflash_b200.utils.kernel_marks import summarize
-        print(name, summarize(buf))
+        from sparkflash_b200.utils import kernel_marks as KM
+        if name == "attn":
+            for li, b in enumerate(buf):
+                print(name, "layer", li, KM.summarize_attention(b))
+        elif name == "seam":
+            words = N.seam_read_marks(rows)
+            print(name, KM.summarize_seam(words, rows) if words is not None else "no marks in this library")
+        elif name in ("moe_gate_up", "moe_down") and args.persistent_counters:
+            print(name, KM.summarize_persistent(buf, "gate_up" if name == "moe_gate_up" else "down"))
+        else:
+            print(name, KM.summarize(buf))
     if not args.decode:
         print(f"last chunk: {rows} rows at context {pos} in {ev0.elapsed_time(ev1):.3f} ms ({args.layers} layers)")
     print("ok")
