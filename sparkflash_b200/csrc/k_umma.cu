@@ -1745,6 +1745,202 @@ umma_down_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const __g
   if (warp == 1) tmem_dealloc(tmem, 256);
 }
 
+// ---- persistent grouped down projection, two column tiles per work item --------------------------------------------------------
+// The one-tile form above carries 8 KB of weights and 8 KB of activations per stage, so only half of its ring of stages is
+// HBM traffic.  Here a work item is a PAIR of neighbouring column tiles of one segment: both weight tiles share the stage's
+// activation tile (stage = 2 x 16 KB + 8 KB, five stages: 80 KB of weights in flight per SM instead of 56), each has its own
+// accumulator (two sets of two) and the fp32 tiles leave through a 16 KB staging buffer, 32 pair rows at a time.  Arithmetic,
+// order and output bits are those of the one-tile kernels.
+constexpr int PD2_STAGES = 5;
+struct UmmaDownPersist2Smem {
+  alignas(1024) uint8_t a[PD2_STAGES][2][UM_A_BYTES];
+  alignas(1024) uint8_t b[PD2_STAGES][PD_NP * UM_BK];
+  alignas(1024) float outf[32 * 128];              // 32 pair rows of one tile on their way out
+  alignas(128) uint8_t sfa[PD2_STAGES][2][512];
+  alignas(128) uint8_t sfb[PD2_STAGES][512];
+  alignas(8) uint64_t full[PD2_STAGES];
+  alignas(8) uint64_t empty[PD2_STAGES];
+  alignas(8) uint64_t sfready[PD2_STAGES];
+  alignas(8) uint64_t acc_full[2];
+  alignas(8) uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  volatile int fail;
+  volatile int ep_ok;
+};
+
+__global__ void __launch_bounds__(PD_THREADS, 1)
+umma_down_persistent2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
+                             const __grid_constant__ CUtensorMap tmapB, UmmaArgs a, int n_tile_pairs, int n_segs) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = UmmaDownPersist2Smem;
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int NP = PD_NP, ST = PD2_STAGES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nks = (a.inter + UM_BK - 1) / UM_BK;
+  const int total = n_tile_pairs * n_segs;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ST; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); mbar_init(&S.sfready[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], 1); }
+    S.fail = 0;
+    S.ep_ok = 1;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, 512);
+    tmem_relinquish();
+  }
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_wait();
+  const uint32_t tmem = S.tmem_base;
+  // accumulators: set b at columns 128 b (tile 0) and 128 b + 64 (tile 1); scale-factor slots per stage and operand from 256
+  const uint32_t t_sfa0 = tmem + 256, t_sfa1 = tmem + 288, t_sfb = tmem + 320;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
+        const int tp = t % n_tile_pairs, seg = t / n_tile_pairs;
+        const int e = a.seg_expert[seg];
+        if (e == -1) continue;                                   // an unused segment: no role touches a barrier for it
+        const CUtensorMap* ma;
+        int a_fp4, row0;
+        const uint8_t* sfa;
+        if (e >= 0) {
+          ma = &tmapA; a_fp4 = a.a_fp4;
+          row0 = e * a.d + tp * 256;
+          sfa = a.sfa + ((size_t)(row0 >> 7) * a.katoms_a) * 512;
+        } else {
+          ma = &tmapA2; a_fp4 = 0;
+          row0 = tp * 256;
+          sfa = a.sfa2 + ((size_t)(tp * 2) * a.katoms_a) * 512;
+        }
+        const uint8_t* sfa1 = sfa + (size_t)a.katoms_a * 512;      // the next 128 weight rows
+        const uint8_t* sfb = a.sfb + (size_t)seg * a.katoms_b * 512;
+        const uint32_t stage_tx = 2 * (a_fp4 ? UM_A_BYTES / 2 : UM_A_BYTES) + NP * UM_BK + 3 * 512;
+        for (int i = 0; i < nks; ++i, ++it) {
+          const int s = it % ST;
+          if (it >= ST && !mbar_wait(&S.empty[s], ((it / ST) - 1) & 1)) { S.fail = 1; break; }
+          mbar_expect_tx(&S.full[s], stage_tx);
+          tma_load_2d(S.a[s][0], ma, i * UM_BK, row0, &S.full[s]);
+          tma_load_2d(S.a[s][1], ma, i * UM_BK, row0 + 128, &S.full[s]);
+          tma_load_2d(S.b[s], &tmapB, i * UM_BK, seg * NP, &S.full[s]);
+          bulk_load(S.sfa[s][0], sfa + (size_t)i * 512, 512, &S.full[s]);
+          bulk_load(S.sfa[s][1], sfa1 + (size_t)i * 512, 512, &S.full[s]);
+          bulk_load(S.sfb[s], sfb + (size_t)i * 512, 512, &S.full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      uint32_t it = 0;
+      int lt = 0;
+      for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
+        const int e = a.seg_expert[t / n_tile_pairs];
+        if (e == -1) continue;
+        const uint32_t idesc = make_idesc((e >= 0 && a.a_fp4) ? 5 : 0, 0, 128, NP);
+        const int buf = lt & 1;
+        if (lt >= 2 && !mbar_wait(&S.acc_empty[buf], ((lt >> 1) - 1) & 1)) { S.fail = 3; break; }
+        tc_fence_after();
+        const uint32_t t_acc = tmem + (uint32_t)buf * 128;
+        bool ok = true;
+        for (int i = 0; i < nks; ++i, ++it) {
+          const int s = it % ST;
+          if (!mbar_wait(&S.sfready[s], (it / ST) & 1)) { S.fail = 2; ok = false; break; }
+          tc_fence_after();
+          const uint32_t sl = (uint32_t)s * 4;
+          const uint32_t a0_addr = smem_u32(S.a[s][0]), a1_addr = smem_u32(S.a[s][1]), b_addr = smem_u32(S.b[s]);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t id = idesc | ((uint32_t)kk << 29) | ((uint32_t)kk << 4);
+            const uint64_t bd = make_desc(b_addr + kk * 32, 1024, 16, 2);
+            tc_mma_bs(t_acc, make_desc(a0_addr + kk * 32, 1024, 16, 2), bd, id, t_sfa0 + sl, t_sfb + sl, (i > 0 || kk > 0) ? 1u : 0u);
+            tc_mma_bs(t_acc + NP, make_desc(a1_addr + kk * 32, 1024, 16, 2), bd, id, t_sfa1 + sl, t_sfb + sl, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&S.empty[s]);
+        }
+        tc_commit(&S.acc_full[buf]);      // arrives even after a failed wait, so the epilogue never waits for its limit
+        if (!ok) break;
+        ++lt;
+      }
+    }
+  } else if (warp == 6) {
+    if (elect_one()) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total && !S.fail; t += gridDim.x) {
+        if (a.seg_expert[t / n_tile_pairs] == -1) continue;
+        bool ok = true;
+        for (int i = 0; i < nks; ++i, ++it) {
+          const int s = it % ST;
+          if (!mbar_wait(&S.full[s], (it / ST) & 1)) { S.fail = 4; ok = false; break; }
+          tc_fence_after();
+          tc_cp_sf(t_sfa0 + (uint32_t)s * 4, make_desc(smem_u32(S.sfa[s][0]), 128, 0, 0));
+          tc_cp_sf(t_sfa1 + (uint32_t)s * 4, make_desc(smem_u32(S.sfa[s][1]), 128, 0, 0));
+          tc_cp_sf(t_sfb + (uint32_t)s * 4, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
+          tc_commit(&S.sfready[s]);
+        }
+        if (!ok) break;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    bool pending = false;
+    int lt = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x) {
+      const int tp = t % n_tile_pairs, seg = t / n_tile_pairs;
+      if (a.seg_expert[seg] == -1) continue;       // CTA-uniform (every thread reads the same word)
+      const int nv = a.seg_count[seg];
+      const int buf = lt & 1;
+      if (warp == 2) {
+        bool got = true;
+        if (lane == 0) got = mbar_wait(&S.acc_full[buf], (lt >> 1) & 1) && !S.fail;
+        got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+        if (lane == 0 && !got) S.ep_ok = 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!S.ep_ok) break;
+      tc_fence_after();
+      // four rounds: (tile 0, pairs 0..31), (tile 0, pairs 32..63), (tile 1, ...); a round whose pairs do not exist is skipped
+#pragma unroll 1
+      for (int h = 0; h < 4; ++h) {
+        const int j = h >> 1, p0 = (h & 1) * 32;
+        if (p0 >= nv) continue;                    // CTA-uniform
+        uint32_t v[2][16];
+        const uint32_t t_acc = tmem + (uint32_t)buf * 128 + (uint32_t)j * NP + p0;
+        tc_ld16(t_acc + ((uint32_t)(q * 32) << 16), v[0]);
+        tc_ld16(t_acc + ((uint32_t)(q * 32) << 16) + 16, v[1]);
+        tc_wait_ld();
+        if (pending) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the staging rows have been read out
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (p0 + ch * 16 + i < nv) S.outf[(ch * 16 + i) * 128 + q * 32 + lane] = __uint_as_float(v[ch][i]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        pending = false;
+        if (q == 0 && p0 + lane < nv) {
+          bulk_store(a.out_f + (int64_t)(seg * NP + p0 + lane) * a.out_stride + (tp * 2 + j) * 128, smem_u32(S.outf + lane * 128), 512);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          pending = true;
+        }
+      }
+      tc_fence_before();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) mbar_arrive(&S.acc_empty[buf]);       // every warp's TMEM reads of this set are done
+      ++lt;
+    }
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    if ((S.fail || !S.ep_ok) && lane == 0 && q == 0) status_set(a.status, ST_TIMEOUT, 90 + S.fail, blockIdx.x, lt);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1872,7 +2068,7 @@ static thread_local GatherSpec g_gather;
 
 // Tuning switches for measurements (0 = the shipped choice): [1] stages of the 64-pair down projection (2 shipped; 3, 4),
 // [2] stages of the 64-pair gate/up (2 = two CTAs per SM; 3, 5 = one CTA per SM), [3] / [4] segment-major grid order of the
-// grouped down / gate-up kernels, [5] persistent many-row dense kernel, [6] persistent 64-pair gate/up kernel, [7] persistent 64-pair down kernel (1 = never, 2 = whenever the shape allows).
+// grouped down / gate-up kernels, [5] persistent many-row dense kernel, [6] persistent 64-pair gate/up kernel, [7] persistent 64-pair down kernel (1 = never, 2 = whenever the shape allows, 3 = the same with one column tile per work item).
 static int g_tune[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 // Phase marks (um_mark) of the NEXT launch of a tensor-core GEMM of this library: cleared by that launch.
 static thread_local unsigned long long* g_marks = nullptr;
@@ -2207,10 +2403,19 @@ int sfb_umma_down_grouped(const void* tmapA, const void* tmapA2, const void* tma
   a.a_fp4 = 1; a.mode = UM_DOWN_GROUPED; a.inter = inter; a.d = d; a.out_f = out_f; a.out_stride = d; a.seg_expert = seg_expert;
   a.seg_count = seg_count; a.status = (Status*)status; a.splits = 1;
   // many (column tile, segment) pairs: one persistent CTA per SM ([7]: 0 this rule, 1 never, 2 whenever the shape allows)
-  if (seg_size == 64 && g_push.n == 0 && g_gather.n == 0 && g_tune[7] != 1 && (g_tune[7] == 2 || (d / 128) * segments >= 296)) {
+  if (seg_size == 64 && g_push.n == 0 && g_gather.n == 0 && g_tune[7] != 1 && (g_tune[7] >= 2 || (d / 128) * segments >= 296)) {
     apply_marks(a);
     static int sms = 0;
     if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+    if ((d / 128) % 2 == 0 && g_tune[7] != 3) {      // pairs of column tiles sharing the activation tile ([7] = 3: one tile per item)
+      const int total2 = (d / 256) * segments;
+      const size_t smem2 = sizeof(UmmaDownPersist2Smem) + 1024;
+      static bool done2 = false;
+      if (!done2) { cudaFuncSetAttribute(umma_down_persistent2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2); done2 = true; }
+      return (int)sfb_launch(umma_down_persistent2_kernel, dim3(total2 < sms ? total2 : sms), dim3(PD_THREADS), smem2, stream,
+                             *(const CUtensorMap*)tmapA, *(const CUtensorMap*)(tmapA2 ? tmapA2 : tmapA), *(const CUtensorMap*)tmapB, a,
+                             d / 256, segments);
+    }
     const int total = (d / 128) * segments;
     const size_t smem = sizeof(UmmaDownPersistSmem) + 1024;
     static bool done = false;

@@ -574,8 +574,8 @@ def test_wide_moe_segments_and_the_persistent_kernels_give_the_bits_of_16_pair_s
     prompt = _prompt(cfg, 60, seed=23)
     outs = []
     try:
-        for wide_rows, persistent in ((10 ** 6, 1), (4, 1), (4, 2)):
-            N.umma_tune(6, persistent)
+        for wide_rows, persistent in ((10 ** 6, 1), (4, 1), (4, 2), (4, 3)):     # 3: the down kernel with one column tile per work item
+            N.umma_tune(6, min(persistent, 2))
             N.umma_tune(7, persistent)
             e = E.Engine(dw, max_lanes=2, max_context=256, max_rows=64, arm="tc", use_graphs=False, keep_logits=True)
             e.GROUP_WIDE_ROWS = wide_rows
@@ -588,6 +588,7 @@ def test_wide_moe_segments_and_the_persistent_kernels_give_the_bits_of_16_pair_s
         N.umma_tune(7, 0)
     assert torch.equal(outs[0], outs[1])
     assert torch.equal(outs[1], outs[2])
+    assert torch.equal(outs[2], outs[3])
 
 
 def test_guard_bands_stay_intact_over_decode_and_chunk_steps_and_report_a_changed_band(tiny):
