@@ -1300,7 +1300,7 @@ constexpr int PG_THREADS = 288;
 
 __global__ void __launch_bounds__(PG_THREADS, 1)
 umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
-                              const __grid_constant__ CUtensorMap tmapB, UmmaArgs a, int n_tiles, int n_segs) {
+                              const __grid_constant__ CUtensorMap tmapB, UmmaArgs a, int n_tiles, int n_segs, int g_tune_dev_copier) {
   extern __shared__ uint8_t smem_raw[];
   using Smem = UmmaGateupPersistSmem;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -1392,10 +1392,14 @@ umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const _
         for (int i = 0; i < nks; ++i, ++it) {
           const int s = it % PG_STAGES;
           const long long w1 = SFB_MARKS_ON ? clock64() : 0;
-          if (!mbar_wait(&S.sfready[s][h], (it / PG_STAGES) & 1)) { S.fail = 2; ok = false; break; }
+          if (!mbar_wait(g_tune_dev_copier ? &S.sfready[s][h] : &S.full[s], (it / PG_STAGES) & 1)) { S.fail = 2; ok = false; break; }
           if (SFB_MARKS_ON) c_full += clock64() - w1;
           tc_fence_after();
           const uint32_t sl = (uint32_t)s * 4;
+          if (!g_tune_dev_copier) {      // this thread copies its own operands' scales: one hand-over less per stage
+            tc_cp_sf(t_sa + sl, make_desc(smem_u32(S.sfa[s][h]), 128, 0, 0));
+            tc_cp_sf(t_sb + sl, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
+          }
           const uint32_t w_addr = smem_u32(S.a[s][h]), b_addr = smem_u32(S.b[s]);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
@@ -1417,7 +1421,7 @@ umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const _
       }
     }
   } else if (warp == 7 || warp == 8) {
-    if (elect_one()) {
+    if (g_tune_dev_copier && elect_one()) {
       const int h = warp == 7 ? 0 : 1;
       const uint32_t t_sa = h ? t_sfu : t_sfg, t_sb = h ? t_sfb2 : t_sfb;
       uint32_t it = 0;
@@ -2369,7 +2373,7 @@ int sfb_umma_gate_up_grouped(const void* tmapA, const void* tmapA2, const void* 
     if (!done) { cudaFuncSetAttribute(umma_gateup_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
     const int total = (inter / 128) * segments;
     return (int)sfb_launch(umma_gateup_persistent_kernel, dim3(total < sms ? total : sms), dim3(PG_THREADS), smem, stream, *mA, *mA2,
-                           *(const CUtensorMap*)tmapB, a, inter / 128, segments);
+                           *(const CUtensorMap*)tmapB, a, inter / 128, segments, g_tune[2] == 7 ? 1 : 0);
   }
   if (seg_size == 64) {      // segments of up to 64 pairs: two 2-stage CTAs per SM (a stage holds 32 KiB of weights and 8 KiB of tokens)
     const size_t smem64 = sizeof(UmmaSmem<64, 2, 2>) + 1024;
