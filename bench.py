@@ -490,7 +490,7 @@ def main() -> None:
     ap.add_argument("--arm", default=os.environ.get("SFB_ARM", "tc"), choices=["tc", "cuda"])
     ap.add_argument("--long-context", default="131072,1048576", help="comma-separated cached context lengths: decode tok/s with the KV "
                     "caches of lane 0 filled with random entries up to that position ('' = skip)")
-    ap.add_argument("--prefill-chunk", type=int, default=1024, help="rows per prompt chunk")
+    ap.add_argument("--prefill-chunk", type=int, default=4096, help="rows per prompt chunk (the reference prefills 4,096-row chunks)")
     ap.add_argument("--no-mtp", action="store_true", help="skip the DSpark draft-path section")
     ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel section (2+ GPUs)")
     args = ap.parse_args()
