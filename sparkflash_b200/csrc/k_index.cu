@@ -210,20 +210,45 @@ __device__ __forceinline__ void select_run(const float* sc, const int* list, int
       const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
       for (int i = threadIdx.x; i < 256; i += SEL_THREADS) hist[i] = 0;
       __syncthreads();
-      for (int i = threadIdx.x; i < len; i += SEL_THREADS) {
-        uint32_t key = order_key(at(i));
-        if (key > NEG_INF_KEY && (key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+      // histogram of the pass's byte: the lanes of a warp that hit the same bin add once (scores cluster in a few bins of the
+      // top bytes, and one shared-memory atomic per lane serialised them)
+      for (int i0 = 0; i0 < len; i0 += SEL_THREADS) {
+        const int i = i0 + threadIdx.x;
+        uint32_t bin = 256u + (threadIdx.x & 31);      // no bin: a value of its own, matched by no other lane
+        if (i < len) {
+          const uint32_t key = order_key(at(i));
+          if (key > NEG_INF_KEY && (key & mask) == prefix) bin = (key >> shift) & 255u;
+        }
+        const uint32_t same = __match_any_sync(0xffffffffu, bin);
+        if (bin < 256u && (threadIdx.x & 31) == (uint32_t)(__ffs(same) - 1)) atomicAdd(&hist[bin], (uint32_t)__popc(same));
       }
       __syncthreads();
-      if (threadIdx.x == 0) {
-        uint32_t acc = 0;
-        int b = 255;
-        for (; b > 0; --b) {
-          if (acc + hist[b] >= need) break;
-          acc += hist[b];
+      // the bin in which the count from the top reaches `need`: the largest b with sum(hist[b..255]) >= need (bin 0 when only
+      // the whole histogram does).  One warp: lane l owns bins 8l..8l+7, a shuffle scan gives the count above them.
+      if (threadIdx.x < 32) {
+        const int l = threadIdx.x;
+        uint32_t h[8], own = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { h[j] = hist[8 * l + j]; own += h[j]; }
+        uint32_t incl = own;                        // own bins and every bin above them
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t v = __shfl_down_sync(0xffffffffu, incl, o);
+          if (l + o < 32) incl += v;
         }
-        s_prefix = prefix | ((uint32_t)b << shift);
-        s_need = need - acc;
+        const uint32_t above = incl - own;
+        if (above < need && (incl >= need || l == 0)) {      // exactly one lane: the crossing lies in its bins
+          uint32_t acc = above;
+          int j = 7;
+          for (; j > 0; --j) {
+            if (acc + h[j] >= need) break;
+            acc += h[j];
+          }
+          if (l > 0 || acc + h[j] >= need || j == 0) {
+            s_prefix = prefix | ((uint32_t)(8 * l + j) << shift);
+            s_need = need - acc;
+          }
+        }
       }
       __syncthreads();
       prefix = s_prefix; need = s_need;
