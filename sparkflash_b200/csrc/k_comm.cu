@@ -46,6 +46,103 @@ __global__ void __launch_bounds__(256) push_rows_kernel(PushArgs a) {
   }
 }
 
+// ---- two-shot all-reduce of a many-row partial: reduce-scatter, fold on the owner, all-gather -----------------------------------
+// Shot 1: rank p sends rows [j rs, (j + 1) rs) of its partial to rows [0, rs) of slot p on rank j, then raises its flag on
+// every rank.  Shot 2 (fold_push_rs_kernel): rank j waits for the W flags, adds the W slots' rows in rank order (fp32, one
+// bf16 rounding: the sum a one-shot consumer forms), stores the result to rows [rs, 2 rs) of slot j on every rank and raises
+// its flag to the second epoch.  A consumer then finds row t in slot t / rs at row rs + t % rs.  Each rank sends
+// 2 (W - 1) / W of a partial instead of W - 1 partials.
+struct PushRsArgs {
+  const uint4* src;           // [n, src_row16] this rank's partial
+  uint4* dst[8];              // this rank's slot on every rank
+  uint32_t* flag[8];          // this rank's flag on every rank
+  int W, n, rs_rows, row16, src_row16;
+  const uint32_t* epoch_ptr;
+  uint32_t epoch_add;
+  unsigned int* done;         // zero between launches
+};
+
+__global__ void __launch_bounds__(256) push_rows_rs_kernel(PushRsArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int is_last;
+  const int64_t total = (int64_t)a.n * a.row16;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int row = (int)(i / a.row16), c = (int)(i - (int64_t)row * a.row16);
+    const int j = row / a.rs_rows;
+    a.dst[j][(int64_t)(row - j * a.rs_rows) * a.row16 + c] = a.src[(int64_t)row * a.src_row16 + c];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(a.done, 1u);
+    is_last = prev == gridDim.x - 1;
+    if (is_last) *a.done = 0;
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x < a.W) {
+    __threadfence_system();
+    st_release_sys(a.flag[threadIdx.x], *a.epoch_ptr + a.epoch_add);
+  }
+}
+
+struct FoldPushArgs {
+  const uint4* slot[8];       // the W slots of this rank's own buffer
+  const uint32_t* flag[8];    // their arrival flags (shot 1)
+  uint4* dst[8];              // this rank's slot on every rank
+  uint32_t* oflag[8];         // this rank's flag on every rank
+  int W, rows, rs_rows, row16;
+  const uint32_t* epoch_ptr;
+  uint32_t epoch_wait, epoch_raise;
+  uint64_t wait_ns;
+  unsigned int* done;
+  Status* status;
+};
+
+__global__ void __launch_bounds__(256) fold_push_rs_kernel(FoldPushArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int is_last, ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < a.W && !wait_flag_ge(a.flag[threadIdx.x], *a.epoch_ptr + a.epoch_wait, a.wait_ns)) {
+    status_set(a.status, ST_TIMEOUT, 31, threadIdx.x, (int)(*a.epoch_ptr + a.epoch_wait));
+    ok = 0;
+  }
+  __syncthreads();
+  const int64_t total = (int64_t)a.rows * a.row16;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; ok && i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < a.W; ++r) {
+      const uint4 v = a.slot[r][i];
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p2[e]);
+        acc[2 * e] += f.x; acc[2 * e + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+    const int64_t at = (int64_t)a.rs_rows * a.row16 + i;      // rows [rs, 2 rs) of the slot
+    for (int r = 0; r < a.W; ++r) a.dst[r][at] = o;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(a.done, 1u);
+    is_last = prev == gridDim.x - 1;
+    if (is_last) *a.done = 0;
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x < a.W) {      // raised even after a timeout: the peers go on and the host reads the status word
+    __threadfence_system();
+    st_release_sys(a.oflag[threadIdx.x], *a.epoch_ptr + a.epoch_raise);
+  }
+}
+
 __global__ void epoch_bump_kernel(uint32_t* epoch, uint32_t add) { *epoch += add; }
 
 // Test / emulation helper: wait (bounded) until every flag reaches the epoch; records a timeout in status.
@@ -225,6 +322,39 @@ int sfb_fold_slots(const void* const* slots, const void* const* flags, int W, in
   a.residual = (const __nv_bfloat16*)residual; a.norm_w = (const float*)norm_w; a.eps = eps; a.out_sum = (__nv_bfloat16*)out_sum;
   a.out = (__nv_bfloat16*)out; a.out_q = (uint8_t*)out_q; a.out_atom = (uint8_t*)out_atom; a.status = (Status*)status;
   return (int)sfb_launch(fold_slots_kernel, dim3(n), dim3(128), 0, stream, a);
+}
+
+// shot 1 of the two-shot all-reduce: dst / flags = this rank's slot / flag on every rank; row_bytes a multiple of 16
+int sfb_push_rows_rs(const void* src, int64_t src_row_bytes, const void* const* dst_ptrs, const void* const* flag_ptrs, int W, int n,
+                     int rs_rows, int64_t row_bytes, const void* epoch_ptr, uint32_t epoch_add, void* done, cudaStream_t stream) {
+  if (W < 1 || W > 8 || n < 1 || rs_rows < 1 || (int64_t)rs_rows * W < n || (row_bytes & 15) || (src_row_bytes & 15)) return (int)cudaErrorInvalidValue;
+  PushRsArgs a{};
+  a.src = (const uint4*)src;
+  for (int r = 0; r < W; ++r) { a.dst[r] = (uint4*)dst_ptrs[r]; a.flag[r] = (uint32_t*)flag_ptrs[r]; }
+  a.W = W; a.n = n; a.rs_rows = rs_rows; a.row16 = (int)(row_bytes / 16); a.src_row16 = (int)(src_row_bytes / 16);
+  a.epoch_ptr = (const uint32_t*)epoch_ptr; a.epoch_add = epoch_add; a.done = (unsigned int*)done;
+  int64_t blocks = ((int64_t)n * a.row16 + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  return (int)sfb_launch(push_rows_rs_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, a);
+}
+
+// shot 2: slots / flags = the W slots of this rank's buffer and their flags; dst / oflags = this rank's slot / flag on every rank
+int sfb_fold_push_rs(const void* const* slots, const void* const* flags, const void* const* dst_ptrs, const void* const* oflag_ptrs, int W,
+                     int rows, int rs_rows, int64_t row_bytes, const void* epoch_ptr, uint32_t epoch_wait, uint32_t epoch_raise,
+                     uint64_t wait_ns, void* done, void* status, cudaStream_t stream) {
+  if (W < 1 || W > 8 || rows < 0 || rows > rs_rows || (row_bytes & 15)) return (int)cudaErrorInvalidValue;
+  FoldPushArgs a{};
+  for (int r = 0; r < W; ++r) {
+    a.slot[r] = (const uint4*)slots[r]; a.flag[r] = (const uint32_t*)flags[r];
+    a.dst[r] = (uint4*)dst_ptrs[r]; a.oflag[r] = (uint32_t*)oflag_ptrs[r];
+  }
+  a.W = W; a.rows = rows; a.rs_rows = rs_rows; a.row16 = (int)(row_bytes / 16);
+  a.epoch_ptr = (const uint32_t*)epoch_ptr; a.epoch_wait = epoch_wait; a.epoch_raise = epoch_raise;
+  a.wait_ns = wait_ns ? wait_ns : 2000000000ull; a.done = (unsigned int*)done; a.status = (Status*)status;
+  int64_t blocks = ((int64_t)rows * a.row16 + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  return (int)sfb_launch(fold_push_rs_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, a);
 }
 
 int sfb_epoch_bump(void* epoch, uint32_t add, cudaStream_t stream) {

@@ -62,6 +62,8 @@ struct FoldArgs {
   uint64_t wait_ns;              // time limit of the flag wait
   int n, hc, d;
   float norm_eps;
+  int rs_rows;                   // > 0: the partials were reduced by a two-shot exchange - row t has ONE part, in y[t / rs_rows] at
+                                 //      row rs_rows + t % rs_rows (the W flags are still waited for); many-row kernels only
 };
 
 // HC > 0 fixes the number of residual copies at compile time (the coefficient arrays then live in registers; indexed with a
@@ -237,8 +239,10 @@ __global__ void __launch_bounds__(FOLDR_THREADS) seam_fold_rows_kernel(FoldArgs 
       }
       if (a.has_post) {
         float y[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < a.W; ++r) {
-          const uint2 u = *reinterpret_cast<const uint2*>(a.y[r] + (size_t)row * d + col);
+        const int nparts = a.rs_rows > 0 ? 1 : a.W;
+        for (int r = 0; r < nparts; ++r) {
+          const __nv_bfloat16* yr = a.rs_rows > 0 ? a.y[row / a.rs_rows] + (size_t)(a.rs_rows + row % a.rs_rows) * d : a.y[r] + (size_t)row * d;
+          const uint2 u = *reinterpret_cast<const uint2*>(yr + col);
           const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&u);
           const float2 f0 = __bfloat1622float2(y2[0]), f1 = __bfloat1622float2(y2[1]);
           y[0] += f0.x; y[1] += f0.y; y[2] += f1.x; y[3] += f1.y;
@@ -370,7 +374,7 @@ __global__ void __launch_bounds__(FOLDR_THREADS) seam_fold_rows_bulk_kernel(Fold
   FOLD_MARK(0);
   const int row = blockIdx.x;
   const int hc = HC > 0 ? HC : a.hc, d = a.d;
-  const int W = a.has_post ? a.W : 0;
+  const int W = a.has_post ? (a.rs_rows > 0 ? 1 : a.W) : 0;      // parts of the row in shared memory
   const int KB = d / 32;
   __nv_bfloat16* sh_h = reinterpret_cast<__nv_bfloat16*>(fold_sm);
   __nv_bfloat16* sh_y = sh_h + (size_t)hc * d;
@@ -396,7 +400,8 @@ __global__ void __launch_bounds__(FOLDR_THREADS) seam_fold_rows_bulk_kernel(Fold
     asm volatile("fence.proxy.async;" ::: "memory");      // the partials were published to the generic proxy; the copies read them
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fold_smem_u32(bar)), "r"((uint32_t)((hc + W) * d * 2)) : "memory");
     fold_bulk_load(sh_h, a.h + (size_t)row * hc * d, (uint32_t)(hc * d * 2), bar);
-    for (int r = 0; r < W; ++r) fold_bulk_load(sh_y + (size_t)r * d, a.y[r] + (size_t)row * d, (uint32_t)(d * 2), bar);
+    if (a.rs_rows > 0 && W) fold_bulk_load(sh_y, a.y[row / a.rs_rows] + (size_t)(a.rs_rows + row % a.rs_rows) * d, (uint32_t)(d * 2), bar);
+    else for (int r = 0; r < W; ++r) fold_bulk_load(sh_y + (size_t)r * d, a.y[r] + (size_t)row * d, (uint32_t)(d * 2), bar);
   }
   float post[MAX_HC], comb[MAX_HC * MAX_HC], ap[MAX_HC];
 #pragma unroll
@@ -750,9 +755,10 @@ int sfb_seam_fold(void* h, const void* const* y_ptrs, const void* const* flag_pt
                   uint32_t epoch_add, uint64_t wait_ns, int W,
                   int has_post, const float* coef_prev, const float* a_pre, int a_stride, void* ysum,
                   const float* norm_w, void* xn, void* xq, void* xs, void* xs_atom, int atom_mode, void* status,
-                  int n, int hc, int d, float norm_eps, float* hss, cudaStream_t stream) {
+                  int n, int hc, int d, float norm_eps, float* hss, int rs_rows, cudaStream_t stream) {
   if (hc > MAX_HC || W > 8 || (hc & (hc - 1)) || d % (32 * FOLD_CLUSTER) || d > FOLD_CLUSTER * FOLD_THREADS * FOLD_MAX_IT)
     return (int)cudaErrorInvalidValue;
+  if (rs_rows > 0 && (!has_post || n <= 128 || d % 128 || (int64_t)rs_rows * W < n)) return (int)cudaErrorInvalidValue;
   FoldArgs a{};
   a.h = (__nv_bfloat16*)h;
   for (int r = 0; r < 8; ++r) {
@@ -762,14 +768,14 @@ int sfb_seam_fold(void* h, const void* const* y_ptrs, const void* const* flag_pt
   a.epoch_ptr = (const uint32_t*)epoch_ptr; a.epoch_add = epoch_add; a.wait_ns = wait_ns ? wait_ns : 2000000000ull; a.W = W; a.has_post = has_post; a.coef_prev = coef_prev; a.a_pre = a_pre; a.a_stride = a_stride;
   a.ysum = (__nv_bfloat16*)ysum; a.norm_w = norm_w; a.xn = (__nv_bfloat16*)xn; a.xq = (uint8_t*)xq;
   a.xs = (uint8_t*)xs; a.xs_atom = (uint8_t*)xs_atom; a.atom_mode = atom_mode; a.status = (Status*)status;
-  a.n = n; a.hc = hc; a.d = d; a.norm_eps = norm_eps; a.hss = hss;
+  a.n = n; a.hc = hc; a.d = d; a.norm_eps = norm_eps; a.hss = hss; a.rs_rows = rs_rows;
   if (n > 128 && d % 128 == 0 && d <= FOLDR_THREADS * 4 * FOLDR_MAX_IT) {     // many rows: one block per row
     // rows through bulk copies when every row of every buffer starts on a 16-byte boundary and a row's buffers fit in
     // shared memory (g_seam_tune: 1 = never)
-    const int Wp = has_post ? W : 0;
+    const int Wp = has_post ? (rs_rows > 0 ? 1 : W) : 0;      // parts of a row held in shared memory
     const size_t smem = (size_t)(hc + Wp + 1) * d * 2 + d + ((d / 32 + 15) & ~15) + 16;
     uintptr_t bits = (uintptr_t)h | (uintptr_t)ysum | (uintptr_t)xn | (uintptr_t)xq | (uintptr_t)xs;
-    for (int r = 0; r < Wp; ++r) bits |= (uintptr_t)y_ptrs[r];
+    for (int r = 0; r < (has_post ? W : 0); ++r) bits |= (uintptr_t)y_ptrs[r];
     if (g_seam_tune != 1 && d % 512 == 0 && (bits & 15) == 0 && smem <= 200 * 1024 && (xq == nullptr || xs != nullptr)) {
       static bool attr = false;
       if (!attr) {

@@ -12,6 +12,7 @@ tp4_graph.rs (graph replay), docs/design.md:47-72.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -340,9 +341,10 @@ class Engine:
         if self._coef_event is not None:
             main.wait_event(self._coef_event)   # coefficients of seam k-1 are ready
             self._coef_event = None
-        flags, epoch_ptr, epoch_add = None, None, 0
-        if isinstance(y_parts, tuple):      # fused collective: (slots, flags, epoch_add)
-            y_parts, flags, epoch_add = y_parts
+        flags, epoch_ptr, epoch_add, rs_rows = None, None, 0, 0
+        if isinstance(y_parts, tuple):      # fused collective: (slots, flags, epoch_add[, rows per owner of a two-shot exchange])
+            rs_rows = y_parts[3] if len(y_parts) > 3 else 0
+            y_parts, flags, epoch_add = y_parts[:3]
             epoch_ptr = self.comm.epoch_ptr
         bulk_coef = n > 128 and self.tcb is not None and fn is not None and engram_j is None
         N.seam_fold(self.h, y_parts, None if first else prev, self.w.onehot if first else prev,
@@ -351,7 +353,7 @@ class Engine:
                     flags=flags, epoch_ptr=epoch_ptr, epoch_add=epoch_add,
                     wait_ns=self.comm.wait_ns if flags is not None else 0,
                     xs_atom=None if (self.tcl is None or not quant) else (self.tcb.xs_atom if atoms == 0 else self.tcb.xs_atom_tok),
-                    atom_mode=atoms, hss=self._coef_bulk()["hss"] if bulk_coef else None)
+                    atom_mode=atoms, hss=self._coef_bulk()["hss"] if bulk_coef else None, rs_rows=rs_rows)
         self._k()
         if engram_j is not None:
             # the memory writes into the block's input after the previous block's output has been folded in: apply it, then
@@ -795,9 +797,29 @@ class Engine:
     def _fused(self) -> bool:
         return self.world > 1 and self.comm is not None and getattr(self.comm, "name", "") == "fused"
 
+    # Many-row partials cross the links in two shots (reduce-scatter, fold on the owner, all-gather of the folded rows) from
+    # this many rows and ranks on: a rank then sends 2 (W - 1) / W of its partial instead of W - 1 copies.  Reference
+    # behaviour: tp4_forward.rs:13196-13231 (two-shot exchange above 16 rows).
+    TWO_SHOT_ROWS = int(os.environ.get("SFB_TWO_SHOT_ROWS", "512"))
+    TWO_SHOT_WORLD = int(os.environ.get("SFB_TWO_SHOT_WORLD", "4"))
+
+    def _two_shot(self, n: int) -> bool:
+        return (self._fused() and n >= self.TWO_SHOT_ROWS and self.world >= self.TWO_SHOT_WORLD
+                and 2 * ((n + self.world - 1) // self.world) <= self.max_rows)
+
+    def _second_shot(self, parts, n: int):
+        """Shot 2 of a two-shot exchange started by ``_reduce_parts`` (anything else passes through): fold the rows this rank
+        owns and publish them; the seam then reads one part per row."""
+        if not (isinstance(parts, tuple) and parts and parts[0] == "rs"):
+            return parts
+        _, kind, sub = parts
+        self.comm.fold_push_rs(n, kind, sub + 1, sub + 2, status=self.status); self._k()
+        slots, flags = self.comm.slots(kind)
+        return (slots, flags, sub + 2, self.comm.rs_rows(n, self.world))
+
     def _arm_push(self, kind: int, sub: int) -> bool:
         """Fused arm: make the next tcgen05 GEMM launch push its output to every rank (sublayer index ``sub``)."""
-        if not self._fused():
+        if not self._fused() or self._two_shot(self.__dict__.get("_step_rows", 0)):
             return False
         self.comm.arm_umma_push(kind, sub + 1)
         return True
@@ -812,6 +834,9 @@ class Engine:
             self.ledger.count("collective")
         if not self._fused():
             return self.comm.parts(y, n)
+        if not pushed and self._two_shot(n):
+            self.comm.push_rs(y, n, kind, sub + 1); self._k()
+            return ("rs", kind, sub)
         if not pushed:
             self.comm.push(y, n, kind, sub + 1); self._k()
         slots, flags = self.comm.slots(kind)
@@ -826,6 +851,8 @@ class Engine:
         that a lockstep driver can interleave several ranks living in one process; a normal run just exhausts it."""
         cfg, w = self.cfg, self.w
         fused = self._fused()
+        self._step_rows = n
+        two_shot = self._two_shot(n)
         if fused:
             self.comm.begin_step(); self._k()
         N.embed(w.embed, self.tokens, self.h, n, cfg.hc_mult, cfg.hidden_size, cfg.vocab_size, self.status); self._k()
@@ -859,6 +886,9 @@ class Engine:
             self._dbg(f"L{l}.sel", self.sel, n); self._dbg(f"L{l}.sel_cnt", self.sel_cnt, n)
             parts = self._reduce_parts(self.y_attn, n, 0, 2 * l, self._pushed)
             yield ("attn", l)
+            if two_shot:
+                parts = self._second_shot(parts, n)
+                yield ("attn2", l)
             self._seam(n, k, parts, L.hc_ffn_fn, L.hc_ffn_base, L.hc_ffn_scale, L.ffn_norm, atoms=1); k += 1
             self._dbg(f"L{l}.ffn_in", self.xn, n)
             self._prefetch(n, (L.s13, L.s2))
@@ -868,6 +898,9 @@ class Engine:
             self._dbg(f"L{l}.route_ids", self.ids, n); self._dbg(f"L{l}.route_w", self.wts, n)
             y_prev = self._reduce_parts(self.y_ffn, n, 1, 2 * l + 1, self._pushed)
             yield ("ffn", l)
+            if two_shot:
+                y_prev = self._second_shot(y_prev, n)
+                yield ("ffn2", l)
         if self.drafter:
             self._dspark_seed(n)
         if stop_after is not None:

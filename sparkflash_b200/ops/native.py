@@ -74,7 +74,7 @@ def coef_stride(hc: int) -> int:
 
 
 def seam_fold(h, y_parts, coef_prev, a_pre, a_stride, norm_w, xn, xq, xs, n, hc, d, norm_eps, ysum=None,
-              flags=None, epoch_ptr=None, epoch_add=0, wait_ns=0, status=None, xs_atom=None, atom_mode=0, hss=None):
+              flags=None, epoch_ptr=None, epoch_add=0, wait_ns=0, status=None, xs_atom=None, atom_mode=0, hss=None, rs_rows=0):
     """Critical-path half of an mHC seam (see csrc/k_seam.cu).  ``y_parts``: list of W partial outputs
     (tensors or raw device addresses) or None for the first seam of a forward."""
     has_post = y_parts is not None
@@ -85,7 +85,7 @@ def seam_fold(h, y_parts, coef_prev, a_pre, a_stride, norm_w, xn, xq, xs, n, hc,
     code = lib().sfb_seam_fold(_p(h), yp, fp, ep, c_uint32(epoch_add), c_uint64(wait_ns), c_int(W), c_int(1 if has_post else 0), _p(coef_prev),
                                _p(a_pre), c_int(a_stride), _p(ysum), _p(norm_w), _p(xn), _p(xq), _p(xs), _p(xs_atom),
                                c_int(atom_mode), _p(status), c_int(n), c_int(hc), c_int(d), c_float(norm_eps), _p(hss),
-                               _stream())
+                               c_int(rs_rows), _stream())
     _check(code, "seam_fold")
 
 

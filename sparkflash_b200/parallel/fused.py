@@ -12,6 +12,8 @@ NVSwitch).  Producer kernels (the tcgen05 GEMM epilogue of ``wo_b`` and of the M
 generic ``push_rows`` kernel) store this rank's partial into slot ``rank`` of *every* rank's ``y`` and then
 raise flag ``rank`` everywhere; the mHC seam on each rank waits - with a time limit - on its own flags and
 folds its own W slots in rank order.  That is the all-reduce: one kernel boundary, no separate collective.
+Many-row partials can go in two shots instead (``push_rs`` / ``fold_push_rs``): reduce-scatter into rows [0, rs) of the
+slots, fold on the owner, all-gather into rows [rs, 2 rs); a rank then sends 2 (W - 1) / W of a partial, not W - 1.
 
 Reference behaviour replaced: crates/sparkflash-comm/src/device_reduce.rs:693-1082 (RunReduce),
 rdma/write_exchange.rs, tp4_forward.rs:13234-13249 (one-shot exchange + opt_sum_ranks_bf16).
@@ -162,6 +164,33 @@ class FusedComm:
         N._check(_L().sfb_push_rows(N._p(y), N._ptr_array(outs), N._ptr_array(flags), c_int(self.world),
                                     c_int64(nbytes), c_void_p(self.epoch_ptr), c_uint32(epoch_add),
                                     c_void_p(self.done_ptr), N._stream()), "push_rows")
+
+    # ---- two-shot all-reduce of a many-row partial (reduce-scatter, fold on the owner, all-gather) --------------------
+    @staticmethod
+    def rs_rows(n: int, world: int) -> int:
+        """Rows a rank owns in the two-shot exchange of an n-row partial."""
+        return (n + world - 1) // world
+
+    def push_rs(self, y: torch.Tensor, n: int, kind: int, epoch_add: int) -> None:
+        """Shot 1: rows [j rs, (j + 1) rs) of this rank's partial go to rows [0, rs) of this rank's slot on rank j."""
+        outs, flags = self.push_targets(kind)
+        row_bytes = self.layout.d * 2
+        N._check(_L().sfb_push_rows_rs(N._p(y), c_int64(y.stride(0) * y.element_size()), N._ptr_array(outs), N._ptr_array(flags),
+                                       c_int(self.world), c_int(n), c_int(self.rs_rows(n, self.world)), c_int64(row_bytes),
+                                       c_void_p(self.epoch_ptr), c_uint32(epoch_add), c_void_p(self.done_ptr), N._stream()),
+                 "push_rows_rs")
+
+    def fold_push_rs(self, n: int, kind: int, epoch_wait: int, epoch_raise: int, status=None) -> None:
+        """Shot 2: this rank adds the W slots' rows it owns (rank order, fp32, one bf16 rounding) and stores the result to rows
+        [rs, 2 rs) of its slot on every rank; the flags go to the second epoch."""
+        rs = self.rs_rows(n, self.world)
+        rows = max(0, min(rs, n - self.rank * rs))
+        slots, flags = self.slots(kind)
+        outs, oflags = self.push_targets(kind)
+        N._check(_L().sfb_fold_push_rs(N._ptr_array(slots), N._ptr_array(flags), N._ptr_array(outs), N._ptr_array(oflags),
+                                       c_int(self.world), c_int(rows), c_int(rs), c_int64(self.layout.d * 2), c_void_p(self.epoch_ptr),
+                                       c_uint32(epoch_wait), c_uint32(epoch_raise), c_uint64(self.wait_ns), c_void_p(self.done_ptr),
+                                       N._p(status), N._stream()), "fold_push_rs")
 
     def push_best(self, best_val: torch.Tensor, best_id: torch.Tensor, n: int, epoch_add: int) -> None:
         """Publish this rank's sampler winners to every rank (values then ids; the flag follows the ids)."""

@@ -537,6 +537,115 @@ def test_virtual_tensor_parallel_ranks_take_a_128_row_step(tiny):
     assert big_last[-16:] == small_last and big_toks == small_toks
 
 
+def test_two_shot_exchange_kernels_sum_in_rank_order():
+    """Reduce-scatter push, fold on the owner and all-gather push over four lockstep ranks: every rank ends up with, for
+    row t, the bf16 rounding of the fp32 sum of the four partials in rank order, in slot t / rs at row rs + t % rs."""
+    from sparkflash_b200.parallel.fused import FusedComm
+    W, R, d, n = 4, 256, 512, 203
+    comms = FusedComm.local_group(W, R, d)
+    g = torch.Generator().manual_seed(5)
+    parts = [(torch.randn(R, d, generator=g) * 0.7).to(torch.bfloat16).cuda() for _ in range(W)]
+    status = torch.zeros(8, dtype=torch.int32, device="cuda")
+
+    class _E:       # what FusedComm reads of an engine
+        class w:
+            layers = [0, 0]
+    for c in comms:
+        c.attach_local(_E)
+        c.begin_step()
+    for r, c in enumerate(comms):
+        c.push_rs(parts[r], n, 1, 3)
+    for c in comms:
+        c.fold_push_rs(n, 1, 3, 4, status=status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    acc = torch.zeros(n, d)
+    for r in range(W):
+        acc += parts[r][:n].float().cpu()
+    want = acc.to(torch.bfloat16)
+    rs = FusedComm.rs_rows(n, W)
+
+    class _Raw:      # a device address as a byte tensor
+        def __init__(self, ptr, nbytes):
+            self.__cuda_array_interface__ = {"shape": (nbytes,), "strides": None, "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+    def raw(ptr, nbytes, dtype):
+        return torch.as_tensor(_Raw(ptr, nbytes), device="cuda").view(dtype)
+    for c in comms:
+        lay = c.layout
+        got = torch.empty(n, d, dtype=torch.bfloat16)
+        for j in range(W):
+            lo, hi = j * rs, min(n, (j + 1) * rs)
+            if hi > lo:
+                slot = raw(lay.y(c.base, 1, j), R * d * 2, torch.bfloat16).view(R, d)
+                got[lo:hi] = slot[rs:rs + hi - lo].cpu()
+        assert torch.equal(got, want)
+        flags = raw(lay.flag(c.base, 1, 0), 4 * W, torch.int32).cpu()
+        epoch = int(raw(c.epoch_ptr, 4, torch.int32).cpu()[0])
+        assert flags.tolist() == [epoch + 4] * W
+    for c in comms:
+        c.close()
+
+
+def test_two_shot_seams_give_the_bits_of_the_one_shot_push(tiny):
+    """A many-row step whose partial outputs cross in two shots (reduce-scatter, fold on the owner, all-gather) leaves the same
+    residual stream, caches and sampled tokens as the one-shot push: the owner's sum is the sum every rank formed before."""
+    from sparkflash_b200.models.deepseek_v41 import engine as E, prepare as P
+    from sparkflash_b200.parallel.fused import FusedComm
+    cfg, ck, w, orc, dw = tiny
+    W, n = 2, 160
+    prompt = _prompt(cfg, n, seed=29)
+    saved = (E.Engine.TWO_SHOT_ROWS, E.Engine.TWO_SHOT_WORLD)
+
+    def run(two_shot: bool):
+        E.Engine.TWO_SHOT_ROWS, E.Engine.TWO_SHOT_WORLD = (129 if two_shot else 10 ** 9), 2
+        comms = FusedComm.local_group(W, n, cfg.hidden_size)
+        engs = []
+        for r in range(W):
+            e = E.Engine(P.prepare_from_checkpoint(ck, cfg, r, W), max_lanes=1, max_context=256, max_rows=n,
+                         comm=comms[r], use_graphs=False, arm="tc")
+            comms[r].attach_local(e)
+            engs.append(e)
+        assert engs[0]._two_shot(n) == two_shot and not engs[0]._two_shot(1)
+
+        def step(tokens, positions):
+            m = len(tokens)
+            for e in engs:
+                e.tokens[:m] = torch.tensor(tokens, dtype=torch.int32, device=e.dev)
+                e.row_lane[:m] = 0
+                e.row_pos[:m] = torch.tensor(positions, dtype=torch.int32, device=e.dev)
+                e.temp[:m] = 0.0; e.seed[:m] = 0
+            gens = [e._forward_gen(m, 1024) for e in engs]
+            live = True
+            while live:
+                live = False
+                for gg in gens:
+                    try:
+                        next(gg); live = True
+                    except StopIteration:
+                        pass
+            torch.cuda.synchronize()
+            for e in engs:
+                e.check_status()
+            return [e.tokens_out[:m].clone() for e in engs], [e.h[:m].clone() for e in engs]
+        toks, hs = step(prompt, list(range(n)))
+        tail = []
+        tok = int(toks[0][-1])
+        for i in range(4):
+            t2, _ = step([tok], [n + i])
+            tok = int(t2[0][0]); tail.append(tok)
+        return toks, hs, tail
+    try:
+        one = run(False)
+        two = run(True)
+    finally:
+        E.Engine.TWO_SHOT_ROWS, E.Engine.TWO_SHOT_WORLD = saved
+    for r in range(W):
+        assert torch.equal(one[1][r], two[1][r])        # residual copies after the last seam
+        assert torch.equal(one[0][r], two[0][r])        # sampled tokens of every row
+    assert one[2] == two[2]
+
+
 def test_step_ledger_and_segment_identity(tiny):
     """The engine counts launches, collectives and host<->device crossings per step against a budget, and a captured
     graph is tied to the launch list it was recorded from."""
