@@ -207,7 +207,8 @@ class EngineConfig:
     decoder_skip: bool = True
     speculation: bool = True
     spec_depth: int = 5
-    two_shot_rows: int = 16
+    two_shot_rows: int = 512       # many-row partials cross the links in two shots from this many rows ...
+    two_shot_world: int = 8        # ... and this many ranks on
     stall_secs: float = 120.0
     max_context: int = 1048576
     cuda_graphs: bool = True
@@ -243,6 +244,7 @@ ENV_OVERRIDES: dict[str, tuple[str, Any]] = {
     "SFB_SPECULATION": ("engine.speculation", _b),
     "SFB_SPEC_DEPTH": ("engine.spec_depth", int),
     "SFB_TWO_SHOT_ROWS": ("engine.two_shot_rows", int),
+    "SFB_TWO_SHOT_WORLD": ("engine.two_shot_world", int),
     "SFB_STALL_SECS": ("engine.stall_secs", float),
     "SFB_MAX_CONTEXT": ("engine.max_context", int),
     "SFB_CUDA_GRAPHS": ("engine.cuda_graphs", _b),

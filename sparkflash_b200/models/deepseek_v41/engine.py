@@ -19,6 +19,7 @@ import torch
 
 from ...config import ModelConfig
 from ...ops import native as N
+from ...ops import plan as _plan
 from .prepare import DeviceWeights, LayerW
 
 
@@ -801,8 +802,8 @@ class Engine:
     # this many rows and ranks on: a rank then sends 2 (W - 1) / W of its partial instead of W - 1 copies (1.75 against 7 at
     # eight ranks; at two and four ranks the two extra kernels cost more than the links save).  Reference
     # behaviour: tp4_forward.rs:13196-13231 (two-shot exchange above 16 rows).
-    TWO_SHOT_ROWS = int(os.environ.get("SFB_TWO_SHOT_ROWS", "512"))
-    TWO_SHOT_WORLD = int(os.environ.get("SFB_TWO_SHOT_WORLD", "8"))      # measured: 0.94x at 2 ranks, 0.98x at 4 (4,096-row chunks)
+    TWO_SHOT_ROWS = int(os.environ.get("SFB_TWO_SHOT_ROWS", str(_plan.TWO_SHOT_ROWS)))
+    TWO_SHOT_WORLD = int(os.environ.get("SFB_TWO_SHOT_WORLD", str(_plan.TWO_SHOT_WORLD)))      # measured: 0.94x at 2 ranks, 0.98x at 4 (4,096-row chunks)
 
     def _two_shot(self, n: int) -> bool:
         return (self._fused() and n >= self.TWO_SHOT_ROWS and self.world >= self.TWO_SHOT_WORLD

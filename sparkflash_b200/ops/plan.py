@@ -70,18 +70,21 @@ class CollectivePlan:
         return self.bytes_sent_per_rank / link_bytes_per_s
 
 
-TWO_SHOT_ROWS = 64          # reference: SPARKFLASH_TWO_SHOT_ROWS = 16 on RoCE; NVLink's latency moves the crossover up
+# reference: SPARKFLASH_TWO_SHOT_ROWS = 16 on RoCE.  Over NVLink the two extra kernels of the two-shot form cost more than the
+# links save below 8 ranks (32K prefill 0.94x at 2 ranks, 0.98x at 4), so the engine takes it from 512 rows and 8 ranks on
+TWO_SHOT_ROWS = 512
+TWO_SHOT_WORLD = 8
 
 
 def plan_collective(rows: int, d: int, world: int, arm: str = "fused", two_shot_rows: int = TWO_SHOT_ROWS,
-                    bulk_chunks: int = 1) -> CollectivePlan:
+                    bulk_chunks: int = 1, two_shot_world: int = TWO_SHOT_WORLD) -> CollectivePlan:
     if world <= 1:
         return CollectivePlan(CollectiveKind.NONE, 1, rows, d)
     if arm == "nccl":
         return CollectivePlan(CollectiveKind.NCCL, world, rows, d)
     if bulk_chunks > 1:
         return CollectivePlan(CollectiveKind.OVERLAPPED, world, rows, d, chunks_in_flight=min(3, bulk_chunks))
-    if rows <= two_shot_rows:
+    if rows < two_shot_rows or world < two_shot_world:
         return CollectivePlan(CollectiveKind.ONE_SHOT, world, rows, d)
     return CollectivePlan(CollectiveKind.TWO_SHOT, world, rows, d)
 

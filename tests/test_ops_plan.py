@@ -46,6 +46,8 @@ def test_collective_plan_forms_and_bytes():
     a = P.plan_collective(8, d, 8)
     b = P.plan_collective(1024, d, 8)
     assert a.kind is P.CollectiveKind.ONE_SHOT and b.kind is P.CollectiveKind.TWO_SHOT
+    assert P.plan_collective(1024, d, 4).kind is P.CollectiveKind.ONE_SHOT                # below 8 ranks the one-shot push measured faster
+    assert P.plan_collective(1024, d, 4, two_shot_world=4).kind is P.CollectiveKind.TWO_SHOT
     assert a.bytes_sent_per_rank == 8 * d * 2 * 7
     assert b.bytes_sent_per_rank == 2 * 1024 * d * 2 * 7 // 8            # 2 (W-1)/W of the message
     assert P.plan_collective(1024, d, 8, arm="nccl").kind is P.CollectiveKind.NCCL
