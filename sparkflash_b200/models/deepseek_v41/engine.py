@@ -1010,6 +1010,7 @@ class Engine:
     def _draft_gen(self, n: int, S: int = 1):
         cfg, w = self.cfg, self.w
         d = cfg.hidden_size
+        self._step_rows = n
         if self._fused():
             self.comm.begin_step(); self._k()
         N.embed(w.embed, self.tokens, self.h, n, cfg.hc_mult, d, cfg.vocab_size, self.status); self._k()
