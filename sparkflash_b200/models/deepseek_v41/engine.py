@@ -807,7 +807,8 @@ class Engine:
 
     def _two_shot(self, n: int) -> bool:
         return (self._fused() and n >= self.TWO_SHOT_ROWS and self.world >= self.TWO_SHOT_WORLD
-                and 2 * ((n + self.world - 1) // self.world) <= self.max_rows)
+                and 2 * ((n + self.world - 1) // self.world) <= self.max_rows
+                and self.__dict__.get("_two_shot_ok", True))      # the draft forward has no second-shot stage
 
     def _second_shot(self, parts, n: int):
         """Shot 2 of a two-shot exchange started by ``_reduce_parts`` (anything else passes through): fold the rows this rank
@@ -854,6 +855,7 @@ class Engine:
         cfg, w = self.cfg, self.w
         fused = self._fused()
         self._step_rows = n
+        self._two_shot_ok = True
         two_shot = self._two_shot(n)
         if fused:
             self.comm.begin_step(); self._k()
@@ -1011,6 +1013,7 @@ class Engine:
         cfg, w = self.cfg, self.w
         d = cfg.hidden_size
         self._step_rows = n
+        self._two_shot_ok = False
         if self._fused():
             self.comm.begin_step(); self._k()
         N.embed(w.embed, self.tokens, self.h, n, cfg.hc_mult, d, cfg.vocab_size, self.status); self._k()
