@@ -105,6 +105,38 @@ def test_kernel_marks_summary_separates_idle_ctas_and_old_launches():
     assert summarize(torch.zeros(32, dtype=torch.int64)) == {"ctas": 0}
 
 
+def test_mark_summaries_of_the_attention_seam_and_persistent_kernels():
+    """The attention kernel's phase marks, the bulk-copy seam's and the persistent MoE kernels' cycle counters are turned into
+    named durations: synthetic records with known gaps come back as those gaps."""
+    import torch
+    from sparkflash_b200.utils import kernel_marks as KM
+    buf = torch.zeros(16 * 8, dtype=torch.int64)
+    m = buf.view(-1, 16)
+    t0 = 1_000_000
+    order = [0, 1, 2, 3, 4, 5, 6, 8, 12, 9, 10, 7]            # the slots in the order the kernel passes them
+    for cta in range(3):
+        for i, slot in enumerate(order):
+            m[cta, slot] = t0 + cta * 100 + i * 1000           # 1 us between consecutive marks
+        m[cta, 11] = m[cta, 8] + 400
+    a = KM.summarize_attention(buf)
+    assert a["ctas"] == 3 and a["cta_life_us"] == 11.0 and a["kernel_span_us"] == 11.2
+    assert a["first_tile_decoded_us"] == 1.0 and a["epilogue_accumulator_pass_us"] == 1.0 and a["epilogue_rope_quant_pass_us"] == 1.0
+    assert KM.summarize_attention(torch.zeros(32, dtype=torch.int64)) == {"ctas": 0}
+    words = []
+    for row in range(4):
+        words += [5000 + row * 10 + k * 2000 for k in range(7)] + [0]
+    s_ = KM.summarize_seam(words, 4)
+    assert s_["rows"] == 4 and s_["block_life_us"] == 12.0 and s_["fold_us"] == 2.0 and s_["kernel_span_us"] == 12.0
+    pc = torch.zeros(16 * 4, dtype=torch.int64)
+    pv = pc.view(-1, 16)
+    pv[0, :9] = torch.tensor([20, 1000, 50, 300, 900, 600, 360, 980, 420])
+    pv[1, :9] = torch.tensor([22, 1200, 70, 500, 1100, 800, 396, 1180, 620])
+    down = KM.summarize_persistent(pc, "down")
+    assert down["ctas"] == 2 and down["tiles"] == 21.0 and down["mma_wait_scales"] == 400.0 and down["producer_wait_free"] == 520.0
+    gu = KM.summarize_persistent(pc, "gate_up")
+    assert gu["mma_wait_data"] == 400.0 and "ksteps" not in gu
+
+
 def test_roofline_accounting_groups_launches_and_uses_the_measured_peaks(tmp_path):
     from sparkflash_b200.utils import roofline as R
     assert R.classify("umma_gate_up_grouped") == "moe_gate_up" and R.classify("umma_down_grouped") == "moe_down"
