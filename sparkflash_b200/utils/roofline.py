@@ -32,7 +32,7 @@ CLASSES = (
     ("attention", ("attn_",)),
     ("indexer", ("index_", "select_topk", "hsi_")),
     ("sampler", ("sample",)),
-    ("seams", ("seam_", "fold_slots", "push_rows", "tap_mean")),
+    ("seams", ("seam_", "fold_slots", "fold_push", "push_rows", "tap_mean")),
     ("kv", ("qkv_post", "compress_append", "rope_table", "embed")),
     ("dense", ("umma_", "gemv", "splitk", "quant_rows")),
 )
