@@ -1294,13 +1294,15 @@ struct UmmaGateupPersistSmem {
   volatile int fail;
   volatile int ep_ok;
 };
-// warps: 0 TMA producer, 1 / 6 MMA issue (gate / up), 2..5 epilogue, 7 / 8 scale-factor copies (gate / up).  A thread issues
-// one tcgen05 operation per ~80 cycles; with the copies on their own threads an MMA thread issues five per k-step, not seven.
+// warps: 0 TMA producer, 1 / 6 MMA issue (gate / up), 2..5 epilogue, 7 / 8 scale-factor copies (gate / up) when
+// copier_threads is set.  With single-thread roles entered through elect.sync an MMA thread issues its two scale copies and
+// four MMAs per k-step well inside the stage's turn-over, and doing the copies itself saves one hand-over per stage (the
+// shipped choice); the copier threads date from roles entered by lane index, where seven operations per k-step paced the loop.
 constexpr int PG_THREADS = 288;
 
 __global__ void __launch_bounds__(PG_THREADS, 1)
 umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapA2,
-                              const __grid_constant__ CUtensorMap tmapB, UmmaArgs a, int n_tiles, int n_segs, int g_tune_dev_copier) {
+                              const __grid_constant__ CUtensorMap tmapB, UmmaArgs a, int n_tiles, int n_segs, int copier_threads) {
   extern __shared__ uint8_t smem_raw[];
   using Smem = UmmaGateupPersistSmem;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -1392,11 +1394,11 @@ umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const _
         for (int i = 0; i < nks; ++i, ++it) {
           const int s = it % PG_STAGES;
           const long long w1 = SFB_MARKS_ON ? clock64() : 0;
-          if (!mbar_wait(g_tune_dev_copier ? &S.sfready[s][h] : &S.full[s], (it / PG_STAGES) & 1)) { S.fail = 2; ok = false; break; }
+          if (!mbar_wait(copier_threads ? &S.sfready[s][h] : &S.full[s], (it / PG_STAGES) & 1)) { S.fail = 2; ok = false; break; }
           if (SFB_MARKS_ON) c_full += clock64() - w1;
           tc_fence_after();
           const uint32_t sl = (uint32_t)s * 4;
-          if (!g_tune_dev_copier) {      // this thread copies its own operands' scales: one hand-over less per stage
+          if (!copier_threads) {      // this thread copies its own operands' scales: one hand-over less per stage
             tc_cp_sf(t_sa + sl, make_desc(smem_u32(S.sfa[s][h]), 128, 0, 0));
             tc_cp_sf(t_sb + sl, make_desc(smem_u32(S.sfb[s]), 128, 0, 0));
           }
@@ -1421,7 +1423,7 @@ umma_gateup_persistent_kernel(const __grid_constant__ CUtensorMap tmapA, const _
       }
     }
   } else if (warp == 7 || warp == 8) {
-    if (g_tune_dev_copier && elect_one()) {
+    if (copier_threads && elect_one()) {
       const int h = warp == 7 ? 0 : 1;
       const uint32_t t_sa = h ? t_sfu : t_sfg, t_sb = h ? t_sfb2 : t_sfb;
       uint32_t it = 0;
